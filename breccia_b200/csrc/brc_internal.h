@@ -1,0 +1,83 @@
+// Internal definitions shared by the translation units of libbreccia_kv.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+#include <vector>
+
+#include "breccia_kv.h"
+
+// Bits of the device-side check word (brc_pool::status_dev).
+#define BRC_DEV_BAD_PAGE 1u    // block-table entry >= n_pages
+#define BRC_DEV_BAD_POS 2u     // position past the caller's bound
+#define BRC_DEV_WAIT_LIMIT 4u  // a bounded mbarrier wait gave up
+#define BRC_DEV_BAD_SHAPE 8u   // more work units than a kernel's table holds
+
+// Stage ids of the optional GPU timers are public (breccia_kv.h); this is their count.
+#define BRC_STAGE_COUNT 6
+
+struct brc_pool {
+    int32_t device = -1;
+    uint32_t n_layers = 0, n_kv_head = 0, head_dim = 0, page_tokens = 0, n_pages = 0;
+    uint64_t half_page_bytes = 0;   // K (or V) bytes of one page of one layer
+    uint64_t layer_bytes = 0;       // K (or V) bytes of one layer
+    uint8_t *k_base = nullptr;      // [n_layers][n_pages][n_kv][page_tokens][head_dim] f16
+    uint8_t *v_base = nullptr;
+    uint32_t *status_dev = nullptr; // device check word
+    uint32_t *status_host = nullptr;  // pinned mirror
+    uint32_t *ids_dev = nullptr;    // small staging for host-provided id lists
+    uint32_t ids_cap = 0;
+    int sm_count = 0;
+    // TMA views of the whole K / V allocation: 2-D [rows][head_dim] f16, box
+    // [page_tokens rows][64 columns], 128-byte swizzle.
+    alignas(64) CUtensorMap tm_k;
+    alignas(64) CUtensorMap tm_v;
+    bool has_tma = false;
+
+    // per-stage GPU timers (off unless brc_timing_enable)
+    bool timing = false;
+    struct stage_events {
+        std::vector<cudaEvent_t> begin, end;  // recorded pairs since the last read
+        std::vector<cudaEvent_t> spare;       // reusable events
+    } stages[BRC_STAGE_COUNT];
+
+    // allocator
+    mutable std::mutex mu;
+    std::vector<uint32_t> refcount;
+    std::vector<uint32_t> free_list;  // LIFO
+};
+
+void brc_set_error(const char *fmt, ...) __attribute__((format(printf, 1, 2)));
+brc_status brc_fail(brc_status code, const char *fmt, ...) __attribute__((format(printf, 2, 3)));
+
+#define BRC_CUDA(expr)                                                                           \
+    do {                                                                                         \
+        cudaError_t _e = (expr);                                                                 \
+        if (_e != cudaSuccess)                                                                   \
+            return brc_fail(BRC_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), \
+                            __FILE__, __LINE__);                                                 \
+    } while (0)
+
+// RAII: make the pool's device current for the duration of a call, restore after.
+struct brc_device_guard {
+    int prev = -1;
+    bool ok = true;
+    explicit brc_device_guard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; prev = -1; }
+        if (ok && prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+    }
+    ~brc_device_guard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+// Record a begin/end event pair around a launch when timing is on (no-ops otherwise).
+void brc_stage_begin(brc_pool *pool, int stage, cudaStream_t s);
+void brc_stage_end(brc_pool *pool, int stage, cudaStream_t s);
+
+static inline cudaStream_t brc_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }

@@ -1,0 +1,774 @@
+// Paged GQA decode attention for sm_100a: split-KV partial kernel + log-sum-exp combine.
+//
+// Replaces, for a batch of sequences at T = 1, the reference's four dispatches
+// scores -> softmax -> split-K apply -> reduce (crates/breccia-kernels/src/qsa/mod.rs:1439-1461,
+// 1491-1521; shaders qsa_attn_scores_small.comp, ops_softmax.comp, qsa_attn_apply_split.comp,
+// qsa_attn_apply_reduce.comp).  The reference materialises the score matrix in memory and re-reads V
+// once per query head; here every cached byte is read from HBM exactly once per step:
+//
+//   * work unit = (sequence, kv head); its pages form one flat list of "page-units" over the whole
+//     batch, cut into equal contiguous shares, one per CTA (one CTA per SM), so every SM streams the
+//     same number of 16 KiB page tiles whatever the length distribution;
+//   * a producer warp walks the block table and issues TMA tiled loads (128-byte swizzle) of the K and
+//     V tile of each page into a shared-memory ring guarded by full/empty mbarriers;
+//   * four consumer warps take pages round-robin.  Per page: S^T[16 cells x 8 heads] = K . Q^T with
+//     mma.sync m16n8k16 (K fragments by ldmatrix from the swizzled tile, Q^T fragments resident in
+//     registers), online softmax in base 2 with warp shuffles across the cell dimension, the
+//     probabilities transposed in registers by movmatrix into the B operand, and
+//     O^T[head_dim x 8 heads] += V^T . P^T with V^T fragments from ldmatrix.trans.  P is split into a
+//     binary16 head and tail so the product carries ~22 significant bits;
+//   * at the end of a unit's share the warps merge (m, l, O) through shared memory and write one
+//     partial; the combine kernel merges the partials of a unit, normalises and applies the gate.
+//
+// HBM-bound by design: 8 FLOP per cached byte, all of it on the tensor pipe.
+#include <algorithm>
+
+#include "brc_device.cuh"
+#include "brc_internal.h"
+
+namespace {
+
+constexpr int NW = 4;                      // consumer warps
+constexpr int NTHREADS = (NW + 1) * 32;    // + one producer warp
+constexpr int MAX_UNITS = 2048;            // (sequence, kv head) units per launch
+constexpr int GROUP_TILE = 8;              // query heads per kv head held by one n-tile
+constexpr uint32_t SMEM_LIMIT = 232448;    // 227 KiB opt-in maximum per CTA
+constexpr uint64_t WAIT_NS = 4000000000ull;
+
+template <int HD>
+struct Cfg {
+    static constexpr int KSTEPS = HD / 16;
+    static constexpr int MT = HD / 16;
+    static constexpr int BOXES = HD / 64;
+    static constexpr int TILE_BYTES = 16 * HD * 2;
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    static constexpr int OPAD = HD + 4;                          // padded row of the merge scratch
+    static constexpr int SCRATCH_WARP = GROUP_TILE * OPAD + 16;  // floats per warp
+    static constexpr int SCRATCH_BYTES = NW * SCRATCH_WARP * 4;
+    static constexpr int PREFIX_BYTES = (MAX_UNITS + 4) * 4;
+    static constexpr int BAR_BYTES = 1024;
+    static constexpr int FIXED_BYTES = SCRATCH_BYTES + PREFIX_BYTES + BAR_BYTES + 1024 /*alignment slack*/;
+};
+
+struct DecodeParams {
+    const void *q;                 // [n_seqs][n_head][HD]
+    const uint32_t *block_tables;  // [n_seqs][table_stride]
+    const uint32_t *seq_lens;      // [n_seqs]
+    float *part_acc;               // [slots][GROUP_TILE][HD]
+    float *part_ml;                // [slots][GROUP_TILE][2]
+    uint32_t *status;
+    uint32_t n_seqs, table_stride, max_seq_len;
+    uint32_t n_kv_head, group, n_head;
+    uint32_t n_pages;    // pages per layer
+    uint32_t layer_row0; // first row of this layer in the TMA view
+    uint32_t n_stages;
+    float scale_log2;    // scale * log2(e)
+};
+
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait on an mbarrier phase: gives up after WAIT_NS of wall time (or 2^30 polls).
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity) {
+    if (brc::mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t i = 0; i < (1u << 30); ++i) {
+        if (brc::mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 63u && globaltimer_ns() - t0 > WAIT_NS) return false;
+    }
+    return false;
+}
+
+__device__ __forceinline__ uint32_t pages_of(uint32_t len) { return (len + 15u) >> 4; }
+
+// Largest u in [0, n_units) with S[u] <= g  (S ascending, S[0] = 0).
+__device__ __forceinline__ uint32_t unit_of(const uint32_t *S, uint32_t n_units, uint32_t g) {
+    uint32_t lo = 0, hi = n_units;
+    while (hi - lo > 1) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (S[mid] <= g) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+__device__ __forceinline__ uint32_t share_begin(uint32_t cta, uint32_t total, uint32_t n_cta) {
+    return (uint32_t)(((uint64_t)cta * total) / n_cta);
+}
+
+template <int HD, bool Q_F32>
+__global__ void __launch_bounds__(NTHREADS, 1)
+    decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                          const DecodeParams p) {
+    using C = Cfg<HD>;
+    extern __shared__ uint8_t smem_raw[];
+    // The 128-byte swizzle pattern repeats every 1024 bytes: tiles must start on that boundary.
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
+    uint8_t *ring = smem;
+    float *scratch = reinterpret_cast<float *>(ring + (size_t)p.n_stages * C::STAGE_BYTES);
+    uint32_t *S = reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(scratch) + C::SCRATCH_BYTES);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(S) + C::PREFIX_BYTES);
+    const uint32_t full0 = brc::smem_u32(bars);
+    const uint32_t empty0 = full0 + 8u * p.n_stages;
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t n_units = p.n_seqs * p.n_kv_head;
+
+    if (tid == 0) {
+        for (uint32_t i = 0; i < p.n_stages; ++i) {
+            brc::mbar_init(full0 + 8u * i, 1);
+            brc::mbar_init(empty0 + 8u * i, 1);
+        }
+        brc::mbar_fence_init();
+        brc::tma_prefetch_desc(&tm_k);
+        brc::tma_prefetch_desc(&tm_v);
+    }
+    // Exclusive prefix of pages per unit, S[0..n_units]; every CTA computes it (n_units <= 2048).
+    if (warp == 0) {
+        uint32_t run = 0;
+        for (uint32_t base = 0; base < n_units; base += 32) {
+            const uint32_t u = base + lane;
+            uint32_t pg = 0;
+            if (u < n_units) {
+                uint32_t len = p.seq_lens[u / p.n_kv_head];
+                if (len > p.max_seq_len) {
+                    atomicOr(p.status, BRC_DEV_BAD_POS);
+                    p.status[1] = len;
+                    len = p.max_seq_len;
+                }
+                pg = pages_of(len);
+            }
+            uint32_t inc = pg;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t v = __shfl_up_sync(0xffffffffu, inc, o);
+                if ((int)lane >= o) inc += v;
+            }
+            if (u < n_units) S[u] = run + inc - pg;
+            run += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (lane == 0) S[n_units] = run;
+    }
+    __syncthreads();
+
+    const uint32_t total = S[n_units];
+    const uint32_t a = share_begin(blockIdx.x, total, gridDim.x);
+    const uint32_t b = share_begin(blockIdx.x + 1, total, gridDim.x);
+    if (a >= b) return;
+    const uint32_t count = b - a;
+
+    if (warp == NW) {
+        // ------------------------------------------------------------------ producer warp
+        const uint64_t policy = brc::l2_policy_evict_first();
+        uint32_t dead = 0;
+        uint32_t issued = 0;
+        for (uint32_t k0 = 0; k0 < count && !dead; k0 += 32) {
+            const uint32_t k = k0 + lane;
+            uint32_t row = 0;
+            if (k < count) {
+                const uint32_t g = a + k;
+                const uint32_t u = unit_of(S, n_units, g);
+                const uint32_t s = u / p.n_kv_head, kvh = u % p.n_kv_head;
+                uint32_t page = __ldg(p.block_tables + (uint64_t)s * p.table_stride + (g - S[u]));
+                if (page >= p.n_pages) {
+                    atomicOr(p.status, BRC_DEV_BAD_PAGE);
+                    p.status[1] = page;
+                    page = 0;  // stay inside the pool; the result of this unit is void and the call reports it
+                }
+                row = p.layer_row0 + (page * p.n_kv_head + kvh) * 16u;
+            }
+            const uint32_t n_here = min(32u, count - k0);
+            for (uint32_t i = 0; i < n_here; ++i) {
+                const uint32_t r = __shfl_sync(0xffffffffu, row, i);
+                if (lane == 0) {
+                    const uint32_t kk = k0 + i;
+                    const uint32_t stage = kk % p.n_stages;
+                    const uint32_t round = kk / p.n_stages;
+                    if (!wait_bounded(empty0 + 8u * stage, (round & 1u) ^ 1u)) {
+                        dead = 1;
+                    } else {
+                        const uint32_t fb = full0 + 8u * stage;
+                        brc::mbar_arrive_expect_tx(fb, C::STAGE_BYTES);
+                        const uint32_t dst = brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES);
+#pragma unroll
+                        for (int bx = 0; bx < C::BOXES; ++bx) {
+                            brc::tma_load_2d(dst + bx * 2048, &tm_k, bx * 64, (int32_t)r, fb, policy);
+                            brc::tma_load_2d(dst + C::TILE_BYTES + bx * 2048, &tm_v, bx * 64, (int32_t)r, fb, policy);
+                        }
+                        issued = kk + 1;
+                    }
+                }
+                dead = __shfl_sync(0xffffffffu, dead, 0);
+                if (dead) break;
+            }
+        }
+        if (dead && lane == 0) {
+            atomicOr(p.status, BRC_DEV_WAIT_LIMIT);
+            p.status[1] = 1000000u + blockIdx.x;
+            // Let the copies already in flight land before this CTA's shared memory is released.
+            const uint32_t first = issued > p.n_stages ? issued - p.n_stages : 0;
+            for (uint32_t kk = first; kk < issued; ++kk)
+                wait_bounded(full0 + 8u * (kk % p.n_stages), (kk / p.n_stages) & 1u);
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------------- consumer warps
+    const uint32_t t0 = lane >> 2;            // cell row of c0/c1 (c2/c3: +8); also the head of the B operand
+    const uint32_t h0 = (lane & 3u) * 2u;     // head column of c0/c2 (c1/c3: +1)
+    // ldmatrix lane constants (see the swizzle note in the file header).
+    const uint32_t k_r = (lane & 7u) + ((lane >> 3) & 1u) * 8u;
+    const uint32_t k_x = (lane >> 4) ^ (k_r & 7u);
+    const uint32_t k_lane = k_r * 128u;
+    const uint32_t v_r = (lane & 7u) + (lane >> 4) * 8u;
+    const uint32_t v_x = ((lane >> 3) & 1u) ^ (v_r & 7u);
+    const uint32_t v_lane = v_r * 128u;
+
+    uint32_t kw = warp;                        // next local page index of this warp
+    uint32_t stage = warp % p.n_stages, parity = 0;
+    uint32_t dead = 0;
+
+    uint32_t u = unit_of(S, n_units, a);
+    uint32_t g0 = a;
+    while (g0 < b) {
+        const uint32_t ge = min(b, S[u + 1]);
+        const uint32_t s = u / p.n_kv_head, kvh = u % p.n_kv_head;
+        const uint32_t len = min(p.seq_lens[s], p.max_seq_len);
+        const uint32_t unit_first = S[u];
+
+        // Q^T fragments (B operand, k = d, n = head): b0 = Q[head t0][16 ks + 2 (lane & 3) + {0,1}],
+        // b1 = same + 8.  Heads past the group read as zero.
+        uint32_t qh[C::KSTEPS][2];
+        uint32_t ql[Q_F32 ? C::KSTEPS : 1][2];
+        {
+            const bool live = t0 < p.group;
+            const uint64_t qoff = ((uint64_t)s * p.n_head + kvh * p.group + t0) * HD + (lane & 3u) * 2u;
+#pragma unroll
+            for (int ks = 0; ks < C::KSTEPS; ++ks) {
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    if (Q_F32) {
+                        float2 x = make_float2(0.f, 0.f);
+                        if (live) x = __ldg(reinterpret_cast<const float2 *>(static_cast<const float *>(p.q) + qoff + ks * 16 + half * 8));
+                        const __half2 hi = __floats2half2_rn(x.x, x.y);
+                        const float2 hf = __half22float2(hi);
+                        qh[ks][half] = *reinterpret_cast<const uint32_t *>(&hi);
+                        ql[Q_F32 ? ks : 0][half] = brc::pack_half2(x.x - hf.x, x.y - hf.y);
+                    } else {
+                        qh[ks][half] = live ? __ldg(reinterpret_cast<const uint32_t *>(static_cast<const uint16_t *>(p.q) + qoff + ks * 16 + half * 8)) : 0u;
+                    }
+                }
+            }
+        }
+
+        float o[C::MT][4];
+#pragma unroll
+        for (int mt = 0; mt < C::MT; ++mt) o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f;
+        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+        const uint32_t local_end = ge - a;
+        for (; kw < local_end; kw += NW) {
+            if (!dead) {
+                if (!wait_bounded(full0 + 8u * stage, parity)) {
+                    dead = 1;
+                    if (lane == 0) {
+                        atomicOr(p.status, BRC_DEV_WAIT_LIMIT);
+                        p.status[1] = 2000000u + blockIdx.x;
+                    }
+                }
+            }
+            if (!dead) {
+                const uint32_t page_in_unit = a + kw - unit_first;
+                const uint32_t nv = min(16u, len - page_in_unit * 16u);  // live cells in this page (>= 1)
+                const uint32_t kbase = brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES);
+                const uint32_t vbase = kbase + C::TILE_BYTES;
+
+                if (nv < 16u) {
+                    // Cells past the sequence end may hold anything (NaN included); their scores are
+                    // masked below, and their V rows are cleared so 0 * NaN never reaches the sum.
+                    for (uint32_t i = lane; i < (16u - nv) * 8u * C::BOXES; i += 32) {
+                        const uint32_t row = nv + i / (8u * C::BOXES);
+                        const uint32_t within = i % (8u * C::BOXES);
+                        const uint32_t addr = vbase + (within >> 3) * 2048u + row * 128u + (within & 7u) * 16u;
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(addr), "r"(0u) : "memory");
+                    }
+                    __syncwarp();
+                }
+
+                // ---- S^T = K . Q^T   (two accumulators to halve the dependent mma chain)
+                float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int ks = 0; ks < C::KSTEPS; ++ks) {
+                    uint32_t af[4];
+                    brc::ldmatrix_x4(af, kbase + (ks >> 2) * 2048u + k_lane + ((k_x ^ ((ks & 3) * 2u)) << 4));
+                    if (ks & 1) {
+                        brc::mma_16816(sb, af, qh[ks][0], qh[ks][1]);
+                        if (Q_F32) brc::mma_16816(sb, af, ql[Q_F32 ? ks : 0][0], ql[Q_F32 ? ks : 0][1]);
+                    } else {
+                        brc::mma_16816(sa, af, qh[ks][0], qh[ks][1]);
+                        if (Q_F32) brc::mma_16816(sa, af, ql[Q_F32 ? ks : 0][0], ql[Q_F32 ? ks : 0][1]);
+                    }
+                }
+                float sc[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) sc[i] = (sa[i] + sb[i]) * p.scale_log2;
+                if (nv < 16u) {
+                    if (t0 >= nv) sc[0] = sc[1] = -INFINITY;
+                    if (t0 + 8u >= nv) sc[2] = sc[3] = -INFINITY;
+                }
+                // ---- online softmax over the 16 cells (rows: lanes with equal lane & 3 share heads)
+                float x0 = fmaxf(sc[0], sc[2]), x1 = fmaxf(sc[1], sc[3]);
+#pragma unroll
+                for (int off = 4; off < 32; off <<= 1) {
+                    x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, off));
+                    x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, off));
+                }
+                const float n0 = fmaxf(m0, x0), n1 = fmaxf(m1, x1);
+                const float al0 = brc::fast_exp2(m0 - n0), al1 = brc::fast_exp2(m1 - n1);
+                m0 = n0;
+                m1 = n1;
+                const float p0 = brc::fast_exp2(sc[0] - n0), p1 = brc::fast_exp2(sc[1] - n1);
+                const float p2 = brc::fast_exp2(sc[2] - n0), p3 = brc::fast_exp2(sc[3] - n1);
+                l0 = l0 * al0 + (p0 + p2);
+                l1 = l1 * al1 + (p1 + p3);
+                if (__any_sync(0xffffffffu, (al0 != 1.f) | (al1 != 1.f))) {
+#pragma unroll
+                    for (int mt = 0; mt < C::MT; ++mt) {
+                        o[mt][0] *= al0;
+                        o[mt][1] *= al1;
+                        o[mt][2] *= al0;
+                        o[mt][3] *= al1;
+                    }
+                }
+                // ---- P^T as the B operand: binary16 head + tail, transposed in registers
+                const __half2 ph01 = __floats2half2_rn(p0, p1), ph23 = __floats2half2_rn(p2, p3);
+                const float2 f01 = __half22float2(ph01), f23 = __half22float2(ph23);
+                const uint32_t bh0 = brc::movmatrix_trans(*reinterpret_cast<const uint32_t *>(&ph01));
+                const uint32_t bh1 = brc::movmatrix_trans(*reinterpret_cast<const uint32_t *>(&ph23));
+                const uint32_t bl0 = brc::movmatrix_trans(brc::pack_half2(p0 - f01.x, p1 - f01.y));
+                const uint32_t bl1 = brc::movmatrix_trans(brc::pack_half2(p2 - f23.x, p3 - f23.y));
+                // ---- O^T += V^T . P^T
+#pragma unroll
+                for (int mt = 0; mt < C::MT; ++mt) {
+                    uint32_t af[4];
+                    brc::ldmatrix_x4_trans(af, vbase + (mt >> 2) * 2048u + v_lane + ((v_x ^ ((mt & 3) * 2u)) << 4));
+                    brc::mma_16816(o[mt], af, bh0, bh1);
+                    brc::mma_16816(o[mt], af, bl0, bl1);
+                }
+                // ---- hand the stage back to the producer
+                if (nv < 16u) brc::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) brc::mbar_arrive(empty0 + 8u * stage);
+            }
+            stage += NW;
+            if (stage >= p.n_stages) {
+                stage -= p.n_stages;
+                parity ^= 1u;
+            }
+        }
+
+        // ---- merge the four warps' (m, l, O) and write this share's partial for the unit
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+        }
+        float *sw = scratch + warp * C::SCRATCH_WARP;
+#pragma unroll
+        for (int mt = 0; mt < C::MT; ++mt) {
+            const uint32_t d0 = mt * 16 + t0;
+            sw[h0 * C::OPAD + d0] = o[mt][0];
+            sw[(h0 + 1) * C::OPAD + d0] = o[mt][1];
+            sw[h0 * C::OPAD + d0 + 8] = o[mt][2];
+            sw[(h0 + 1) * C::OPAD + d0 + 8] = o[mt][3];
+        }
+        if (lane < 4) {
+            float *ml = sw + GROUP_TILE * C::OPAD;
+            ml[h0 * 2] = m0;
+            ml[h0 * 2 + 1] = l0;
+            ml[h0 * 2 + 2] = m1;
+            ml[h0 * 2 + 3] = l1;
+        }
+        brc::named_bar_sync(1, NW * 32);
+        {
+            const uint32_t slot = u + blockIdx.x;
+            float *acc_out = p.part_acc + (size_t)slot * GROUP_TILE * HD;
+            float *ml_out = p.part_ml + (size_t)slot * GROUP_TILE * 2;
+            for (uint32_t h = 0; h < p.group; ++h) {
+                float mw[NW], lw[NW], M = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < NW; ++w) {
+                    const float *ml = scratch + w * C::SCRATCH_WARP + GROUP_TILE * C::OPAD;
+                    mw[w] = ml[h * 2];
+                    lw[w] = ml[h * 2 + 1];
+                    if (lw[w] > 0.f) M = fmaxf(M, mw[w]);
+                }
+                float L = 0.f, wt[NW];
+#pragma unroll
+                for (int w = 0; w < NW; ++w) {
+                    wt[w] = lw[w] > 0.f ? brc::fast_exp2(mw[w] - M) : 0.f;
+                    L += wt[w] * lw[w];
+                }
+                for (uint32_t d = tid; d < HD; d += NW * 32) {
+                    float v = 0.f;
+#pragma unroll
+                    for (int w = 0; w < NW; ++w)
+                        if (wt[w] != 0.f) v += wt[w] * scratch[w * C::SCRATCH_WARP + h * C::OPAD + d];
+                    acc_out[h * HD + d] = dead ? 0.f : v;
+                }
+                if (tid == 0) {
+                    ml_out[h * 2] = M;
+                    ml_out[h * 2 + 1] = dead ? 0.f : L;
+                }
+            }
+        }
+        brc::named_bar_sync(1, NW * 32);
+
+        g0 = ge;
+        ++u;
+        while (u < n_units && S[u + 1] == S[u]) ++u;  // units without pages have no share
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// combine: merge the partials of each (sequence, head), normalise, gate
+// ---------------------------------------------------------------------------------------------
+struct CombineParams {
+    const float *part_acc;
+    const float *part_ml;
+    const uint32_t *seq_lens;
+    const float *gate;    // nullable
+    float *out;           // final: [n_seqs][n_head][HD];  partial mode: acc [n_seqs][n_head][HD]
+    float *out_ml;        // partial mode: [n_seqs][n_head][2], else nullptr
+    uint32_t n_seqs, n_kv_head, group, n_head, max_seq_len;
+    uint32_t gate_head_stride;
+    uint32_t n_cta;       // grid size of the partial kernel
+};
+
+__device__ __forceinline__ float sigmoid_f32(float x) {
+    if (x >= 0.f) return 1.f / (1.f + expf(-x));
+    const float e = expf(x);
+    return e / (1.f + e);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(HD) decode_combine_kernel(const CombineParams p) {
+    __shared__ uint32_t red[2][HD / 32];
+    const uint32_t s = blockIdx.x / p.n_head, h = blockIdx.x % p.n_head;
+    const uint32_t kvh = h / p.group, hl = h % p.group;
+    const uint32_t u = s * p.n_kv_head + kvh;
+    const uint32_t n_units = p.n_seqs * p.n_kv_head;
+    const uint32_t tid = threadIdx.x;
+
+    // pages before this unit and in total
+    uint32_t before = 0, total = 0;
+    for (uint32_t i = tid; i < n_units; i += HD) {
+        const uint32_t pg = pages_of(min(p.seq_lens[i / p.n_kv_head], p.max_seq_len));
+        total += pg;
+        if (i < u) before += pg;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        before += __shfl_xor_sync(0xffffffffu, before, off);
+        total += __shfl_xor_sync(0xffffffffu, total, off);
+    }
+    if ((tid & 31) == 0) {
+        red[0][tid >> 5] = before;
+        red[1][tid >> 5] = total;
+    }
+    __syncthreads();
+    before = 0;
+    total = 0;
+#pragma unroll
+    for (int w = 0; w < HD / 32; ++w) {
+        before += red[0][w];
+        total += red[1][w];
+    }
+    const uint32_t mine = pages_of(min(p.seq_lens[s], p.max_seq_len));
+
+    float acc = 0.f, M = -INFINITY, L = 0.f;
+    if (mine > 0) {
+        // CTAs of the partial kernel whose share [begin(i), begin(i+1)) meets [before, before + mine)
+        const uint32_t first_g = before, last_g = before + mine - 1;
+        uint32_t i_lo = (uint32_t)(((uint64_t)first_g * p.n_cta) / total);
+        while (i_lo + 1 < p.n_cta && share_begin(i_lo + 1, total, p.n_cta) <= first_g) ++i_lo;
+        while (i_lo > 0 && share_begin(i_lo, total, p.n_cta) > first_g) --i_lo;
+        uint32_t i_hi = (uint32_t)(((uint64_t)last_g * p.n_cta) / total);
+        while (i_hi + 1 < p.n_cta && share_begin(i_hi + 1, total, p.n_cta) <= last_g) ++i_hi;
+        while (i_hi > 0 && share_begin(i_hi, total, p.n_cta) > last_g) --i_hi;
+
+        // A CTA whose share is empty (fewer page-units than CTAs) wrote no partial: skip its slot.
+        for (uint32_t i = i_lo; i <= i_hi; ++i) {
+            if (share_begin(i, total, p.n_cta) == share_begin(i + 1, total, p.n_cta)) continue;
+            const float *ml = p.part_ml + ((size_t)(u + i) * GROUP_TILE + hl) * 2;
+            if (ml[1] > 0.f) M = fmaxf(M, ml[0]);
+        }
+        for (uint32_t i = i_lo; i <= i_hi; ++i) {
+            if (share_begin(i, total, p.n_cta) == share_begin(i + 1, total, p.n_cta)) continue;
+            const size_t slot = u + i;
+            const float *ml = p.part_ml + (slot * GROUP_TILE + hl) * 2;
+            const float l = ml[1];
+            if (!(l > 0.f)) continue;
+            const float w = exp2f(ml[0] - M);
+            L += w * l;
+            acc += w * p.part_acc[(slot * GROUP_TILE + hl) * HD + tid];
+        }
+    }
+    const size_t o = ((size_t)s * p.n_head + h) * HD + tid;
+    if (p.out_ml) {
+        p.out[o] = acc;
+        if (tid == 0) {
+            p.out_ml[((size_t)s * p.n_head + h) * 2] = M;
+            p.out_ml[((size_t)s * p.n_head + h) * 2 + 1] = L;
+        }
+    } else {
+        float r = L > 0.f ? acc / L : 0.f;
+        if (p.gate) r *= sigmoid_f32(p.gate[((size_t)s * p.n_head + h) * p.gate_head_stride + tid]);
+        p.out[o] = r;
+    }
+}
+
+// Merge n_parts exchanged partial buffers (acc block followed by (m, l) block each).
+template <int HD>
+__global__ void __launch_bounds__(HD)
+    parts_combine_kernel(const uint8_t *parts, uint32_t n_parts, uint64_t part_stride, uint32_t n_rows /* n_seqs*n_head */,
+                         const float *gate, uint32_t gate_head_stride, float *out) {
+    const uint32_t row = blockIdx.x, tid = threadIdx.x;
+    float M = -INFINITY;
+    for (uint32_t r = 0; r < n_parts; ++r) {
+        const float *ml = reinterpret_cast<const float *>(parts + r * part_stride + (size_t)n_rows * HD * 4) + (size_t)row * 2;
+        if (ml[1] > 0.f) M = fmaxf(M, ml[0]);
+    }
+    float acc = 0.f, L = 0.f;
+    for (uint32_t r = 0; r < n_parts; ++r) {
+        const float *base = reinterpret_cast<const float *>(parts + r * part_stride);
+        const float *ml = base + (size_t)n_rows * HD + (size_t)row * 2;
+        const float l = ml[1];
+        if (!(l > 0.f)) continue;
+        const float w = exp2f(ml[0] - M);
+        L += w * l;
+        acc += w * base[(size_t)row * HD + tid];
+    }
+    float v = L > 0.f ? acc / L : 0.f;
+    if (gate) v *= sigmoid_f32(gate[(size_t)row * gate_head_stride + tid]);
+    out[(size_t)row * HD + tid] = v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+uint32_t stages_for(uint32_t head_dim) {
+    const uint32_t stage = head_dim == 256 ? Cfg<256>::STAGE_BYTES : Cfg<128>::STAGE_BYTES;
+    const uint32_t fixed = head_dim == 256 ? Cfg<256>::FIXED_BYTES : Cfg<128>::FIXED_BYTES;
+    return std::min<uint32_t>((SMEM_LIMIT - fixed) / stage, 24u);
+}
+
+uint32_t smem_for(uint32_t head_dim, uint32_t n_stages) {
+    const uint32_t stage = head_dim == 256 ? Cfg<256>::STAGE_BYTES : Cfg<128>::STAGE_BYTES;
+    const uint32_t fixed = head_dim == 256 ? Cfg<256>::FIXED_BYTES : Cfg<128>::FIXED_BYTES;
+    return n_stages * stage + fixed;
+}
+
+uint32_t seqs_per_launch(const brc_pool *pool) { return MAX_UNITS / pool->n_kv_head; }
+
+uint32_t grid_ctas(const brc_pool *pool) { return (uint32_t)(pool->sm_count > 0 ? pool->sm_count : 148); }
+
+// Workspace: partial slots for one launch (units + CTAs), acc then (m, l).
+uint64_t slots_for(const brc_pool *pool, uint32_t n_seqs) {
+    const uint32_t per = std::min<uint32_t>(n_seqs, seqs_per_launch(pool));
+    return (uint64_t)per * pool->n_kv_head + grid_ctas(pool);
+}
+
+template <int HD, bool Q_F32>
+brc_status launch_partial(brc_pool *pool, const DecodeParams &p, uint32_t grid, uint32_t smem, cudaStream_t st) {
+    static bool configured[64] = {};
+    auto kern = decode_partial_kernel<HD, Q_F32>;
+    if (pool->device < 64 && !configured[pool->device]) {
+        BRC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT));
+        configured[pool->device] = true;
+    }
+    brc_stage_begin(pool, BRC_STAGE_ATTN_PARTIAL, st);
+    kern<<<grid, NTHREADS, smem, st>>>(pool->tm_k, pool->tm_v, p);
+    brc_stage_end(pool, BRC_STAGE_ATTN_PARTIAL, st);
+    BRC_CUDA(cudaGetLastError());
+    return BRC_OK;
+}
+
+brc_status validate_decode(const brc_pool *pool, const char *who, uint32_t layer, const void *q, int32_t q_dtype,
+                           uint32_t n_head, const uint32_t *bt, uint32_t table_stride, const uint32_t *lens,
+                           uint32_t n_seqs, uint32_t max_seq_len, const void *out, const void *ws, uint64_t ws_bytes) {
+    if (!pool) return brc_fail(BRC_ERR_INVALID, "%s: pool is NULL", who);
+    if (pool->device < 0 || !pool->has_tma)
+        return brc_fail(BRC_ERR_CUDA, "%s: this pool holds bookkeeping only (no device memory); compute calls need a GPU pool", who);
+    if (layer >= pool->n_layers) return brc_fail(BRC_ERR_INVALID, "%s: layer %u but the pool has %u", who, layer, pool->n_layers);
+    if (!q || !bt || !lens || !out) return brc_fail(BRC_ERR_INVALID, "%s: NULL query, block table, length or output pointer", who);
+    if (q_dtype != BRC_DTYPE_F32 && q_dtype != BRC_DTYPE_F16)
+        return brc_fail(BRC_ERR_INVALID, "%s: q_dtype %d is neither f32 (0) nor f16 (1)", who, q_dtype);
+    if (n_head == 0 || n_head % pool->n_kv_head != 0)
+        return brc_fail(BRC_ERR_INVALID, "%s: %u query heads do not divide over %u kv heads", who, n_head, pool->n_kv_head);
+    if (n_head / pool->n_kv_head > GROUP_TILE)
+        return brc_fail(BRC_ERR_UNSUPPORTED, "%s: %u query heads per kv head (kernels hold up to %d)", who,
+                        n_head / pool->n_kv_head, GROUP_TILE);
+    const uint64_t capacity = (uint64_t)table_stride * pool->page_tokens;
+    if (max_seq_len > capacity)
+        return brc_fail(BRC_ERR_CAPACITY, "%s would read cells up to %u but each block table holds %llu (%u pages of %u cells)",
+                        who, max_seq_len, (unsigned long long)capacity, table_stride, pool->page_tokens);
+    if ((reinterpret_cast<uintptr_t>(q) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u))
+        return brc_fail(BRC_ERR_INVALID, "%s: query and output pointers must be 16-byte aligned", who);
+    if (n_seqs) {
+        uint64_t need = 0;
+        brc_decode_workspace_bytes(pool, n_seqs, n_head, &need);
+        if (!ws || ws_bytes < need)
+            return brc_fail(BRC_ERR_INVALID, "%s: workspace of %llu bytes, %llu needed", who, (unsigned long long)ws_bytes,
+                            (unsigned long long)need);
+    }
+    return BRC_OK;
+}
+
+// mode_partial: out = merged acc, out_ml = (m, l); else final output.
+brc_status run_decode(brc_pool *pool, uint32_t layer, const void *q, int32_t q_dtype, uint32_t n_head, const float *gate,
+                      uint32_t gate_head_stride, const uint32_t *bt, uint32_t table_stride, const uint32_t *lens,
+                      uint32_t n_seqs, uint32_t max_seq_len, float scale, float *out, float *out_ml, void *ws,
+                      cudaStream_t st) {
+    brc_device_guard guard(pool->device);
+    const uint32_t hd = pool->head_dim;
+    const uint32_t n_stages = stages_for(hd);
+    const uint32_t smem = smem_for(hd, n_stages);
+    const uint32_t grid = grid_ctas(pool);
+    const uint32_t per = seqs_per_launch(pool);
+    const uint64_t slots = slots_for(pool, n_seqs);
+    float *part_acc = static_cast<float *>(ws);
+    float *part_ml = part_acc + slots * GROUP_TILE * hd;
+    const size_t q_elem = q_dtype == BRC_DTYPE_F32 ? 4 : 2;
+    for (uint32_t s0 = 0; s0 < n_seqs; s0 += per) {
+        const uint32_t ns = std::min(per, n_seqs - s0);
+        DecodeParams p;
+        p.q = static_cast<const uint8_t *>(q) + (size_t)s0 * n_head * hd * q_elem;
+        p.block_tables = bt + (size_t)s0 * table_stride;
+        p.seq_lens = lens + s0;
+        p.part_acc = part_acc;
+        p.part_ml = part_ml;
+        p.status = pool->status_dev;
+        p.n_seqs = ns;
+        p.table_stride = table_stride;
+        p.max_seq_len = max_seq_len;
+        p.n_kv_head = pool->n_kv_head;
+        p.group = n_head / pool->n_kv_head;
+        p.n_head = n_head;
+        p.n_pages = pool->n_pages;
+        p.layer_row0 = layer * pool->n_pages * pool->n_kv_head * pool->page_tokens;
+        p.n_stages = n_stages;
+        p.scale_log2 = scale * 1.4426950408889634f;
+        brc_status rc;
+        if (hd == 256)
+            rc = q_dtype == BRC_DTYPE_F32 ? launch_partial<256, true>(pool, p, grid, smem, st)
+                                          : launch_partial<256, false>(pool, p, grid, smem, st);
+        else
+            rc = q_dtype == BRC_DTYPE_F32 ? launch_partial<128, true>(pool, p, grid, smem, st)
+                                          : launch_partial<128, false>(pool, p, grid, smem, st);
+        if (rc != BRC_OK) return rc;
+        CombineParams c;
+        c.part_acc = part_acc;
+        c.part_ml = part_ml;
+        c.seq_lens = lens + s0;
+        c.gate = gate ? gate + (size_t)s0 * n_head * gate_head_stride : nullptr;
+        c.out = out + (size_t)s0 * n_head * hd;
+        c.out_ml = out_ml ? out_ml + (size_t)s0 * n_head * 2 : nullptr;
+        c.n_seqs = ns;
+        c.n_kv_head = pool->n_kv_head;
+        c.group = p.group;
+        c.n_head = n_head;
+        c.max_seq_len = max_seq_len;
+        c.gate_head_stride = gate_head_stride;
+        c.n_cta = grid;
+        brc_stage_begin(pool, BRC_STAGE_ATTN_COMBINE, st);
+        if (hd == 256)
+            decode_combine_kernel<256><<<ns * n_head, 256, 0, st>>>(c);
+        else
+            decode_combine_kernel<128><<<ns * n_head, 128, 0, st>>>(c);
+        brc_stage_end(pool, BRC_STAGE_ATTN_COMBINE, st);
+        BRC_CUDA(cudaGetLastError());
+    }
+    return BRC_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+brc_status brc_decode_workspace_bytes(const brc_pool *pool, uint32_t n_seqs, uint32_t n_head, uint64_t *out_bytes) {
+    if (!pool || !out_bytes) return brc_fail(BRC_ERR_INVALID, "brc_decode_workspace_bytes: NULL argument");
+    (void)n_head;
+    const uint64_t slots = slots_for(pool, n_seqs);
+    *out_bytes = slots * GROUP_TILE * ((uint64_t)pool->head_dim + 2u) * sizeof(float);
+    return BRC_OK;
+}
+
+brc_status brc_paged_decode_attn(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype, uint32_t n_head,
+                                 const float *gate_dev, uint32_t gate_head_stride, const uint32_t *block_tables_dev,
+                                 uint32_t table_stride, const uint32_t *seq_lens_dev, uint32_t n_seqs,
+                                 uint32_t max_seq_len, float scale, float *out_dev, void *workspace_dev,
+                                 uint64_t workspace_bytes, void *stream) {
+    if (brc_status rc = validate_decode(pool, "brc_paged_decode_attn", layer, q_dev, q_dtype, n_head, block_tables_dev,
+                                        table_stride, seq_lens_dev, n_seqs, max_seq_len, out_dev, workspace_dev,
+                                        workspace_bytes))
+        return rc;
+    if (gate_dev && gate_head_stride < pool->head_dim)
+        return brc_fail(BRC_ERR_INVALID, "brc_paged_decode_attn: gate_head_stride %u < head_dim %u", gate_head_stride,
+                        pool->head_dim);
+    if (n_seqs == 0) return BRC_OK;
+    return run_decode(pool, layer, q_dev, q_dtype, n_head, gate_dev, gate_head_stride, block_tables_dev, table_stride,
+                      seq_lens_dev, n_seqs, max_seq_len, scale, out_dev, nullptr, workspace_dev, brc_stream(stream));
+}
+
+brc_status brc_decode_partial_bytes(uint32_t n_seqs, uint32_t n_head, uint32_t head_dim, uint64_t *out_bytes) {
+    if (!out_bytes) return brc_fail(BRC_ERR_INVALID, "brc_decode_partial_bytes: NULL argument");
+    *out_bytes = (uint64_t)n_seqs * n_head * ((uint64_t)head_dim + 2u) * sizeof(float);
+    return BRC_OK;
+}
+
+brc_status brc_decode_partial(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype, uint32_t n_head,
+                              const uint32_t *block_tables_dev, uint32_t table_stride, const uint32_t *seq_lens_dev,
+                              uint32_t n_seqs, uint32_t max_seq_len, float scale, void *partial_dev, void *workspace_dev,
+                              uint64_t workspace_bytes, void *stream) {
+    if (brc_status rc = validate_decode(pool, "brc_decode_partial", layer, q_dev, q_dtype, n_head, block_tables_dev,
+                                        table_stride, seq_lens_dev, n_seqs, max_seq_len, partial_dev, workspace_dev,
+                                        workspace_bytes))
+        return rc;
+    if (n_seqs == 0) return BRC_OK;
+    float *acc = static_cast<float *>(partial_dev);
+    float *ml = acc + (size_t)n_seqs * n_head * pool->head_dim;
+    return run_decode(pool, layer, q_dev, q_dtype, n_head, nullptr, 0, block_tables_dev, table_stride, seq_lens_dev,
+                      n_seqs, max_seq_len, scale, acc, ml, workspace_dev, brc_stream(stream));
+}
+
+brc_status brc_decode_combine(int32_t device, const void *parts_dev, uint32_t n_parts, uint64_t part_stride_bytes,
+                              uint32_t n_seqs, uint32_t n_head, uint32_t head_dim, const float *gate_dev,
+                              uint32_t gate_head_stride, float *out_dev, void *stream) {
+    if (!parts_dev || !out_dev) return brc_fail(BRC_ERR_INVALID, "brc_decode_combine: NULL pointer");
+    if (head_dim != 256 && head_dim != 128)
+        return brc_fail(BRC_ERR_UNSUPPORTED, "brc_decode_combine: head_dim %u (kernels are built for 128 and 256)", head_dim);
+    uint64_t need = 0;
+    brc_decode_partial_bytes(n_seqs, n_head, head_dim, &need);
+    if (n_parts == 0 || (n_parts > 1 && part_stride_bytes < need) || (part_stride_bytes & 15u))
+        return brc_fail(BRC_ERR_INVALID, "brc_decode_combine: %u parts laid %llu bytes apart, each needs %llu (16-byte multiple)",
+                        n_parts, (unsigned long long)part_stride_bytes, (unsigned long long)need);
+    if (gate_dev && gate_head_stride < head_dim)
+        return brc_fail(BRC_ERR_INVALID, "brc_decode_combine: gate_head_stride %u < head_dim %u", gate_head_stride, head_dim);
+    if (n_seqs == 0 || n_head == 0) return BRC_OK;
+    brc_device_guard guard(device);
+    if (!guard.ok) return brc_fail(BRC_ERR_CUDA, "brc_decode_combine: cannot make device %d current", device);
+    const uint32_t rows = n_seqs * n_head;
+    if (head_dim == 256)
+        parts_combine_kernel<256><<<rows, 256, 0, brc_stream(stream)>>>(static_cast<const uint8_t *>(parts_dev), n_parts,
+                                                                       part_stride_bytes, rows, gate_dev, gate_head_stride, out_dev);
+    else
+        parts_combine_kernel<128><<<rows, 128, 0, brc_stream(stream)>>>(static_cast<const uint8_t *>(parts_dev), n_parts,
+                                                                       part_stride_bytes, rows, gate_dev, gate_head_stride, out_dev);
+    BRC_CUDA(cudaGetLastError());
+    return BRC_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,264 @@
+/*
+ * libbreccia_kv — C ABI of the B200 (sm_100a) paged KV-cache hot path.
+ *
+ * Drop-in boundary for the `breccia-kernels::qsa` operator surface of
+ * carlkrott/breccia: a caller that today drives `QsaState` / `Qsa::{kv_append,
+ * attend, apply}` binds these entry points instead.  Each declaration cites the
+ * reference interface it replaces (path inside the reference project : line).
+ *
+ * Conventions (the reference's, kept):
+ *   - every entry point returns a status (0 = OK, negative = error) and never
+ *     throws or aborts; `brc_last_error()` gives a thread-local message with
+ *     the offending numbers (reference: `anyhow::Result`, qsa/mod.rs:1108-1116);
+ *   - shape / capacity violations are refused on the host BEFORE any launch;
+ *   - the caller owns state explicitly (create / destroy), nothing here
+ *     allocates inside a launch, and launches are asynchronous on the stream
+ *     passed as `void*` (a `cudaStream_t`; NULL = the legacy default stream);
+ *   - pointers named `*_dev` are device addresses on the pool's GPU, everything
+ *     else is host memory;
+ *   - there is no CPU fallback: without a usable GPU every compute call fails
+ *     with BRC_ERR_CUDA.
+ *
+ * Page layout (crates/breccia-kernels/src/qsa/mod.rs:22-28, identical):
+ *   K and V pools of one layer are arrays of u16 binary16 bits,
+ *     element = ((page * n_kv_head + kv_head) * page_tokens + cell_in_page) * head_dim + d
+ *   one pool per (GPU, layer) shared by all sequences; a sequence is a block
+ *   table of physical page ids.  A page id addresses the same slot in every
+ *   layer's K and V pool.
+ */
+#ifndef BRECCIA_KV_H
+#define BRECCIA_KV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(BRC_BUILDING_LIB)
+#define BRC_API __attribute__((visibility("default")))
+#else
+#define BRC_API
+#endif
+
+typedef int32_t brc_status;
+
+#define BRC_OK 0
+#define BRC_ERR_INVALID (-1)      /* bad argument / shape                         */
+#define BRC_ERR_CAPACITY (-2)     /* write past the block table / pool exhausted  */
+#define BRC_ERR_CUDA (-3)         /* a CUDA runtime / driver call failed          */
+#define BRC_ERR_NO_PAGES (-4)     /* allocator has too few free pages             */
+#define BRC_ERR_TIMEOUT (-5)      /* a bounded device-side wait gave up           */
+#define BRC_ERR_DEVICE_CHECK (-6) /* a kernel's own bounds check refused an index */
+#define BRC_ERR_UNSUPPORTED (-7)  /* geometry outside what the kernels are built for */
+#define BRC_ERR_NOT_RESIDENT (-8) /* page is in the host tier                     */
+
+/* dtype tags for query / source tensors */
+#define BRC_DTYPE_F32 0
+#define BRC_DTYPE_F16 1
+
+typedef struct brc_pool brc_pool;
+typedef struct brc_radix brc_radix;
+typedef struct brc_tier brc_tier;
+
+typedef struct brc_geometry {
+    uint32_t n_layers;
+    uint32_t n_kv_head;
+    uint32_t head_dim;
+    uint32_t page_tokens;
+    uint32_t n_pages;
+    int32_t device;
+    uint64_t half_page_bytes; /* bytes of K (or V) of one page of one layer */
+    uint64_t total_bytes;     /* K + V, all layers                          */
+} brc_geometry;
+
+/* Thread-local text of the last error returned on this thread ("" if none). */
+BRC_API const char *brc_last_error(void);
+BRC_API int32_t brc_abi_version(void);
+
+/* ---------------------------------------------------------------- pool / state
+ * Replaces QsaState::{new, with_layout, reset, bytes, release}
+ * (crates/breccia-kernels/src/qsa/mod.rs:393,399,551,572,591) with ONE pool per
+ * (GPU, layer set) shared by all sequences.  Pools are zero-filled on creation
+ * like the reference (qsa/mod.rs:399-535). */
+BRC_API brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim,
+                                   uint32_t page_tokens, uint32_t n_pages, brc_pool **out);
+/* A pool without device memory: page ids, refcounts and (later) prefix-tree and
+ * tier bookkeeping only.  Every entry point that would touch the GPU refuses it
+ * with BRC_ERR_CUDA.  Exists so schedulers and tests can exercise the host-side
+ * state machine on a machine without a GPU; it computes nothing. */
+BRC_API brc_status brc_pool_create_bookkeeping(uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim,
+                                               uint32_t page_tokens, uint32_t n_pages, brc_pool **out);
+BRC_API brc_status brc_pool_destroy(brc_pool *pool);
+BRC_API brc_status brc_pool_geometry(const brc_pool *pool, brc_geometry *out);
+/* qsa/mod.rs:572 (`bytes`) */
+BRC_API brc_status brc_pool_bytes(const brc_pool *pool, uint64_t *out);
+/* qsa/mod.rs:551-570 (`reset`: pools back to zero) */
+BRC_API brc_status brc_pool_zero(brc_pool *pool, void *stream);
+/* Test hook: fills every pool byte with 0xFF (binary16 NaN), the analogue of the
+ * reference's BRECCIA_FAULT_POISON_QSA flag (qsa/mod.rs:509-523). */
+BRC_API brc_status brc_pool_poison_nan(brc_pool *pool, void *stream);
+BRC_API brc_status brc_pool_k_ptr(const brc_pool *pool, uint32_t layer, void **out_dev);
+BRC_API brc_status brc_pool_v_ptr(const brc_pool *pool, uint32_t layer, void **out_dev);
+/* Byte-range read-back / upload of one layer's K (which = 0) or V (which = 1)
+ * pool, ordered on `stream` and complete on return (the reference's
+ * `gemv::download` / `upload_into`, crates/breccia-kernels/src/gemv.rs:1059-1071).
+ * Host memory may be pageable. */
+BRC_API brc_status brc_pool_read(brc_pool *pool, int32_t which, uint32_t layer, uint64_t byte_offset, void *dst,
+                                 uint64_t bytes, void *stream);
+BRC_API brc_status brc_pool_write(brc_pool *pool, int32_t which, uint32_t layer, uint64_t byte_offset,
+                                  const void *src, uint64_t bytes, void *stream);
+/* Synchronises `stream`, then reports and clears the device-side check word:
+ * BRC_OK, BRC_ERR_DEVICE_CHECK (an out-of-range page id or position reached a
+ * kernel, which skipped the access) or BRC_ERR_TIMEOUT (a bounded wait gave
+ * up).  Mirrors the reference's bounded fence wait
+ * (crates/breccia-vk/src/ctx.rs:1541-1561) without aborting the process. */
+BRC_API brc_status brc_pool_check(brc_pool *pool, void *stream);
+
+/* ---------------------------------------------------------------- page allocator / refcounts
+ * No counterpart in the reference (design note docs/reference-engines/
+ * 02-kv-and-context.md:543-581: block = id + refcount + free queue).  Host-side,
+ * thread-safe.  Freshly allocated pages have refcount 1. */
+BRC_API brc_status brc_pages_alloc(brc_pool *pool, uint32_t n, uint32_t *out_ids);
+BRC_API brc_status brc_pages_retain(brc_pool *pool, const uint32_t *ids, uint32_t n);
+/* Drops one reference each; a page returns to the free list at refcount 0. */
+BRC_API brc_status brc_pages_release(brc_pool *pool, const uint32_t *ids, uint32_t n);
+BRC_API brc_status brc_page_refcount(const brc_pool *pool, uint32_t id, uint32_t *out);
+BRC_API brc_status brc_pages_free_count(const brc_pool *pool, uint32_t *out);
+
+/* ---------------------------------------------------------------- KV append
+ * Replaces Qsa::kv_append (crates/breccia-kernels/src/qsa/mod.rs:1107-1156) and
+ * shaders/qsa_kv_append.comp:137-161, batched over sequences.
+ *
+ * Sequence s appends its tokens at cells pos0_dev[s] .. through its block table
+ * row block_tables_dev[s*table_stride ..].  Tokens per sequence are uniform
+ * (`tokens_per_seq`, cu_tokens_dev == NULL) or ragged (cu_tokens_dev[n_seqs+1]
+ * exclusive prefix of token counts; tokens_per_seq ignored).  Sources are
+ * [total_tokens][n_kv_head*head_dim], f32 (reference) or f16 bits already on
+ * the storage grid.  f32 sources are encoded by the reference's integer
+ * round-to-nearest-even rule (shaders/f16_storage.glsl:26-55), bit-exact.
+ *
+ * `max_pos_end` is the caller's bound on pos0[s]+tokens(s); the host refuses
+ * max_pos_end > table_stride*page_tokens (the reference's capacity check) and
+ * the kernel skips, and reports through brc_pool_check, any token beyond it or
+ * any block-table entry >= n_pages. */
+BRC_API brc_status brc_kv_append(brc_pool *pool, uint32_t layer, const uint32_t *block_tables_dev,
+                                 uint32_t table_stride, const uint32_t *pos0_dev, uint32_t n_seqs,
+                                 uint32_t tokens_per_seq, const uint32_t *cu_tokens_dev, uint32_t total_tokens,
+                                 uint32_t max_pos_end, const void *k_src_dev, const void *v_src_dev,
+                                 int32_t src_dtype, void *stream);
+
+/* ---------------------------------------------------------------- page gather / copy / fork
+ * Gather: the reference reads pages back only through an identity table
+ * (crates/breccia-engine/src/graph.rs:2204-2228, `dump_state`); this reads
+ * `n_tokens` cells of one sequence through a real block table into logical
+ * [n_tokens][n_kv_head][head_dim] binary16 arrays. */
+BRC_API brc_status brc_page_gather(brc_pool *pool, uint32_t layer, const uint32_t *block_table_dev,
+                                   uint32_t table_len, uint32_t n_tokens, void *k_out_dev, void *v_out_dev,
+                                   void *stream);
+/* Copies whole pages src_ids[i] -> dst_ids[i] in every layer, K and V (no
+ * counterpart in the reference).  Ids are device arrays; pairs must not chain
+ * (no dst that is also a src). */
+BRC_API brc_status brc_page_copy(brc_pool *pool, const uint32_t *src_ids_dev, const uint32_t *dst_ids_dev,
+                                 uint32_t n, void *stream);
+/* Copy-on-write fork of a sequence of `n_tokens` cells (no counterpart in the
+ * reference): every full page of the parent is shared (refcount + 1); a
+ * partially filled last page is copied into a freshly allocated page.  Host
+ * tables in, host table out; `*out_new_page` is the private copy's id or
+ * UINT32_MAX when the length is page-aligned. */
+BRC_API brc_status brc_seq_fork(brc_pool *pool, const uint32_t *parent_table, uint32_t n_tokens,
+                                uint32_t *child_table, uint32_t *out_new_page, void *stream);
+
+/* ---------------------------------------------------------------- paged decode attention
+ * Replaces Qsa::topk_dense + Qsa::attend + Qsa::apply at T = 1
+ * (crates/breccia-kernels/src/qsa/mod.rs:1365-1376,1382-1462,1466-1580;
+ * shaders qsa_attn_scores_small.comp, ops_softmax.comp,
+ * qsa_attn_apply_split.comp, qsa_attn_apply_reduce.comp) for a batch of
+ * sequences: out[s,h,:] = sigmoid(gate[s,h,:]) * softmax_c(scale * q[s,h].k_c) . v_c
+ * over cells c < seq_lens_dev[s] (the dense selection `topk_dense` emits), with
+ * kv head = h * n_kv_head / n_head.  Cells at or past seq_len are never read
+ * into the result, whatever the pool holds there.
+ *
+ *   q_dev     [n_seqs][n_head][head_dim], f16 bits or f32 (reference: f32)
+ *   gate_dev  NULL, or f32 with gate[s,h,d] at gate_dev[(s*n_head + h)*gate_head_stride + d]
+ *             (the reference reads it in place from the second half of each
+ *             head's 2*head_dim block: pass q_full + head_dim, stride 2*head_dim)
+ *   out_dev   [n_seqs][n_head][head_dim] f32
+ *   scale     the reference uses 1/sqrt(head_dim)
+ *   workspace_dev  scratch of at least brc_decode_workspace_bytes(); contents
+ *             are undefined afterwards; calls that overlap in time need
+ *             separate workspaces.
+ *   max_seq_len    caller's bound on seq_lens; refused if > table_stride*page_tokens.
+ * A sequence of length 0 yields zeros. */
+BRC_API brc_status brc_decode_workspace_bytes(const brc_pool *pool, uint32_t n_seqs, uint32_t n_head,
+                                              uint64_t *out_bytes);
+BRC_API brc_status brc_paged_decode_attn(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype,
+                                         uint32_t n_head, const float *gate_dev, uint32_t gate_head_stride,
+                                         const uint32_t *block_tables_dev, uint32_t table_stride,
+                                         const uint32_t *seq_lens_dev, uint32_t n_seqs, uint32_t max_seq_len,
+                                         float scale, float *out_dev, void *workspace_dev,
+                                         uint64_t workspace_bytes, void *stream);
+
+/* The two halves, exposed for split-KV across GPUs (no counterpart in the
+ * reference, whose split-K partials stay on one device:
+ * qsa/mod.rs:1491-1521).  `brc_decode_partial` runs the same split-KV kernel
+ * but emits, per (sequence, head), the un-normalised partial
+ *   m = max_c(scale*log2(e) * q.k_c),  l = sum_c 2^(s_c - m),  acc[d] = sum_c 2^(s_c - m) v_c[d]
+ * as `partial_dev`: [n_seqs][n_head][head_dim] f32 acc followed by
+ * [n_seqs][n_head][2] f32 (m, l); brc_decode_partial_bytes gives the size.
+ * `brc_decode_combine` merges `n_parts` such buffers laid `part_stride_bytes`
+ * apart (e.g. an all-gather receive buffer), applies the gate and writes out. */
+BRC_API brc_status brc_decode_partial_bytes(uint32_t n_seqs, uint32_t n_head, uint32_t head_dim,
+                                            uint64_t *out_bytes);
+BRC_API brc_status brc_decode_partial(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype,
+                                      uint32_t n_head, const uint32_t *block_tables_dev, uint32_t table_stride,
+                                      const uint32_t *seq_lens_dev, uint32_t n_seqs, uint32_t max_seq_len,
+                                      float scale, void *partial_dev, void *workspace_dev,
+                                      uint64_t workspace_bytes, void *stream);
+BRC_API brc_status brc_decode_combine(int32_t device, const void *parts_dev, uint32_t n_parts,
+                                      uint64_t part_stride_bytes, uint32_t n_seqs, uint32_t n_head,
+                                      uint32_t head_dim, const float *gate_dev, uint32_t gate_head_stride,
+                                      float *out_dev, void *stream);
+
+/* ---------------------------------------------------------------- one decode step over layers
+ * The composition the reference performs per attention layer in Qsa::forward
+ * (crates/breccia-kernels/src/qsa/mod.rs:1587-1645: kv_append -> attend ->
+ * apply) and the engine repeats for its 12 attention layers
+ * (crates/breccia-engine/src/graph.rs:5899-5966), for a batch of sequences:
+ *   pos0[s] = seq_lens[s]; seq_lens[s] += 1                (on the device)
+ *   for layer in layer0 .. layer0+n_layers:
+ *       append k_new/v_new[layer][s] at cell pos0[s];  out[layer] = decode attention
+ * q / k_new / v_new / gate / out are per-layer arrays laid `*_layer_stride_bytes`
+ * apart ([n_seqs][n_head][head_dim] and [n_seqs][n_kv_head*head_dim]).
+ * `max_seq_len_after` bounds seq_lens AFTER the increment. */
+BRC_API brc_status brc_decode_step(brc_pool *pool, uint32_t layer0, uint32_t n_layers,
+                                   const uint32_t *block_tables_dev, uint32_t table_stride, uint32_t *seq_lens_dev,
+                                   uint32_t *pos0_dev, uint32_t n_seqs, uint32_t max_seq_len_after, const void *q_dev,
+                                   int32_t q_dtype, uint64_t q_layer_stride_bytes, uint32_t n_head,
+                                   const void *k_new_dev, const void *v_new_dev, int32_t kv_dtype,
+                                   uint64_t kv_layer_stride_bytes, const float *gate_dev, uint32_t gate_head_stride,
+                                   uint64_t gate_layer_stride_bytes, float scale, float *out_dev,
+                                   uint64_t out_layer_stride_bytes, void *workspace_dev, uint64_t workspace_bytes,
+                                   void *stream);
+
+/* ---------------------------------------------------------------- per-stage GPU timers
+ * Counterpart of the reference's BRECCIA_GPU_TIME probe and its stage ids
+ * KV_APPEND / ATTN (crates/breccia-kernels/src/dispatch_batch.rs:453-512,
+ * qsa/mod.rs:1600-1642).  While enabled, each kernel launch of a stage is
+ * bracketed by CUDA events on the launching stream; brc_timing_read waits for
+ * them, returns the number of launches and their summed device time since the
+ * previous read, and clears the list.  Off by default (event records cost). */
+#define BRC_STAGE_KV_APPEND 0
+#define BRC_STAGE_ATTN_PARTIAL 1
+#define BRC_STAGE_ATTN_COMBINE 2
+#define BRC_STAGE_PAGE_COPY 3
+#define BRC_STAGE_PAGE_GATHER 4
+#define BRC_STAGE_PREFILL 5
+BRC_API brc_status brc_timing_enable(brc_pool *pool, int32_t on);
+BRC_API brc_status brc_timing_read(brc_pool *pool, int32_t stage, uint32_t *out_launches, double *out_total_ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BRECCIA_KV_H */

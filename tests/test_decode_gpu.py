@@ -1,0 +1,287 @@
+"""Paged decode attention on the GPU through the C ABI against the oracle.
+
+Tolerance (BASELINE north_star, fp32 accumulate over f16 KV): max-abs <= 2e-3, max-rel <= 1e-2.
+The reference's own measure max|g-w|/max(|w|,1) (bar 1e-5 for its kernels) is asserted too."""
+import ctypes as C
+import hashlib
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from breccia_b200 import _lib, synth
+from breccia_b200._lib import DTYPE_F16, DTYPE_F32
+from breccia_b200.qsa import DecodeBatch, KvPool, Qsa, QsaState, decode_combine, decode_partial_bytes
+from helpers import ATTN_MAX_ABS, ATTN_MAX_REL, attention_errors, dev_u32, fill_pool_from_host
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+from make_cfg1_golden import CONTEXT, HD, N_HEAD, N_KV, POOL_PAGES, cfg1_inputs  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+REF_MEASURE_BAR = 1e-5  # crates/breccia-kernels/tests/attn_conformance.rs:1148-1158
+
+
+def assert_attention_close(got, want, what=""):
+    max_abs, max_rel, ref = attention_errors(got, want)
+    assert np.isfinite(np.asarray(got)).all(), f"{what}: non-finite output"
+    assert max_abs <= ATTN_MAX_ABS, f"{what}: max-abs {max_abs:.3e} > {ATTN_MAX_ABS}"
+    assert max_rel <= ATTN_MAX_REL, f"{what}: max-rel {max_rel:.3e} > {ATTN_MAX_REL}"
+    assert ref <= REF_MEASURE_BAR, f"{what}: reference measure {ref:.3e} > {REF_MEASURE_BAR}"
+    return max_abs, max_rel, ref
+
+
+def test_cfg1_conformance_against_committed_golden(cuda_device):
+    """BASELINE config 1 end to end through the mirror API: fill 1024 cells through kv_append in
+    256-cell chunks, append one token, one decode step; cache pages bit-exact, output in tolerance."""
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "cfg1_golden.npz"))
+    table, k_ctx, v_ctx, k_new, v_new, q = cfg1_inputs()
+    pool = KvPool(0, 1, N_KV, HD, POOL_PAGES)
+    qsa = Qsa(pool, N_HEAD)
+    state = QsaState(pool, CONTEXT + 1, block_table=table)
+    ws = qsa.workspace(256)
+    for start in range(0, CONTEXT, 256):
+        ws.k_cur.copy_(torch.from_numpy(k_ctx[start:start + 256]))
+        ws.v_cur.copy_(torch.from_numpy(v_ctx[start:start + 256]))
+        qsa.kv_append(state, ws, start)
+    ws1 = qsa.workspace(1, q_dtype=DTYPE_F16)
+    ws1.k_cur.copy_(torch.from_numpy(k_new))
+    ws1.v_cur.copy_(torch.from_numpy(v_new))
+    ws1.q.copy_(torch.from_numpy(q).view(1, N_HEAD, HD))
+    qsa.kv_append(state, ws1, CONTEXT)
+    qsa.topk_dense(ws1, CONTEXT)
+    qsa.attend(state, ws1, CONTEXT)
+    qsa.apply(state, ws1, CONTEXT)
+    pool.check()
+    kp, vp = pool.read(0, 0), pool.read(1, 0)
+    assert hashlib.sha256(kp.tobytes()).digest() == bytes(g["k_pool_sha256"])
+    assert hashlib.sha256(vp.tobytes()).digest() == bytes(g["v_pool_sha256"])
+    assert np.array_equal(kp[table[64]], g["last_page_k"])
+    out = ws1.attn_out.cpu().numpy()[0]
+    errs = assert_attention_close(out, g["out"], "cfg1")
+    print("cfg1 max_abs %.2e max_rel %.2e ref_measure %.2e" % errs)
+    # f32 query path gives the same answer
+    ws2 = qsa.workspace(1, q_dtype=DTYPE_F32)
+    ws2.q.copy_(torch.from_numpy(q).view(1, N_HEAD, HD))
+    qsa.topk_dense(ws2, CONTEXT)
+    qsa.attend(state, ws2, CONTEXT)
+    assert_attention_close(ws2.attn_out.cpu().numpy()[0], g["out"], "cfg1 f32 q")
+    pool.release()
+
+
+def _batch_case(n_head, n_kv, hd, lens, seed, n_layers=1, layer=0, gate=False, q_dtype=DTYPE_F16, poison=False):
+    lens = np.asarray(lens, np.int64)
+    tables, n_pool = synth.scattered_tables(seed, np.maximum(lens, 1), pool_factor=1.3)
+    pool = KvPool(0, n_layers, n_kv, hd, n_pool)
+    if poison:
+        pool.poison_nan()
+    k, v = fill_pool_from_host(pool, layer, seed + 10)
+    if poison:
+        # everything the sequences do not own, and the tail of every last page, is NaN
+        k = k.reshape(n_pool, n_kv, 16, hd).copy()
+        v = v.reshape(n_pool, n_kv, 16, hd).copy()
+        live = np.zeros((n_pool, 16), bool)
+        for s, n in enumerate(lens):
+            for c in range(int(n)):
+                live[tables[s, c // 16], c % 16] = True
+        k[~live] = 0xFFFF
+        v[~live] = 0xFFFF
+        pool.write(0, layer, k)
+        pool.write(1, layer, v)
+        k, v = k.reshape(-1), v.reshape(-1)
+    q32 = synth.normal(seed + 20, lens.size * n_head * hd, 1.0).reshape(lens.size, n_head, hd)
+    if q_dtype == DTYPE_F16:
+        q32 = oracle.to_f16(q32)
+    g = synth.normal(seed + 30, lens.size * n_head * 2 * hd, 1.0).reshape(lens.size, n_head, 2, hd) if gate else None
+    batch = DecodeBatch(pool, n_head, tables, lens, q_dtype=q_dtype)
+    qd = torch.from_numpy(q32).cuda()
+    if q_dtype == DTYPE_F16:
+        qd = qd.half()
+    out = torch.full((lens.size, n_head, hd), float("nan"), device="cuda")
+    gd = torch.from_numpy(g).cuda() if gate else None
+    batch.attend(layer, qd, out, gate=gd.view(-1)[hd:] if gate else None, gate_head_stride=2 * hd if gate else 0)
+    pool.check()
+    want, _ = oracle.decode_batch(k, v, tables, lens, q32, n_head, n_kv, hd, gate=g[:, :, 1, :] if gate else None)
+    return pool, batch, qd, out.cpu().numpy(), want
+
+
+@pytest.mark.parametrize("lens", [[1], [15], [16], [17], [1025], [4097, 3, 160, 16, 1, 2049, 31, 700]])
+def test_ragged_lengths_and_page_edges(cuda_device, lens):
+    pool, _, _, got, want = _batch_case(16, 2, 256, lens, seed=40 + len(lens))
+    assert_attention_close(got, want, f"lens {lens}")
+    pool.release()
+
+
+def test_reference_geometry_shapes_2062_cells_with_gate(cuda_device):
+    """The reference's 2062-cell single-query case shape (dense, gate from the second half of each
+    head's 512-wide block, f32 query), crates/breccia-kernels/tests/attn_conformance.rs:897-1037,
+    at 16 heads (8 per kv head) since the kernels hold one 8-head tile."""
+    pool, _, _, got, want = _batch_case(16, 2, 256, [2062], seed=0xE3, gate=True, q_dtype=DTYPE_F32)
+    errs = assert_attention_close(got, want, "2062 cells")
+    print("2062 cells max_abs %.2e max_rel %.2e ref_measure %.2e" % errs)
+    pool.release()
+
+
+@pytest.mark.parametrize("n_head,n_kv,hd", [(16, 2, 256), (8, 2, 256), (4, 4, 256), (32, 4, 128), (6, 2, 128)])
+def test_geometries(cuda_device, n_head, n_kv, hd):
+    pool, _, _, got, want = _batch_case(n_head, n_kv, hd, [333, 48, 1000], seed=60 + n_head, n_layers=2, layer=1)
+    assert_attention_close(got, want, f"{n_head}q/{n_kv}kv hd{hd}")
+    pool.release()
+
+
+def test_nan_poison_outside_live_cells_never_reaches_the_output(cuda_device):
+    """Unowned pages and the cells past each sequence end hold NaN (the reference's poison flag,
+    qsa/mod.rs:509-523): the output must equal the oracle's, which never looks there."""
+    pool, _, _, got, want = _batch_case(16, 2, 256, [5, 100, 1, 511, 16], seed=77, poison=True)
+    assert_attention_close(got, want, "poisoned pool")
+    pool.release()
+
+
+def test_empty_sequence_yields_zeros_and_empty_batch_is_a_no_op(cuda_device):
+    pool, batch, qd, got, want = _batch_case(16, 2, 256, [0, 40, 0], seed=81)
+    assert not got[0].any() and not got[2].any()
+    assert_attention_close(got, want, "with empty sequences")
+    L = _lib.load()
+    assert L.brc_paged_decode_attn(pool.handle, 0, C.c_void_p(qd.data_ptr()), DTYPE_F16, 16, None, 0,
+                                   C.c_void_p(batch.block_tables.data_ptr()), batch.table_stride,
+                                   C.c_void_p(batch.seq_lens.data_ptr()), 0, 0, 0.0625, C.c_void_p(qd.data_ptr()),
+                                   None, 0, None) == 0
+    pool.release()
+
+
+def test_block_table_permutation_invariance(cuda_device):
+    """The same logical cache under two different physical placements gives bit-identical output."""
+    n_head, n_kv, hd, n = 16, 2, 256, 777
+    n_pages = (n + 15) // 16
+    k = synth.normal(5, n_pages * 16 * n_kv * hd, 0.5).reshape(n_pages, 16, n_kv, hd)
+    v = synth.normal(6, n_pages * 16 * n_kv * hd, 0.5).reshape(n_pages, 16, n_kv, hd)
+    q = torch.from_numpy(oracle.to_f16(synth.normal(7, n_head * hd))).cuda().half().view(1, n_head, hd)
+    outs = []
+    for seed in (1, 2):
+        pool = KvPool(0, 1, n_kv, hd, 3 * n_pages)
+        table = synth.permutation(seed, 3 * n_pages)[:n_pages]
+        kp = np.zeros((3 * n_pages, n_kv, 16, hd), np.uint16)
+        vp = np.zeros_like(kp)
+        kp[table] = oracle.f32_to_f16_bits_np(k).transpose(0, 2, 1, 3)
+        vp[table] = oracle.f32_to_f16_bits_np(v).transpose(0, 2, 1, 3)
+        pool.write(0, 0, kp)
+        pool.write(1, 0, vp)
+        batch = DecodeBatch(pool, n_head, table[None, :], [n])
+        out = torch.empty((1, n_head, hd), device="cuda")
+        batch.attend(0, q, out)
+        pool.check()
+        outs.append(out.cpu().numpy())
+        pool.release()
+    assert np.array_equal(outs[0], outs[1])
+
+
+def test_chunking_does_not_change_the_answer(cuda_device):
+    """Rows of a multi-row call are causal (row t sees cells <= pos0 + t) and equal the same rows
+    computed one at a time — the reference's T = 1 / 8 / 32 agreement test
+    (crates/breccia-kernels/tests/attn_conformance.rs:769-776)."""
+    n_head, n_kv, hd, pos0, T = 16, 2, 256, 100, 8
+    pool = KvPool(0, 1, n_kv, hd, 16)
+    qsa = Qsa(pool, n_head)
+    state = QsaState(pool, pos0 + T)
+    k = synth.normal(1, (pos0 + T) * n_kv * hd, 0.5).reshape(pos0 + T, -1)
+    v = synth.normal(2, (pos0 + T) * n_kv * hd, 0.5).reshape(pos0 + T, -1)
+    wsf = qsa.workspace(pos0 + T)
+    wsf.k_cur.copy_(torch.from_numpy(k))
+    wsf.v_cur.copy_(torch.from_numpy(v))
+    qsa.kv_append(state, wsf, 0)
+    q = synth.normal(3, T * n_head * hd).reshape(T, n_head, hd)
+    ws = qsa.workspace(T)
+    ws.q.copy_(torch.from_numpy(q))
+    qsa.topk_dense(ws, pos0)
+    qsa.attend(state, ws, pos0)
+    many = ws.attn_out.cpu().numpy()
+    kf, vf = oracle.to_f16(k).reshape(pos0 + T, n_kv, hd), oracle.to_f16(v).reshape(pos0 + T, n_kv, hd)
+    ws1 = qsa.workspace(1)
+    for t in range(T):
+        ws1.q.copy_(torch.from_numpy(q[t:t + 1]))
+        qsa.topk_dense(ws1, pos0 + t)
+        qsa.attend(state, ws1, pos0 + t)
+        one = ws1.attn_out.cpu().numpy()[0]
+        want = oracle.attend(q[t], kf, vf, np.arange(pos0 + T, dtype=np.uint32), pos0 + t, n_head, n_kv, hd)
+        assert_attention_close(many[t], want, f"row {t}")
+        assert np.abs(one - many[t]).max() <= 2e-6
+    pool.check()
+    pool.release()
+
+
+def test_partials_then_combine_equals_fused_call(cuda_device):
+    """brc_decode_partial over two halves of the KV range + brc_decode_combine == one fused call
+    (the split-KV-across-GPUs path, exercised on one device)."""
+    n_head, n_kv, hd = 16, 2, 256
+    lens = np.array([2048, 640])
+    pool, batch, qd, fused, want = _batch_case(n_head, n_kv, hd, lens, seed=91)
+    nbytes = decode_partial_bytes(lens.size, n_head, hd)
+    assert nbytes == lens.size * 16512
+    parts = torch.zeros(2 * nbytes, dtype=torch.uint8, device="cuda")
+    half = lens // 2 // 16 * 16
+    tables = batch.block_tables.cpu().numpy().astype(np.uint32)
+    lo = DecodeBatch(pool, n_head, tables, half)
+    hi_tables = np.zeros_like(tables)
+    for s in range(lens.size):
+        n = (lens[s] - half[s] + 15) // 16
+        hi_tables[s, :n] = tables[s, half[s] // 16: half[s] // 16 + n]
+    hi = DecodeBatch(pool, n_head, hi_tables, lens - half)
+    lo.partial(0, qd, parts[:nbytes])
+    hi.partial(0, qd, parts[nbytes:])
+    out = torch.empty((lens.size, n_head, hd), device="cuda")
+    decode_combine(0, parts, 2, nbytes, lens.size, n_head, hd, out)
+    pool.check()
+    assert_attention_close(out.cpu().numpy(), want, "partials + combine")
+    assert np.abs(out.cpu().numpy() - fused).max() <= 2e-6
+    # (m, l, acc) of one head against the oracle's partial
+    acc = parts[:nbytes].view(torch.float32)[: lens.size * n_head * hd].view(lens.size, n_head, hd).cpu().numpy()
+    ml = parts[:nbytes].view(torch.float32)[lens.size * n_head * hd:].view(lens.size, n_head, 2).cpu().numpy()
+    kpool, vpool = pool.read(0, 0).reshape(-1), pool.read(1, 0).reshape(-1)
+    _, kf = oracle.gather(kpool, tables[1], int(half[1]), n_kv, hd)
+    _, vf = oracle.gather(vpool, tables[1], int(half[1]), n_kv, hd)
+    q1 = qd[1].float().cpu().numpy()
+    m, l, a = oracle.partial_head(q1[9], kf, vf, 0, int(half[1]), 1, n_kv, hd, 1 / 16.0)
+    assert abs(ml[1, 9, 0] - m) < 1e-4 and abs(ml[1, 9, 1] - l) / l < 1e-5
+    assert np.abs(acc[1, 9] - a).max() < 1e-4 * max(1.0, np.abs(a).max())
+    pool.release()
+
+
+def test_more_units_than_one_launch_holds(cuda_device):
+    """1100 short sequences x 2 kv heads exceed the 2048 units one launch schedules: the host loops."""
+    lens = (np.arange(1100) % 37 + 1).astype(np.int64)
+    pool, _, _, got, want = _batch_case(16, 2, 256, lens, seed=97)
+    assert_attention_close(got, want, "1100 sequences")
+    pool.release()
+
+
+def test_decode_refusals(cuda_device):
+    pool = KvPool(0, 1, 2, 256, 8)
+    L = _lib.load()
+    q = torch.zeros((1, 16, 256), dtype=torch.half, device="cuda")
+    out = torch.zeros((1, 16, 256), device="cuda")
+    table, lens = dev_u32([[0, 1, 2, 3]]), dev_u32([10])
+    ws = torch.zeros(1 << 22, dtype=torch.uint8, device="cuda")
+    args = lambda **kw: [pool.handle, kw.get("layer", 0), C.c_void_p(q.data_ptr()), kw.get("dt", 1), kw.get("nh", 16), None, 0,
+                         C.c_void_p(table.data_ptr()), 4, C.c_void_p(lens.data_ptr()), 1, kw.get("maxlen", 10), 0.0625,
+                         C.c_void_p(out.data_ptr()), C.c_void_p(ws.data_ptr()), kw.get("wsb", ws.numel()), None]
+    assert L.brc_paged_decode_attn(*args(maxlen=65)) == _lib.ERR_CAPACITY
+    assert b"cells up to 65" in L.brc_last_error()
+    assert L.brc_paged_decode_attn(*args(layer=3)) == _lib.ERR_INVALID
+    assert L.brc_paged_decode_attn(*args(nh=15)) == _lib.ERR_INVALID
+    assert L.brc_paged_decode_attn(*args(nh=24)) == _lib.ERR_UNSUPPORTED
+    assert L.brc_paged_decode_attn(*args(dt=9)) == _lib.ERR_INVALID
+    assert L.brc_paged_decode_attn(*args(wsb=16)) == _lib.ERR_INVALID
+    # a length beyond the caller's bound and a table entry beyond the pool are caught on the device
+    lens.fill_(40)
+    assert L.brc_paged_decode_attn(*args(maxlen=10)) == 0
+    with pytest.raises(_lib.BrcError, match="position past bound"):
+        pool.check()
+    lens.fill_(10)
+    table.fill_(1000)
+    assert L.brc_paged_decode_attn(*args()) == 0
+    with pytest.raises(_lib.BrcError, match="page id >= n_pages"):
+        pool.check()
+    pool.release()
