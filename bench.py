@@ -42,6 +42,8 @@ def parse_args():
                     help="cfg2: lengths uniform in [512, 8192]; fixed8k: every sequence at 8192")
     ap.add_argument("--seed", type=int, default=20261125)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=12,
+                    help="attention layers per step (12 = the BASELINE workload; fewer only for small profiler captures)")
     return ap.parse_args()
 
 
@@ -399,6 +401,7 @@ def run_reference(args):
 
 if __name__ == "__main__":
     a = parse_args()
+    N_LAYERS = a.layers
     if a.impl == "reference":
         run_reference(a)
     else:

@@ -27,7 +27,7 @@ struct brc_pool {
     uint64_t half_page_bytes = 0;   // K (or V) bytes of one page of one layer
     uint64_t layer_bytes = 0;       // K (or V) bytes of one layer
     uint8_t *k_base = nullptr;      // [n_layers][n_pages][n_kv][page_tokens][head_dim] f16
-    uint8_t *v_base = nullptr;
+    uint8_t *v_base = nullptr;      // same allocation as k_base, `layer_bytes * n_layers` further on
     uint32_t *status_dev = nullptr; // device check word
     uint32_t *status_host = nullptr;  // pinned mirror
     uint32_t *ids_dev = nullptr;    // small staging for host-provided id lists
@@ -37,6 +37,9 @@ struct brc_pool {
     // [page_tokens rows][64 columns], 128-byte swizzle.
     alignas(64) CUtensorMap tm_k;
     alignas(64) CUtensorMap tm_v;
+    // 3-D view over both: (column, row, {K, V}); one box = a 64-column group of the K tile and of the V
+    // tile of one page of one kv head.
+    alignas(64) CUtensorMap tm_kv;
     bool has_tma = false;
 
     // per-stage GPU timers (off unless brc_timing_enable)

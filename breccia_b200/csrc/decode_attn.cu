@@ -9,8 +9,9 @@
 //   * work unit = (sequence, kv head); its pages form one flat list of "page-units" over the whole
 //     batch, cut into equal contiguous shares, one per CTA (one CTA per SM), so every SM streams the
 //     same number of 16 KiB page tiles whatever the length distribution;
-//   * a producer warp walks the block table and issues TMA tiled loads (128-byte swizzle) of the K and
-//     V tile of each page into a shared-memory ring guarded by full/empty mbarriers;
+//   * a producer warp walks the block table and issues, per page, one TMA tiled load per 64-column
+//     group (a 3-D box [64 columns][16 rows][K|V] over a view that spans the K and the V pool, 128-byte
+//     swizzle) into a shared-memory ring guarded by full/empty mbarriers;
 //   * four consumer warps take pages round-robin.  Per page: S^T[16 cells x 8 heads] = K . Q^T with
 //     mma.sync m16n8k16 (K fragments by ldmatrix from the swizzled tile, Q^T fragments resident in
 //     registers), online softmax in base 2 with warp shuffles across the cell dimension, the
@@ -100,8 +101,7 @@ __device__ __forceinline__ uint32_t share_begin(uint32_t cta, uint32_t total, ui
 
 template <int HD, bool Q_F32>
 __global__ void __launch_bounds__(NTHREADS, 1)
-    decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                          const DecodeParams p) {
+    decode_partial_kernel(const __grid_constant__ CUtensorMap tm_kv, const DecodeParams p) {
     using C = Cfg<HD>;
     extern __shared__ uint8_t smem_raw[];
     // The 128-byte swizzle pattern repeats every 1024 bytes: tiles must start on that boundary.
@@ -122,8 +122,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             brc::mbar_init(empty0 + 8u * i, 1);
         }
         brc::mbar_fence_init();
-        brc::tma_prefetch_desc(&tm_k);
-        brc::tma_prefetch_desc(&tm_v);
+        brc::tma_prefetch_desc(&tm_kv);
     }
     // Exclusive prefix of pages per unit, S[0..n_units]; every CTA computes it (n_units <= 2048).
     if (warp == 0) {
@@ -182,32 +181,33 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             const uint32_t n_here = min(32u, count - k0);
             for (uint32_t i = 0; i < n_here; ++i) {
                 const uint32_t r = __shfl_sync(0xffffffffu, row, i);
+                const uint32_t kk = k0 + i;
+                const uint32_t stage = kk % p.n_stages;
+                const uint32_t fb = full0 + 8u * stage;
                 if (lane == 0) {
-                    const uint32_t kk = k0 + i;
-                    const uint32_t stage = kk % p.n_stages;
-                    const uint32_t round = kk / p.n_stages;
-                    if (!wait_bounded(empty0 + 8u * stage, (round & 1u) ^ 1u)) {
+                    if (!wait_bounded(empty0 + 8u * stage, ((kk / p.n_stages) & 1u) ^ 1u))
                         dead = 1;
-                    } else {
-                        const uint32_t fb = full0 + 8u * stage;
+                    else
                         brc::mbar_arrive_expect_tx(fb, C::STAGE_BYTES);
-                        const uint32_t dst = brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES);
-#pragma unroll
-                        for (int bx = 0; bx < C::BOXES; ++bx) {
-                            brc::tma_load_2d(dst + bx * 2048, &tm_k, bx * 64, (int32_t)r, fb, policy);
-                            brc::tma_load_2d(dst + C::TILE_BYTES + bx * 2048, &tm_v, bx * 64, (int32_t)r, fb, policy);
-                        }
-                        issued = kk + 1;
-                    }
                 }
                 dead = __shfl_sync(0xffffffffu, dead, 0);
                 if (dead) break;
+                // One operation per 64-column group, each bringing that group of the K tile and of the
+                // V tile (box 64 x 16 rows x {K, V}); the groups are issued by neighbouring lanes of one
+                // instruction.  Shared memory: [group][K|V][row][64 columns], 128-byte swizzled.
+                if (lane < C::BOXES)
+                    brc::tma_load_3d(brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES) + lane * 4096u, &tm_kv,
+                                     (int32_t)(lane * 64u), (int32_t)r, 0, fb, policy);
+                issued = kk + 1;
             }
         }
         if (dead && lane == 0) {
             atomicOr(p.status, BRC_DEV_WAIT_LIMIT);
             p.status[1] = 1000000u + blockIdx.x;
-            // Let the copies already in flight land before this CTA's shared memory is released.
+        }
+        // Nothing may still be landing in this CTA's shared memory when it is released: wait (bounded)
+        // for the copies of the last ring's worth of pages, whatever the consumers did with them.
+        if (lane == 0) {
             const uint32_t first = issued > p.n_stages ? issued - p.n_stages : 0;
             for (uint32_t kk = first; kk < issued; ++kk)
                 wait_bounded(full0 + 8u * (kk % p.n_stages), (kk / p.n_stages) & 1u);
@@ -283,7 +283,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                 const uint32_t page_in_unit = a + kw - unit_first;
                 const uint32_t nv = min(16u, len - page_in_unit * 16u);  // live cells in this page (>= 1)
                 const uint32_t kbase = brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES);
-                const uint32_t vbase = kbase + C::TILE_BYTES;
+                const uint32_t vbase = kbase + 2048u;  // within each 4 KiB column group: K slab, then V slab
 
                 if (nv < 16u) {
                     // Cells past the sequence end may hold anything (NaN included); their scores are
@@ -291,7 +291,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                     for (uint32_t i = lane; i < (16u - nv) * 8u * C::BOXES; i += 32) {
                         const uint32_t row = nv + i / (8u * C::BOXES);
                         const uint32_t within = i % (8u * C::BOXES);
-                        const uint32_t addr = vbase + (within >> 3) * 2048u + row * 128u + (within & 7u) * 16u;
+                        const uint32_t addr = vbase + (within >> 3) * 4096u + row * 128u + (within & 7u) * 16u;
                         asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(addr), "r"(0u) : "memory");
                     }
                     __syncwarp();
@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 #pragma unroll
                 for (int ks = 0; ks < C::KSTEPS; ++ks) {
                     uint32_t af[4];
-                    brc::ldmatrix_x4(af, kbase + (ks >> 2) * 2048u + k_lane + ((k_x ^ ((ks & 3) * 2u)) << 4));
+                    brc::ldmatrix_x4(af, kbase + (ks >> 2) * 4096u + k_lane + ((k_x ^ ((ks & 3) * 2u)) << 4));
                     if (ks & 1) {
                         brc::mma_16816(sb, af, qh[ks][0], qh[ks][1]);
                         if (Q_F32) brc::mma_16816(sb, af, ql[Q_F32 ? ks : 0][0], ql[Q_F32 ? ks : 0][1]);
@@ -353,7 +353,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 #pragma unroll
                 for (int mt = 0; mt < C::MT; ++mt) {
                     uint32_t af[4];
-                    brc::ldmatrix_x4_trans(af, vbase + (mt >> 2) * 2048u + v_lane + ((v_x ^ ((mt & 3) * 2u)) << 4));
+                    brc::ldmatrix_x4_trans(af, vbase + (mt >> 2) * 4096u + v_lane + ((v_x ^ ((mt & 3) * 2u)) << 4));
                     brc::mma_16816(o[mt], af, bh0, bh1);
                     brc::mma_16816(o[mt], af, bl0, bl1);
                 }
@@ -590,7 +590,7 @@ brc_status launch_partial(brc_pool *pool, const DecodeParams &p, uint32_t grid, 
         configured[pool->device] = true;
     }
     brc_stage_begin(pool, BRC_STAGE_ATTN_PARTIAL, st);
-    kern<<<grid, NTHREADS, smem, st>>>(pool->tm_k, pool->tm_v, p);
+    kern<<<grid, NTHREADS, smem, st>>>(pool->tm_kv, p);
     brc_stage_end(pool, BRC_STAGE_ATTN_PARTIAL, st);
     BRC_CUDA(cudaGetLastError());
     return BRC_OK;

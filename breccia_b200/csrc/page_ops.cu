@@ -220,12 +220,12 @@ brc_status brc_page_gather(brc_pool *pool, uint32_t layer, const uint32_t *block
     if (brc_status rc = need_device_pool(pool, "brc_page_gather")) return rc;
     if (layer >= pool->n_layers)
         return brc_fail(BRC_ERR_INVALID, "brc_page_gather: layer %u but the pool has %u", layer, pool->n_layers);
-    if (!block_table_dev || !k_out_dev || !v_out_dev)
-        return brc_fail(BRC_ERR_INVALID, "brc_page_gather: NULL pointer");
     if ((uint64_t)n_tokens > (uint64_t)table_len * pool->page_tokens)
         return brc_fail(BRC_ERR_CAPACITY, "page_gather of %u cells but the block table holds %llu (%u pages)", n_tokens,
                         (unsigned long long)table_len * pool->page_tokens, table_len);
     if (n_tokens == 0) return BRC_OK;
+    if (!block_table_dev || !k_out_dev || !v_out_dev)
+        return brc_fail(BRC_ERR_INVALID, "brc_page_gather: NULL pointer");
     brc_device_guard guard(pool->device);
     const uint64_t work = (uint64_t)n_tokens * pool->n_kv_head * (pool->head_dim / 8u);
     const uint32_t grid = grid_for(work, 256, pool->sm_count, 8);

@@ -107,6 +107,26 @@ static brc_status make_map(CUtensorMap *tm, void *base, uint64_t rows, uint32_t 
     return BRC_OK;
 }
 
+// 3-D view (column, row, K|V) over the single allocation that holds both pools: strides ascend
+// (row = head_dim * 2 bytes, K|V = offset of the V pool), and one box [64 columns][page rows][2]
+// brings a 64-column group of the K tile and of the V tile of a page in one operation.
+static brc_status make_kv_map(CUtensorMap *tm, void *k_base, uint64_t v_offset_bytes, uint64_t rows, uint32_t head_dim,
+                              uint32_t page_tokens) {
+    encode_tiled_fn enc = get_encode_tiled();
+    if (!enc) return brc_fail(BRC_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {head_dim, rows, 2u};
+    cuuint64_t strides[2] = {(cuuint64_t)head_dim * 2u, v_offset_bytes};
+    cuuint32_t box[3] = {64u, page_tokens, 2u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, k_base, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return brc_fail(BRC_ERR_CUDA, "cuTensorMapEncodeTiled (3-D K|V view) failed with CUresult %d (rows %llu, V offset %llu)",
+                        (int)r, (unsigned long long)rows, (unsigned long long)v_offset_bytes);
+    return BRC_OK;
+}
+
 extern "C" {
 
 brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim,
@@ -144,14 +164,15 @@ brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n_kv_head
     p->layer_bytes = p->half_page_bytes * n_pages;
     const uint64_t bytes = p->layer_bytes * n_layers;
     cudaError_t e;
-    if ((e = cudaMalloc(&p->k_base, bytes)) != cudaSuccess || (e = cudaMalloc(&p->v_base, bytes)) != cudaSuccess ||
-        (e = cudaMalloc(&p->status_dev, 256)) != cudaSuccess ||
+    // K and V live in one allocation so a single tensor map can address both.
+    if ((e = cudaMalloc(&p->k_base, 2 * bytes)) != cudaSuccess || (e = cudaMalloc(&p->status_dev, 256)) != cudaSuccess ||
         (e = cudaMallocHost(&p->status_host, 256)) != cudaSuccess) {
         brc_status rc = brc_fail(BRC_ERR_CUDA, "brc_pool_create: allocating 2 x %llu bytes on device %d failed: %s",
                                  (unsigned long long)bytes, device, cudaGetErrorString(e));
         brc_pool_destroy(p);
         return rc;
     }
+    p->v_base = p->k_base + bytes;
     p->ids_cap = 1u << 16;
     if ((e = cudaMalloc(&p->ids_dev, (size_t)p->ids_cap * 2 * sizeof(uint32_t))) != cudaSuccess ||
         (e = cudaMemset(p->k_base, 0, bytes)) != cudaSuccess || (e = cudaMemset(p->v_base, 0, bytes)) != cudaSuccess ||
@@ -163,6 +184,7 @@ brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n_kv_head
     cudaDeviceGetAttribute(&p->sm_count, cudaDevAttrMultiProcessorCount, device);
     brc_status rc = make_map(&p->tm_k, p->k_base, rows, head_dim, page_tokens);
     if (rc == BRC_OK) rc = make_map(&p->tm_v, p->v_base, rows, head_dim, page_tokens);
+    if (rc == BRC_OK) rc = make_kv_map(&p->tm_kv, p->k_base, bytes, rows, head_dim, page_tokens);
     if (rc != BRC_OK) {
         brc_pool_destroy(p);
         return rc;
@@ -202,8 +224,7 @@ brc_status brc_pool_destroy(brc_pool *pool) {
     if (!pool) return BRC_OK;
     if (pool->device >= 0) {
         brc_device_guard guard(pool->device);
-        if (pool->k_base) cudaFree(pool->k_base);
-        if (pool->v_base) cudaFree(pool->v_base);
+        if (pool->k_base) cudaFree(pool->k_base);  // V is the second half of the same allocation
         if (pool->status_dev) cudaFree(pool->status_dev);
         if (pool->status_host) cudaFreeHost(pool->status_host);
         if (pool->ids_dev) cudaFree(pool->ids_dev);

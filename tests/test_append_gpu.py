@@ -58,8 +58,9 @@ def test_f16_store_rule_on_hard_bit_patterns(cuda_device):
     table = synth.permutation(11, n_pages)
     k_dev = torch.from_numpy(src.copy()).cuda()
     v_dev = torch.from_numpy(src[::-1].copy()).cuda()
-    _lib.call("brc_kv_append", pool.handle, 0, C.c_void_p(dev_u32(table).data_ptr()), n_pages,
-              C.c_void_p(dev_u32([0]).data_ptr()), 1, n_tok, None, n_tok, n_tok, C.c_void_p(k_dev.data_ptr()),
+    table_dev, pos_dev = dev_u32(table), dev_u32([0])   # named: they must outlive the launch
+    _lib.call("brc_kv_append", pool.handle, 0, C.c_void_p(table_dev.data_ptr()), n_pages,
+              C.c_void_p(pos_dev.data_ptr()), 1, n_tok, None, n_tok, n_tok, C.c_void_p(k_dev.data_ptr()),
               C.c_void_p(v_dev.data_ptr()), _lib.DTYPE_F32, None)
     pool.check()
     want_k = np.zeros(n_pages * 2 * 16 * 256 // 2, np.uint32)
@@ -83,13 +84,15 @@ def test_batched_ragged_append_matches_oracle(cuda_device, head_dim, n_kv):
     pool = KvPool(0, n_layers, n_kv, head_dim, n_pool)
     total = int(cu[-1])
     row = n_kv * head_dim
+    tables_dev, pos_dev, cu_dev = dev_u32(tables), dev_u32(pos0), dev_u32(cu)
     for layer in (0, 2):
         k = synth.normal(100 + layer, total * row, 0.5).reshape(total, row)
         v = synth.normal(200 + layer, total * row, 0.5).reshape(total, row)
-        _lib.call("brc_kv_append", pool.handle, layer, C.c_void_p(dev_u32(tables).data_ptr()), tables.shape[1],
-                  C.c_void_p(dev_u32(pos0).data_ptr()), pos0.size, 0, C.c_void_p(dev_u32(cu).data_ptr()), total,
-                  int((pos0 + counts).max()), C.c_void_p(torch.from_numpy(k).cuda().data_ptr()),
-                  C.c_void_p(torch.from_numpy(v).cuda().data_ptr()), _lib.DTYPE_F32, None)
+        k_dev, v_dev = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda()
+        _lib.call("brc_kv_append", pool.handle, layer, C.c_void_p(tables_dev.data_ptr()), tables.shape[1],
+                  C.c_void_p(pos_dev.data_ptr()), pos0.size, 0, C.c_void_p(cu_dev.data_ptr()), total,
+                  int((pos0 + counts).max()), C.c_void_p(k_dev.data_ptr()), C.c_void_p(v_dev.data_ptr()),
+                  _lib.DTYPE_F32, None)
         torch.cuda.synchronize()
         want_k = np.zeros(n_pool * n_kv * 16 * head_dim // 2, np.uint32)
         want_v = np.zeros_like(want_k)
@@ -103,8 +106,8 @@ def test_batched_ragged_append_matches_oracle(cuda_device, head_dim, n_kv):
     # f16 sources: stored as they are, subnormal bit patterns flushed to signed zero
     h = rng.integers(0, 1 << 16, (total, row), dtype=np.uint32).astype(np.uint16)
     hk = torch.from_numpy(h.view(np.int16)).cuda()
-    _lib.call("brc_kv_append", pool.handle, 1, C.c_void_p(dev_u32(tables).data_ptr()), tables.shape[1],
-              C.c_void_p(dev_u32(pos0).data_ptr()), pos0.size, 0, C.c_void_p(dev_u32(cu).data_ptr()), total,
+    _lib.call("brc_kv_append", pool.handle, 1, C.c_void_p(tables_dev.data_ptr()), tables.shape[1],
+              C.c_void_p(pos_dev.data_ptr()), pos0.size, 0, C.c_void_p(cu_dev.data_ptr()), total,
               int((pos0 + counts).max()), C.c_void_p(hk.data_ptr()), C.c_void_p(hk.data_ptr()), _lib.DTYPE_F16, None)
     pool.check()
     flushed = np.where((h & 0x7C00) == 0, h & 0x8000, h).astype(np.uint16)

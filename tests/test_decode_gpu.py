@@ -87,8 +87,9 @@ def _batch_case(n_head, n_kv, hd, lens, seed, n_layers=1, layer=0, gate=False, q
         for s, n in enumerate(lens):
             for c in range(int(n)):
                 live[tables[s, c // 16], c % 16] = True
-        k[~live] = 0xFFFF
-        v[~live] = 0xFFFF
+        dead = np.broadcast_to(~live[:, None, :, None], k.shape)
+        k[dead] = 0xFFFF
+        v[dead] = 0xFFFF
         pool.write(0, layer, k)
         pool.write(1, layer, v)
         k, v = k.reshape(-1), v.reshape(-1)

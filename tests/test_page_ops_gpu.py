@@ -19,7 +19,8 @@ def test_gather_through_a_scattered_table(cuda_device, head_dim, n_kv, n_tokens)
     pool = KvPool(0, 2, n_kv, head_dim, n_pages)
     k, v = fill_pool_from_host(pool, 1, 31)
     table = synth.permutation(9, n_pages)[:70]
-    kd, vd = pool.gather(1, dev_u32(table), n_tokens)
+    table_dev = dev_u32(table)
+    kd, vd = pool.gather(1, table_dev, n_tokens)
     pool.check()
     if n_tokens:
         kb, _ = oracle.gather(k, table, n_tokens, n_kv, head_dim)
@@ -27,7 +28,7 @@ def test_gather_through_a_scattered_table(cuda_device, head_dim, n_kv, n_tokens)
         assert np.array_equal(kd.view(torch.int16).cpu().numpy().view(np.uint16), kb)
         assert np.array_equal(vd.view(torch.int16).cpu().numpy().view(np.uint16), vb)
     L = _lib.load()
-    assert L.brc_page_gather(pool.handle, 1, C.c_void_p(dev_u32(table).data_ptr()), 70, 70 * 16 + 1,
+    assert L.brc_page_gather(pool.handle, 1, C.c_void_p(table_dev.data_ptr()), 70, 70 * 16 + 1,
                              C.c_void_p(kd.data_ptr()), C.c_void_p(vd.data_ptr()), None) == _lib.ERR_CAPACITY
     pool.release()
 
