@@ -40,6 +40,7 @@ struct brc_pool {
     // 3-D view over both: (column, row, {K, V}); one box = a 64-column group of the K tile and of the V
     // tile of one page of one kv head.
     alignas(64) CUtensorMap tm_kv;
+    alignas(64) CUtensorMap tm_kv2;  // same view, box of 2 * page_tokens rows (two kv heads); even n_kv_head only
     bool has_tma = false;
 
     // per-stage GPU timers (off unless brc_timing_enable)

@@ -6,20 +6,25 @@
 // qsa_attn_apply_reduce.comp).  The reference materialises the score matrix in memory and re-reads V
 // once per query head; here every cached byte is read from HBM exactly once per step:
 //
-//   * work unit = (sequence, kv head); its pages form one flat list of "page-units" over the whole
-//     batch, cut into equal contiguous shares, one per CTA (one CTA per SM), so every SM streams the
-//     same number of 16 KiB page tiles whatever the length distribution;
-//   * a producer warp walks the block table and issues, per page, one TMA tiled load per 64-column
-//     group (a 3-D box [64 columns][16 rows][K|V] over a view that spans the K and the V pool, 128-byte
-//     swizzle) into a shared-memory ring guarded by full/empty mbarriers;
-//   * four consumer warps take pages round-robin.  Per page: S^T[16 cells x 8 heads] = K . Q^T with
-//     mma.sync m16n8k16 (K fragments by ldmatrix from the swizzled tile, Q^T fragments resident in
-//     registers), online softmax in base 2 with warp shuffles across the cell dimension, the
-//     probabilities transposed in registers by movmatrix into the B operand, and
-//     O^T[head_dim x 8 heads] += V^T . P^T with V^T fragments from ldmatrix.trans.  P is split into a
-//     binary16 head and tail so the product carries ~22 significant bits;
-//   * at the end of a unit's share the warps merge (m, l, O) through shared memory and write one
-//     partial; the combine kernel merges the partials of a unit, normalises and applies the gate.
+//   * work unit = (sequence, group of KVB kv heads); KVB = 2 when the number of kv heads is even, so a
+//     page's rows of two neighbouring kv heads (contiguous in the pool) travel together.  The pages of
+//     all units form one flat list of "page-units", cut into equal contiguous shares, one per CTA
+//     (one CTA per SM), so every SM streams the same number of tiles whatever the length distribution;
+//   * a producer warp walks the block table and issues, per page-unit, one TMA tiled load per
+//     64-column group: a 3-D box [64 columns][16 KVB rows][K|V] over a view that spans the K and the
+//     V pool (128-byte swizzle), 8 KiB per operation at KVB = 2.  Measured on B200, a TMA operation
+//     costs >= ~215 SM cycles whatever its size, so 4 KiB operations cap a SM at ~19 B/cycle while
+//     8 KiB operations reach the HBM limit (~26 B/cycle/SM); this is why two kv heads share a box.
+//     Stages of a shared-memory ring are guarded by full/empty mbarriers;
+//   * four consumer warps: warp w serves kv head (w % KVB) of every (w / KVB)-th page-unit.  Per page:
+//     S^T[16 cells x 8 heads] = K . Q^T with mma.sync m16n8k16 (K fragments by ldmatrix from the
+//     swizzled tile, Q^T fragments resident in registers), online softmax in base 2 with warp shuffles
+//     across the cell dimension, the probabilities transposed in registers by movmatrix into the B
+//     operand, and O^T[head_dim x 8 heads] += V^T . P^T with V^T fragments from ldmatrix.trans.  P is
+//     split into a binary16 head and tail so the product carries ~22 significant bits;
+//   * at the end of a unit's share the warps merge (m, l, O) per kv head through shared memory and
+//     write one partial per kv head; the combine kernel merges the partials of a unit, normalises and
+//     applies the gate.
 //
 // HBM-bound by design: 8 FLOP per cached byte, all of it on the tensor pipe.
 #include <algorithm>
@@ -31,19 +36,22 @@ namespace {
 
 constexpr int NW = 4;                      // consumer warps
 constexpr int NTHREADS = (NW + 1) * 32;    // + one producer warp
-constexpr int MAX_UNITS = 2048;            // (sequence, kv head) units per launch
+constexpr int MAX_UNITS = 2048;            // (sequence, kv-head group) units per launch
 constexpr int GROUP_TILE = 8;              // query heads per kv head held by one n-tile
 constexpr uint32_t SMEM_LIMIT = 232448;    // 227 KiB opt-in maximum per CTA
-constexpr uint64_t WAIT_NS = 4000000000ull;
+constexpr uint64_t WAIT_NS = 1000000000ull;  // one second: far beyond any legitimate wait here
 
-template <int HD>
+template <int HD, int KVB>
 struct Cfg {
     static constexpr int KSTEPS = HD / 16;
     static constexpr int MT = HD / 16;
-    static constexpr int BOXES = HD / 64;
-    static constexpr int TILE_BYTES = 16 * HD * 2;
-    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-    static constexpr int OPAD = HD + 4;                          // padded row of the merge scratch
+    static constexpr int BOXES = HD / 64;                  // 64-column groups = TMA operations per stage
+    static constexpr int ROWS = 16 * KVB;                  // pool rows per box: 16 cells of KVB kv heads
+    static constexpr int SLAB_BYTES = ROWS * 128;          // one [rows][64 columns] slab
+    static constexpr int GROUP_BYTES = 2 * SLAB_BYTES;     // K slab then V slab of one column group
+    static constexpr int STAGE_BYTES = BOXES * GROUP_BYTES;
+    static constexpr int NWP = NW / KVB;                   // warps that share one kv head (page interleave)
+    static constexpr int OPAD = HD + 4;                    // padded row of the merge scratch
     static constexpr int SCRATCH_WARP = GROUP_TILE * OPAD + 16;  // floats per warp
     static constexpr int SCRATCH_BYTES = NW * SCRATCH_WARP * 4;
     static constexpr int PREFIX_BYTES = (MAX_UNITS + 4) * 4;
@@ -55,8 +63,8 @@ struct DecodeParams {
     const void *q;                 // [n_seqs][n_head][HD]
     const uint32_t *block_tables;  // [n_seqs][table_stride]
     const uint32_t *seq_lens;      // [n_seqs]
-    float *part_acc;               // [slots][GROUP_TILE][HD]
-    float *part_ml;                // [slots][GROUP_TILE][2]
+    float *part_acc;               // [slots][KVB][GROUP_TILE][HD]
+    float *part_ml;                // [slots][KVB][GROUP_TILE][2]
     uint32_t *status;
     uint32_t n_seqs, table_stride, max_seq_len;
     uint32_t n_kv_head, group, n_head;
@@ -99,10 +107,10 @@ __device__ __forceinline__ uint32_t share_begin(uint32_t cta, uint32_t total, ui
     return (uint32_t)(((uint64_t)cta * total) / n_cta);
 }
 
-template <int HD, bool Q_F32>
+template <int HD, bool Q_F32, int KVB>
 __global__ void __launch_bounds__(NTHREADS, 1)
     decode_partial_kernel(const __grid_constant__ CUtensorMap tm_kv, const DecodeParams p) {
-    using C = Cfg<HD>;
+    using C = Cfg<HD, KVB>;
     extern __shared__ uint8_t smem_raw[];
     // The 128-byte swizzle pattern repeats every 1024 bytes: tiles must start on that boundary.
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
@@ -114,12 +122,13 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     const uint32_t empty0 = full0 + 8u * p.n_stages;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t n_units = p.n_seqs * p.n_kv_head;
+    const uint32_t n_groups = p.n_kv_head / KVB;   // kv-head groups per sequence
+    const uint32_t n_units = p.n_seqs * n_groups;
 
     if (tid == 0) {
         for (uint32_t i = 0; i < p.n_stages; ++i) {
             brc::mbar_init(full0 + 8u * i, 1);
-            brc::mbar_init(empty0 + 8u * i, 1);
+            brc::mbar_init(empty0 + 8u * i, KVB);   // every kv head's warp hands the stage back
         }
         brc::mbar_fence_init();
         brc::tma_prefetch_desc(&tm_kv);
@@ -131,7 +140,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             const uint32_t u = base + lane;
             uint32_t pg = 0;
             if (u < n_units) {
-                uint32_t len = p.seq_lens[u / p.n_kv_head];
+                uint32_t len = p.seq_lens[u / n_groups];
                 if (len > p.max_seq_len) {
                     atomicOr(p.status, BRC_DEV_BAD_POS);
                     p.status[1] = len;
@@ -169,14 +178,14 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             if (k < count) {
                 const uint32_t g = a + k;
                 const uint32_t u = unit_of(S, n_units, g);
-                const uint32_t s = u / p.n_kv_head, kvh = u % p.n_kv_head;
+                const uint32_t s = u / n_groups, kv0 = (u % n_groups) * KVB;
                 uint32_t page = __ldg(p.block_tables + (uint64_t)s * p.table_stride + (g - S[u]));
                 if (page >= p.n_pages) {
                     atomicOr(p.status, BRC_DEV_BAD_PAGE);
                     p.status[1] = page;
                     page = 0;  // stay inside the pool; the result of this unit is void and the call reports it
                 }
-                row = p.layer_row0 + (page * p.n_kv_head + kvh) * 16u;
+                row = p.layer_row0 + (page * p.n_kv_head + kv0) * 16u;
             }
             const uint32_t n_here = min(32u, count - k0);
             for (uint32_t i = 0; i < n_here; ++i) {
@@ -192,11 +201,10 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                 }
                 dead = __shfl_sync(0xffffffffu, dead, 0);
                 if (dead) break;
-                // One operation per 64-column group, each bringing that group of the K tile and of the
-                // V tile (box 64 x 16 rows x {K, V}); the groups are issued by neighbouring lanes of one
-                // instruction.  Shared memory: [group][K|V][row][64 columns], 128-byte swizzled.
+                // One operation per 64-column group (issued by neighbouring lanes of one instruction).
+                // Shared memory: [group][K|V][row = kv head * 16 + cell][64 columns], 128-byte swizzled.
                 if (lane < C::BOXES)
-                    brc::tma_load_3d(brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES) + lane * 4096u, &tm_kv,
+                    brc::tma_load_3d(brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES) + lane * C::GROUP_BYTES, &tm_kv,
                                      (int32_t)(lane * 64u), (int32_t)r, 0, fb, policy);
                 issued = kk + 1;
             }
@@ -207,8 +215,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         }
         // Nothing may still be landing in this CTA's shared memory when it is released: wait (bounded)
         // for the copies of the last ring's worth of pages, whatever the consumers did with them.
+        // Only those: an earlier page's barrier has since moved on to a later page's phase.
         if (lane == 0) {
-            const uint32_t first = issued > p.n_stages ? issued - p.n_stages : 0;
+            const uint32_t first = count > p.n_stages ? count - p.n_stages : 0;
             for (uint32_t kk = first; kk < issued; ++kk)
                 wait_bounded(full0 + 8u * (kk % p.n_stages), (kk / p.n_stages) & 1u);
         }
@@ -216,25 +225,28 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     }
 
     // ---------------------------------------------------------------------- consumer warps
+    const uint32_t kl = warp % KVB;           // kv head of the group this warp serves
+    const uint32_t cw = warp / KVB;           // its place among the NWP warps that interleave pages
     const uint32_t t0 = lane >> 2;            // cell row of c0/c1 (c2/c3: +8); also the head of the B operand
     const uint32_t h0 = (lane & 3u) * 2u;     // head column of c0/c2 (c1/c3: +1)
-    // ldmatrix lane constants (see the swizzle note in the file header).
+    // ldmatrix lane constants.  A slab row is 128 bytes; 16-byte chunk j of row r sits at chunk
+    // j ^ (r & 7) (the TMA 128-byte swizzle); this kv head's rows start at kl * 16, a multiple of 8.
     const uint32_t k_r = (lane & 7u) + ((lane >> 3) & 1u) * 8u;
     const uint32_t k_x = (lane >> 4) ^ (k_r & 7u);
-    const uint32_t k_lane = k_r * 128u;
+    const uint32_t k_lane = (kl * 16u + k_r) * 128u;
     const uint32_t v_r = (lane & 7u) + (lane >> 4) * 8u;
     const uint32_t v_x = ((lane >> 3) & 1u) ^ (v_r & 7u);
-    const uint32_t v_lane = v_r * 128u;
+    const uint32_t v_lane = C::SLAB_BYTES + (kl * 16u + v_r) * 128u;
 
-    uint32_t kw = warp;                        // next local page index of this warp
-    uint32_t stage = warp % p.n_stages, parity = 0;
+    uint32_t kw = cw;                          // next local page-unit of this warp
+    uint32_t stage = cw % p.n_stages, parity = 0;
     uint32_t dead = 0;
 
     uint32_t u = unit_of(S, n_units, a);
     uint32_t g0 = a;
     while (g0 < b) {
         const uint32_t ge = min(b, S[u + 1]);
-        const uint32_t s = u / p.n_kv_head, kvh = u % p.n_kv_head;
+        const uint32_t s = u / n_groups, kvh = (u % n_groups) * KVB + kl;
         const uint32_t len = min(p.seq_lens[s], p.max_seq_len);
         const uint32_t unit_first = S[u];
 
@@ -269,29 +281,30 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
         const uint32_t local_end = ge - a;
-        for (; kw < local_end; kw += NW) {
+        for (; kw < local_end; kw += C::NWP) {
             if (!dead) {
                 if (!wait_bounded(full0 + 8u * stage, parity)) {
                     dead = 1;
                     if (lane == 0) {
                         atomicOr(p.status, BRC_DEV_WAIT_LIMIT);
                         p.status[1] = 2000000u + blockIdx.x;
+                        p.status[2] = kw;      // local page-unit the wait was for
+                        p.status[3] = count;   // page-units of this CTA's share
                     }
                 }
             }
             if (!dead) {
                 const uint32_t page_in_unit = a + kw - unit_first;
                 const uint32_t nv = min(16u, len - page_in_unit * 16u);  // live cells in this page (>= 1)
-                const uint32_t kbase = brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES);
-                const uint32_t vbase = kbase + 2048u;  // within each 4 KiB column group: K slab, then V slab
+                const uint32_t sbase = brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES);
 
                 if (nv < 16u) {
                     // Cells past the sequence end may hold anything (NaN included); their scores are
                     // masked below, and their V rows are cleared so 0 * NaN never reaches the sum.
                     for (uint32_t i = lane; i < (16u - nv) * 8u * C::BOXES; i += 32) {
-                        const uint32_t row = nv + i / (8u * C::BOXES);
+                        const uint32_t row = kl * 16u + nv + i / (8u * C::BOXES);
                         const uint32_t within = i % (8u * C::BOXES);
-                        const uint32_t addr = vbase + (within >> 3) * 4096u + row * 128u + (within & 7u) * 16u;
+                        const uint32_t addr = sbase + (within >> 3) * C::GROUP_BYTES + C::SLAB_BYTES + row * 128u + (within & 7u) * 16u;
                         asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(addr), "r"(0u) : "memory");
                     }
                     __syncwarp();
@@ -302,7 +315,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 #pragma unroll
                 for (int ks = 0; ks < C::KSTEPS; ++ks) {
                     uint32_t af[4];
-                    brc::ldmatrix_x4(af, kbase + (ks >> 2) * 4096u + k_lane + ((k_x ^ ((ks & 3) * 2u)) << 4));
+                    brc::ldmatrix_x4(af, sbase + (ks >> 2) * C::GROUP_BYTES + k_lane + ((k_x ^ ((ks & 3) * 2u)) << 4));
                     if (ks & 1) {
                         brc::mma_16816(sb, af, qh[ks][0], qh[ks][1]);
                         if (Q_F32) brc::mma_16816(sb, af, ql[Q_F32 ? ks : 0][0], ql[Q_F32 ? ks : 0][1]);
@@ -353,7 +366,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 #pragma unroll
                 for (int mt = 0; mt < C::MT; ++mt) {
                     uint32_t af[4];
-                    brc::ldmatrix_x4_trans(af, vbase + (mt >> 2) * 4096u + v_lane + ((v_x ^ ((mt & 3) * 2u)) << 4));
+                    brc::ldmatrix_x4_trans(af, sbase + (mt >> 2) * C::GROUP_BYTES + v_lane + ((v_x ^ ((mt & 3) * 2u)) << 4));
                     brc::mma_16816(o[mt], af, bh0, bh1);
                     brc::mma_16816(o[mt], af, bl0, bl1);
                 }
@@ -362,14 +375,14 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                 __syncwarp();
                 if (lane == 0) brc::mbar_arrive(empty0 + 8u * stage);
             }
-            stage += NW;
+            stage += C::NWP;
             if (stage >= p.n_stages) {
                 stage -= p.n_stages;
                 parity ^= 1u;
             }
         }
 
-        // ---- merge the four warps' (m, l, O) and write this share's partial for the unit
+        // ---- merge, per kv head, the (m, l, O) of its warps and write this share's partial
 #pragma unroll
         for (int off = 4; off < 32; off <<= 1) {
             l0 += __shfl_xor_sync(0xffffffffu, l0, off);
@@ -393,29 +406,30 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         }
         brc::named_bar_sync(1, NW * 32);
         {
-            const uint32_t slot = u + blockIdx.x;
-            float *acc_out = p.part_acc + (size_t)slot * GROUP_TILE * HD;
-            float *ml_out = p.part_ml + (size_t)slot * GROUP_TILE * 2;
-            for (uint32_t h = 0; h < p.group; ++h) {
-                float mw[NW], lw[NW], M = -INFINITY;
+            const size_t slot0 = (size_t)(u + blockIdx.x) * KVB;
+            for (uint32_t kh = 0; kh < KVB * p.group; ++kh) {
+                const uint32_t k2 = kh / p.group, h = kh % p.group;   // kv head of the group, query head
+                float *acc_out = p.part_acc + (slot0 + k2) * GROUP_TILE * HD;
+                float *ml_out = p.part_ml + (slot0 + k2) * GROUP_TILE * 2;
+                float mw[C::NWP], lw[C::NWP], M = -INFINITY;
 #pragma unroll
-                for (int w = 0; w < NW; ++w) {
-                    const float *ml = scratch + w * C::SCRATCH_WARP + GROUP_TILE * C::OPAD;
+                for (int w = 0; w < C::NWP; ++w) {
+                    const float *ml = scratch + (w * KVB + k2) * C::SCRATCH_WARP + GROUP_TILE * C::OPAD;
                     mw[w] = ml[h * 2];
                     lw[w] = ml[h * 2 + 1];
                     if (lw[w] > 0.f) M = fmaxf(M, mw[w]);
                 }
-                float L = 0.f, wt[NW];
+                float L = 0.f, wt[C::NWP];
 #pragma unroll
-                for (int w = 0; w < NW; ++w) {
+                for (int w = 0; w < C::NWP; ++w) {
                     wt[w] = lw[w] > 0.f ? brc::fast_exp2(mw[w] - M) : 0.f;
                     L += wt[w] * lw[w];
                 }
                 for (uint32_t d = tid; d < HD; d += NW * 32) {
                     float v = 0.f;
 #pragma unroll
-                    for (int w = 0; w < NW; ++w)
-                        if (wt[w] != 0.f) v += wt[w] * scratch[w * C::SCRATCH_WARP + h * C::OPAD + d];
+                    for (int w = 0; w < C::NWP; ++w)
+                        if (wt[w] != 0.f) v += wt[w] * scratch[(w * KVB + k2) * C::SCRATCH_WARP + h * C::OPAD + d];
                     acc_out[h * HD + d] = dead ? 0.f : v;
                 }
                 if (tid == 0) {
@@ -445,6 +459,7 @@ struct CombineParams {
     uint32_t n_seqs, n_kv_head, group, n_head, max_seq_len;
     uint32_t gate_head_stride;
     uint32_t n_cta;       // grid size of the partial kernel
+    uint32_t kvb;         // kv heads per unit in the partial kernel
 };
 
 __device__ __forceinline__ float sigmoid_f32(float x) {
@@ -458,14 +473,15 @@ __global__ void __launch_bounds__(HD) decode_combine_kernel(const CombineParams 
     __shared__ uint32_t red[2][HD / 32];
     const uint32_t s = blockIdx.x / p.n_head, h = blockIdx.x % p.n_head;
     const uint32_t kvh = h / p.group, hl = h % p.group;
-    const uint32_t u = s * p.n_kv_head + kvh;
-    const uint32_t n_units = p.n_seqs * p.n_kv_head;
+    const uint32_t n_groups = p.n_kv_head / p.kvb;
+    const uint32_t u = s * n_groups + kvh / p.kvb, kl = kvh % p.kvb;
+    const uint32_t n_units = p.n_seqs * n_groups;
     const uint32_t tid = threadIdx.x;
 
     // pages before this unit and in total
     uint32_t before = 0, total = 0;
     for (uint32_t i = tid; i < n_units; i += HD) {
-        const uint32_t pg = pages_of(min(p.seq_lens[i / p.n_kv_head], p.max_seq_len));
+        const uint32_t pg = pages_of(min(p.seq_lens[i / n_groups], p.max_seq_len));
         total += pg;
         if (i < u) before += pg;
     }
@@ -502,12 +518,12 @@ __global__ void __launch_bounds__(HD) decode_combine_kernel(const CombineParams 
         // A CTA whose share is empty (fewer page-units than CTAs) wrote no partial: skip its slot.
         for (uint32_t i = i_lo; i <= i_hi; ++i) {
             if (share_begin(i, total, p.n_cta) == share_begin(i + 1, total, p.n_cta)) continue;
-            const float *ml = p.part_ml + ((size_t)(u + i) * GROUP_TILE + hl) * 2;
+            const float *ml = p.part_ml + (((size_t)(u + i) * p.kvb + kl) * GROUP_TILE + hl) * 2;
             if (ml[1] > 0.f) M = fmaxf(M, ml[0]);
         }
         for (uint32_t i = i_lo; i <= i_hi; ++i) {
             if (share_begin(i, total, p.n_cta) == share_begin(i + 1, total, p.n_cta)) continue;
-            const size_t slot = u + i;
+            const size_t slot = (size_t)(u + i) * p.kvb + kl;
             const float *ml = p.part_ml + (slot * GROUP_TILE + hl) * 2;
             const float l = ml[1];
             if (!(l > 0.f)) continue;
@@ -559,41 +575,57 @@ __global__ void __launch_bounds__(HD)
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
-uint32_t stages_for(uint32_t head_dim) {
-    const uint32_t stage = head_dim == 256 ? Cfg<256>::STAGE_BYTES : Cfg<128>::STAGE_BYTES;
-    const uint32_t fixed = head_dim == 256 ? Cfg<256>::FIXED_BYTES : Cfg<128>::FIXED_BYTES;
-    return std::min<uint32_t>((SMEM_LIMIT - fixed) / stage, 24u);
+uint32_t kvb_of(const brc_pool *pool) { return pool->n_kv_head % 2u == 0u ? 2u : 1u; }
+
+uint32_t stage_bytes_of(uint32_t head_dim, uint32_t kvb) { return kvb * 2u * 16u * head_dim * 2u; }
+
+uint32_t fixed_bytes_of(uint32_t head_dim) {
+    return head_dim == 256 ? Cfg<256, 1>::FIXED_BYTES : Cfg<128, 1>::FIXED_BYTES;  // independent of KVB
 }
 
-uint32_t smem_for(uint32_t head_dim, uint32_t n_stages) {
-    const uint32_t stage = head_dim == 256 ? Cfg<256>::STAGE_BYTES : Cfg<128>::STAGE_BYTES;
-    const uint32_t fixed = head_dim == 256 ? Cfg<256>::FIXED_BYTES : Cfg<128>::FIXED_BYTES;
-    return n_stages * stage + fixed;
+// Ring depth: what fits, rounded down to a multiple of the NW / KVB warps that interleave page-units.
+// Page-unit kk uses stage kk % n_stages and consumer slot kk % (NW / KVB); with the multiple, a stage
+// is always consumed by the same warps.  This matters: a parity wait on an mbarrier is only valid if
+// the waiter knows the previous phase of that barrier has completed.  A warp that has itself consumed
+// round r - 1 of a stage knows; a different warp asking for round r while round r - 1 is still
+// landing would see "parity r done" (it is round r - 2 that is), read a half-written stage and hand
+// it back a second time.
+uint32_t stages_for(uint32_t head_dim, uint32_t kvb) {
+    const uint32_t fit = std::min<uint32_t>((SMEM_LIMIT - fixed_bytes_of(head_dim)) / stage_bytes_of(head_dim, kvb), 24u);
+    const uint32_t nwp = NW / kvb;
+    return fit / nwp * nwp;
 }
 
-uint32_t seqs_per_launch(const brc_pool *pool) { return MAX_UNITS / pool->n_kv_head; }
+uint32_t seqs_per_launch(const brc_pool *pool) { return MAX_UNITS / (pool->n_kv_head / kvb_of(pool)); }
 
 uint32_t grid_ctas(const brc_pool *pool) { return (uint32_t)(pool->sm_count > 0 ? pool->sm_count : 148); }
 
-// Workspace: partial slots for one launch (units + CTAs), acc then (m, l).
+// Workspace: partial slots for one launch, (units + CTAs) x KVB kv heads; acc then (m, l).
 uint64_t slots_for(const brc_pool *pool, uint32_t n_seqs) {
     const uint32_t per = std::min<uint32_t>(n_seqs, seqs_per_launch(pool));
-    return (uint64_t)per * pool->n_kv_head + grid_ctas(pool);
+    const uint32_t kvb = kvb_of(pool);
+    return ((uint64_t)per * (pool->n_kv_head / kvb) + grid_ctas(pool)) * kvb;
 }
 
-template <int HD, bool Q_F32>
+template <int HD, bool Q_F32, int KVB>
 brc_status launch_partial(brc_pool *pool, const DecodeParams &p, uint32_t grid, uint32_t smem, cudaStream_t st) {
     static bool configured[64] = {};
-    auto kern = decode_partial_kernel<HD, Q_F32>;
+    auto kern = decode_partial_kernel<HD, Q_F32, KVB>;
     if (pool->device < 64 && !configured[pool->device]) {
         BRC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT));
         configured[pool->device] = true;
     }
     brc_stage_begin(pool, BRC_STAGE_ATTN_PARTIAL, st);
-    kern<<<grid, NTHREADS, smem, st>>>(pool->tm_kv, p);
+    kern<<<grid, NTHREADS, smem, st>>>(KVB == 2 ? pool->tm_kv2 : pool->tm_kv, p);
     brc_stage_end(pool, BRC_STAGE_ATTN_PARTIAL, st);
     BRC_CUDA(cudaGetLastError());
     return BRC_OK;
+}
+
+template <int HD, bool Q_F32>
+brc_status launch_partial_kvb(brc_pool *pool, const DecodeParams &p, uint32_t grid, uint32_t smem, cudaStream_t st) {
+    return kvb_of(pool) == 2 ? launch_partial<HD, Q_F32, 2>(pool, p, grid, smem, st)
+                             : launch_partial<HD, Q_F32, 1>(pool, p, grid, smem, st);
 }
 
 brc_status validate_decode(const brc_pool *pool, const char *who, uint32_t layer, const void *q, int32_t q_dtype,
@@ -603,7 +635,6 @@ brc_status validate_decode(const brc_pool *pool, const char *who, uint32_t layer
     if (pool->device < 0 || !pool->has_tma)
         return brc_fail(BRC_ERR_CUDA, "%s: this pool holds bookkeeping only (no device memory); compute calls need a GPU pool", who);
     if (layer >= pool->n_layers) return brc_fail(BRC_ERR_INVALID, "%s: layer %u but the pool has %u", who, layer, pool->n_layers);
-    if (!q || !bt || !lens || !out) return brc_fail(BRC_ERR_INVALID, "%s: NULL query, block table, length or output pointer", who);
     if (q_dtype != BRC_DTYPE_F32 && q_dtype != BRC_DTYPE_F16)
         return brc_fail(BRC_ERR_INVALID, "%s: q_dtype %d is neither f32 (0) nor f16 (1)", who, q_dtype);
     if (n_head == 0 || n_head % pool->n_kv_head != 0)
@@ -615,27 +646,28 @@ brc_status validate_decode(const brc_pool *pool, const char *who, uint32_t layer
     if (max_seq_len > capacity)
         return brc_fail(BRC_ERR_CAPACITY, "%s would read cells up to %u but each block table holds %llu (%u pages of %u cells)",
                         who, max_seq_len, (unsigned long long)capacity, table_stride, pool->page_tokens);
+    if (n_seqs == 0) return BRC_OK;
+    if (!q || !bt || !lens || !out) return brc_fail(BRC_ERR_INVALID, "%s: NULL query, block table, length or output pointer", who);
     if ((reinterpret_cast<uintptr_t>(q) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u))
         return brc_fail(BRC_ERR_INVALID, "%s: query and output pointers must be 16-byte aligned", who);
-    if (n_seqs) {
-        uint64_t need = 0;
-        brc_decode_workspace_bytes(pool, n_seqs, n_head, &need);
-        if (!ws || ws_bytes < need)
-            return brc_fail(BRC_ERR_INVALID, "%s: workspace of %llu bytes, %llu needed", who, (unsigned long long)ws_bytes,
-                            (unsigned long long)need);
-    }
+    uint64_t need = 0;
+    brc_decode_workspace_bytes(pool, n_seqs, n_head, &need);
+    if (!ws || ws_bytes < need)
+        return brc_fail(BRC_ERR_INVALID, "%s: workspace of %llu bytes, %llu needed", who, (unsigned long long)ws_bytes,
+                        (unsigned long long)need);
     return BRC_OK;
 }
 
-// mode_partial: out = merged acc, out_ml = (m, l); else final output.
+// out_ml != nullptr: partial mode (out = merged acc, out_ml = (m, l)); else final output.
 brc_status run_decode(brc_pool *pool, uint32_t layer, const void *q, int32_t q_dtype, uint32_t n_head, const float *gate,
                       uint32_t gate_head_stride, const uint32_t *bt, uint32_t table_stride, const uint32_t *lens,
                       uint32_t n_seqs, uint32_t max_seq_len, float scale, float *out, float *out_ml, void *ws,
                       cudaStream_t st) {
     brc_device_guard guard(pool->device);
     const uint32_t hd = pool->head_dim;
-    const uint32_t n_stages = stages_for(hd);
-    const uint32_t smem = smem_for(hd, n_stages);
+    const uint32_t kvb = kvb_of(pool);
+    const uint32_t n_stages = stages_for(hd, kvb);
+    const uint32_t smem = n_stages * stage_bytes_of(hd, kvb) + fixed_bytes_of(hd);
     const uint32_t grid = grid_ctas(pool);
     const uint32_t per = seqs_per_launch(pool);
     const uint64_t slots = slots_for(pool, n_seqs);
@@ -663,11 +695,11 @@ brc_status run_decode(brc_pool *pool, uint32_t layer, const void *q, int32_t q_d
         p.scale_log2 = scale * 1.4426950408889634f;
         brc_status rc;
         if (hd == 256)
-            rc = q_dtype == BRC_DTYPE_F32 ? launch_partial<256, true>(pool, p, grid, smem, st)
-                                          : launch_partial<256, false>(pool, p, grid, smem, st);
+            rc = q_dtype == BRC_DTYPE_F32 ? launch_partial_kvb<256, true>(pool, p, grid, smem, st)
+                                          : launch_partial_kvb<256, false>(pool, p, grid, smem, st);
         else
-            rc = q_dtype == BRC_DTYPE_F32 ? launch_partial<128, true>(pool, p, grid, smem, st)
-                                          : launch_partial<128, false>(pool, p, grid, smem, st);
+            rc = q_dtype == BRC_DTYPE_F32 ? launch_partial_kvb<128, true>(pool, p, grid, smem, st)
+                                          : launch_partial_kvb<128, false>(pool, p, grid, smem, st);
         if (rc != BRC_OK) return rc;
         CombineParams c;
         c.part_acc = part_acc;
@@ -683,6 +715,7 @@ brc_status run_decode(brc_pool *pool, uint32_t layer, const void *q, int32_t q_d
         c.max_seq_len = max_seq_len;
         c.gate_head_stride = gate_head_stride;
         c.n_cta = grid;
+        c.kvb = kvb;
         brc_stage_begin(pool, BRC_STAGE_ATTN_COMBINE, st);
         if (hd == 256)
             decode_combine_kernel<256><<<ns * n_head, 256, 0, st>>>(c);

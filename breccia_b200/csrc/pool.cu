@@ -185,6 +185,10 @@ brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n_kv_head
     brc_status rc = make_map(&p->tm_k, p->k_base, rows, head_dim, page_tokens);
     if (rc == BRC_OK) rc = make_map(&p->tm_v, p->v_base, rows, head_dim, page_tokens);
     if (rc == BRC_OK) rc = make_kv_map(&p->tm_kv, p->k_base, bytes, rows, head_dim, page_tokens);
+    // With an even number of kv heads, the rows of two neighbouring kv heads of a page are contiguous:
+    // a box of 2 * page_tokens rows brings both (8 KiB per operation instead of 4 KiB).
+    if (rc == BRC_OK && n_kv_head % 2u == 0u)
+        rc = make_kv_map(&p->tm_kv2, p->k_base, bytes, rows, head_dim, 2u * page_tokens);
     if (rc != BRC_OK) {
         brc_pool_destroy(p);
         return rc;
@@ -329,7 +333,8 @@ brc_status brc_pool_check(brc_pool *pool, void *stream) {
     const uint32_t detail = pool->status_host[1];
     if (w == 0) return BRC_OK;
     if (w & BRC_DEV_WAIT_LIMIT)
-        return brc_fail(BRC_ERR_TIMEOUT, "a kernel gave up a bounded wait (check word 0x%x, detail %u)", w, detail);
+        return brc_fail(BRC_ERR_TIMEOUT, "a kernel gave up a bounded wait (check word 0x%x, detail %u, at %u of %u)", w, detail,
+                        pool->status_host[2], pool->status_host[3]);
     return brc_fail(BRC_ERR_DEVICE_CHECK,
                     "a kernel refused an index: check word 0x%x (%s%s%s), last offending value %u", w,
                     (w & BRC_DEV_BAD_PAGE) ? "page id >= n_pages " : "", (w & BRC_DEV_BAD_POS) ? "position past bound " : "",

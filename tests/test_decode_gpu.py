@@ -126,10 +126,45 @@ def test_reference_geometry_shapes_2062_cells_with_gate(cuda_device):
     pool.release()
 
 
-@pytest.mark.parametrize("n_head,n_kv,hd", [(16, 2, 256), (8, 2, 256), (4, 4, 256), (32, 4, 128), (6, 2, 128)])
+@pytest.mark.parametrize("n_head,n_kv,hd", [(16, 2, 256), (8, 2, 256), (4, 4, 256), (32, 4, 128), (6, 2, 128), (8, 1, 256), (12, 3, 128)])
 def test_geometries(cuda_device, n_head, n_kv, hd):
     pool, _, _, got, want = _batch_case(n_head, n_kv, hd, [333, 48, 1000], seed=60 + n_head, n_layers=2, layer=1)
     assert_attention_close(got, want, f"{n_head}q/{n_kv}kv hd{hd}")
+    pool.release()
+
+
+def test_cfg2_layer_at_full_size_matches_oracle_and_repeats_bit_identically(cuda_device):
+    """One layer of BASELINE config 2 at full size (32 sequences, lengths uniform in [512, 8192],
+    pages scattered in a pool of 1.25x need: every CTA streams dozens of pages through its ring and
+    crosses several sequence boundaries).  Output in tolerance against the oracle, and ten
+    back-to-back launches give bit-identical results."""
+    n_head, n_kv, hd = 16, 2, 256
+    lens = synth.uniform_ints(20261125, 32, 512, 8192)
+    tables, n_pool = synth.scattered_tables(20261125 + 7, lens, pool_factor=1.25)
+    pool = KvPool(0, 1, n_kv, hd, n_pool)
+    rng = np.random.default_rng(5)
+    n = n_pool * n_kv * 16 * hd
+    k = np.empty(n, np.uint16)
+    v = np.empty(n, np.uint16)
+    for at in range(0, n, 1 << 22):
+        m = min(1 << 22, n - at)
+        k[at:at + m] = oracle.f32_to_f16_bits_np(rng.standard_normal(m, dtype=np.float32) * np.float32(0.5))
+        v[at:at + m] = oracle.f32_to_f16_bits_np(rng.standard_normal(m, dtype=np.float32) * np.float32(0.5))
+    pool.write(0, 0, k)
+    pool.write(1, 0, v)
+    q32 = oracle.to_f16(synth.normal(77, lens.size * n_head * hd, 1.0)).reshape(lens.size, n_head, hd)
+    qd = torch.from_numpy(q32).cuda().half()
+    batch = DecodeBatch(pool, n_head, tables, lens)
+    outs = [torch.full((lens.size, n_head, hd), float("nan"), device="cuda") for _ in range(10)]
+    for o in outs:
+        batch.attend(0, qd, o)
+    pool.check()
+    want, _ = oracle.decode_batch(k, v, tables, lens, q32, n_head, n_kv, hd)
+    got = outs[0].cpu().numpy()
+    errs = assert_attention_close(got, want, "cfg2 layer")
+    print("cfg2 layer max_abs %.2e max_rel %.2e ref_measure %.2e" % errs)
+    for o in outs[1:]:
+        assert np.array_equal(o.cpu().numpy(), got)
     pool.release()
 
 
