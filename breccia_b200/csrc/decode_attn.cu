@@ -51,7 +51,7 @@ struct Cfg {
     static constexpr int GROUP_BYTES = 2 * SLAB_BYTES;     // K slab then V slab of one column group
     static constexpr int STAGE_BYTES = BOXES * GROUP_BYTES;
     static constexpr int NWP = NW / KVB;                   // warps that share one kv head (page interleave)
-    static constexpr int OPAD = HD + 4;                    // padded row of the merge scratch
+    static constexpr int OPAD = HD / 2 + 4;                // padded row of the merge scratch (half of head_dim)
     static constexpr int SCRATCH_WARP = GROUP_TILE * OPAD + 16;  // floats per warp
     static constexpr int SCRATCH_BYTES = NW * SCRATCH_WARP * 4;
     static constexpr int PREFIX_BYTES = (MAX_UNITS + 4) * 4;
@@ -388,15 +388,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             l0 += __shfl_xor_sync(0xffffffffu, l0, off);
             l1 += __shfl_xor_sync(0xffffffffu, l1, off);
         }
+        // The exchange goes through shared memory in two halves of head_dim (half the scratch, which
+        // buys the ring more stages).
         float *sw = scratch + warp * C::SCRATCH_WARP;
-#pragma unroll
-        for (int mt = 0; mt < C::MT; ++mt) {
-            const uint32_t d0 = mt * 16 + t0;
-            sw[h0 * C::OPAD + d0] = o[mt][0];
-            sw[(h0 + 1) * C::OPAD + d0] = o[mt][1];
-            sw[h0 * C::OPAD + d0 + 8] = o[mt][2];
-            sw[(h0 + 1) * C::OPAD + d0 + 8] = o[mt][3];
-        }
         if (lane < 4) {
             float *ml = sw + GROUP_TILE * C::OPAD;
             ml[h0 * 2] = m0;
@@ -404,12 +398,22 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             ml[h0 * 2 + 2] = m1;
             ml[h0 * 2 + 3] = l1;
         }
-        brc::named_bar_sync(1, NW * 32);
-        {
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+#pragma unroll
+            for (int mh = 0; mh < C::MT / 2; ++mh) {
+                const int mt = hf * (C::MT / 2) + mh;
+                const uint32_t d0 = mh * 16 + t0;
+                sw[h0 * C::OPAD + d0] = o[mt][0];
+                sw[(h0 + 1) * C::OPAD + d0] = o[mt][1];
+                sw[h0 * C::OPAD + d0 + 8] = o[mt][2];
+                sw[(h0 + 1) * C::OPAD + d0 + 8] = o[mt][3];
+            }
+            brc::named_bar_sync(1, NW * 32);
             const size_t slot0 = (size_t)(u + blockIdx.x) * KVB;
             for (uint32_t kh = 0; kh < KVB * p.group; ++kh) {
                 const uint32_t k2 = kh / p.group, h = kh % p.group;   // kv head of the group, query head
-                float *acc_out = p.part_acc + (slot0 + k2) * GROUP_TILE * HD;
+                float *acc_out = p.part_acc + (slot0 + k2) * GROUP_TILE * HD + hf * (HD / 2);
                 float *ml_out = p.part_ml + (slot0 + k2) * GROUP_TILE * 2;
                 float mw[C::NWP], lw[C::NWP], M = -INFINITY;
 #pragma unroll
@@ -425,20 +429,20 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                     wt[w] = lw[w] > 0.f ? brc::fast_exp2(mw[w] - M) : 0.f;
                     L += wt[w] * lw[w];
                 }
-                for (uint32_t d = tid; d < HD; d += NW * 32) {
+                for (uint32_t d = tid; d < HD / 2; d += NW * 32) {
                     float v = 0.f;
 #pragma unroll
                     for (int w = 0; w < C::NWP; ++w)
                         if (wt[w] != 0.f) v += wt[w] * scratch[(w * KVB + k2) * C::SCRATCH_WARP + h * C::OPAD + d];
                     acc_out[h * HD + d] = dead ? 0.f : v;
                 }
-                if (tid == 0) {
+                if (hf == 0 && tid == 0) {
                     ml_out[h * 2] = M;
                     ml_out[h * 2 + 1] = dead ? 0.f : L;
                 }
             }
+            brc::named_bar_sync(1, NW * 32);
         }
-        brc::named_bar_sync(1, NW * 32);
 
         g0 = ge;
         ++u;
