@@ -74,6 +74,7 @@ SIGNATURES = {
     "brc_decode_workspace_bytes": [_vp, _u32, _u32, _u64p],
     "brc_paged_decode_attn": [_vp, _u32, _vp, _i32, _u32, _vp, _u32, _vp, _u32, _vp, _u32, _u32, _f32, _vp, _vp,
                               _u64, _vp],
+    "brc_paged_decode_attn_static": [_vp, _u32, _vp, _i32, _u32, _vp, _u32, _vp, _u32, _vp, _u32, _u32, _f32, _vp, _vp],
     "brc_decode_partial_bytes": [_u32, _u32, _u32, _u64p],
     "brc_decode_partial": [_vp, _u32, _vp, _i32, _u32, _vp, _u32, _vp, _u32, _u32, _f32, _vp, _vp, _u64, _vp],
     "brc_decode_combine": [_i32, _vp, _u32, _u64, _u32, _u32, _u32, _vp, _u32, _vp, _vp],

@@ -809,3 +809,82 @@ brc_status brc_decode_combine(int32_t device, const void *parts_dev, uint32_t n_
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Decode attention for callers that cannot allocate device memory.
+//
+// Two kinds of caller are meant.  An engine that handed its whole HBM budget to its own arena at
+// start-up has nothing left for a later cudaMalloc, and must not fragment what it planned.  And a
+// latency-critical decode loop cannot afford cudaMalloc at all: the call synchronises the device, so
+// every stream would stall behind it.  For them the split-KV partials live in the array below, which
+// is part of the library image: every GPU that loads the library holds BRC_STATIC_WS_BYTES of it
+// until the process exits, whether or not this entry point is ever called.
+// ---------------------------------------------------------------------------------------------
+#define BRC_STATIC_WS_BYTES (4u << 20)
+
+static __device__ __align__(256) unsigned char g_static_decode_ws[BRC_STATIC_WS_BYTES];
+
+namespace {
+
+// In host code the array's name is only a handle for the runtime, not a device address; the address
+// is asked for once per device, with that device current, and kept.
+std::mutex g_static_ws_mu;
+void *g_static_ws_ptr[64] = {};
+
+brc_status static_ws_for(int device, void **out) {
+    if (device < 0 || device >= 64) return brc_fail(BRC_ERR_INVALID, "static decode scratch: device %d out of range", device);
+    std::lock_guard<std::mutex> lock(g_static_ws_mu);
+    if (!g_static_ws_ptr[device]) {
+        void *ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_decode_ws);
+        if (e != cudaSuccess || !ptr)
+            return brc_fail(BRC_ERR_CUDA, "static decode scratch: cudaGetSymbolAddress on device %d failed: %s", device,
+                            cudaGetErrorString(e));
+        g_static_ws_ptr[device] = ptr;
+    }
+    *out = g_static_ws_ptr[device];
+    return BRC_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+brc_status brc_paged_decode_attn_static(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype, uint32_t n_head,
+                                        const float *gate_dev, uint32_t gate_head_stride,
+                                        const uint32_t *block_tables_dev, uint32_t table_stride,
+                                        const uint32_t *seq_lens_dev, uint32_t n_seqs, uint32_t max_seq_len, float scale,
+                                        float *out_dev, void *stream) {
+    if (!pool) return brc_fail(BRC_ERR_INVALID, "brc_paged_decode_attn_static: pool is NULL");
+    if (pool->device < 0 || !pool->has_tma)
+        return brc_fail(BRC_ERR_CUDA, "brc_paged_decode_attn_static: this pool holds bookkeeping only (no device memory)");
+    uint64_t need = 0;
+    brc_decode_workspace_bytes(pool, n_seqs, n_head, &need);
+    if (need > BRC_STATIC_WS_BYTES) {
+        const uint64_t per_slot = (uint64_t)GROUP_TILE * (pool->head_dim + 2u) * sizeof(float);
+        const uint64_t slots = BRC_STATIC_WS_BYTES / per_slot;
+        const uint64_t fixed = (uint64_t)grid_ctas(pool) * kvb_of(pool);
+        return brc_fail(BRC_ERR_CAPACITY,
+                        "brc_paged_decode_attn_static: %u sequences need %llu bytes of scratch but the built-in array holds %u "
+                        "(room for about %llu sequences with this pool); use brc_paged_decode_attn with a caller-owned workspace",
+                        n_seqs, (unsigned long long)need, BRC_STATIC_WS_BYTES,
+                        (unsigned long long)(slots > fixed ? (slots - fixed) / pool->n_kv_head : 0));
+    }
+    void *ws = nullptr;
+    {
+        brc_device_guard guard(pool->device);
+        if (!guard.ok) return brc_fail(BRC_ERR_CUDA, "brc_paged_decode_attn_static: cannot make device %d current", pool->device);
+        if (brc_status rc = static_ws_for(pool->device, &ws)) return rc;
+    }
+    if (brc_status rc = validate_decode(pool, "brc_paged_decode_attn_static", layer, q_dev, q_dtype, n_head, block_tables_dev,
+                                        table_stride, seq_lens_dev, n_seqs, max_seq_len, out_dev, ws, BRC_STATIC_WS_BYTES))
+        return rc;
+    if (gate_dev && gate_head_stride < pool->head_dim)
+        return brc_fail(BRC_ERR_INVALID, "brc_paged_decode_attn_static: gate_head_stride %u < head_dim %u", gate_head_stride,
+                        pool->head_dim);
+    if (n_seqs == 0) return BRC_OK;
+    return run_decode(pool, layer, q_dev, q_dtype, n_head, gate_dev, gate_head_stride, block_tables_dev, table_stride,
+                      seq_lens_dev, n_seqs, max_seq_len, scale, out_dev, nullptr, ws, brc_stream(stream));
+}
+
+}  // extern "C"

@@ -221,6 +221,30 @@ BRC_API brc_status brc_decode_combine(int32_t device, const void *parts_dev, uin
                                       uint32_t head_dim, const float *gate_dev, uint32_t gate_head_stride,
                                       float *out_dev, void *stream);
 
+/* Paged decode attention without a workspace argument and without any device
+ * allocation (no counterpart in the reference).  Same inputs, outputs and
+ * results as brc_paged_decode_attn; the split-KV partials go to a fixed array
+ * that is part of the library image (4 MiB on every GPU that loads the library,
+ * held until the process exits).  It is meant for callers that must not call
+ * cudaMalloc: an engine whose arena took the whole HBM budget at start-up, or a
+ * decode loop that cannot accept the device-wide synchronisation cudaMalloc
+ * implies.
+ *   - Limit: the batch must fit the array (about 100 sequences at 2 kv heads on a
+ *     148-SM GPU); a larger batch is refused with BRC_ERR_CAPACITY and a message
+ *     that names the limit.  Use the workspace variant for those.
+ *   - The first call on each device looks up the array's device address (a
+ *     host-side query, no allocation).  Make that first call outside any stream
+ *     capture.
+ *   - All calls on a device share the one array and it keeps whatever the last
+ *     call left there; nothing in it needs to start at zero.  Two calls that run
+ *     at the same time on one GPU (different streams or threads) would overwrite
+ *     each other's partials: issue them on one stream, or serialise them. */
+BRC_API brc_status brc_paged_decode_attn_static(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype,
+                                                uint32_t n_head, const float *gate_dev, uint32_t gate_head_stride,
+                                                const uint32_t *block_tables_dev, uint32_t table_stride,
+                                                const uint32_t *seq_lens_dev, uint32_t n_seqs, uint32_t max_seq_len,
+                                                float scale, float *out_dev, void *stream);
+
 /* ---------------------------------------------------------------- one decode step over layers
  * The composition the reference performs per attention layer in Qsa::forward
  * (crates/breccia-kernels/src/qsa/mod.rs:1587-1645: kv_append -> attend ->
