@@ -290,7 +290,7 @@ def run_native(args):
             "clocks": clocks,
             "e2e": {"value": N_SEQS * world / (ms_e2e * 1e-3), "unit": "tok/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": steps * (1 + 3 * N_LAYERS),
+            "gpu_launches": steps * (1 + N_LAYERS),
             "roofline": {"kernel": "decode_partial_kernel<256,f16 q>", "bound": "hbm", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
                          "algorithmic_bytes_per_launch": alg_bytes, "avg_launch_us": dur_s * 1e6,

@@ -80,6 +80,21 @@ SIGNATURES = {
     "brc_decode_combine": [_i32, _vp, _u32, _u64, _u32, _u32, _u32, _vp, _u32, _vp, _vp],
     "brc_decode_step": [_vp, _u32, _u32, _vp, _u32, _vp, _vp, _u32, _u32, _vp, _i32, _u64, _u32, _vp, _vp, _i32, _u64,
                         _vp, _u32, _u64, _f32, _vp, _u64, _vp, _u64, _vp],
+    "brc_radix_create": [_vp, _vpp],
+    "brc_radix_destroy": [_vp],
+    "brc_radix_match": [_vp, _u32p, _u32, _u32p, _u32, _u32p],
+    "brc_radix_insert": [_vp, _u32p, _u32, _u32p, _u32, _u32p],
+    "brc_radix_evict": [_vp, _u32, _u32p],
+    "brc_radix_stats": [_vp, _u64p, _u64p, _u64p, _u64p],
+    "brc_tier_create": [_vp, _u32, _vpp],
+    "brc_tier_destroy": [_vp],
+    "brc_tier_demote": [_vp, _u32p, _u32, _u32p, _vp],
+    "brc_tier_promote": [_vp, _u32p, _u32, _u32p],
+    "brc_tier_fence": [_vp, _vp],
+    "brc_tier_sync": [_vp],
+    "brc_tier_touch": [_vp, _u32p, _u32],
+    "brc_tier_lru": [_vp, _u32, _u32p, _u32p],
+    "brc_tier_stats": [_vp, _u64p, _u64p, _u64p, _u64p, _u32p],
     "brc_timing_enable": [_vp, _i32],
     "brc_timing_read": [_vp, _i32, _u32p, C.POINTER(C.c_double)],
 }

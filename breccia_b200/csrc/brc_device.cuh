@@ -40,6 +40,14 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
     return (f32_to_f16_bits(hi) << 16) | f32_to_f16_bits(lo);
 }
 
+// Two binary16 values as stored: an exponent field of zero becomes a signed zero (what the
+// reference's loader would read, shaders/f16_storage.glsl:62-64), so the pool never holds subnormals.
+__device__ __forceinline__ uint32_t flush_f16x2(uint32_t w) {
+    if ((w & 0x7c00u) == 0u) w &= 0xffff8000u;
+    if ((w & 0x7c000000u) == 0u) w &= 0x8000ffffu;
+    return w;
+}
+
 // ---------------------------------------------------------------------------------------------
 // shared-memory addressing and mbarriers
 // ---------------------------------------------------------------------------------------------
@@ -86,6 +94,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
 // Order this thread's generic-proxy shared-memory writes before later async-proxy (TMA) accesses.
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// Order this thread's generic-proxy global-memory writes before later async-proxy (TMA) reads of them.
+__device__ __forceinline__ void fence_proxy_async_global() {
+    asm volatile("fence.proxy.async.global;" ::: "memory");
 }
 
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads) {

@@ -18,6 +18,12 @@
 #define BRC_DEV_WAIT_LIMIT 4u  // a bounded mbarrier wait gave up
 #define BRC_DEV_BAD_SHAPE 8u   // more work units than a kernel's table holds
 
+// brc_pool::status_dev: 64 words of check state, then the decode kernels' per-unit arrival counters
+// (2048 words, zero between launches: the kernels reset what they count).
+#define BRC_STATUS_WORDS 64u
+#define BRC_DONE_WORDS 2048u
+#define BRC_STATUS_BYTES ((BRC_STATUS_WORDS + BRC_DONE_WORDS) * 4u)
+
 // Stage ids of the optional GPU timers are public (breccia_kv.h); this is their count.
 #define BRC_STAGE_COUNT 6
 
@@ -83,5 +89,13 @@ struct brc_device_guard {
 // Record a begin/end event pair around a launch when timing is on (no-ops otherwise).
 void brc_stage_begin(brc_pool *pool, int stage, cudaStream_t s);
 void brc_stage_end(brc_pool *pool, int stage, cudaStream_t s);
+
+// Decode attention of one layer with the step's KV append fused into the kernel (decode_attn.cu).
+brc_status brc_decode_attn_append_fused(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype, uint32_t n_head,
+                                        const float *gate_dev, uint32_t gate_head_stride, const uint32_t *block_tables_dev,
+                                        uint32_t table_stride, const uint32_t *seq_lens_dev, uint32_t n_seqs,
+                                        uint32_t max_seq_len, float scale, float *out_dev, void *workspace_dev,
+                                        uint64_t workspace_bytes, const void *k_new_dev, const void *v_new_dev,
+                                        int32_t kv_dtype, void *stream);
 
 static inline cudaStream_t brc_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }

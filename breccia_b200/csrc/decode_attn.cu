@@ -1,4 +1,4 @@
-// Paged GQA decode attention for sm_100a: split-KV partial kernel + log-sum-exp combine.
+// Paged GQA decode attention for sm_100a: one split-KV kernel with an in-kernel log-sum-exp combine.
 //
 // Replaces, for a batch of sequences at T = 1, the reference's four dispatches
 // scores -> softmax -> split-K apply -> reduce (crates/breccia-kernels/src/qsa/mod.rs:1439-1461,
@@ -22,9 +22,13 @@
 //     across the cell dimension, the probabilities transposed in registers by movmatrix into the B
 //     operand, and O^T[head_dim x 8 heads] += V^T . P^T with V^T fragments from ldmatrix.trans.  P is
 //     split into a binary16 head and tail so the product carries ~22 significant bits;
-//   * at the end of a unit's share the warps merge (m, l, O) per kv head through shared memory and
-//     write one partial per kv head; the combine kernel merges the partials of a unit, normalises and
-//     applies the gate.
+//   * at the end of a unit's share the warps merge (m, l, O) per kv head through shared memory, write
+//     one partial per kv head and take a ticket on the unit; the CTA that takes a unit's last ticket
+//     merges all of its partials (log-sum-exp), normalises, applies the gate and writes the output
+//     rows.  No CTA ever waits for another, and there is no second kernel;
+//   * a decode step's KV append can ride along: the CTA that is about to stream the page holding a
+//     sequence's newest cell first writes that cell (same encoding and address rule as the append
+//     kernel), fenced against its own TMA read.
 //
 // HBM-bound by design: 8 FLOP per cached byte, all of it on the tensor pipe.
 #include <algorithm>
@@ -65,6 +69,18 @@ struct DecodeParams {
     const uint32_t *seq_lens;      // [n_seqs]
     float *part_acc;               // [slots][KVB][GROUP_TILE][HD]
     float *part_ml;                // [slots][KVB][GROUP_TILE][2]
+    uint32_t *done;                // [n_units] shares of a unit completed so far (zero between launches)
+    float *out;                    // final [n_seqs][n_head][HD]; partial mode: merged acc, same shape
+    float *out_ml;                 // partial mode: [n_seqs][n_head][2] (m, l); nullptr = final output
+    const float *gate;             // nullable
+    uint32_t gate_head_stride;
+    // fused append (nullable): this step's K/V of the cell seq_len - 1 of every sequence,
+    // [n_seqs][n_kv_head * HD], written into the pool by the CTA that streams that cell's page
+    const void *k_new;
+    const void *v_new;
+    uint32_t kv_new_f32;           // 1: f32 sources, 0: binary16
+    uint8_t *k_base;               // base of the K pool (row 0 of the TMA view)
+    uint64_t v_offset;             // bytes from the K pool to the V pool
     uint32_t *status;
     uint32_t n_seqs, table_stride, max_seq_len;
     uint32_t n_kv_head, group, n_head;
@@ -107,6 +123,178 @@ __device__ __forceinline__ uint32_t share_begin(uint32_t cta, uint32_t total, ui
     return (uint32_t)(((uint64_t)cta * total) / n_cta);
 }
 
+__device__ __forceinline__ float sigmoid_f32(float x) {
+    if (x >= 0.f) return 1.f / (1.f + expf(-x));
+    const float e = expf(x);
+    return e / (1.f + e);
+}
+
+// CTAs whose share [begin(i), begin(i+1)) meets the page-unit range [first_g, last_g].
+__device__ __forceinline__ void share_range(uint32_t first_g, uint32_t last_g, uint32_t total, uint32_t n_cta,
+                                            uint32_t &i_lo, uint32_t &i_hi) {
+    i_lo = (uint32_t)(((uint64_t)first_g * n_cta) / total);
+    while (i_lo + 1 < n_cta && share_begin(i_lo + 1, total, n_cta) <= first_g) ++i_lo;
+    while (i_lo > 0 && share_begin(i_lo, total, n_cta) > first_g) --i_lo;
+    i_hi = (uint32_t)(((uint64_t)last_g * n_cta) / total);
+    while (i_hi + 1 < n_cta && share_begin(i_hi + 1, total, n_cta) <= last_g) ++i_hi;
+    while (i_hi > 0 && share_begin(i_hi, total, n_cta) > last_g) --i_hi;
+}
+
+// Log-sum-exp merge of all shares of unit u (every one of them is complete and visible), run by the
+// NW * 32 consumer threads of the CTA that took the unit's last ticket.  Writes the final output
+// rows (normalised, gated) or, in partial mode, the merged (acc, m, l).  Partials come from other SMs:
+// they are read from L2 (ld.global.cg), never from this SM's L1.  Shares are taken COMBINE_CHUNK at a
+// time: their (m, l) go to shared memory in one parallel sweep, one thread per output row turns them
+// into weights, and the accumulation then issues independent 16-byte loads (nothing in the inner loop
+// waits on a previous load).  `sm` is the CTA's merge scratch, free at this point.
+constexpr uint32_t COMBINE_CHUNK = 32;
+
+template <int HD, int KVB>
+__device__ __forceinline__ void combine_unit(const DecodeParams &p, uint32_t u, uint32_t i_lo, uint32_t i_hi, uint32_t total,
+                                             uint32_t tid, float *sm) {
+    constexpr uint32_t TPR = HD / 4;                    // threads per output row (float4 each)
+    constexpr uint32_t ROWS_PER_PASS = (NW * 32) / TPR;
+    constexpr uint32_t MAX_ROWS = KVB * GROUP_TILE;
+    constexpr uint32_t PASSES = (MAX_ROWS + ROWS_PER_PASS - 1) / ROWS_PER_PASS;
+    const uint32_t n_rows = KVB * p.group;              // (kv head of the unit, query head)
+    const uint32_t n_groups = p.n_kv_head / KVB;
+    const uint32_t s = u / n_groups, kv0 = (u % n_groups) * KVB;
+    const uint32_t d = (tid % TPR) * 4;
+    const bool dense = total >= gridDim.x;              // then no CTA has an empty share
+
+    uint32_t *list = reinterpret_cast<uint32_t *>(sm);                        // [COMBINE_CHUNK] share (CTA) ids
+    uint32_t *n_list = list + COMBINE_CHUNK;                                  // [1] (+ padding)
+    float2 *mls = reinterpret_cast<float2 *>(list + COMBINE_CHUNK + 8);       // [COMBINE_CHUNK][MAX_ROWS]
+    float *wsm = reinterpret_cast<float *>(mls + COMBINE_CHUNK * MAX_ROWS);   // [COMBINE_CHUNK][MAX_ROWS]
+    float *row_scale = wsm + COMBINE_CHUNK * MAX_ROWS;                        // [MAX_ROWS] rescale of what is held
+
+    float4 acc[PASSES];
+#pragma unroll
+    for (uint32_t ps = 0; ps < PASSES; ++ps) acc[ps] = make_float4(0.f, 0.f, 0.f, 0.f);
+    float M = -INFINITY, L = 0.f;                        // of row `tid`, held by threads tid < n_rows
+
+    for (uint32_t i0 = i_lo; i0 <= i_hi;) {
+        // ---- the next chunk of non-empty shares
+        uint32_t i_next;
+        if (dense) {
+            const uint32_t n = min(COMBINE_CHUNK, i_hi - i0 + 1);
+            if (tid < n) list[tid] = i0 + tid;
+            if (tid == 0) n_list[0] = n;
+            i_next = i0 + n;
+        } else {
+            if (tid == 0) {
+                uint32_t n = 0, i = i0;
+                for (; i <= i_hi && n < COMBINE_CHUNK; ++i)
+                    if (share_begin(i, total, gridDim.x) != share_begin(i + 1, total, gridDim.x)) list[n++] = i;
+                n_list[0] = n;
+                n_list[1] = i;
+            }
+            i_next = 0;
+        }
+        brc::named_bar_sync(1, NW * 32);
+        const uint32_t n = n_list[0];
+        if (!dense) i_next = n_list[1];
+        // ---- (m, l) of every (share, row), one load per thread per sweep
+        for (uint32_t idx = tid; idx < n * n_rows; idx += NW * 32) {
+            const uint32_t pc = idx / n_rows, row = idx % n_rows;
+            const uint32_t k2 = row / p.group, h = row % p.group;
+            mls[pc * MAX_ROWS + row] =
+                __ldcg(reinterpret_cast<const float2 *>(p.part_ml + (((size_t)(u + list[pc]) * KVB + k2) * GROUP_TILE + h) * 2));
+        }
+        brc::named_bar_sync(1, NW * 32);
+        // ---- weights: thread = row
+        if (tid < n_rows) {
+            float Mc = M;
+            for (uint32_t pc = 0; pc < n; ++pc) {
+                const float2 ml = mls[pc * MAX_ROWS + tid];
+                if (ml.y > 0.f) Mc = fmaxf(Mc, ml.x);
+            }
+            const float keep = (L > 0.f) ? exp2f(M - Mc) : 0.f;   // rescale of what earlier chunks gave
+            L *= keep;
+            for (uint32_t pc = 0; pc < n; ++pc) {
+                const float2 ml = mls[pc * MAX_ROWS + tid];
+                const float w = ml.y > 0.f ? exp2f(ml.x - Mc) : 0.f;
+                wsm[pc * MAX_ROWS + tid] = w;
+                L += w * ml.y;
+            }
+            M = Mc;
+            row_scale[tid] = keep;
+        }
+        brc::named_bar_sync(1, NW * 32);
+        // ---- accumulate: every row pass of four shares at a time, i.e. 4 * PASSES independent 16-byte
+        //      loads in flight per thread before anything is consumed (the partials sit in L2)
+#pragma unroll
+        for (uint32_t ps = 0; ps < PASSES; ++ps) {
+            const uint32_t row = min(ps * ROWS_PER_PASS + tid / TPR, n_rows - 1);
+            const float keep = row_scale[row];
+            acc[ps].x *= keep;
+            acc[ps].y *= keep;
+            acc[ps].z *= keep;
+            acc[ps].w *= keep;
+        }
+        for (uint32_t pc0 = 0; pc0 < n; pc0 += 4) {
+            float4 a[PASSES][4];
+#pragma unroll
+            for (uint32_t ps = 0; ps < PASSES; ++ps) {
+                const uint32_t row = min(ps * ROWS_PER_PASS + tid / TPR, n_rows - 1);   // clamped rows are not stored
+                const uint32_t k2 = row / p.group, h = row % p.group;
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j) {
+                    const uint32_t pc = min(pc0 + j, n - 1);                            // clamped shares get weight 0
+                    a[ps][j] = __ldcg(reinterpret_cast<const float4 *>(
+                        p.part_acc + (((size_t)(u + list[pc]) * KVB + k2) * GROUP_TILE + h) * HD + d));
+                }
+            }
+#pragma unroll
+            for (uint32_t ps = 0; ps < PASSES; ++ps) {
+                const uint32_t row = min(ps * ROWS_PER_PASS + tid / TPR, n_rows - 1);
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j) {
+                    const float w = pc0 + j < n ? wsm[(pc0 + j) * MAX_ROWS + row] : 0.f;
+                    acc[ps].x += w * a[ps][j].x;
+                    acc[ps].y += w * a[ps][j].y;
+                    acc[ps].z += w * a[ps][j].z;
+                    acc[ps].w += w * a[ps][j].w;
+                }
+            }
+        }
+        brc::named_bar_sync(1, NW * 32);   // the lists are rewritten by the next chunk
+        i0 = i_next;
+    }
+    // ---- rows' (M, L) to everyone, then the output
+    if (tid < n_rows) {
+        mls[tid] = make_float2(M, L);
+    }
+    brc::named_bar_sync(1, NW * 32);
+#pragma unroll
+    for (uint32_t ps = 0; ps < PASSES; ++ps) {
+        const uint32_t row = ps * ROWS_PER_PASS + tid / TPR;
+        if (row >= n_rows) continue;
+        const uint32_t k2 = row / p.group, h = row % p.group;
+        const float2 ml = mls[row];
+        const uint32_t head = (kv0 + k2) * p.group + h;
+        const size_t o = ((size_t)s * p.n_head + head) * HD + d;
+        if (p.out_ml) {
+            *reinterpret_cast<float4 *>(p.out + o) = acc[ps];
+            if (d == 0) {
+                p.out_ml[((size_t)s * p.n_head + head) * 2] = ml.x;
+                p.out_ml[((size_t)s * p.n_head + head) * 2 + 1] = ml.y;
+            }
+        } else {
+            const float inv = ml.y > 0.f ? 1.f / ml.y : 0.f;
+            float4 r = make_float4(acc[ps].x * inv, acc[ps].y * inv, acc[ps].z * inv, acc[ps].w * inv);
+            if (p.gate) {
+                const float *g = p.gate + ((size_t)s * p.n_head + head) * p.gate_head_stride + d;
+                r.x *= sigmoid_f32(g[0]);
+                r.y *= sigmoid_f32(g[1]);
+                r.z *= sigmoid_f32(g[2]);
+                r.w *= sigmoid_f32(g[3]);
+            }
+            *reinterpret_cast<float4 *>(p.out + o) = r;
+        }
+    }
+}
+
 template <int HD, bool Q_F32, int KVB>
 __global__ void __launch_bounds__(NTHREADS, 1)
     decode_partial_kernel(const __grid_constant__ CUtensorMap tm_kv, const DecodeParams p) {
@@ -120,6 +308,10 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(S) + C::PREFIX_BYTES);
     const uint32_t full0 = brc::smem_u32(bars);
     const uint32_t empty0 = full0 + 8u * p.n_stages;
+    // small words after the barriers (2 x 24 barriers at most = 384 bytes): flags, merge weights
+    volatile uint32_t *flags = reinterpret_cast<volatile uint32_t *>(bars + 64);
+    volatile uint32_t *dead_cta = flags + 1;
+    float *wts = reinterpret_cast<float *>(const_cast<uint32_t *>(flags) + 8);  // [NWP][KVB * GROUP_TILE]
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t n_groups = p.n_kv_head / KVB;   // kv-head groups per sequence
@@ -132,6 +324,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         }
         brc::mbar_fence_init();
         brc::tma_prefetch_desc(&tm_kv);
+        dead_cta[0] = 0u;
     }
     // Exclusive prefix of pages per unit, S[0..n_units]; every CTA computes it (n_units <= 2048).
     if (warp == 0) {
@@ -161,6 +354,20 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     }
     __syncthreads();
 
+    // A sequence without cells has no pages, hence no share and no ticket: its rows are written here.
+    for (uint32_t u = blockIdx.x; u < n_units; u += gridDim.x) {
+        if (S[u + 1] != S[u]) continue;
+        const uint32_t s = u / n_groups, kv0 = (u % n_groups) * KVB;
+        for (uint32_t i = tid; i < KVB * p.group * HD; i += NTHREADS) {
+            const uint32_t head = kv0 * p.group + i / HD;
+            p.out[((size_t)s * p.n_head + head) * HD + i % HD] = 0.f;
+            if (p.out_ml && i % HD == 0) {
+                p.out_ml[((size_t)s * p.n_head + head) * 2] = -INFINITY;
+                p.out_ml[((size_t)s * p.n_head + head) * 2 + 1] = 0.f;
+            }
+        }
+    }
+
     const uint32_t total = S[n_units];
     const uint32_t a = share_begin(blockIdx.x, total, gridDim.x);
     const uint32_t b = share_begin(blockIdx.x + 1, total, gridDim.x);
@@ -175,6 +382,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         for (uint32_t k0 = 0; k0 < count && !dead; k0 += 32) {
             const uint32_t k = k0 + lane;
             uint32_t row = 0;
+            uint32_t app = 0;  // fused append: bit 31 = this page holds the sequence's newest cell, low bits = (s, kv0)
             if (k < count) {
                 const uint32_t g = a + k;
                 const uint32_t u = unit_of(S, n_units, g);
@@ -184,6 +392,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                     atomicOr(p.status, BRC_DEV_BAD_PAGE);
                     p.status[1] = page;
                     page = 0;  // stay inside the pool; the result of this unit is void and the call reports it
+                } else if (p.k_new) {
+                    const uint32_t len = min(p.seq_lens[s], p.max_seq_len);
+                    if (g - S[u] == (len - 1u) >> 4) app = 0x80000000u | (((len - 1u) & 15u) << 24) | u;
                 }
                 row = p.layer_row0 + (page * p.n_kv_head + kv0) * 16u;
             }
@@ -201,6 +412,43 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                 }
                 dead = __shfl_sync(0xffffffffu, dead, 0);
                 if (dead) break;
+                if (p.k_new) {
+                    // Fused KV append (the reference's qsa_kv_append.comp rule, one cell): the page about to
+                    // be streamed holds the sequence's newest cell, whose K/V this step brings.  Exactly one
+                    // CTA streams that page, so it writes the cell first; the proxy fence orders these
+                    // generic-proxy stores before the TMA (async-proxy) read of the same rows.
+                    const uint32_t ap = __shfl_sync(0xffffffffu, app, i);
+                    if (ap & 0x80000000u) {
+                        const uint32_t au = ap & 0xffffffu, cell = (ap >> 24) & 15u;
+                        const uint32_t as = au / n_groups, akv0 = (au % n_groups) * KVB;
+                        if (lane < HD / 8) {
+#pragma unroll
+                            for (int k2 = 0; k2 < KVB; ++k2) {
+                                const uint64_t src = ((uint64_t)as * p.n_kv_head + akv0 + k2) * HD + lane * 8u;
+                                const uint64_t dst = ((uint64_t)(r + k2 * 16u + cell) * HD + lane * 8u) * 2u;
+                                uint4 ko, vo;
+                                if (p.kv_new_f32) {
+                                    const float4 *ks = reinterpret_cast<const float4 *>(static_cast<const float *>(p.k_new) + src);
+                                    const float4 *vs = reinterpret_cast<const float4 *>(static_cast<const float *>(p.v_new) + src);
+                                    const float4 x0 = __ldg(ks), x1 = __ldg(ks + 1), y0 = __ldg(vs), y1 = __ldg(vs + 1);
+                                    ko = make_uint4(brc::pack_f16x2(x0.x, x0.y), brc::pack_f16x2(x0.z, x0.w),
+                                                    brc::pack_f16x2(x1.x, x1.y), brc::pack_f16x2(x1.z, x1.w));
+                                    vo = make_uint4(brc::pack_f16x2(y0.x, y0.y), brc::pack_f16x2(y0.z, y0.w),
+                                                    brc::pack_f16x2(y1.x, y1.y), brc::pack_f16x2(y1.z, y1.w));
+                                } else {
+                                    ko = __ldg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(p.k_new) + src));
+                                    vo = __ldg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(p.v_new) + src));
+                                    ko = make_uint4(brc::flush_f16x2(ko.x), brc::flush_f16x2(ko.y), brc::flush_f16x2(ko.z), brc::flush_f16x2(ko.w));
+                                    vo = make_uint4(brc::flush_f16x2(vo.x), brc::flush_f16x2(vo.y), brc::flush_f16x2(vo.z), brc::flush_f16x2(vo.w));
+                                }
+                                *reinterpret_cast<uint4 *>(p.k_base + dst) = ko;
+                                *reinterpret_cast<uint4 *>(p.k_base + p.v_offset + dst) = vo;
+                            }
+                            brc::fence_proxy_async_global();
+                        }
+                        __syncwarp();
+                    }
+                }
                 // One operation per 64-column group (issued by neighbouring lanes of one instruction).
                 // Shared memory: [group][K|V][row = kv head * 16 + cell][64 columns], 128-byte swizzled.
                 if (lane < C::BOXES)
@@ -382,6 +630,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             }
         }
 
+        if (dead && lane == 0) dead_cta[0] = 1u;
         // ---- merge, per kv head, the (m, l, O) of its warps and write this share's partial
 #pragma unroll
         for (int off = 4; off < 32; off <<= 1) {
@@ -389,7 +638,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             l1 += __shfl_xor_sync(0xffffffffu, l1, off);
         }
         // The exchange goes through shared memory in two halves of head_dim (half the scratch, which
-        // buys the ring more stages).
+        // buys the ring more stages).  Weights of the warps are computed once, by one thread per head.
         float *sw = scratch + warp * C::SCRATCH_WARP;
         if (lane < 4) {
             float *ml = sw + GROUP_TILE * C::OPAD;
@@ -398,6 +647,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             ml[h0 * 2 + 2] = m1;
             ml[h0 * 2 + 3] = l1;
         }
+        const size_t slot0 = (size_t)(u + blockIdx.x) * KVB;
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
 #pragma unroll
@@ -410,12 +660,10 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                 sw[(h0 + 1) * C::OPAD + d0 + 8] = o[mt][3];
             }
             brc::named_bar_sync(1, NW * 32);
-            const size_t slot0 = (size_t)(u + blockIdx.x) * KVB;
-            for (uint32_t kh = 0; kh < KVB * p.group; ++kh) {
-                const uint32_t k2 = kh / p.group, h = kh % p.group;   // kv head of the group, query head
-                float *acc_out = p.part_acc + (slot0 + k2) * GROUP_TILE * HD + hf * (HD / 2);
-                float *ml_out = p.part_ml + (slot0 + k2) * GROUP_TILE * 2;
-                float mw[C::NWP], lw[C::NWP], M = -INFINITY;
+            if (hf == 0 && tid < KVB * GROUP_TILE) {
+                // thread = (kv head of the group, query head): weights 2^(m_w - M) of its NWP warps
+                const uint32_t k2 = tid / GROUP_TILE, h = tid % GROUP_TILE;
+                float mw[C::NWP], lw[C::NWP], M = -INFINITY, L = 0.f;
 #pragma unroll
                 for (int w = 0; w < C::NWP; ++w) {
                     const float *ml = scratch + (w * KVB + k2) * C::SCRATCH_WARP + GROUP_TILE * C::OPAD;
@@ -423,130 +671,61 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                     lw[w] = ml[h * 2 + 1];
                     if (lw[w] > 0.f) M = fmaxf(M, mw[w]);
                 }
-                float L = 0.f, wt[C::NWP];
 #pragma unroll
                 for (int w = 0; w < C::NWP; ++w) {
-                    wt[w] = lw[w] > 0.f ? brc::fast_exp2(mw[w] - M) : 0.f;
-                    L += wt[w] * lw[w];
+                    const float wt = (lw[w] > 0.f && !dead_cta[0]) ? brc::fast_exp2(mw[w] - M) : 0.f;
+                    wts[w * KVB * GROUP_TILE + tid] = wt;
+                    L += wt * lw[w];
                 }
-                for (uint32_t d = tid; d < HD / 2; d += NW * 32) {
+                if (h < p.group) {
+                    float *ml_out = p.part_ml + ((slot0 + k2) * GROUP_TILE + h) * 2;
+                    ml_out[0] = M;
+                    ml_out[1] = L;
+                }
+            }
+            if (hf == 0) brc::named_bar_sync(1, NW * 32);
+            // flat, independent iterations: (kv head, query head) = j, d = tid (+ 128)
+#pragma unroll 4
+            for (uint32_t idx = tid; idx < KVB * GROUP_TILE * (HD / 2); idx += NW * 32) {
+                const uint32_t kh = idx / (HD / 2), d = idx % (HD / 2);
+                const uint32_t k2 = kh / GROUP_TILE, h = kh % GROUP_TILE;
+                if (h < p.group) {
                     float v = 0.f;
 #pragma unroll
                     for (int w = 0; w < C::NWP; ++w)
-                        if (wt[w] != 0.f) v += wt[w] * scratch[(w * KVB + k2) * C::SCRATCH_WARP + h * C::OPAD + d];
-                    acc_out[h * HD + d] = dead ? 0.f : v;
-                }
-                if (hf == 0 && tid == 0) {
-                    ml_out[h * 2] = M;
-                    ml_out[h * 2 + 1] = dead ? 0.f : L;
+                        v += wts[w * KVB * GROUP_TILE + kh] * scratch[(w * KVB + k2) * C::SCRATCH_WARP + h * C::OPAD + d];
+                    p.part_acc[((slot0 + k2) * GROUP_TILE + h) * HD + hf * (HD / 2) + d] = v;
                 }
             }
+            __threadfence();  // publish this thread's partial before the unit's ticket is taken
             brc::named_bar_sync(1, NW * 32);
         }
+
+        // ---- ticket: the CTA that completes the last share of a unit combines all of its shares
+        uint32_t i_lo, i_hi;
+        share_range(unit_first, S[u + 1] - 1, total, gridDim.x, i_lo, i_hi);
+        if (tid == 0) {
+            uint32_t pieces = i_hi - i_lo + 1;
+            if (total < gridDim.x) {   // fewer page-units than CTAs: some shares in between are empty
+                pieces = 0;
+                for (uint32_t i = i_lo; i <= i_hi; ++i)
+                    pieces += share_begin(i, total, gridDim.x) != share_begin(i + 1, total, gridDim.x);
+            }
+            const uint32_t ticket = atomicAdd(p.done + u, 1u);
+            const uint32_t last = ticket + 1u == pieces;
+            if (last) p.done[u] = 0;   // every share has arrived: leave the counter clean for the next launch
+            flags[0] = last;
+        }
+        brc::named_bar_sync(1, NW * 32);
+        if (flags[0]) {
+            __threadfence();
+            combine_unit<HD, KVB>(p, u, i_lo, i_hi, total, tid, scratch);
+        }
+        brc::named_bar_sync(1, NW * 32);
 
         g0 = ge;
         ++u;
         while (u < n_units && S[u + 1] == S[u]) ++u;  // units without pages have no share
-    }
-}
-
-// ---------------------------------------------------------------------------------------------
-// combine: merge the partials of each (sequence, head), normalise, gate
-// ---------------------------------------------------------------------------------------------
-struct CombineParams {
-    const float *part_acc;
-    const float *part_ml;
-    const uint32_t *seq_lens;
-    const float *gate;    // nullable
-    float *out;           // final: [n_seqs][n_head][HD];  partial mode: acc [n_seqs][n_head][HD]
-    float *out_ml;        // partial mode: [n_seqs][n_head][2], else nullptr
-    uint32_t n_seqs, n_kv_head, group, n_head, max_seq_len;
-    uint32_t gate_head_stride;
-    uint32_t n_cta;       // grid size of the partial kernel
-    uint32_t kvb;         // kv heads per unit in the partial kernel
-};
-
-__device__ __forceinline__ float sigmoid_f32(float x) {
-    if (x >= 0.f) return 1.f / (1.f + expf(-x));
-    const float e = expf(x);
-    return e / (1.f + e);
-}
-
-template <int HD>
-__global__ void __launch_bounds__(HD) decode_combine_kernel(const CombineParams p) {
-    __shared__ uint32_t red[2][HD / 32];
-    const uint32_t s = blockIdx.x / p.n_head, h = blockIdx.x % p.n_head;
-    const uint32_t kvh = h / p.group, hl = h % p.group;
-    const uint32_t n_groups = p.n_kv_head / p.kvb;
-    const uint32_t u = s * n_groups + kvh / p.kvb, kl = kvh % p.kvb;
-    const uint32_t n_units = p.n_seqs * n_groups;
-    const uint32_t tid = threadIdx.x;
-
-    // pages before this unit and in total
-    uint32_t before = 0, total = 0;
-    for (uint32_t i = tid; i < n_units; i += HD) {
-        const uint32_t pg = pages_of(min(p.seq_lens[i / n_groups], p.max_seq_len));
-        total += pg;
-        if (i < u) before += pg;
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-        before += __shfl_xor_sync(0xffffffffu, before, off);
-        total += __shfl_xor_sync(0xffffffffu, total, off);
-    }
-    if ((tid & 31) == 0) {
-        red[0][tid >> 5] = before;
-        red[1][tid >> 5] = total;
-    }
-    __syncthreads();
-    before = 0;
-    total = 0;
-#pragma unroll
-    for (int w = 0; w < HD / 32; ++w) {
-        before += red[0][w];
-        total += red[1][w];
-    }
-    const uint32_t mine = pages_of(min(p.seq_lens[s], p.max_seq_len));
-
-    float acc = 0.f, M = -INFINITY, L = 0.f;
-    if (mine > 0) {
-        // CTAs of the partial kernel whose share [begin(i), begin(i+1)) meets [before, before + mine)
-        const uint32_t first_g = before, last_g = before + mine - 1;
-        uint32_t i_lo = (uint32_t)(((uint64_t)first_g * p.n_cta) / total);
-        while (i_lo + 1 < p.n_cta && share_begin(i_lo + 1, total, p.n_cta) <= first_g) ++i_lo;
-        while (i_lo > 0 && share_begin(i_lo, total, p.n_cta) > first_g) --i_lo;
-        uint32_t i_hi = (uint32_t)(((uint64_t)last_g * p.n_cta) / total);
-        while (i_hi + 1 < p.n_cta && share_begin(i_hi + 1, total, p.n_cta) <= last_g) ++i_hi;
-        while (i_hi > 0 && share_begin(i_hi, total, p.n_cta) > last_g) --i_hi;
-
-        // A CTA whose share is empty (fewer page-units than CTAs) wrote no partial: skip its slot.
-        for (uint32_t i = i_lo; i <= i_hi; ++i) {
-            if (share_begin(i, total, p.n_cta) == share_begin(i + 1, total, p.n_cta)) continue;
-            const float *ml = p.part_ml + (((size_t)(u + i) * p.kvb + kl) * GROUP_TILE + hl) * 2;
-            if (ml[1] > 0.f) M = fmaxf(M, ml[0]);
-        }
-        for (uint32_t i = i_lo; i <= i_hi; ++i) {
-            if (share_begin(i, total, p.n_cta) == share_begin(i + 1, total, p.n_cta)) continue;
-            const size_t slot = (size_t)(u + i) * p.kvb + kl;
-            const float *ml = p.part_ml + (slot * GROUP_TILE + hl) * 2;
-            const float l = ml[1];
-            if (!(l > 0.f)) continue;
-            const float w = exp2f(ml[0] - M);
-            L += w * l;
-            acc += w * p.part_acc[(slot * GROUP_TILE + hl) * HD + tid];
-        }
-    }
-    const size_t o = ((size_t)s * p.n_head + h) * HD + tid;
-    if (p.out_ml) {
-        p.out[o] = acc;
-        if (tid == 0) {
-            p.out_ml[((size_t)s * p.n_head + h) * 2] = M;
-            p.out_ml[((size_t)s * p.n_head + h) * 2 + 1] = L;
-        }
-    } else {
-        float r = L > 0.f ? acc / L : 0.f;
-        if (p.gate) r *= sigmoid_f32(p.gate[((size_t)s * p.n_head + h) * p.gate_head_stride + tid]);
-        p.out[o] = r;
     }
 }
 
@@ -662,11 +841,20 @@ brc_status validate_decode(const brc_pool *pool, const char *who, uint32_t layer
     return BRC_OK;
 }
 
-// out_ml != nullptr: partial mode (out = merged acc, out_ml = (m, l)); else final output.
+// Optional fused append of one decode step (all nullptr / 0 when the call only attends).
+struct FusedAppend {
+    const void *k_new = nullptr;   // [n_seqs][n_kv_head * head_dim], the cell seq_len - 1 of every sequence
+    const void *v_new = nullptr;
+    int32_t dtype = BRC_DTYPE_F32;
+};
+
+// out_ml != nullptr: partial mode (out = merged acc, out_ml = (m, l)); else final output.  One launch
+// per <= 2048 units: the kernel streams the cache, merges its own shares and, through per-unit
+// tickets, combines them (no second kernel).
 brc_status run_decode(brc_pool *pool, uint32_t layer, const void *q, int32_t q_dtype, uint32_t n_head, const float *gate,
                       uint32_t gate_head_stride, const uint32_t *bt, uint32_t table_stride, const uint32_t *lens,
                       uint32_t n_seqs, uint32_t max_seq_len, float scale, float *out, float *out_ml, void *ws,
-                      cudaStream_t st) {
+                      cudaStream_t st, const FusedAppend &app = FusedAppend()) {
     brc_device_guard guard(pool->device);
     const uint32_t hd = pool->head_dim;
     const uint32_t kvb = kvb_of(pool);
@@ -678,6 +866,7 @@ brc_status run_decode(brc_pool *pool, uint32_t layer, const void *q, int32_t q_d
     float *part_acc = static_cast<float *>(ws);
     float *part_ml = part_acc + slots * GROUP_TILE * hd;
     const size_t q_elem = q_dtype == BRC_DTYPE_F32 ? 4 : 2;
+    const size_t kv_elem = app.dtype == BRC_DTYPE_F32 ? 4 : 2;
     for (uint32_t s0 = 0; s0 < n_seqs; s0 += per) {
         const uint32_t ns = std::min(per, n_seqs - s0);
         DecodeParams p;
@@ -686,6 +875,16 @@ brc_status run_decode(brc_pool *pool, uint32_t layer, const void *q, int32_t q_d
         p.seq_lens = lens + s0;
         p.part_acc = part_acc;
         p.part_ml = part_ml;
+        p.done = pool->status_dev + BRC_STATUS_WORDS;
+        p.out = out + (size_t)s0 * n_head * hd;
+        p.out_ml = out_ml ? out_ml + (size_t)s0 * n_head * 2 : nullptr;
+        p.gate = gate ? gate + (size_t)s0 * n_head * gate_head_stride : nullptr;
+        p.gate_head_stride = gate_head_stride;
+        p.k_new = app.k_new ? static_cast<const uint8_t *>(app.k_new) + (size_t)s0 * pool->n_kv_head * hd * kv_elem : nullptr;
+        p.v_new = app.v_new ? static_cast<const uint8_t *>(app.v_new) + (size_t)s0 * pool->n_kv_head * hd * kv_elem : nullptr;
+        p.kv_new_f32 = app.dtype == BRC_DTYPE_F32;
+        p.k_base = pool->k_base;
+        p.v_offset = (uint64_t)(pool->v_base - pool->k_base);
         p.status = pool->status_dev;
         p.n_seqs = ns;
         p.table_stride = table_stride;
@@ -705,33 +904,37 @@ brc_status run_decode(brc_pool *pool, uint32_t layer, const void *q, int32_t q_d
             rc = q_dtype == BRC_DTYPE_F32 ? launch_partial_kvb<128, true>(pool, p, grid, smem, st)
                                           : launch_partial_kvb<128, false>(pool, p, grid, smem, st);
         if (rc != BRC_OK) return rc;
-        CombineParams c;
-        c.part_acc = part_acc;
-        c.part_ml = part_ml;
-        c.seq_lens = lens + s0;
-        c.gate = gate ? gate + (size_t)s0 * n_head * gate_head_stride : nullptr;
-        c.out = out + (size_t)s0 * n_head * hd;
-        c.out_ml = out_ml ? out_ml + (size_t)s0 * n_head * 2 : nullptr;
-        c.n_seqs = ns;
-        c.n_kv_head = pool->n_kv_head;
-        c.group = p.group;
-        c.n_head = n_head;
-        c.max_seq_len = max_seq_len;
-        c.gate_head_stride = gate_head_stride;
-        c.n_cta = grid;
-        c.kvb = kvb;
-        brc_stage_begin(pool, BRC_STAGE_ATTN_COMBINE, st);
-        if (hd == 256)
-            decode_combine_kernel<256><<<ns * n_head, 256, 0, st>>>(c);
-        else
-            decode_combine_kernel<128><<<ns * n_head, 128, 0, st>>>(c);
-        brc_stage_end(pool, BRC_STAGE_ATTN_COMBINE, st);
-        BRC_CUDA(cudaGetLastError());
     }
     return BRC_OK;
 }
 
 }  // namespace
+
+// Decode attention of one layer with this step's KV append fused in (used by brc_decode_step): the
+// cell seq_len - 1 of every sequence is written from k_new / v_new by the kernel itself.
+brc_status brc_decode_attn_append_fused(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype, uint32_t n_head,
+                                        const float *gate_dev, uint32_t gate_head_stride, const uint32_t *block_tables_dev,
+                                        uint32_t table_stride, const uint32_t *seq_lens_dev, uint32_t n_seqs,
+                                        uint32_t max_seq_len, float scale, float *out_dev, void *workspace_dev,
+                                        uint64_t workspace_bytes, const void *k_new_dev, const void *v_new_dev,
+                                        int32_t kv_dtype, void *stream) {
+    if (brc_status rc = validate_decode(pool, "brc_decode_step", layer, q_dev, q_dtype, n_head, block_tables_dev, table_stride,
+                                        seq_lens_dev, n_seqs, max_seq_len, out_dev, workspace_dev, workspace_bytes))
+        return rc;
+    if (gate_dev && gate_head_stride < pool->head_dim)
+        return brc_fail(BRC_ERR_INVALID, "brc_decode_step: gate_head_stride %u < head_dim %u", gate_head_stride, pool->head_dim);
+    if (kv_dtype != BRC_DTYPE_F32 && kv_dtype != BRC_DTYPE_F16)
+        return brc_fail(BRC_ERR_INVALID, "brc_decode_step: kv_dtype %d is neither f32 (0) nor f16 (1)", kv_dtype);
+    if (!k_new_dev || !v_new_dev || (reinterpret_cast<uintptr_t>(k_new_dev) & 15u) || (reinterpret_cast<uintptr_t>(v_new_dev) & 15u))
+        return brc_fail(BRC_ERR_INVALID, "brc_decode_step: new K/V pointers must be non-NULL and 16-byte aligned");
+    if (n_seqs == 0) return BRC_OK;
+    FusedAppend app;
+    app.k_new = k_new_dev;
+    app.v_new = v_new_dev;
+    app.dtype = kv_dtype;
+    return run_decode(pool, layer, q_dev, q_dtype, n_head, gate_dev, gate_head_stride, block_tables_dev, table_stride,
+                      seq_lens_dev, n_seqs, max_seq_len, scale, out_dev, nullptr, workspace_dev, brc_stream(stream), app);
+}
 
 extern "C" {
 
@@ -818,7 +1021,8 @@ brc_status brc_decode_combine(int32_t device, const void *parts_dev, uint32_t n_
 // latency-critical decode loop cannot afford cudaMalloc at all: the call synchronises the device, so
 // every stream would stall behind it.  For them the split-KV partials live in the array below, which
 // is part of the library image: every GPU that loads the library holds BRC_STATIC_WS_BYTES of it
-// until the process exits, whether or not this entry point is ever called.
+// until the process exits, whether or not this entry point is ever called.  Nothing in the array has
+// to start at any value: every partial is written before it is read.
 // ---------------------------------------------------------------------------------------------
 #define BRC_STATIC_WS_BYTES (4u << 20)
 

@@ -165,7 +165,7 @@ brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n_kv_head
     const uint64_t bytes = p->layer_bytes * n_layers;
     cudaError_t e;
     // K and V live in one allocation so a single tensor map can address both.
-    if ((e = cudaMalloc(&p->k_base, 2 * bytes)) != cudaSuccess || (e = cudaMalloc(&p->status_dev, 256)) != cudaSuccess ||
+    if ((e = cudaMalloc(&p->k_base, 2 * bytes)) != cudaSuccess || (e = cudaMalloc(&p->status_dev, BRC_STATUS_BYTES)) != cudaSuccess ||
         (e = cudaMallocHost(&p->status_host, 256)) != cudaSuccess) {
         brc_status rc = brc_fail(BRC_ERR_CUDA, "brc_pool_create: allocating 2 x %llu bytes on device %d failed: %s",
                                  (unsigned long long)bytes, device, cudaGetErrorString(e));
@@ -176,7 +176,7 @@ brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n_kv_head
     p->ids_cap = 1u << 16;
     if ((e = cudaMalloc(&p->ids_dev, (size_t)p->ids_cap * 2 * sizeof(uint32_t))) != cudaSuccess ||
         (e = cudaMemset(p->k_base, 0, bytes)) != cudaSuccess || (e = cudaMemset(p->v_base, 0, bytes)) != cudaSuccess ||
-        (e = cudaMemset(p->status_dev, 0, 256)) != cudaSuccess || (e = cudaDeviceSynchronize()) != cudaSuccess) {
+        (e = cudaMemset(p->status_dev, 0, BRC_STATUS_BYTES)) != cudaSuccess || (e = cudaDeviceSynchronize()) != cudaSuccess) {
         brc_status rc = brc_fail(BRC_ERR_CUDA, "brc_pool_create: initialising the pool failed: %s", cudaGetErrorString(e));
         brc_pool_destroy(p);
         return rc;
@@ -332,6 +332,10 @@ brc_status brc_pool_check(brc_pool *pool, void *stream) {
     const uint32_t w = pool->status_host[0];
     const uint32_t detail = pool->status_host[1];
     if (w == 0) return BRC_OK;
+    // A kernel that gave up or skipped work may have left the decode kernels' per-unit arrival counters
+    // (which are otherwise returned to zero by the kernels themselves) in an odd state: clear them.
+    cudaMemsetAsync(pool->status_dev, 0, BRC_STATUS_BYTES, s);
+    cudaStreamSynchronize(s);
     if (w & BRC_DEV_WAIT_LIMIT)
         return brc_fail(BRC_ERR_TIMEOUT, "a kernel gave up a bounded wait (check word 0x%x, detail %u, at %u of %u)", w, detail,
                         pool->status_host[2], pool->status_host[3]);

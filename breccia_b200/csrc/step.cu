@@ -51,15 +51,14 @@ brc_status brc_decode_step(brc_pool *pool, uint32_t layer0, uint32_t n_layers, c
     for (uint32_t i = 0; i < n_layers; ++i) {
         const uint8_t *k = static_cast<const uint8_t *>(k_new_dev) + i * kv_layer_stride_bytes;
         const uint8_t *v = static_cast<const uint8_t *>(v_new_dev) + i * kv_layer_stride_bytes;
-        if (brc_status rc = brc_kv_append(pool, layer0 + i, block_tables_dev, table_stride, pos0_dev, n_seqs, 1, nullptr,
-                                          n_seqs, max_seq_len_after, k, v, kv_dtype, stream))
-            return rc;
         const uint8_t *q = static_cast<const uint8_t *>(q_dev) + i * q_layer_stride_bytes;
         const float *g = gate_dev ? reinterpret_cast<const float *>(reinterpret_cast<const uint8_t *>(gate_dev) + i * gate_layer_stride_bytes) : nullptr;
         float *o = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(out_dev) + i * out_layer_stride_bytes);
-        if (brc_status rc = brc_paged_decode_attn(pool, layer0 + i, q, q_dtype, n_head, g, gate_head_stride, block_tables_dev,
-                                                  table_stride, seq_lens_dev, n_seqs, max_seq_len_after, scale, o,
-                                                  workspace_dev, workspace_bytes, stream))
+        // one kernel per layer: it writes the new cell (fused append) and attends over the whole cache
+        if (brc_status rc = brc_decode_attn_append_fused(pool, layer0 + i, q, q_dtype, n_head, g, gate_head_stride,
+                                                         block_tables_dev, table_stride, seq_lens_dev, n_seqs,
+                                                         max_seq_len_after, scale, o, workspace_dev, workspace_bytes, k, v,
+                                                         kv_dtype, stream))
             return rc;
     }
     return BRC_OK;

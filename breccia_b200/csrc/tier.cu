@@ -1,0 +1,228 @@
+// Tiered paging of KV pages between HBM and pinned host memory on a side stream.
+//
+// The reference has no KV tiering (docs/plan/BRECCIA-PLAN.md:52-56: Phase 6 / M5, not started); its
+// only analogue is the H2D transfer ring (crates/breccia-vk/src/transfer.rs:120-138, 247-369) and the
+// rules of its design note: only complete pages move, a page is in exactly one tier, promotion is
+// asynchronous and off the decode critical path, all layers of a page move together
+// (docs/reference-engines/02-kv-and-context.md:543-581, 617-626).  Here:
+//   * the host tier is one pinned allocation of `host_pages` slots; a slot holds a page of every
+//     layer, K then V ([K: layer][half page] [V: layer][half page] = 2 * n_layers * half_page_bytes);
+//   * demote copies a page HBM -> slot (two strided copies: the page's K of all layers, its V of all
+//     layers) on the tier's own stream, releases the HBM page and hands back the slot;
+//   * promote allocates a fresh HBM page, copies slot -> page and frees the slot; the caller patches
+//     its block table with the new id;
+//   * brc_tier_fence makes another stream wait for every copy issued so far.  A freed HBM page may be
+//     handed out again at once by the allocator: whoever writes it must fence first;
+//   * an LRU helper ranks resident pages by the last brc_tier_touch.
+// One cudaMemcpy2DAsync per (page, K|V): 12 rows of 16 KiB at 12 layers.
+#include <algorithm>
+#include <new>
+#include <vector>
+
+#include "brc_internal.h"
+
+struct brc_tier {
+    brc_pool *pool = nullptr;
+    uint8_t *host = nullptr;        // pinned
+    uint32_t host_pages = 0;
+    uint64_t slot_bytes = 0;
+    cudaStream_t stream = nullptr;  // side stream of the tier
+    cudaEvent_t event = nullptr;    // recorded after every batch
+    std::mutex mu;
+    std::vector<uint32_t> free_slots;
+    std::vector<uint8_t> slot_used;
+    std::vector<uint64_t> last_use;  // per HBM page, 0 = never touched
+    uint64_t clock = 0;
+    uint64_t demoted_pages = 0, promoted_pages = 0, d2h_bytes = 0, h2d_bytes = 0;
+};
+
+extern "C" {
+
+brc_status brc_tier_create(brc_pool *pool, uint32_t host_pages, brc_tier **out) {
+    if (!pool || !out) return brc_fail(BRC_ERR_INVALID, "brc_tier_create: NULL argument");
+    *out = nullptr;
+    if (pool->device < 0 || !pool->k_base)
+        return brc_fail(BRC_ERR_CUDA, "brc_tier_create: this pool holds bookkeeping only (no device memory)");
+    if (host_pages == 0) return brc_fail(BRC_ERR_INVALID, "brc_tier_create: host_pages is 0");
+    brc_device_guard guard(pool->device);
+    brc_tier *t = new (std::nothrow) brc_tier();
+    if (!t) return brc_fail(BRC_ERR_INVALID, "brc_tier_create: out of host memory");
+    t->pool = pool;
+    t->host_pages = host_pages;
+    t->slot_bytes = 2ull * pool->n_layers * pool->half_page_bytes;
+    cudaError_t e;
+    if ((e = cudaMallocHost(&t->host, (size_t)t->slot_bytes * host_pages)) != cudaSuccess ||
+        (e = cudaStreamCreateWithFlags(&t->stream, cudaStreamNonBlocking)) != cudaSuccess ||
+        (e = cudaEventCreateWithFlags(&t->event, cudaEventDisableTiming)) != cudaSuccess) {
+        brc_status rc = brc_fail(BRC_ERR_CUDA, "brc_tier_create: %u pinned slots of %llu bytes: %s", host_pages,
+                                 (unsigned long long)t->slot_bytes, cudaGetErrorString(e));
+        brc_tier_destroy(t);
+        return rc;
+    }
+    cudaEventRecord(t->event, t->stream);
+    t->free_slots.resize(host_pages);
+    for (uint32_t i = 0; i < host_pages; ++i) t->free_slots[i] = host_pages - 1 - i;
+    t->slot_used.assign(host_pages, 0);
+    t->last_use.assign(pool->n_pages, 0);
+    *out = t;
+    return BRC_OK;
+}
+
+brc_status brc_tier_destroy(brc_tier *tier) {
+    if (!tier) return BRC_OK;
+    brc_device_guard guard(tier->pool->device);
+    if (tier->stream) {
+        cudaStreamSynchronize(tier->stream);
+        cudaStreamDestroy(tier->stream);
+    }
+    if (tier->event) cudaEventDestroy(tier->event);
+    if (tier->host) cudaFreeHost(tier->host);
+    delete tier;
+    return BRC_OK;
+}
+
+// One page, both directions: K rows of all layers, then V rows of all layers.
+static cudaError_t copy_page(brc_tier *t, uint32_t page, uint32_t slot, bool to_host) {
+    brc_pool *p = t->pool;
+    uint8_t *hk = t->host + (uint64_t)slot * t->slot_bytes;
+    uint8_t *hv = hk + (uint64_t)p->n_layers * p->half_page_bytes;
+    uint8_t *dk = p->k_base + (uint64_t)page * p->half_page_bytes;
+    uint8_t *dv = p->v_base + (uint64_t)page * p->half_page_bytes;
+    cudaError_t e;
+    if (to_host) {
+        e = cudaMemcpy2DAsync(hk, p->half_page_bytes, dk, p->layer_bytes, p->half_page_bytes, p->n_layers,
+                              cudaMemcpyDeviceToHost, t->stream);
+        if (e == cudaSuccess)
+            e = cudaMemcpy2DAsync(hv, p->half_page_bytes, dv, p->layer_bytes, p->half_page_bytes, p->n_layers,
+                                  cudaMemcpyDeviceToHost, t->stream);
+    } else {
+        e = cudaMemcpy2DAsync(dk, p->layer_bytes, hk, p->half_page_bytes, p->half_page_bytes, p->n_layers,
+                              cudaMemcpyHostToDevice, t->stream);
+        if (e == cudaSuccess)
+            e = cudaMemcpy2DAsync(dv, p->layer_bytes, hv, p->half_page_bytes, p->half_page_bytes, p->n_layers,
+                                  cudaMemcpyHostToDevice, t->stream);
+    }
+    return e;
+}
+
+brc_status brc_tier_demote(brc_tier *tier, const uint32_t *page_ids, uint32_t n, uint32_t *out_slots, void *after_stream) {
+    if (!tier || (!page_ids && n) || (!out_slots && n)) return brc_fail(BRC_ERR_INVALID, "brc_tier_demote: NULL argument");
+    if (n == 0) return BRC_OK;
+    brc_pool *p = tier->pool;
+    brc_device_guard guard(p->device);
+    std::lock_guard<std::mutex> lock(tier->mu);
+    if (tier->free_slots.size() < n)
+        return brc_fail(BRC_ERR_CAPACITY, "brc_tier_demote: %u pages but %zu of %u host slots are free", n,
+                        tier->free_slots.size(), tier->host_pages);
+    for (uint32_t i = 0; i < n; ++i) {
+        uint32_t rc = 0;
+        if (brc_status st = brc_page_refcount(p, page_ids[i], &rc)) return st;
+        if (rc != 1)
+            return brc_fail(BRC_ERR_INVALID, "brc_tier_demote: page %u has %u holders; only a page with exactly one holder "
+                                             "(the caller) can leave HBM", page_ids[i], rc);
+    }
+    // the copies must see everything `after_stream` has written to these pages so far
+    if (after_stream) {
+        cudaEvent_t ev;
+        BRC_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        BRC_CUDA(cudaEventRecord(ev, brc_stream(after_stream)));
+        BRC_CUDA(cudaStreamWaitEvent(tier->stream, ev, 0));
+        BRC_CUDA(cudaEventDestroy(ev));
+    }
+    for (uint32_t i = 0; i < n; ++i) {
+        const uint32_t slot = tier->free_slots.back();
+        cudaError_t e = copy_page(tier, page_ids[i], slot, true);
+        if (e != cudaSuccess) return brc_fail(BRC_ERR_CUDA, "brc_tier_demote: copy of page %u failed: %s", page_ids[i], cudaGetErrorString(e));
+        tier->free_slots.pop_back();
+        tier->slot_used[slot] = 1;
+        out_slots[i] = slot;
+        tier->last_use[page_ids[i]] = 0;
+    }
+    BRC_CUDA(cudaEventRecord(tier->event, tier->stream));
+    tier->demoted_pages += n;
+    tier->d2h_bytes += (uint64_t)n * tier->slot_bytes;
+    // the HBM pages go back to the allocator; their next writer must brc_tier_fence first
+    return brc_pages_release(p, page_ids, n);
+}
+
+brc_status brc_tier_promote(brc_tier *tier, const uint32_t *slots, uint32_t n, uint32_t *out_page_ids) {
+    if (!tier || (!slots && n) || (!out_page_ids && n)) return brc_fail(BRC_ERR_INVALID, "brc_tier_promote: NULL argument");
+    if (n == 0) return BRC_OK;
+    brc_pool *p = tier->pool;
+    brc_device_guard guard(p->device);
+    std::lock_guard<std::mutex> lock(tier->mu);
+    for (uint32_t i = 0; i < n; ++i)
+        if (slots[i] >= tier->host_pages || !tier->slot_used[slots[i]])
+            return brc_fail(BRC_ERR_NOT_RESIDENT, "brc_tier_promote: host slot %u holds no page", slots[i]);
+    if (brc_status rc = brc_pages_alloc(p, n, out_page_ids)) return rc;
+    for (uint32_t i = 0; i < n; ++i) {
+        cudaError_t e = copy_page(tier, out_page_ids[i], slots[i], false);
+        if (e != cudaSuccess) return brc_fail(BRC_ERR_CUDA, "brc_tier_promote: copy of slot %u failed: %s", slots[i], cudaGetErrorString(e));
+        tier->slot_used[slots[i]] = 0;
+        tier->free_slots.push_back(slots[i]);
+        tier->last_use[out_page_ids[i]] = ++tier->clock;
+    }
+    BRC_CUDA(cudaEventRecord(tier->event, tier->stream));
+    tier->promoted_pages += n;
+    tier->h2d_bytes += (uint64_t)n * tier->slot_bytes;
+    return BRC_OK;
+}
+
+brc_status brc_tier_fence(brc_tier *tier, void *stream) {
+    if (!tier) return brc_fail(BRC_ERR_INVALID, "brc_tier_fence: tier is NULL");
+    brc_device_guard guard(tier->pool->device);
+    std::lock_guard<std::mutex> lock(tier->mu);
+    BRC_CUDA(cudaStreamWaitEvent(brc_stream(stream), tier->event, 0));
+    return BRC_OK;
+}
+
+brc_status brc_tier_sync(brc_tier *tier) {
+    if (!tier) return brc_fail(BRC_ERR_INVALID, "brc_tier_sync: tier is NULL");
+    brc_device_guard guard(tier->pool->device);
+    BRC_CUDA(cudaStreamSynchronize(tier->stream));
+    return BRC_OK;
+}
+
+brc_status brc_tier_touch(brc_tier *tier, const uint32_t *page_ids, uint32_t n) {
+    if (!tier || (!page_ids && n)) return brc_fail(BRC_ERR_INVALID, "brc_tier_touch: NULL argument");
+    std::lock_guard<std::mutex> lock(tier->mu);
+    const uint64_t now = ++tier->clock;
+    for (uint32_t i = 0; i < n; ++i) {
+        if (page_ids[i] >= tier->pool->n_pages)
+            return brc_fail(BRC_ERR_INVALID, "brc_tier_touch: page %u of %u", page_ids[i], tier->pool->n_pages);
+        tier->last_use[page_ids[i]] = now;
+    }
+    return BRC_OK;
+}
+
+brc_status brc_tier_lru(brc_tier *tier, uint32_t n, uint32_t *out_page_ids, uint32_t *out_n) {
+    if (!tier || !out_n || (!out_page_ids && n)) return brc_fail(BRC_ERR_INVALID, "brc_tier_lru: NULL argument");
+    std::lock_guard<std::mutex> lock(tier->mu);
+    // touched pages with exactly one holder, least recently touched first
+    std::vector<std::pair<uint64_t, uint32_t>> cand;
+    for (uint32_t pg = 0; pg < tier->pool->n_pages; ++pg) {
+        if (!tier->last_use[pg]) continue;
+        uint32_t rc = 0;
+        if (brc_page_refcount(tier->pool, pg, &rc) != BRC_OK || rc != 1) continue;
+        cand.emplace_back(tier->last_use[pg], pg);
+    }
+    const uint32_t k = std::min<uint32_t>(n, (uint32_t)cand.size());
+    std::partial_sort(cand.begin(), cand.begin() + k, cand.end());
+    for (uint32_t i = 0; i < k; ++i) out_page_ids[i] = cand[i].second;
+    *out_n = k;
+    return BRC_OK;
+}
+
+brc_status brc_tier_stats(brc_tier *tier, uint64_t *out_demoted_pages, uint64_t *out_promoted_pages, uint64_t *out_d2h_bytes,
+                          uint64_t *out_h2d_bytes, uint32_t *out_free_slots) {
+    if (!tier) return brc_fail(BRC_ERR_INVALID, "brc_tier_stats: tier is NULL");
+    std::lock_guard<std::mutex> lock(tier->mu);
+    if (out_demoted_pages) *out_demoted_pages = tier->demoted_pages;
+    if (out_promoted_pages) *out_promoted_pages = tier->promoted_pages;
+    if (out_d2h_bytes) *out_d2h_bytes = tier->d2h_bytes;
+    if (out_h2d_bytes) *out_h2d_bytes = tier->h2d_bytes;
+    if (out_free_slots) *out_free_slots = (uint32_t)tier->free_slots.size();
+    return BRC_OK;
+}
+
+}  // extern "C"

@@ -266,6 +266,57 @@ BRC_API brc_status brc_decode_step(brc_pool *pool, uint32_t layer0, uint32_t n_l
                                    uint64_t out_layer_stride_bytes, void *workspace_dev, uint64_t workspace_bytes,
                                    void *stream);
 
+/* ---------------------------------------------------------------- radix prefix tree (host side)
+ * No counterpart in the reference ("Radix/prompt prefix sharing | open",
+ * docs/BRIEF.md:287); built to its design note: 16-token blocks identified by
+ * their tokens and everything before them, refcounted, with a free queue
+ * (docs/reference-engines/02-kv-and-context.md:543-581).  An edge is one full
+ * page of token ids; a node holds one reference on the page caching that page
+ * of the prefix in every layer.
+ *   match  : longest run of full pages of `tokens` present in the tree; each
+ *            returned page gets one more reference, owned by the caller.
+ *   insert : adds missing nodes for the full pages of `tokens` backed by
+ *            `pages`; the tree takes its own reference on the pages it adopts
+ *            (`*out_n_new` of them); existing nodes keep their page.
+ *   evict  : drops up to n least-recently-used leaves whose page only the tree
+ *            holds, returning those pages to the allocator. */
+BRC_API brc_status brc_radix_create(brc_pool *pool, brc_radix **out);
+BRC_API brc_status brc_radix_destroy(brc_radix *radix);
+BRC_API brc_status brc_radix_match(brc_radix *radix, const uint32_t *tokens, uint32_t n_tokens, uint32_t *out_pages,
+                                   uint32_t max_pages, uint32_t *out_n_pages);
+BRC_API brc_status brc_radix_insert(brc_radix *radix, const uint32_t *tokens, uint32_t n_tokens, const uint32_t *pages,
+                                    uint32_t n_pages, uint32_t *out_n_new);
+BRC_API brc_status brc_radix_evict(brc_radix *radix, uint32_t n_pages, uint32_t *out_n_evicted);
+BRC_API brc_status brc_radix_stats(brc_radix *radix, uint64_t *out_nodes, uint64_t *out_hit_pages,
+                                   uint64_t *out_miss_pages, uint64_t *out_evictions);
+
+/* ---------------------------------------------------------------- HBM <-> pinned host tiering
+ * No KV tiering exists in the reference (docs/plan/BRECCIA-PLAN.md:52-56); the
+ * nearest code is its H2D transfer ring (crates/breccia-vk/src/transfer.rs:
+ * 120-138, 247-369: fixed slots, pinned staging, arrive/release ordering,
+ * RingStats) and the rules of its design note: whole pages only, a page lives in
+ * exactly one tier, all layers move together, promotion is asynchronous
+ * (docs/reference-engines/02-kv-and-context.md:543-581, 617-626).
+ *   demote : pages with exactly one holder go HBM -> host slots on the tier's
+ *            side stream (ordered after `after_stream`'s work so far, if given);
+ *            the HBM pages return to the allocator, `out_slots` names the copies.
+ *   promote: host slots -> freshly allocated HBM pages (`out_page_ids`), slots freed.
+ *   fence  : `stream` waits for every tier copy issued so far (call it before a
+ *            stream reads promoted pages or writes pages freed by a demotion).
+ *   touch / lru: last-use stamps of resident pages and the n least recently used
+ *            single-holder pages, for the caller's demotion policy. */
+BRC_API brc_status brc_tier_create(brc_pool *pool, uint32_t host_pages, brc_tier **out);
+BRC_API brc_status brc_tier_destroy(brc_tier *tier);
+BRC_API brc_status brc_tier_demote(brc_tier *tier, const uint32_t *page_ids, uint32_t n, uint32_t *out_slots,
+                                   void *after_stream);
+BRC_API brc_status brc_tier_promote(brc_tier *tier, const uint32_t *slots, uint32_t n, uint32_t *out_page_ids);
+BRC_API brc_status brc_tier_fence(brc_tier *tier, void *stream);
+BRC_API brc_status brc_tier_sync(brc_tier *tier);
+BRC_API brc_status brc_tier_touch(brc_tier *tier, const uint32_t *page_ids, uint32_t n);
+BRC_API brc_status brc_tier_lru(brc_tier *tier, uint32_t n, uint32_t *out_page_ids, uint32_t *out_n);
+BRC_API brc_status brc_tier_stats(brc_tier *tier, uint64_t *out_demoted_pages, uint64_t *out_promoted_pages,
+                                  uint64_t *out_d2h_bytes, uint64_t *out_h2d_bytes, uint32_t *out_free_slots);
+
 /* ---------------------------------------------------------------- per-stage GPU timers
  * Counterpart of the reference's BRECCIA_GPU_TIME probe and its stage ids
  * KV_APPEND / ATTN (crates/breccia-kernels/src/dispatch_batch.rs:453-512,

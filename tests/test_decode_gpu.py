@@ -168,6 +168,48 @@ def test_cfg2_layer_at_full_size_matches_oracle_and_repeats_bit_identically(cuda
     pool.release()
 
 
+@pytest.mark.parametrize("kv_f16", [False, True])
+def test_decode_step_appends_bit_exactly_and_attends(cuda_device, kv_f16):
+    """brc_decode_step over three layers, three steps in a row: positions advance on the device, the
+    new cell of every sequence is written by the attention kernel itself (fused append) — the pool
+    must equal the oracle's append bit for bit — and the outputs must match the oracle's attention.
+    Lengths include a sequence whose new cell opens a fresh page and a sequence of length 0."""
+    n_head, n_kv, hd, n_layers = 16, 2, 256, 3
+    lens = np.array([16, 5, 1023, 0, 300, 31])
+    tables, n_pool = synth.scattered_tables(55, lens, pool_factor=1.4, extra_tokens=4)
+    pool = KvPool(0, n_layers, n_kv, hd, n_pool)
+    host = []
+    for layer in range(n_layers):
+        k, v = fill_pool_from_host(pool, layer, 500 + 2 * layer)
+        host.append([k.view(np.uint32).copy(), v.view(np.uint32).copy()])
+    batch = DecodeBatch(pool, n_head, tables, lens)
+    cur = lens.copy()
+    for step in range(3):
+        q32 = oracle.to_f16(synth.normal(600 + step, n_layers * lens.size * n_head * hd)).reshape(n_layers, lens.size, n_head, hd)
+        kn = synth.normal(700 + step, n_layers * lens.size * n_kv * hd, 0.5).reshape(n_layers, lens.size, n_kv * hd)
+        vn = synth.normal(800 + step, n_layers * lens.size * n_kv * hd, 0.5).reshape(n_layers, lens.size, n_kv * hd)
+        if kv_f16:
+            kn, vn = oracle.to_f16(kn), oracle.to_f16(vn)
+            kd, vd = torch.from_numpy(kn).cuda().half(), torch.from_numpy(vn).cuda().half()
+        else:
+            kd, vd = torch.from_numpy(kn).cuda(), torch.from_numpy(vn).cuda()
+        out = torch.full((n_layers, lens.size, n_head, hd), float("nan"), device="cuda")
+        batch.step(torch.from_numpy(q32).cuda().half(), kd, vd, out, kv_dtype=_lib.DTYPE_F16 if kv_f16 else DTYPE_F32)
+        pool.check()
+        got = out.cpu().numpy()
+        for layer in range(n_layers):
+            kw, vw = host[layer]
+            for s in range(lens.size):
+                assert oracle.kv_append(kw, vw, tables[s], kn[layer, s], vn[layer, s], int(cur[s]), n_kv, hd) == 0
+            assert np.array_equal(pool.read(0, layer).reshape(-1), kw.view(np.uint16)), f"K pool, layer {layer}, step {step}"
+            assert np.array_equal(pool.read(1, layer).reshape(-1), vw.view(np.uint16)), f"V pool, layer {layer}, step {step}"
+            want, _ = oracle.decode_batch(kw.view(np.uint16), vw.view(np.uint16), tables, cur + 1, q32[layer], n_head, n_kv, hd)
+            assert_attention_close(got[layer], want, f"step {step} layer {layer}")
+        cur += 1
+    assert batch.seq_lens.cpu().numpy().tolist() == cur.tolist()
+    pool.release()
+
+
 def test_nan_poison_outside_live_cells_never_reaches_the_output(cuda_device):
     """Unowned pages and the cells past each sequence end hold NaN (the reference's poison flag,
     qsa/mod.rs:509-523): the output must equal the oracle's, which never looks there."""

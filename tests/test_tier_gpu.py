@@ -1,0 +1,114 @@
+"""Tiered paging HBM <-> pinned host: bit-exact round trips of whole pages (all layers, K and V)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from breccia_b200 import _lib, synth
+from breccia_b200.qsa import DecodeBatch, KvPool
+from helpers import fill_pool_from_host
+
+pytestmark = pytest.mark.gpu
+U32P = C.POINTER(C.c_uint32)
+
+
+def arr(a):
+    a = np.ascontiguousarray(a, np.uint32)
+    return a, a.ctypes.data_as(U32P)
+
+
+def test_demote_promote_round_trip_is_bit_exact_and_pages_move_between_tiers(cuda_device):
+    n_layers, n_pages = 3, 40
+    pool = KvPool(0, n_layers, 2, 256, n_pages)
+    L = _lib.load()
+    mine, mp = arr(np.zeros(30))
+    assert L.brc_pages_alloc(pool.handle, 30, mp) == 0
+    before = []
+    for layer in range(n_layers):
+        fill_pool_from_host(pool, layer, 900 + 2 * layer)
+        before.append((pool.read(0, layer).copy(), pool.read(1, layer).copy()))
+    tier = C.c_void_p()
+    assert L.brc_tier_create(pool.handle, 16, C.byref(tier)) == 0
+    # LRU: touch everything, then re-touch a few; the least recently used come out first
+    assert L.brc_tier_touch(tier, mp, 30) == 0
+    hot, hp = arr(mine[:20])
+    assert L.brc_tier_touch(tier, hp, 20) == 0
+    vict, vp = arr(np.zeros(10))
+    nv = C.c_uint32()
+    assert L.brc_tier_lru(tier, 10, vp, C.byref(nv)) == 0 and nv.value == 10
+    assert sorted(vict.tolist()) == sorted(mine[20:].tolist())
+    slots, sp = arr(np.zeros(10))
+    assert L.brc_tier_demote(tier, vp, 10, sp, None) == 0
+    assert pool.free_count() == n_pages - 30 + 10
+    assert L.brc_tier_sync(tier) == 0
+    # scribble over the freed HBM pages: the host copy must be independent of them
+    pool.poison_nan()
+    for layer in range(n_layers):
+        pool.write(0, layer, before[layer][0])
+        pool.write(1, layer, before[layer][1])
+        junk = np.full((2, 16, 256), 0xABCD, np.uint16)
+        for pg in vict:
+            pool.write(0, layer, junk, byte_offset=int(pg) * pool.half_page_bytes)
+            pool.write(1, layer, junk, byte_offset=int(pg) * pool.half_page_bytes)
+    back, bp = arr(np.zeros(10))
+    assert L.brc_tier_promote(tier, sp, 10, bp) == 0
+    assert L.brc_tier_fence(tier, None) == 0
+    torch.cuda.synchronize()
+    for layer in range(n_layers):
+        k, v = pool.read(0, layer), pool.read(1, layer)
+        for old, new in zip(vict, back):
+            assert np.array_equal(k[new], before[layer][0][old]), f"K layer {layer} page {old}->{new}"
+            assert np.array_equal(v[new], before[layer][1][old])
+    st = [C.c_uint64() for _ in range(4)]
+    fs = C.c_uint32()
+    assert L.brc_tier_stats(tier, *(C.byref(x) for x in st), C.byref(fs)) == 0
+    slot_bytes = 2 * n_layers * pool.half_page_bytes
+    assert [x.value for x in st] == [10, 10, 10 * slot_bytes, 10 * slot_bytes] and fs.value == 16
+    # refusals: a shared page cannot leave HBM, an empty slot cannot be promoted, the tier can fill up
+    pool.retain(mine[:1])
+    one, op = arr(mine[:1])
+    assert L.brc_tier_demote(tier, op, 1, sp, None) == _lib.ERR_INVALID and b"holders" in L.brc_last_error()
+    pool.release_pages(mine[:1])
+    assert L.brc_tier_promote(tier, sp, 1, bp) == _lib.ERR_NOT_RESIDENT
+    many, manyp = arr(mine[:17])
+    big, bigp = arr(np.zeros(17))
+    assert L.brc_tier_demote(tier, manyp, 17, bigp, None) == _lib.ERR_CAPACITY
+    L.brc_tier_destroy(tier)
+    pool.release()
+
+
+def test_attention_over_promoted_pages_equals_attention_before_demotion(cuda_device):
+    """Decode, demote half of a sequence's pages, promote them to other page ids, patch the block
+    table, decode again: identical output (the cache content did not change, only its placement)."""
+    n_head, n_kv, hd = 16, 2, 256
+    lens = np.array([1000])
+    n_seq_pages = 63
+    pool = KvPool(0, 2, n_kv, hd, 100)
+    L = _lib.load()
+    table, tp = arr(np.zeros(n_seq_pages))
+    assert L.brc_pages_alloc(pool.handle, n_seq_pages, tp) == 0
+    for layer in range(2):
+        fill_pool_from_host(pool, layer, 950 + 2 * layer)
+    q = torch.from_numpy(synth.normal(960, n_head * hd)).cuda().half().view(1, n_head, hd)
+    out0 = torch.empty((1, n_head, hd), device="cuda")
+    DecodeBatch(pool, n_head, table[None, :], lens).attend(1, q, out0)
+    tier = C.c_void_p()
+    assert L.brc_tier_create(pool.handle, 40, C.byref(tier)) == 0
+    cold, cp = arr(table[::2].copy())
+    slots, sp = arr(np.zeros(cold.size))
+    assert L.brc_tier_demote(tier, cp, cold.size, sp, C.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
+    filler, fp = arr(np.zeros(5))
+    assert L.brc_pages_alloc(pool.handle, 5, fp) == 0      # so the promoted pages land elsewhere
+    new, npp = arr(np.zeros(cold.size))
+    assert L.brc_tier_promote(tier, sp, cold.size, npp) == 0
+    assert L.brc_tier_fence(tier, C.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
+    table2 = table.copy()
+    table2[::2] = new
+    assert not np.array_equal(table2, table)
+    out1 = torch.empty((1, n_head, hd), device="cuda")
+    DecodeBatch(pool, n_head, table2[None, :], lens).attend(1, q, out1)
+    pool.check()
+    assert np.array_equal(out0.cpu().numpy(), out1.cpu().numpy())
+    L.brc_tier_destroy(tier)
+    pool.release()
