@@ -21,7 +21,9 @@
 // brc_pool::status_dev: 64 words of check state, then the decode kernels' per-unit arrival counters
 // (2048 words, zero between launches: the kernels reset what they count).
 #define BRC_STATUS_WORDS 64u
-#define BRC_DONE_WORDS 2048u
+#define BRC_DONE_BANK_WORDS 2048u
+#define BRC_DONE_BANKS 64u     // one bank per layer of a decode step whose layers overlap
+#define BRC_DONE_WORDS (BRC_DONE_BANK_WORDS * BRC_DONE_BANKS)
 #define BRC_STATUS_BYTES ((BRC_STATUS_WORDS + BRC_DONE_WORDS) * 4u)
 
 // Stage ids of the optional GPU timers are public (breccia_kv.h); this is their count.
@@ -96,6 +98,6 @@ brc_status brc_decode_attn_append_fused(brc_pool *pool, uint32_t layer, const vo
                                         uint32_t table_stride, const uint32_t *seq_lens_dev, uint32_t n_seqs,
                                         uint32_t max_seq_len, float scale, float *out_dev, void *workspace_dev,
                                         uint64_t workspace_bytes, const void *k_new_dev, const void *v_new_dev,
-                                        int32_t kv_dtype, void *stream);
+                                        int32_t kv_dtype, uint32_t index_in_step, uint32_t layers_in_step, void *stream);
 
 static inline cudaStream_t brc_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }

@@ -87,6 +87,7 @@ struct DecodeParams {
     uint32_t n_pages;    // pages per layer
     uint32_t layer_row0; // first row of this layer in the TMA view
     uint32_t n_stages;
+    uint32_t pdl;        // 1: let the next kernel in the stream start as this one's CTAs retire
     float scale_log2;    // scale * log2(e)
 };
 
@@ -367,6 +368,11 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             }
         }
     }
+
+    // Programmatic dependent launch: the next kernel of the stream (the next layer of the same decode
+    // step, which reads nothing this kernel writes and has its own partial buffers and counters) may
+    // take over each SM as soon as this kernel's CTA there retires, instead of idling through the tail.
+    if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const uint32_t total = S[n_units];
     const uint32_t a = share_begin(blockIdx.x, total, gridDim.x);
@@ -799,7 +805,21 @@ brc_status launch_partial(brc_pool *pool, const DecodeParams &p, uint32_t grid, 
         configured[pool->device] = true;
     }
     brc_stage_begin(pool, BRC_STAGE_ATTN_PARTIAL, st);
-    kern<<<grid, NTHREADS, smem, st>>>(KVB == 2 ? pool->tm_kv2 : pool->tm_kv, p);
+    if (p.pdl) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(NTHREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        BRC_CUDA(cudaLaunchKernelEx(&cfg, kern, KVB == 2 ? pool->tm_kv2 : pool->tm_kv, p));
+    } else {
+        kern<<<grid, NTHREADS, smem, st>>>(KVB == 2 ? pool->tm_kv2 : pool->tm_kv, p);
+    }
     brc_stage_end(pool, BRC_STAGE_ATTN_PARTIAL, st);
     BRC_CUDA(cudaGetLastError());
     return BRC_OK;
@@ -846,6 +866,10 @@ struct FusedAppend {
     const void *k_new = nullptr;   // [n_seqs][n_kv_head * head_dim], the cell seq_len - 1 of every sequence
     const void *v_new = nullptr;
     int32_t dtype = BRC_DTYPE_F32;
+    // Overlap with the neighbouring layers of the same step: this launch uses bank `bank` (0 / 1) of
+    // the partial buffers and arrival counters, so the kernel before it may still be combining.
+    bool overlap = false;
+    uint32_t bank = 0;
 };
 
 // out_ml != nullptr: partial mode (out = merged acc, out_ml = (m, l)); else final output.  One launch
@@ -863,7 +887,8 @@ brc_status run_decode(brc_pool *pool, uint32_t layer, const void *q, int32_t q_d
     const uint32_t grid = grid_ctas(pool);
     const uint32_t per = seqs_per_launch(pool);
     const uint64_t slots = slots_for(pool, n_seqs);
-    float *part_acc = static_cast<float *>(ws);
+    const uint64_t bank_floats = slots * GROUP_TILE * ((uint64_t)hd + 2u);
+    float *part_acc = static_cast<float *>(ws) + (app.overlap ? app.bank * bank_floats : 0);
     float *part_ml = part_acc + slots * GROUP_TILE * hd;
     const size_t q_elem = q_dtype == BRC_DTYPE_F32 ? 4 : 2;
     const size_t kv_elem = app.dtype == BRC_DTYPE_F32 ? 4 : 2;
@@ -875,7 +900,8 @@ brc_status run_decode(brc_pool *pool, uint32_t layer, const void *q, int32_t q_d
         p.seq_lens = lens + s0;
         p.part_acc = part_acc;
         p.part_ml = part_ml;
-        p.done = pool->status_dev + BRC_STATUS_WORDS;
+        p.done = pool->status_dev + BRC_STATUS_WORDS + (app.overlap ? app.bank * BRC_DONE_BANK_WORDS : 0u);
+        p.pdl = app.overlap && !pool->timing && n_seqs <= per;   // per-stage events would serialise anyway
         p.out = out + (size_t)s0 * n_head * hd;
         p.out_ml = out_ml ? out_ml + (size_t)s0 * n_head * 2 : nullptr;
         p.gate = gate ? gate + (size_t)s0 * n_head * gate_head_stride : nullptr;
@@ -917,7 +943,7 @@ brc_status brc_decode_attn_append_fused(brc_pool *pool, uint32_t layer, const vo
                                         uint32_t table_stride, const uint32_t *seq_lens_dev, uint32_t n_seqs,
                                         uint32_t max_seq_len, float scale, float *out_dev, void *workspace_dev,
                                         uint64_t workspace_bytes, const void *k_new_dev, const void *v_new_dev,
-                                        int32_t kv_dtype, void *stream) {
+                                        int32_t kv_dtype, uint32_t index_in_step, uint32_t layers_in_step, void *stream) {
     if (brc_status rc = validate_decode(pool, "brc_decode_step", layer, q_dev, q_dtype, n_head, block_tables_dev, table_stride,
                                         seq_lens_dev, n_seqs, max_seq_len, out_dev, workspace_dev, workspace_bytes))
         return rc;
@@ -932,6 +958,14 @@ brc_status brc_decode_attn_append_fused(brc_pool *pool, uint32_t layer, const vo
     app.k_new = k_new_dev;
     app.v_new = v_new_dev;
     app.dtype = kv_dtype;
+    // A workspace of layers_in_step times the minimum gives every layer of the step its own partial
+    // buffers and arrival counters: the layers (independent of one another) may then overlap freely.
+    // Nothing less is safe: a kernel whose CTAs have little or no work lets its successors start at
+    // once, so any number of the step's kernels can be in flight together.
+    uint64_t need = 0;
+    brc_decode_workspace_bytes(pool, n_seqs, n_head, &need);
+    app.overlap = layers_in_step > 1 && layers_in_step <= BRC_DONE_BANKS && workspace_bytes >= (uint64_t)layers_in_step * need;
+    app.bank = index_in_step;
     return run_decode(pool, layer, q_dev, q_dtype, n_head, gate_dev, gate_head_stride, block_tables_dev, table_stride,
                       seq_lens_dev, n_seqs, max_seq_len, scale, out_dev, nullptr, workspace_dev, brc_stream(stream), app);
 }

@@ -58,7 +58,7 @@ brc_status brc_decode_step(brc_pool *pool, uint32_t layer0, uint32_t n_layers, c
         if (brc_status rc = brc_decode_attn_append_fused(pool, layer0 + i, q, q_dtype, n_head, g, gate_head_stride,
                                                          block_tables_dev, table_stride, seq_lens_dev, n_seqs,
                                                          max_seq_len_after, scale, o, workspace_dev, workspace_bytes, k, v,
-                                                         kv_dtype, stream))
+                                                         kv_dtype, i, n_layers, stream))
             return rc;
     }
     return BRC_OK;

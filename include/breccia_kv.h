@@ -255,7 +255,17 @@ BRC_API brc_status brc_paged_decode_attn_static(brc_pool *pool, uint32_t layer, 
  *       append k_new/v_new[layer][s] at cell pos0[s];  out[layer] = decode attention
  * q / k_new / v_new / gate / out are per-layer arrays laid `*_layer_stride_bytes`
  * apart ([n_seqs][n_head][head_dim] and [n_seqs][n_kv_head*head_dim]).
- * `max_seq_len_after` bounds seq_lens AFTER the increment. */
+ * `max_seq_len_after` bounds seq_lens AFTER the increment.
+ * The append is carried out by the attention kernel itself (the CTA about to
+ * stream the page of a sequence's newest cell writes that cell first), so a step
+ * is one small kernel plus one kernel per layer.  The layers of a step do not
+ * depend on one another; when `workspace_bytes` is at least n_layers times
+ * brc_decode_workspace_bytes(), each layer gets its own partial buffers and the
+ * kernels are launched so that a layer may start on every SM the previous one
+ * has left (programmatic dependent launch).  With a smaller workspace the
+ * layers run strictly one after another; results are the same.
+ * Decode calls on one pool must not run concurrently on different streams: they
+ * share the pool's arrival counters. */
 BRC_API brc_status brc_decode_step(brc_pool *pool, uint32_t layer0, uint32_t n_layers,
                                    const uint32_t *block_tables_dev, uint32_t table_stride, uint32_t *seq_lens_dev,
                                    uint32_t *pos0_dev, uint32_t n_seqs, uint32_t max_seq_len_after, const void *q_dev,
