@@ -1,0 +1,519 @@
+// Chunked-prefill attention over a paged prefix on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// Replaces the reference's T >= 16 path: qsa_attn_scores_gqa.comp + ops_softmax.comp +
+// qsa_attn_apply_gqa.comp driven tile by tile from Qsa::forward
+// (crates/breccia-kernels/src/qsa/mod.rs:1631-1641), i.e. one workgroup per (token, kv head) doing
+// CUDA-core style dot products.  Semantics kept: all cells of the chunk are in the cache before any
+// row attends; row t (position pos0 + t) sees cells <= pos0 + t; kv head = h * n_kv / n_head; f16 K/V,
+// fp32 accumulation; gate optional (sigmoid, applied last).
+//
+// One CTA = one (sequence, kv head, 16 query tokens): a 128-row tile, row = token * 8 + query head of
+// the group (GQA: the 8 query heads of a kv head share every K/V byte the CTA stages).  Per block of
+// 64 cells (4 pages):
+//   S[128 x 64]  = Q[128 x 256] . K^T      tcgen05.mma kind::f16, M=128 N=64, 16 steps of K=16, fp32 in TMEM
+//   P            = 2^(scale' S - m)        4 softmax warps, one thread per row, tcgen05.ld; causal mask
+//   O[128 x 256] += P[128 x 64] . V        tcgen05.mma M=128 N=256, 4 steps of K=16, V read MN-major
+// Q, K, V and P sit in shared memory in the canonical 128-byte-swizzled layouts the matrix descriptors
+// name.  K/V pages are gathered through the block table by four loader warps with 16-byte cp.async
+// (a 16-cell page is too small a TMA box: ~215 cycles per operation whatever its size), two stages in
+// flight; cells at or past the end of the cache are zero-filled.  O stays in TMEM across blocks and is
+// rescaled only when a row's maximum grew by more than 2^8 since the scale in use (rare after the
+// first blocks), so P may exceed 1 by at most that factor — harmless in binary16 with fp32 sums.
+// Every wait is bounded; TMEM is released on every path.
+#include <algorithm>
+
+#include "brc_device.cuh"
+#include "brc_internal.h"
+
+namespace {
+
+constexpr int PF_HD = 256;
+constexpr int PF_ROWS = 128;              // 16 tokens x 8 head slots
+constexpr int PF_TOK = 16;
+constexpr int PF_BLK = 64;                // cells per block
+constexpr int PF_STAGES = 2;
+constexpr int PF_SOFTMAX_WARPS = 4;       // warps 0-3: TMEM lane quarter = warp id
+constexpr int PF_MMA_WARP = 4;
+constexpr int PF_LOAD_WARP0 = 5;          // warps 5-8
+constexpr int PF_LOAD_WARPS = 4;
+constexpr int PF_THREADS = (PF_SOFTMAX_WARPS + 1 + PF_LOAD_WARPS) * 32;
+constexpr uint32_t PF_Q_BYTES = PF_ROWS * PF_HD * 2;      // 64 KiB: 4 slabs [128 rows][128 B]
+constexpr uint32_t PF_Q_SLAB = PF_ROWS * 128;
+constexpr uint32_t PF_KV_SLAB = PF_BLK * 128;             // [64 cells][128 B]
+constexpr uint32_t PF_K_BYTES = 4 * PF_KV_SLAB;           // 32 KiB
+constexpr uint32_t PF_STAGE_BYTES = 2 * PF_K_BYTES;       // K then V
+constexpr uint32_t PF_P_BYTES = PF_ROWS * 128;            // [128 rows][64 cells] f16
+constexpr uint32_t PF_SMEM = 1024 + PF_Q_BYTES + PF_P_BYTES + PF_STAGES * PF_STAGE_BYTES + 1024;
+constexpr uint32_t PF_TMEM_COLS = 512;
+constexpr uint32_t PF_S_COL = 0, PF_O_COL = 64;
+constexpr uint64_t PF_WAIT_NS = 1000000000ull;
+constexpr float PF_RESCALE_THRESHOLD = 8.0f;              // log2 units
+
+struct PrefillParams {
+    const void *q;                 // [n_seqs][chunk][n_head][256], f16 or f32
+    const uint8_t *k_layer;        // this layer's K pool
+    const uint8_t *v_layer;
+    const uint32_t *block_tables;  // [n_seqs][table_stride]
+    const uint32_t *pos0;          // [n_seqs]
+    const float *gate;             // nullable, [n_seqs][chunk][n_head][..] with gate_head_stride
+    float *out;                    // [n_seqs][chunk][n_head][256] f32
+    uint32_t *status;
+    uint32_t n_seqs, chunk, table_stride, max_pos_end;
+    uint32_t n_kv_head, group, n_head, n_pages, q_f32, gate_head_stride;
+    float scale_log2;
+};
+
+__device__ __forceinline__ uint64_t pf_globaltimer() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ bool pf_wait(uint32_t bar, uint32_t parity) {
+    if (brc::mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = pf_globaltimer();
+    for (uint32_t i = 0; i < (1u << 30); ++i) {
+        if (brc::mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 63u && pf_globaltimer() - t0 > PF_WAIT_NS) return false;
+    }
+    return false;
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+// K-major operands: rows 128 B apart inside an 8-row group, groups `sbo` bytes apart (lbo unused = 1).
+// MN-major operands: 64 contiguous elements per 128-byte row, 64-element groups `lbo` bytes apart,
+// 8-row (K) groups `sbo` bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fffu);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
+    d |= (uint64_t)1 << 46;   // version
+    d |= (uint64_t)2 << 61;   // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor, kind::f16: D = f32, A = B = f16, M = 128.
+__device__ __forceinline__ uint32_t umma_idesc(uint32_t n, bool b_mn_major) {
+    return (1u << 4) | ((b_mn_major ? 1u : 0u) << 16) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+          "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+          "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+          "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+          "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
+          "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+          "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+          "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
+          "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// 16-byte async copy; src_bytes = 0 writes zeros.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ float pf_sigmoid(float x) {
+    if (x >= 0.f) return 1.f / (1.f + expf(-x));
+    const float e = expf(x);
+    return e / (1.f + e);
+}
+
+__global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const PrefillParams p) {
+    extern __shared__ uint8_t pf_smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023u) & ~uintptr_t(1023));
+    uint8_t *q_sm = smem;
+    uint8_t *p_sm = q_sm + PF_Q_BYTES;
+    uint8_t *st_sm = p_sm + PF_P_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(st_sm + PF_STAGES * PF_STAGE_BYTES);
+    const uint32_t bar_full = brc::smem_u32(bars);            // [PF_STAGES]
+    const uint32_t bar_empty = bar_full + 8u * PF_STAGES;      // [PF_STAGES]
+    const uint32_t bar_q = bar_empty + 8u * PF_STAGES;
+    const uint32_t bar_s = bar_q + 8u;
+    const uint32_t bar_p = bar_s + 8u;
+    const uint32_t bar_o = bar_p + 8u;
+    volatile uint32_t *misc = reinterpret_cast<volatile uint32_t *>(bars + 16);   // [0] tmem base, [1] dead
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t kvh = blockIdx.x % p.n_kv_head;
+    const uint32_t tile = blockIdx.x / p.n_kv_head;
+    const uint32_t s = blockIdx.y;
+    const uint32_t t0 = tile * PF_TOK;
+    const uint32_t pos0 = p.pos0[s];
+    const uint32_t kv_len = pos0 + p.chunk;                    // cells in the cache (all of the chunk is appended)
+    if (kv_len > p.max_pos_end) {
+        if (tid == 0) { atomicOr(p.status, BRC_DEV_BAD_POS); p.status[1] = kv_len; }
+        return;
+    }
+    const uint32_t n_tok = min((uint32_t)PF_TOK, p.chunk - t0);
+    const uint32_t cells_needed = pos0 + t0 + n_tok;           // the tile's last row sees cells < this
+    const uint32_t n_blk = (cells_needed + PF_BLK - 1) / PF_BLK;
+
+    if (tid == 0) {
+        for (int i = 0; i < PF_STAGES; ++i) {
+            brc::mbar_init(bar_full + 8u * i, PF_LOAD_WARPS * 32);
+            brc::mbar_init(bar_empty + 8u * i, 1);
+        }
+        brc::mbar_init(bar_q, PF_LOAD_WARPS * 32);
+        brc::mbar_init(bar_s, 1);
+        brc::mbar_init(bar_p, PF_SOFTMAX_WARPS * 32);
+        brc::mbar_init(bar_o, 1);
+        brc::mbar_fence_init();
+        misc[1] = 0u;
+    }
+    if (warp == PF_MMA_WARP) {   // one warp owns the TMEM allocation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(brc::smem_u32(const_cast<uint32_t *>(misc))),
+                     "r"(PF_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = misc[0];
+
+    if (warp >= PF_LOAD_WARP0) {
+        // ------------------------------------------------------------------ loader warps
+        const uint32_t lt = tid - PF_LOAD_WARP0 * 32;   // 0..127
+        // Q tile: row = token * 8 + head slot; 32 chunks of 16 B per row; 4 slabs of [128 rows][128 B]
+        for (uint32_t c = lt; c < PF_ROWS * 32; c += PF_LOAD_WARPS * 32) {
+            const uint32_t row = c >> 5, ch = c & 31u;
+            const uint32_t tl = row >> 3, h = row & 7u;
+            const bool live = tl < n_tok && h < p.group;
+            const uint32_t dst = brc::smem_u32(q_sm) + (ch >> 3) * PF_Q_SLAB + row * 128u + (((ch & 7u) ^ (row & 7u)) << 4);
+            const uint64_t qrow = ((uint64_t)(s * p.chunk + t0 + (live ? tl : 0)) * p.n_head + kvh * p.group + (live ? h : 0)) * PF_HD;
+            if (!p.q_f32) {
+                cp_async16(dst, static_cast<const uint16_t *>(p.q) + qrow + ch * 8u, live ? 16u : 0u);
+            } else {
+                uint4 w = make_uint4(0, 0, 0, 0);
+                if (live) {
+                    const float4 *src = reinterpret_cast<const float4 *>(static_cast<const float *>(p.q) + qrow + ch * 8u);
+                    const float4 a = __ldg(src), b = __ldg(src + 1);
+                    w = make_uint4(brc::pack_half2(a.x, a.y), brc::pack_half2(a.z, a.w), brc::pack_half2(b.x, b.y), brc::pack_half2(b.z, b.w));
+                }
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(w.x), "r"(w.y), "r"(w.z), "r"(w.w) : "memory");
+            }
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        brc::fence_proxy_async_smem();
+        brc::mbar_arrive(bar_q);
+
+        const uint32_t *table = p.block_tables + (uint64_t)s * p.table_stride;
+        for (uint32_t j = 0; j < n_blk && !misc[1]; ++j) {
+            const uint32_t stg = j % PF_STAGES;
+            if (!pf_wait(bar_empty + 8u * stg, ((j / PF_STAGES) & 1u) ^ 1u)) {
+                misc[1] = 1u;
+                if (lt == 0) { atomicOr(p.status, BRC_DEV_WAIT_LIMIT); p.status[1] = 3000000u + blockIdx.x; }
+                break;
+            }
+            const uint32_t k_dst = brc::smem_u32(st_sm) + stg * PF_STAGE_BYTES, v_dst = k_dst + PF_K_BYTES;
+            for (uint32_t c = lt; c < PF_BLK * 32; c += PF_LOAD_WARPS * 32) {
+                const uint32_t r = c >> 5, ch = c & 31u;
+                const uint32_t cell = j * PF_BLK + r;
+                const bool live = cell < kv_len;   // past the end of the cache: zeros (and no table read)
+                uint32_t page = 0;
+                if (live) {
+                    page = __ldg(table + (cell >> 4));
+                    if (page >= p.n_pages) {
+                        atomicOr(p.status, BRC_DEV_BAD_PAGE);
+                        p.status[1] = page;
+                        page = 0;
+                    }
+                }
+                const uint64_t src = (((uint64_t)page * p.n_kv_head + kvh) * 16u + (cell & 15u)) * (PF_HD * 2u) + ch * 16u;
+                const uint32_t off = (ch >> 3) * PF_KV_SLAB + r * 128u + (((ch & 7u) ^ (r & 7u)) << 4);
+                cp_async16(k_dst + off, p.k_layer + src, live ? 16u : 0u);
+                cp_async16(v_dst + off, p.v_layer + src, live ? 16u : 0u);
+            }
+            cp_async_commit();
+            if (j > 0) {   // the block before this one has landed: publish it
+                cp_async_wait<1>();
+                brc::fence_proxy_async_smem();
+                brc::mbar_arrive(bar_full + 8u * ((j - 1) % PF_STAGES));
+            }
+        }
+        cp_async_wait<0>();
+        brc::fence_proxy_async_smem();
+        if (n_blk > 0 && !misc[1]) brc::mbar_arrive(bar_full + 8u * ((n_blk - 1) % PF_STAGES));
+    } else if (warp == PF_MMA_WARP) {
+        // ------------------------------------------------------------------ MMA issue (one thread)
+        if (lane == 0) {
+            const uint32_t idesc_s = umma_idesc(PF_BLK, false);
+            const uint32_t idesc_o = umma_idesc(PF_HD, true);
+            bool ok = pf_wait(bar_q, 0);
+            brc::fence_proxy_async_smem();
+            for (uint32_t j = 0; j < n_blk && ok && !misc[1]; ++j) {
+                const uint32_t stg = j % PF_STAGES;
+                const uint32_t k_sm = brc::smem_u32(st_sm) + stg * PF_STAGE_BYTES, v_sm = k_sm + PF_K_BYTES;
+                ok = pf_wait(bar_full + 8u * stg, (j / PF_STAGES) & 1u);
+                if (!ok) break;
+                brc::fence_proxy_async_smem();
+                tc_fence_after();
+                // S = Q . K^T: 16 steps of K = 16 (32 bytes inside a 128-byte swizzled row; 4 steps per slab)
+#pragma unroll
+                for (uint32_t ks = 0; ks < PF_HD / 16; ++ks) {
+                    const uint64_t a = umma_desc(brc::smem_u32(q_sm) + (ks >> 2) * PF_Q_SLAB + (ks & 3u) * 32u, 16, 1024);
+                    const uint64_t b = umma_desc(k_sm + (ks >> 2) * PF_KV_SLAB + (ks & 3u) * 32u, 16, 1024);
+                    umma_f16(tmem + PF_S_COL, a, b, idesc_s, ks > 0);
+                }
+                umma_commit(bar_s);
+                ok = pf_wait(bar_p, j & 1u);
+                if (!ok) break;
+                tc_fence_after();
+                // O += P . V: 4 steps of K = 16 cells; V is MN-major: 16 cells = 2048 bytes down a slab,
+                // the four 64-column slabs are 8 KiB apart (leading offset), 8-cell groups 1 KiB apart
+#pragma unroll
+                for (uint32_t ks = 0; ks < PF_BLK / 16; ++ks) {
+                    const uint64_t a = umma_desc(brc::smem_u32(p_sm) + ks * 32u, 16, 1024);
+                    const uint64_t b = umma_desc(v_sm + ks * 2048u, PF_KV_SLAB, 1024);
+                    umma_f16(tmem + PF_O_COL, a, b, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                }
+                umma_commit(bar_o);
+                umma_commit(bar_empty + 8u * stg);
+            }
+            if (!ok) {
+                misc[1] = 1u;
+                atomicOr(p.status, BRC_DEV_WAIT_LIMIT);
+                p.status[1] = 4000000u + blockIdx.x;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax warps: thread = row
+        const uint32_t row = tid;                       // TMEM lane
+        const uint32_t tl = row >> 3, h = row & 7u;
+        const uint32_t limit = pos0 + t0 + tl;          // last cell this row sees
+        const uint32_t lane_base = (warp * 32u) << 16;  // this warp's TMEM lane quarter
+        float m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (uint32_t j = 0; j < n_blk; ++j) {
+            // warp-uniform control flow: the TMEM accesses below are warp-wide
+            if (__any_sync(0xffffffffu, misc[1] != 0u)) break;
+            ok = __all_sync(0xffffffffu, pf_wait(bar_s, j & 1u));
+            if (!ok) break;
+            tc_fence_after();
+            float sc[PF_BLK];
+            {
+                float v[32];
+                tmem_ld32(tmem + lane_base + PF_S_COL, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) sc[i] = v[i] * p.scale_log2;
+                tmem_ld32(tmem + lane_base + PF_S_COL + 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) sc[32 + i] = v[i] * p.scale_log2;
+            }
+            const uint32_t c0 = j * PF_BLK;
+            float mx = -INFINITY;
+            if (c0 + PF_BLK - 1 > limit) {
+#pragma unroll
+                for (int i = 0; i < PF_BLK; ++i) {
+                    if (c0 + i > limit) sc[i] = -INFINITY;
+                    mx = fmaxf(mx, sc[i]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < PF_BLK; ++i) mx = fmaxf(mx, sc[i]);
+            }
+            // P overwrites the previous block's P and O may be rescaled: both need the previous P.V done
+            if (j > 0) {
+                ok = __all_sync(0xffffffffu, pf_wait(bar_o, (j - 1) & 1u));
+                if (!ok) break;
+                tc_fence_after();
+            }
+            // Raise the scale in use when this row's maximum grew a lot (or at its first live block):
+            // O *= 2^(old - new).  TMEM loads and stores are warp-wide, so the warp goes through the
+            // rescale together and rows that need none multiply by one.
+            const bool raise = mx > m_used + PF_RESCALE_THRESHOLD;
+            float f = 1.f;
+            if (raise) {
+                if (m_used != -INFINITY) f = brc::fast_exp2(m_used - mx);
+                l *= f;
+                m_used = mx;
+            }
+            if (j > 0 && __any_sync(0xffffffffu, f != 1.f)) {
+#pragma unroll 1
+                for (int cg = 0; cg < PF_HD / 32; ++cg) {
+                    float v[32];
+                    tmem_ld32(tmem + lane_base + PF_O_COL + cg * 32, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] *= f;
+                    tmem_st32(tmem + lane_base + PF_O_COL + cg * 32, v);
+                }
+            }
+            // P row (binary16) into its swizzled shared-memory row: 8 chunks of 8 cells
+            const uint32_t prow = brc::smem_u32(p_sm) + row * 128u;
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+                uint32_t w[4];
+#pragma unroll
+                for (int k2 = 0; k2 < 4; ++k2) {
+                    const float a = m_used == -INFINITY ? 0.f : brc::fast_exp2(sc[ch * 8 + k2 * 2] - m_used);
+                    const float b = m_used == -INFINITY ? 0.f : brc::fast_exp2(sc[ch * 8 + k2 * 2 + 1] - m_used);
+                    l += a + b;
+                    w[k2] = brc::pack_half2(a, b);
+                }
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(prow + ((ch ^ (row & 7u)) << 4)), "r"(w[0]), "r"(w[1]),
+                             "r"(w[2]), "r"(w[3])
+                             : "memory");
+            }
+            brc::fence_proxy_async_smem();
+            tc_fence_before();
+            brc::mbar_arrive(bar_p);
+        }
+        if (ok && n_blk > 0 && !__any_sync(0xffffffffu, misc[1] != 0u)) {
+            ok = __all_sync(0xffffffffu, pf_wait(bar_o, (n_blk - 1) & 1u));
+            if (ok) {
+                tc_fence_after();
+                const bool live = tl < n_tok && h < p.group;
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                const uint64_t orow = ((uint64_t)(s * p.chunk + t0 + tl) * p.n_head + kvh * p.group + h);
+#pragma unroll 1
+                for (int cg = 0; cg < PF_HD / 32; ++cg) {
+                    float v[32];
+                    tmem_ld32(tmem + lane_base + PF_O_COL + cg * 32, v);
+                    if (live) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            float4 r = make_float4(v[i] * inv, v[i + 1] * inv, v[i + 2] * inv, v[i + 3] * inv);
+                            if (p.gate) {
+                                const float *g = p.gate + orow * p.gate_head_stride + cg * 32 + i;
+                                r.x *= pf_sigmoid(g[0]);
+                                r.y *= pf_sigmoid(g[1]);
+                                r.z *= pf_sigmoid(g[2]);
+                                r.w *= pf_sigmoid(g[3]);
+                            }
+                            *reinterpret_cast<float4 *>(p.out + orow * PF_HD + cg * 32 + i) = r;
+                        }
+                    }
+                }
+            }
+        }
+        if (!ok) {
+            misc[1] = 1u;
+            if (lane == 0) { atomicOr(p.status, BRC_DEV_WAIT_LIMIT); p.status[1] = 5000000u + blockIdx.x; }
+        }
+    }
+    // everyone is done with TMEM (or has given up): release it
+    tc_fence_before();
+    __syncthreads();
+    if (warp == PF_MMA_WARP) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(PF_TMEM_COLS) : "memory");
+    }
+}
+
+
+}  // namespace
+
+extern "C" {
+
+brc_status brc_paged_prefill_attn(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype, uint32_t n_head,
+                                  const float *gate_dev, uint32_t gate_head_stride, const uint32_t *block_tables_dev,
+                                  uint32_t table_stride, const uint32_t *pos0_dev, uint32_t n_seqs, uint32_t chunk_len,
+                                  uint32_t max_pos_end, float scale, float *out_dev, void *stream) {
+    if (!pool) return brc_fail(BRC_ERR_INVALID, "brc_paged_prefill_attn: pool is NULL");
+    if (pool->device < 0 || !pool->k_base)
+        return brc_fail(BRC_ERR_CUDA, "brc_paged_prefill_attn: this pool holds bookkeeping only (no device memory)");
+    if (layer >= pool->n_layers)
+        return brc_fail(BRC_ERR_INVALID, "brc_paged_prefill_attn: layer %u but the pool has %u", layer, pool->n_layers);
+    if (pool->head_dim != PF_HD)
+        return brc_fail(BRC_ERR_UNSUPPORTED, "brc_paged_prefill_attn: head_dim %u (the tensor-core prefill path is built for %d)",
+                        pool->head_dim, PF_HD);
+    if (q_dtype != BRC_DTYPE_F32 && q_dtype != BRC_DTYPE_F16)
+        return brc_fail(BRC_ERR_INVALID, "brc_paged_prefill_attn: q_dtype %d is neither f32 (0) nor f16 (1)", q_dtype);
+    if (n_head == 0 || n_head % pool->n_kv_head != 0)
+        return brc_fail(BRC_ERR_INVALID, "brc_paged_prefill_attn: %u query heads do not divide over %u kv heads", n_head,
+                        pool->n_kv_head);
+    if (n_head / pool->n_kv_head > 8)
+        return brc_fail(BRC_ERR_UNSUPPORTED, "brc_paged_prefill_attn: %u query heads per kv head (a tile holds up to 8)",
+                        n_head / pool->n_kv_head);
+    const uint64_t capacity = (uint64_t)table_stride * pool->page_tokens;
+    if (max_pos_end > capacity)
+        return brc_fail(BRC_ERR_CAPACITY,
+                        "brc_paged_prefill_attn would read cells up to %u but each block table holds %llu (%u pages of %u cells)",
+                        max_pos_end, (unsigned long long)capacity, table_stride, pool->page_tokens);
+    if (gate_dev && gate_head_stride < pool->head_dim)
+        return brc_fail(BRC_ERR_INVALID, "brc_paged_prefill_attn: gate_head_stride %u < head_dim %u", gate_head_stride, pool->head_dim);
+    if (n_seqs == 0 || chunk_len == 0) return BRC_OK;
+    if (!q_dev || !block_tables_dev || !pos0_dev || !out_dev)
+        return brc_fail(BRC_ERR_INVALID, "brc_paged_prefill_attn: NULL query, block table, position or output pointer");
+    if ((reinterpret_cast<uintptr_t>(q_dev) & 15u) || (reinterpret_cast<uintptr_t>(out_dev) & 15u))
+        return brc_fail(BRC_ERR_INVALID, "brc_paged_prefill_attn: query and output pointers must be 16-byte aligned");
+    if (n_seqs > 65535u) return brc_fail(BRC_ERR_INVALID, "brc_paged_prefill_attn: %u sequences in one call (limit 65535)", n_seqs);
+    brc_device_guard guard(pool->device);
+    static bool configured[64] = {};
+    if (pool->device < 64 && !configured[pool->device]) {
+        BRC_CUDA(cudaFuncSetAttribute(prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
+        configured[pool->device] = true;
+    }
+    PrefillParams p;
+    p.q = q_dev;
+    p.k_layer = pool->k_base + (uint64_t)layer * pool->layer_bytes;
+    p.v_layer = pool->v_base + (uint64_t)layer * pool->layer_bytes;
+    p.block_tables = block_tables_dev;
+    p.pos0 = pos0_dev;
+    p.gate = gate_dev;
+    p.out = out_dev;
+    p.status = pool->status_dev;
+    p.n_seqs = n_seqs;
+    p.chunk = chunk_len;
+    p.table_stride = table_stride;
+    p.max_pos_end = max_pos_end;
+    p.n_kv_head = pool->n_kv_head;
+    p.group = n_head / pool->n_kv_head;
+    p.n_head = n_head;
+    p.n_pages = pool->n_pages;
+    p.q_f32 = q_dtype == BRC_DTYPE_F32;
+    p.gate_head_stride = gate_head_stride;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    const uint32_t tiles = (chunk_len + PF_TOK - 1) / PF_TOK;
+    dim3 grid(tiles * pool->n_kv_head, n_seqs);
+    brc_stage_begin(pool, BRC_STAGE_PREFILL, brc_stream(stream));
+    prefill_attn_kernel<<<grid, PF_THREADS, PF_SMEM, brc_stream(stream)>>>(p);
+    brc_stage_end(pool, BRC_STAGE_PREFILL, brc_stream(stream));
+    BRC_CUDA(cudaGetLastError());
+    return BRC_OK;
+}
+
+}  // extern "C"
+

@@ -276,6 +276,26 @@ BRC_API brc_status brc_decode_step(brc_pool *pool, uint32_t layer0, uint32_t n_l
                                    uint64_t out_layer_stride_bytes, void *workspace_dev, uint64_t workspace_bytes,
                                    void *stream);
 
+/* ---------------------------------------------------------------- chunked-prefill attention (tensor cores)
+ * Replaces the reference's T >= 16 path: qsa_attn_scores_gqa.comp + ops_softmax.comp
+ * + qsa_attn_apply_gqa.comp, tiled from Qsa::forward
+ * (crates/breccia-kernels/src/qsa/mod.rs:1631-1641; GQA_MIN_TOKENS, ATTN_TILE
+ * :116-135).  Every sequence brings `chunk_len` query rows at positions
+ * pos0_dev[s] .. pos0_dev[s] + chunk_len - 1; all of the chunk's cells must already
+ * be in the cache (the reference appends before it attends, qsa/mod.rs:1617->1638);
+ * row t sees cells <= pos0 + t.  Sequences may share prefix pages.
+ *   q_dev    [n_seqs][chunk_len][n_head][head_dim], f16 bits or f32 (rounded to f16 for the
+ *            tensor cores); out_dev same shape, f32; gate as in brc_paged_decode_attn with
+ *            rows (s, t, h).
+ *   max_pos_end  caller's bound on pos0[s] + chunk_len; refused if > table_stride*page_tokens.
+ * head_dim 256 and up to 8 query heads per kv head.  tcgen05.mma with accumulators in
+ * TMEM; K/V pages gathered through the block table. */
+BRC_API brc_status brc_paged_prefill_attn(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype,
+                                          uint32_t n_head, const float *gate_dev, uint32_t gate_head_stride,
+                                          const uint32_t *block_tables_dev, uint32_t table_stride,
+                                          const uint32_t *pos0_dev, uint32_t n_seqs, uint32_t chunk_len,
+                                          uint32_t max_pos_end, float scale, float *out_dev, void *stream);
+
 /* ---------------------------------------------------------------- radix prefix tree (host side)
  * No counterpart in the reference ("Radix/prompt prefix sharing | open",
  * docs/BRIEF.md:287); built to its design note: 16-token blocks identified by
