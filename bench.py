@@ -166,6 +166,7 @@ def run_native(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        os.environ["NCCL_DEBUG"] = "WARN"   # no version banner on stdout: rank 0 prints exactly one JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     steps, warmup = args.steps, max(args.warmup, 0)
@@ -324,10 +325,11 @@ def cpu_baseline_sample(pool, batch, q):
     tables = batch.block_tables.cpu().numpy().astype(np.uint32)
     lens = batch.seq_lens.cpu().numpy().astype(np.uint32)
     spent, layers_done = 0.0, 0
-    while layers_done < N_LAYERS and spent < 12.0:
-        kp = pool.read(0, layers_done).reshape(-1)
-        vp = pool.read(1, layers_done).reshape(-1)
-        ql = q[layers_done].float().cpu().numpy()
+    while spent < 12.0 and layers_done < 10 * N_LAYERS:   # about 12 s of CPU work, layers taken round-robin
+        layer = layers_done % N_LAYERS
+        kp = pool.read(0, layer).reshape(-1)
+        vp = pool.read(1, layer).reshape(-1)
+        ql = q[layer].float().cpu().numpy()
         t0 = time.perf_counter()
         _, used = oracle.decode_batch(kp, vp, tables, lens, ql, N_HEAD, N_KV, HD, n_threads=threads)
         spent += time.perf_counter() - t0
@@ -335,7 +337,7 @@ def cpu_baseline_sample(pool, batch, q):
         threads = used
     per_layer = spent / layers_done
     return {"value": N_SEQS / (per_layer * N_LAYERS), "unit": "tok/s", "cores": threads, "kind": "port",
-            "sample": f"{layers_done} of {N_LAYERS} layers of one decode step of the same 32 sequences "
+            "sample": f"{layers_done} layer-passes (of the {N_LAYERS} layers of one decode step) over the same 32 sequences "
                       f"({spent:.1f} s of CPU work), scaled to 12 layers; f64 attention as in qsa/cpu.rs"}
 
 

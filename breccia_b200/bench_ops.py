@@ -1,0 +1,188 @@
+"""Per-operator benchmark of the paged-KV path (the counterpart of the reference's `breccia bench ops
+--op qsa`, crates/breccia-kernels/src/qsa/bench.rs; one JSON line per cell with the fields of its
+`OpCell`: op, case, units, bytes or flops, us, GB/s or TFLOP/s, iters).
+
+    python -m breccia_b200.bench_ops [--op prefill|append|gather|copy|fork|tier|all] [--iters N]
+
+Timing: CUDA events on the launching stream, 3 warm-up runs, the mean of `iters` runs.  Shapes are the
+BASELINE configurations: prefill = 64 sequences sharing a 4096-token prefix, 256-token chunk each
+(GQA 16q/2kv, head_dim 256); the byte movers run on the same pool.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+
+import numpy as np
+import torch
+
+from . import _lib, synth
+from ._lib import DTYPE_F16, DTYPE_F32
+from .qsa import KvPool, _ptr, _stream_ptr
+
+N_HEAD, N_KV, HD = 16, 2, 256
+
+
+def timed(fn, iters: int) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / iters  # us
+
+
+def emit(**kw):
+    print(json.dumps(kw), flush=True)
+
+
+def dev_u32(a):
+    return torch.as_tensor(np.ascontiguousarray(a, np.uint32).astype(np.int32), device="cuda")
+
+
+def cfg4_tables(pool: KvPool, n_seqs: int, prefix: int, chunk: int):
+    """Shared prefix pages + private suffix pages; a partial last prefix page is forked copy-on-write."""
+    n_prefix_pages = (prefix + 15) // 16
+    owner = pool.alloc(n_prefix_pages)
+    total_pages = (prefix + chunk + 15) // 16
+    tables = np.zeros((n_seqs, total_pages), np.uint32)
+    fork_us = 0.0
+    for s in range(n_seqs):
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        child, fresh = pool.fork(owner, prefix)
+        t1.record()
+        torch.cuda.synchronize()
+        fork_us += t0.elapsed_time(t1) * 1e3
+        tables[s, :n_prefix_pages] = child
+        tables[s, n_prefix_pages:] = pool.alloc(total_pages - n_prefix_pages)
+    return owner, tables, fork_us / n_seqs
+
+
+def bench_prefill(iters: int, prefix: int):
+    n_seqs, chunk = 64, 256
+    n_pages = (prefix + 15) // 16 + n_seqs * 18 + 8
+    pool = KvPool(0, 1, N_KV, HD, n_pages)
+    owner, tables, fork_us = cfg4_tables(pool, n_seqs, prefix, chunk)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(4)
+    # fill the prefix once (through the owner's table) and every suffix (chunk append of 64 x 256 tokens)
+    t_dev = dev_u32(tables)
+    zero = dev_u32([0])
+    kp = torch.randn((prefix, N_KV * HD), generator=gen, device="cuda") * 0.5
+    vp = torch.randn((prefix, N_KV * HD), generator=gen, device="cuda") * 0.5
+    # each sequence's copy-on-write page holds the same prefix cells, so write the prefix through every table
+    for s in range(n_seqs if prefix % 16 else 1):
+        _lib.call("brc_kv_append", pool.handle, 0, C.c_void_p(t_dev[s].data_ptr()), tables.shape[1], _ptr(zero), 1, prefix, None,
+                  prefix, prefix, _ptr(kp), _ptr(vp), DTYPE_F32, _stream_ptr())
+    pos0 = dev_u32(np.full(n_seqs, prefix))
+    ks = torch.randn((n_seqs * chunk, N_KV * HD), generator=gen, device="cuda") * 0.5
+    vs = torch.randn((n_seqs * chunk, N_KV * HD), generator=gen, device="cuda") * 0.5
+
+    def append():
+        _lib.call("brc_kv_append", pool.handle, 0, _ptr(t_dev), tables.shape[1], _ptr(pos0), n_seqs, chunk, None,
+                  n_seqs * chunk, prefix + chunk, _ptr(ks), _ptr(vs), DTYPE_F32, _stream_ptr())
+
+    us = timed(append, iters)
+    nbytes = n_seqs * chunk * (N_KV * HD * 2 * 2 + N_KV * HD * 4 * 2)
+    emit(op="kv_append", case=f"chunk append, {n_seqs} sequences x {chunk} tokens, f32 sources, 1 layer", units=n_seqs * chunk,
+         bytes=nbytes, us=us, gbps=nbytes / us / 1e3, iters=iters)
+    q = (torch.randn((n_seqs, chunk, N_HEAD, HD), generator=gen, device="cuda")).half()
+    out = torch.empty((n_seqs, chunk, N_HEAD, HD), dtype=torch.float32, device="cuda")
+
+    def prefill():
+        _lib.call("brc_paged_prefill_attn", pool.handle, 0, _ptr(q), DTYPE_F16, N_HEAD, None, 0, _ptr(t_dev), tables.shape[1],
+                  _ptr(pos0), n_seqs, chunk, prefix + chunk, 1.0 / 16.0, _ptr(out), _stream_ptr())
+
+    us = timed(prefill, iters)
+    pool.check()
+    visible = chunk * prefix + chunk * (chunk + 1) // 2
+    flops = 4.0 * N_HEAD * HD * visible * n_seqs
+    emit(op="paged_prefill_attn", case=f"{n_seqs} sequences, shared {prefix}-token prefix, {chunk}-token chunk, 16q/2kv hd256, 1 layer",
+         units=n_seqs * chunk, flops=flops, us=us, tflops=flops / us / 1e6, iters=iters,
+         cow_fork_us_per_sequence=fork_us, partial_prefix_page=bool(prefix % 16))
+    pool.release()
+
+
+def bench_movers(iters: int):
+    n_layers, n_pages = 12, 4096
+    pool = KvPool(0, n_layers, N_KV, HD, n_pages)
+    ids = pool.alloc(n_pages)
+    perm = synth.permutation(9, n_pages)
+    # gather: 8192 cells of one sequence through a scattered table
+    table = dev_u32(perm[:512])
+    k_out, v_out = pool.gather(0, table, 8192)
+
+    def gather():
+        _lib.call("brc_page_gather", pool.handle, 0, _ptr(table), 512, 8192, _ptr(k_out), _ptr(v_out), _stream_ptr())
+
+    us = timed(gather, iters)
+    nbytes = 2 * 8192 * N_KV * HD * 2 * 2
+    emit(op="page_gather", case="8192 cells of one sequence, 1 layer, K and V", units=512, bytes=nbytes, us=us,
+         gbps=nbytes / us / 1e3, iters=iters)
+    # copy: 1024 pages, all 12 layers, K and V
+    src, dst = dev_u32(perm[:1024]), dev_u32(perm[1024:2048])
+
+    def copy():
+        _lib.call("brc_page_copy", pool.handle, _ptr(src), _ptr(dst), 1024, _stream_ptr())
+
+    us = timed(copy, iters)
+    nbytes = 2 * 1024 * n_layers * 2 * pool.half_page_bytes
+    emit(op="page_copy", case="1024 pages x 12 layers, K and V (read + write)", units=1024, bytes=nbytes, us=us,
+         gbps=nbytes / us / 1e3, iters=iters)
+    # tiering: demote / promote 512 pages (all layers) on the tier's side stream
+    L = _lib.load()
+    tier = C.c_void_p()
+    _lib.call("brc_tier_create", pool.handle, 600, C.byref(tier))
+    n = 512
+    pages = np.ascontiguousarray(ids[:n], np.uint32)
+    slots = np.zeros(n, np.uint32)
+    back = np.zeros(n, np.uint32)
+    U32P = C.POINTER(C.c_uint32)
+    d_us, p_us = [], []
+    for _ in range(max(2, iters // 4)):
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        torch.cuda.synchronize()
+        import time
+        t0 = time.perf_counter()
+        _lib.call("brc_tier_demote", tier, pages.ctypes.data_as(U32P), n, slots.ctypes.data_as(U32P), None)
+        _lib.call("brc_tier_sync", tier)
+        t1 = time.perf_counter()
+        _lib.call("brc_tier_promote", tier, slots.ctypes.data_as(U32P), n, back.ctypes.data_as(U32P))
+        _lib.call("brc_tier_sync", tier)
+        t2 = time.perf_counter()
+        pages = back.copy()
+        d_us.append((t1 - t0) * 1e6)
+        p_us.append((t2 - t1) * 1e6)
+    nbytes = n * 2 * n_layers * pool.half_page_bytes
+    emit(op="tier_demote", case=f"{n} pages x 12 layers HBM -> pinned host (wall clock incl. issue)", units=n, bytes=nbytes,
+         us=min(d_us), gbps=nbytes / min(d_us) / 1e3, iters=len(d_us))
+    emit(op="tier_promote", case=f"{n} pages x 12 layers pinned host -> HBM (wall clock incl. issue)", units=n, bytes=nbytes,
+         us=min(p_us), gbps=nbytes / min(p_us) / 1e3, iters=len(p_us))
+    _lib.call("brc_tier_destroy", tier)
+    pool.release()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="all", choices=["all", "prefill", "movers"])
+    ap.add_argument("--iters", type=int, default=20)
+    a = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench_ops needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(0)
+    if a.op in ("all", "prefill"):
+        bench_prefill(a.iters, 4096)
+        bench_prefill(a.iters, 4088)   # last prefix page partial: forked copy-on-write per sequence
+    if a.op in ("all", "movers"):
+        bench_movers(a.iters)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,70 @@
+"""Worker of tests/test_splitkv_multigpu.py (launched with torch.distributed.run, one rank per GPU):
+one long sequence split along its KV length over the ranks; every rank must obtain the attention
+output of the whole sequence.  Rank 0 checks it against the oracle.  Prints one line and exits 0 / 1."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import oracle  # noqa: E402
+from breccia_b200 import synth  # noqa: E402
+from breccia_b200.qsa import DecodeBatch, KvPool  # noqa: E402
+from breccia_b200.splitkv import SplitKvDecode, kv_range  # noqa: E402
+
+
+def main():
+    n_tokens = int(sys.argv[1]) if len(sys.argv) > 1 else 5000
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    n_head, n_kv, hd = 16, 2, 256
+    # the whole sequence's K/V (logical order), the same on every rank
+    k = oracle.f32_to_f16_bits_np(synth.normal(1, n_tokens * n_kv * hd, 0.5)).reshape(n_tokens, n_kv, hd)
+    v = oracle.f32_to_f16_bits_np(synth.normal(2, n_tokens * n_kv * hd, 0.5)).reshape(n_tokens, n_kv, hd)
+    q = oracle.to_f16(synth.normal(3, n_head * hd)).reshape(1, n_head, hd)
+    b, e = kv_range(rank, world, n_tokens)
+    n_local = e - b
+    n_pages = max((n_local + 15) // 16, 1)
+    pool = KvPool(local, 1, n_kv, hd, n_pages + 3)
+    table = synth.permutation(10 + rank, n_pages + 3)[:n_pages]
+    kp = np.zeros((n_pages + 3, n_kv, 16, hd), np.uint16)
+    vp = np.zeros_like(kp)
+    for c in range(n_local):
+        kp[table[c // 16], :, c % 16, :] = k[b + c]
+        vp[table[c // 16], :, c % 16, :] = v[b + c]
+    pool.write(0, 0, kp)
+    pool.write(1, 0, vp)
+    split = SplitKvDecode(pool, n_head, table, n_local)
+    qd = torch.from_numpy(q).cuda().half()
+    out = torch.full((1, n_head, hd), float("nan"), device="cuda")
+    for _ in range(3):
+        split.attend(0, qd, out)
+    pool.check()
+    got = out.cpu().numpy()[0]
+    # every rank must hold the same answer
+    ref = out.clone()
+    dist.broadcast(ref, 0)
+    same = bool(torch.equal(ref, out))
+    ok = same
+    if rank == 0:
+        kf = oracle.f16_bits_to_f32(k)
+        vf = oracle.f16_bits_to_f32(v)
+        want = oracle.attend(q[0], kf, vf, np.arange(n_tokens, dtype=np.uint32), n_tokens - 1, n_head, n_kv, hd)
+        err = float(np.abs(got - want).max())
+        ok = ok and np.isfinite(got).all() and err <= 2e-3
+        print(f"splitkv world {world} tokens {n_tokens}: max_abs {err:.2e} identical_on_all_ranks {same}", flush=True)
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    pool.release()
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag.item()) == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()
