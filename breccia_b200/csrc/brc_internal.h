@@ -21,7 +21,7 @@
 // brc_pool::status_dev: 64 words of check state, then the decode kernels' per-unit arrival counters
 // (2048 words, zero between launches: the kernels reset what they count).
 #define BRC_STATUS_WORDS 64u
-#define BRC_DONE_BANK_WORDS 2048u
+#define BRC_DONE_BANK_WORDS 2560u  // 2048 unit tickets + 2 x 256 run tickets of the two-level merge
 #define BRC_DONE_BANKS 64u     // one bank per layer of a decode step whose layers overlap
 #define BRC_DONE_WORDS (BRC_DONE_BANK_WORDS * BRC_DONE_BANKS)
 #define BRC_STATUS_BYTES ((BRC_STATUS_WORDS + BRC_DONE_WORDS) * 4u)

@@ -149,10 +149,16 @@ __device__ __forceinline__ void share_range(uint32_t first_g, uint32_t last_g, u
 // into weights, and the accumulation then issues independent 16-byte loads (nothing in the inner loop
 // waits on a previous load).  `sm` is the CTA's merge scratch, free at this point.
 constexpr uint32_t COMBINE_CHUNK = 32;
+constexpr uint32_t TWO_LEVEL_MIN = 24;    // a unit over more shares than this is merged in two levels
+constexpr uint32_t MAX_RUN_CTAS = 256;    // run tickets: 2 words per CTA after the MAX_UNITS unit tickets
 
+//
+// The shares merged are i_lo, i_lo + stride, ... <= i_hi.  With to_slot the merged (acc, m, l) go back
+// into the partial slot of share i_lo instead of the output: that is the first level of the two-level
+// merge of a unit that spans many CTAs (see the ticket code in the kernel).
 template <int HD, int KVB>
-__device__ __forceinline__ void combine_unit(const DecodeParams &p, uint32_t u, uint32_t i_lo, uint32_t i_hi, uint32_t total,
-                                             uint32_t tid, float *sm) {
+__device__ __forceinline__ void combine_unit(const DecodeParams &p, uint32_t u, uint32_t i_lo, uint32_t i_hi, uint32_t stride,
+                                             bool to_slot, uint32_t total, uint32_t tid, float *sm) {
     constexpr uint32_t TPR = HD / 4;                    // threads per output row (float4 each)
     constexpr uint32_t ROWS_PER_PASS = (NW * 32) / TPR;
     constexpr uint32_t MAX_ROWS = KVB * GROUP_TILE;
@@ -178,10 +184,10 @@ __device__ __forceinline__ void combine_unit(const DecodeParams &p, uint32_t u, 
         // ---- the next chunk of non-empty shares
         uint32_t i_next;
         if (dense) {
-            const uint32_t n = min(COMBINE_CHUNK, i_hi - i0 + 1);
-            if (tid < n) list[tid] = i0 + tid;
+            const uint32_t n = min(COMBINE_CHUNK, (i_hi - i0) / stride + 1);
+            if (tid < n) list[tid] = i0 + tid * stride;
             if (tid == 0) n_list[0] = n;
-            i_next = i0 + n;
+            i_next = i0 + n * stride;
         } else {
             if (tid == 0) {
                 uint32_t n = 0, i = i0;
@@ -275,7 +281,11 @@ __device__ __forceinline__ void combine_unit(const DecodeParams &p, uint32_t u, 
         const float2 ml = mls[row];
         const uint32_t head = (kv0 + k2) * p.group + h;
         const size_t o = ((size_t)s * p.n_head + head) * HD + d;
-        if (p.out_ml) {
+        if (to_slot) {
+            const size_t slot = ((size_t)(u + i_lo) * KVB + k2) * GROUP_TILE + h;
+            *reinterpret_cast<float4 *>(p.part_acc + slot * HD + d) = acc[ps];
+            if (d == 0) *reinterpret_cast<float2 *>(p.part_ml + slot * 2) = ml;
+        } else if (p.out_ml) {
             *reinterpret_cast<float4 *>(p.out + o) = acc[ps];
             if (d == 0) {
                 p.out_ml[((size_t)s * p.n_head + head) * 2] = ml.x;
@@ -710,22 +720,62 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         // ---- ticket: the CTA that completes the last share of a unit combines all of its shares
         uint32_t i_lo, i_hi;
         share_range(unit_first, S[u + 1] - 1, total, gridDim.x, i_lo, i_hi);
-        if (tid == 0) {
-            uint32_t pieces = i_hi - i_lo + 1;
-            if (total < gridDim.x) {   // fewer page-units than CTAs: some shares in between are empty
-                pieces = 0;
-                for (uint32_t i = i_lo; i <= i_hi; ++i)
-                    pieces += share_begin(i, total, gridDim.x) != share_begin(i + 1, total, gridDim.x);
+        // A unit that spans many CTAs (one long sequence alone on the GPU spans all of them) is merged
+        // in two levels, or its last arriver would pull every share through one SM: runs of `fan`
+        // consecutive shares have a ticket of their own, the run's last arriver merges the run into the
+        // slot of its first share, and the last run to finish merges the runs.
+        const uint32_t span = i_hi - i_lo + 1;
+        const bool two_level = total >= gridDim.x && span > TWO_LEVEL_MIN && gridDim.x <= MAX_RUN_CTAS;
+        if (!two_level) {
+            if (tid == 0) {
+                uint32_t pieces = span;
+                if (total < gridDim.x) {   // fewer page-units than CTAs: some shares in between are empty
+                    pieces = 0;
+                    for (uint32_t i = i_lo; i <= i_hi; ++i)
+                        pieces += share_begin(i, total, gridDim.x) != share_begin(i + 1, total, gridDim.x);
+                }
+                const uint32_t ticket = atomicAdd(p.done + u, 1u);
+                const uint32_t last = ticket + 1u == pieces;
+                if (last) p.done[u] = 0;   // every share has arrived: leave the counter clean for the next launch
+                flags[0] = last;
             }
-            const uint32_t ticket = atomicAdd(p.done + u, 1u);
-            const uint32_t last = ticket + 1u == pieces;
-            if (last) p.done[u] = 0;   // every share has arrived: leave the counter clean for the next launch
-            flags[0] = last;
-        }
-        brc::named_bar_sync(1, NW * 32);
-        if (flags[0]) {
-            __threadfence();
-            combine_unit<HD, KVB>(p, u, i_lo, i_hi, total, tid, scratch);
+            brc::named_bar_sync(1, NW * 32);
+            if (flags[0]) {
+                __threadfence();
+                combine_unit<HD, KVB>(p, u, i_lo, i_hi, 1, false, total, tid, scratch);
+            }
+        } else {
+            uint32_t fan = 1;
+            while (fan * fan < span) ++fan;                 // ~sqrt: both levels merge about as many
+            const uint32_t run = (blockIdx.x - i_lo) / fan;
+            const uint32_t r_lo = i_lo + run * fan, r_hi = min(r_lo + fan - 1, i_hi);
+            if (tid == 0) {
+                // Runs of neighbouring units can start on the same CTA only as (last run of one unit,
+                // first run of the next): the second word of the pair keeps those apart.
+                uint32_t *cnt = p.done + MAX_UNITS + 2u * r_lo + (run != 0u);
+                const uint32_t ticket = atomicAdd(cnt, 1u);
+                const uint32_t last = ticket + 1u == r_hi - r_lo + 1u;
+                if (last) *cnt = 0;
+                flags[0] = last;
+            }
+            brc::named_bar_sync(1, NW * 32);
+            if (flags[0]) {
+                __threadfence();
+                combine_unit<HD, KVB>(p, u, r_lo, r_hi, 1, true, total, tid, scratch);
+                __threadfence();   // the run's merged partial is visible before the unit's ticket is taken
+                brc::named_bar_sync(1, NW * 32);
+                if (tid == 0) {
+                    const uint32_t ticket = atomicAdd(p.done + u, 1u);
+                    const uint32_t last = ticket + 1u == (span + fan - 1u) / fan;
+                    if (last) p.done[u] = 0;
+                    flags[0] = last;
+                }
+                brc::named_bar_sync(1, NW * 32);
+                if (flags[0]) {
+                    __threadfence();
+                    combine_unit<HD, KVB>(p, u, i_lo, i_hi, fan, false, total, tid, scratch);
+                }
+            }
         }
         brc::named_bar_sync(1, NW * 32);
 

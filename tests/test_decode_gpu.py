@@ -327,6 +327,33 @@ def test_partials_then_combine_equals_fused_call(cuda_device):
     pool.release()
 
 
+@pytest.mark.parametrize("n_head,n_kv,lens", [
+    (16, 2, [24000]),            # one unit over every CTA: runs of ~13 shares, then the runs
+    (16, 2, [9000, 12000]),      # two units of ~60 and ~85 shares; they meet inside one CTA
+    (8, 1, [13000, 40, 9000]),   # one kv head per unit (a 16-row box), a short unit in between
+    (32, 4, [30000]),            # two units per sequence (4 kv heads), head_dim 128
+])
+def test_units_spanning_many_ctas_merge_in_two_levels(cuda_device, n_head, n_kv, lens):
+    """Long sequences alone on the GPU: every unit spans more than 24 CTA shares, so the in-kernel merge
+    runs in two levels (runs of shares, then the runs).  Final output and the partial (acc, m, l) form,
+    twice over, so that the tickets are seen to reset."""
+    hd = 128 if n_head == 32 else 256
+    pool, batch, qd, got, want = _batch_case(n_head, n_kv, hd, lens, seed=120 + len(lens) + n_kv)
+    assert_attention_close(got, want, f"two-level merge {lens}")
+    again = torch.full_like(torch.from_numpy(got), float("nan")).cuda()
+    batch.attend(0, qd, again)
+    assert np.array_equal(again.cpu().numpy(), got), "second launch differs: a ticket was left dirty"
+    n = len(lens)
+    nbytes = decode_partial_bytes(n, n_head, hd)
+    part = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    batch.partial(0, qd, part)
+    out = torch.empty((n, n_head, hd), device="cuda")
+    decode_combine(0, part, 1, nbytes, n, n_head, hd, out)
+    pool.check()
+    assert_attention_close(out.cpu().numpy(), want, f"two-level merge, partial form {lens}")
+    pool.release()
+
+
 def test_more_units_than_one_launch_holds(cuda_device):
     """1100 short sequences x 2 kv heads exceed the 2048 units one launch schedules: the host loops."""
     lens = (np.arange(1100) % 37 + 1).astype(np.int64)
