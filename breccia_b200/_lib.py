@@ -96,6 +96,14 @@ SIGNATURES = {
     "brc_tier_touch": [_vp, _u32p, _u32],
     "brc_tier_lru": [_vp, _u32, _u32p, _u32p],
     "brc_tier_stats": [_vp, _u64p, _u64p, _u64p, _u64p, _u32p],
+    "brc_comm_create": [_vp, _u32, _u32, _u32, _u32, _vpp],
+    "brc_comm_ipc_handle": [_vp, _vp],
+    "brc_comm_connect_ipc": [_vp, _vp, _u32],
+    "brc_comm_connect_local": [_vp, _vpp, _u32],
+    "brc_comm_set_wait_ms": [_vp, _u32],
+    "brc_comm_destroy": [_vp],
+    "brc_splitkv_exchange_combine": [_vp, _vp, _u32, _vp, _u32, _vp, _vp],
+    "brc_splitkv_attend": [_vp, _u32, _vp, _i32, _vp, _u32, _vp, _u32, _vp, _u32, _u32, _f32, _vp, _vp, _u64, _vp],
     "brc_timing_enable": [_vp, _i32],
     "brc_timing_read": [_vp, _i32, _u32p, C.POINTER(C.c_double)],
 }

@@ -33,6 +33,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--graph", action="store_true", help="replay the step from a CUDA graph instead of launching every call from Python")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="p2p: one kernel stores the partials to the peers and merges; nccl: all-gather + merge kernel")
     a = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -49,7 +51,7 @@ def main():
     n_pages = (n_local + 15) // 16
     pool = KvPool(local, N_LAYERS, N_KV, HD, n_pages + 8)
     table = synth.permutation(100 + rank, n_pages + 8)[:n_pages]
-    split = SplitKvDecode(pool, N_HEAD, table, n_local)
+    split = SplitKvDecode(pool, N_HEAD, table, n_local, exchange=a.exchange)
     gen = torch.Generator(device=dev)
     gen.manual_seed(7 + rank)
     zero = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -113,14 +115,16 @@ def main():
         print(json.dumps({"metric": "splitkv_decode_tok_per_s", "value": 1e3 / ms_step, "unit": "tok/s", "n_gpus": world,
                           "steps": a.steps, "ms_per_step": ms_step, "scaling": "strong", "higher_is_better": True, "cuda_graph": bool(a.graph),
                           "kv_gb_per_s": kv_bytes / (ms_step * 1e-3) / 1e9, "us_per_layer": ms_step * 1e3 / N_LAYERS,
-                          "exchange": "ncclAllGather of 16512 B per rank per layer + brc_decode_combine",
+                          "exchange": ("stores of 16512 B per peer per layer into peer memory + flags + merge, one kernel (brc_splitkv_attend)"
+                                       if a.exchange == "p2p" else "ncclAllGather of 16512 B per rank per layer + brc_decode_combine"),
                           "config": {"workload": f"1 sequence x {a.tokens} cells, 12 layers, GQA 16q/2kv, head_dim 256, "
                                                  f"f16 KV, KV range split over {world} GPU(s)"}}), flush=True)
+    split.close()
     del run, graph   # a captured graph that holds NCCL nodes must go before the communicator does
     torch.cuda.synchronize()
     pool.release()
     if world > 1:
-        if a.graph:
+        if a.graph and a.exchange == "nccl":
             # tearing the communicator down after a capture has been seen to block: leave at once instead
             import sys
             sys.stdout.flush()

@@ -61,6 +61,7 @@ typedef int32_t brc_status;
 typedef struct brc_pool brc_pool;
 typedef struct brc_radix brc_radix;
 typedef struct brc_tier brc_tier;
+typedef struct brc_comm brc_comm;
 
 typedef struct brc_geometry {
     uint32_t n_layers;
@@ -244,6 +245,49 @@ BRC_API brc_status brc_paged_decode_attn_static(brc_pool *pool, uint32_t layer, 
                                                 const uint32_t *block_tables_dev, uint32_t table_stride,
                                                 const uint32_t *seq_lens_dev, uint32_t n_seqs, uint32_t max_seq_len,
                                                 float scale, float *out_dev, void *stream);
+
+/* ---------------------------------------------------------------- split-KV across GPUs
+ * One long sequence whose cells are split into contiguous, page-aligned ranges
+ * over the GPUs of one box (rank r holds range r in its own pool).  No
+ * counterpart in the reference, whose split-K partials stay on one device
+ * (crates/breccia-kernels/src/qsa/mod.rs:1491-1521); the merge rule is the one
+ * its reduce shader applies to chunks (qsa_attn_apply_reduce.comp:25-42),
+ * extended by the running max.
+ *
+ * A brc_comm is one rank's end of the exchange: a receive buffer in this rank's
+ * HBM with one slot per source rank (and four banks, so that ranks may be a
+ * call apart), plus release flags.  Peers map it either through CUDA IPC (one
+ * process per GPU: pass the 64-byte handles of all ranks, in rank order, to
+ * brc_comm_connect_ipc; how they travel between processes is the caller's
+ * business) or directly (one process driving several GPUs:
+ * brc_comm_connect_local with the handles of all ranks).
+ *
+ * brc_splitkv_attend = the local split-KV kernel (brc_decode_partial into the
+ * comm's own buffer) + ONE kernel that stores the 16 512-byte-per-sequence
+ * partial into every peer's slot with ordinary global stores over NVLink,
+ * releases a flag per peer, waits for the peers' flags (time limit, default 1 s:
+ * on expiry the output is left untouched and brc_pool_check reports
+ * BRC_ERR_TIMEOUT) and merges.  Every rank computes the same output.  All ranks
+ * must make the same sequence of calls.  No load ever targets peer memory and
+ * nothing is multicast.  brc_splitkv_exchange_combine is the second half alone
+ * (partial_dev NULL = the comm's own buffer). */
+#define BRC_IPC_HANDLE_BYTES 64
+BRC_API brc_status brc_comm_create(brc_pool *pool, uint32_t world, uint32_t rank, uint32_t max_seqs,
+                                   uint32_t n_head, brc_comm **out);
+BRC_API brc_status brc_comm_ipc_handle(brc_comm *comm, void *handle_out64);
+BRC_API brc_status brc_comm_connect_ipc(brc_comm *comm, const void *handles, uint32_t n_handles);
+BRC_API brc_status brc_comm_connect_local(brc_comm *comm, brc_comm *const *comms, uint32_t n_comms);
+BRC_API brc_status brc_comm_set_wait_ms(brc_comm *comm, uint32_t ms);
+BRC_API brc_status brc_comm_destroy(brc_comm *comm);
+BRC_API brc_status brc_splitkv_exchange_combine(brc_comm *comm, const void *partial_dev, uint32_t n_seqs,
+                                                const float *gate_dev, uint32_t gate_head_stride,
+                                                float *out_dev, void *stream);
+BRC_API brc_status brc_splitkv_attend(brc_comm *comm, uint32_t layer, const void *q_dev, int32_t q_dtype,
+                                      const float *gate_dev, uint32_t gate_head_stride,
+                                      const uint32_t *block_tables_dev, uint32_t table_stride,
+                                      const uint32_t *seq_lens_dev, uint32_t n_seqs, uint32_t max_seq_len,
+                                      float scale, float *out_dev, void *workspace_dev,
+                                      uint64_t workspace_bytes, void *stream);
 
 /* ---------------------------------------------------------------- one decode step over layers
  * The composition the reference performs per attention layer in Qsa::forward

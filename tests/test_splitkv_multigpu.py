@@ -21,3 +21,32 @@ def test_split_kv_across_gpus_equals_the_whole(cuda_device, n_tokens):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
     print(r.stdout[-2000:], r.stderr[-2000:])
     assert r.returncode == 0
+
+
+def test_split_kv_machinery_with_one_rank(cuda_device):
+    """World of one: the exchange kernel has no peer to store to or wait for and reduces to the merge."""
+    import numpy as np
+
+    import oracle
+    from breccia_b200 import synth
+    from breccia_b200.qsa import KvPool
+    from breccia_b200.splitkv import SplitKvDecode
+    from helpers import fill_pool_from_host
+
+    n_head, n_kv, hd, n_tokens = 16, 2, 256, 3000
+    n_pages = (n_tokens + 15) // 16
+    pool = KvPool(0, 1, n_kv, hd, n_pages + 4)
+    k, v = fill_pool_from_host(pool, 0, 31)
+    table = synth.permutation(5, n_pages + 4)[:n_pages]
+    q = oracle.to_f16(synth.normal(6, n_head * hd)).reshape(1, n_head, hd)
+    gate = synth.normal(7, n_head * hd).reshape(1, n_head, hd).astype(np.float32)
+    split = SplitKvDecode(pool, n_head, table, n_tokens)
+    out = torch.full((1, n_head, hd), float("nan"), device="cuda")
+    g = torch.from_numpy(gate).cuda()
+    for _ in range(6):
+        split.attend(0, torch.from_numpy(q).cuda().half(), out, gate=g, gate_head_stride=hd)
+    pool.check()
+    want, _ = oracle.decode_batch(k, v, table[None, :], np.array([n_tokens]), q, n_head, n_kv, hd, gate=gate)
+    assert np.abs(out.cpu().numpy() - want).max() <= 2e-3
+    split.close()
+    pool.release()
