@@ -9,7 +9,7 @@ The access pattern (seeded, stated here because the configuration leaves it open
 sequences; the window at step t is what step t wants to decode.  In every step
   * the sequences of the window whose pages are all in HBM decode one token (brc_decode_step: append +
     attention in all 12 layers) on the main stream, after a fence on the tier's copies issued so far;
-  * meanwhile, on the tier's side stream, 10 % of the not-resident pages that the NEXT step's window
+  * meanwhile, on the tier's two side streams (one per direction), 10 % of the not-resident pages that the NEXT step's window
     needs are promoted (in window order, so sequences complete one after another), and as many pages
     are demoted first to make room: least-recently-decoded sequences outside both windows give up
     pages from their tail.
@@ -40,22 +40,39 @@ def u32p(a: np.ndarray):
     return a.ctypes.data_as(U32P)
 
 
-def pcie_peak(nbytes: int = 512 << 20) -> tuple[float, float]:
-    """Pinned cudaMemcpyAsync rate, host->device and device->host, GB/s (best of 3)."""
-    host = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
-    dev = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
-    rates = []
-    for src, dst in ((host, dev), (dev, host)):
-        best = 0.0
+def pcie_peak(nbytes: int = 512 << 20) -> dict:
+    """Pinned cudaMemcpyAsync rates in GB/s (best of 4): each direction alone, and both at once on two
+    streams (what a link that carries promotions and demotions together can give per direction)."""
+    host_in, host_out = torch.empty(nbytes, dtype=torch.uint8).pin_memory(), torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    dev_in, dev_out = torch.empty(nbytes, dtype=torch.uint8, device="cuda"), torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def run(do_in: bool, do_out: bool) -> tuple[float, float]:
+        best_in = best_out = 0.0
         for _ in range(4):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            dst.copy_(src, non_blocking=True)
-            e1.record()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
             torch.cuda.synchronize()
-            best = max(best, nbytes / (e0.elapsed_time(e1) * 1e-3) / 1e9)
-        rates.append(best)
-    return rates[0], rates[1]
+            if do_in:
+                with torch.cuda.stream(s_in):
+                    ev[0].record()
+                    dev_in.copy_(host_in, non_blocking=True)
+                    ev[1].record()
+            if do_out:
+                with torch.cuda.stream(s_out):
+                    ev[2].record()
+                    host_out.copy_(dev_out, non_blocking=True)
+                    ev[3].record()
+            torch.cuda.synchronize()
+            if do_in:
+                best_in = max(best_in, nbytes / (ev[0].elapsed_time(ev[1]) * 1e-3) / 1e9)
+            if do_out:
+                best_out = max(best_out, nbytes / (ev[2].elapsed_time(ev[3]) * 1e-3) / 1e9)
+        return best_in, best_out
+
+    h2d, _ = run(True, False)
+    _, d2h = run(False, True)
+    h2d_both, d2h_both = run(True, True)
+    return {"h2d": h2d, "d2h": d2h, "h2d_while_d2h": h2d_both, "d2h_while_h2d": d2h_both}
 
 
 def main():
@@ -105,7 +122,7 @@ def main():
             loc[s] = -(slots.astype(np.int64) + 1)
     _lib.call("brc_tier_sync", tier)
     last_decoded = np.full(n, -1, np.int64)
-    h2d_peak, d2h_peak = pcie_peak()
+    peaks = pcie_peak()
 
     dev = "cuda:0"
     gen = torch.Generator(device=dev)
@@ -202,8 +219,11 @@ def main():
         "decoded_sequences_per_step": decoded_tokens / a.steps,
         "h2d_gb_per_s": promoted * slot_bytes / sec / 1e9, "d2h_gb_per_s": demoted * slot_bytes / sec / 1e9,
         "pages_promoted_per_step": promoted / a.steps, "pages_demoted_per_step": demoted / a.steps,
-        "pinned_copy_peak_gb_per_s": {"h2d": h2d_peak, "d2h": d2h_peak},
-        "paging_frac_of_copy_peak": (promoted + demoted) * slot_bytes / sec / 1e9 / max(h2d_peak, d2h_peak),
+        "pinned_copy_peak_gb_per_s": peaks,
+        "h2d_frac_of_copy_peak": promoted * slot_bytes / sec / 1e9 / peaks["h2d"],
+        "d2h_frac_of_copy_peak": demoted * slot_bytes / sec / 1e9 / peaks["d2h"],
+        "h2d_frac_of_two_way_peak": promoted * slot_bytes / sec / 1e9 / peaks["h2d_while_d2h"],
+        "d2h_frac_of_two_way_peak": demoted * slot_bytes / sec / 1e9 / peaks["d2h_while_h2d"],
         "config": {"workload": f"tiering churn: {n} sequences, context uniform in [{a.min_len}, {a.max_len}], 12 layers, GQA 16q/2kv, "
                                f"head_dim 256, f16 KV; HBM pool {hbm_pages} pages = {a.hbm_frac:.0%} of the {need} needed, "
                                f"{host_pages} pinned host slots of {slot_bytes} B; window {W} sliding by {a.slide} per step, "

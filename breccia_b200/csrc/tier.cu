@@ -10,9 +10,15 @@
 //   * demote packs the pages of a batch (24 separate 16 KiB pieces each at 12 layers) into a staging
 //     buffer in HBM with one kernel, then copies staging -> slots with one cudaMemcpyAsync per run of
 //     neighbouring slots (free slots are handed out lowest first, so a batch is mostly one run), on the
-//     tier's own stream; it releases the HBM pages and hands back the slots;
+//     tier's outbound stream; it releases the HBM pages and hands back the slots;
 //   * promote allocates fresh HBM pages, copies slots -> staging (one copy per run of neighbouring
 //     slots) and scatters staging -> pages with one kernel; the caller patches its block tables;
+//   * promotions run on a second stream with a staging buffer of their own, so the link carries both
+//     directions at once; what orders the two streams is tracked per slot and per page (which batch
+//     last wrote or read it) and enforced with the events of those batches, so a promotion only ever
+//     waits for the demotion that filled its slots and for the pack kernel that emptied its pages;
+//   * free slots are handed out in address order from a moving cursor: a batch lands on neighbouring
+//     slots, and a slot that was just freed is not reused until the cursor comes round again;
 //   * brc_tier_fence makes another stream wait for every copy issued so far.  A freed HBM page may be
 //     handed out again at once by the allocator: whoever writes it must fence first;
 //   * an LRU helper ranks resident pages by the last brc_tier_touch.
@@ -25,17 +31,24 @@
 
 #include "brc_internal.h"
 
+constexpr uint32_t EVENT_RING = 64;     // batches per direction whose completion can still be waited for
+
 struct brc_tier {
     brc_pool *pool = nullptr;
     uint8_t *host = nullptr;        // pinned
     uint32_t host_pages = 0;
     uint64_t slot_bytes = 0;
-    cudaStream_t stream = nullptr;  // side stream of the tier
-    cudaEvent_t event = nullptr;    // recorded after every batch
+    cudaStream_t out_stream = nullptr, in_stream = nullptr;   // demotions / promotions
+    uint8_t *out_staging = nullptr, *in_staging = nullptr;    // HBM, STAGE_PAGES slots each
+    cudaEvent_t packed = nullptr;                             // after the newest pack kernel (pages read out)
+    cudaEvent_t out_done[EVENT_RING] = {}, in_done[EVENT_RING] = {};
+    uint64_t out_batch = 0, in_batch = 0;                     // batches issued so far (batch b uses ring entry b % EVENT_RING)
     std::mutex mu;
-    std::set<uint32_t> free_slots;  // handed out lowest first: batches land on neighbouring slots
-    uint8_t *staging = nullptr;     // HBM, STAGE_PAGES slots
     std::vector<uint8_t> slot_used;
+    std::vector<uint64_t> slot_written_by;   // demotion batch that last filled the slot
+    std::vector<uint64_t> slot_read_by;      // promotion batch that last emptied it
+    std::vector<uint64_t> page_written_by;   // promotion batch that last filled the HBM page
+    uint32_t free_slot_count = 0, cursor = 0;
     std::vector<uint64_t> last_use;  // per HBM page, 0 = never touched
     uint64_t clock = 0;
     uint64_t demoted_pages = 0, promoted_pages = 0, d2h_bytes = 0, h2d_bytes = 0;
@@ -87,17 +100,32 @@ brc_status brc_tier_create(brc_pool *pool, uint32_t host_pages, brc_tier **out) 
     t->slot_bytes = 2ull * pool->n_layers * pool->half_page_bytes;
     cudaError_t e;
     if ((e = cudaMallocHost(&t->host, (size_t)t->slot_bytes * host_pages)) != cudaSuccess ||
-        (e = cudaMalloc(&t->staging, (size_t)t->slot_bytes * STAGE_PAGES)) != cudaSuccess ||
-        (e = cudaStreamCreateWithFlags(&t->stream, cudaStreamNonBlocking)) != cudaSuccess ||
-        (e = cudaEventCreateWithFlags(&t->event, cudaEventDisableTiming)) != cudaSuccess) {
+        (e = cudaMalloc(&t->out_staging, (size_t)t->slot_bytes * STAGE_PAGES)) != cudaSuccess ||
+        (e = cudaMalloc(&t->in_staging, (size_t)t->slot_bytes * STAGE_PAGES)) != cudaSuccess ||
+        (e = cudaStreamCreateWithFlags(&t->out_stream, cudaStreamNonBlocking)) != cudaSuccess ||
+        (e = cudaStreamCreateWithFlags(&t->in_stream, cudaStreamNonBlocking)) != cudaSuccess ||
+        (e = cudaEventCreateWithFlags(&t->packed, cudaEventDisableTiming)) != cudaSuccess) {
         brc_status rc = brc_fail(BRC_ERR_CUDA, "brc_tier_create: %u pinned slots of %llu bytes: %s", host_pages,
                                  (unsigned long long)t->slot_bytes, cudaGetErrorString(e));
         brc_tier_destroy(t);
         return rc;
     }
-    cudaEventRecord(t->event, t->stream);
-    for (uint32_t i = 0; i < host_pages; ++i) t->free_slots.insert(t->free_slots.end(), i);
+    for (uint32_t i = 0; i < EVENT_RING; ++i) {
+        if ((e = cudaEventCreateWithFlags(&t->out_done[i], cudaEventDisableTiming)) != cudaSuccess ||
+            (e = cudaEventCreateWithFlags(&t->in_done[i], cudaEventDisableTiming)) != cudaSuccess) {
+            brc_status rc = brc_fail(BRC_ERR_CUDA, "brc_tier_create: cudaEventCreate: %s", cudaGetErrorString(e));
+            brc_tier_destroy(t);
+            return rc;
+        }
+    }
+    cudaEventRecord(t->packed, t->out_stream);
+    cudaEventRecord(t->out_done[0], t->out_stream);   // batch 0 = nothing, complete
+    cudaEventRecord(t->in_done[0], t->in_stream);
     t->slot_used.assign(host_pages, 0);
+    t->slot_written_by.assign(host_pages, 0);
+    t->slot_read_by.assign(host_pages, 0);
+    t->page_written_by.assign(pool->n_pages, 0);
+    t->free_slot_count = host_pages;
     t->last_use.assign(pool->n_pages, 0);
     *out = t;
     return BRC_OK;
@@ -106,13 +134,19 @@ brc_status brc_tier_create(brc_pool *pool, uint32_t host_pages, brc_tier **out) 
 brc_status brc_tier_destroy(brc_tier *tier) {
     if (!tier) return BRC_OK;
     brc_device_guard guard(tier->pool->device);
-    if (tier->stream) {
-        cudaStreamSynchronize(tier->stream);
-        cudaStreamDestroy(tier->stream);
+    for (cudaStream_t st : {tier->out_stream, tier->in_stream})
+        if (st) {
+            cudaStreamSynchronize(st);
+            cudaStreamDestroy(st);
+        }
+    if (tier->packed) cudaEventDestroy(tier->packed);
+    for (uint32_t i = 0; i < EVENT_RING; ++i) {
+        if (tier->out_done[i]) cudaEventDestroy(tier->out_done[i]);
+        if (tier->in_done[i]) cudaEventDestroy(tier->in_done[i]);
     }
-    if (tier->event) cudaEventDestroy(tier->event);
     if (tier->host) cudaFreeHost(tier->host);
-    if (tier->staging) cudaFree(tier->staging);
+    if (tier->out_staging) cudaFree(tier->out_staging);
+    if (tier->in_staging) cudaFree(tier->in_staging);
     delete tier;
     return BRC_OK;
 }
@@ -120,14 +154,16 @@ brc_status brc_tier_destroy(brc_tier *tier) {
 // Copies between staging positions [0, n) and the host slots `slots[0..n)` (ascending): one copy per
 // run of neighbouring slots.
 static cudaError_t copy_runs(brc_tier *t, const uint32_t *slots, uint32_t n, bool to_host) {
+    uint8_t *staging = to_host ? t->out_staging : t->in_staging;
+    cudaStream_t st = to_host ? t->out_stream : t->in_stream;
     for (uint32_t i = 0; i < n;) {
         uint32_t j = i + 1;
         while (j < n && slots[j] == slots[j - 1] + 1) ++j;
         uint8_t *h = t->host + (uint64_t)slots[i] * t->slot_bytes;
-        uint8_t *d = t->staging + (uint64_t)i * t->slot_bytes;
+        uint8_t *d = staging + (uint64_t)i * t->slot_bytes;
         const size_t bytes = (size_t)(j - i) * t->slot_bytes;
-        cudaError_t e = to_host ? cudaMemcpyAsync(h, d, bytes, cudaMemcpyDeviceToHost, t->stream)
-                                : cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, t->stream);
+        cudaError_t e = to_host ? cudaMemcpyAsync(h, d, bytes, cudaMemcpyDeviceToHost, st)
+                                : cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, st);
         if (e != cudaSuccess) return e;
         i = j;
     }
@@ -138,11 +174,27 @@ static void launch_pack(brc_tier *t, const PageList &pl, uint32_t n, bool to_sta
     brc_pool *p = t->pool;
     const uint32_t grid = n * 2u * p->n_layers;
     if (to_staging)
-        tier_pack_kernel<true><<<grid, 256, 0, t->stream>>>(p->k_base, p->v_base, t->staging, pl, p->n_layers, p->half_page_bytes,
-                                                            p->layer_bytes);
+        tier_pack_kernel<true><<<grid, 256, 0, t->out_stream>>>(p->k_base, p->v_base, t->out_staging, pl, p->n_layers,
+                                                                p->half_page_bytes, p->layer_bytes);
     else
-        tier_pack_kernel<false><<<grid, 256, 0, t->stream>>>(p->k_base, p->v_base, t->staging, pl, p->n_layers, p->half_page_bytes,
-                                                             p->layer_bytes);
+        tier_pack_kernel<false><<<grid, 256, 0, t->in_stream>>>(p->k_base, p->v_base, t->in_staging, pl, p->n_layers,
+                                                                p->half_page_bytes, p->layer_bytes);
+}
+
+// Make `waiter` wait for batch `dep` of the other direction unless that batch is known to be complete:
+// before ring entry b % EVENT_RING is recorded again for batch b, the host waits for batch b - EVENT_RING.
+static cudaError_t wait_for_batch(cudaStream_t waiter, const cudaEvent_t *ring, uint64_t newest, uint64_t dep) {
+    if (dep == 0 || dep + EVENT_RING <= newest) return cudaSuccess;
+    return cudaStreamWaitEvent(waiter, ring[dep % EVENT_RING], 0);
+}
+
+static cudaError_t record_batch(cudaStream_t st, cudaEvent_t *ring, uint64_t batch) {
+    cudaEvent_t ev = ring[batch % EVENT_RING];
+    if (batch >= EVENT_RING) {
+        cudaError_t e = cudaEventSynchronize(ev);   // batch - EVENT_RING: long done unless the host runs far ahead
+        if (e != cudaSuccess) return e;
+    }
+    return cudaEventRecord(ev, st);
 }
 
 brc_status brc_tier_demote(brc_tier *tier, const uint32_t *page_ids, uint32_t n, uint32_t *out_slots, void *after_stream) {
@@ -151,9 +203,9 @@ brc_status brc_tier_demote(brc_tier *tier, const uint32_t *page_ids, uint32_t n,
     brc_pool *p = tier->pool;
     brc_device_guard guard(p->device);
     std::lock_guard<std::mutex> lock(tier->mu);
-    if (tier->free_slots.size() < n)
-        return brc_fail(BRC_ERR_CAPACITY, "brc_tier_demote: %u pages but %zu of %u host slots are free", n,
-                        tier->free_slots.size(), tier->host_pages);
+    if (tier->free_slot_count < n)
+        return brc_fail(BRC_ERR_CAPACITY, "brc_tier_demote: %u pages but %u of %u host slots are free", n, tier->free_slot_count,
+                        tier->host_pages);
     for (uint32_t i = 0; i < n; ++i) {
         uint32_t rc = 0;
         if (brc_status st = brc_page_refcount(p, page_ids[i], &rc)) return st;
@@ -166,30 +218,49 @@ brc_status brc_tier_demote(brc_tier *tier, const uint32_t *page_ids, uint32_t n,
         cudaEvent_t ev;
         BRC_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
         BRC_CUDA(cudaEventRecord(ev, brc_stream(after_stream)));
-        BRC_CUDA(cudaStreamWaitEvent(tier->stream, ev, 0));
+        BRC_CUDA(cudaStreamWaitEvent(tier->out_stream, ev, 0));
         BRC_CUDA(cudaEventDestroy(ev));
     }
     for (uint32_t i0 = 0; i0 < n; i0 += STAGE_PAGES) {
         const uint32_t m = std::min(STAGE_PAGES, n - i0);
+        const uint64_t batch = tier->out_batch + 1;
         PageList pl;
         uint32_t slots[STAGE_PAGES];
-        auto it = tier->free_slots.begin();
-        for (uint32_t i = 0; i < m; ++i, ++it) {
-            pl.ids[i] = page_ids[i0 + i];
-            slots[i] = *it;   // ascending
+        // the next m free slots from the cursor on, in address order (wrapping once at most)
+        uint32_t c = tier->cursor, found = 0, wrapped_at = m;
+        for (uint32_t scanned = 0; found < m && scanned < tier->host_pages; ++scanned) {
+            if (!tier->slot_used[c]) slots[found++] = c;
+            if (++c == tier->host_pages) {
+                c = 0;
+                if (found < m && wrapped_at == m) wrapped_at = found;
+            }
         }
-        launch_pack(tier, pl, m, true);
-        cudaError_t e = cudaGetLastError();
-        if (e == cudaSuccess) e = copy_runs(tier, slots, m, true);
-        if (e != cudaSuccess) return brc_fail(BRC_ERR_CUDA, "brc_tier_demote: copy of %u pages failed: %s", m, cudaGetErrorString(e));
+        tier->cursor = c;
+        if (wrapped_at < m) std::rotate(slots, slots + wrapped_at, slots + m);   // ascending again
+        uint64_t dep_read = 0, dep_write = 0;
         for (uint32_t i = 0; i < m; ++i) {
-            tier->free_slots.erase(slots[i]);
+            pl.ids[i] = page_ids[i0 + i];
+            dep_read = std::max(dep_read, tier->slot_read_by[slots[i]]);           // a promotion still reading the slot
+            dep_write = std::max(dep_write, tier->page_written_by[pl.ids[i]]);     // a promotion still filling the page
+        }
+        cudaError_t e = wait_for_batch(tier->out_stream, tier->in_done, tier->in_batch, std::max(dep_read, dep_write));
+        if (e == cudaSuccess) {
+            launch_pack(tier, pl, m, true);
+            e = cudaGetLastError();
+        }
+        if (e == cudaSuccess) e = cudaEventRecord(tier->packed, tier->out_stream);
+        if (e == cudaSuccess) e = copy_runs(tier, slots, m, true);
+        if (e == cudaSuccess) e = record_batch(tier->out_stream, tier->out_done, batch);
+        if (e != cudaSuccess) return brc_fail(BRC_ERR_CUDA, "brc_tier_demote: copy of %u pages failed: %s", m, cudaGetErrorString(e));
+        tier->out_batch = batch;
+        for (uint32_t i = 0; i < m; ++i) {
             tier->slot_used[slots[i]] = 1;
+            tier->slot_written_by[slots[i]] = batch;
             out_slots[i0 + i] = slots[i];
             tier->last_use[page_ids[i0 + i]] = 0;
         }
+        tier->free_slot_count -= m;
     }
-    BRC_CUDA(cudaEventRecord(tier->event, tier->stream));
     tier->demoted_pages += n;
     tier->d2h_bytes += (uint64_t)n * tier->slot_bytes;
     // the HBM pages go back to the allocator; their next writer must brc_tier_fence first
@@ -215,28 +286,37 @@ brc_status brc_tier_promote(brc_tier *tier, const uint32_t *slots, uint32_t n, u
     }
     for (uint32_t i0 = 0; i0 < n; i0 += STAGE_PAGES) {
         const uint32_t m = std::min(STAGE_PAGES, n - i0);
+        const uint64_t batch = tier->in_batch + 1;
         // staging order = ascending slot order, so that neighbouring slots arrive with one copy
         uint32_t order[STAGE_PAGES], sorted[STAGE_PAGES];
         for (uint32_t i = 0; i < m; ++i) order[i] = i0 + i;
         std::sort(order, order + m, [&](uint32_t a, uint32_t b) { return slots[a] < slots[b]; });
         PageList pl;
+        uint64_t dep = 0;
         for (uint32_t i = 0; i < m; ++i) {
             sorted[i] = slots[order[i]];
             pl.ids[i] = out_page_ids[order[i]];
+            dep = std::max(dep, tier->slot_written_by[sorted[i]]);   // the demotion that filled the slot
         }
-        cudaError_t e = copy_runs(tier, sorted, m, false);
+        cudaError_t e = wait_for_batch(tier->in_stream, tier->out_done, tier->out_batch, dep);
+        // the pages may have been freed by a demotion whose pack kernel has yet to read them
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(tier->in_stream, tier->packed, 0);
+        if (e == cudaSuccess) e = copy_runs(tier, sorted, m, false);
         if (e == cudaSuccess) {
             launch_pack(tier, pl, m, false);
             e = cudaGetLastError();
         }
+        if (e == cudaSuccess) e = record_batch(tier->in_stream, tier->in_done, batch);
         if (e != cudaSuccess) return brc_fail(BRC_ERR_CUDA, "brc_tier_promote: copy of %u slots failed: %s", m, cudaGetErrorString(e));
+        tier->in_batch = batch;
         for (uint32_t i = 0; i < m; ++i) {
             tier->slot_used[sorted[i]] = 0;
-            tier->free_slots.insert(sorted[i]);
+            tier->slot_read_by[sorted[i]] = batch;
+            tier->page_written_by[pl.ids[i]] = batch;
             tier->last_use[pl.ids[i]] = ++tier->clock;
         }
+        tier->free_slot_count += m;
     }
-    BRC_CUDA(cudaEventRecord(tier->event, tier->stream));
     tier->promoted_pages += n;
     tier->h2d_bytes += (uint64_t)n * tier->slot_bytes;
     return BRC_OK;
@@ -246,14 +326,16 @@ brc_status brc_tier_fence(brc_tier *tier, void *stream) {
     if (!tier) return brc_fail(BRC_ERR_INVALID, "brc_tier_fence: tier is NULL");
     brc_device_guard guard(tier->pool->device);
     std::lock_guard<std::mutex> lock(tier->mu);
-    BRC_CUDA(cudaStreamWaitEvent(brc_stream(stream), tier->event, 0));
+    BRC_CUDA(cudaStreamWaitEvent(brc_stream(stream), tier->out_done[tier->out_batch % EVENT_RING], 0));
+    BRC_CUDA(cudaStreamWaitEvent(brc_stream(stream), tier->in_done[tier->in_batch % EVENT_RING], 0));
     return BRC_OK;
 }
 
 brc_status brc_tier_sync(brc_tier *tier) {
     if (!tier) return brc_fail(BRC_ERR_INVALID, "brc_tier_sync: tier is NULL");
     brc_device_guard guard(tier->pool->device);
-    BRC_CUDA(cudaStreamSynchronize(tier->stream));
+    BRC_CUDA(cudaStreamSynchronize(tier->out_stream));
+    BRC_CUDA(cudaStreamSynchronize(tier->in_stream));
     return BRC_OK;
 }
 
@@ -295,7 +377,7 @@ brc_status brc_tier_stats(brc_tier *tier, uint64_t *out_demoted_pages, uint64_t 
     if (out_promoted_pages) *out_promoted_pages = tier->promoted_pages;
     if (out_d2h_bytes) *out_d2h_bytes = tier->d2h_bytes;
     if (out_h2d_bytes) *out_h2d_bytes = tier->h2d_bytes;
-    if (out_free_slots) *out_free_slots = (uint32_t)tier->free_slots.size();
+    if (out_free_slots) *out_free_slots = tier->free_slot_count;
     return BRC_OK;
 }
 
