@@ -15,8 +15,10 @@
 //   O[128 x 256] += P[128 x 64] . V        tcgen05.mma M=128 N=256, 4 steps of K=16, V read MN-major
 // Q, K, V and P sit in shared memory in the canonical 128-byte-swizzled layouts the matrix descriptors
 // name.  K/V pages are gathered through the block table by four loader warps with 16-byte cp.async
-// (a 16-cell page is too small a TMA box: ~215 cycles per operation whatever its size), two stages in
-// flight; cells at or past the end of the cache are zero-filled.  O stays in TMEM across blocks and is
+// (a 16-cell page is too small a TMA box: ~215 cycles per operation whatever its size), K and V in
+// separate two-deep rings; cells at or past the end of the cache are zero-filled.  S and P are double
+// buffered: the MMA thread issues S of block j + 1 before P.V of block j, so the tensor pipe computes
+// the next scores while the softmax warps work on the current ones.  O stays in TMEM across blocks and is
 // rescaled only when a row's maximum grew by more than 2^8 since the scale in use (rare after the
 // first blocks), so P may exceed 1 by at most that factor — harmless in binary16 with fp32 sums.
 // Every wait is bounded; TMEM is released on every path.
@@ -43,9 +45,9 @@ constexpr uint32_t PF_KV_SLAB = PF_BLK * 128;             // [64 cells][128 B]
 constexpr uint32_t PF_K_BYTES = 4 * PF_KV_SLAB;           // 32 KiB
 constexpr uint32_t PF_STAGE_BYTES = 2 * PF_K_BYTES;       // K then V
 constexpr uint32_t PF_P_BYTES = PF_ROWS * 128;            // [128 rows][64 cells] f16
-constexpr uint32_t PF_SMEM = 1024 + PF_Q_BYTES + PF_P_BYTES + PF_STAGES * PF_STAGE_BYTES + 1024;
+constexpr uint32_t PF_SMEM = 1024 + PF_Q_BYTES + 2 * PF_P_BYTES + PF_STAGES * PF_STAGE_BYTES + 1024;
 constexpr uint32_t PF_TMEM_COLS = 512;
-constexpr uint32_t PF_S_COL = 0, PF_O_COL = 64;
+constexpr uint32_t PF_S0_COL = 0, PF_O_COL = 64, PF_S1_COL = 320;   // two S buffers of 64 columns around O
 constexpr uint64_t PF_WAIT_NS = 1000000000ull;
 constexpr float PF_RESCALE_THRESHOLD = 8.0f;              // log2 units
 
@@ -145,6 +147,17 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
+    float a[32], b[32];
+    tmem_ld32(taddr, a);
+    tmem_ld32(taddr + 32, b);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        v[i] = a[i];
+        v[32 + i] = b[i];
+    }
+}
+
 // 16-byte async copy; src_bytes = 0 writes zeros.
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -163,16 +176,19 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
     extern __shared__ uint8_t pf_smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023u) & ~uintptr_t(1023));
     uint8_t *q_sm = smem;
-    uint8_t *p_sm = q_sm + PF_Q_BYTES;
-    uint8_t *st_sm = p_sm + PF_P_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(st_sm + PF_STAGES * PF_STAGE_BYTES);
-    const uint32_t bar_full = brc::smem_u32(bars);            // [PF_STAGES]
-    const uint32_t bar_empty = bar_full + 8u * PF_STAGES;      // [PF_STAGES]
-    const uint32_t bar_q = bar_empty + 8u * PF_STAGES;
-    const uint32_t bar_s = bar_q + 8u;
-    const uint32_t bar_p = bar_s + 8u;
-    const uint32_t bar_o = bar_p + 8u;
-    volatile uint32_t *misc = reinterpret_cast<volatile uint32_t *>(bars + 16);   // [0] tmem base, [1] dead
+    uint8_t *p_sm = q_sm + PF_Q_BYTES;                       // [2][128 rows][128 B]
+    uint8_t *k_sm0 = p_sm + 2 * PF_P_BYTES;                  // [PF_STAGES][32 KiB]
+    uint8_t *v_sm0 = k_sm0 + PF_STAGES * PF_K_BYTES;         // [PF_STAGES][32 KiB]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(v_sm0 + PF_STAGES * PF_K_BYTES);
+    const uint32_t bar_kfull = brc::smem_u32(bars);          // [2] loaders -> MMA
+    const uint32_t bar_vfull = bar_kfull + 16u;              // [2]
+    const uint32_t bar_kempty = bar_vfull + 16u;             // [2] S MMAs of the stage retired
+    const uint32_t bar_vempty = bar_kempty + 16u;            // [2] P.V MMAs of the stage retired
+    const uint32_t bar_s = bar_vempty + 16u;                 // [2] S buffer written
+    const uint32_t bar_p = bar_s + 16u;                      // [2] P buffer written, S buffer read
+    const uint32_t bar_o = bar_p + 16u;                      // [2] P.V of the block retired
+    const uint32_t bar_q = bar_o + 16u;
+    volatile uint32_t *misc = reinterpret_cast<volatile uint32_t *>(bars + 24);   // [0] tmem base, [1] dead
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t kvh = blockIdx.x % p.n_kv_head;
@@ -190,14 +206,16 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
     const uint32_t n_blk = (cells_needed + PF_BLK - 1) / PF_BLK;
 
     if (tid == 0) {
-        for (int i = 0; i < PF_STAGES; ++i) {
-            brc::mbar_init(bar_full + 8u * i, PF_LOAD_WARPS * 32);
-            brc::mbar_init(bar_empty + 8u * i, 1);
+        for (uint32_t i = 0; i < 2; ++i) {
+            brc::mbar_init(bar_kfull + 8u * i, PF_LOAD_WARPS * 32);
+            brc::mbar_init(bar_vfull + 8u * i, PF_LOAD_WARPS * 32);
+            brc::mbar_init(bar_kempty + 8u * i, 1);
+            brc::mbar_init(bar_vempty + 8u * i, 1);
+            brc::mbar_init(bar_s + 8u * i, 1);
+            brc::mbar_init(bar_p + 8u * i, PF_SOFTMAX_WARPS * 32);
+            brc::mbar_init(bar_o + 8u * i, 1);
         }
         brc::mbar_init(bar_q, PF_LOAD_WARPS * 32);
-        brc::mbar_init(bar_s, 1);
-        brc::mbar_init(bar_p, PF_SOFTMAX_WARPS * 32);
-        brc::mbar_init(bar_o, 1);
         brc::mbar_fence_init();
         misc[1] = 0u;
     }
@@ -239,83 +257,117 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
         brc::fence_proxy_async_smem();
         brc::mbar_arrive(bar_q);
 
+        // K and V of a block travel as two cp.async groups, K first, each into its own two-deep ring: K
+        // of block j is published as soon as the next group has been issued behind it, and its stage is
+        // free again when the S MMAs of block j retire, long before the block's V stage is.
+        // Thread -> (row r0 + 4 i, 16-byte chunk ch) of the [64 cells][512 B] tile, i < 16; the rows of a
+        // thread walk through the block's 4 pages, 4 rows per page.
         const uint32_t *table = p.block_tables + (uint64_t)s * p.table_stride;
-        for (uint32_t j = 0; j < n_blk && !misc[1]; ++j) {
-            const uint32_t stg = j % PF_STAGES;
-            if (!pf_wait(bar_empty + 8u * stg, ((j / PF_STAGES) & 1u) ^ 1u)) {
-                misc[1] = 1u;
-                if (lt == 0) { atomicOr(p.status, BRC_DEV_WAIT_LIMIT); p.status[1] = 3000000u + blockIdx.x; }
-                break;
-            }
-            const uint32_t k_dst = brc::smem_u32(st_sm) + stg * PF_STAGE_BYTES, v_dst = k_dst + PF_K_BYTES;
-            for (uint32_t c = lt; c < PF_BLK * 32; c += PF_LOAD_WARPS * 32) {
-                const uint32_t r = c >> 5, ch = c & 31u;
-                const uint32_t cell = j * PF_BLK + r;
-                const bool live = cell < kv_len;   // past the end of the cache: zeros (and no table read)
-                uint32_t page = 0;
-                if (live) {
-                    page = __ldg(table + (cell >> 4));
-                    if (page >= p.n_pages) {
+        const uint32_t ch = lt & 31u, r0 = lt >> 5;
+        uint32_t pending_bar = 0;   // barrier of the newest group but one (0 = none)
+        bool dead = false;
+        for (uint32_t j = 0; j < n_blk && !dead; ++j) {
+            const uint32_t stg = j & 1u, par = ((j >> 1) & 1u) ^ 1u;
+            uint32_t page[4];
+#pragma unroll
+            for (uint32_t g = 0; g < 4; ++g) {
+                const uint32_t cell = j * PF_BLK + g * 16u;
+                page[g] = 0;
+                if (cell < kv_len) {
+                    page[g] = __ldg(table + (cell >> 4));
+                    if (page[g] >= p.n_pages) {
                         atomicOr(p.status, BRC_DEV_BAD_PAGE);
-                        p.status[1] = page;
-                        page = 0;
+                        p.status[1] = page[g];
+                        page[g] = 0;
                     }
                 }
-                const uint64_t src = (((uint64_t)page * p.n_kv_head + kvh) * 16u + (cell & 15u)) * (PF_HD * 2u) + ch * 16u;
-                const uint32_t off = (ch >> 3) * PF_KV_SLAB + r * 128u + (((ch & 7u) ^ (r & 7u)) << 4);
-                cp_async16(k_dst + off, p.k_layer + src, live ? 16u : 0u);
-                cp_async16(v_dst + off, p.v_layer + src, live ? 16u : 0u);
             }
-            cp_async_commit();
-            if (j > 0) {   // the block before this one has landed: publish it
-                cp_async_wait<1>();
-                brc::fence_proxy_async_smem();
-                brc::mbar_arrive(bar_full + 8u * ((j - 1) % PF_STAGES));
+#pragma unroll
+            for (uint32_t kv = 0; kv < 2; ++kv) {
+                if (!pf_wait((kv ? bar_vempty : bar_kempty) + 8u * stg, par) || misc[1]) {
+                    dead = true;
+                    break;
+                }
+                const uint32_t dst0 = brc::smem_u32(kv ? v_sm0 : k_sm0) + stg * PF_K_BYTES;
+                const uint8_t *base = kv ? p.v_layer : p.k_layer;
+#pragma unroll
+                for (uint32_t i = 0; i < 16; ++i) {
+                    const uint32_t r = r0 + 4u * i;
+                    const uint32_t cell = j * PF_BLK + r;
+                    const bool live = cell < kv_len;   // past the end of the cache: zeros
+                    const uint64_t src = (((uint64_t)page[i >> 2] * p.n_kv_head + kvh) * 16u + (r & 15u)) * (PF_HD * 2u) + ch * 16u;
+                    const uint32_t off = (ch >> 3) * PF_KV_SLAB + r * 128u + (((ch & 7u) ^ (r & 7u)) << 4);
+                    cp_async16(dst0 + off, base + src, live ? 16u : 0u);
+                }
+                cp_async_commit();
+                if (pending_bar) {   // the group before this one has landed: publish it
+                    cp_async_wait<1>();
+                    brc::fence_proxy_async_smem();
+                    brc::mbar_arrive(pending_bar);
+                }
+                pending_bar = (kv ? bar_vfull : bar_kfull) + 8u * stg;
             }
         }
         cp_async_wait<0>();
         brc::fence_proxy_async_smem();
-        if (n_blk > 0 && !misc[1]) brc::mbar_arrive(bar_full + 8u * ((n_blk - 1) % PF_STAGES));
+        if (dead) {
+            if (!misc[1] && lt == 0) { atomicOr(p.status, BRC_DEV_WAIT_LIMIT); p.status[1] = 3000000u + blockIdx.x; }
+            misc[1] = 1u;
+        } else if (pending_bar) {
+            brc::mbar_arrive(pending_bar);
+        }
     } else if (warp == PF_MMA_WARP) {
         // ------------------------------------------------------------------ MMA issue (one thread)
+        // S of block j + 1 is issued before P.V of block j: the tensor pipe works on the next scores while
+        // the softmax warps turn the current ones into P, and on P.V while they read the next scores.
         if (lane == 0) {
             const uint32_t idesc_s = umma_idesc(PF_BLK, false);
             const uint32_t idesc_o = umma_idesc(PF_HD, true);
             bool ok = pf_wait(bar_q, 0);
             brc::fence_proxy_async_smem();
-            for (uint32_t j = 0; j < n_blk && ok && !misc[1]; ++j) {
-                const uint32_t stg = j % PF_STAGES;
-                const uint32_t k_sm = brc::smem_u32(st_sm) + stg * PF_STAGE_BYTES, v_sm = k_sm + PF_K_BYTES;
-                ok = pf_wait(bar_full + 8u * stg, (j / PF_STAGES) & 1u);
-                if (!ok) break;
-                brc::fence_proxy_async_smem();
+            auto issue_s = [&](uint32_t j) -> bool {
+                const uint32_t stg = j & 1u;
+                if (!pf_wait(bar_kfull + 8u * stg, (j >> 1) & 1u)) return false;
                 tc_fence_after();
+                const uint32_t k_sm = brc::smem_u32(k_sm0) + stg * PF_K_BYTES;
                 // S = Q . K^T: 16 steps of K = 16 (32 bytes inside a 128-byte swizzled row; 4 steps per slab)
 #pragma unroll
                 for (uint32_t ks = 0; ks < PF_HD / 16; ++ks) {
                     const uint64_t a = umma_desc(brc::smem_u32(q_sm) + (ks >> 2) * PF_Q_SLAB + (ks & 3u) * 32u, 16, 1024);
                     const uint64_t b = umma_desc(k_sm + (ks >> 2) * PF_KV_SLAB + (ks & 3u) * 32u, 16, 1024);
-                    umma_f16(tmem + PF_S_COL, a, b, idesc_s, ks > 0);
+                    umma_f16(tmem + (stg ? PF_S1_COL : PF_S0_COL), a, b, idesc_s, ks > 0);
                 }
-                umma_commit(bar_s);
-                ok = pf_wait(bar_p, j & 1u);
+                umma_commit(bar_s + 8u * stg);
+                umma_commit(bar_kempty + 8u * stg);
+                return true;
+            };
+            if (ok && n_blk > 0) ok = issue_s(0);
+            for (uint32_t j = 0; j < n_blk && ok && !misc[1]; ++j) {
+                const uint32_t stg = j & 1u, par = (j >> 1) & 1u;
+                // The S buffer of block j + 1 was last read by the softmax of block j - 1, whose bar_p this
+                // thread waited for before issuing P.V of block j - 1.
+                if (j + 1 < n_blk) {
+                    ok = issue_s(j + 1);
+                    if (!ok) break;
+                }
+                ok = pf_wait(bar_p + 8u * stg, par) && pf_wait(bar_vfull + 8u * stg, par);
                 if (!ok) break;
                 tc_fence_after();
+                const uint32_t v_sm = brc::smem_u32(v_sm0) + stg * PF_K_BYTES;
                 // O += P . V: 4 steps of K = 16 cells; V is MN-major: 16 cells = 2048 bytes down a slab,
                 // the four 64-column slabs are 8 KiB apart (leading offset), 8-cell groups 1 KiB apart
 #pragma unroll
                 for (uint32_t ks = 0; ks < PF_BLK / 16; ++ks) {
-                    const uint64_t a = umma_desc(brc::smem_u32(p_sm) + ks * 32u, 16, 1024);
+                    const uint64_t a = umma_desc(brc::smem_u32(p_sm) + stg * PF_P_BYTES + ks * 32u, 16, 1024);
                     const uint64_t b = umma_desc(v_sm + ks * 2048u, PF_KV_SLAB, 1024);
                     umma_f16(tmem + PF_O_COL, a, b, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
                 }
-                umma_commit(bar_o);
-                umma_commit(bar_empty + 8u * stg);
+                umma_commit(bar_o + 8u * stg);
+                umma_commit(bar_vempty + 8u * stg);
             }
             if (!ok) {
+                if (!misc[1]) { atomicOr(p.status, BRC_DEV_WAIT_LIMIT); p.status[1] = 4000000u + blockIdx.x; }
                 misc[1] = 1u;
-                atomicOr(p.status, BRC_DEV_WAIT_LIMIT);
-                p.status[1] = 4000000u + blockIdx.x;
             }
         }
     } else {
@@ -324,24 +376,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
         const uint32_t tl = row >> 3, h = row & 7u;
         const uint32_t limit = pos0 + t0 + tl;          // last cell this row sees
         const uint32_t lane_base = (warp * 32u) << 16;  // this warp's TMEM lane quarter
-        float m_used = -INFINITY, l = 0.f;
+        float m_used = -INFINITY, l = 0.f;              // m_used in units of scale_log2 * score
         bool ok = true;
         for (uint32_t j = 0; j < n_blk; ++j) {
+            const uint32_t stg = j & 1u, par = (j >> 1) & 1u;
             // warp-uniform control flow: the TMEM accesses below are warp-wide
-            if (__any_sync(0xffffffffu, misc[1] != 0u)) break;
-            ok = __all_sync(0xffffffffu, pf_wait(bar_s, j & 1u));
+            if (__any_sync(0xffffffffu, misc[1] != 0u)) { ok = true; break; }
+            ok = __all_sync(0xffffffffu, pf_wait(bar_s + 8u * stg, par));
             if (!ok) break;
             tc_fence_after();
             float sc[PF_BLK];
-            {
-                float v[32];
-                tmem_ld32(tmem + lane_base + PF_S_COL, v);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) sc[i] = v[i] * p.scale_log2;
-                tmem_ld32(tmem + lane_base + PF_S_COL + 32, v);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) sc[32 + i] = v[i] * p.scale_log2;
-            }
+            tmem_ld64(tmem + lane_base + (stg ? PF_S1_COL : PF_S0_COL), sc);
             const uint32_t c0 = j * PF_BLK;
             float mx = -INFINITY;
             if (c0 + PF_BLK - 1 > limit) {
@@ -354,12 +399,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
 #pragma unroll
                 for (int i = 0; i < PF_BLK; ++i) mx = fmaxf(mx, sc[i]);
             }
-            // P overwrites the previous block's P and O may be rescaled: both need the previous P.V done
-            if (j > 0) {
-                ok = __all_sync(0xffffffffu, pf_wait(bar_o, (j - 1) & 1u));
-                if (!ok) break;
-                tc_fence_after();
-            }
+            mx *= p.scale_log2;   // the scale is positive: max commutes with it
             // Raise the scale in use when this row's maximum grew a lot (or at its first live block):
             // O *= 2^(old - new).  TMEM loads and stores are warp-wide, so the warp goes through the
             // rescale together and rows that need none multiply by one.
@@ -371,6 +411,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
                 m_used = mx;
             }
             if (j > 0 && __any_sync(0xffffffffu, f != 1.f)) {
+                // O is about to change: P.V of the block before this one must have retired
+                ok = __all_sync(0xffffffffu, pf_wait(bar_o + 8u * ((j - 1) & 1u), ((j - 1) >> 1) & 1u));
+                if (!ok) break;
+                tc_fence_after();
 #pragma unroll 1
                 for (int cg = 0; cg < PF_HD / 32; ++cg) {
                     float v[32];
@@ -380,28 +424,34 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
                     tmem_st32(tmem + lane_base + PF_O_COL + cg * 32, v);
                 }
             }
+            // This block's P buffer was last read by P.V of block j - 2
+            if (j >= 2) {
+                ok = __all_sync(0xffffffffu, pf_wait(bar_o + 8u * stg, (par ^ 1u)));
+                if (!ok) break;
+            }
             // P row (binary16) into its swizzled shared-memory row: 8 chunks of 8 cells
-            const uint32_t prow = brc::smem_u32(p_sm) + row * 128u;
+            const uint32_t prow = brc::smem_u32(p_sm) + stg * PF_P_BYTES + row * 128u;
+            const float neg_m = m_used == -INFINITY ? 0.f : -m_used;   // a row with no live cell yet has only -inf scores
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
+            for (int c8 = 0; c8 < 8; ++c8) {
                 uint32_t w[4];
 #pragma unroll
                 for (int k2 = 0; k2 < 4; ++k2) {
-                    const float a = m_used == -INFINITY ? 0.f : brc::fast_exp2(sc[ch * 8 + k2 * 2] - m_used);
-                    const float b = m_used == -INFINITY ? 0.f : brc::fast_exp2(sc[ch * 8 + k2 * 2 + 1] - m_used);
+                    const float a = brc::fast_exp2(fmaf(sc[c8 * 8 + k2 * 2], p.scale_log2, neg_m));
+                    const float b = brc::fast_exp2(fmaf(sc[c8 * 8 + k2 * 2 + 1], p.scale_log2, neg_m));
                     l += a + b;
                     w[k2] = brc::pack_half2(a, b);
                 }
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(prow + ((ch ^ (row & 7u)) << 4)), "r"(w[0]), "r"(w[1]),
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(prow + ((c8 ^ (row & 7u)) << 4)), "r"(w[0]), "r"(w[1]),
                              "r"(w[2]), "r"(w[3])
                              : "memory");
             }
             brc::fence_proxy_async_smem();
             tc_fence_before();
-            brc::mbar_arrive(bar_p);
+            brc::mbar_arrive(bar_p + 8u * stg);
         }
         if (ok && n_blk > 0 && !__any_sync(0xffffffffu, misc[1] != 0u)) {
-            ok = __all_sync(0xffffffffu, pf_wait(bar_o, (n_blk - 1) & 1u));
+            ok = __all_sync(0xffffffffu, pf_wait(bar_o + 8u * ((n_blk - 1) & 1u), ((n_blk - 1) >> 1) & 1u));
             if (ok) {
                 tc_fence_after();
                 const bool live = tl < n_tok && h < p.group;
@@ -429,8 +479,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
             }
         }
         if (!ok) {
+            if (!misc[1] && lane == 0) { atomicOr(p.status, BRC_DEV_WAIT_LIMIT); p.status[1] = 5000000u + blockIdx.x; }
             misc[1] = 1u;
-            if (lane == 0) { atomicOr(p.status, BRC_DEV_WAIT_LIMIT); p.status[1] = 5000000u + blockIdx.x; }
         }
     }
     // everyone is done with TMEM (or has given up): release it

@@ -50,3 +50,35 @@ def test_split_kv_machinery_with_one_rank(cuda_device):
     assert np.abs(out.cpu().numpy() - want).max() <= 2e-3
     split.close()
     pool.release()
+
+
+def test_a_peer_that_never_arrives_times_out_and_leaves_the_context_usable(cuda_device):
+    """Rank 0 of a world of two exchanges alone (rank 1's end exists but never calls): the wait for its
+    flag runs out after 20 ms, the output stays as it was, the pool reports BRC_ERR_TIMEOUT, and the next
+    call on the same context works."""
+    import ctypes as C
+
+    from breccia_b200 import _lib
+    from breccia_b200.qsa import KvPool, decode_partial_bytes
+
+    n_head, hd = 16, 256
+    pool = KvPool(0, 1, 2, hd, 8)
+    comms = [C.c_void_p(), C.c_void_p()]
+    for r in range(2):
+        _lib.call("brc_comm_create", pool.handle, 2, r, 1, n_head, C.byref(comms[r]))
+    arr = (C.c_void_p * 2)(comms[0], comms[1])
+    for r in range(2):
+        _lib.call("brc_comm_connect_local", comms[r], arr, 2)
+    _lib.call("brc_comm_set_wait_ms", comms[0], 20)
+    part = torch.zeros(decode_partial_bytes(1, n_head, hd), dtype=torch.uint8, device="cuda")
+    out = torch.full((1, n_head, hd), 7.0, device="cuda")
+    _lib.call("brc_splitkv_exchange_combine", comms[0], C.c_void_p(part.data_ptr()), 1, None, 0, C.c_void_p(out.data_ptr()), None)
+    torch.cuda.synchronize()
+    with pytest.raises(_lib.BrcError, match="wait"):
+        pool.check()
+    assert bool((out == 7.0).all())
+    pool.check()                      # the check word was cleared; the context still works
+    assert float((out + 1).sum()) == 8.0 * n_head * hd
+    for c in comms:
+        _lib.call("brc_comm_destroy", c)
+    pool.release()
