@@ -162,6 +162,9 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -257,14 +260,14 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
         brc::fence_proxy_async_smem();
         brc::mbar_arrive(bar_q);
 
-        // K and V of a block travel as two cp.async groups, K first, each into its own two-deep ring: K
-        // of block j is published as soon as the next group has been issued behind it, and its stage is
-        // free again when the S MMAs of block j retire, long before the block's V stage is.
+        // K and V of a block go into two-deep rings of their own: the K stage is free again when the S
+        // MMAs of block j retire, long before the block's V stage is.  The copies write shared memory
+        // through the generic proxy; the MMA thread orders them before its (async-proxy) operand reads
+        // with a proxy fence after it has seen the stage's barrier complete.
         // Thread -> (row r0 + 4 i, 16-byte chunk ch) of the [64 cells][512 B] tile, i < 16; the rows of a
         // thread walk through the block's 4 pages, 4 rows per page.
         const uint32_t *table = p.block_tables + (uint64_t)s * p.table_stride;
         const uint32_t ch = lt & 31u, r0 = lt >> 5;
-        uint32_t pending_bar = 0;   // barrier of the newest group but one (0 = none)
         bool dead = false;
         for (uint32_t j = 0; j < n_blk && !dead; ++j) {
             const uint32_t stg = j & 1u, par = ((j >> 1) & 1u) ^ 1u;
@@ -299,22 +302,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
                     const uint32_t off = (ch >> 3) * PF_KV_SLAB + r * 128u + (((ch & 7u) ^ (r & 7u)) << 4);
                     cp_async16(dst0 + off, base + src, live ? 16u : 0u);
                 }
-                cp_async_commit();
-                if (pending_bar) {   // the group before this one has landed: publish it
-                    cp_async_wait<1>();
-                    brc::fence_proxy_async_smem();
-                    brc::mbar_arrive(pending_bar);
-                }
-                pending_bar = (kv ? bar_vfull : bar_kfull) + 8u * stg;
+                // The arrival is carried by the copies themselves: it fires when all of this thread's copies
+                // issued so far have landed, so the loader never waits for data, only for a free stage.
+                cp_async_arrive_noinc((kv ? bar_vfull : bar_kfull) + 8u * stg);
             }
         }
-        cp_async_wait<0>();
-        brc::fence_proxy_async_smem();
+        asm volatile("cp.async.wait_all;" ::: "memory");
         if (dead) {
             if (!misc[1] && lt == 0) { atomicOr(p.status, BRC_DEV_WAIT_LIMIT); p.status[1] = 3000000u + blockIdx.x; }
             misc[1] = 1u;
-        } else if (pending_bar) {
-            brc::mbar_arrive(pending_bar);
         }
     } else if (warp == PF_MMA_WARP) {
         // ------------------------------------------------------------------ MMA issue (one thread)
@@ -328,6 +324,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
             auto issue_s = [&](uint32_t j) -> bool {
                 const uint32_t stg = j & 1u;
                 if (!pf_wait(bar_kfull + 8u * stg, (j >> 1) & 1u)) return false;
+                brc::fence_proxy_async_smem();
                 tc_fence_after();
                 const uint32_t k_sm = brc::smem_u32(k_sm0) + stg * PF_K_BYTES;
                 // S = Q . K^T: 16 steps of K = 16 (32 bytes inside a 128-byte swizzled row; 4 steps per slab)
@@ -352,6 +349,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
                 }
                 ok = pf_wait(bar_p + 8u * stg, par) && pf_wait(bar_vfull + 8u * stg, par);
                 if (!ok) break;
+                brc::fence_proxy_async_smem();
                 tc_fence_after();
                 const uint32_t v_sm = brc::smem_u32(v_sm0) + stg * PF_K_BYTES;
                 // O += P . V: 4 steps of K = 16 cells; V is MN-major: 16 cells = 2048 bytes down a slab,
