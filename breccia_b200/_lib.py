@@ -104,6 +104,7 @@ SIGNATURES = {
     "brc_comm_destroy": [_vp],
     "brc_splitkv_exchange_combine": [_vp, _vp, _u32, _vp, _u32, _vp, _vp],
     "brc_splitkv_attend": [_vp, _u32, _vp, _i32, _vp, _u32, _vp, _u32, _vp, _u32, _u32, _f32, _vp, _vp, _u64, _vp],
+    "brc_splitkv_step": [_vp, _u32, _u32, _vp, _i32, _u64, _vp, _u32, _vp, _u32, _vp, _u32, _u32, _f32, _vp, _vp, _u64, _vp],
     "brc_timing_enable": [_vp, _i32],
     "brc_timing_read": [_vp, _i32, _u32p, C.POINTER(C.c_double)],
 }

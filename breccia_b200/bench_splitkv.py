@@ -33,6 +33,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--graph", action="store_true", help="replay the step from a CUDA graph instead of launching every call from Python")
+    ap.add_argument("--per-layer", action="store_true",
+                    help="one attention call per layer, each waiting for the one before (a model's dependency chain); the "
+                         "default launches the layers of a step together, as the batched decode benchmark does")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
                     help="p2p: one kernel stores the partials to the peers and merges; nccl: all-gather + merge kernel")
     a = ap.parse_args()
@@ -51,7 +54,7 @@ def main():
     n_pages = (n_local + 15) // 16
     pool = KvPool(local, N_LAYERS, N_KV, HD, n_pages + 8)
     table = synth.permutation(100 + rank, n_pages + 8)[:n_pages]
-    split = SplitKvDecode(pool, N_HEAD, table, n_local, exchange=a.exchange)
+    split = SplitKvDecode(pool, N_HEAD, table, n_local, exchange=a.exchange, max_layers=N_LAYERS)
     gen = torch.Generator(device=dev)
     gen.manual_seed(7 + rank)
     zero = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -67,8 +70,11 @@ def main():
     out = torch.empty((N_LAYERS, 1, N_HEAD, HD), dtype=torch.float32, device=dev)
 
     def step():
-        for layer in range(N_LAYERS):
-            split.attend(layer, q[layer], out[layer])
+        if a.per_layer or a.exchange == "nccl":
+            for layer in range(N_LAYERS):
+                split.attend(layer, q[layer], out[layer])
+        else:
+            split.step(q, out)
 
     def barrier():
         if world > 1:
@@ -114,6 +120,7 @@ def main():
     if rank == 0:
         print(json.dumps({"metric": "splitkv_decode_tok_per_s", "value": 1e3 / ms_step, "unit": "tok/s", "n_gpus": world,
                           "steps": a.steps, "ms_per_step": ms_step, "scaling": "strong", "higher_is_better": True, "cuda_graph": bool(a.graph),
+                          "layers": "one call each, in order" if (a.per_layer or a.exchange == "nccl") else "launched together (brc_splitkv_step)",
                           "kv_gb_per_s": kv_bytes / (ms_step * 1e-3) / 1e9, "us_per_layer": ms_step * 1e3 / N_LAYERS,
                           "exchange": ("stores of 16512 B per peer per layer into peer memory + flags + merge, one kernel (brc_splitkv_attend)"
                                        if a.exchange == "p2p" else "ncclAllGather of 16512 B per rank per layer + brc_decode_combine"),

@@ -100,4 +100,13 @@ brc_status brc_decode_attn_append_fused(brc_pool *pool, uint32_t layer, const vo
                                         uint64_t workspace_bytes, const void *k_new_dev, const void *v_new_dev,
                                         int32_t kv_dtype, uint32_t index_in_step, uint32_t layers_in_step, void *stream);
 
+// brc_decode_partial as one of `layers_in_step` independent layers launched back to back, acc and
+// (m, l) to separate pointers (decode_attn.cu; used by brc_splitkv_step).  Not exported.
+extern "C" brc_status brc_decode_partial_in_step(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype,
+                                                 uint32_t n_head, const uint32_t *block_tables_dev, uint32_t table_stride,
+                                                 const uint32_t *seq_lens_dev, uint32_t n_seqs, uint32_t max_seq_len,
+                                                 float scale, float *acc_dev, float *ml_dev, void *workspace_dev,
+                                                 uint64_t workspace_bytes, uint32_t index_in_step, uint32_t layers_in_step,
+                                                 void *stream);
+
 static inline cudaStream_t brc_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }

@@ -354,4 +354,34 @@ brc_status brc_splitkv_attend(brc_comm *c, uint32_t layer, const void *q_dev, in
     return brc_splitkv_exchange_combine(c, nullptr, n_seqs, gate_dev, gate_head_stride, out_dev, stream);
 }
 
+brc_status brc_splitkv_step(brc_comm *c, uint32_t layer0, uint32_t n_layers, const void *q_dev, int32_t q_dtype,
+                            uint64_t q_layer_stride_bytes, const float *gate_dev, uint32_t gate_head_stride,
+                            const uint32_t *block_tables_dev, uint32_t table_stride, const uint32_t *seq_lens_dev,
+                            uint32_t n_seqs, uint32_t max_seq_len, float scale, float *out_dev, void *workspace_dev,
+                            uint64_t workspace_bytes, void *stream) {
+    if (!c) return brc_fail(BRC_ERR_INVALID, "brc_splitkv_step: NULL handle");
+    if (!c->connected) return brc_fail(BRC_ERR_INVALID, "brc_splitkv_step: the peers are not connected yet");
+    if (n_layers == 0 || n_seqs == 0) return BRC_OK;
+    if ((uint64_t)n_layers * n_seqs > c->max_seqs)
+        return brc_fail(BRC_ERR_CAPACITY, "brc_splitkv_step: %u layers x %u sequences but the buffers hold %u (sequence, layer) rows",
+                        n_layers, n_seqs, c->max_seqs);
+    if (layer0 + n_layers > c->pool->n_layers)
+        return brc_fail(BRC_ERR_INVALID, "brc_splitkv_step: layers %u..%u but the pool has %u", layer0, layer0 + n_layers,
+                        c->pool->n_layers);
+    // The partials of the step form one buffer as if the layers were further sequences:
+    // acc [n_layers][n_seqs][n_head][hd], then (m, l) [n_layers][n_seqs][n_head][2].
+    const uint32_t hd = c->pool->head_dim;
+    const size_t rows = (size_t)n_seqs * c->n_head;
+    float *acc = reinterpret_cast<float *>(c->local_part);
+    float *ml = acc + (size_t)n_layers * rows * hd;
+    for (uint32_t i = 0; i < n_layers; ++i) {
+        if (brc_status rc = brc_decode_partial_in_step(c->pool, layer0 + i, static_cast<const uint8_t *>(q_dev) + i * q_layer_stride_bytes,
+                                                       q_dtype, c->n_head, block_tables_dev, table_stride, seq_lens_dev, n_seqs,
+                                                       max_seq_len, scale, acc + i * rows * hd, ml + i * rows * 2, workspace_dev,
+                                                       workspace_bytes, i, n_layers, stream))
+            return rc;
+    }
+    return brc_splitkv_exchange_combine(c, nullptr, n_layers * n_seqs, gate_dev, gate_head_stride, out_dev, stream);
+}
+
 }  // extern "C"

@@ -1068,6 +1068,28 @@ brc_status brc_decode_partial(brc_pool *pool, uint32_t layer, const void *q_dev,
                       n_seqs, max_seq_len, scale, acc, ml, workspace_dev, brc_stream(stream));
 }
 
+// brc_decode_partial as layer `index_in_step` of `layers_in_step` independent layers launched back to
+// back (brc_splitkv_step): with a workspace of layers_in_step times the minimum, every layer has its
+// own partial buffers and arrival counters and the kernels overlap through programmatic dependent
+// launch, exactly as in brc_decode_step.  acc and (m, l) go to separate pointers.
+brc_status brc_decode_partial_in_step(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype, uint32_t n_head,
+                                      const uint32_t *block_tables_dev, uint32_t table_stride, const uint32_t *seq_lens_dev,
+                                      uint32_t n_seqs, uint32_t max_seq_len, float scale, float *acc_dev, float *ml_dev,
+                                      void *workspace_dev, uint64_t workspace_bytes, uint32_t index_in_step,
+                                      uint32_t layers_in_step, void *stream) {
+    if (brc_status rc = validate_decode(pool, "brc_splitkv_step", layer, q_dev, q_dtype, n_head, block_tables_dev, table_stride,
+                                        seq_lens_dev, n_seqs, max_seq_len, acc_dev, workspace_dev, workspace_bytes))
+        return rc;
+    if (n_seqs == 0) return BRC_OK;
+    FusedAppend app;   // nothing to append: only the bank and the overlap are used
+    uint64_t need = 0;
+    brc_decode_workspace_bytes(pool, n_seqs, n_head, &need);
+    app.overlap = layers_in_step > 1 && layers_in_step <= BRC_DONE_BANKS && workspace_bytes >= (uint64_t)layers_in_step * need;
+    app.bank = index_in_step;
+    return run_decode(pool, layer, q_dev, q_dtype, n_head, nullptr, 0, block_tables_dev, table_stride, seq_lens_dev, n_seqs,
+                      max_seq_len, scale, acc_dev, ml_dev, workspace_dev, brc_stream(stream), app);
+}
+
 brc_status brc_decode_combine(int32_t device, const void *parts_dev, uint32_t n_parts, uint64_t part_stride_bytes,
                               uint32_t n_seqs, uint32_t n_head, uint32_t head_dim, const float *gate_dev,
                               uint32_t gate_head_stride, float *out_dev, void *stream) {

@@ -42,7 +42,9 @@ class SplitKvDecode:
     """This rank's share of one long sequence and the machinery of a split-KV decode step."""
 
     def __init__(self, pool: KvPool, n_head: int, local_table: np.ndarray, local_len: int, group=None,
-                 q_dtype: int = DTYPE_F16, exchange: str = "p2p"):
+                 q_dtype: int = DTYPE_F16, exchange: str = "p2p", max_layers: int = 1):
+        """`max_layers` sizes the exchange buffers for `step`, which moves the partials of that many
+        layers with one kernel."""
         if exchange not in ("p2p", "nccl"):
             raise ValueError("exchange is 'p2p' or 'nccl'")
         self.pool, self.n_head, self.group, self.exchange = pool, n_head, group, exchange
@@ -57,7 +59,8 @@ class SplitKvDecode:
             self.gathered = torch.zeros(self.world * self.part_bytes, dtype=torch.uint8, device=dev)
             return
         comm = C.c_void_p()
-        _lib.call("brc_comm_create", pool.handle, self.world, self.rank, 1, n_head, C.byref(comm))
+        self.max_layers = max_layers
+        _lib.call("brc_comm_create", pool.handle, self.world, self.rank, max_layers, n_head, C.byref(comm))
         self.comm = comm
         if self.world > 1:
             mine = (C.c_uint8 * IPC_HANDLE_BYTES)()
@@ -91,6 +94,21 @@ class SplitKvDecode:
             parts = self.partial
         decode_combine(self.pool.device, parts, self.world, self.part_bytes, 1, self.n_head, self.pool.head_dim, out,
                        gate=gate, gate_head_stride=gate_head_stride)
+
+    def step(self, q: torch.Tensor, out: torch.Tensor, layer0: int = 0) -> None:
+        """One decode token over the layers q carries, the layers' attention calls being independent of
+        one another: q [L, 1, n_head, hd] -> out [L, 1, n_head, hd] f32 (contiguous).  The local kernels of
+        all layers overlap; one exchange kernel moves all partials (brc_splitkv_step)."""
+        b = self.batch
+        if self.comm is None:
+            for i in range(q.shape[0]):
+                self.attend(layer0 + i, q[i], out[i])
+            return
+        if not out.is_contiguous():
+            raise ValueError("out must be contiguous")
+        _lib.call("brc_splitkv_step", self.comm, layer0, q.shape[0], _ptr(q), b.q_dtype, q.stride(0) * q.element_size(), None, 0,
+                  _ptr(b.block_tables), b.table_stride, _ptr(b.seq_lens), 1, b.capacity, b.scale, _ptr(out), _ptr(b.scratch),
+                  b.scratch.numel(), _stream_ptr())
 
     def close(self) -> None:
         """Unmap the peers' buffers and free this rank's (all ranks, after their last step)."""

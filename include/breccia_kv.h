@@ -288,6 +288,23 @@ BRC_API brc_status brc_splitkv_attend(brc_comm *comm, uint32_t layer, const void
                                       const uint32_t *seq_lens_dev, uint32_t n_seqs, uint32_t max_seq_len,
                                       float scale, float *out_dev, void *workspace_dev,
                                       uint64_t workspace_bytes, void *stream);
+/* One decode token over `n_layers` layers whose attention calls do not depend on
+ * one another (the counterpart of brc_decode_step for the split-KV case, append
+ * excluded): the local split-KV kernels of all layers are launched back to back
+ * and overlap through programmatic dependent launch when `workspace_bytes` is at
+ * least n_layers times brc_decode_workspace_bytes(); then ONE exchange + merge
+ * kernel moves the partials of all layers (n_layers x 16 512 B per sequence per
+ * peer).  The comm must have been created with max_seqs >= n_layers * n_seqs.
+ * q is [n_layers] arrays `q_layer_stride_bytes` apart; out is
+ * [n_layers][n_seqs][n_head][head_dim] f32, contiguous; gate (nullable) is
+ * addressed as gate[row * gate_head_stride + d] with row = (layer, sequence,
+ * head) in that order. */
+BRC_API brc_status brc_splitkv_step(brc_comm *comm, uint32_t layer0, uint32_t n_layers, const void *q_dev,
+                                    int32_t q_dtype, uint64_t q_layer_stride_bytes, const float *gate_dev,
+                                    uint32_t gate_head_stride, const uint32_t *block_tables_dev,
+                                    uint32_t table_stride, const uint32_t *seq_lens_dev, uint32_t n_seqs,
+                                    uint32_t max_seq_len, float scale, float *out_dev, void *workspace_dev,
+                                    uint64_t workspace_bytes, void *stream);
 
 /* ---------------------------------------------------------------- one decode step over layers
  * The composition the reference performs per attention layer in Qsa::forward

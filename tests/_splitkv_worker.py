@@ -17,6 +17,12 @@ from breccia_b200.qsa import DecodeBatch, KvPool  # noqa: E402
 from breccia_b200.splitkv import SplitKvDecode, kv_range  # noqa: E402
 
 
+def _step_same_layer(split, q3, out3):
+    """brc_splitkv_step over the three layers of the worker's pool (which hold the same pages), so the
+    three outputs must equal the single-layer result bit for bit."""
+    split.step(q3, out3)
+
+
 def main():
     n_tokens = int(sys.argv[1]) if len(sys.argv) > 1 else 5000
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
@@ -31,15 +37,16 @@ def main():
     b, e = kv_range(rank, world, n_tokens)
     n_local = e - b
     n_pages = max((n_local + 15) // 16, 1)
-    pool = KvPool(local, 1, n_kv, hd, n_pages + 3)
+    pool = KvPool(local, 3, n_kv, hd, n_pages + 3)
     table = synth.permutation(10 + rank, n_pages + 3)[:n_pages]
     kp = np.zeros((n_pages + 3, n_kv, 16, hd), np.uint16)
     vp = np.zeros_like(kp)
     for c in range(n_local):
         kp[table[c // 16], :, c % 16, :] = k[b + c]
         vp[table[c // 16], :, c % 16, :] = v[b + c]
-    pool.write(0, 0, kp)
-    pool.write(1, 0, vp)
+    for layer in range(3):
+        pool.write(0, layer, kp)
+        pool.write(1, layer, vp)
     qd = torch.from_numpy(q).cuda().half()
     ok = True
     want = None
@@ -63,6 +70,16 @@ def main():
             err = float(np.abs(got - want).max())
             ok = ok and bool(np.isfinite(got).all()) and err <= 2e-3
             print(f"splitkv {exchange} world {world} tokens {n_tokens}: max_abs {err:.2e} identical_on_all_ranks {same}", flush=True)
+        if exchange == "p2p":
+            # the step form over 3 "layers" (the pool has one: the same layer three times) gives three copies
+            step = SplitKvDecode(pool, n_head, table, n_local, max_layers=3)
+            q3 = qd.unsqueeze(0).repeat(3, 1, 1, 1).contiguous()
+            out3 = torch.full((3, 1, n_head, hd), float("nan"), device="cuda")
+            _step_same_layer(step, q3, out3)
+            torch.cuda.synchronize()
+            pool.check()
+            ok = ok and bool(torch.equal(out3[0], out)) and bool(torch.equal(out3[1], out)) and bool(torch.equal(out3[2], out))
+            step.close()
         split.close()
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

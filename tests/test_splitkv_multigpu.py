@@ -52,6 +52,37 @@ def test_split_kv_machinery_with_one_rank(cuda_device):
     pool.release()
 
 
+def test_split_kv_step_over_layers_with_one_rank(cuda_device):
+    """brc_splitkv_step: the layers of one token launched together (overlapping kernels, one bank of
+    partials per layer), then one exchange + merge kernel for all of them; every layer against the oracle."""
+    import numpy as np
+
+    import oracle
+    from breccia_b200 import synth
+    from breccia_b200.qsa import KvPool
+    from breccia_b200.splitkv import SplitKvDecode
+    from helpers import fill_pool_from_host
+
+    n_head, n_kv, hd, n_tokens, n_layers = 16, 2, 256, 9000, 4
+    n_pages = (n_tokens + 15) // 16
+    pool = KvPool(0, n_layers, n_kv, hd, n_pages + 4)
+    kv = [fill_pool_from_host(pool, layer, 41 + layer) for layer in range(n_layers)]
+    table = synth.permutation(8, n_pages + 4)[:n_pages]
+    q = oracle.to_f16(synth.normal(9, n_layers * n_head * hd)).reshape(n_layers, 1, n_head, hd)
+    split = SplitKvDecode(pool, n_head, table, n_tokens, max_layers=n_layers)
+    out = torch.full((n_layers, 1, n_head, hd), float("nan"), device="cuda")
+    qd = torch.from_numpy(q).cuda().half()
+    for _ in range(3):
+        split.step(qd, out)
+    pool.check()
+    got = out.cpu().numpy()
+    for layer in range(n_layers):
+        want, _ = oracle.decode_batch(kv[layer][0], kv[layer][1], table[None, :], np.array([n_tokens]), q[layer], n_head, n_kv, hd)
+        assert np.abs(got[layer] - want).max() <= 2e-3, f"layer {layer}"
+    split.close()
+    pool.release()
+
+
 def test_a_peer_that_never_arrives_times_out_and_leaves_the_context_usable(cuda_device):
     """Rank 0 of a world of two exchanges alone (rank 1's end exists but never calls): the wait for its
     flag runs out after 20 ms, the output stays as it was, the pool reports BRC_ERR_TIMEOUT, and the next

@@ -112,3 +112,59 @@ def test_attention_over_promoted_pages_equals_attention_before_demotion(cuda_dev
     assert np.array_equal(out0.cpu().numpy(), out1.cpu().numpy())
     L.brc_tier_destroy(tier)
     pool.release()
+
+
+def test_back_to_back_batches_in_both_directions_keep_every_byte(cuda_device):
+    """Demotions and promotions issued back to back with no host-side wait in between: batches larger
+    than one staging pass (256 pages), slots reused as the cursor comes round, pages freed by a demotion
+    refilled at once by a promotion, promoted pages demoted again straight away.  Whatever the two copy
+    streams overlap, every page must come back with its bytes."""
+    n_layers, n_pages, n_move = 2, 700, 300
+    pool = KvPool(0, n_layers, 2, 256, n_pages)
+    L = _lib.load()
+    ids, ip = arr(np.zeros(600))
+    assert L.brc_pages_alloc(pool.handle, 600, ip) == 0
+    want = []
+    for layer in range(n_layers):
+        fill_pool_from_host(pool, layer, 950 + layer)
+        want.append((pool.read(0, layer).copy(), pool.read(1, layer).copy()))
+    tier = C.c_void_p()
+    assert L.brc_tier_create(pool.handle, 640, C.byref(tier)) == 0   # 640 slots: the cursor wraps in round 3
+    where = {int(p): int(p) for p in ids}          # original page -> where its bytes are now (HBM page id)
+    group_a, group_b = [int(p) for p in ids[:n_move]], [int(p) for p in ids[n_move:2 * n_move]]
+    slots_a = None
+    for rnd in range(4):
+        # A goes out (or comes back) while B does the opposite, without waiting for anything
+        if slots_a is None:
+            pages, pp = arr([where[p] for p in group_a])
+            slots_a, sp = arr(np.zeros(n_move))
+            assert L.brc_tier_demote(tier, pp, n_move, sp, None) == 0
+            pages_b, pbp = arr([where[p] for p in group_b])
+            slots_b, sbp = arr(np.zeros(n_move))
+            assert L.brc_tier_demote(tier, pbp, n_move, sbp, None) == 0
+            back, bp = arr(np.zeros(n_move))
+            assert L.brc_tier_promote(tier, sbp, n_move, bp) == 0       # B straight back in
+            for p, new in zip(group_b, back):
+                where[p] = int(new)
+        else:
+            back, bp = arr(np.zeros(n_move))
+            _, sp = arr(slots_a)
+            assert L.brc_tier_promote(tier, sp, n_move, bp) == 0         # A comes back ...
+            for p, new in zip(group_a, back):
+                where[p] = int(new)
+            pages, pp = arr([where[p] for p in group_a])
+            slots_a, sp = arr(np.zeros(n_move))
+            assert L.brc_tier_demote(tier, pp, n_move, sp, None) == 0    # ... and leaves again at once
+    back, bp = arr(np.zeros(n_move))
+    _, sp = arr(slots_a)
+    assert L.brc_tier_promote(tier, sp, n_move, bp) == 0
+    for p, new in zip(group_a, back):
+        where[p] = int(new)
+    assert L.brc_tier_sync(tier) == 0
+    for layer in range(n_layers):
+        k, v = pool.read(0, layer), pool.read(1, layer)
+        for p in group_a + group_b:
+            assert np.array_equal(k[where[p]], want[layer][0][p]), f"K layer {layer} page {p}"
+            assert np.array_equal(v[where[p]], want[layer][1][p]), f"V layer {layer} page {p}"
+    L.brc_tier_destroy(tier)
+    pool.release()
