@@ -13,10 +13,12 @@
 //   S[128 x 64]  = Q[128 x 256] . K^T      tcgen05.mma kind::f16, M=128 N=64, 16 steps of K=16, fp32 in TMEM
 //   P            = 2^(scale' S - m)        4 softmax warps, one thread per row, tcgen05.ld; causal mask
 //   O[128 x 256] += P[128 x 64] . V        tcgen05.mma M=128 N=256, 4 steps of K=16, V read MN-major
-// Q, K, V and P sit in shared memory in the canonical 128-byte-swizzled layouts the matrix descriptors
-// name.  K/V pages are gathered through the block table by four loader warps with 16-byte cp.async
+// Q and P are A operands read from tensor memory (Q is stored there once; P overwrites the S buffer it
+// was computed from), so shared memory holds only K and V tiles, in the canonical 128-byte-swizzled
+// layouts the matrix descriptors name: with A in shared memory every S MMA re-read 4 KiB of Q for 2 KiB
+// of K, and the kernel ran at the shared-memory bandwidth, not at the tensor pipe's.  K/V pages are gathered through the block table by four loader warps with 16-byte cp.async
 // (a 16-cell page is too small a TMA box: ~215 cycles per operation whatever its size), K and V in
-// separate two-deep rings; cells at or past the end of the cache are zero-filled.  S and P are double
+// separate three-deep rings; cells at or past the end of the cache are zero-filled.  S and P are double
 // buffered: the MMA thread issues S of block j + 1 before P.V of block j, so the tensor pipe computes
 // the next scores while the softmax warps work on the current ones.  O stays in TMEM across blocks and is
 // rescaled only when a row's maximum grew by more than 2^8 since the scale in use (rare after the
@@ -33,7 +35,7 @@ constexpr int PF_HD = 256;
 constexpr int PF_ROWS = 128;              // 16 tokens x 8 head slots
 constexpr int PF_TOK = 16;
 constexpr int PF_BLK = 64;                // cells per block
-constexpr int PF_STAGES = 2;
+constexpr int PF_STAGES = 3;               // depth of the K ring and of the V ring
 constexpr int PF_SOFTMAX_WARPS = 4;       // warps 0-3: TMEM lane quarter = warp id
 constexpr int PF_MMA_WARP = 4;
 constexpr int PF_LOAD_WARP0 = 5;          // warps 5-8
@@ -45,9 +47,11 @@ constexpr uint32_t PF_KV_SLAB = PF_BLK * 128;             // [64 cells][128 B]
 constexpr uint32_t PF_K_BYTES = 4 * PF_KV_SLAB;           // 32 KiB
 constexpr uint32_t PF_STAGE_BYTES = 2 * PF_K_BYTES;       // K then V
 constexpr uint32_t PF_P_BYTES = PF_ROWS * 128;            // [128 rows][64 cells] f16
-constexpr uint32_t PF_SMEM = 1024 + PF_Q_BYTES + 2 * PF_P_BYTES + PF_STAGES * PF_STAGE_BYTES + 1024;
+constexpr uint32_t PF_SMEM = 1024 + PF_STAGES * PF_STAGE_BYTES + 1024;
 constexpr uint32_t PF_TMEM_COLS = 512;
-constexpr uint32_t PF_S0_COL = 0, PF_O_COL = 64, PF_S1_COL = 320;   // two S buffers of 64 columns around O
+// Tensor memory: Q (128 rows x 256 binary16 = 128 columns), O (256 columns, fp32), two S buffers of 64 columns
+// (fp32) whose first 32 columns are overwritten by P (binary16 pairs).
+constexpr uint32_t PF_Q_COL = 0, PF_O_COL = 128, PF_S0_COL = 384, PF_S1_COL = 448;
 constexpr uint64_t PF_WAIT_NS = 1000000000ull;
 constexpr float PF_RESCALE_THRESHOLD = 8.0f;              // log2 units
 
@@ -108,6 +112,22 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
         : "memory");
 }
 
+// The same with the A operand in tensor memory (row = lane, two binary16 per 32-bit column cell).
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// One lane of the (converged) warp, the same one every time.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -147,6 +167,18 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+          "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]),
+          "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]),
+          "r"(v[30]), "r"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
     float a[32], b[32];
     tmem_ld32(taddr, a);
@@ -178,20 +210,18 @@ __device__ __forceinline__ float pf_sigmoid(float x) {
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const PrefillParams p) {
     extern __shared__ uint8_t pf_smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023u) & ~uintptr_t(1023));
-    uint8_t *q_sm = smem;
-    uint8_t *p_sm = q_sm + PF_Q_BYTES;                       // [2][128 rows][128 B]
-    uint8_t *k_sm0 = p_sm + 2 * PF_P_BYTES;                  // [PF_STAGES][32 KiB]
+    uint8_t *k_sm0 = smem;                                   // [PF_STAGES][32 KiB]
     uint8_t *v_sm0 = k_sm0 + PF_STAGES * PF_K_BYTES;         // [PF_STAGES][32 KiB]
     uint64_t *bars = reinterpret_cast<uint64_t *>(v_sm0 + PF_STAGES * PF_K_BYTES);
-    const uint32_t bar_kfull = brc::smem_u32(bars);          // [2] loaders -> MMA
-    const uint32_t bar_vfull = bar_kfull + 16u;              // [2]
-    const uint32_t bar_kempty = bar_vfull + 16u;             // [2] S MMAs of the stage retired
-    const uint32_t bar_vempty = bar_kempty + 16u;            // [2] P.V MMAs of the stage retired
-    const uint32_t bar_s = bar_vempty + 16u;                 // [2] S buffer written
-    const uint32_t bar_p = bar_s + 16u;                      // [2] P buffer written, S buffer read
+    const uint32_t bar_kfull = brc::smem_u32(bars);          // [PF_STAGES] loaders -> MMA
+    const uint32_t bar_vfull = bar_kfull + 8u * PF_STAGES;   // [PF_STAGES]
+    const uint32_t bar_kempty = bar_vfull + 8u * PF_STAGES;  // [PF_STAGES] S MMAs of the stage retired
+    const uint32_t bar_vempty = bar_kempty + 8u * PF_STAGES; // [PF_STAGES] P.V MMAs of the stage retired
+    const uint32_t bar_s = bar_vempty + 8u * PF_STAGES;      // [2] S buffer written
+    const uint32_t bar_p = bar_s + 16u;                      // [2] P written over the S buffer
     const uint32_t bar_o = bar_p + 16u;                      // [2] P.V of the block retired
-    const uint32_t bar_q = bar_o + 16u;
-    volatile uint32_t *misc = reinterpret_cast<volatile uint32_t *>(bars + 24);   // [0] tmem base, [1] dead
+    const uint32_t bar_q = bar_o + 16u;                      // Q is in tensor memory
+    volatile uint32_t *misc = reinterpret_cast<volatile uint32_t *>(bars + 32);   // [0] tmem base, [1] dead
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t kvh = blockIdx.x % p.n_kv_head;
@@ -209,16 +239,18 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
     const uint32_t n_blk = (cells_needed + PF_BLK - 1) / PF_BLK;
 
     if (tid == 0) {
-        for (uint32_t i = 0; i < 2; ++i) {
+        for (uint32_t i = 0; i < PF_STAGES; ++i) {
             brc::mbar_init(bar_kfull + 8u * i, PF_LOAD_WARPS * 32);
             brc::mbar_init(bar_vfull + 8u * i, PF_LOAD_WARPS * 32);
             brc::mbar_init(bar_kempty + 8u * i, 1);
             brc::mbar_init(bar_vempty + 8u * i, 1);
+        }
+        for (uint32_t i = 0; i < 2; ++i) {
             brc::mbar_init(bar_s + 8u * i, 1);
             brc::mbar_init(bar_p + 8u * i, PF_SOFTMAX_WARPS * 32);
             brc::mbar_init(bar_o + 8u * i, 1);
         }
-        brc::mbar_init(bar_q, PF_LOAD_WARPS * 32);
+        brc::mbar_init(bar_q, PF_SOFTMAX_WARPS * 32);
         brc::mbar_fence_init();
         misc[1] = 0u;
     }
@@ -235,42 +267,18 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
 
     if (warp >= PF_LOAD_WARP0) {
         // ------------------------------------------------------------------ loader warps
-        const uint32_t lt = tid - PF_LOAD_WARP0 * 32;   // 0..127
-        // Q tile: row = token * 8 + head slot; 32 chunks of 16 B per row; 4 slabs of [128 rows][128 B]
-        for (uint32_t c = lt; c < PF_ROWS * 32; c += PF_LOAD_WARPS * 32) {
-            const uint32_t row = c >> 5, ch = c & 31u;
-            const uint32_t tl = row >> 3, h = row & 7u;
-            const bool live = tl < n_tok && h < p.group;
-            const uint32_t dst = brc::smem_u32(q_sm) + (ch >> 3) * PF_Q_SLAB + row * 128u + (((ch & 7u) ^ (row & 7u)) << 4);
-            const uint64_t qrow = ((uint64_t)(s * p.chunk + t0 + (live ? tl : 0)) * p.n_head + kvh * p.group + (live ? h : 0)) * PF_HD;
-            if (!p.q_f32) {
-                cp_async16(dst, static_cast<const uint16_t *>(p.q) + qrow + ch * 8u, live ? 16u : 0u);
-            } else {
-                uint4 w = make_uint4(0, 0, 0, 0);
-                if (live) {
-                    const float4 *src = reinterpret_cast<const float4 *>(static_cast<const float *>(p.q) + qrow + ch * 8u);
-                    const float4 a = __ldg(src), b = __ldg(src + 1);
-                    w = make_uint4(brc::pack_half2(a.x, a.y), brc::pack_half2(a.z, a.w), brc::pack_half2(b.x, b.y), brc::pack_half2(b.z, b.w));
-                }
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(w.x), "r"(w.y), "r"(w.z), "r"(w.w) : "memory");
-            }
-        }
-        cp_async_commit();
-        cp_async_wait<0>();
-        brc::fence_proxy_async_smem();
-        brc::mbar_arrive(bar_q);
-
-        // K and V of a block go into two-deep rings of their own: the K stage is free again when the S
-        // MMAs of block j retire, long before the block's V stage is.  The copies write shared memory
-        // through the generic proxy; the MMA thread orders them before its (async-proxy) operand reads
-        // with a proxy fence after it has seen the stage's barrier complete.
+        // K and V of a block go into rings of their own (PF_STAGES deep): the K stage is free again when
+        // the S MMAs of block j retire, long before the block's V stage is.  The copies write shared
+        // memory through the generic proxy; the MMA thread orders them before its (async-proxy) operand
+        // reads with a proxy fence after it has seen the stage's barrier complete.
         // Thread -> (row r0 + 4 i, 16-byte chunk ch) of the [64 cells][512 B] tile, i < 16; the rows of a
         // thread walk through the block's 4 pages, 4 rows per page.
+        const uint32_t lt = tid - PF_LOAD_WARP0 * 32;   // 0..127
         const uint32_t *table = p.block_tables + (uint64_t)s * p.table_stride;
         const uint32_t ch = lt & 31u, r0 = lt >> 5;
         bool dead = false;
+        uint32_t stg = 0, par = 1;                      // stage j % PF_STAGES, parity of its "empty" phase
         for (uint32_t j = 0; j < n_blk && !dead; ++j) {
-            const uint32_t stg = j & 1u, par = ((j >> 1) & 1u) ^ 1u;
             uint32_t page[4];
 #pragma unroll
             for (uint32_t g = 0; g < 4; ++g) {
@@ -306,6 +314,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
                 // issued so far have landed, so the loader never waits for data, only for a free stage.
                 cp_async_arrive_noinc((kv ? bar_vfull : bar_kfull) + 8u * stg);
             }
+            if (++stg == PF_STAGES) { stg = 0; par ^= 1u; }
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
         if (dead) {
@@ -313,60 +322,73 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
             misc[1] = 1u;
         }
     } else if (warp == PF_MMA_WARP) {
-        // ------------------------------------------------------------------ MMA issue (one thread)
+        // ------------------------------------------------------------------ MMA issue
+        // Both A operands come from tensor memory (Q, written once by the softmax warps; P, written over
+        // the S buffer it was computed from), so shared memory only serves the K and V tiles.
         // S of block j + 1 is issued before P.V of block j: the tensor pipe works on the next scores while
         // the softmax warps turn the current ones into P, and on P.V while they read the next scores.
-        if (lane == 0) {
-            const uint32_t idesc_s = umma_idesc(PF_BLK, false);
-            const uint32_t idesc_o = umma_idesc(PF_HD, true);
-            bool ok = pf_wait(bar_q, 0);
+        // The whole warp runs the loop (waits, descriptor arithmetic: warp-uniform, so it stays on the
+        // uniform datapath); one elected lane issues the MMAs and commits.
+        const bool leader = elect_one();
+        const uint32_t idesc_s = umma_idesc(PF_BLK, false);
+        const uint32_t idesc_o = umma_idesc(PF_HD, true);
+        const uint32_t k_base = brc::smem_u32(k_sm0), v_base = brc::smem_u32(v_sm0);
+        bool ok = __all_sync(0xffffffffu, pf_wait(bar_q, 0));
+        tc_fence_after();
+        auto issue_s = [&](uint32_t j) -> bool {
+            const uint32_t stg = j % PF_STAGES, buf = j & 1u;
+            if (!__all_sync(0xffffffffu, pf_wait(bar_kfull + 8u * stg, (j / PF_STAGES) & 1u))) return false;
             brc::fence_proxy_async_smem();
-            auto issue_s = [&](uint32_t j) -> bool {
-                const uint32_t stg = j & 1u;
-                if (!pf_wait(bar_kfull + 8u * stg, (j >> 1) & 1u)) return false;
-                brc::fence_proxy_async_smem();
-                tc_fence_after();
-                const uint32_t k_sm = brc::smem_u32(k_sm0) + stg * PF_K_BYTES;
-                // S = Q . K^T: 16 steps of K = 16 (32 bytes inside a 128-byte swizzled row; 4 steps per slab)
+            tc_fence_after();
+            const uint32_t k_sm = k_base + stg * PF_K_BYTES;
+            const uint32_t s_tm = tmem + (buf ? PF_S1_COL : PF_S0_COL);
+            if (leader) {
+                // S = Q . K^T: 16 steps of K = 16: 8 columns of Q in tensor memory (two binary16 per
+                // 32-bit cell), 32 bytes inside a 128-byte swizzled row of K (4 steps per slab)
 #pragma unroll
                 for (uint32_t ks = 0; ks < PF_HD / 16; ++ks) {
-                    const uint64_t a = umma_desc(brc::smem_u32(q_sm) + (ks >> 2) * PF_Q_SLAB + (ks & 3u) * 32u, 16, 1024);
                     const uint64_t b = umma_desc(k_sm + (ks >> 2) * PF_KV_SLAB + (ks & 3u) * 32u, 16, 1024);
-                    umma_f16(tmem + (stg ? PF_S1_COL : PF_S0_COL), a, b, idesc_s, ks > 0);
+                    umma_f16_ts(s_tm, tmem + PF_Q_COL + ks * 8u, b, idesc_s, ks > 0);
                 }
-                umma_commit(bar_s + 8u * stg);
+                umma_commit(bar_s + 8u * buf);
                 umma_commit(bar_kempty + 8u * stg);
-                return true;
-            };
-            if (ok && n_blk > 0) ok = issue_s(0);
-            for (uint32_t j = 0; j < n_blk && ok && !misc[1]; ++j) {
-                const uint32_t stg = j & 1u, par = (j >> 1) & 1u;
-                // The S buffer of block j + 1 was last read by the softmax of block j - 1, whose bar_p this
-                // thread waited for before issuing P.V of block j - 1.
-                if (j + 1 < n_blk) {
-                    ok = issue_s(j + 1);
-                    if (!ok) break;
-                }
-                ok = pf_wait(bar_p + 8u * stg, par) && pf_wait(bar_vfull + 8u * stg, par);
+            }
+            __syncwarp();
+            return true;
+        };
+        if (ok && n_blk > 0) ok = issue_s(0);
+        for (uint32_t j = 0; j < n_blk && ok; ++j) {
+            if (__any_sync(0xffffffffu, misc[1] != 0u)) break;
+            const uint32_t stg = j % PF_STAGES, buf = j & 1u;
+            // The S buffer of block j + 1 held P of block j - 1, whose P.V was issued before this
+            // point: the tensor pipe runs in issue order.
+            if (j + 1 < n_blk) {
+                ok = issue_s(j + 1);
                 if (!ok) break;
-                brc::fence_proxy_async_smem();
-                tc_fence_after();
-                const uint32_t v_sm = brc::smem_u32(v_sm0) + stg * PF_K_BYTES;
-                // O += P . V: 4 steps of K = 16 cells; V is MN-major: 16 cells = 2048 bytes down a slab,
-                // the four 64-column slabs are 8 KiB apart (leading offset), 8-cell groups 1 KiB apart
+            }
+            ok = __all_sync(0xffffffffu, pf_wait(bar_p + 8u * buf, (j >> 1) & 1u) && pf_wait(bar_vfull + 8u * stg, (j / PF_STAGES) & 1u));
+            if (!ok) break;
+            brc::fence_proxy_async_smem();
+            tc_fence_after();
+            const uint32_t v_sm = v_base + stg * PF_K_BYTES;
+            const uint32_t p_tm = tmem + (buf ? PF_S1_COL : PF_S0_COL);
+            if (leader) {
+                // O += P . V: 4 steps of K = 16 cells: 8 columns of P in tensor memory; V is MN-major:
+                // 16 cells = 2048 bytes down a slab, the four 64-column slabs are 8 KiB apart (leading
+                // offset), 8-cell groups 1 KiB apart
 #pragma unroll
                 for (uint32_t ks = 0; ks < PF_BLK / 16; ++ks) {
-                    const uint64_t a = umma_desc(brc::smem_u32(p_sm) + stg * PF_P_BYTES + ks * 32u, 16, 1024);
                     const uint64_t b = umma_desc(v_sm + ks * 2048u, PF_KV_SLAB, 1024);
-                    umma_f16(tmem + PF_O_COL, a, b, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                    umma_f16_ts(tmem + PF_O_COL, p_tm + ks * 8u, b, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
                 }
-                umma_commit(bar_o + 8u * stg);
+                umma_commit(bar_o + 8u * buf);
                 umma_commit(bar_vempty + 8u * stg);
             }
-            if (!ok) {
-                if (!misc[1]) { atomicOr(p.status, BRC_DEV_WAIT_LIMIT); p.status[1] = 4000000u + blockIdx.x; }
-                misc[1] = 1u;
-            }
+            __syncwarp();
+        }
+        if (!ok) {
+            if (!misc[1] && lane == 0) { atomicOr(p.status, BRC_DEV_WAIT_LIMIT); p.status[1] = 4000000u + blockIdx.x; }
+            misc[1] = 1u;
         }
     } else {
         // ------------------------------------------------------------------ softmax warps: thread = row
@@ -374,17 +396,46 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
         const uint32_t tl = row >> 3, h = row & 7u;
         const uint32_t limit = pos0 + t0 + tl;          // last cell this row sees
         const uint32_t lane_base = (warp * 32u) << 16;  // this warp's TMEM lane quarter
+        const bool live_row = tl < n_tok && h < p.group;
+        // Q row (token t0 + tl, query head h of the group) into tensor memory: two binary16 per 32-bit
+        // cell, 128 cells; rows outside the tile are zero.
+        {
+            const uint64_t qrow = ((uint64_t)(s * p.chunk + t0 + (live_row ? tl : 0)) * p.n_head + kvh * p.group + (live_row ? h : 0)) * PF_HD;
+#pragma unroll 1
+            for (uint32_t c = 0; c < 4; ++c) {          // 64 elements = 32 cells per pass
+                uint32_t w[32];
+                if (!p.q_f32) {
+                    const uint4 *src = reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(p.q) + qrow + c * 64u);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const uint4 x = live_row ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
+                        w[i * 4] = x.x, w[i * 4 + 1] = x.y, w[i * 4 + 2] = x.z, w[i * 4 + 3] = x.w;
+                    }
+                } else {
+                    const float4 *src = reinterpret_cast<const float4 *>(static_cast<const float *>(p.q) + qrow + c * 64u);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float4 x = live_row ? __ldg(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        w[i * 2] = brc::pack_half2(x.x, x.y), w[i * 2 + 1] = brc::pack_half2(x.z, x.w);
+                    }
+                }
+                tmem_st32u(tmem + lane_base + PF_Q_COL + c * 32u, w);
+            }
+            tc_fence_before();
+            brc::mbar_arrive(bar_q);
+        }
         float m_used = -INFINITY, l = 0.f;              // m_used in units of scale_log2 * score
         bool ok = true;
         for (uint32_t j = 0; j < n_blk; ++j) {
-            const uint32_t stg = j & 1u, par = (j >> 1) & 1u;
+            const uint32_t buf = j & 1u, par = (j >> 1) & 1u;
+            const uint32_t s_col = buf ? PF_S1_COL : PF_S0_COL;
             // warp-uniform control flow: the TMEM accesses below are warp-wide
             if (__any_sync(0xffffffffu, misc[1] != 0u)) { ok = true; break; }
-            ok = __all_sync(0xffffffffu, pf_wait(bar_s + 8u * stg, par));
+            ok = __all_sync(0xffffffffu, pf_wait(bar_s + 8u * buf, par));
             if (!ok) break;
             tc_fence_after();
             float sc[PF_BLK];
-            tmem_ld64(tmem + lane_base + (stg ? PF_S1_COL : PF_S0_COL), sc);
+            tmem_ld64(tmem + lane_base + s_col, sc);
             const uint32_t c0 = j * PF_BLK;
             float mx = -INFINITY;
             if (c0 + PF_BLK - 1 > limit) {
@@ -422,44 +473,33 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
                     tmem_st32(tmem + lane_base + PF_O_COL + cg * 32, v);
                 }
             }
-            // This block's P buffer was last read by P.V of block j - 2
-            if (j >= 2) {
-                ok = __all_sync(0xffffffffu, pf_wait(bar_o + 8u * stg, (par ^ 1u)));
-                if (!ok) break;
-            }
-            // P row (binary16) into its swizzled shared-memory row: 8 chunks of 8 cells
-            const uint32_t prow = brc::smem_u32(p_sm) + stg * PF_P_BYTES + row * 128u;
+            // P row (binary16, two cells per 32-bit cell) over the first 32 columns of the S buffer it came
+            // from: S of block j is in registers, and the buffer's previous P (block j - 2) was consumed
+            // before the MMAs that wrote this S (the tensor pipe runs in issue order).
             const float neg_m = m_used == -INFINITY ? 0.f : -m_used;   // a row with no live cell yet has only -inf scores
+            uint32_t w[32];
 #pragma unroll
-            for (int c8 = 0; c8 < 8; ++c8) {
-                uint32_t w[4];
-#pragma unroll
-                for (int k2 = 0; k2 < 4; ++k2) {
-                    const float a = brc::fast_exp2(fmaf(sc[c8 * 8 + k2 * 2], p.scale_log2, neg_m));
-                    const float b = brc::fast_exp2(fmaf(sc[c8 * 8 + k2 * 2 + 1], p.scale_log2, neg_m));
-                    l += a + b;
-                    w[k2] = brc::pack_half2(a, b);
-                }
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(prow + ((c8 ^ (row & 7u)) << 4)), "r"(w[0]), "r"(w[1]),
-                             "r"(w[2]), "r"(w[3])
-                             : "memory");
+            for (int i = 0; i < 32; ++i) {
+                const float a = brc::fast_exp2(fmaf(sc[2 * i], p.scale_log2, neg_m));
+                const float b = brc::fast_exp2(fmaf(sc[2 * i + 1], p.scale_log2, neg_m));
+                l += a + b;
+                w[i] = brc::pack_half2(a, b);
             }
-            brc::fence_proxy_async_smem();
+            tmem_st32u(tmem + lane_base + s_col, w);
             tc_fence_before();
-            brc::mbar_arrive(bar_p + 8u * stg);
+            brc::mbar_arrive(bar_p + 8u * buf);
         }
         if (ok && n_blk > 0 && !__any_sync(0xffffffffu, misc[1] != 0u)) {
             ok = __all_sync(0xffffffffu, pf_wait(bar_o + 8u * ((n_blk - 1) & 1u), ((n_blk - 1) >> 1) & 1u));
             if (ok) {
                 tc_fence_after();
-                const bool live = tl < n_tok && h < p.group;
                 const float inv = l > 0.f ? 1.f / l : 0.f;
                 const uint64_t orow = ((uint64_t)(s * p.chunk + t0 + tl) * p.n_head + kvh * p.group + h);
 #pragma unroll 1
                 for (int cg = 0; cg < PF_HD / 32; ++cg) {
                     float v[32];
                     tmem_ld32(tmem + lane_base + PF_O_COL + cg * 32, v);
-                    if (live) {
+                    if (live_row) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 4) {
                             float4 r = make_float4(v[i] * inv, v[i + 1] * inv, v[i + 2] * inv, v[i + 3] * inv);
