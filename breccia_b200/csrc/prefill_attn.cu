@@ -437,17 +437,18 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
             float sc[PF_BLK];
             tmem_ld64(tmem + lane_base + s_col, sc);
             const uint32_t c0 = j * PF_BLK;
-            float mx = -INFINITY;
             if (c0 + PF_BLK - 1 > limit) {
 #pragma unroll
-                for (int i = 0; i < PF_BLK; ++i) {
+                for (int i = 0; i < PF_BLK; ++i)
                     if (c0 + i > limit) sc[i] = -INFINITY;
-                    mx = fmaxf(mx, sc[i]);
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < PF_BLK; ++i) mx = fmaxf(mx, sc[i]);
             }
+            // eight independent chains: a single chain of 64 dependent maxima costs more than the exponentials
+            float mx8[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) mx8[i] = sc[i];
+#pragma unroll
+            for (int i = 8; i < PF_BLK; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], sc[i]);
+            float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
             mx *= p.scale_log2;   // the scale is positive: max commutes with it
             // Raise the scale in use when this row's maximum grew a lot (or at its first live block):
             // O *= 2^(old - new).  TMEM loads and stores are warp-wide, so the warp goes through the
@@ -478,13 +479,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
             // before the MMAs that wrote this S (the tensor pipe runs in issue order).
             const float neg_m = m_used == -INFINITY ? 0.f : -m_used;   // a row with no live cell yet has only -inf scores
             uint32_t w[32];
+            float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
                 const float a = brc::fast_exp2(fmaf(sc[2 * i], p.scale_log2, neg_m));
                 const float b = brc::fast_exp2(fmaf(sc[2 * i + 1], p.scale_log2, neg_m));
-                l += a + b;
+                l4[i & 3] += a + b;
                 w[i] = brc::pack_half2(a, b);
             }
+            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             tmem_st32u(tmem + lane_base + s_col, w);
             tc_fence_before();
             brc::mbar_arrive(bar_p + 8u * buf);
