@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the paged KV decode hot path (BASELINE config "Batched decode").
+"""Benchmark of the paged KV decode hot path (the batched-decode workload).
 
     python bench.py --gpus N --steps K --warmup W            # this library on N GPUs (torchrun for N > 1)
     python bench.py --impl reference --steps K --warmup W    # the reference's CPU algorithm on the host cores
@@ -43,7 +43,7 @@ def parse_args():
     ap.add_argument("--seed", type=int, default=20261125)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=12,
-                    help="attention layers per step (12 = the BASELINE workload; fewer only for small profiler captures)")
+                    help="attention layers per step (12 = the full workload; fewer only for small profiler captures)")
     return ap.parse_args()
 
 

@@ -105,6 +105,10 @@ SIGNATURES = {
     "brc_splitkv_exchange_combine": [_vp, _vp, _u32, _vp, _u32, _vp, _vp],
     "brc_splitkv_attend": [_vp, _u32, _vp, _i32, _vp, _u32, _vp, _u32, _vp, _u32, _u32, _f32, _vp, _vp, _u64, _vp],
     "brc_splitkv_step": [_vp, _u32, _u32, _vp, _i32, _u64, _vp, _u32, _vp, _u32, _vp, _u32, _u32, _f32, _vp, _vp, _u64, _vp],
+    "brc_state_dump": [_vp, _u32, _u32p, _u32, _u32, _u32, C.c_char_p, _vp],
+    "brc_state_load": [_vp, _u32, _u32p, _u32, _u32, _u32, C.c_char_p, _vp],
+    "brc_qk_prepare_append": [_vp, _u32, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _f32, _vp, _u32, _u32, _vp, _u32, _vp, _u32, _u32,
+                              _u32, _vp, _i32, _vp],
     "brc_timing_enable": [_vp, _i32],
     "brc_timing_read": [_vp, _i32, _u32p, C.POINTER(C.c_double)],
 }

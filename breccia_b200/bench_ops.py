@@ -5,7 +5,7 @@
     python -m breccia_b200.bench_ops [--op prefill|append|gather|copy|fork|tier|all] [--iters N]
 
 Timing: CUDA events on the launching stream, 3 warm-up runs, the mean of `iters` runs.  Shapes are the
-BASELINE configurations: prefill = 64 sequences sharing a 4096-token prefix, 256-token chunk each
+benchmark configurations: prefill = 64 sequences sharing a 4096-token prefix, 256-token chunk each
 (GQA 16q/2kv, head_dim 256); the byte movers run on the same pool.
 """
 from __future__ import annotations

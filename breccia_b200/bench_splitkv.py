@@ -1,4 +1,4 @@
-"""Benchmark of BASELINE config 3: one sequence of 131 072 cells, 12 layers, decode attention split along
+"""Benchmark of the long-context single-stream workload: one sequence of 131 072 cells, 12 layers, decode attention split along
 the KV length over the GPUs of one box, partials merged over NVLink.
 
     python -m breccia_b200.bench_splitkv                                   # 1 GPU

@@ -1,4 +1,4 @@
-"""Benchmark of BASELINE config 5, tiered paging churn: 128 decoding sequences, context lengths uniform
+"""Benchmark of the tiered-paging churn workload: 128 decoding sequences, context lengths uniform
 in [1024, 16384] (seeded), 12 layers, GQA 16q/2kv, head_dim 256, f16 KV, the HBM page pool capped at
 60 % of the total need, the rest of the pages in pinned host memory.
 

@@ -1,4 +1,4 @@
-"""Long single-stream decode split along the KV length across GPUs (BASELINE config 3).
+"""Long single-stream decode split along the KV length across GPUs (the long-context single-stream workload).
 
 One process per GPU (torch.distributed, NCCL over NVLink).  Rank r of n holds the cells
 [r * L / n, (r + 1) * L / n) of the sequence (page-aligned) in its own pool, under a local block table

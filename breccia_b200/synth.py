@@ -1,4 +1,4 @@
-"""Seeded synthetic inputs for the BASELINE workloads (host-side, NumPy only).
+"""Seeded synthetic inputs for the benchmark workloads (host-side, NumPy only).
 
 One generator feeds the GPU path, the oracle and the CPU baseline so all three see identical bits:
 splitmix64 (counter mode) -> Box-Muller in float64 -> float32.  Block tables are slices of one seeded

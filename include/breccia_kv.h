@@ -288,6 +288,49 @@ BRC_API brc_status brc_splitkv_attend(brc_comm *comm, uint32_t layer, const void
                                       const uint32_t *seq_lens_dev, uint32_t n_seqs, uint32_t max_seq_len,
                                       float scale, float *out_dev, void *workspace_dev,
                                       uint64_t workspace_bytes, void *stream);
+/* ---------------------------------------------------------------- query / key preparation + append
+ * The steps Qsa::forward runs between the projections and the cache
+ * (crates/breccia-kernels/src/qsa/mod.rs:1607-1617), five dispatches there, one
+ * launch here:
+ *   q_norm   per-head RMSNorm of the query half of each head's `q | gate` block
+ *            (qsa_q_norm.comp:37-71; q_head_stride = 512 in the reference,
+ *            = head_dim when the projection carries no gate half)
+ *   k_norm   per-kv-head RMSNorm of k_cur (Qsa::k_norm, qsa/mod.rs:1051-1058)
+ *   rope_q / rope_k   partial NEOX rotary, pairs (j, j + n_rot/2), (cos, sin) from
+ *            the caller's table [max_pos][n_rot/2][2] f32 built as
+ *            ops/cpu.rs:103-117 builds it; the position of token t of sequence s
+ *            is pos0[s] + t, clamped into the table (ops_rope.comp:62-95)
+ *   kv_append   normalised + rotated K and plain V to cells pos0[s] + t through
+ *            the block table, binary16 by the pool's rule (qsa_kv_append.comp:137-161)
+ * q_out [n_seqs * tokens_per_seq][n_head][head_dim] (f32 or f16) is what the
+ * attention entry points take as their query.  k_cur / v_cur are not modified
+ * (the reference normalises and rotates k_cur in place).  Refuses, on the host,
+ * writes past the block table with the reference's wording. */
+BRC_API brc_status brc_qk_prepare_append(brc_pool *pool, uint32_t layer, const float *q_full_dev,
+                                         uint32_t q_head_stride, uint32_t n_head, const float *k_cur_dev,
+                                         const float *v_cur_dev, const float *q_gamma_dev,
+                                         const float *k_gamma_dev, float eps, const float *rope_table_dev,
+                                         uint32_t n_rot, uint32_t max_pos, const uint32_t *block_tables_dev,
+                                         uint32_t table_stride, const uint32_t *pos0_dev, uint32_t n_seqs,
+                                         uint32_t tokens_per_seq, uint32_t max_pos_end, void *q_out_dev,
+                                         int32_t q_out_dtype, void *stream);
+
+/* ---------------------------------------------------------------- page files
+ * The reference's state dump (crates/breccia-engine/src/graph.rs:2179-2231,
+ * BRECCIA_DUMP_STATE): the first ceil((pos + 1) / 16) pages of a block's K pool
+ * and V pool as raw device bytes, <dir>/p<pos:06>-b<block:02>-qsa_k.bin and
+ * ...-qsa_v.bin.  Its page table is the identity; here the pages are named by
+ * the sequence's block table (HOST array), so the files hold the same bytes the
+ * reference writes for the same cache contents.  brc_state_load fills the pages
+ * the table names from such a file pair (a persisted prefix).  Lab facility, as
+ * in the reference: both calls synchronise `stream`.  The directory must exist. */
+BRC_API brc_status brc_state_dump(brc_pool *pool, uint32_t layer, const uint32_t *block_table_host,
+                                  uint32_t table_len, uint32_t pos, uint32_t block, const char *dir,
+                                  void *stream);
+BRC_API brc_status brc_state_load(brc_pool *pool, uint32_t layer, const uint32_t *block_table_host,
+                                  uint32_t table_len, uint32_t pos, uint32_t block, const char *dir,
+                                  void *stream);
+
 /* One decode token over `n_layers` layers whose attention calls do not depend on
  * one another (the counterpart of brc_decode_step for the split-KV case, append
  * excluded): the local split-KV kernels of all layers are launched back to back

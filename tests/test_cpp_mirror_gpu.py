@@ -1,4 +1,4 @@
-"""BASELINE config 1 driven from C++ through include/breccia_qsa.hpp (QsaState / QsaWorkspace / Qsa with
+"""The conformance configuration driven from C++ through include/breccia_qsa.hpp (QsaState / QsaWorkspace / Qsa with
 the reference's call sequence: kv_append in chunks, one more token, topk_dense, attend, apply).  The
 program's cache pages must be bit-exact and its output in tolerance against the committed golden
 vectors of the oracle."""

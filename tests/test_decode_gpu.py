@@ -1,6 +1,6 @@
 """Paged decode attention on the GPU through the C ABI against the oracle.
 
-Tolerance (BASELINE north_star, fp32 accumulate over f16 KV): max-abs <= 2e-3, max-rel <= 1e-2.
+Tolerance (target, fp32 accumulate over f16 KV): max-abs <= 2e-3, max-rel <= 1e-2.
 The reference's own measure max|g-w|/max(|w|,1) (bar 1e-5 for its kernels) is asserted too."""
 import ctypes as C
 import hashlib
@@ -35,7 +35,7 @@ def assert_attention_close(got, want, what=""):
 
 
 def test_cfg1_conformance_against_committed_golden(cuda_device):
-    """BASELINE config 1 end to end through the mirror API: fill 1024 cells through kv_append in
+    """The conformance configuration end to end through the mirror API: fill 1024 cells through kv_append in
     256-cell chunks, append one token, one decode step; cache pages bit-exact, output in tolerance."""
     g = np.load(os.path.join(os.path.dirname(__file__), "golden", "cfg1_golden.npz"))
     table, k_ctx, v_ctx, k_new, v_new, q = cfg1_inputs()
@@ -134,7 +134,7 @@ def test_geometries(cuda_device, n_head, n_kv, hd):
 
 
 def test_cfg2_layer_at_full_size_matches_oracle_and_repeats_bit_identically(cuda_device):
-    """One layer of BASELINE config 2 at full size (32 sequences, lengths uniform in [512, 8192],
+    """One layer of the batched-decode workload at full size (32 sequences, lengths uniform in [512, 8192],
     pages scattered in a pool of 1.25x need: every CTA streams dozens of pages through its ring and
     crosses several sequence boundaries).  Output in tolerance against the oracle, and ten
     back-to-back launches give bit-identical results."""

@@ -1,6 +1,6 @@
 """Chunked-prefill attention (tcgen05 path) through the C ABI against the oracle.
 
-Tolerance (BASELINE north_star): max-abs <= 2e-3, max-rel <= 1e-2 (fp32 accumulate over f16 K/V; the
+Tolerance (target): max-abs <= 2e-3, max-rel <= 1e-2 (fp32 accumulate over f16 K/V; the
 probabilities enter the tensor cores as binary16)."""
 import ctypes as C
 

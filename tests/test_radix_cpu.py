@@ -38,7 +38,7 @@ def free(L, pool):
 
 
 def test_shared_prefix_of_64_sequences(env):
-    """BASELINE config 4's bookkeeping: one 4096-token prefix (256 pages), 64 sequences that match it:
+    """The shared-prefix workload's bookkeeping: one 4096-token prefix (256 pages), 64 sequences that match it:
     every prefix page ends with 1 (owner) + 1 (tree) + 64 references; releasing the sequences and the
     owner leaves the tree as the only holder, and eviction then frees everything."""
     L, pool, radix = env

@@ -129,7 +129,7 @@ def test_back_to_back_batches_in_both_directions_keep_every_byte(cuda_device):
         fill_pool_from_host(pool, layer, 950 + layer)
         want.append((pool.read(0, layer).copy(), pool.read(1, layer).copy()))
     tier = C.c_void_p()
-    assert L.brc_tier_create(pool.handle, 640, C.byref(tier)) == 0   # 640 slots: the cursor wraps in round 3
+    assert L.brc_tier_create(pool.handle, 640, C.byref(tier)) == 0   # 640 slots: the cursor wraps in the third pass
     where = {int(p): int(p) for p in ids}          # original page -> where its bytes are now (HBM page id)
     group_a, group_b = [int(p) for p in ids[:n_move]], [int(p) for p in ids[n_move:2 * n_move]]
     slots_a = None
