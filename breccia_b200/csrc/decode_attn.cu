@@ -323,6 +323,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     volatile uint32_t *flags = reinterpret_cast<volatile uint32_t *>(bars + 64);
     volatile uint32_t *dead_cta = flags + 1;
     float *wts = reinterpret_cast<float *>(const_cast<uint32_t *>(flags) + 8);  // [NWP][KVB * GROUP_TILE]
+    float *inv_l = wts + NW * GROUP_TILE;                                       // [KVB * GROUP_TILE] 1 / l of the merged rows
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t n_groups = p.n_kv_head / KVB;   // kv-head groups per sequence
@@ -664,6 +665,11 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             ml[h0 * 2 + 3] = l1;
         }
         const size_t slot0 = (size_t)(u + blockIdx.x) * KVB;
+        // A unit that lies wholly inside this CTA's share has no other share to meet: its rows go
+        // straight to the output (normalised and gated, or as the merged partial), with no partial slot,
+        // no fence, no ticket and no read-back.  With many short sequences most units are of this kind.
+        const bool whole = unit_first >= a && S[u + 1] <= b;
+        const uint32_t seq_of_u = u / n_groups, kv0_of_u = (u % n_groups) * KVB;
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
 #pragma unroll
@@ -693,10 +699,17 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                     wts[w * KVB * GROUP_TILE + tid] = wt;
                     L += wt * lw[w];
                 }
+                inv_l[tid] = L > 0.f ? 1.f / L : 0.f;
                 if (h < p.group) {
-                    float *ml_out = p.part_ml + ((slot0 + k2) * GROUP_TILE + h) * 2;
-                    ml_out[0] = M;
-                    ml_out[1] = L;
+                    if (!whole) {
+                        float *ml_out = p.part_ml + ((slot0 + k2) * GROUP_TILE + h) * 2;
+                        ml_out[0] = M;
+                        ml_out[1] = L;
+                    } else if (p.out_ml) {
+                        float *ml_out = p.out_ml + ((size_t)seq_of_u * p.n_head + (kv0_of_u + k2) * p.group + h) * 2;
+                        ml_out[0] = M;
+                        ml_out[1] = L;
+                    }
                 }
             }
             if (hf == 0) brc::named_bar_sync(1, NW * 32);
@@ -710,11 +723,27 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 #pragma unroll
                     for (int w = 0; w < C::NWP; ++w)
                         v += wts[w * KVB * GROUP_TILE + kh] * scratch[(w * KVB + k2) * C::SCRATCH_WARP + h * C::OPAD + d];
-                    p.part_acc[((slot0 + k2) * GROUP_TILE + h) * HD + hf * (HD / 2) + d] = v;
+                    if (!whole) {
+                        p.part_acc[((slot0 + k2) * GROUP_TILE + h) * HD + hf * (HD / 2) + d] = v;
+                    } else {
+                        const size_t row = (size_t)seq_of_u * p.n_head + (kv0_of_u + k2) * p.group + h;
+                        const uint32_t col = hf * (HD / 2) + d;
+                        if (!p.out_ml) {
+                            v *= inv_l[kh];
+                            if (p.gate) v *= sigmoid_f32(p.gate[row * p.gate_head_stride + col]);
+                        }
+                        p.out[row * HD + col] = v;
+                    }
                 }
             }
-            __threadfence();  // publish this thread's partial before the unit's ticket is taken
+            if (!whole) __threadfence();  // publish this thread's partial before the unit's ticket is taken
             brc::named_bar_sync(1, NW * 32);
+        }
+        if (whole) {
+            g0 = ge;
+            ++u;
+            while (u < n_units && S[u + 1] == S[u]) ++u;  // units without pages have no share
+            continue;
         }
 
         // ---- ticket: the CTA that completes the last share of a unit combines all of its shares
