@@ -306,7 +306,10 @@ __device__ __forceinline__ void combine_unit(const DecodeParams &p, uint32_t u, 
     }
 }
 
-template <int HD, bool Q_F32, int KVB>
+// WHOLE_FAST: compile the direct-output path for units that lie wholly inside one CTA's share.  It pays when
+// there are at least as many units as CTAs (many short sequences); with few long sequences no unit can
+// be of that kind, and leaving the path out keeps the streaming loop's code as lean as it was.
+template <int HD, bool Q_F32, int KVB, bool WHOLE_FAST>
 __global__ void __launch_bounds__(NTHREADS, 1)
     decode_partial_kernel(const __grid_constant__ CUtensorMap tm_kv, const DecodeParams p) {
     using C = Cfg<HD, KVB>;
@@ -668,7 +671,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         // A unit that lies wholly inside this CTA's share has no other share to meet: its rows go
         // straight to the output (normalised and gated, or as the merged partial), with no partial slot,
         // no fence, no ticket and no read-back.  With many short sequences most units are of this kind.
-        const bool whole = unit_first >= a && S[u + 1] <= b;
+        const bool whole = WHOLE_FAST && unit_first >= a && S[u + 1] <= b;
         const uint32_t seq_of_u = u / n_groups, kv0_of_u = (u % n_groups) * KVB;
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
@@ -878,11 +881,15 @@ uint64_t slots_for(const brc_pool *pool, uint32_t n_seqs) {
 template <int HD, bool Q_F32, int KVB>
 brc_status launch_partial(brc_pool *pool, const DecodeParams &p, uint32_t grid, uint32_t smem, cudaStream_t st) {
     static bool configured[64] = {};
-    auto kern = decode_partial_kernel<HD, Q_F32, KVB>;
     if (pool->device < 64 && !configured[pool->device]) {
-        BRC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT));
+        BRC_CUDA(cudaFuncSetAttribute(decode_partial_kernel<HD, Q_F32, KVB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)SMEM_LIMIT));
+        BRC_CUDA(cudaFuncSetAttribute(decode_partial_kernel<HD, Q_F32, KVB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)SMEM_LIMIT));
         configured[pool->device] = true;
     }
+    const bool many_units = p.n_seqs * (p.n_kv_head / KVB) >= grid;
+    auto kern = many_units ? decode_partial_kernel<HD, Q_F32, KVB, true> : decode_partial_kernel<HD, Q_F32, KVB, false>;
     brc_stage_begin(pool, BRC_STAGE_ATTN_PARTIAL, st);
     if (p.pdl) {
         cudaLaunchConfig_t cfg = {};
