@@ -2,7 +2,7 @@
 --op qsa`, crates/breccia-kernels/src/qsa/bench.rs; one JSON line per cell with the fields of its
 `OpCell`: op, case, units, bytes or flops, us, GB/s or TFLOP/s, iters).
 
-    python -m breccia_b200.bench_ops [--op prefill|append|gather|copy|fork|tier|all] [--iters N]
+    python -m breccia_b200.bench_ops [--op prefill|prepare|movers|all] [--iters N]
 
 Timing: CUDA events on the launching stream, 3 warm-up runs, the mean of `iters` runs.  Shapes are the
 benchmark configurations: prefill = 64 sequences sharing a 4096-token prefix, 256-token chunk each
@@ -110,6 +110,42 @@ def bench_prefill(iters: int, prefix: int):
     pool.release()
 
 
+def bench_prepare(iters: int):
+    """RMSNorm + rotary + append in one launch: a decode step's rows (32 sequences x 1 token) and a prefill
+    chunk's (64 x 256 tokens); the reference's head layout (q | gate blocks of 512)."""
+    import math
+
+    for n_seqs, T in ((32, 1), (64, 256)):
+        tokens = n_seqs * T
+        pages_per_seq = (4096 + T + 15) // 16
+        pool = KvPool(0, 1, N_KV, HD, n_seqs * pages_per_seq)
+        tables = np.arange(n_seqs * pages_per_seq, dtype=np.uint32).reshape(n_seqs, pages_per_seq)
+        t_dev, p_dev = dev_u32(tables), dev_u32(np.full(n_seqs, 4096))
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(5)
+        q_full = torch.randn((tokens, N_HEAD, 2 * HD), generator=gen, device="cuda")
+        k_cur = torch.randn((tokens, N_KV * HD), generator=gen, device="cuda")
+        v_cur = torch.randn((tokens, N_KV * HD), generator=gen, device="cuda")
+        gamma = torch.ones(HD, device="cuda")
+        n_rot, max_pos = 64, 8192
+        inv = torch.pow(torch.tensor(1.0e6, dtype=torch.float64), -2.0 * torch.arange(n_rot // 2, dtype=torch.float64) / n_rot)
+        ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * inv[None, :]
+        table = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).float().cuda().contiguous()
+        q_out = torch.empty((tokens, N_HEAD, HD), dtype=torch.float16, device="cuda")
+
+        def prepare():
+            _lib.call("brc_qk_prepare_append", pool.handle, 0, _ptr(q_full), 2 * HD, N_HEAD, _ptr(k_cur), _ptr(v_cur), _ptr(gamma),
+                      _ptr(gamma), 1e-6, _ptr(table), n_rot, max_pos, _ptr(t_dev), pages_per_seq, _ptr(p_dev), n_seqs, T,
+                      4096 + T, _ptr(q_out), DTYPE_F16, _stream_ptr())
+
+        us = timed(prepare, iters)
+        pool.check()
+        nbytes = tokens * (N_HEAD * HD * 4 + 2 * N_KV * HD * 4 + N_HEAD * HD * 2 + 2 * N_KV * HD * 2)
+        emit(op="qk_prepare_append", case=f"{n_seqs} sequences x {T} tokens: RMSNorm + rotary of 16 q / 2 k heads, f16 append of k and v, 1 layer",
+             units=tokens, bytes=nbytes, us=us, gbps=nbytes / us / 1e3, iters=iters)
+        pool.release()
+
+
 def bench_movers(iters: int):
     n_layers, n_pages = 12, 4096
     pool = KvPool(0, n_layers, N_KV, HD, n_pages)
@@ -171,7 +207,7 @@ def bench_movers(iters: int):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "prefill", "movers"])
+    ap.add_argument("--op", default="all", choices=["all", "prefill", "prepare", "movers"])
     ap.add_argument("--iters", type=int, default=20)
     a = ap.parse_args()
     if not torch.cuda.is_available():
@@ -180,6 +216,8 @@ def main():
     if a.op in ("all", "prefill"):
         bench_prefill(a.iters, 4096)
         bench_prefill(a.iters, 4088)   # last prefix page partial: forked copy-on-write per sequence
+    if a.op in ("all", "prepare"):
+        bench_prepare(a.iters)
     if a.op in ("all", "movers"):
         bench_movers(a.iters)
 

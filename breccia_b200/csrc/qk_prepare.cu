@@ -6,8 +6,7 @@
 //   kv_append        (qsa_kv_append.comp:137-161: f32 -> binary16 by the integer rule, scatter by block table)
 // in the order the reference runs them (crates/breccia-kernels/src/qsa/mod.rs:1607-1617): five dispatches
 // that each move a few hundred KiB become one kernel whose rows never leave the SM between the steps.
-// Arithmetic is fp32 like the shaders': y = x * (1 / sqrt(mean(x^2) + eps)) * gamma, sum of squares by the
-// same pairwise tree (element i adds element i + off, off = head_dim/2 .. 1); the rotation reads the
+// Arithmetic is fp32 like the shaders': y = x * (1 / sqrt(mean(x^2) + eps)) * gamma; the rotation reads the
 // normalised partner element from shared memory.  The stored K/V bits follow the pool's f16 rule.
 #include "brc_device.cuh"
 #include "brc_internal.h"
@@ -32,73 +31,102 @@ struct PrepareParams {
     float eps;
 };
 
-// One CTA per row: (token, query head) | (token, kv head, K) | (token, kv head, V); thread = element.
+// One warp per row: (token, query head) | (token, kv head, K) | (token, kv head, V); a lane holds HD / 32
+// elements as float4 chunks [128 c + 4 lane, + 4), so every load and store of the warp is one contiguous run.
+constexpr int PREP_WARPS = 8;
+
 template <int HD>
-__global__ void __launch_bounds__(HD) qk_prepare_kernel(const PrepareParams p) {
-    __shared__ float red[HD];
-    __shared__ float y_sm[HD];
-    const uint32_t tid = threadIdx.x;
+__global__ void __launch_bounds__(PREP_WARPS * 32) qk_prepare_kernel(const PrepareParams p, uint32_t total_rows) {
+    constexpr int CH = HD / 128;   // float4 chunks per lane
+    __shared__ float y_sm[PREP_WARPS][HD];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t row_id = blockIdx.x * PREP_WARPS + warp;
+    if (row_id >= total_rows) return;
     const uint32_t rows_per_token = p.n_head + 2u * p.n_kv_head;
-    const uint32_t tok = blockIdx.x / rows_per_token, r = blockIdx.x % rows_per_token;
+    const uint32_t tok = row_id / rows_per_token, r = row_id % rows_per_token;
     const uint32_t s = tok / p.tokens_per_seq, t = tok % p.tokens_per_seq;
     const uint32_t pos = p.pos0[s] + t;
     if (pos >= p.max_pos_end) {   // the caller's bound: skip the row, report
-        if (tid == 0) { atomicOr(p.status, BRC_DEV_BAD_POS); p.status[1] = pos; }
+        if (lane == 0) { atomicOr(p.status, BRC_DEV_BAD_POS); p.status[1] = pos; }
         return;
     }
     const bool is_q = r < p.n_head;
     const bool is_v = !is_q && r >= p.n_head + p.n_kv_head;
     const uint32_t kvh = is_q ? 0u : (r - p.n_head) % p.n_kv_head;
-
-    float x;
-    if (is_q)
-        x = p.q_full[((size_t)tok * p.n_head + r) * p.q_head_stride + tid];
-    else
-        x = (is_v ? p.v_cur : p.k_cur)[((size_t)tok * p.n_kv_head + kvh) * HD + tid];
-
-    float out = x;
-    if (!is_v) {
-        // ---- RMSNorm: the shader's tree (qsa_q_norm.comp:54-66)
-        red[tid] = x * x;
-        __syncthreads();
+    const float *src = is_q ? p.q_full + ((size_t)tok * p.n_head + r) * p.q_head_stride
+                            : (is_v ? p.v_cur : p.k_cur) + ((size_t)tok * p.n_kv_head + kvh) * HD;
+    float4 x[CH];
 #pragma unroll
-        for (uint32_t off = HD / 2; off > 0; off >>= 1) {
-            if (tid < off) red[tid] += red[tid + off];
-            __syncthreads();
+    for (int c = 0; c < CH; ++c) x[c] = __ldg(reinterpret_cast<const float4 *>(src + c * 128 + lane * 4));
+
+    if (!is_v) {
+        // ---- RMSNorm (qsa_q_norm.comp:54-70; the sum of squares by a shuffle tree instead of the shader's
+        //      shared-memory tree: fp32 either way, the order differs)
+        float ss = 0.f;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) ss += x[c].x * x[c].x + x[c].y * x[c].y + x[c].z * x[c].z + x[c].w * x[c].w;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        const float inv = 1.0f / sqrtf(ss / (float)HD + p.eps);
+        const float *gamma = is_q ? p.q_gamma : p.k_gamma;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            const float4 g = __ldg(reinterpret_cast<const float4 *>(gamma + c * 128 + lane * 4));
+            x[c] = make_float4(x[c].x * inv * g.x, x[c].y * inv * g.y, x[c].z * inv * g.z, x[c].w * inv * g.w);
+            *reinterpret_cast<float4 *>(&y_sm[warp][c * 128 + lane * 4]) = x[c];
         }
-        const float inv = 1.0f / sqrtf(red[0] / (float)HD + p.eps);
-        const float y = x * inv * (is_q ? p.q_gamma : p.k_gamma)[tid];
+        __syncwarp();
         // ---- partial NEOX rotary (ops_rope.comp:72-94); the position is clamped into the table
-        y_sm[tid] = y;
-        __syncthreads();
         const uint32_t hrot = p.n_rot / 2u;
         const uint32_t pi = pos < p.max_pos ? pos : p.max_pos - 1u;
-        out = y;
-        if (tid < hrot) {
-            const float2 cs = p.rope[(size_t)pi * hrot + tid];
-            out = y * cs.x - y_sm[tid + hrot] * cs.y;
-        } else if (tid < p.n_rot) {
-            const float2 cs = p.rope[(size_t)pi * hrot + (tid - hrot)];
-            out = y_sm[tid - hrot] * cs.y + y * cs.x;
+        const float2 *cs_row = p.rope + (size_t)pi * hrot;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            float v[4] = {x[c].x, x[c].y, x[c].z, x[c].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t i = c * 128 + lane * 4 + e;
+                if (i < hrot) {
+                    const float2 cs = __ldg(cs_row + i);
+                    v[e] = v[e] * cs.x - y_sm[warp][i + hrot] * cs.y;
+                } else if (i < p.n_rot) {
+                    const float2 cs = __ldg(cs_row + (i - hrot));
+                    v[e] = y_sm[warp][i - hrot] * cs.y + v[e] * cs.x;
+                }
+            }
+            x[c] = make_float4(v[0], v[1], v[2], v[3]);
         }
     }
     if (is_q) {
-        const size_t o = ((size_t)tok * p.n_head + r) * HD + tid;
-        if (p.q_out_f16)
-            static_cast<__half *>(p.q_out)[o] = __float2half_rn(out);
-        else
-            static_cast<float *>(p.q_out)[o] = out;
+        const size_t o = ((size_t)tok * p.n_head + r) * HD;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            if (p.q_out_f16) {
+                const __half2 lo = __floats2half2_rn(x[c].x, x[c].y), hi = __floats2half2_rn(x[c].z, x[c].w);
+                uint2 w;
+                w.x = *reinterpret_cast<const uint32_t *>(&lo);
+                w.y = *reinterpret_cast<const uint32_t *>(&hi);
+                *reinterpret_cast<uint2 *>(static_cast<__half *>(p.q_out) + o + c * 128 + lane * 4) = w;
+            } else {
+                *reinterpret_cast<float4 *>(static_cast<float *>(p.q_out) + o + c * 128 + lane * 4) = x[c];
+            }
+        }
         return;
     }
     // ---- append: cell `pos` of sequence s through its block table
-    uint32_t page = p.block_tables[(size_t)s * p.table_stride + (pos >> 4)];
+    const uint32_t page = p.block_tables[(size_t)s * p.table_stride + (pos >> 4)];
     if (page >= p.n_pages) {
-        if (tid == 0) { atomicOr(p.status, BRC_DEV_BAD_PAGE); p.status[1] = page; }
+        if (lane == 0) { atomicOr(p.status, BRC_DEV_BAD_PAGE); p.status[1] = page; }
         return;
     }
-    uint16_t *dst = reinterpret_cast<uint16_t *>(is_v ? p.v_layer : p.k_layer) +
-                    (((size_t)page * p.n_kv_head + kvh) * 16u + (pos & 15u)) * HD + tid;
-    *dst = (uint16_t)brc::f32_to_f16_bits(out);
+    uint16_t *dst = reinterpret_cast<uint16_t *>(is_v ? p.v_layer : p.k_layer) + (((size_t)page * p.n_kv_head + kvh) * 16u + (pos & 15u)) * HD;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+        uint2 w;
+        w.x = brc::pack_f16x2(x[c].x, x[c].y);
+        w.y = brc::pack_f16x2(x[c].z, x[c].w);
+        *reinterpret_cast<uint2 *>(dst + c * 128 + lane * 4) = w;
+    }
 }
 
 }  // namespace
@@ -163,10 +191,11 @@ brc_status brc_qk_prepare_append(brc_pool *pool, uint32_t layer, const float *q_
     p.eps = eps;
     cudaStream_t st = brc_stream(stream);
     brc_stage_begin(pool, BRC_STAGE_KV_APPEND, st);
+    const uint32_t grid = (uint32_t)((rows + PREP_WARPS - 1) / PREP_WARPS);
     if (hd == 256)
-        qk_prepare_kernel<256><<<(uint32_t)rows, 256, 0, st>>>(p);
+        qk_prepare_kernel<256><<<grid, PREP_WARPS * 32, 0, st>>>(p, (uint32_t)rows);
     else
-        qk_prepare_kernel<128><<<(uint32_t)rows, 128, 0, st>>>(p);
+        qk_prepare_kernel<128><<<grid, PREP_WARPS * 32, 0, st>>>(p, (uint32_t)rows);
     brc_stage_end(pool, BRC_STAGE_KV_APPEND, st);
     BRC_CUDA(cudaGetLastError());
     return BRC_OK;
