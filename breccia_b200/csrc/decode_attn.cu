@@ -739,7 +739,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                     }
                 }
             }
-            if (!whole) __threadfence();  // publish this thread's partial before the unit's ticket is taken
+            if (!whole && hf == 1) __threadfence();  // publish this thread's partial (both halves) before the unit's ticket is taken
             brc::named_bar_sync(1, NW * 32);
         }
         if (whole) {
