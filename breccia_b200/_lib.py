@@ -109,6 +109,7 @@ SIGNATURES = {
     "brc_state_load": [_vp, _u32, _u32p, _u32, _u32, _u32, C.c_char_p, _vp],
     "brc_qk_prepare_append": [_vp, _u32, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _f32, _vp, _u32, _u32, _vp, _u32, _vp, _u32, _u32,
                               _u32, _vp, _i32, _vp],
+    "brc_paged_sparse_attn": [_vp, _u32, _vp, _i32, _u32, _vp, _u32, _vp, _u32, _vp, _u32, _u32, _vp, _u32, _vp, _u32, _f32, _vp, _vp],
     "brc_timing_enable": [_vp, _i32],
     "brc_timing_read": [_vp, _i32, _u32p, C.POINTER(C.c_double)],
 }

@@ -288,6 +288,29 @@ BRC_API brc_status brc_splitkv_attend(brc_comm *comm, uint32_t layer, const void
                                       const uint32_t *seq_lens_dev, uint32_t n_seqs, uint32_t max_seq_len,
                                       float scale, float *out_dev, void *workspace_dev,
                                       uint64_t workspace_bytes, void *stream);
+/* ---------------------------------------------------------------- attention over selected blocks
+ * The reference's sparse form of Qsa::attend + Qsa::apply: per query row a list
+ * of selected 4-cell blocks, `ids [rows][max_ids]` (ascending) with `counts
+ * [rows]` entries in use; slot r * 4 + k names cell ids[r] * 4 + k, and cells
+ * beyond the row's own position are masked (crates/breccia-kernels/src/qsa/
+ * mod.rs:620-625, 1382-1580; qsa_attn_scores.comp:8-19, 62-118;
+ * qsa_attn_apply.comp:85-140; CPU statement: cpu::attend over cpu::cells_of,
+ * qsa/cpu.rs:197-257).  The lists are taken as the reference's top-k stage
+ * produces them; building them (indexer, top-k) is outside this library.
+ * Rows are grouped by sequence: row r belongs to sequence r / rows_per_seq and
+ * sits at position pos0[sequence] + r % rows_per_seq (T = 1 decode:
+ * rows_per_seq = 1; speculative verify or prefill rows: > 1, causal per row).
+ * q [rows][n_head][head_dim] f32 or f16; out [rows][n_head][head_dim] f32;
+ * gate as in brc_paged_decode_attn.  Any n_head that divides over the kv heads
+ * is accepted (no 8-heads-per-kv-head limit here).  A row whose lists select
+ * no live cell yields zeros.  No workspace. */
+BRC_API brc_status brc_paged_sparse_attn(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype,
+                                         uint32_t n_head, const float *gate_dev, uint32_t gate_head_stride,
+                                         const uint32_t *block_tables_dev, uint32_t table_stride,
+                                         const uint32_t *pos0_dev, uint32_t n_seqs, uint32_t rows_per_seq,
+                                         const uint32_t *ids_dev, uint32_t max_ids, const uint32_t *counts_dev,
+                                         uint32_t max_pos_end, float scale, float *out_dev, void *stream);
+
 /* ---------------------------------------------------------------- query / key preparation + append
  * The steps Qsa::forward runs between the projections and the cache
  * (crates/breccia-kernels/src/qsa/mod.rs:1607-1617), five dispatches there, one
