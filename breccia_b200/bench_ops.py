@@ -2,7 +2,7 @@
 --op qsa`, crates/breccia-kernels/src/qsa/bench.rs; one JSON line per cell with the fields of its
 `OpCell`: op, case, units, bytes or flops, us, GB/s or TFLOP/s, iters).
 
-    python -m breccia_b200.bench_ops [--op prefill|prepare|movers|all] [--iters N]
+    python -m breccia_b200.bench_ops [--op prefill|prepare|sparse|movers|all] [--iters N]
 
 Timing: CUDA events on the launching stream, 3 warm-up runs, the mean of `iters` runs.  Shapes are the
 benchmark configurations: prefill = 64 sequences sharing a 4096-token prefix, 256-token chunk each
@@ -146,6 +146,35 @@ def bench_prepare(iters: int):
         pool.release()
 
 
+def bench_sparse(iters: int):
+    """The reference's decode shape: one row per sequence at position ~32 k, 513 selected 4-cell blocks (2052 cells),
+    24 query heads over 2 kv heads; one sequence and a batch of 32."""
+    from .qsa import sparse_attend
+
+    n_head, ctx, n_sel = 24, 32768, 513
+    for n_seqs in (1, 32):
+        pages = ctx // 16
+        pool = KvPool(0, 1, N_KV, HD, n_seqs * pages)
+        tables = synth.permutation(3, n_seqs * pages).reshape(n_seqs, pages)
+        ids = np.stack([np.sort(synth.permutation(10 + s, ctx // 4)[:n_sel]) for s in range(n_seqs)]).astype(np.uint32)
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(6)
+        q = torch.randn((n_seqs, n_head, HD), generator=gen, device="cuda")
+        out = torch.empty((n_seqs, n_head, HD), device="cuda")
+        t_dev, p_dev, i_dev = dev_u32(tables), dev_u32(np.full(n_seqs, ctx - 1)), dev_u32(ids)
+        c_dev = dev_u32(np.full(n_seqs, n_sel))
+
+        def run():
+            sparse_attend(pool, 0, q, n_head, t_dev, p_dev, 1, i_dev, c_dev, ctx, out)
+
+        us = timed(run, iters)
+        pool.check()
+        nbytes = n_seqs * n_sel * 4 * N_KV * HD * 2 * 2      # every selected cell's K and V once per kv head
+        emit(op="paged_sparse_attn", case=f"{n_seqs} sequence(s), 1 row each, {n_sel} selected blocks = {n_sel * 4} cells of {ctx}, "
+             f"{n_head}q/{N_KV}kv hd{HD}, 1 layer", units=n_seqs, bytes=nbytes, us=us, gbps=nbytes / us / 1e3, iters=iters)
+        pool.release()
+
+
 def bench_movers(iters: int):
     n_layers, n_pages = 12, 4096
     pool = KvPool(0, n_layers, N_KV, HD, n_pages)
@@ -207,7 +236,7 @@ def bench_movers(iters: int):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "prefill", "prepare", "movers"])
+    ap.add_argument("--op", default="all", choices=["all", "prefill", "prepare", "sparse", "movers"])
     ap.add_argument("--iters", type=int, default=20)
     a = ap.parse_args()
     if not torch.cuda.is_available():
@@ -218,6 +247,8 @@ def main():
         bench_prefill(a.iters, 4088)   # last prefix page partial: forked copy-on-write per sequence
     if a.op in ("all", "prepare"):
         bench_prepare(a.iters)
+    if a.op in ("all", "sparse"):
+        bench_sparse(a.iters)
     if a.op in ("all", "movers"):
         bench_movers(a.iters)
 

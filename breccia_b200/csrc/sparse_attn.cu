@@ -79,41 +79,57 @@ __global__ void __launch_bounds__(SP_WARPS * 32) sparse_attn_kernel(const Sparse
         }
         const size_t base = (((size_t)page * p.n_kv_head + kvh) * 16u + (cell0 & 15u)) * HD + lane * EPL;
         const uint32_t n_live = min(4u, pos - cell0 + 1u);
-        for (uint32_t c = 0; c < n_live; ++c) {
-            float kf[EPL], vf[EPL];
+        // the block's four K rows and four V rows are requested before anything is consumed
+        float kf[4][EPL], vf[4][EPL];
+#pragma unroll
+        for (uint32_t c = 0; c < 4; ++c) {
+            const size_t at = (base + (size_t)min(c, n_live - 1u) * HD) * 2u;   // masked cells re-read a live one (weight 0)
             if (EPL == 8) {
-                const uint4 kb = *reinterpret_cast<const uint4 *>(p.k_layer + (base + (size_t)c * HD) * 2u);
-                const uint4 vb = *reinterpret_cast<const uint4 *>(p.v_layer + (base + (size_t)c * HD) * 2u);
+                const uint4 kb = *reinterpret_cast<const uint4 *>(p.k_layer + at);
+                const uint4 vb = *reinterpret_cast<const uint4 *>(p.v_layer + at);
                 const __half2 *kh = reinterpret_cast<const __half2 *>(&kb), *vh = reinterpret_cast<const __half2 *>(&vb);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float2 a = __half22float2(kh[e]), b = __half22float2(vh[e]);
-                    kf[2 * e] = a.x, kf[2 * e + 1] = a.y, vf[2 * e] = b.x, vf[2 * e + 1] = b.y;
+                    const float2 x = __half22float2(kh[e]), y = __half22float2(vh[e]);
+                    kf[c][2 * e] = x.x, kf[c][2 * e + 1] = x.y, vf[c][2 * e] = y.x, vf[c][2 * e + 1] = y.y;
                 }
             } else {
-                const uint2 kb = *reinterpret_cast<const uint2 *>(p.k_layer + (base + (size_t)c * HD) * 2u);
-                const uint2 vb = *reinterpret_cast<const uint2 *>(p.v_layer + (base + (size_t)c * HD) * 2u);
+                const uint2 kb = *reinterpret_cast<const uint2 *>(p.k_layer + at);
+                const uint2 vb = *reinterpret_cast<const uint2 *>(p.v_layer + at);
                 const __half2 *kh = reinterpret_cast<const __half2 *>(&kb), *vh = reinterpret_cast<const __half2 *>(&vb);
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    const float2 a = __half22float2(kh[e]), b = __half22float2(vh[e]);
-                    kf[2 * e] = a.x, kf[2 * e + 1] = a.y, vf[2 * e] = b.x, vf[2 * e + 1] = b.y;
+                    const float2 x = __half22float2(kh[e]), y = __half22float2(vh[e]);
+                    kf[c][2 * e] = x.x, kf[c][2 * e + 1] = x.y, vf[c][2 * e] = y.x, vf[c][2 * e + 1] = y.y;
                 }
             }
-            float sc = 0.f;
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) sc = fmaf(qv[e], kf[e], sc);
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, off);
-            // online softmax, base 2 (the scale carries log2 e)
-            const float m_new = fmaxf(m, sc);
-            const float f = m == -INFINITY ? 0.f : exp2f(m - m_new);
-            const float pr = exp2f(sc - m_new);
-            l = l * f + pr;
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) o[e] = fmaf(pr, vf[e], o[e] * f);
-            m = m_new;
         }
+        float sc[4];
+#pragma unroll
+        for (uint32_t c = 0; c < 4; ++c) {
+            sc[c] = 0.f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) sc[c] = fmaf(qv[e], kf[c][e], sc[c]);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+            for (uint32_t c = 0; c < 4; ++c) sc[c] += __shfl_xor_sync(0xffffffffu, sc[c], off);
+        }
+#pragma unroll
+        for (uint32_t c = 0; c < 4; ++c)
+            if (c >= n_live) sc[c] = -INFINITY;
+        // online softmax, base 2 (the scale carries log2 e); cell 0 of the block is always live
+        const float m_new = fmaxf(fmaxf(m, sc[0]), fmaxf(fmaxf(sc[1], sc[2]), sc[3]));
+        const float f = m == -INFINITY ? 0.f : exp2f(m - m_new);
+        float pr[4];
+#pragma unroll
+        for (uint32_t c = 0; c < 4; ++c) pr[c] = exp2f(sc[c] - m_new);
+        l = l * f + (pr[0] + pr[1]) + (pr[2] + pr[3]);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e)
+            o[e] = fmaf(pr[0], vf[0][e], fmaf(pr[1], vf[1][e], fmaf(pr[2], vf[2][e], fmaf(pr[3], vf[3][e], o[e] * f))));
+        m = m_new;
     }
 #pragma unroll
     for (int e = 0; e < EPL; ++e) part_o[warp][lane * EPL + e] = o[e];

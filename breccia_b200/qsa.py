@@ -342,6 +342,18 @@ class DecodeBatch:
                   self.scratch.numel(), _stream_ptr())
 
 
+def sparse_attend(pool: KvPool, layer: int, q: torch.Tensor, n_head: int, block_tables: torch.Tensor, pos0: torch.Tensor,
+                  rows_per_seq: int, ids: torch.Tensor, counts: torch.Tensor, max_pos_end: int, out: torch.Tensor,
+                  gate: torch.Tensor | None = None, gate_head_stride: int = 0) -> None:
+    """Attention over selected 4-cell blocks (reference: Qsa::attend + Qsa::apply over the `ids` / `counts` lists of
+    its top-k stage, qsa/mod.rs:620-625, 1382-1580).  q [rows, n_head, hd] f32 or f16; ids [rows, max_ids] int32;
+    counts [rows]; block_tables [n_seqs, stride]; pos0 [n_seqs]; out [rows, n_head, hd] f32."""
+    q_dtype = DTYPE_F32 if q.dtype == torch.float32 else DTYPE_F16
+    _lib.call("brc_paged_sparse_attn", pool.handle, layer, _ptr(q), q_dtype, n_head, _ptr(gate), gate_head_stride,
+              _ptr(block_tables), block_tables.shape[1], _ptr(pos0), block_tables.shape[0], rows_per_seq, _ptr(ids),
+              ids.shape[1], _ptr(counts), max_pos_end, 1.0 / math.sqrt(pool.head_dim), _ptr(out), _stream_ptr())
+
+
 def decode_partial_bytes(n_seqs: int, n_head: int, head_dim: int) -> int:
     out = C.c_uint64()
     _lib.call("brc_decode_partial_bytes", n_seqs, n_head, head_dim, C.byref(out))
