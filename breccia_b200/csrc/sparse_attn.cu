@@ -7,9 +7,9 @@
 // qsa_attn_apply.comp:85-140; the CPU statement is cpu::attend over cpu::cells_of, qsa/cpu.rs:197-257).
 // This entry point takes those lists as they are.  At most ~2052 cells per row are read, so the work is
 // small and latency-sized; the kernel is plain CUDA-core code:
-//   one CTA per (row, query head), 8 warps; warp w takes the selected blocks w, w + 8, ...; a lane holds
+//   one CTA per (row, query head), 8 or 16 warps; warp w takes the selected blocks w, w + warps, ...; a lane holds
 //   head_dim / 32 elements of q, of the running O and of each K / V row (one 16- or 8-byte load per row);
-//   the dot product is reduced by shuffles; every warp keeps an online softmax (base 2); the eight
+//   the dot product is reduced by shuffles; every warp keeps an online softmax (base 2); the warps'
 //   (m, l, O) are merged through shared memory; sigmoid(gate) last.
 // Any number of query heads per kv head is accepted (the reference's 24q / 2kv included).
 #include "brc_device.cuh"
@@ -17,7 +17,6 @@
 
 namespace {
 
-constexpr int SP_WARPS = 8;
 
 struct SparseParams {
     const void *q;                 // [rows][n_head][HD], f32 or binary16
@@ -41,7 +40,9 @@ __device__ __forceinline__ float sp_sigmoid(float x) {
     return e / (1.f + e);
 }
 
-template <int HD>
+// SP_WARPS: 16 when the launch has few CTAs (one decode row: every head's list is cut sixteen ways), 8 when rows x
+// heads already fill the GPU (more CTAs per SM, a cheaper merge).
+template <int HD, int SP_WARPS>
 __global__ void __launch_bounds__(SP_WARPS * 32) sparse_attn_kernel(const SparseParams p) {
     constexpr int EPL = HD / 32;   // elements per lane: 8 (one 16-byte load of binary16) or 4
     __shared__ float part_o[SP_WARPS][HD];
@@ -135,7 +136,7 @@ __global__ void __launch_bounds__(SP_WARPS * 32) sparse_attn_kernel(const Sparse
     for (int e = 0; e < EPL; ++e) part_o[warp][lane * EPL + e] = o[e];
     if (lane == 0) { part_ml[warp][0] = m; part_ml[warp][1] = l; }
     __syncthreads();
-    // merge the eight warps' partials: thread = output element
+    // merge the warps' partials: thread = output element
     for (uint32_t d = threadIdx.x; d < HD; d += SP_WARPS * 32) {
         float M = -INFINITY;
 #pragma unroll
@@ -211,10 +212,15 @@ brc_status brc_paged_sparse_attn(brc_pool *pool, uint32_t layer, const void *q_d
     const dim3 grid(n_head, (uint32_t)rows);
     cudaStream_t st = brc_stream(stream);
     brc_stage_begin(pool, BRC_STAGE_ATTN_PARTIAL, st);
-    if (hd == 256)
-        sparse_attn_kernel<256><<<grid, SP_WARPS * 32, 0, st>>>(p);
-    else
-        sparse_attn_kernel<128><<<grid, SP_WARPS * 32, 0, st>>>(p);
+    const uint64_t sms = (uint64_t)(pool->sm_count > 0 ? pool->sm_count : 148);
+    const bool few = rows * n_head < 2u * sms;
+    if (hd == 256) {
+        if (few) sparse_attn_kernel<256, 16><<<grid, 512, 0, st>>>(p);
+        else sparse_attn_kernel<256, 8><<<grid, 256, 0, st>>>(p);
+    } else {
+        if (few) sparse_attn_kernel<128, 16><<<grid, 512, 0, st>>>(p);
+        else sparse_attn_kernel<128, 8><<<grid, 256, 0, st>>>(p);
+    }
     brc_stage_end(pool, BRC_STAGE_ATTN_PARTIAL, st);
     BRC_CUDA(cudaGetLastError());
     return BRC_OK;
