@@ -356,11 +356,10 @@ brc_status brc_tier_lru(brc_tier *tier, uint32_t n, uint32_t *out_page_ids, uint
     std::lock_guard<std::mutex> lock(tier->mu);
     // touched pages with exactly one holder, least recently touched first
     std::vector<std::pair<uint64_t, uint32_t>> cand;
-    for (uint32_t pg = 0; pg < tier->pool->n_pages; ++pg) {
-        if (!tier->last_use[pg]) continue;
-        uint32_t rc = 0;
-        if (brc_page_refcount(tier->pool, pg, &rc) != BRC_OK || rc != 1) continue;
-        cand.emplace_back(tier->last_use[pg], pg);
+    {
+        std::lock_guard<std::mutex> pool_lock(tier->pool->mu);   // one look at all refcounts, not a lock per page
+        for (uint32_t pg = 0; pg < tier->pool->n_pages; ++pg)
+            if (tier->last_use[pg] && tier->pool->refcount[pg] == 1) cand.emplace_back(tier->last_use[pg], pg);
     }
     const uint32_t k = std::min<uint32_t>(n, (uint32_t)cand.size());
     std::partial_sort(cand.begin(), cand.begin() + k, cand.end());
