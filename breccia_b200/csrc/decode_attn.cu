@@ -83,7 +83,8 @@ struct DecodeParams {
     uint64_t v_offset;             // bytes from the K pool to the V pool
     uint32_t *status;
     uint32_t n_seqs, table_stride, max_seq_len;
-    uint32_t n_kv_head, group, n_head;
+    uint32_t n_kv_head, group, n_head;   // group = query heads per kv head handled by THIS launch (<= GROUP_TILE)
+    uint32_t group_all, head0;           // query heads per kv head in q / out, and the first of them this launch takes
     uint32_t n_pages;    // pages per layer
     uint32_t layer_row0; // first row of this layer in the TMA view
     uint32_t n_stages;
@@ -279,7 +280,7 @@ __device__ __forceinline__ void combine_unit(const DecodeParams &p, uint32_t u, 
         if (row >= n_rows) continue;
         const uint32_t k2 = row / p.group, h = row % p.group;
         const float2 ml = mls[row];
-        const uint32_t head = (kv0 + k2) * p.group + h;
+        const uint32_t head = (kv0 + k2) * p.group_all + p.head0 + h;
         const size_t o = ((size_t)s * p.n_head + head) * HD + d;
         if (to_slot) {
             const size_t slot = ((size_t)(u + i_lo) * KVB + k2) * GROUP_TILE + h;
@@ -374,7 +375,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         if (S[u + 1] != S[u]) continue;
         const uint32_t s = u / n_groups, kv0 = (u % n_groups) * KVB;
         for (uint32_t i = tid; i < KVB * p.group * HD; i += NTHREADS) {
-            const uint32_t head = kv0 * p.group + i / HD;
+            const uint32_t head = (kv0 + (i / HD) / p.group) * p.group_all + p.head0 + (i / HD) % p.group;
             p.out[((size_t)s * p.n_head + head) * HD + i % HD] = 0.f;
             if (p.out_ml && i % HD == 0) {
                 p.out_ml[((size_t)s * p.n_head + head) * 2] = -INFINITY;
@@ -524,7 +525,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         uint32_t ql[Q_F32 ? C::KSTEPS : 1][2];
         {
             const bool live = t0 < p.group;
-            const uint64_t qoff = ((uint64_t)s * p.n_head + kvh * p.group + t0) * HD + (lane & 3u) * 2u;
+            const uint64_t qoff = ((uint64_t)s * p.n_head + kvh * p.group_all + p.head0 + t0) * HD + (lane & 3u) * 2u;
 #pragma unroll
             for (int ks = 0; ks < C::KSTEPS; ++ks) {
 #pragma unroll
@@ -709,7 +710,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                         ml_out[0] = M;
                         ml_out[1] = L;
                     } else if (p.out_ml) {
-                        float *ml_out = p.out_ml + ((size_t)seq_of_u * p.n_head + (kv0_of_u + k2) * p.group + h) * 2;
+                        float *ml_out = p.out_ml + ((size_t)seq_of_u * p.n_head + (kv0_of_u + k2) * p.group_all + p.head0 + h) * 2;
                         ml_out[0] = M;
                         ml_out[1] = L;
                     }
@@ -729,7 +730,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                     if (!whole) {
                         p.part_acc[((slot0 + k2) * GROUP_TILE + h) * HD + hf * (HD / 2) + d] = v;
                     } else {
-                        const size_t row = (size_t)seq_of_u * p.n_head + (kv0_of_u + k2) * p.group + h;
+                        const size_t row = (size_t)seq_of_u * p.n_head + (kv0_of_u + k2) * p.group_all + p.head0 + h;
                         const uint32_t col = hf * (HD / 2) + d;
                         if (!p.out_ml) {
                             v *= inv_l[kh];
@@ -928,9 +929,9 @@ brc_status validate_decode(const brc_pool *pool, const char *who, uint32_t layer
         return brc_fail(BRC_ERR_INVALID, "%s: q_dtype %d is neither f32 (0) nor f16 (1)", who, q_dtype);
     if (n_head == 0 || n_head % pool->n_kv_head != 0)
         return brc_fail(BRC_ERR_INVALID, "%s: %u query heads do not divide over %u kv heads", who, n_head, pool->n_kv_head);
-    if (n_head / pool->n_kv_head > GROUP_TILE)
-        return brc_fail(BRC_ERR_UNSUPPORTED, "%s: %u query heads per kv head (kernels hold up to %d)", who,
-                        n_head / pool->n_kv_head, GROUP_TILE);
+    if (n_head / pool->n_kv_head > 4 * GROUP_TILE)
+        return brc_fail(BRC_ERR_UNSUPPORTED, "%s: %u query heads per kv head (up to %d, in passes of %d)", who,
+                        n_head / pool->n_kv_head, 4 * GROUP_TILE, GROUP_TILE);
     const uint64_t capacity = (uint64_t)table_stride * pool->page_tokens;
     if (max_seq_len > capacity)
         return brc_fail(BRC_ERR_CAPACITY, "%s would read cells up to %u but each block table holds %llu (%u pages of %u cells)",
@@ -1002,20 +1003,31 @@ brc_status run_decode(brc_pool *pool, uint32_t layer, const void *q, int32_t q_d
         p.table_stride = table_stride;
         p.max_seq_len = max_seq_len;
         p.n_kv_head = pool->n_kv_head;
-        p.group = n_head / pool->n_kv_head;
+        p.group_all = n_head / pool->n_kv_head;
         p.n_head = n_head;
         p.n_pages = pool->n_pages;
         p.layer_row0 = layer * pool->n_pages * pool->n_kv_head * pool->page_tokens;
         p.n_stages = n_stages;
         p.scale_log2 = scale * 1.4426950408889634f;
-        brc_status rc;
-        if (hd == 256)
-            rc = q_dtype == BRC_DTYPE_F32 ? launch_partial_kvb<256, true>(pool, p, grid, smem, st)
-                                          : launch_partial_kvb<256, false>(pool, p, grid, smem, st);
-        else
-            rc = q_dtype == BRC_DTYPE_F32 ? launch_partial_kvb<128, true>(pool, p, grid, smem, st)
-                                          : launch_partial_kvb<128, false>(pool, p, grid, smem, st);
-        if (rc != BRC_OK) return rc;
+        // A tile holds GROUP_TILE query heads per kv head.  More than that (the reference model has 12) are
+        // taken in passes of GROUP_TILE heads, each streaming the cache again: correct, at that price.  The
+        // passes share one bank of partials and counters, so they run strictly one after the other, and
+        // only the first one appends.
+        const uint32_t passes = (p.group_all + GROUP_TILE - 1) / GROUP_TILE;
+        if (passes > 1) p.pdl = 0;
+        for (uint32_t pass = 0; pass < passes; ++pass) {
+            p.head0 = pass * GROUP_TILE;
+            p.group = std::min<uint32_t>(GROUP_TILE, p.group_all - p.head0);
+            if (pass > 0) p.k_new = p.v_new = nullptr;
+            brc_status rc;
+            if (hd == 256)
+                rc = q_dtype == BRC_DTYPE_F32 ? launch_partial_kvb<256, true>(pool, p, grid, smem, st)
+                                              : launch_partial_kvb<256, false>(pool, p, grid, smem, st);
+            else
+                rc = q_dtype == BRC_DTYPE_F32 ? launch_partial_kvb<128, true>(pool, p, grid, smem, st)
+                                              : launch_partial_kvb<128, false>(pool, p, grid, smem, st);
+            if (rc != BRC_OK) return rc;
+        }
     }
     return BRC_OK;
 }

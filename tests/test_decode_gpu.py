@@ -126,7 +126,9 @@ def test_reference_geometry_shapes_2062_cells_with_gate(cuda_device):
     pool.release()
 
 
-@pytest.mark.parametrize("n_head,n_kv,hd", [(16, 2, 256), (8, 2, 256), (4, 4, 256), (32, 4, 128), (6, 2, 128), (8, 1, 256), (12, 3, 128)])
+@pytest.mark.parametrize("n_head,n_kv,hd", [(16, 2, 256), (8, 2, 256), (4, 4, 256), (32, 4, 128), (6, 2, 128), (8, 1, 256), (12, 3, 128),
+                                            (24, 2, 256),    # the reference model's heads: 12 per kv head, two passes of 8 + 4
+                                            (20, 1, 128)])   # 20 per kv head: three passes, one kv head per unit
 def test_geometries(cuda_device, n_head, n_kv, hd):
     pool, _, _, got, want = _batch_case(n_head, n_kv, hd, [333, 48, 1000], seed=60 + n_head, n_layers=2, layer=1)
     assert_attention_close(got, want, f"{n_head}q/{n_kv}kv hd{hd}")
@@ -376,7 +378,7 @@ def test_decode_refusals(cuda_device):
     assert b"cells up to 65" in L.brc_last_error()
     assert L.brc_paged_decode_attn(*args(layer=3)) == _lib.ERR_INVALID
     assert L.brc_paged_decode_attn(*args(nh=15)) == _lib.ERR_INVALID
-    assert L.brc_paged_decode_attn(*args(nh=24)) == _lib.ERR_UNSUPPORTED
+    assert L.brc_paged_decode_attn(*args(nh=80)) == _lib.ERR_UNSUPPORTED   # 40 per kv head: more than four passes of 8
     assert L.brc_paged_decode_attn(*args(dt=9)) == _lib.ERR_INVALID
     assert L.brc_paged_decode_attn(*args(wsb=16)) == _lib.ERR_INVALID
     # a length beyond the caller's bound and a table entry beyond the pool are caught on the device
@@ -389,4 +391,38 @@ def test_decode_refusals(cuda_device):
     assert L.brc_paged_decode_attn(*args()) == 0
     with pytest.raises(_lib.BrcError, match="page id >= n_pages"):
         pool.check()
+    pool.release()
+
+
+def test_twelve_heads_per_kv_head_in_two_passes(cuda_device):
+    """The reference model's 24q / 2kv: the kernels take 8 query heads per kv head at a time, so the launch runs
+    two passes (heads 0-7 and 8-11 of each kv head).  f32 query with gate, the partial form, and a decode step
+    whose fused append must happen once."""
+    n_head, n_kv, hd = 24, 2, 256
+    lens = np.array([700, 33, 2062])
+    pool, batch, qd, got, want = _batch_case(n_head, n_kv, hd, lens, seed=140, gate=True, q_dtype=DTYPE_F32)
+    assert_attention_close(got, want, "24q/2kv with gate")
+    nbytes = decode_partial_bytes(lens.size, n_head, hd)
+    part = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    batch.partial(0, qd, part)
+    out = torch.empty((lens.size, n_head, hd), device="cuda")
+    decode_combine(0, part, 1, nbytes, lens.size, n_head, hd, out)
+    pool.check()
+    k, v = pool.read(0, 0).reshape(-1), pool.read(1, 0).reshape(-1)
+    tables = batch.block_tables.cpu().numpy().astype(np.uint32)
+    want_plain, _ = oracle.decode_batch(k, v, tables, lens, qd.cpu().numpy(), n_head, n_kv, hd)
+    assert_attention_close(out.cpu().numpy(), want_plain, "24q/2kv partial form")
+    # one decode step: the new cell is appended by the first pass only and seen by both
+    k_new = torch.from_numpy(synth.normal(141, lens.size * n_kv * hd, 0.5).reshape(1, lens.size, n_kv * hd)).cuda()
+    v_new = torch.from_numpy(synth.normal(142, lens.size * n_kv * hd, 0.5).reshape(1, lens.size, n_kv * hd)).cuda()
+    step_out = torch.empty((1, lens.size, n_head, hd), device="cuda")
+    batch.step(qd.unsqueeze(0).contiguous(), k_new, v_new, step_out)
+    pool.check()
+    k2, v2 = pool.read(0, 0).reshape(-1), pool.read(1, 0).reshape(-1)
+    want_step, _ = oracle.decode_batch(k2, v2, tables, lens + 1, qd.cpu().numpy(), n_head, n_kv, hd)
+    assert_attention_close(step_out[0].cpu().numpy(), want_step, "24q/2kv decode step")
+    kb = oracle.f32_to_f16_bits_np(k_new.cpu().numpy()).reshape(lens.size, n_kv, hd)
+    kp = k2.reshape(-1, n_kv, 16, hd)
+    for s, n in enumerate(lens):
+        assert np.array_equal(kp[tables[s, n // 16], :, n % 16, :], kb[s])
     pool.release()
