@@ -179,7 +179,9 @@ BRC_API brc_status brc_seq_fork(brc_pool *pool, const uint32_t *parent_table, ui
  * sequences: out[s,h,:] = sigmoid(gate[s,h,:]) * softmax_c(scale * q[s,h].k_c) . v_c
  * over cells c < seq_lens_dev[s] (the dense selection `topk_dense` emits), with
  * kv head = h * n_kv_head / n_head.  Cells at or past seq_len are never read
- * into the result, whatever the pool holds there.
+ * into the result, whatever the pool holds there.  Up to 8 query heads per kv
+ * head share one stream of the cache; more (up to 32, e.g. the reference
+ * model's 12) are taken in passes of 8, each streaming the cache again.
  *
  *   q_dev     [n_seqs][n_head][head_dim], f16 bits or f32 (reference: f32)
  *   gate_dev  NULL, or f32 with gate[s,h,d] at gate_dev[(s*n_head + h)*gate_head_stride + d]
