@@ -240,7 +240,7 @@ def run_native(args):
     k_h = k_new.cpu().pin_memory()
     v_h = v_new.cpu().pin_memory()
     out_h = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-    staging = {"q": torch.empty_like(q), "k": torch.empty_like(k_new), "v": torch.empty_like(v_new), "out": out}
+    staging = batch.host_staging(N_LAYERS)
     e2e_steps = steps
     ms_e2e_total, _ = timed(lambda: batch.step_host(q_h, k_h, v_h, out_h, staging), 3, e2e_steps)
     ms_e2e = ms_e2e_total / e2e_steps

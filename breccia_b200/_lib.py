@@ -80,6 +80,11 @@ SIGNATURES = {
     "brc_decode_combine": [_i32, _vp, _u32, _u64, _u32, _u32, _u32, _vp, _u32, _vp, _vp],
     "brc_decode_step": [_vp, _u32, _u32, _vp, _u32, _vp, _vp, _u32, _u32, _vp, _i32, _u64, _u32, _vp, _vp, _i32, _u64,
                         _vp, _u32, _u64, _f32, _vp, _u64, _vp, _u64, _vp],
+    "brc_decode_step_part": [_vp, _u32, _u32, _u32, _u32, _vp, _u32, _vp, _vp, _u32, _u32, _vp, _i32, _u64, _u32, _vp, _vp,
+                             _i32, _u64, _vp, _u32, _u64, _f32, _vp, _u64, _vp, _u64, _vp],
+    "brc_decode_step_host_staging_bytes": [_vp, _u32, _u32, _u32, _i32, _i32, _u64p],
+    "brc_decode_step_host": [_vp, _u32, _u32, _u32, _vp, _u32, _vp, _vp, _u32, _u32, _vp, _i32, _u32, _vp, _vp, _i32, _f32,
+                             _vp, _vp, _u64, _vp, _u64, _vp],
     "brc_paged_prefill_attn": [_vp, _u32, _vp, _i32, _u32, _vp, _u32, _vp, _u32, _vp, _u32, _u32, _u32, _f32, _vp, _vp],
     "brc_radix_create": [_vp, _vpp],
     "brc_radix_destroy": [_vp],

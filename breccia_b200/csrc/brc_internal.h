@@ -58,6 +58,12 @@ struct brc_pool {
         std::vector<cudaEvent_t> spare;       // reusable events
     } stages[BRC_STAGE_COUNT];
 
+    // brc_decode_step_host: an upload and a download stream and one event pair per part, made on first use
+    static constexpr uint32_t HOST_PARTS_MAX = 8;
+    cudaStream_t host_up = nullptr, host_down = nullptr;
+    cudaEvent_t host_uploaded[HOST_PARTS_MAX] = {}, host_computed[HOST_PARTS_MAX] = {};
+    cudaEvent_t host_all_down = nullptr;
+
     // allocator
     mutable std::mutex mu;
     std::vector<uint32_t> refcount;

@@ -237,6 +237,11 @@ brc_status brc_pool_destroy(brc_pool *pool) {
             for (cudaEvent_t e : st.end) cudaEventDestroy(e);
             for (cudaEvent_t e : st.spare) cudaEventDestroy(e);
         }
+        if (pool->host_up) cudaStreamDestroy(pool->host_up);
+        if (pool->host_down) cudaStreamDestroy(pool->host_down);
+        for (cudaEvent_t e : pool->host_uploaded) if (e) cudaEventDestroy(e);
+        for (cudaEvent_t e : pool->host_computed) if (e) cudaEventDestroy(e);
+        if (pool->host_all_down) cudaEventDestroy(pool->host_all_down);
     }
     delete pool;
     return BRC_OK;

@@ -319,17 +319,45 @@ class DecodeBatch:
                   k_new.stride(0) * k_new.element_size(), None, 0, 0, self.scale, _ptr(out),
                   out.stride(0) * out.element_size(), _ptr(self.scratch), self.scratch.numel(), _stream_ptr())
 
+    def step_part(self, first: int, count: int, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
+                  out: torch.Tensor, layer0: int = 0, kv_dtype: int = DTYPE_F32) -> None:
+        """Layers [first, first + count) of the step `step` would run on the same tensors
+        (brc_decode_step_part); the part with first == 0 advances the positions."""
+        if first == 0:
+            if int(self.seq_lens_host.max()) + 1 > self.capacity:
+                raise BrcError(_lib.ERR_CAPACITY, f"decode step would write cell {int(self.seq_lens_host.max())} but "
+                                                  f"each block table holds {self.capacity}")
+            self.seq_lens_host += 1
+        _lib.call("brc_decode_step_part", self.pool.handle, layer0, q.shape[0], first, count, _ptr(self.block_tables),
+                  self.table_stride, _ptr(self.seq_lens), _ptr(self.pos0), self.n_seqs, int(self.seq_lens_host.max()),
+                  _ptr(q), self.q_dtype, q.stride(0) * q.element_size(), self.n_head, _ptr(k_new), _ptr(v_new), kv_dtype,
+                  k_new.stride(0) * k_new.element_size(), None, 0, 0, self.scale, _ptr(out),
+                  out.stride(0) * out.element_size(), _ptr(self.scratch), self.scratch.numel(), _stream_ptr())
+
+    def host_staging(self, n_layers: int, kv_dtype: int = DTYPE_F32) -> torch.Tensor:
+        """The device buffer step_host needs for steps of n_layers layers."""
+        need = C.c_uint64()
+        _lib.call("brc_decode_step_host_staging_bytes", self.pool.handle, n_layers, self.n_seqs, self.n_head, self.q_dtype,
+                  kv_dtype, C.byref(need))
+        return torch.empty(need.value, dtype=torch.uint8, device=self.seq_lens.device)
+
     def step_host(self, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor, out_host: torch.Tensor,
-                  staging: dict, layer0: int = 0) -> None:
-        """The same step for a caller whose activations live in (pinned) host memory: uploads this
-        step's q / k / v, runs the step, downloads the attention output and waits for it.
-        `staging` holds the device-side buffers (keys q, k, v, out), allocated once by the caller."""
-        staging["q"].copy_(q_host, non_blocking=True)
-        staging["k"].copy_(k_host, non_blocking=True)
-        staging["v"].copy_(v_host, non_blocking=True)
-        self.step(staging["q"], staging["k"], staging["v"], staging["out"], layer0)
-        out_host.copy_(staging["out"], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+                  staging: torch.Tensor, layer0: int = 0, parts: int = 3, kv_dtype: int = DTYPE_F32) -> None:
+        """The same step for a caller whose activations live in (pinned) host memory, one call into the
+        library (brc_decode_step_host): q / k / v go up and the attention output comes back in `parts`
+        groups of layers, the copies of one group hidden behind the kernels of its neighbours.  Returns
+        when out_host is complete.  `staging` comes from host_staging()."""
+        for t in (q_host, k_host, v_host, out_host):
+            if t.is_cuda or not t.is_contiguous():
+                raise ValueError("step_host takes contiguous host tensors")
+        if int(self.seq_lens_host.max()) + 1 > self.capacity:
+            raise BrcError(_lib.ERR_CAPACITY, f"decode step would write cell {int(self.seq_lens_host.max())} but each "
+                                              f"block table holds {self.capacity}")
+        self.seq_lens_host += 1
+        _lib.call("brc_decode_step_host", self.pool.handle, layer0, q_host.shape[0], parts, _ptr(self.block_tables),
+                  self.table_stride, _ptr(self.seq_lens), _ptr(self.pos0), self.n_seqs, int(self.seq_lens_host.max()),
+                  _ptr(q_host), self.q_dtype, self.n_head, _ptr(k_host), _ptr(v_host), kv_dtype, self.scale, _ptr(out_host),
+                  _ptr(staging), staging.numel(), _ptr(self.scratch), self.scratch.numel(), _stream_ptr())
 
     def reset_lengths(self, seq_lens) -> None:
         self.seq_lens_host = np.asarray(seq_lens, np.int64).copy()

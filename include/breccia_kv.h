@@ -405,6 +405,49 @@ BRC_API brc_status brc_decode_step(brc_pool *pool, uint32_t layer0, uint32_t n_l
                                    uint64_t out_layer_stride_bytes, void *workspace_dev, uint64_t workspace_bytes,
                                    void *stream);
 
+/* Layers [first, first + count) of the step brc_decode_step would run with the same
+ * remaining arguments (every pointer and stride is the whole step's).  The part with
+ * first == 0 advances the positions, so the parts of one step go to one stream, that
+ * part first.  For a caller whose activations arrive from the host layer by layer
+ * (the engine records its layers in order, crates/breccia-engine/src/graph.rs:5899-5966):
+ * it can upload the next layers' q / k / v and download the finished layers' output
+ * on other streams while this part computes. */
+BRC_API brc_status brc_decode_step_part(brc_pool *pool, uint32_t layer0, uint32_t n_layers, uint32_t first,
+                                        uint32_t count, const uint32_t *block_tables_dev, uint32_t table_stride,
+                                        uint32_t *seq_lens_dev, uint32_t *pos0_dev, uint32_t n_seqs,
+                                        uint32_t max_seq_len_after, const void *q_dev, int32_t q_dtype,
+                                        uint64_t q_layer_stride_bytes, uint32_t n_head, const void *k_new_dev,
+                                        const void *v_new_dev, int32_t kv_dtype, uint64_t kv_layer_stride_bytes,
+                                        const float *gate_dev, uint32_t gate_head_stride,
+                                        uint64_t gate_layer_stride_bytes, float scale, float *out_dev,
+                                        uint64_t out_layer_stride_bytes, void *workspace_dev,
+                                        uint64_t workspace_bytes, void *stream);
+
+/* The same step for a caller whose activations live in HOST memory (pinned, or the
+ * copies are synchronous): q_host [n_layers][n_seqs][n_head][head_dim] (q_dtype),
+ * k_new_host / v_new_host [n_layers][n_seqs][n_kv_head*head_dim] (kv_dtype),
+ * out_host [n_layers][n_seqs][n_head][head_dim] f32, all contiguous.  The layers go
+ * in `parts` groups (1..8, clamped to n_layers): uploads run ahead on a stream of
+ * the pool's own, each group's kernels go to `stream` (brc_decode_step_part), and
+ * each group's output leaves on a third stream while the next group computes, so
+ * only the first upload and the last download are not hidden behind the attention
+ * kernels.  `staging_dev` (256-byte aligned, at least
+ * brc_decode_step_host_staging_bytes()) holds the device copies and belongs to the
+ * call while it runs.  Returns when out_host is complete; `stream` is ordered after
+ * the downloads.  Positions, block tables and the workspace are device-resident as
+ * for brc_decode_step. */
+BRC_API brc_status brc_decode_step_host_staging_bytes(const brc_pool *pool, uint32_t n_layers, uint32_t n_seqs,
+                                                      uint32_t n_head, int32_t q_dtype, int32_t kv_dtype,
+                                                      uint64_t *out_bytes);
+BRC_API brc_status brc_decode_step_host(brc_pool *pool, uint32_t layer0, uint32_t n_layers, uint32_t parts,
+                                        const uint32_t *block_tables_dev, uint32_t table_stride,
+                                        uint32_t *seq_lens_dev, uint32_t *pos0_dev, uint32_t n_seqs,
+                                        uint32_t max_seq_len_after, const void *q_host, int32_t q_dtype,
+                                        uint32_t n_head, const void *k_new_host, const void *v_new_host,
+                                        int32_t kv_dtype, float scale, float *out_host, void *staging_dev,
+                                        uint64_t staging_bytes, void *workspace_dev, uint64_t workspace_bytes,
+                                        void *stream);
+
 /* ---------------------------------------------------------------- chunked-prefill attention (tensor cores)
  * Replaces the reference's T >= 16 path: qsa_attn_scores_gqa.comp + ops_softmax.comp
  * + qsa_attn_apply_gqa.comp, tiled from Qsa::forward

@@ -212,6 +212,73 @@ def test_decode_step_appends_bit_exactly_and_attends(cuda_device, kv_f16):
     pool.release()
 
 
+@pytest.mark.parametrize("parts", [1, 2, 5])
+def test_step_from_host_buffers_in_parts_equals_the_device_step(cuda_device, parts):
+    """brc_decode_step_host (pinned host q / k / v in, output back to the host, layers in `parts` groups
+    with uploads and downloads on streams of their own) against brc_decode_step on a twin pool: outputs,
+    both pools and the advanced lengths must be bit-identical, two steps in a row."""
+    n_head, n_kv, hd, n_layers = 16, 2, 256, 5
+    lens = np.array([16, 5, 700, 0, 31, 255])
+    tables, n_pool = synth.scattered_tables(56, lens, pool_factor=1.4, extra_tokens=4)
+    pools = [KvPool(0, n_layers, n_kv, hd, n_pool) for _ in range(2)]
+    for pool in pools:
+        for layer in range(n_layers):
+            fill_pool_from_host(pool, layer, 520 + 2 * layer)
+    dev_batch, host_batch = DecodeBatch(pools[0], n_head, tables, lens), DecodeBatch(pools[1], n_head, tables, lens)
+    shape_q, shape_kv = (n_layers, lens.size, n_head, hd), (n_layers, lens.size, n_kv * hd)
+    staging = host_batch.host_staging(n_layers)
+    out_h = torch.empty(shape_q).pin_memory()
+    for step in range(2):
+        q_h = torch.from_numpy(oracle.to_f16(synth.normal(610 + step, int(np.prod(shape_q)))).reshape(shape_q)).half().pin_memory()
+        k_h = torch.from_numpy(synth.normal(710 + step, int(np.prod(shape_kv)), 0.5).reshape(shape_kv)).pin_memory()
+        v_h = torch.from_numpy(synth.normal(810 + step, int(np.prod(shape_kv)), 0.5).reshape(shape_kv)).pin_memory()
+        want = torch.full(shape_q, float("nan"), device="cuda")
+        dev_batch.step(q_h.cuda(), k_h.cuda(), v_h.cuda(), want)
+        out_h.fill_(float("nan"))
+        host_batch.step_host(q_h, k_h, v_h, out_h, staging, parts=parts)
+        for pool in pools:
+            pool.check()
+        assert torch.equal(out_h, want.cpu()), f"step {step}"
+        for layer in range(n_layers):
+            for which in (0, 1):
+                assert np.array_equal(pools[0].read(which, layer), pools[1].read(which, layer)), f"pool {which} layer {layer}"
+    assert torch.equal(dev_batch.seq_lens, host_batch.seq_lens)
+    assert host_batch.seq_lens_host.tolist() == (lens + 2).tolist()
+    for pool in pools:
+        pool.release()
+
+
+def test_step_in_two_parts_on_one_stream_equals_the_whole_step(cuda_device):
+    """brc_decode_step_part twice (layers 0-1, then 2-4) against brc_decode_step on a twin pool; a part
+    that reaches past the step's layers is refused."""
+    n_head, n_kv, hd, n_layers = 16, 2, 256, 5
+    lens = np.array([40, 3, 333, 0])
+    tables, n_pool = synth.scattered_tables(57, lens, pool_factor=1.4, extra_tokens=4)
+    pools = [KvPool(0, n_layers, n_kv, hd, n_pool) for _ in range(2)]
+    for pool in pools:
+        for layer in range(n_layers):
+            fill_pool_from_host(pool, layer, 540 + 2 * layer)
+    whole, split = DecodeBatch(pools[0], n_head, tables, lens), DecodeBatch(pools[1], n_head, tables, lens)
+    q = torch.from_numpy(oracle.to_f16(synth.normal(620, n_layers * lens.size * n_head * hd))).cuda().half().reshape(n_layers, lens.size, n_head, hd)
+    kn = torch.from_numpy(synth.normal(720, n_layers * lens.size * n_kv * hd, 0.5)).cuda().reshape(n_layers, lens.size, n_kv * hd)
+    vn = torch.from_numpy(synth.normal(820, n_layers * lens.size * n_kv * hd, 0.5)).cuda().reshape(n_layers, lens.size, n_kv * hd)
+    want, got = torch.full(q.shape, float("nan"), device="cuda"), torch.full(q.shape, float("nan"), device="cuda")
+    whole.step(q, kn, vn, want)
+    split.step_part(0, 2, q, kn, vn, got)
+    split.step_part(2, 3, q, kn, vn, got)
+    for pool in pools:
+        pool.check()
+    assert torch.equal(got, want)
+    assert torch.equal(whole.seq_lens, split.seq_lens)
+    for layer in range(n_layers):
+        assert np.array_equal(pools[0].read(0, layer), pools[1].read(0, layer))
+    with pytest.raises(_lib.BrcError) as err:
+        split.step_part(3, 3, q, kn, vn, got)
+    assert err.value.code == _lib.ERR_INVALID
+    for pool in pools:
+        pool.release()
+
+
 def test_nan_poison_outside_live_cells_never_reaches_the_output(cuda_device):
     """Unowned pages and the cells past each sequence end hold NaN (the reference's poison flag,
     qsa/mod.rs:509-523): the output must equal the oracle's, which never looks there."""
