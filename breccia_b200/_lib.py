@@ -82,8 +82,10 @@ SIGNATURES = {
                         _vp, _u32, _u64, _f32, _vp, _u64, _vp, _u64, _vp],
     "brc_decode_step_part": [_vp, _u32, _u32, _u32, _u32, _vp, _u32, _vp, _vp, _u32, _u32, _vp, _i32, _u64, _u32, _vp, _vp,
                              _i32, _u64, _vp, _u32, _u64, _f32, _vp, _u64, _vp, _u64, _vp],
+    "brc_pool_create_q8v": [_i32, _u32, _u32, _u32, _u32, _u32, _vpp],
+    "brc_pool_v_layout": [_vp, C.POINTER(C.c_int32)],
     "brc_decode_step_host_staging_bytes": [_vp, _u32, _u32, _u32, _i32, _i32, _u64p],
-    "brc_decode_step_host": [_vp, _u32, _u32, _u32, _vp, _u32, _vp, _vp, _u32, _u32, _vp, _i32, _u32, _vp, _vp, _i32, _f32,
+    "brc_decode_step_host": [_vp, _u32, _u32, _u32, _u32, _vp, _u32, _vp, _vp, _u32, _u32, _vp, _i32, _u32, _vp, _vp, _i32, _f32,
                              _vp, _vp, _u64, _vp, _u64, _vp],
     "brc_paged_prefill_attn": [_vp, _u32, _vp, _i32, _u32, _vp, _u32, _vp, _u32, _vp, _u32, _u32, _u32, _f32, _vp, _vp],
     "brc_radix_create": [_vp, _vpp],

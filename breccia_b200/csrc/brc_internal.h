@@ -36,6 +36,10 @@ struct brc_pool {
     uint64_t layer_bytes = 0;       // K (or V) bytes of one layer
     uint8_t *k_base = nullptr;      // [n_layers][n_pages][n_kv][page_tokens][head_dim] f16
     uint8_t *v_base = nullptr;      // same allocation as k_base, `layer_bytes * n_layers` further on
+    // V page bodies: binary16 like K, or q8_0 (blocks of 32 values: one f32 scale + 32 signed bytes, 36 B;
+    // row = head_dim / 32 blocks; rows in the same order as the binary16 layout)
+    bool v_q8 = false;
+    uint64_t v_layer_bytes = 0;     // V bytes of one layer: layer_bytes, or 9/16 of it for q8_0
     uint32_t *status_dev = nullptr; // device check word
     uint32_t *status_host = nullptr;  // pinned mirror
     uint32_t *ids_dev = nullptr;    // small staging for host-provided id lists
@@ -79,6 +83,16 @@ brc_status brc_fail(brc_status code, const char *fmt, ...) __attribute__((format
         if (_e != cudaSuccess)                                                                   \
             return brc_fail(BRC_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), \
                             __FILE__, __LINE__);                                                 \
+    } while (0)
+
+// Entry points whose kernels read or write V as binary16 refuse a pool that stores it as q8_0.
+#define BRC_REFUSE_Q8V(pool, who)                                                                                  \
+    do {                                                                                                           \
+        if ((pool)->v_q8)                                                                                          \
+            return brc_fail(BRC_ERR_UNSUPPORTED,                                                                   \
+                            "%s: this pool stores V as q8_0; built for it are brc_kv_append (f32 sources), "      \
+                            "brc_paged_sparse_attn and brc_pool_read / brc_pool_write",                            \
+                            who);                                                                                  \
     } while (0)
 
 // RAII: make the pool's device current for the duration of a call, restore after.

@@ -922,6 +922,7 @@ brc_status validate_decode(const brc_pool *pool, const char *who, uint32_t layer
                            uint32_t n_head, const uint32_t *bt, uint32_t table_stride, const uint32_t *lens,
                            uint32_t n_seqs, uint32_t max_seq_len, const void *out, const void *ws, uint64_t ws_bytes) {
     if (!pool) return brc_fail(BRC_ERR_INVALID, "%s: pool is NULL", who);
+    BRC_REFUSE_Q8V(pool, who);
     if (pool->device < 0 || !pool->has_tma)
         return brc_fail(BRC_ERR_CUDA, "%s: this pool holds bookkeeping only (no device memory); compute calls need a GPU pool", who);
     if (layer >= pool->n_layers) return brc_fail(BRC_ERR_INVALID, "%s: layer %u but the pool has %u", who, layer, pool->n_layers);
@@ -1214,6 +1215,7 @@ brc_status brc_paged_decode_attn_static(brc_pool *pool, uint32_t layer, const vo
                                         const uint32_t *seq_lens_dev, uint32_t n_seqs, uint32_t max_seq_len, float scale,
                                         float *out_dev, void *stream) {
     if (!pool) return brc_fail(BRC_ERR_INVALID, "brc_paged_decode_attn_static: pool is NULL");
+    BRC_REFUSE_Q8V(pool, "brc_paged_decode_attn_static");
     if (pool->device < 0 || !pool->has_tma)
         return brc_fail(BRC_ERR_CUDA, "brc_paged_decode_attn_static: this pool holds bookkeeping only (no device memory)");
     uint64_t need = 0;

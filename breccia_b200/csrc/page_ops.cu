@@ -36,7 +36,11 @@ __device__ __forceinline__ uint32_t seq_of_token(const uint32_t *cu, uint32_t n,
 // The address rule is the reference's (shaders/qsa_kv_append.comp:137-161):
 //   cell = pos0 + t, page = table[cell / page_tokens],
 //   element = ((page * n_kv + kvh) * page_tokens + cell % page_tokens) * head_dim + d.
-template <bool SRC_F32>
+// V_Q8: the V row is stored as q8_0 instead (store rule of shaders/qsa_kv_append.comp:117-133): per block of
+// 32 values scale = amax / 127 (1 for an all-zero block), q = round-half-away(clamp(x / scale, +-127)), taken
+// from the f32 value; a block is one f32 scale then 32 signed bytes.  The four threads that share a block each
+// read all of it for the maximum (the repeats hit L1) and quantise their own eight values.
+template <bool SRC_F32, bool V_Q8>
 __global__ void __launch_bounds__(256) kv_append_kernel(const AppendParams p) {
     const uint32_t vec_per_row = p.head_dim / 8u;
     const uint32_t vec_per_token = p.n_kv_head * vec_per_row;
@@ -68,6 +72,27 @@ __global__ void __launch_bounds__(256) kv_append_kernel(const AppendParams p) {
         const uint64_t dst = (row * p.head_dim + (uint64_t)v8 * 8u) * 2u;  // bytes
         const uint64_t src = ((uint64_t)tok * p.n_kv_head + kvh) * p.head_dim + (uint64_t)v8 * 8u;  // elements
         uint4 ko, vo;
+        if (V_Q8) {
+            const float *vrow = static_cast<const float *>(p.v_src) + src - (uint64_t)(v8 & 3u) * 8u;   // the block's 32 values
+            float amax = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float4 x = __ldg(reinterpret_cast<const float4 *>(vrow) + j);
+                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
+            }
+            const float scale = amax > 0.f ? __fdiv_rn(amax, 127.f) : 1.f;
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(vrow) + 2u * (v8 & 3u));
+            const float4 b = __ldg(reinterpret_cast<const float4 *>(vrow) + 2u * (v8 & 3u) + 1);
+            auto quant = [scale](float x) {
+                return (uint32_t)(int32_t)roundf(fminf(fmaxf(__fdiv_rn(x, scale), -127.f), 127.f)) & 0xffu;
+            };
+            const uint32_t w0 = quant(a.x) | (quant(a.y) << 8) | (quant(a.z) << 16) | (quant(a.w) << 24);
+            const uint32_t w1 = quant(b.x) | (quant(b.y) << 8) | (quant(b.z) << 16) | (quant(b.w) << 24);
+            uint32_t *blk = reinterpret_cast<uint32_t *>(p.v_layer) + (row * (p.head_dim / 32u) + (v8 >> 2)) * 9u;
+            if ((v8 & 3u) == 0u) blk[0] = __float_as_uint(scale);
+            blk[1u + 2u * (v8 & 3u)] = w0;
+            blk[2u + 2u * (v8 & 3u)] = w1;
+        }
         if (SRC_F32) {
             const float4 *ks = reinterpret_cast<const float4 *>(static_cast<const float *>(p.k_src) + src);
             const float4 *vs = reinterpret_cast<const float4 *>(static_cast<const float *>(p.v_src) + src);
@@ -91,7 +116,7 @@ __global__ void __launch_bounds__(256) kv_append_kernel(const AppendParams p) {
             vo = make_uint4(flush(vo.x), flush(vo.y), flush(vo.z), flush(vo.w));
         }
         *reinterpret_cast<uint4 *>(p.k_layer + dst) = ko;
-        *reinterpret_cast<uint4 *>(p.v_layer + dst) = vo;
+        if (!V_Q8) *reinterpret_cast<uint4 *>(p.v_layer + dst) = vo;
     }
 }
 
@@ -151,8 +176,9 @@ uint32_t grid_for(uint64_t work_items, uint32_t block, int sm_count, uint32_t pe
     return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(need, cap));
 }
 
-brc_status need_device_pool(const brc_pool *pool, const char *who) {
+brc_status need_device_pool(const brc_pool *pool, const char *who, bool q8v_ok = false) {
     if (!pool) return brc_fail(BRC_ERR_INVALID, "%s: pool is NULL", who);
+    if (!q8v_ok) BRC_REFUSE_Q8V(pool, who);
     if (pool->device < 0 || !pool->k_base)
         return brc_fail(BRC_ERR_CUDA, "%s: this pool holds bookkeeping only (no device memory); compute calls need a GPU pool",
                         who);
@@ -167,7 +193,9 @@ brc_status brc_kv_append(brc_pool *pool, uint32_t layer, const uint32_t *block_t
                          const uint32_t *pos0_dev, uint32_t n_seqs, uint32_t tokens_per_seq,
                          const uint32_t *cu_tokens_dev, uint32_t total_tokens, uint32_t max_pos_end,
                          const void *k_src_dev, const void *v_src_dev, int32_t src_dtype, void *stream) {
-    if (brc_status rc = need_device_pool(pool, "brc_kv_append")) return rc;
+    if (brc_status rc = need_device_pool(pool, "brc_kv_append", true)) return rc;
+    if (pool->v_q8 && src_dtype != BRC_DTYPE_F32)
+        return brc_fail(BRC_ERR_UNSUPPORTED, "brc_kv_append: a q8_0 V pool quantises from f32 sources only (src_dtype %d)", src_dtype);
     if (layer >= pool->n_layers)
         return brc_fail(BRC_ERR_INVALID, "brc_kv_append: layer %u but the pool has %u", layer, pool->n_layers);
     if (!block_tables_dev || !pos0_dev || !k_src_dev || !v_src_dev)
@@ -187,7 +215,7 @@ brc_status brc_kv_append(brc_pool *pool, uint32_t layer, const uint32_t *block_t
     brc_device_guard guard(pool->device);
     AppendParams p;
     p.k_layer = pool->k_base + (uint64_t)layer * pool->layer_bytes;
-    p.v_layer = pool->v_base + (uint64_t)layer * pool->layer_bytes;
+    p.v_layer = pool->v_base + (uint64_t)layer * pool->v_layer_bytes;
     p.block_tables = block_tables_dev;
     p.pos0 = pos0_dev;
     p.cu_tokens = cu_tokens_dev;
@@ -206,10 +234,12 @@ brc_status brc_kv_append(brc_pool *pool, uint32_t layer, const uint32_t *block_t
     const uint64_t work = (uint64_t)total_tokens * pool->n_kv_head * (pool->head_dim / 8u);
     const uint32_t grid = grid_for(work, 256, pool->sm_count, 8);
     brc_stage_begin(pool, BRC_STAGE_KV_APPEND, brc_stream(stream));
-    if (src_dtype == BRC_DTYPE_F32)
-        kv_append_kernel<true><<<grid, 256, 0, brc_stream(stream)>>>(p);
+    if (pool->v_q8)
+        kv_append_kernel<true, true><<<grid, 256, 0, brc_stream(stream)>>>(p);
+    else if (src_dtype == BRC_DTYPE_F32)
+        kv_append_kernel<true, false><<<grid, 256, 0, brc_stream(stream)>>>(p);
     else
-        kv_append_kernel<false><<<grid, 256, 0, brc_stream(stream)>>>(p);
+        kv_append_kernel<false, false><<<grid, 256, 0, brc_stream(stream)>>>(p);
     brc_stage_end(pool, BRC_STAGE_KV_APPEND, brc_stream(stream));
     BRC_CUDA(cudaGetLastError());
     return BRC_OK;

@@ -127,10 +127,8 @@ static brc_status make_kv_map(CUtensorMap *tm, void *k_base, uint64_t v_offset_b
     return BRC_OK;
 }
 
-extern "C" {
-
-brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim,
-                           uint32_t page_tokens, uint32_t n_pages, brc_pool **out) {
+static brc_status create_pool(int32_t device, uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim,
+                              uint32_t page_tokens, uint32_t n_pages, bool v_q8, brc_pool **out) {
     if (!out) return brc_fail(BRC_ERR_INVALID, "brc_pool_create: out is NULL");
     *out = nullptr;
     if (n_layers == 0 || n_kv_head == 0 || n_pages == 0)
@@ -163,9 +161,12 @@ brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n_kv_head
     p->half_page_bytes = (uint64_t)n_kv_head * page_tokens * head_dim * 2u;
     p->layer_bytes = p->half_page_bytes * n_pages;
     const uint64_t bytes = p->layer_bytes * n_layers;
+    p->v_q8 = v_q8;
+    p->v_layer_bytes = v_q8 ? p->layer_bytes / 16u * 9u : p->layer_bytes;   // 36 B per 32 values against 64 B
+    const uint64_t v_bytes = p->v_layer_bytes * n_layers;
     cudaError_t e;
     // K and V live in one allocation so a single tensor map can address both.
-    if ((e = cudaMalloc(&p->k_base, 2 * bytes)) != cudaSuccess || (e = cudaMalloc(&p->status_dev, BRC_STATUS_BYTES)) != cudaSuccess ||
+    if ((e = cudaMalloc(&p->k_base, bytes + v_bytes)) != cudaSuccess || (e = cudaMalloc(&p->status_dev, BRC_STATUS_BYTES)) != cudaSuccess ||
         (e = cudaMallocHost(&p->status_host, 256)) != cudaSuccess) {
         brc_status rc = brc_fail(BRC_ERR_CUDA, "brc_pool_create: allocating 2 x %llu bytes on device %d failed: %s",
                                  (unsigned long long)bytes, device, cudaGetErrorString(e));
@@ -175,7 +176,7 @@ brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n_kv_head
     p->v_base = p->k_base + bytes;
     p->ids_cap = 1u << 16;
     if ((e = cudaMalloc(&p->ids_dev, (size_t)p->ids_cap * 2 * sizeof(uint32_t))) != cudaSuccess ||
-        (e = cudaMemset(p->k_base, 0, bytes)) != cudaSuccess || (e = cudaMemset(p->v_base, 0, bytes)) != cudaSuccess ||
+        (e = cudaMemset(p->k_base, 0, bytes)) != cudaSuccess || (e = cudaMemset(p->v_base, 0, v_bytes)) != cudaSuccess ||
         (e = cudaMemset(p->status_dev, 0, BRC_STATUS_BYTES)) != cudaSuccess || (e = cudaDeviceSynchronize()) != cudaSuccess) {
         brc_status rc = brc_fail(BRC_ERR_CUDA, "brc_pool_create: initialising the pool failed: %s", cudaGetErrorString(e));
         brc_pool_destroy(p);
@@ -183,21 +184,40 @@ brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n_kv_head
     }
     cudaDeviceGetAttribute(&p->sm_count, cudaDevAttrMultiProcessorCount, device);
     brc_status rc = make_map(&p->tm_k, p->k_base, rows, head_dim, page_tokens);
-    if (rc == BRC_OK) rc = make_map(&p->tm_v, p->v_base, rows, head_dim, page_tokens);
-    if (rc == BRC_OK) rc = make_kv_map(&p->tm_kv, p->k_base, bytes, rows, head_dim, page_tokens);
+    // (a q8_0 V pool has no binary16 V rows to map: the kernels that use these views refuse it)
+    if (rc == BRC_OK && !v_q8) rc = make_map(&p->tm_v, p->v_base, rows, head_dim, page_tokens);
+    if (rc == BRC_OK && !v_q8) rc = make_kv_map(&p->tm_kv, p->k_base, bytes, rows, head_dim, page_tokens);
     // With an even number of kv heads, the rows of two neighbouring kv heads of a page are contiguous:
     // a box of 2 * page_tokens rows brings both (8 KiB per operation instead of 4 KiB).
-    if (rc == BRC_OK && n_kv_head % 2u == 0u)
+    if (rc == BRC_OK && !v_q8 && n_kv_head % 2u == 0u)
         rc = make_kv_map(&p->tm_kv2, p->k_base, bytes, rows, head_dim, 2u * page_tokens);
     if (rc != BRC_OK) {
         brc_pool_destroy(p);
         return rc;
     }
-    p->has_tma = true;
+    p->has_tma = !v_q8;
     p->refcount.assign(n_pages, 0u);
     p->free_list.resize(n_pages);
     for (uint32_t i = 0; i < n_pages; ++i) p->free_list[i] = n_pages - 1 - i;  // pop_back yields 0,1,2,...
     *out = p;
+    return BRC_OK;
+}
+
+extern "C" {
+
+brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim,
+                           uint32_t page_tokens, uint32_t n_pages, brc_pool **out) {
+    return create_pool(device, n_layers, n_kv_head, head_dim, page_tokens, n_pages, false, out);
+}
+
+brc_status brc_pool_create_q8v(int32_t device, uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim,
+                               uint32_t page_tokens, uint32_t n_pages, brc_pool **out) {
+    return create_pool(device, n_layers, n_kv_head, head_dim, page_tokens, n_pages, true, out);
+}
+
+brc_status brc_pool_v_layout(const brc_pool *pool, int32_t *out_layout) {
+    if (!pool || !out_layout) return brc_fail(BRC_ERR_INVALID, "brc_pool_v_layout: NULL argument");
+    *out_layout = pool->v_q8 ? BRC_V_Q8_0 : BRC_V_F16;
     return BRC_OK;
 }
 
@@ -217,6 +237,7 @@ brc_status brc_pool_create_bookkeeping(uint32_t n_layers, uint32_t n_kv_head, ui
     p->n_pages = n_pages;
     p->half_page_bytes = (uint64_t)n_kv_head * page_tokens * head_dim * 2u;
     p->layer_bytes = p->half_page_bytes * n_pages;
+    p->v_layer_bytes = p->layer_bytes;
     p->refcount.assign(n_pages, 0u);
     p->free_list.resize(n_pages);
     for (uint32_t i = 0; i < n_pages; ++i) p->free_list[i] = n_pages - 1 - i;
@@ -256,13 +277,13 @@ brc_status brc_pool_geometry(const brc_pool *pool, brc_geometry *out) {
     out->n_pages = pool->n_pages;
     out->device = pool->device;
     out->half_page_bytes = pool->half_page_bytes;
-    out->total_bytes = 2u * pool->layer_bytes * pool->n_layers;
+    out->total_bytes = (pool->layer_bytes + pool->v_layer_bytes) * pool->n_layers;
     return BRC_OK;
 }
 
 brc_status brc_pool_bytes(const brc_pool *pool, uint64_t *out) {
     if (!pool || !out) return brc_fail(BRC_ERR_INVALID, "brc_pool_bytes: NULL argument");
-    *out = 2u * pool->layer_bytes * pool->n_layers;
+    *out = (pool->layer_bytes + pool->v_layer_bytes) * pool->n_layers;
     return BRC_OK;
 }
 
@@ -271,7 +292,7 @@ static brc_status pool_fill(brc_pool *pool, int value, void *stream, const char 
     brc_device_guard guard(pool->device);
     const uint64_t bytes = pool->layer_bytes * pool->n_layers;
     BRC_CUDA(cudaMemsetAsync(pool->k_base, value, bytes, brc_stream(stream)));
-    BRC_CUDA(cudaMemsetAsync(pool->v_base, value, bytes, brc_stream(stream)));
+    BRC_CUDA(cudaMemsetAsync(pool->v_base, value, pool->v_layer_bytes * pool->n_layers, brc_stream(stream)));
     return BRC_OK;
 }
 
@@ -293,7 +314,7 @@ brc_status brc_pool_v_ptr(const brc_pool *pool, uint32_t layer, void **out_dev) 
     if (!pool || !out_dev) return brc_fail(BRC_ERR_INVALID, "brc_pool_v_ptr: NULL argument");
     if (layer >= pool->n_layers)
         return brc_fail(BRC_ERR_INVALID, "brc_pool_v_ptr: layer %u but the pool has %u", layer, pool->n_layers);
-    *out_dev = pool->v_base + (uint64_t)layer * pool->layer_bytes;
+    *out_dev = pool->v_base + (uint64_t)layer * pool->v_layer_bytes;
     return BRC_OK;
 }
 
@@ -303,11 +324,12 @@ static brc_status pool_rw(brc_pool *pool, int32_t which, uint32_t layer, uint64_
     if (pool->device < 0 || !pool->k_base) return brc_fail(BRC_ERR_CUDA, "%s: this pool holds bookkeeping only", who);
     if (which != 0 && which != 1) return brc_fail(BRC_ERR_INVALID, "%s: which = %d (0 = K, 1 = V)", who, which);
     if (layer >= pool->n_layers) return brc_fail(BRC_ERR_INVALID, "%s: layer %u but the pool has %u", who, layer, pool->n_layers);
-    if (off > pool->layer_bytes || bytes > pool->layer_bytes - off)
+    const uint64_t one_layer = which ? pool->v_layer_bytes : pool->layer_bytes;
+    if (off > one_layer || bytes > one_layer - off)
         return brc_fail(BRC_ERR_CAPACITY, "%s: bytes %llu..%llu but one layer's pool holds %llu", who,
-                        (unsigned long long)off, (unsigned long long)(off + bytes), (unsigned long long)pool->layer_bytes);
+                        (unsigned long long)off, (unsigned long long)(off + bytes), (unsigned long long)one_layer);
     brc_device_guard guard(pool->device);
-    uint8_t *dev = (which ? pool->v_base : pool->k_base) + (uint64_t)layer * pool->layer_bytes + off;
+    uint8_t *dev = (which ? pool->v_base : pool->k_base) + (uint64_t)layer * one_layer + off;
     cudaStream_t s = brc_stream(stream);
     if (read)
         BRC_CUDA(cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, s));

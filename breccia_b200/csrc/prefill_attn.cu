@@ -543,6 +543,7 @@ brc_status brc_paged_prefill_attn(brc_pool *pool, uint32_t layer, const void *q_
                                   uint32_t table_stride, const uint32_t *pos0_dev, uint32_t n_seqs, uint32_t chunk_len,
                                   uint32_t max_pos_end, float scale, float *out_dev, void *stream) {
     if (!pool) return brc_fail(BRC_ERR_INVALID, "brc_paged_prefill_attn: pool is NULL");
+    BRC_REFUSE_Q8V(pool, "brc_paged_prefill_attn");
     if (pool->device < 0 || !pool->k_base)
         return brc_fail(BRC_ERR_CUDA, "brc_paged_prefill_attn: this pool holds bookkeeping only (no device memory)");
     if (layer >= pool->n_layers)

@@ -140,6 +140,7 @@ brc_status brc_qk_prepare_append(brc_pool *pool, uint32_t layer, const float *q_
                                  const uint32_t *pos0_dev, uint32_t n_seqs, uint32_t tokens_per_seq, uint32_t max_pos_end,
                                  void *q_out_dev, int32_t q_out_dtype, void *stream) {
     if (!pool) return brc_fail(BRC_ERR_INVALID, "brc_qk_prepare_append: pool is NULL");
+    BRC_REFUSE_Q8V(pool, "brc_qk_prepare_append");
     if (pool->device < 0 || !pool->k_base)
         return brc_fail(BRC_ERR_CUDA, "brc_qk_prepare_append: this pool holds bookkeeping only (no device memory)");
     if (layer >= pool->n_layers) return brc_fail(BRC_ERR_INVALID, "brc_qk_prepare_append: layer %u but the pool has %u", layer, pool->n_layers);

@@ -12,6 +12,9 @@
 //   the dot product is reduced by shuffles; every warp keeps an online softmax (base 2); the warps'
 //   (m, l, O) are merged through shared memory; sigmoid(gate) last.
 // Any number of query heads per kv head is accepted (the reference's 24q / 2kv included).
+// On a pool whose V pages are q8_0 (blocks of one f32 scale + 32 signed bytes) a lane reads the scale word of its
+// block and the one or two words that hold its own quanta and multiplies in registers (qsa_attn_apply.comp:69-77):
+// 36 bytes cross the memory system per 32 values instead of 64.
 #include "brc_device.cuh"
 #include "brc_internal.h"
 
@@ -42,7 +45,7 @@ __device__ __forceinline__ float sp_sigmoid(float x) {
 
 // SP_WARPS: 16 when the launch has few CTAs (one decode row: every head's list is cut sixteen ways), 8 when rows x
 // heads already fill the GPU (more CTAs per SM, a cheaper merge).
-template <int HD, int SP_WARPS>
+template <int HD, int SP_WARPS, bool V_Q8>
 __global__ void __launch_bounds__(SP_WARPS * 32) sparse_attn_kernel(const SparseParams p) {
     constexpr int EPL = HD / 32;   // elements per lane: 8 (one 16-byte load of binary16) or 4
     __shared__ float part_o[SP_WARPS][HD];
@@ -85,23 +88,44 @@ __global__ void __launch_bounds__(SP_WARPS * 32) sparse_attn_kernel(const Sparse
 #pragma unroll
         for (uint32_t c = 0; c < 4; ++c) {
             const size_t at = (base + (size_t)min(c, n_live - 1u) * HD) * 2u;   // masked cells re-read a live one (weight 0)
+            uint32_t kw[EPL / 2], vw[EPL / 2];
             if (EPL == 8) {
                 const uint4 kb = *reinterpret_cast<const uint4 *>(p.k_layer + at);
-                const uint4 vb = *reinterpret_cast<const uint4 *>(p.v_layer + at);
-                const __half2 *kh = reinterpret_cast<const __half2 *>(&kb), *vh = reinterpret_cast<const __half2 *>(&vb);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 x = __half22float2(kh[e]), y = __half22float2(vh[e]);
-                    kf[c][2 * e] = x.x, kf[c][2 * e + 1] = x.y, vf[c][2 * e] = y.x, vf[c][2 * e + 1] = y.y;
-                }
+                kw[0] = kb.x, kw[1] = kb.y, kw[EPL / 2 - 2] = kb.z, kw[EPL / 2 - 1] = kb.w;
             } else {
                 const uint2 kb = *reinterpret_cast<const uint2 *>(p.k_layer + at);
-                const uint2 vb = *reinterpret_cast<const uint2 *>(p.v_layer + at);
-                const __half2 *kh = reinterpret_cast<const __half2 *>(&kb), *vh = reinterpret_cast<const __half2 *>(&vb);
+                kw[0] = kb.x, kw[1] = kb.y;
+            }
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const float2 x = __half22float2(kh[e]), y = __half22float2(vh[e]);
-                    kf[c][2 * e] = x.x, kf[c][2 * e + 1] = x.y, vf[c][2 * e] = y.x, vf[c][2 * e + 1] = y.y;
+            for (int e = 0; e < EPL / 2; ++e) {
+                const float2 x = __half22float2(*reinterpret_cast<const __half2 *>(&kw[e]));
+                kf[c][2 * e] = x.x, kf[c][2 * e + 1] = x.y;
+            }
+            if (V_Q8) {
+                // row of the cell in the pool, then the lane's block: EPL * lane / 32
+                const size_t vrow = ((size_t)page * p.n_kv_head + kvh) * 16u + (cell0 & 15u) + min(c, n_live - 1u);
+                const uint32_t *blk = reinterpret_cast<const uint32_t *>(p.v_layer) + (vrow * (HD / 32) + (lane * EPL) / 32u) * 9u;
+                const float vs = __uint_as_float(blk[0]);
+                const uint32_t first = 1u + ((lane * EPL) % 32u) / 4u;
+#pragma unroll
+                for (int w = 0; w < EPL / 4; ++w) {
+                    const uint32_t packed = blk[first + w];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        vf[c][4 * w + j] = (float)(int8_t)(packed >> (8 * j)) * vs;
+                }
+            } else {
+                if (EPL == 8) {
+                    const uint4 vb = *reinterpret_cast<const uint4 *>(p.v_layer + at);
+                    vw[0] = vb.x, vw[1] = vb.y, vw[EPL / 2 - 2] = vb.z, vw[EPL / 2 - 1] = vb.w;
+                } else {
+                    const uint2 vb = *reinterpret_cast<const uint2 *>(p.v_layer + at);
+                    vw[0] = vb.x, vw[1] = vb.y;
+                }
+#pragma unroll
+                for (int e = 0; e < EPL / 2; ++e) {
+                    const float2 y = __half22float2(*reinterpret_cast<const __half2 *>(&vw[e]));
+                    vf[c][2 * e] = y.x, vf[c][2 * e + 1] = y.y;
                 }
             }
         }
@@ -191,7 +215,7 @@ brc_status brc_paged_sparse_attn(brc_pool *pool, uint32_t layer, const void *q_d
     SparseParams p;
     p.q = q_dev;
     p.k_layer = pool->k_base + (uint64_t)layer * pool->layer_bytes;
-    p.v_layer = pool->v_base + (uint64_t)layer * pool->layer_bytes;
+    p.v_layer = pool->v_base + (uint64_t)layer * pool->v_layer_bytes;
     p.block_tables = block_tables_dev;
     p.pos0 = pos0_dev;
     p.ids = ids_dev;
@@ -214,12 +238,20 @@ brc_status brc_paged_sparse_attn(brc_pool *pool, uint32_t layer, const void *q_d
     brc_stage_begin(pool, BRC_STAGE_ATTN_PARTIAL, st);
     const uint64_t sms = (uint64_t)(pool->sm_count > 0 ? pool->sm_count : 148);
     const bool few = rows * n_head < 2u * sms;
-    if (hd == 256) {
-        if (few) sparse_attn_kernel<256, 16><<<grid, 512, 0, st>>>(p);
-        else sparse_attn_kernel<256, 8><<<grid, 256, 0, st>>>(p);
+    if (pool->v_q8) {
+        if (hd == 256) {
+            if (few) sparse_attn_kernel<256, 16, true><<<grid, 512, 0, st>>>(p);
+            else sparse_attn_kernel<256, 8, true><<<grid, 256, 0, st>>>(p);
+        } else {
+            if (few) sparse_attn_kernel<128, 16, true><<<grid, 512, 0, st>>>(p);
+            else sparse_attn_kernel<128, 8, true><<<grid, 256, 0, st>>>(p);
+        }
+    } else if (hd == 256) {
+        if (few) sparse_attn_kernel<256, 16, false><<<grid, 512, 0, st>>>(p);
+        else sparse_attn_kernel<256, 8, false><<<grid, 256, 0, st>>>(p);
     } else {
-        if (few) sparse_attn_kernel<128, 16><<<grid, 512, 0, st>>>(p);
-        else sparse_attn_kernel<128, 8><<<grid, 256, 0, st>>>(p);
+        if (few) sparse_attn_kernel<128, 16, false><<<grid, 512, 0, st>>>(p);
+        else sparse_attn_kernel<128, 8, false><<<grid, 256, 0, st>>>(p);
     }
     brc_stage_end(pool, BRC_STAGE_ATTN_PARTIAL, st);
     BRC_CUDA(cudaGetLastError());

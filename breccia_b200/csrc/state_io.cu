@@ -43,6 +43,7 @@ brc_status move_pages(brc_pool *pool, bool is_v, uint32_t layer, const uint32_t 
 brc_status check_args(const brc_pool *pool, const char *who, uint32_t layer, const uint32_t *table, uint32_t table_len,
                       uint32_t pos, const char *dir, uint32_t *out_pages) {
     if (!pool || !dir) return brc_fail(BRC_ERR_INVALID, "%s: NULL pool or directory", who);
+    BRC_REFUSE_Q8V(pool, who);
     if (pool->device < 0 || !pool->k_base) return brc_fail(BRC_ERR_CUDA, "%s: this pool holds bookkeeping only (no device memory)", who);
     if (layer >= pool->n_layers) return brc_fail(BRC_ERR_INVALID, "%s: layer %u but the pool has %u", who, layer, pool->n_layers);
     const uint32_t pages = pos / pool->page_tokens + 1;   // ceil((pos + 1) / page_tokens)

@@ -30,6 +30,7 @@ static brc_status decode_step_range(brc_pool *pool, uint32_t layer0, uint32_t n_
                                     float scale, float *out_dev, uint64_t out_layer_stride_bytes, void *workspace_dev,
                                     uint64_t workspace_bytes, void *stream) {
     if (!pool) return brc_fail(BRC_ERR_INVALID, "brc_decode_step: pool is NULL");
+    BRC_REFUSE_Q8V(pool, "brc_decode_step");
     if (pool->device < 0 || !pool->k_base)
         return brc_fail(BRC_ERR_CUDA, "brc_decode_step: this pool holds bookkeeping only (no device memory)");
     if ((uint64_t)layer0 + n_layers > pool->n_layers)
@@ -124,13 +125,14 @@ brc_status brc_decode_step_host_staging_bytes(const brc_pool *pool, uint32_t n_l
     return BRC_OK;
 }
 
-brc_status brc_decode_step_host(brc_pool *pool, uint32_t layer0, uint32_t n_layers, uint32_t parts,
+brc_status brc_decode_step_host(brc_pool *pool, uint32_t layer0, uint32_t n_layers, uint32_t parts, uint32_t flags,
                                 const uint32_t *block_tables_dev, uint32_t table_stride, uint32_t *seq_lens_dev,
                                 uint32_t *pos0_dev, uint32_t n_seqs, uint32_t max_seq_len_after, const void *q_host,
                                 int32_t q_dtype, uint32_t n_head, const void *k_new_host, const void *v_new_host,
                                 int32_t kv_dtype, float scale, float *out_host, void *staging_dev, uint64_t staging_bytes,
                                 void *workspace_dev, uint64_t workspace_bytes, void *stream) {
     if (!pool) return brc_fail(BRC_ERR_INVALID, "brc_decode_step_host: pool is NULL");
+    BRC_REFUSE_Q8V(pool, "brc_decode_step_host");
     if (pool->device < 0 || !pool->k_base)
         return brc_fail(BRC_ERR_CUDA, "brc_decode_step_host: this pool holds bookkeeping only (no device memory)");
     if (!q_host || !k_new_host || !v_new_host || !out_host || !staging_dev)
@@ -159,32 +161,50 @@ brc_status brc_decode_step_host(brc_pool *pool, uint32_t layer0, uint32_t n_laye
         BRC_CUDA(cudaEventCreateWithFlags(&pool->host_all_down, cudaEventDisableTiming));
     }
     uint8_t *st = static_cast<uint8_t *>(staging_dev);
+    // Pinned host memory is addressable from the device: the kernels then store the output straight
+    // into out_host (posted writes over PCIe, off the kernels' critical path) and nothing is downloaded.
+    // Reading q / k / v the same way would put PCIe round trips in front of every CTA's first tile, so
+    // those are uploaded.
+    float *out_direct = nullptr;
+    {
+        cudaPointerAttributes attr;
+        if (flags & BRC_STEP_HOST_DOWNLOAD)
+            ;
+        else if (cudaPointerGetAttributes(&attr, out_host) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer)
+            out_direct = static_cast<float *>(attr.devicePointer);
+        else
+            cudaGetLastError();   // pageable memory is not an error here: staged download
+    }
     const uint8_t *qh = static_cast<const uint8_t *>(q_host), *kh = static_cast<const uint8_t *>(k_new_host),
                   *vh = static_cast<const uint8_t *>(v_new_host);
     uint8_t *oh = reinterpret_cast<uint8_t *>(out_host);
     cudaStream_t s = brc_stream(stream);
     auto lo = [&](uint32_t i) { return (uint32_t)((uint64_t)n_layers * i / parts); };
+    // The first part's upload goes to `stream` itself (nothing to overlap it with, and no event between
+    // the copy and the first kernel); the later ones run ahead on the upload stream.
     auto upload = [&](uint32_t i) -> cudaError_t {
         const uint64_t a = lo(i), n = lo(i + 1) - a;
-        cudaError_t e = cudaMemcpyAsync(st + l.q_off + a * l.q_layer, qh + a * l.q_layer, n * l.q_layer, cudaMemcpyHostToDevice, pool->host_up);
-        if (e == cudaSuccess) e = cudaMemcpyAsync(st + l.k_off + a * l.kv_layer, kh + a * l.kv_layer, n * l.kv_layer, cudaMemcpyHostToDevice, pool->host_up);
-        if (e == cudaSuccess) e = cudaMemcpyAsync(st + l.v_off + a * l.kv_layer, vh + a * l.kv_layer, n * l.kv_layer, cudaMemcpyHostToDevice, pool->host_up);
-        if (e == cudaSuccess) e = cudaEventRecord(pool->host_uploaded[i], pool->host_up);
+        cudaStream_t us = i == 0 ? s : pool->host_up;
+        cudaError_t e = cudaMemcpyAsync(st + l.q_off + a * l.q_layer, qh + a * l.q_layer, n * l.q_layer, cudaMemcpyHostToDevice, us);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(st + l.k_off + a * l.kv_layer, kh + a * l.kv_layer, n * l.kv_layer, cudaMemcpyHostToDevice, us);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(st + l.v_off + a * l.kv_layer, vh + a * l.kv_layer, n * l.kv_layer, cudaMemcpyHostToDevice, us);
+        if (e == cudaSuccess && i > 0) e = cudaEventRecord(pool->host_uploaded[i], us);
         return e;
     };
-    // Order of issue: the upload of part i + 1 goes out before the kernels of part i, so the copy
-    // engines are never waiting for this thread; each part's output leaves as soon as it is computed.
-    BRC_CUDA(upload(0));
+    // Order of issue: every upload before the first kernel, so the copy engine never waits for this
+    // thread; each part's output leaves as soon as it is computed.
+    for (uint32_t i = 0; i < parts; ++i) BRC_CUDA(upload(i));
     brc_status rc = BRC_OK;
     for (uint32_t i = 0; i < parts && rc == BRC_OK; ++i) {
-        if (i + 1 < parts) BRC_CUDA(upload(i + 1));
         const uint32_t a = lo(i), n = lo(i + 1) - a;
-        BRC_CUDA(cudaStreamWaitEvent(s, pool->host_uploaded[i], 0));
+        if (i > 0) BRC_CUDA(cudaStreamWaitEvent(s, pool->host_uploaded[i], 0));
         rc = decode_step_range(pool, layer0, n_layers, a, n, block_tables_dev, table_stride, seq_lens_dev, pos0_dev, n_seqs,
                                max_seq_len_after, st + l.q_off, q_dtype, l.q_layer, n_head, st + l.k_off, st + l.v_off, kv_dtype,
-                               l.kv_layer, nullptr, 0, 0, scale, reinterpret_cast<float *>(st + l.out_off), l.out_layer,
-                               workspace_dev, workspace_bytes, stream);
+                               l.kv_layer, nullptr, 0, 0, scale,
+                               out_direct ? out_direct : reinterpret_cast<float *>(st + l.out_off), l.out_layer, workspace_dev,
+                               workspace_bytes, stream);
         if (rc != BRC_OK) break;
+        if (out_direct) continue;
         BRC_CUDA(cudaEventRecord(pool->host_computed[i], s));
         BRC_CUDA(cudaStreamWaitEvent(pool->host_down, pool->host_computed[i], 0));
         BRC_CUDA(cudaMemcpyAsync(oh + a * l.out_layer, st + l.out_off + a * l.out_layer, n * l.out_layer, cudaMemcpyDeviceToHost,
@@ -193,8 +213,8 @@ brc_status brc_decode_step_host(brc_pool *pool, uint32_t layer0, uint32_t n_laye
     // Whatever was issued has to drain before the caller may touch its buffers again, error or not.
     cudaError_t e = cudaEventRecord(pool->host_all_down, pool->host_down);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(s, pool->host_all_down, 0);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(pool->host_up);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e == cudaSuccess && rc != BRC_OK) e = cudaStreamSynchronize(pool->host_up);   // kernels that waited for it never went out
     if (rc != BRC_OK) return rc;
     BRC_CUDA(e);
     return BRC_OK;

@@ -89,6 +89,7 @@ extern "C" {
 brc_status brc_tier_create(brc_pool *pool, uint32_t host_pages, brc_tier **out) {
     if (!pool || !out) return brc_fail(BRC_ERR_INVALID, "brc_tier_create: NULL argument");
     *out = nullptr;
+    BRC_REFUSE_Q8V(pool, "brc_tier_create");
     if (pool->device < 0 || !pool->k_base)
         return brc_fail(BRC_ERR_CUDA, "brc_tier_create: this pool holds bookkeeping only (no device memory)");
     if (host_pages == 0) return brc_fail(BRC_ERR_INVALID, "brc_tier_create: host_pages is 0");

@@ -35,12 +35,17 @@ def _u32_array(a) -> np.ndarray:
 
 
 class KvPool:
-    """Paged f16 K/V pools of all layers on one GPU plus the page allocator (brc_pool)."""
+    """Paged f16 K/V pools of all layers on one GPU plus the page allocator (brc_pool).  v_q8: V page bodies
+    as q8_0 blocks (the reference's VLayout::Q8_0, qsa/mod.rs:245-349): append from f32 and attention over
+    selected blocks work on such a pool, the dense kernels refuse it."""
 
     def __init__(self, device: int, n_layers: int, n_kv_head: int, head_dim: int, n_pages: int,
-                 page_tokens: int = PAGE_CELLS, bookkeeping_only: bool = False):
+                 page_tokens: int = PAGE_CELLS, bookkeeping_only: bool = False, v_q8: bool = False):
         self._h = C.c_void_p()
-        if bookkeeping_only:
+        self.v_q8 = v_q8
+        if v_q8:
+            _lib.call("brc_pool_create_q8v", device, n_layers, n_kv_head, head_dim, page_tokens, n_pages, C.byref(self._h))
+        elif bookkeeping_only:
             _lib.call("brc_pool_create_bookkeeping", n_layers, n_kv_head, head_dim, page_tokens, n_pages,
                       C.byref(self._h))
         else:
@@ -96,7 +101,10 @@ class KvPool:
 
     def read(self, which: int, layer: int) -> np.ndarray:
         """Whole K (0) or V (1) pool of a layer as uint16 [n_pages, n_kv, page_tokens, head_dim]."""
-        out = np.empty((self.n_pages, self.n_kv_head, self.page_tokens, self.head_dim), np.uint16)
+        if which == 1 and self.v_q8:   # raw q8_0 rows: [n_pages * n_kv * page_tokens, head_dim / 32 * 36] bytes
+            out = np.empty((self.n_pages * self.n_kv_head * self.page_tokens, self.head_dim // 32 * 36), np.uint8)
+        else:
+            out = np.empty((self.n_pages, self.n_kv_head, self.page_tokens, self.head_dim), np.uint16)
         _lib.call("brc_pool_read", self.handle, which, layer, 0, out.ctypes.data_as(C.c_void_p), out.nbytes,
                   _stream_ptr())
         return out
@@ -342,11 +350,14 @@ class DecodeBatch:
         return torch.empty(need.value, dtype=torch.uint8, device=self.seq_lens.device)
 
     def step_host(self, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor, out_host: torch.Tensor,
-                  staging: torch.Tensor, layer0: int = 0, parts: int = 3, kv_dtype: int = DTYPE_F32) -> None:
+                  staging: torch.Tensor, layer0: int = 0, parts: int = 1, kv_dtype: int = DTYPE_F32,
+                  download: bool = False) -> None:
         """The same step for a caller whose activations live in (pinned) host memory, one call into the
-        library (brc_decode_step_host): q / k / v go up and the attention output comes back in `parts`
-        groups of layers, the copies of one group hidden behind the kernels of its neighbours.  Returns
-        when out_host is complete.  `staging` comes from host_staging()."""
+        library (brc_decode_step_host): q / k / v are uploaded, the kernels store the attention output
+        straight into a pinned out_host (a pageable one is downloaded).  `parts` > 1 uploads the layers in
+        groups on a second stream; on the machines measured the hand-over between the streams cost more
+        than the hidden copy saved, so one part is the default.  Returns when out_host is complete.
+        `staging` comes from host_staging()."""
         for t in (q_host, k_host, v_host, out_host):
             if t.is_cuda or not t.is_contiguous():
                 raise ValueError("step_host takes contiguous host tensors")
@@ -354,7 +365,8 @@ class DecodeBatch:
             raise BrcError(_lib.ERR_CAPACITY, f"decode step would write cell {int(self.seq_lens_host.max())} but each "
                                               f"block table holds {self.capacity}")
         self.seq_lens_host += 1
-        _lib.call("brc_decode_step_host", self.pool.handle, layer0, q_host.shape[0], parts, _ptr(self.block_tables),
+        _lib.call("brc_decode_step_host", self.pool.handle, layer0, q_host.shape[0], parts, 1 if download else 0,
+                  _ptr(self.block_tables),
                   self.table_stride, _ptr(self.seq_lens), _ptr(self.pos0), self.n_seqs, int(self.seq_lens_host.max()),
                   _ptr(q_host), self.q_dtype, self.n_head, _ptr(k_host), _ptr(v_host), kv_dtype, self.scale, _ptr(out_host),
                   _ptr(staging), staging.numel(), _ptr(self.scratch), self.scratch.numel(), _stream_ptr())

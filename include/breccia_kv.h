@@ -85,6 +85,20 @@ BRC_API int32_t brc_abi_version(void);
  * like the reference (qsa/mod.rs:399-535). */
 BRC_API brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim,
                                    uint32_t page_tokens, uint32_t n_pages, brc_pool **out);
+/* The same pool with V page bodies stored as q8_0, the reference's VLayout::Q8_0
+ * (qsa/mod.rs:245-349; QsaState::with_layout, qsa/mod.rs:399): a V row is
+ * head_dim / 32 blocks of one f32 scale followed by 32 signed bytes (36 B for 32
+ * values against 64 B: 0.5625x the V bytes), rows in the order of the binary16
+ * layout; K stays binary16.  Built for such a pool: brc_kv_append from f32 sources
+ * (store rule of shaders/qsa_kv_append.comp:117-133), brc_paged_sparse_attn
+ * (in-register dequantisation, qsa_attn_apply.comp:69-77), brc_pool_read /
+ * brc_pool_write / brc_pool_v_ptr, the allocator and the prefix tree.  Every other
+ * entry point that reads or writes V refuses it with BRC_ERR_UNSUPPORTED. */
+#define BRC_V_F16 0
+#define BRC_V_Q8_0 1
+BRC_API brc_status brc_pool_create_q8v(int32_t device, uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim,
+                                       uint32_t page_tokens, uint32_t n_pages, brc_pool **out);
+BRC_API brc_status brc_pool_v_layout(const brc_pool *pool, int32_t *out_layout);
 /* A pool without device memory: page ids, refcounts and (later) prefix-tree and
  * tier bookkeeping only.  Every entry point that would touch the GPU refuses it
  * with BRC_ERR_CUDA.  Exists so schedulers and tests can exercise the host-side
@@ -428,10 +442,11 @@ BRC_API brc_status brc_decode_step_part(brc_pool *pool, uint32_t layer0, uint32_
  * k_new_host / v_new_host [n_layers][n_seqs][n_kv_head*head_dim] (kv_dtype),
  * out_host [n_layers][n_seqs][n_head][head_dim] f32, all contiguous.  The layers go
  * in `parts` groups (1..8, clamped to n_layers): uploads run ahead on a stream of
- * the pool's own, each group's kernels go to `stream` (brc_decode_step_part), and
- * each group's output leaves on a third stream while the next group computes, so
- * only the first upload and the last download are not hidden behind the attention
- * kernels.  `staging_dev` (256-byte aligned, at least
+ * the pool's own and each group's kernels go to `stream` (brc_decode_step_part), so
+ * only the first group's upload is not hidden behind the attention kernels.  When
+ * out_host is pinned (addressable from the device) the kernels store the output
+ * straight into it and nothing is downloaded; otherwise each group's output leaves
+ * on a third stream while the next group computes.  `staging_dev` (256-byte aligned, at least
  * brc_decode_step_host_staging_bytes()) holds the device copies and belongs to the
  * call while it runs.  Returns when out_host is complete; `stream` is ordered after
  * the downloads.  Positions, block tables and the workspace are device-resident as
@@ -439,7 +454,8 @@ BRC_API brc_status brc_decode_step_part(brc_pool *pool, uint32_t layer0, uint32_
 BRC_API brc_status brc_decode_step_host_staging_bytes(const brc_pool *pool, uint32_t n_layers, uint32_t n_seqs,
                                                       uint32_t n_head, int32_t q_dtype, int32_t kv_dtype,
                                                       uint64_t *out_bytes);
-BRC_API brc_status brc_decode_step_host(brc_pool *pool, uint32_t layer0, uint32_t n_layers, uint32_t parts,
+#define BRC_STEP_HOST_DOWNLOAD 1u /* flags: stage the output on the device and copy it down even when out_host is pinned */
+BRC_API brc_status brc_decode_step_host(brc_pool *pool, uint32_t layer0, uint32_t n_layers, uint32_t parts, uint32_t flags,
                                         const uint32_t *block_tables_dev, uint32_t table_stride,
                                         uint32_t *seq_lens_dev, uint32_t *pos0_dev, uint32_t n_seqs,
                                         uint32_t max_seq_len_after, const void *q_host, int32_t q_dtype,

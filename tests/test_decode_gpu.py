@@ -212,11 +212,14 @@ def test_decode_step_appends_bit_exactly_and_attends(cuda_device, kv_f16):
     pool.release()
 
 
-@pytest.mark.parametrize("parts", [1, 2, 5])
-def test_step_from_host_buffers_in_parts_equals_the_device_step(cuda_device, parts):
+@pytest.mark.parametrize("parts,pinned_out,download", [(1, True, False), (2, True, False), (5, True, False), (1, False, False),
+                                                       (3, False, False), (1, True, True), (3, True, True)])
+def test_step_from_host_buffers_in_parts_equals_the_device_step(cuda_device, parts, pinned_out, download):
     """brc_decode_step_host (pinned host q / k / v in, output back to the host, layers in `parts` groups
     with uploads and downloads on streams of their own) against brc_decode_step on a twin pool: outputs,
-    both pools and the advanced lengths must be bit-identical, two steps in a row."""
+    both pools and the advanced lengths must be bit-identical, two steps in a row.  A pinned output buffer
+    is written by the kernels directly unless the caller asks for the download; a pageable one is downloaded
+    group by group."""
     n_head, n_kv, hd, n_layers = 16, 2, 256, 5
     lens = np.array([16, 5, 700, 0, 31, 255])
     tables, n_pool = synth.scattered_tables(56, lens, pool_factor=1.4, extra_tokens=4)
@@ -227,7 +230,7 @@ def test_step_from_host_buffers_in_parts_equals_the_device_step(cuda_device, par
     dev_batch, host_batch = DecodeBatch(pools[0], n_head, tables, lens), DecodeBatch(pools[1], n_head, tables, lens)
     shape_q, shape_kv = (n_layers, lens.size, n_head, hd), (n_layers, lens.size, n_kv * hd)
     staging = host_batch.host_staging(n_layers)
-    out_h = torch.empty(shape_q).pin_memory()
+    out_h = torch.empty(shape_q).pin_memory() if pinned_out else torch.empty(shape_q)
     for step in range(2):
         q_h = torch.from_numpy(oracle.to_f16(synth.normal(610 + step, int(np.prod(shape_q)))).reshape(shape_q)).half().pin_memory()
         k_h = torch.from_numpy(synth.normal(710 + step, int(np.prod(shape_kv)), 0.5).reshape(shape_kv)).pin_memory()
@@ -235,7 +238,7 @@ def test_step_from_host_buffers_in_parts_equals_the_device_step(cuda_device, par
         want = torch.full(shape_q, float("nan"), device="cuda")
         dev_batch.step(q_h.cuda(), k_h.cuda(), v_h.cuda(), want)
         out_h.fill_(float("nan"))
-        host_batch.step_host(q_h, k_h, v_h, out_h, staging, parts=parts)
+        host_batch.step_host(q_h, k_h, v_h, out_h, staging, parts=parts, download=download)
         for pool in pools:
             pool.check()
         assert torch.equal(out_h, want.cpu()), f"step {step}"

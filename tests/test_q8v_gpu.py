@@ -1,0 +1,107 @@
+"""q8_0 V page bodies on the GPU: the append's store rule bit for bit against the oracle, and attention over selected
+blocks with in-register dequantisation against the oracle's `attend` over the dequantised rows — the shape of the
+reference's test (64 cells, block ids [0, 5, 9, 15], gate on; crates/breccia-kernels/tests/attn_conformance.rs:
+1354-1452) and a longer ragged one.  Bars as for binary16 V: max-abs <= 2e-3, max-rel <= 1e-2, reference measure <= 1e-5."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle import q8v
+from breccia_b200 import _lib, synth
+from breccia_b200._lib import DTYPE_F32
+from breccia_b200.qsa import KvPool
+from helpers import ATTN_MAX_ABS, ATTN_MAX_REL, attention_errors, dev_u32
+
+pytestmark = pytest.mark.gpu
+P = lambda x: C.c_void_p(x.data_ptr())
+
+
+def append(pool, layer, table, pos0, k_rows, v_rows):
+    t_dev, p_dev = dev_u32(table[None, :]), dev_u32(np.array([pos0]))
+    kd, vd = torch.from_numpy(k_rows).cuda(), torch.from_numpy(v_rows).cuda()
+    n = k_rows.shape[0]
+    _lib.call("brc_kv_append", pool.handle, layer, P(t_dev), table.size, P(p_dev), 1, n, None, n, pos0 + n, P(kd), P(vd),
+              DTYPE_F32, None)
+    pool.check()
+
+
+def sparse(pool, layer, q, n_head, table, pos, ids, gate=None):
+    hd = pool.head_dim
+    qd = torch.from_numpy(q).cuda()
+    out = torch.full((1, n_head, hd), float("nan"), device="cuda")
+    t_dev, p_dev = dev_u32(table[None, :]), dev_u32(np.array([pos]))
+    i_dev, c_dev = dev_u32(np.asarray(ids, np.uint32)[None, :]), dev_u32(np.array([len(ids)]))
+    g_dev = torch.from_numpy(gate).cuda() if gate is not None else None
+    _lib.call("brc_paged_sparse_attn", pool.handle, layer, P(qd), DTYPE_F32, n_head,
+              C.c_void_p(g_dev.view(-1)[hd:].data_ptr()) if gate is not None else None, 2 * hd if gate is not None else 0,
+              P(t_dev), table.size, P(p_dev), 1, 1, P(i_dev), len(ids), P(c_dev), pos + 1, 1.0 / np.sqrt(hd), P(out), None)
+    pool.check()
+    return out.cpu().numpy()[0]
+
+
+@pytest.mark.parametrize("n_head,n_kv,hd,cells,ids", [
+    (24, 2, 256, 64, [0, 5, 9, 15]),                       # the reference's case
+    (16, 2, 256, 1003, list(range(0, 251, 3)) + [250]),    # ragged: the last block holds the row's own cell and 1 future one
+    (8, 4, 128, 200, list(range(50))),
+])
+def test_q8_0_v_append_bit_exact_and_sparse_attention(cuda_device, n_head, n_kv, hd, cells, ids):
+    n_pages = (cells + 15) // 16
+    pool = KvPool(0, 2, n_kv, hd, n_pages + 5, v_q8=True)
+    layout = C.c_int32(-1)
+    _lib.call("brc_pool_v_layout", pool.handle, C.byref(layout))
+    assert layout.value == 1
+    assert pool.bytes() == 2 * (n_pages + 5) * n_kv * 16 * hd * 2 * (1 + 0.5625)
+    table = synth.permutation(91, n_pages + 5)[:n_pages].astype(np.uint32)
+    dim = n_kv * hd
+    k_all = oracle.normalish(0xF1, cells * dim).reshape(cells, dim)
+    v_all = oracle.normalish(0xF2, cells * dim).reshape(cells, dim)
+    v_all[7, :32] = 0.0                                     # an all-zero block keeps scale 1
+    q = oracle.normalish(0xF3, n_head * hd).reshape(1, n_head, hd)
+    q_full = oracle.normalish(0xF4, n_head * 2 * hd).reshape(1, n_head, 2, hd)
+    first = min(cells, 40)
+    append(pool, 1, table, 0, k_all[:first], v_all[:first])      # two calls, the second starting inside a page
+    if cells > first:
+        append(pool, 1, table, first, k_all[first:], v_all[first:])
+    # the pool's V bytes are the oracle's, bit for bit; K stays binary16
+    want_pool = np.zeros(((n_pages + 5) * n_kv * 16, q8v.row_bytes(hd)), np.uint8)
+    q8v.v_append(want_pool, table, v_all, 0, n_kv, hd)
+    assert np.array_equal(pool.read(1, 1), want_pool)
+    assert not pool.read(1, 0).any()
+    kw = np.zeros((n_pages + 5) * n_kv * 16 * hd // 2, np.uint32)
+    assert oracle.kv_append(kw, kw.copy(), table, k_all, v_all, 0, n_kv, hd) == 0
+    assert np.array_equal(pool.read(0, 1).reshape(-1), kw.view(np.uint16))
+    # attention over the selected blocks
+    got = sparse(pool, 1, q, n_head, table, cells - 1, ids, gate=q_full)
+    kf = oracle.to_f16(k_all)
+    vq = q8v.to_q8_0(v_all.reshape(cells * n_kv, hd)).reshape(cells, dim)
+    want = oracle.attend(q[0], kf, vq, oracle.cells_of(ids, 4), cells - 1, n_head, n_kv, hd, gate=q_full[0, :, 1, :])
+    max_abs, max_rel, ref = attention_errors(got, want)
+    print(f"q8_0 V {n_head}q/{n_kv}kv hd{hd} {cells} cells: max_abs {max_abs:.2e} max_rel {max_rel:.2e} ref {ref:.2e}")
+    assert np.isfinite(got).all()
+    assert max_abs <= ATTN_MAX_ABS and max_rel <= ATTN_MAX_REL and ref <= 1e-5
+    # and it differs from the binary16 answer by no more than the storage loss allows
+    want_f16 = oracle.attend(q[0], kf, oracle.to_f16(v_all), oracle.cells_of(ids, 4), cells - 1, n_head, n_kv, hd,
+                             gate=q_full[0, :, 1, :])
+    assert np.abs(got - want_f16).max() <= 0.05
+    pool.release()
+
+
+def test_entry_points_built_for_binary16_v_refuse_a_q8_0_pool(cuda_device):
+    pool = KvPool(0, 1, 2, 256, 8, v_q8=True)
+    x = torch.zeros(4096, device="cuda")
+    t = dev_u32(np.zeros((1, 2)))
+    with pytest.raises(_lib.BrcError) as err:
+        _lib.call("brc_paged_decode_attn", pool.handle, 0, P(x), DTYPE_F32, 16, None, 0, P(t), 2, P(t), 1, 16, 0.0625, P(x),
+                  P(x), x.numel() * 4, None)
+    assert err.value.code == _lib.ERR_UNSUPPORTED and "q8_0" in err.value.message
+    with pytest.raises(_lib.BrcError) as err:
+        _lib.call("brc_page_gather", pool.handle, 0, P(t), 2, 16, P(x), P(x), None)
+    assert err.value.code == _lib.ERR_UNSUPPORTED
+    with pytest.raises(_lib.BrcError) as err:      # binary16 sources are refused: the rule quantises from f32
+        _lib.call("brc_kv_append", pool.handle, 0, P(t), 2, P(t), 1, 1, None, 1, 1, P(x), P(x), _lib.DTYPE_F16, None)
+    assert err.value.code == _lib.ERR_UNSUPPORTED
+    assert pool.alloc(3).size == 3                  # the allocator works as on any pool
+    pool.release()
