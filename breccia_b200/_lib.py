@@ -82,6 +82,7 @@ SIGNATURES = {
                         _vp, _u32, _u64, _f32, _vp, _u64, _vp, _u64, _vp],
     "brc_decode_step_part": [_vp, _u32, _u32, _u32, _u32, _vp, _u32, _vp, _vp, _u32, _u32, _vp, _i32, _u64, _u32, _vp, _vp,
                              _i32, _u64, _vp, _u32, _u64, _f32, _vp, _u64, _vp, _u64, _vp],
+    "brc_topk_blocks": [_vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _i32, _vp, _vp, _vp],
     "brc_pool_create_q8v": [_i32, _u32, _u32, _u32, _u32, _u32, _vpp],
     "brc_pool_v_layout": [_vp, C.POINTER(C.c_int32)],
     "brc_decode_step_host_staging_bytes": [_vp, _u32, _u32, _u32, _i32, _i32, _u64p],

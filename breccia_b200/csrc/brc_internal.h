@@ -91,7 +91,7 @@ brc_status brc_fail(brc_status code, const char *fmt, ...) __attribute__((format
         if ((pool)->v_q8)                                                                                          \
             return brc_fail(BRC_ERR_UNSUPPORTED,                                                                   \
                             "%s: this pool stores V as q8_0; built for it are brc_kv_append (f32 sources), "      \
-                            "brc_paged_sparse_attn and brc_pool_read / brc_pool_write",                            \
+                            "brc_paged_sparse_attn, brc_page_copy / brc_seq_fork and brc_pool_read / brc_pool_write", \
                             who);                                                                                  \
     } while (0)
 

@@ -146,10 +146,12 @@ __global__ void __launch_bounds__(256)
 }
 
 // Whole-page copies in every layer, K and V.  blockIdx.y = pair; the x dimension strides over the
-// (layer, K|V, 16-byte vector) space of one page.
+// (layer, K|V, 16-byte vector) space of one page.  The V half of a page may be smaller than the K half
+// (q8_0 bodies: 9/16 of it); both are whole numbers of 16-byte vectors.
 __global__ void __launch_bounds__(256)
     page_copy_kernel(uint8_t *k_base, uint8_t *v_base, const uint32_t *src_ids, const uint32_t *dst_ids, uint32_t n_layers,
-                     uint32_t n_pages, uint64_t half_page_bytes, uint64_t layer_bytes, uint32_t *status) {
+                     uint32_t n_pages, uint64_t half_page_bytes, uint64_t layer_bytes, uint64_t v_half_page_bytes,
+                     uint64_t v_layer_bytes, uint32_t *status) {
     const uint32_t pair = blockIdx.y;
     const uint32_t s = src_ids[pair], d = dst_ids[pair];
     if (s >= n_pages || d >= n_pages) {
@@ -157,15 +159,17 @@ __global__ void __launch_bounds__(256)
         return;
     }
     if (s == d) return;
-    const uint32_t vec_per_half = (uint32_t)(half_page_bytes / 16u);
-    const uint64_t total = (uint64_t)n_layers * 2u * vec_per_half;
+    const uint32_t vec_k = (uint32_t)(half_page_bytes / 16u), vec_v = (uint32_t)(v_half_page_bytes / 16u);
+    const uint64_t total = (uint64_t)n_layers * (vec_k + vec_v);
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        const uint32_t v = (uint32_t)(i % vec_per_half);
-        const uint32_t lk = (uint32_t)(i / vec_per_half);
-        const uint32_t layer = lk >> 1;
-        uint8_t *base = (lk & 1u) ? v_base : k_base;
-        const uint4 *sp = reinterpret_cast<const uint4 *>(base + (uint64_t)layer * layer_bytes + (uint64_t)s * half_page_bytes);
-        uint4 *dp = reinterpret_cast<uint4 *>(base + (uint64_t)layer * layer_bytes + (uint64_t)d * half_page_bytes);
+        const uint32_t layer = (uint32_t)(i / (vec_k + vec_v));
+        const uint32_t r = (uint32_t)(i % (vec_k + vec_v));
+        const bool is_v = r >= vec_k;
+        const uint32_t v = is_v ? r - vec_k : r;
+        uint8_t *lay = is_v ? v_base + (uint64_t)layer * v_layer_bytes : k_base + (uint64_t)layer * layer_bytes;
+        const uint64_t page_bytes = is_v ? v_half_page_bytes : half_page_bytes;
+        const uint4 *sp = reinterpret_cast<const uint4 *>(lay + (uint64_t)s * page_bytes);
+        uint4 *dp = reinterpret_cast<uint4 *>(lay + (uint64_t)d * page_bytes);
         dp[v] = sp[v];
     }
 }
@@ -269,7 +273,7 @@ brc_status brc_page_gather(brc_pool *pool, uint32_t layer, const uint32_t *block
 
 brc_status brc_page_copy(brc_pool *pool, const uint32_t *src_ids_dev, const uint32_t *dst_ids_dev, uint32_t n,
                          void *stream) {
-    if (brc_status rc = need_device_pool(pool, "brc_page_copy")) return rc;
+    if (brc_status rc = need_device_pool(pool, "brc_page_copy", true)) return rc;
     if (n == 0) return BRC_OK;
     if (!src_ids_dev || !dst_ids_dev) return brc_fail(BRC_ERR_INVALID, "brc_page_copy: NULL id list");
     if (n > 65535u) return brc_fail(BRC_ERR_INVALID, "brc_page_copy: %u pairs in one call (limit 65535)", n);
@@ -280,7 +284,8 @@ brc_status brc_page_copy(brc_pool *pool, const uint32_t *src_ids_dev, const uint
     dim3 grid(gx, n);
     page_copy_kernel<<<grid, 256, 0, brc_stream(stream)>>>(pool->k_base, pool->v_base, src_ids_dev, dst_ids_dev,
                                                          pool->n_layers, pool->n_pages, pool->half_page_bytes,
-                                                         pool->layer_bytes, pool->status_dev);
+                                                         pool->layer_bytes, pool->v_layer_bytes / pool->n_pages,
+                                                         pool->v_layer_bytes, pool->status_dev);
     BRC_CUDA(cudaGetLastError());
     return BRC_OK;
 }
@@ -294,7 +299,7 @@ brc_status brc_seq_fork(brc_pool *pool, const uint32_t *parent_table, uint32_t n
     const uint32_t full = n_tokens / pt;
     const bool partial = (n_tokens % pt) != 0;
     if (partial)
-        if (brc_status rc = need_device_pool(pool, "brc_seq_fork (partial last page needs a device copy)")) return rc;
+        if (brc_status rc = need_device_pool(pool, "brc_seq_fork (partial last page needs a device copy)", true)) return rc;
     for (uint32_t i = 0; i < full + (partial ? 1u : 0u); ++i)
         if (parent_table[i] >= pool->n_pages)
             return brc_fail(BRC_ERR_INVALID, "brc_seq_fork: parent table entry %u is page %u of %u", i, parent_table[i],

@@ -1,0 +1,163 @@
+// Top-k block selection: the stage of the reference that turns indexer scores into the `ids` / `counts` lists the
+// selected-block attention walks (crates/breccia-kernels/shaders/qsa_topk.comp; CPU statement
+// cpu::topk_blocks, crates/breccia-kernels/src/qsa/cpu.rs:129-151).
+//
+// Contract, the shader's: per row, the min(n_blocks, topk_blocks) highest scores in DESCENDING score order, equal
+// scores resolved towards the LOWER block index; a score <= -1e29 (or NaN) is a dead block and is never selected
+// (the score stage writes that value for blocks the row must not see); then the row's own block
+// (pos / 4) is appended unless the selection already holds it.  `dense` (n_blocks <= topk_blocks): every block up to the
+// row's own, ascending, unscored.  The scores are left untouched (the shader destroys them).
+//
+// The reference runs k argmax passes over the row (O(k * n_blocks), 512 passes).  Here one CTA per row sorts
+// 64-bit keys (orderable score bits, then inverted block index) in shared memory with a bitonic network: rows of up
+// to 8192 blocks in one sort, longer rows in chunks of 7680 new keys merged with the 512 survivors so far, so any
+// row length works with the same 64 KiB of shared memory.
+#include <algorithm>
+
+#include "brc_device.cuh"
+#include "brc_internal.h"
+
+namespace {
+
+constexpr uint32_t TK_THREADS = 1024;
+constexpr uint32_t TK_SORT_MAX = 8192;      // keys per sort: 64 KiB of shared memory
+constexpr uint32_t TK_K_MAX = 1024;         // survivors carried between chunks (the reference's k is 512)
+constexpr uint32_t BLOCK_CELLS = 4;         // qsa::IDX_BLOCK
+
+struct TopkParams {
+    const float *scores;        // [rows][n_blocks]
+    const uint32_t *pos0;       // [n_seqs]
+    uint32_t *ids;              // [rows][max_ids]
+    uint32_t *counts;           // [rows]
+    uint32_t rows_per_seq, n_blocks, topk_blocks, max_ids, dense;
+};
+
+// Larger key = selected earlier: score ascending in the high word, lower block index larger in the low word.
+// Dead blocks (score <= -1e29, NaN) get key 0, below every live key.
+__device__ __forceinline__ uint64_t make_key(float s, uint32_t b) {
+    if (!(s > -1.0e29f)) return 0ull;
+    uint32_t u = s == 0.f ? 0u : __float_as_uint(s);          // -0 and +0 tie, as they compare equal
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return ((uint64_t)u << 32) | (uint64_t)(0xffffffffu - b);
+}
+
+// Descending bitonic sort of n (a power of two) keys in shared memory by the whole CTA.
+__device__ void sort_desc(uint64_t *keys, uint32_t n) {
+    for (uint32_t size = 2; size <= n; size <<= 1) {
+        for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+            __syncthreads();
+            for (uint32_t t = threadIdx.x; t < (n >> 1); t += TK_THREADS) {
+                const uint32_t lo = 2u * t - (t & (stride - 1u));   // insert a zero bit at the stride position
+                const uint32_t hi = lo + stride;
+                const bool down = (lo & size) == 0u;                // first half of each `size` run descends
+                const uint64_t a = keys[lo], b = keys[hi];
+                if ((a < b) == down) { keys[lo] = b; keys[hi] = a; }
+            }
+        }
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(TK_THREADS) topk_blocks_kernel(const TopkParams p) {
+    extern __shared__ uint64_t keys[];
+    __shared__ uint32_t s_count, s_present;
+    const uint32_t row = blockIdx.x, tid = threadIdx.x;
+    const uint32_t own = (p.pos0[row / p.rows_per_seq] + row % p.rows_per_seq) / BLOCK_CELLS;
+    uint32_t *ids = p.ids + (size_t)row * p.max_ids;
+
+    if (p.dense) {
+        uint32_t n = min(min(p.n_blocks, own + 1u), p.max_ids);
+        for (uint32_t i = tid; i < n; i += TK_THREADS) ids[i] = i;
+        if (tid == 0) {
+            if (own >= p.n_blocks && n < p.max_ids) ids[n++] = own;
+            p.counts[row] = n;
+        }
+        return;
+    }
+
+    const float *sc = p.scores + (size_t)row * p.n_blocks;
+    const uint32_t want = min(min(p.n_blocks, p.topk_blocks), p.max_ids);
+    uint32_t n_sort;
+    if (p.n_blocks <= TK_SORT_MAX) {
+        n_sort = 2;
+        while (n_sort < p.n_blocks) n_sort <<= 1;
+        for (uint32_t i = tid; i < n_sort; i += TK_THREADS) keys[i] = i < p.n_blocks ? make_key(sc[i], i) : 0ull;
+        sort_desc(keys, n_sort);
+    } else {
+        // survivors in keys[0 .. want), new keys behind them
+        n_sort = TK_SORT_MAX;
+        const uint32_t fresh = TK_SORT_MAX - want;
+        for (uint32_t i = tid; i < want; i += TK_THREADS) keys[i] = 0ull;
+        for (uint32_t at = 0; at < p.n_blocks; at += fresh) {
+            __syncthreads();
+            for (uint32_t i = tid; i < fresh; i += TK_THREADS)
+                keys[want + i] = at + i < p.n_blocks ? make_key(sc[at + i], at + i) : 0ull;
+            sort_desc(keys, TK_SORT_MAX);
+        }
+    }
+    // keys[0 .. want) are the selection, best first; dead keys (0) sort last
+    if (tid == 0) { s_count = 0; s_present = 0; }
+    __syncthreads();
+    for (uint32_t i = tid; i < want; i += TK_THREADS) {
+        const uint64_t k = keys[i];
+        if (k != 0ull) {
+            const uint32_t b = 0xffffffffu - (uint32_t)k;
+            ids[i] = b;
+            if (b == own) s_present = 1u;
+            if (i + 1u == want || keys[i + 1u] == 0ull) s_count = i + 1u;
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t count = s_count;
+        if (!s_present && count < p.max_ids) ids[count++] = own;
+        p.counts[row] = count;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+brc_status brc_topk_blocks(brc_pool *pool, const float *scores_dev, uint32_t n_seqs, uint32_t rows_per_seq, uint32_t n_blocks,
+                           uint32_t topk_blocks, uint32_t max_ids, const uint32_t *pos0_dev, int32_t dense,
+                           uint32_t *ids_out_dev, uint32_t *counts_out_dev, void *stream) {
+    if (!pool) return brc_fail(BRC_ERR_INVALID, "brc_topk_blocks: pool is NULL");
+    if (pool->device < 0) return brc_fail(BRC_ERR_CUDA, "brc_topk_blocks: this pool holds bookkeeping only (no device memory)");
+    if (n_seqs == 0 || rows_per_seq == 0) return BRC_OK;
+    if (!pos0_dev || !ids_out_dev || !counts_out_dev || (!dense && !scores_dev))
+        return brc_fail(BRC_ERR_INVALID, "brc_topk_blocks: NULL score, position, id or count pointer");
+    if (n_blocks == 0 || topk_blocks == 0) return brc_fail(BRC_ERR_INVALID, "brc_topk_blocks: n_blocks %u, topk_blocks %u", n_blocks, topk_blocks);
+    if (topk_blocks > TK_K_MAX)
+        return brc_fail(BRC_ERR_UNSUPPORTED, "brc_topk_blocks: topk_blocks %u (at most %u; the reference selects 512)", topk_blocks, TK_K_MAX);
+    if (max_ids < std::min(n_blocks, topk_blocks) + 1u)
+        return brc_fail(BRC_ERR_INVALID, "brc_topk_blocks: max_ids %u but a row can hold %u selected blocks and its own",
+                        max_ids, std::min(n_blocks, topk_blocks));
+    if (dense && n_blocks > topk_blocks)
+        return brc_fail(BRC_ERR_INVALID, "brc_topk_blocks: dense selection needs n_blocks %u <= topk_blocks %u", n_blocks, topk_blocks);
+    const uint64_t rows = (uint64_t)n_seqs * rows_per_seq;
+    if (rows > 0x7fffffffull) return brc_fail(BRC_ERR_INVALID, "brc_topk_blocks: %llu rows in one call", (unsigned long long)rows);
+    brc_device_guard guard(pool->device);
+    TopkParams p;
+    p.scores = scores_dev;
+    p.pos0 = pos0_dev;
+    p.ids = ids_out_dev;
+    p.counts = counts_out_dev;
+    p.rows_per_seq = rows_per_seq;
+    p.n_blocks = n_blocks;
+    p.topk_blocks = topk_blocks;
+    p.max_ids = max_ids;
+    p.dense = dense ? 1u : 0u;
+    uint32_t n_sort = TK_SORT_MAX;
+    if (n_blocks <= TK_SORT_MAX) {
+        n_sort = 2;
+        while (n_sort < n_blocks) n_sort <<= 1;
+    }
+    const size_t smem = dense ? 0 : (size_t)n_sort * sizeof(uint64_t);
+    BRC_CUDA(cudaFuncSetAttribute(topk_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(TK_SORT_MAX * sizeof(uint64_t))));
+    topk_blocks_kernel<<<(uint32_t)rows, TK_THREADS, smem, brc_stream(stream)>>>(p);
+    BRC_CUDA(cudaGetLastError());
+    return BRC_OK;
+}
+
+}  // extern "C"

@@ -394,6 +394,21 @@ def sparse_attend(pool: KvPool, layer: int, q: torch.Tensor, n_head: int, block_
               ids.shape[1], _ptr(counts), max_pos_end, 1.0 / math.sqrt(pool.head_dim), _ptr(out), _stream_ptr())
 
 
+def topk_blocks(pool: KvPool, scores: torch.Tensor, pos0: torch.Tensor, rows_per_seq: int, topk: int = 512,
+                dense: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    """The selection lists sparse_attend takes, from indexer scores [rows, n_blocks] f32 (reference: Qsa::topk,
+    shaders/qsa_topk.comp): per row the `topk` best blocks in descending score order (ties towards the lower
+    block, scores <= -1e29 never), then the row's own block.  Returns (ids [rows, min(n_blocks, topk) + 1] int32,
+    counts [rows] int32)."""
+    rows, n_blocks = scores.shape
+    max_ids = min(n_blocks, topk) + 1
+    ids = torch.empty((rows, max_ids), dtype=torch.int32, device=scores.device)
+    counts = torch.empty((rows,), dtype=torch.int32, device=scores.device)
+    _lib.call("brc_topk_blocks", pool.handle, _ptr(scores), pos0.numel(), rows_per_seq, n_blocks, topk, max_ids, _ptr(pos0),
+              1 if dense else 0, _ptr(ids), _ptr(counts), _stream_ptr())
+    return ids, counts
+
+
 def decode_partial_bytes(n_seqs: int, n_head: int, head_dim: int) -> int:
     out = C.c_uint64()
     _lib.call("brc_decode_partial_bytes", n_seqs, n_head, head_dim, C.byref(out))

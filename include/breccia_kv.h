@@ -91,8 +91,9 @@ BRC_API brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n
  * values against 64 B: 0.5625x the V bytes), rows in the order of the binary16
  * layout; K stays binary16.  Built for such a pool: brc_kv_append from f32 sources
  * (store rule of shaders/qsa_kv_append.comp:117-133), brc_paged_sparse_attn
- * (in-register dequantisation, qsa_attn_apply.comp:69-77), brc_pool_read /
- * brc_pool_write / brc_pool_v_ptr, the allocator and the prefix tree.  Every other
+ * (in-register dequantisation, qsa_attn_apply.comp:69-77), brc_page_copy and
+ * brc_seq_fork (whole pages, bytes as they are), brc_pool_read / brc_pool_write /
+ * brc_pool_v_ptr, the allocator and the prefix tree.  Every other
  * entry point that reads or writes V refuses it with BRC_ERR_UNSUPPORTED. */
 #define BRC_V_F16 0
 #define BRC_V_Q8_0 1
@@ -463,6 +464,21 @@ BRC_API brc_status brc_decode_step_host(brc_pool *pool, uint32_t layer0, uint32_
                                         int32_t kv_dtype, float scale, float *out_host, void *staging_dev,
                                         uint64_t staging_bytes, void *workspace_dev, uint64_t workspace_bytes,
                                         void *stream);
+
+/* ---------------------------------------------------------------- top-k block selection
+ * Replaces shaders/qsa_topk.comp (CPU statement cpu::topk_blocks, qsa/cpu.rs:129-151): turns a row's
+ * indexer scores into the `ids` / `counts` lists brc_paged_sparse_attn walks.  Per row (row = sequence *
+ * rows_per_seq + t, position pos0[sequence] + t): the min(n_blocks, topk_blocks) highest scores in
+ * DESCENDING score order, equal scores towards the LOWER block index; a score <= -1e29 or NaN marks a
+ * block the row must not see and is never selected; then the row's own block (position / 4) is
+ * appended unless already selected.  `dense` != 0 (needs n_blocks <= topk_blocks): every block up to the
+ * row's own, ascending, scores not read.  scores [rows][n_blocks] f32 are left untouched (the
+ * reference's shader destroys them); ids_out [rows][max_ids], max_ids >= min(n_blocks, topk_blocks) + 1;
+ * counts_out [rows].  topk_blocks <= 1024 (the reference selects 512); any n_blocks. */
+BRC_API brc_status brc_topk_blocks(brc_pool *pool, const float *scores_dev, uint32_t n_seqs, uint32_t rows_per_seq,
+                                   uint32_t n_blocks, uint32_t topk_blocks, uint32_t max_ids,
+                                   const uint32_t *pos0_dev, int32_t dense, uint32_t *ids_out_dev,
+                                   uint32_t *counts_out_dev, void *stream);
 
 /* ---------------------------------------------------------------- chunked-prefill attention (tensor cores)
  * Replaces the reference's T >= 16 path: qsa_attn_scores_gqa.comp + ops_softmax.comp

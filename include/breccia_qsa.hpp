@@ -51,11 +51,24 @@ struct DeviceAlloc {
 
 constexpr uint32_t PAGE_CELLS = 16;   // qsa/mod.rs:114
 
+// How V page bodies are stored (the reference's VLayout, qsa/mod.rs:245-290): binary16 like K, or q8_0 blocks
+// of one f32 scale + 32 signed bytes (0.5625x the V bytes).  K is binary16 in both.
+enum class VLayout : int32_t { F16 = BRC_V_F16, Q8_0 = BRC_V_Q8_0 };
+
 class KvPool {
 public:
-    KvPool(int32_t device, uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim, uint32_t n_pages) {
-        check(brc_pool_create(device, n_layers, n_kv_head, head_dim, PAGE_CELLS, n_pages, &raw_));
+    KvPool(int32_t device, uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim, uint32_t n_pages,
+           VLayout v_layout = VLayout::F16) {
+        if (v_layout == VLayout::Q8_0)
+            check(brc_pool_create_q8v(device, n_layers, n_kv_head, head_dim, PAGE_CELLS, n_pages, &raw_));
+        else
+            check(brc_pool_create(device, n_layers, n_kv_head, head_dim, PAGE_CELLS, n_pages, &raw_));
         n_layers_ = n_layers, n_kv_head_ = n_kv_head, head_dim_ = head_dim, n_pages_ = n_pages;
+    }
+    VLayout v_layout() const {
+        int32_t v = 0;
+        check(brc_pool_v_layout(raw_, &v));
+        return static_cast<VLayout>(v);
     }
     // bookkeeping only (allocator + refcounts, no device memory): schedulers and CPU tests
     static KvPool bookkeeping(uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim, uint32_t n_pages) {

@@ -49,6 +49,7 @@ static void write_file(const std::string &path, const std::vector<T> &v) {
 static int run_cpu() {
     brc::KvPool pool = brc::KvPool::bookkeeping(12, 2, 256, 64);
     REQUIRE(pool.free_pages() == 64);
+    REQUIRE(pool.v_layout() == brc::VLayout::F16);
     brc::DeviceAlloc none;   // no device: states keep their tables on the host only
     {
         brc::QsaState a(pool, none, 0, 100);   // 7 pages

@@ -105,3 +105,31 @@ def test_entry_points_built_for_binary16_v_refuse_a_q8_0_pool(cuda_device):
     assert err.value.code == _lib.ERR_UNSUPPORTED
     assert pool.alloc(3).size == 3                  # the allocator works as on any pool
     pool.release()
+
+
+def test_fork_copies_the_partial_last_page_of_a_q8_0_pool_as_it_is(cuda_device):
+    """Copy-on-write fork on a q8_0 V pool: full pages shared, the partial last page copied in every layer, K as
+    binary16 and V as its q8_0 bytes; the parent's pages and all other pages stay as they were."""
+    n_kv, hd, n_layers, cells = 2, 256, 3, 21
+    pool = KvPool(0, n_layers, n_kv, hd, 8, v_q8=True)
+    parent = pool.alloc(2)
+    for layer in range(n_layers):
+        k_rows = oracle.normalish(0x51 + layer, cells * n_kv * hd).reshape(cells, n_kv * hd)
+        v_rows = oracle.normalish(0x61 + layer, cells * n_kv * hd).reshape(cells, n_kv * hd)
+        append(pool, layer, parent, 0, k_rows, v_rows)
+    before = [(pool.read(0, layer), pool.read(1, layer)) for layer in range(n_layers)]
+    child, fresh = pool.fork(parent, cells)
+    torch.cuda.synchronize()
+    pool.check()
+    assert child[0] == parent[0] and fresh is not None and child[1] == fresh and fresh not in parent.tolist()
+    rows = n_kv * 16
+    for layer in range(n_layers):
+        k_now, v_now = pool.read(0, layer), pool.read(1, layer)
+        assert np.array_equal(k_now[fresh], before[layer][0][parent[1]])
+        assert np.array_equal(v_now[fresh * rows:(fresh + 1) * rows], before[layer][1][parent[1] * rows:(parent[1] + 1) * rows])
+        assert v_now[fresh * rows:(fresh + 1) * rows].any()
+        keep = [p for p in range(8) if p != fresh]
+        assert np.array_equal(k_now[keep], before[layer][0][keep])
+        v_pages_now, v_pages_before = v_now.reshape(8, -1), before[layer][1].reshape(8, -1)
+        assert np.array_equal(v_pages_now[keep], v_pages_before[keep])
+    pool.release()

@@ -1,0 +1,77 @@
+"""Top-k block selection on the GPU (brc_topk_blocks) against the oracle, id for id and in order — the reference
+tests its shader the same way (exact ids, crates/breccia-kernels/tests/attn_conformance.rs:1457-1513).  Scores are
+drawn from a small set of values so that ties are everywhere, some blocks are dead, and row lengths cross the
+one-sort limit (8192 blocks) into the chunked path."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from oracle.topk_ref import dense_blocks, topk_blocks
+from breccia_b200 import _lib
+from breccia_b200.qsa import KvPool
+from helpers import dev_u32
+
+pytestmark = pytest.mark.gpu
+P = lambda x: C.c_void_p(x.data_ptr())
+
+
+def run_topk(pool, scores, pos0s, rows_per_seq, k, max_ids, dense=False):
+    rows, n_blocks = scores.shape
+    sd = torch.from_numpy(scores).cuda()
+    before = sd.clone()
+    ids = torch.full((rows, max_ids), 0x7FFFFFFF, dtype=torch.int32, device="cuda")
+    counts = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+    p_dev = dev_u32(np.asarray(pos0s))
+    _lib.call("brc_topk_blocks", pool.handle, P(sd), len(pos0s), rows_per_seq, n_blocks, k, max_ids, P(p_dev), 1 if dense else 0,
+              P(ids), P(counts), None)
+    pool.check()
+    assert torch.equal(sd.view(torch.int32), before.view(torch.int32)), "the scores must be left untouched"
+    return ids.cpu().numpy(), counts.cpu().numpy()
+
+
+def make_scores(seed, rows, n_blocks, levels):
+    rng = np.random.default_rng(seed)
+    s = rng.integers(-levels, levels, size=(rows, n_blocks)).astype(np.float32) * np.float32(0.25)
+    s[rng.random((rows, n_blocks)) < 0.1] = np.float32(-1.0e30)       # masked by the score stage
+    s[rng.random((rows, n_blocks)) < 0.01] = np.float32(np.nan)
+    s[rng.random((rows, n_blocks)) < 0.02] = np.float32(-0.0)
+    return s
+
+
+@pytest.mark.parametrize("n_blocks,k,levels", [(3, 512, 2), (100, 512, 4), (513, 512, 50), (700, 512, 3), (8192, 512, 1000),
+                                               (8193, 512, 20), (20000, 512, 5000), (20000, 37, 3), (65536, 512, 100000)])
+def test_selection_matches_the_oracle_id_for_id(cuda_device, n_blocks, k, levels):
+    pool = KvPool(0, 1, 2, 256, 4)
+    n_seqs, rows_per_seq = 3, 2
+    max_ids = min(n_blocks, k) + 1
+    scores = make_scores(n_blocks + k, n_seqs * rows_per_seq, n_blocks, levels)
+    scores[1, :] = np.float32(-1.0e30)                               # a row with nothing visible: only its own block
+    pos0s = [4 * n_blocks - 9, 5, 4 * (n_blocks // 2)]
+    ids, counts = run_topk(pool, scores, pos0s, rows_per_seq, k, max_ids)
+    for row in range(n_seqs * rows_per_seq):
+        own = (pos0s[row // rows_per_seq] + row % rows_per_seq) // 4
+        want = topk_blocks(scores[row], k, own, max_ids)
+        assert counts[row] == len(want), f"row {row}: count {counts[row]} != {len(want)}"
+        assert ids[row, :len(want)].tolist() == want, f"row {row}"
+    pool.release()
+
+
+def test_dense_selection_and_refusals(cuda_device):
+    pool = KvPool(0, 1, 2, 256, 4)
+    scores = np.zeros((4, 40), np.float32)
+    pos0s = [0, 158]                                                 # rows at positions 0, 1, 158, 159 -> own blocks 0, 0, 39, 39
+    ids, counts = run_topk(pool, scores, pos0s, 2, 512, 41, dense=True)
+    for row, pos in enumerate([0, 1, 158, 159]):
+        want = dense_blocks(40, pos // 4, 41)
+        assert counts[row] == len(want) and ids[row, :len(want)].tolist() == want
+    ids, counts = run_topk(pool, scores, [400], 4, 512, 41, dense=True)    # own block 100 lies beyond the 40 scored blocks
+    assert counts.tolist() == [41] * 4 and ids[0, 40] == 100
+    x = torch.zeros(64, device="cuda")
+    for args, code in (((P(x), 1, 1, 40, 512, 40), _lib.ERR_INVALID),            # max_ids too small for 40 blocks + own
+                       ((P(x), 1, 1, 40, 2000, 41), _lib.ERR_UNSUPPORTED)):      # k beyond the kernel's survivors
+        with pytest.raises(_lib.BrcError) as err:
+            _lib.call("brc_topk_blocks", pool.handle, *args, P(x), 0, P(x), P(x), None)
+        assert err.value.code == code
+    pool.release()
