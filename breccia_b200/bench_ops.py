@@ -2,7 +2,7 @@
 --op qsa`, crates/breccia-kernels/src/qsa/bench.rs; one JSON line per cell with the fields of its
 `OpCell`: op, case, units, bytes or flops, us, GB/s or TFLOP/s, iters).
 
-    python -m breccia_b200.bench_ops [--op prefill|prepare|sparse|movers|all] [--iters N]
+    python -m breccia_b200.bench_ops [--op prefill|prepare|sparse|topk|movers|all] [--iters N]
 
 Timing: CUDA events on the launching stream, 3 warm-up runs, the mean of `iters` runs.  Shapes are the
 benchmark configurations: prefill = 64 sequences sharing a 4096-token prefix, 256-token chunk each
@@ -152,9 +152,9 @@ def bench_sparse(iters: int):
     from .qsa import sparse_attend
 
     n_head, ctx, n_sel = 24, 32768, 513
-    for n_seqs in (1, 32):
+    for n_seqs, v_q8 in ((1, False), (32, False), (1, True), (32, True)):
         pages = ctx // 16
-        pool = KvPool(0, 1, N_KV, HD, n_seqs * pages)
+        pool = KvPool(0, 1, N_KV, HD, n_seqs * pages, v_q8=v_q8)
         tables = synth.permutation(3, n_seqs * pages).reshape(n_seqs, pages)
         ids = np.stack([np.sort(synth.permutation(10 + s, ctx // 4)[:n_sel]) for s in range(n_seqs)]).astype(np.uint32)
         gen = torch.Generator(device="cuda")
@@ -169,10 +169,31 @@ def bench_sparse(iters: int):
 
         us = timed(run, iters)
         pool.check()
-        nbytes = n_seqs * n_sel * 4 * N_KV * HD * 2 * 2      # every selected cell's K and V once per kv head
+        # every selected cell's K and V once per kv head; a q8_0 V row is 9/16 of a binary16 one
+        nbytes = int(n_seqs * n_sel * 4 * N_KV * HD * 2 * (1 + (0.5625 if v_q8 else 1)))
         emit(op="paged_sparse_attn", case=f"{n_seqs} sequence(s), 1 row each, {n_sel} selected blocks = {n_sel * 4} cells of {ctx}, "
-             f"{n_head}q/{N_KV}kv hd{HD}, 1 layer", units=n_seqs, bytes=nbytes, us=us, gbps=nbytes / us / 1e3, iters=iters)
+             f"{n_head}q/{N_KV}kv hd{HD}, 1 layer, V {'q8_0' if v_q8 else 'f16'}", units=n_seqs, bytes=nbytes, us=us,
+             gbps=nbytes / us / 1e3, iters=iters)
         pool.release()
+
+
+def bench_topk(iters: int):
+    """Top-k block selection at the reference's shapes: 512 of 8192 blocks (32 768 cells) for one decode row, for 32
+    rows and for a 256-row prefill chunk of 8 sequences; 512 of 65 536 blocks (its longest cache) for one row."""
+    from .qsa import topk_blocks
+
+    pool = KvPool(0, 1, N_KV, HD, 4)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(7)
+    for n_seqs, rows_per_seq, n_blocks in ((1, 1, 8192), (32, 1, 8192), (8, 256, 8192), (1, 1, 65536)):
+        rows = n_seqs * rows_per_seq
+        scores = torch.randn((rows, n_blocks), generator=gen, device="cuda")
+        pos0 = dev_u32(np.full(n_seqs, 4 * n_blocks - rows_per_seq))
+        us = timed(lambda: topk_blocks(pool, scores, pos0, rows_per_seq), iters)
+        pool.check()
+        emit(op="topk_blocks", case=f"{rows} row(s) x {n_blocks} blocks, top 512 + own block", units=rows,
+             bytes=rows * n_blocks * 4, us=us, gbps=rows * n_blocks * 4 / us / 1e3, iters=iters)
+    pool.release()
 
 
 def bench_movers(iters: int):
@@ -236,7 +257,7 @@ def bench_movers(iters: int):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "prefill", "prepare", "sparse", "movers"])
+    ap.add_argument("--op", default="all", choices=["all", "prefill", "prepare", "sparse", "topk", "movers"])
     ap.add_argument("--iters", type=int, default=20)
     a = ap.parse_args()
     if not torch.cuda.is_available():
@@ -249,6 +270,8 @@ def main():
         bench_prepare(a.iters)
     if a.op in ("all", "sparse"):
         bench_sparse(a.iters)
+    if a.op in ("all", "topk"):
+        bench_topk(a.iters)
     if a.op in ("all", "movers"):
         bench_movers(a.iters)
 

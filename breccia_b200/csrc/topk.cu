@@ -8,10 +8,11 @@
 // (pos / 4) is appended unless the selection already holds it.  `dense` (n_blocks <= topk_blocks): every block up to the
 // row's own, ascending, unscored.  The scores are left untouched (the shader destroys them).
 //
-// The reference runs k argmax passes over the row (O(k * n_blocks), 512 passes).  Here one CTA per row sorts
-// 64-bit keys (orderable score bits, then inverted block index) in shared memory with a bitonic network: rows of up
-// to 8192 blocks in one sort, longer rows in chunks of 7680 new keys merged with the 512 survivors so far, so any
-// row length works with the same 64 KiB of shared memory.
+// The reference runs k argmax passes over the row (O(k * n_blocks), 512 passes).  Here one CTA per row selects with a
+// bitonic network over 64-bit keys (orderable score bits, then inverted block index) in shared memory: runs of k keys
+// are sorted, then pairs of runs are reduced to their k largest until one run is left.  Rows of up to 8192 blocks
+// take one pass; longer rows go in chunks of 8192 whose best k are merged with the best so far, so any row length
+// works with the same 72 KiB of shared memory.
 #include <algorithm>
 
 #include "brc_device.cuh"
@@ -41,19 +42,48 @@ __device__ __forceinline__ uint64_t make_key(float s, uint32_t b) {
     return ((uint64_t)u << 32) | (uint64_t)(0xffffffffu - b);
 }
 
-// Descending bitonic sort of n (a power of two) keys in shared memory by the whole CTA.
-__device__ void sort_desc(uint64_t *keys, uint32_t n) {
-    for (uint32_t size = 2; size <= n; size <<= 1) {
-        for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
-            __syncthreads();
-            for (uint32_t t = threadIdx.x; t < (n >> 1); t += TK_THREADS) {
-                const uint32_t lo = 2u * t - (t & (stride - 1u));   // insert a zero bit at the stride position
-                const uint32_t hi = lo + stride;
-                const bool down = (lo & size) == 0u;                // first half of each `size` run descends
-                const uint64_t a = keys[lo], b = keys[hi];
-                if ((a < b) == down) { keys[lo] = b; keys[hi] = a; }
+// One compare-exchange stage of the bitonic network over keys[0 .. n): partners `stride` apart, runs of `size`
+// alternately descending and ascending (the first descends).
+__device__ __forceinline__ void stage(uint64_t *keys, uint32_t n, uint32_t size, uint32_t stride) {
+    __syncthreads();
+    for (uint32_t t = threadIdx.x; t < (n >> 1); t += TK_THREADS) {
+        const uint32_t lo = 2u * t - (t & (stride - 1u));   // insert a zero bit at the stride position
+        const uint32_t hi = lo + stride;
+        const bool down = (lo & size) == 0u;
+        const uint64_t a = keys[lo], b = keys[hi];
+        if ((a < b) == down) { keys[lo] = b; keys[hi] = a; }
+    }
+}
+
+// The `run` largest of keys[0 .. n) (n and run powers of two, run <= n <= TK_SORT_MAX), left in keys[0 .. run) in
+// descending order.  Runs of `run` keys are sorted in alternating directions; then, while more than one run is left,
+// each descending / ascending pair of runs is replaced by its element-wise maximum (a bitonic sequence that holds the
+// pair's `run` largest keys) and the halved array is merged back into sorted runs.  Against a full sort this does the
+// later, widest stages on ever fewer keys.
+__device__ void top_run(uint64_t *keys, uint32_t n, uint32_t run) {
+    for (uint32_t size = 2; size <= run; size <<= 1)
+        for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) stage(keys, n, size, stride);
+    while (n > run) {
+        const uint32_t half = n >> 1;
+        uint64_t m[TK_SORT_MAX / 2 / TK_THREADS];
+        __syncthreads();
+#pragma unroll
+        for (uint32_t r = 0; r < TK_SORT_MAX / 2 / TK_THREADS; ++r) {
+            const uint32_t t = threadIdx.x + r * TK_THREADS;
+            if (t < half) {
+                const uint32_t j = t / run, i = t % run;
+                const uint64_t a = keys[2u * j * run + i], b = keys[(2u * j + 1u) * run + i];
+                m[r] = a > b ? a : b;
             }
         }
+        __syncthreads();
+#pragma unroll
+        for (uint32_t r = 0; r < TK_SORT_MAX / 2 / TK_THREADS; ++r) {
+            const uint32_t t = threadIdx.x + r * TK_THREADS;
+            if (t < half) keys[t] = m[r];
+        }
+        n = half;
+        for (uint32_t stride = run >> 1; stride > 0; stride >>= 1) stage(keys, n, run, stride);
     }
     __syncthreads();
 }
@@ -77,23 +107,32 @@ __global__ void __launch_bounds__(TK_THREADS) topk_blocks_kernel(const TopkParam
 
     const float *sc = p.scores + (size_t)row * p.n_blocks;
     const uint32_t want = min(min(p.n_blocks, p.topk_blocks), p.max_ids);
-    uint32_t n_sort;
+    uint32_t run = 2;
+    while (run < want) run <<= 1;
     if (p.n_blocks <= TK_SORT_MAX) {
-        n_sort = 2;
+        uint32_t n_sort = 2;
         while (n_sort < p.n_blocks) n_sort <<= 1;
         for (uint32_t i = tid; i < n_sort; i += TK_THREADS) keys[i] = i < p.n_blocks ? make_key(sc[i], i) : 0ull;
-        sort_desc(keys, n_sort);
+        top_run(keys, n_sort, min(run, n_sort));
     } else {
-        // survivors in keys[0 .. want), new keys behind them
-        n_sort = TK_SORT_MAX;
-        const uint32_t fresh = TK_SORT_MAX - want;
-        for (uint32_t i = tid; i < want; i += TK_THREADS) keys[i] = 0ull;
-        for (uint32_t at = 0; at < p.n_blocks; at += fresh) {
+        // chunks of TK_SORT_MAX scores: the chunk's best `run`, merged with the best so far (kept behind the chunk)
+        uint64_t *best = keys + TK_SORT_MAX;
+        for (uint32_t i = tid; i < run; i += TK_THREADS) best[i] = 0ull;
+        for (uint32_t at = 0; at < p.n_blocks; at += TK_SORT_MAX) {
             __syncthreads();
-            for (uint32_t i = tid; i < fresh; i += TK_THREADS)
-                keys[want + i] = at + i < p.n_blocks ? make_key(sc[at + i], at + i) : 0ull;
-            sort_desc(keys, TK_SORT_MAX);
+            for (uint32_t i = tid; i < TK_SORT_MAX; i += TK_THREADS)
+                keys[i] = at + i < p.n_blocks ? make_key(sc[at + i], at + i) : 0ull;
+            top_run(keys, TK_SORT_MAX, run);
+            // both descending: the maximum of best[i] and the chunk's run read backwards is bitonic
+            for (uint32_t i = tid; i < run; i += TK_THREADS) {
+                const uint64_t a = best[i], b = keys[run - 1u - i];
+                best[i] = a > b ? a : b;
+            }
+            for (uint32_t stride = run >> 1; stride > 0; stride >>= 1) stage(best, run, run, stride);
         }
+        __syncthreads();
+        for (uint32_t i = tid; i < run; i += TK_THREADS) keys[i] = best[i];
+        __syncthreads();
     }
     // keys[0 .. want) are the selection, best first; dead keys (0) sort last
     if (tid == 0) { s_count = 0; s_present = 0; }
@@ -148,13 +187,13 @@ brc_status brc_topk_blocks(brc_pool *pool, const float *scores_dev, uint32_t n_s
     p.topk_blocks = topk_blocks;
     p.max_ids = max_ids;
     p.dense = dense ? 1u : 0u;
-    uint32_t n_sort = TK_SORT_MAX;
+    uint32_t n_keys = TK_SORT_MAX + TK_K_MAX;           // a chunk and the best so far
     if (n_blocks <= TK_SORT_MAX) {
-        n_sort = 2;
-        while (n_sort < n_blocks) n_sort <<= 1;
+        n_keys = 2;
+        while (n_keys < n_blocks) n_keys <<= 1;
     }
-    const size_t smem = dense ? 0 : (size_t)n_sort * sizeof(uint64_t);
-    BRC_CUDA(cudaFuncSetAttribute(topk_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(TK_SORT_MAX * sizeof(uint64_t))));
+    const size_t smem = dense ? 0 : (size_t)n_keys * sizeof(uint64_t);
+    BRC_CUDA(cudaFuncSetAttribute(topk_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((TK_SORT_MAX + TK_K_MAX) * sizeof(uint64_t))));
     topk_blocks_kernel<<<(uint32_t)rows, TK_THREADS, smem, brc_stream(stream)>>>(p);
     BRC_CUDA(cudaGetLastError());
     return BRC_OK;
