@@ -75,3 +75,35 @@ def test_dense_selection_and_refusals(cuda_device):
             _lib.call("brc_topk_blocks", pool.handle, *args, P(x), 0, P(x), P(x), None)
         assert err.value.code == code
     pool.release()
+
+
+def test_selection_feeds_the_selected_block_attention(cuda_device):
+    """Scores -> brc_topk_blocks -> brc_paged_sparse_attn on the lists it wrote (descending-score order, own block last)
+    against the oracle's attention over the oracle's selection: the two stages fit together without a host round trip."""
+    import oracle
+    from breccia_b200 import synth
+    from breccia_b200.qsa import sparse_attend, topk_blocks as gpu_topk
+    from helpers import ATTN_MAX_ABS, ATTN_MAX_REL, attention_errors, fill_pool_from_host
+
+    n_head, n_kv, hd, pos, k_sel = 16, 2, 256, 4101, 64
+    n_blocks = pos // 4 + 1
+    n_pages = (pos + 16) // 16
+    pool = KvPool(0, 1, n_kv, hd, n_pages + 3)
+    k, v = fill_pool_from_host(pool, 0, 930)
+    table = synth.permutation(931, n_pages + 3)[:n_pages].astype(np.uint32)
+    scores = make_scores(932, 1, n_blocks, 6)
+    scores[0, n_blocks - 1] = np.float32(-1.0e30)          # the row's own block is not scored: it must still be attended
+    q = oracle.normalish(933, n_head * hd).reshape(1, n_head, hd)
+    ids, counts = gpu_topk(pool, torch.from_numpy(scores).cuda(), dev_u32(np.array([pos])), 1, topk=k_sel)
+    want_ids = topk_blocks(scores[0], k_sel, pos // 4, k_sel + 1)
+    assert counts.item() == len(want_ids) == k_sel + 1 and ids[0].tolist() == want_ids
+    out = torch.full((1, n_head, hd), float("nan"), device="cuda")
+    sparse_attend(pool, 0, torch.from_numpy(q).cuda(), n_head, dev_u32(table[None, :]), dev_u32(np.array([pos])), 1, ids, counts,
+                  pos + 1, out)
+    pool.check()
+    _, kf = oracle.gather(k, table, n_pages * 16, n_kv, hd)
+    _, vf = oracle.gather(v, table, n_pages * 16, n_kv, hd)
+    want = oracle.attend(q[0], kf, vf, oracle.cells_of(want_ids, 4), pos, n_head, n_kv, hd)
+    max_abs, max_rel, ref = attention_errors(out.cpu().numpy()[0], want)
+    assert max_abs <= ATTN_MAX_ABS and max_rel <= ATTN_MAX_REL and ref <= 1e-5
+    pool.release()
