@@ -55,14 +55,65 @@ __device__ __forceinline__ void stage(uint64_t *keys, uint32_t n, uint32_t size,
     }
 }
 
+// Compare-exchanges `stride` apart inside a group of 8 keys held in registers (indices are compile-time constants
+// after unrolling).  `base` is the index of the group's first key in the array, for the direction of each pair.
+template <uint32_t STRIDE>
+__device__ __forceinline__ void reg_stage(uint64_t (&k)[8], uint32_t base, uint32_t size) {
+#pragma unroll
+    for (uint32_t i = 0; i < 8; ++i) {
+        if ((i & STRIDE) == 0u) {
+            const bool down = ((base + i) & size) == 0u;
+            const uint64_t a = k[i], b = k[i + STRIDE];
+            if ((a < b) == down) { k[i] = b; k[i + STRIDE] = a; }
+        }
+    }
+}
+
+// The last three stages (strides 4, 2, 1) of the `size` network, or with FIRST the whole network up to size 8:
+// every thread takes groups of 8 neighbouring keys through registers, one barrier instead of three (or six).
+template <bool FIRST>
+__device__ __forceinline__ void stages_in_registers(uint64_t *keys, uint32_t n, uint32_t size) {
+    __syncthreads();
+    for (uint32_t g = threadIdx.x; g < (n >> 3); g += TK_THREADS) {
+        uint64_t k[8];
+        const uint32_t base = g << 3;
+#pragma unroll
+        for (uint32_t i = 0; i < 8; ++i) k[i] = keys[base + i];
+        if (FIRST) {
+            reg_stage<1>(k, base, 2);
+            reg_stage<2>(k, base, 4);
+            reg_stage<1>(k, base, 4);
+        }
+        reg_stage<4>(k, base, size);
+        reg_stage<2>(k, base, size);
+        reg_stage<1>(k, base, size);
+#pragma unroll
+        for (uint32_t i = 0; i < 8; ++i) keys[base + i] = k[i];
+    }
+}
+
+// The stages of the `size` network from stride `from` down to 1.
+__device__ __forceinline__ void stages_down(uint64_t *keys, uint32_t n, uint32_t size, uint32_t from) {
+    if (n >= 8u && size >= 8u) {
+        for (uint32_t stride = from; stride >= 8u; stride >>= 1) stage(keys, n, size, stride);
+        stages_in_registers<false>(keys, n, size);
+    } else {
+        for (uint32_t stride = from; stride > 0; stride >>= 1) stage(keys, n, size, stride);
+    }
+}
+
 // The `run` largest of keys[0 .. n) (n and run powers of two, run <= n <= TK_SORT_MAX), left in keys[0 .. run) in
 // descending order.  Runs of `run` keys are sorted in alternating directions; then, while more than one run is left,
 // each descending / ascending pair of runs is replaced by its element-wise maximum (a bitonic sequence that holds the
 // pair's `run` largest keys) and the halved array is merged back into sorted runs.  Against a full sort this does the
 // later, widest stages on ever fewer keys.
 __device__ void top_run(uint64_t *keys, uint32_t n, uint32_t run) {
-    for (uint32_t size = 2; size <= run; size <<= 1)
-        for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) stage(keys, n, size, stride);
+    uint32_t size = 2;
+    if (n >= 8u && run >= 8u) {
+        stages_in_registers<true>(keys, n, 8);    // sizes 2, 4 and 8 in one go
+        size = 16;
+    }
+    for (; size <= run; size <<= 1) stages_down(keys, n, size, size >> 1);
     while (n > run) {
         const uint32_t half = n >> 1;
         uint64_t m[TK_SORT_MAX / 2 / TK_THREADS];
@@ -83,7 +134,7 @@ __device__ void top_run(uint64_t *keys, uint32_t n, uint32_t run) {
             if (t < half) keys[t] = m[r];
         }
         n = half;
-        for (uint32_t stride = run >> 1; stride > 0; stride >>= 1) stage(keys, n, run, stride);
+        stages_down(keys, n, run, run >> 1);
     }
     __syncthreads();
 }
@@ -128,7 +179,7 @@ __global__ void __launch_bounds__(TK_THREADS) topk_blocks_kernel(const TopkParam
                 const uint64_t a = best[i], b = keys[run - 1u - i];
                 best[i] = a > b ? a : b;
             }
-            for (uint32_t stride = run >> 1; stride > 0; stride >>= 1) stage(best, run, run, stride);
+            stages_down(best, run, run, run >> 1);
         }
         __syncthreads();
         for (uint32_t i = tid; i < run; i += TK_THREADS) keys[i] = best[i];
