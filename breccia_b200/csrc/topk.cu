@@ -12,7 +12,7 @@
 // bitonic network over 64-bit keys (orderable score bits, then inverted block index) in shared memory: runs of k keys
 // are sorted, then pairs of runs are reduced to their k largest until one run is left.  Rows of up to 8192 blocks
 // take one pass; longer rows go in chunks of 8192 whose best k are merged with the best so far, so any row length
-// works with the same 72 KiB of shared memory.
+// works with the same 81 KiB of shared memory.
 #include <algorithm>
 
 #include "brc_device.cuh"
@@ -42,6 +42,10 @@ __device__ __forceinline__ uint64_t make_key(float s, uint32_t b) {
     return ((uint64_t)u << 32) | (uint64_t)(0xffffffffu - b);
 }
 
+// Where key i lives in shared memory: one unused slot after every 8 keys, so that threads which each read 8
+// neighbouring keys (lanes 72 bytes apart instead of 64) spread over all banks.
+__device__ __forceinline__ uint32_t pad(uint32_t i) { return i + (i >> 3); }
+
 // One compare-exchange stage of the bitonic network over keys[0 .. n): partners `stride` apart, runs of `size`
 // alternately descending and ascending (the first descends).
 __device__ __forceinline__ void stage(uint64_t *keys, uint32_t n, uint32_t size, uint32_t stride) {
@@ -50,8 +54,8 @@ __device__ __forceinline__ void stage(uint64_t *keys, uint32_t n, uint32_t size,
         const uint32_t lo = 2u * t - (t & (stride - 1u));   // insert a zero bit at the stride position
         const uint32_t hi = lo + stride;
         const bool down = (lo & size) == 0u;
-        const uint64_t a = keys[lo], b = keys[hi];
-        if ((a < b) == down) { keys[lo] = b; keys[hi] = a; }
+        const uint64_t a = keys[pad(lo)], b = keys[pad(hi)];
+        if ((a < b) == down) { keys[pad(lo)] = b; keys[pad(hi)] = a; }
     }
 }
 
@@ -78,7 +82,7 @@ __device__ __forceinline__ void stages_in_registers(uint64_t *keys, uint32_t n, 
         uint64_t k[8];
         const uint32_t base = g << 3;
 #pragma unroll
-        for (uint32_t i = 0; i < 8; ++i) k[i] = keys[base + i];
+        for (uint32_t i = 0; i < 8; ++i) k[i] = keys[base + g + i];   // pad(base + i) = base + g + i
         if (FIRST) {
             reg_stage<1>(k, base, 2);
             reg_stage<2>(k, base, 4);
@@ -88,7 +92,7 @@ __device__ __forceinline__ void stages_in_registers(uint64_t *keys, uint32_t n, 
         reg_stage<2>(k, base, size);
         reg_stage<1>(k, base, size);
 #pragma unroll
-        for (uint32_t i = 0; i < 8; ++i) keys[base + i] = k[i];
+        for (uint32_t i = 0; i < 8; ++i) keys[base + g + i] = k[i];
     }
 }
 
@@ -123,7 +127,7 @@ __device__ void top_run(uint64_t *keys, uint32_t n, uint32_t run) {
             const uint32_t t = threadIdx.x + r * TK_THREADS;
             if (t < half) {
                 const uint32_t j = t / run, i = t % run;
-                const uint64_t a = keys[2u * j * run + i], b = keys[(2u * j + 1u) * run + i];
+                const uint64_t a = keys[pad(2u * j * run + i)], b = keys[pad((2u * j + 1u) * run + i)];
                 m[r] = a > b ? a : b;
             }
         }
@@ -131,7 +135,7 @@ __device__ void top_run(uint64_t *keys, uint32_t n, uint32_t run) {
 #pragma unroll
         for (uint32_t r = 0; r < TK_SORT_MAX / 2 / TK_THREADS; ++r) {
             const uint32_t t = threadIdx.x + r * TK_THREADS;
-            if (t < half) keys[t] = m[r];
+            if (t < half) keys[pad(t)] = m[r];
         }
         n = half;
         stages_down(keys, n, run, run >> 1);
@@ -163,38 +167,38 @@ __global__ void __launch_bounds__(TK_THREADS) topk_blocks_kernel(const TopkParam
     if (p.n_blocks <= TK_SORT_MAX) {
         uint32_t n_sort = 2;
         while (n_sort < p.n_blocks) n_sort <<= 1;
-        for (uint32_t i = tid; i < n_sort; i += TK_THREADS) keys[i] = i < p.n_blocks ? make_key(sc[i], i) : 0ull;
+        for (uint32_t i = tid; i < n_sort; i += TK_THREADS) keys[pad(i)] = i < p.n_blocks ? make_key(sc[i], i) : 0ull;
         top_run(keys, n_sort, min(run, n_sort));
     } else {
         // chunks of TK_SORT_MAX scores: the chunk's best `run`, merged with the best so far (kept behind the chunk)
-        uint64_t *best = keys + TK_SORT_MAX;
-        for (uint32_t i = tid; i < run; i += TK_THREADS) best[i] = 0ull;
+        uint64_t *best = keys + TK_SORT_MAX + TK_SORT_MAX / 8u;
+        for (uint32_t i = tid; i < run; i += TK_THREADS) best[pad(i)] = 0ull;
         for (uint32_t at = 0; at < p.n_blocks; at += TK_SORT_MAX) {
             __syncthreads();
             for (uint32_t i = tid; i < TK_SORT_MAX; i += TK_THREADS)
-                keys[i] = at + i < p.n_blocks ? make_key(sc[at + i], at + i) : 0ull;
+                keys[pad(i)] = at + i < p.n_blocks ? make_key(sc[at + i], at + i) : 0ull;
             top_run(keys, TK_SORT_MAX, run);
             // both descending: the maximum of best[i] and the chunk's run read backwards is bitonic
             for (uint32_t i = tid; i < run; i += TK_THREADS) {
-                const uint64_t a = best[i], b = keys[run - 1u - i];
-                best[i] = a > b ? a : b;
+                const uint64_t a = best[pad(i)], b = keys[pad(run - 1u - i)];
+                best[pad(i)] = a > b ? a : b;
             }
             stages_down(best, run, run, run >> 1);
         }
         __syncthreads();
-        for (uint32_t i = tid; i < run; i += TK_THREADS) keys[i] = best[i];
+        for (uint32_t i = tid; i < run; i += TK_THREADS) keys[pad(i)] = best[pad(i)];
         __syncthreads();
     }
     // keys[0 .. want) are the selection, best first; dead keys (0) sort last
     if (tid == 0) { s_count = 0; s_present = 0; }
     __syncthreads();
     for (uint32_t i = tid; i < want; i += TK_THREADS) {
-        const uint64_t k = keys[i];
+        const uint64_t k = keys[pad(i)];
         if (k != 0ull) {
             const uint32_t b = 0xffffffffu - (uint32_t)k;
             ids[i] = b;
             if (b == own) s_present = 1u;
-            if (i + 1u == want || keys[i + 1u] == 0ull) s_count = i + 1u;
+            if (i + 1u == want || keys[pad(i + 1u)] == 0ull) s_count = i + 1u;
         }
     }
     __syncthreads();
@@ -243,8 +247,8 @@ brc_status brc_topk_blocks(brc_pool *pool, const float *scores_dev, uint32_t n_s
         n_keys = 2;
         while (n_keys < n_blocks) n_keys <<= 1;
     }
-    const size_t smem = dense ? 0 : (size_t)n_keys * sizeof(uint64_t);
-    BRC_CUDA(cudaFuncSetAttribute(topk_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((TK_SORT_MAX + TK_K_MAX) * sizeof(uint64_t))));
+    const size_t smem = dense ? 0 : (size_t)(n_keys + n_keys / 8u + 1u) * sizeof(uint64_t);   // one slot of padding per 8 keys
+    BRC_CUDA(cudaFuncSetAttribute(topk_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(((TK_SORT_MAX + TK_K_MAX) / 8u * 9u + 1u) * sizeof(uint64_t))));
     topk_blocks_kernel<<<(uint32_t)rows, TK_THREADS, smem, brc_stream(stream)>>>(p);
     BRC_CUDA(cudaGetLastError());
     return BRC_OK;
