@@ -26,6 +26,11 @@
 #define BRC_DONE_WORDS (BRC_DONE_BANK_WORDS * BRC_DONE_BANKS)
 #define BRC_STATUS_BYTES ((BRC_STATUS_WORDS + BRC_DONE_WORDS) * 4u)
 
+// Split-KV across GPUs: ranks of one exchange group, and banks of a receive buffer (ranks may be a
+// call apart, so a peer's next partial must not land on the one still being merged).
+#define BRC_MAX_WORLD 16u
+#define BRC_COMM_BANKS 4u
+
 // Stage ids of the optional GPU timers are public (breccia_kv.h); this is their count.
 #define BRC_STAGE_COUNT 6
 
@@ -67,6 +72,12 @@ struct brc_pool {
     cudaStream_t host_up = nullptr, host_down = nullptr;
     cudaEvent_t host_uploaded[HOST_PARTS_MAX] = {}, host_computed[HOST_PARTS_MAX] = {};
     cudaEvent_t host_all_down = nullptr;
+
+    // decode calls share the arrival counters above: the stream of the last one and an event recorded
+    // behind it, so that a call on another stream is ordered after it
+    cudaStream_t decode_stream = nullptr;
+    bool decode_stream_set = false;
+    cudaEvent_t decode_event = nullptr;
 
     // allocator
     mutable std::mutex mu;
@@ -112,21 +123,50 @@ struct brc_device_guard {
 void brc_stage_begin(brc_pool *pool, int stage, cudaStream_t s);
 void brc_stage_end(brc_pool *pool, int stage, cudaStream_t s);
 
-// Decode attention of one layer with the step's KV append fused into the kernel (decode_attn.cu).
-brc_status brc_decode_attn_append_fused(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype, uint32_t n_head,
-                                        const float *gate_dev, uint32_t gate_head_stride, const uint32_t *block_tables_dev,
-                                        uint32_t table_stride, const uint32_t *seq_lens_dev, uint32_t n_seqs,
-                                        uint32_t max_seq_len, float scale, float *out_dev, void *workspace_dev,
-                                        uint64_t workspace_bytes, const void *k_new_dev, const void *v_new_dev,
-                                        int32_t kv_dtype, uint32_t index_in_step, uint32_t layers_in_step, void *stream);
+// Split-KV across GPUs, as the decode kernel needs it: where this rank's merged partials go and which
+// flags announce them (comm.cu owns the buffers).
+struct brc_push_args {
+    uint32_t world = 1, rank = 0;
+    uint8_t *peer_recv[BRC_MAX_WORLD] = {};   // receive buffers of all ranks as mapped here ([rank] = this rank's own)
+    uint64_t slot_stride = 0, bank_stride = 0;
+    uint64_t flags_offset = 0;                // byte offset of the per-unit flags in a receive buffer
+    uint32_t flag_items = 0;                  // flag words per (bank, source rank)
+    uint32_t *calls = nullptr;                // exchanges completed on this rank
+    uint32_t *fin_ticket = nullptr;           // CTAs of the running launch that have finished
+    uint64_t wait_ns = 0;
+};
 
-// brc_decode_partial as one of `layers_in_step` independent layers launched back to back, acc and
-// (m, l) to separate pointers (decode_attn.cu; used by brc_splitkv_step).  Not exported.
-extern "C" brc_status brc_decode_partial_in_step(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype,
-                                                 uint32_t n_head, const uint32_t *block_tables_dev, uint32_t table_stride,
-                                                 const uint32_t *seq_lens_dev, uint32_t n_seqs, uint32_t max_seq_len,
-                                                 float scale, float *acc_dev, float *ml_dev, void *workspace_dev,
-                                                 uint64_t workspace_bytes, uint32_t index_in_step, uint32_t layers_in_step,
-                                                 void *stream);
+// Decode attention over `n_layers` layers of a batch in as few launches as the workspace allows (one,
+// when it holds n_layers x brc_decode_workspace_bytes()).  Per-layer arrays lie `*_layer_stride_bytes`
+// apart.  k_new / v_new non-NULL: the step's KV append rides in the kernel.  out_ml non-NULL: partial
+// mode.  push with world > 1: merged partials go to the peers and the output comes from the cross-rank
+// merge inside the same launch (decode_attn.cu).
+struct brc_layers_args {
+    uint32_t layer0 = 0, n_layers = 1;
+    const void *q = nullptr;
+    int32_t q_dtype = BRC_DTYPE_F16;
+    uint64_t q_layer_stride_bytes = 0;
+    uint32_t n_head = 0;
+    const float *gate = nullptr;
+    uint32_t gate_head_stride = 0;
+    uint64_t gate_layer_stride_bytes = 0;
+    const uint32_t *block_tables = nullptr;
+    uint32_t table_stride = 0;
+    const uint32_t *seq_lens = nullptr;
+    uint32_t n_seqs = 0, max_seq_len = 0;
+    float scale = 0.f;
+    float *out = nullptr;
+    uint64_t out_layer_stride_bytes = 0;
+    float *out_ml = nullptr;
+    uint64_t out_ml_layer_stride_bytes = 0;
+    void *workspace = nullptr;
+    uint64_t workspace_bytes = 0;
+    const void *k_new = nullptr, *v_new = nullptr;
+    int32_t kv_dtype = BRC_DTYPE_F32;
+    uint64_t kv_layer_stride_bytes = 0;
+    const brc_push_args *push = nullptr;
+};
+brc_status brc_decode_layers(brc_pool *pool, const char *who, const brc_layers_args &args, void *stream);
+uint32_t brc_decode_kvb(const brc_pool *pool);   // kv heads that travel together in one unit (1 or 2)
 
 static inline cudaStream_t brc_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }

@@ -1,9 +1,13 @@
 // Split-KV decode across the GPUs of one box: exchange of the per-head (acc, m, l) partials through
-// peer memory and their log-sum-exp merge, in one kernel.
+// peer memory and their log-sum-exp merge.
 //
 // Every rank owns a receive buffer (cudaMalloc) that its peers map (CUDA IPC between processes, peer
-// access inside one process).  After the local split-KV kernel has produced this rank's partial,
-// `exchange_merge_kernel`
+// access inside one process).  brc_splitkv_attend / brc_splitkv_step hand the buffers to the decode
+// kernel itself (decode_attn.cu): the CTA that completes a (layer, sequence, kv-head group) unit stores
+// its merged partial into every rank's buffer and releases a flag per unit, and the CTA that owns the
+// unit waits for all ranks' flags at the end of its share and merges - one launch per call, the
+// exchange of a layer hidden behind the streaming of the next.  brc_splitkv_exchange_combine is the
+// stand-alone second half for a partial the caller already holds: `exchange_merge_kernel`
 //   1. stores the partial into its slot of every peer's receive buffer (plain 16-byte global stores
 //      over NVLink), fences at system scope, and the CTA that finishes last releases one flag per peer;
 //   2. waits, with a time limit, for the flags of all peers in its own buffer, and merges the partials.
@@ -22,8 +26,8 @@
 
 namespace {
 
-constexpr uint32_t MAX_WORLD = 16;
-constexpr uint32_t N_BANKS = 4;          // calls in flight between the slowest and the fastest rank: at most 2
+constexpr uint32_t MAX_WORLD = BRC_MAX_WORLD;
+constexpr uint32_t N_BANKS = BRC_COMM_BANKS;   // calls in flight between the slowest and the fastest rank: at most 2
 constexpr uint32_t FLAG_STRIDE = 32;     // words between flags: one 128-byte line each
 constexpr uint64_t DEFAULT_WAIT_NS = 1000000000ull;
 
@@ -160,9 +164,12 @@ struct brc_comm {
     brc_pool *pool = nullptr;
     uint32_t world = 1, rank = 0, max_seqs = 0, n_head = 0;
     uint64_t slot_stride = 0, bank_stride = 0, flags_offset = 0, recv_bytes = 0;
+    uint64_t unit_flags_offset = 0;    // per-(bank, source rank, unit) flags of the fused exchange
+    uint32_t flag_items = 0;           // units the buffers hold: max_seqs x kv-head groups
     uint8_t *recv = nullptr;           // this rank's receive buffer (+ flags, + ticket, + local partial)
     uint8_t *local_part = nullptr;     // inside recv's allocation
-    uint32_t *ticket = nullptr;        // [0] ticket of the running launch, [1] exchanges completed
+    uint32_t *ticket = nullptr;        // [0] ticket of the running exchange kernel, [1] exchanges completed, [2] CTAs of the
+                                       // running fused launch that have finished
     uint8_t *peer[MAX_WORLD] = {};
     bool opened_ipc[MAX_WORLD] = {};
     bool connected = false;
@@ -197,7 +204,10 @@ brc_status brc_comm_create(brc_pool *pool, uint32_t world, uint32_t rank, uint32
     c->flags_offset = c->bank_stride * N_BANKS;
     const uint64_t flag_bytes = (uint64_t)N_BANKS * MAX_WORLD * FLAG_STRIDE * 4u;
     const uint64_t ticket_off = c->flags_offset + flag_bytes;
-    const uint64_t local_off = ticket_off + 256;
+    c->unit_flags_offset = ticket_off + 256;
+    c->flag_items = max_seqs * (pool->n_kv_head / brc_decode_kvb(pool));
+    const uint64_t unit_flag_bytes = (((uint64_t)N_BANKS * MAX_WORLD * c->flag_items * 4u) + 255u) & ~255ull;
+    const uint64_t local_off = c->unit_flags_offset + unit_flag_bytes;
     c->recv_bytes = local_off + c->slot_stride;
     cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&c->recv), c->recv_bytes);
     if (e != cudaSuccess) {
@@ -340,19 +350,28 @@ brc_status brc_splitkv_exchange_combine(brc_comm *c, const void *partial_dev, ui
     return BRC_OK;
 }
 
+// The comm's buffers as the decode kernel takes them.
+static brc_push_args push_args_of(const brc_comm *c) {
+    brc_push_args x;
+    x.world = c->world;
+    x.rank = c->rank;
+    for (uint32_t r = 0; r < c->world; ++r) x.peer_recv[r] = c->peer[r];
+    x.slot_stride = c->slot_stride;
+    x.bank_stride = c->bank_stride;
+    x.flags_offset = c->unit_flags_offset;
+    x.flag_items = c->flag_items;
+    x.calls = c->ticket + 1;
+    x.fin_ticket = c->ticket + 2;
+    x.wait_ns = c->wait_ns;
+    return x;
+}
+
 brc_status brc_splitkv_attend(brc_comm *c, uint32_t layer, const void *q_dev, int32_t q_dtype, const float *gate_dev,
                               uint32_t gate_head_stride, const uint32_t *block_tables_dev, uint32_t table_stride,
                               const uint32_t *seq_lens_dev, uint32_t n_seqs, uint32_t max_seq_len, float scale,
                               float *out_dev, void *workspace_dev, uint64_t workspace_bytes, void *stream) {
-    if (!c) return brc_fail(BRC_ERR_INVALID, "brc_splitkv_attend: NULL handle");
-    if (!c->connected) return brc_fail(BRC_ERR_INVALID, "brc_splitkv_attend: the peers are not connected yet");
-    if (n_seqs > c->max_seqs)
-        return brc_fail(BRC_ERR_CAPACITY, "brc_splitkv_attend: %u sequences but the buffers hold %u", n_seqs, c->max_seqs);
-    if (brc_status rc = brc_decode_partial(c->pool, layer, q_dev, q_dtype, c->n_head, block_tables_dev, table_stride,
-                                           seq_lens_dev, n_seqs, max_seq_len, scale, c->local_part, workspace_dev,
-                                           workspace_bytes, stream))
-        return rc;
-    return brc_splitkv_exchange_combine(c, nullptr, n_seqs, gate_dev, gate_head_stride, out_dev, stream);
+    return brc_splitkv_step(c, layer, 1, q_dev, q_dtype, 0, gate_dev, gate_head_stride, block_tables_dev, table_stride, seq_lens_dev,
+                            n_seqs, max_seq_len, scale, out_dev, workspace_dev, workspace_bytes, stream);
 }
 
 brc_status brc_splitkv_step(brc_comm *c, uint32_t layer0, uint32_t n_layers, const void *q_dev, int32_t q_dtype,
@@ -360,29 +379,39 @@ brc_status brc_splitkv_step(brc_comm *c, uint32_t layer0, uint32_t n_layers, con
                             const uint32_t *block_tables_dev, uint32_t table_stride, const uint32_t *seq_lens_dev,
                             uint32_t n_seqs, uint32_t max_seq_len, float scale, float *out_dev, void *workspace_dev,
                             uint64_t workspace_bytes, void *stream) {
-    if (!c) return brc_fail(BRC_ERR_INVALID, "brc_splitkv_step: NULL handle");
-    if (!c->connected) return brc_fail(BRC_ERR_INVALID, "brc_splitkv_step: the peers are not connected yet");
+    const char *who = n_layers == 1 ? "brc_splitkv_attend" : "brc_splitkv_step";
+    if (!c) return brc_fail(BRC_ERR_INVALID, "%s: NULL handle", who);
+    if (!c->connected) return brc_fail(BRC_ERR_INVALID, "%s: the peers are not connected yet", who);
     if (n_layers == 0 || n_seqs == 0) return BRC_OK;
     if ((uint64_t)n_layers * n_seqs > c->max_seqs)
-        return brc_fail(BRC_ERR_CAPACITY, "brc_splitkv_step: %u layers x %u sequences but the buffers hold %u (sequence, layer) rows",
-                        n_layers, n_seqs, c->max_seqs);
-    if (layer0 + n_layers > c->pool->n_layers)
-        return brc_fail(BRC_ERR_INVALID, "brc_splitkv_step: layers %u..%u but the pool has %u", layer0, layer0 + n_layers,
-                        c->pool->n_layers);
-    // The partials of the step form one buffer as if the layers were further sequences:
-    // acc [n_layers][n_seqs][n_head][hd], then (m, l) [n_layers][n_seqs][n_head][2].
+        return n_layers == 1
+                   ? brc_fail(BRC_ERR_CAPACITY, "%s: %u sequences but the buffers hold %u", who, n_seqs, c->max_seqs)
+                   : brc_fail(BRC_ERR_CAPACITY, "%s: %u layers x %u sequences but the buffers hold %u (sequence, layer) rows", who,
+                              n_layers, n_seqs, c->max_seqs);
     const uint32_t hd = c->pool->head_dim;
-    const size_t rows = (size_t)n_seqs * c->n_head;
-    float *acc = reinterpret_cast<float *>(c->local_part);
-    float *ml = acc + (size_t)n_layers * rows * hd;
-    for (uint32_t i = 0; i < n_layers; ++i) {
-        if (brc_status rc = brc_decode_partial_in_step(c->pool, layer0 + i, static_cast<const uint8_t *>(q_dev) + i * q_layer_stride_bytes,
-                                                       q_dtype, c->n_head, block_tables_dev, table_stride, seq_lens_dev, n_seqs,
-                                                       max_seq_len, scale, acc + i * rows * hd, ml + i * rows * 2, workspace_dev,
-                                                       workspace_bytes, i, n_layers, stream))
-            return rc;
-    }
-    return brc_splitkv_exchange_combine(c, nullptr, n_layers * n_seqs, gate_dev, gate_head_stride, out_dev, stream);
+    const brc_push_args push = push_args_of(c);
+    brc_layers_args a;
+    a.layer0 = layer0;
+    a.n_layers = n_layers;
+    a.q = q_dev;
+    a.q_dtype = q_dtype;
+    a.q_layer_stride_bytes = q_layer_stride_bytes;
+    a.n_head = c->n_head;
+    a.gate = gate_dev;
+    a.gate_head_stride = gate_head_stride;
+    a.gate_layer_stride_bytes = (uint64_t)n_seqs * c->n_head * gate_head_stride * sizeof(float);
+    a.block_tables = block_tables_dev;
+    a.table_stride = table_stride;
+    a.seq_lens = seq_lens_dev;
+    a.n_seqs = n_seqs;
+    a.max_seq_len = max_seq_len;
+    a.scale = scale;
+    a.out = out_dev;
+    a.out_layer_stride_bytes = (uint64_t)n_seqs * c->n_head * hd * sizeof(float);
+    a.workspace = workspace_dev;
+    a.workspace_bytes = workspace_bytes;
+    a.push = &push;
+    return brc_decode_layers(c->pool, who, a, stream);
 }
 
 }  // extern "C"

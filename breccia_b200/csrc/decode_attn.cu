@@ -28,7 +28,15 @@
 //     rows.  No CTA ever waits for another, and there is no second kernel;
 //   * a decode step's KV append can ride along: the CTA that is about to stream the page holding a
 //     sequence's newest cell first writes that cell (same encoding and address rule as the append
-//     kernel), fenced against its own TMA read.
+//     kernel), fenced against its own TMA read;
+//   * one launch can cover several layers: the flat list then runs over (layer, unit, page) and is cut
+//     into the same equal shares, so the launch ramp, the schedule scan and the tail are paid once per
+//     decode token instead of once per layer, and most units lie inside one CTA's share;
+//   * split-KV across GPUs rides in the same launch: the CTA that completes a unit stores the merged
+//     (acc, m, l) into this rank's slot of every peer's receive buffer with plain global stores over
+//     NVLink and releases one flag per (unit, peer); the CTA that owns the unit's last page waits
+//     (bounded) for all ranks' flags after it has finished streaming, merges and writes the output, so a
+//     layer's exchange overlaps the streaming of the layers behind it.  No load targets peer memory.
 //
 // HBM-bound by design: 8 FLOP per cached byte, all of it on the tensor pipe.
 #include <algorithm>
@@ -86,10 +94,27 @@ struct DecodeParams {
     uint32_t n_kv_head, group, n_head;   // group = query heads per kv head handled by THIS launch (<= GROUP_TILE)
     uint32_t group_all, head0;           // query heads per kv head in q / out, and the first of them this launch takes
     uint32_t n_pages;    // pages per layer
-    uint32_t layer_row0; // first row of this layer in the TMA view
+    uint32_t layer_row0; // first row of the launch's first layer in the TMA view
     uint32_t n_stages;
-    uint32_t pdl;        // 1: let the next kernel in the stream start as this one's CTAs retire
     float scale_log2;    // scale * log2(e)
+    // layers of this launch: per-layer arrays lie these many ELEMENTS of their own type apart
+    uint32_t n_layers;
+    uint32_t layer_rows;           // rows of one layer in the TMA view
+    uint64_t q_layer_stride;       // elements of q's type
+    uint64_t out_layer_stride;     // floats
+    uint64_t out_ml_layer_stride;  // floats
+    uint64_t gate_layer_stride;    // floats
+    uint64_t kv_new_layer_stride;  // elements of k_new's type
+    // split-KV across GPUs (world > 1): merged partials go to the receive buffers, the output is written by
+    // the cross-rank merge at the end of the launch
+    uint32_t world, rank;
+    uint32_t flag_items;           // flag words per (bank, source rank)
+    uint32_t rows_total;           // n_layers * n_seqs * n_head: rows of the partial as laid out in a slot
+    uint8_t *peer_recv[BRC_MAX_WORLD];
+    uint64_t slot_stride, bank_stride, flags_offset;
+    uint32_t *calls;               // exchanges completed so far on this rank (device-resident epoch)
+    uint32_t *fin_ticket;          // CTAs of this launch that have finished
+    uint64_t wait_ns;
 };
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
@@ -142,6 +167,35 @@ __device__ __forceinline__ void share_range(uint32_t first_g, uint32_t last_g, u
     while (i_hi > 0 && share_begin(i_hi, total, n_cta) > last_g) --i_hi;
 }
 
+// A unit of a launch that covers several layers: flat index over (layer, unit) and its parts.
+struct UnitRef {
+    uint32_t U, layer, u;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *ptr) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void st_release_sys(uint32_t *ptr, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+
+// Flag of (bank, source rank, unit) in the receive buffer `recv`.
+__device__ __forceinline__ uint32_t *unit_flag(uint8_t *recv, const DecodeParams &p, uint32_t bank, uint32_t src, uint32_t U) {
+    return reinterpret_cast<uint32_t *>(recv + p.flags_offset) + ((size_t)(bank * BRC_MAX_WORLD + src) * p.flag_items + U);
+}
+
+// Byte offset, inside any rank's receive buffer, of row R of THIS rank's partial in bank `bank`:
+// acc [rows_total][HD] f32, then (m, l) [rows_total][2] f32.
+__device__ __forceinline__ uint64_t push_acc_off(const DecodeParams &p, uint32_t bank, uint32_t src, size_t R, uint32_t hd, uint32_t d) {
+    return (uint64_t)bank * p.bank_stride + (uint64_t)src * p.slot_stride + (R * hd + d) * 4u;
+}
+__device__ __forceinline__ uint64_t push_ml_off(const DecodeParams &p, uint32_t bank, uint32_t src, size_t R, uint32_t hd) {
+    return (uint64_t)bank * p.bank_stride + (uint64_t)src * p.slot_stride + ((size_t)p.rows_total * hd + R * 2u) * 4u;
+}
+
 // Log-sum-exp merge of all shares of unit u (every one of them is complete and visible), run by the
 // NW * 32 consumer threads of the CTA that took the unit's last ticket.  Writes the final output
 // rows (normalised, gated) or, in partial mode, the merged (acc, m, l).  Partials come from other SMs:
@@ -157,9 +211,13 @@ constexpr uint32_t MAX_RUN_CTAS = 256;    // run tickets: 2 words per CTA after 
 // The shares merged are i_lo, i_lo + stride, ... <= i_hi.  With to_slot the merged (acc, m, l) go back
 // into the partial slot of share i_lo instead of the output: that is the first level of the two-level
 // merge of a unit that spans many CTAs (see the ticket code in the kernel).
+//
+// With p.world > 1 the final merge of a unit does not write the output: its (acc, m, l) go into this
+// rank's slot of every rank's receive buffer (its own included), then one flag per rank is released.
 template <int HD, int KVB>
-__device__ __forceinline__ void combine_unit(const DecodeParams &p, uint32_t u, uint32_t i_lo, uint32_t i_hi, uint32_t stride,
-                                             bool to_slot, uint32_t total, uint32_t tid, float *sm) {
+__device__ __forceinline__ void combine_unit(const DecodeParams &p, const UnitRef ur, uint32_t i_lo, uint32_t i_hi, uint32_t stride,
+                                             bool to_slot, uint32_t total, uint32_t tid, float *sm, uint32_t epoch, uint32_t bank) {
+    const uint32_t u = ur.u;
     constexpr uint32_t TPR = HD / 4;                    // threads per output row (float4 each)
     constexpr uint32_t ROWS_PER_PASS = (NW * 32) / TPR;
     constexpr uint32_t MAX_ROWS = KVB * GROUP_TILE;
@@ -207,7 +265,7 @@ __device__ __forceinline__ void combine_unit(const DecodeParams &p, uint32_t u, 
             const uint32_t pc = idx / n_rows, row = idx % n_rows;
             const uint32_t k2 = row / p.group, h = row % p.group;
             mls[pc * MAX_ROWS + row] =
-                __ldcg(reinterpret_cast<const float2 *>(p.part_ml + (((size_t)(u + list[pc]) * KVB + k2) * GROUP_TILE + h) * 2));
+                __ldcg(reinterpret_cast<const float2 *>(p.part_ml + (((size_t)(ur.U + list[pc]) * KVB + k2) * GROUP_TILE + h) * 2));
         }
         brc::named_bar_sync(1, NW * 32);
         // ---- weights: thread = row
@@ -250,7 +308,7 @@ __device__ __forceinline__ void combine_unit(const DecodeParams &p, uint32_t u, 
                 for (uint32_t j = 0; j < 4; ++j) {
                     const uint32_t pc = min(pc0 + j, n - 1);                            // clamped shares get weight 0
                     a[ps][j] = __ldcg(reinterpret_cast<const float4 *>(
-                        p.part_acc + (((size_t)(u + list[pc]) * KVB + k2) * GROUP_TILE + h) * HD + d));
+                        p.part_acc + (((size_t)(ur.U + list[pc]) * KVB + k2) * GROUP_TILE + h) * HD + d));
                 }
             }
 #pragma unroll
@@ -281,22 +339,30 @@ __device__ __forceinline__ void combine_unit(const DecodeParams &p, uint32_t u, 
         const uint32_t k2 = row / p.group, h = row % p.group;
         const float2 ml = mls[row];
         const uint32_t head = (kv0 + k2) * p.group_all + p.head0 + h;
-        const size_t o = ((size_t)s * p.n_head + head) * HD + d;
+        const size_t o = ur.layer * p.out_layer_stride + ((size_t)s * p.n_head + head) * HD + d;
         if (to_slot) {
-            const size_t slot = ((size_t)(u + i_lo) * KVB + k2) * GROUP_TILE + h;
+            const size_t slot = ((size_t)(ur.U + i_lo) * KVB + k2) * GROUP_TILE + h;
             *reinterpret_cast<float4 *>(p.part_acc + slot * HD + d) = acc[ps];
             if (d == 0) *reinterpret_cast<float2 *>(p.part_ml + slot * 2) = ml;
+        } else if (p.world > 1) {
+            const size_t R = ((size_t)ur.layer * p.n_seqs + s) * p.n_head + head;
+            const uint64_t oa = push_acc_off(p, bank, p.rank, R, HD, d), om = push_ml_off(p, bank, p.rank, R, HD);
+            for (uint32_t r = 0; r < p.world; ++r) {
+                *reinterpret_cast<float4 *>(p.peer_recv[r] + oa) = acc[ps];
+                if (d == 0) *reinterpret_cast<float2 *>(p.peer_recv[r] + om) = ml;
+            }
         } else if (p.out_ml) {
             *reinterpret_cast<float4 *>(p.out + o) = acc[ps];
             if (d == 0) {
-                p.out_ml[((size_t)s * p.n_head + head) * 2] = ml.x;
-                p.out_ml[((size_t)s * p.n_head + head) * 2 + 1] = ml.y;
+                float *om = p.out_ml + ur.layer * p.out_ml_layer_stride + ((size_t)s * p.n_head + head) * 2;
+                om[0] = ml.x;
+                om[1] = ml.y;
             }
         } else {
             const float inv = ml.y > 0.f ? 1.f / ml.y : 0.f;
             float4 r = make_float4(acc[ps].x * inv, acc[ps].y * inv, acc[ps].z * inv, acc[ps].w * inv);
             if (p.gate) {
-                const float *g = p.gate + ((size_t)s * p.n_head + head) * p.gate_head_stride + d;
+                const float *g = p.gate + ur.layer * p.gate_layer_stride + ((size_t)s * p.n_head + head) * p.gate_head_stride + d;
                 r.x *= sigmoid_f32(g[0]);
                 r.y *= sigmoid_f32(g[1]);
                 r.z *= sigmoid_f32(g[2]);
@@ -304,6 +370,89 @@ __device__ __forceinline__ void combine_unit(const DecodeParams &p, uint32_t u, 
             }
             *reinterpret_cast<float4 *>(p.out + o) = r;
         }
+    }
+    if (!to_slot && p.world > 1) {
+        // every thread's stores are ordered at system scope before the flags go out
+        __threadfence_system();
+        brc::named_bar_sync(1, NW * 32);
+        if (tid < p.world) st_release_sys(unit_flag(p.peer_recv[tid], p, bank, p.rank, ur.U), epoch);
+    }
+}
+
+// Cross-rank merge of unit `ur` (split-KV across GPUs): waits, with a time limit, until every rank's
+// merged partial of the unit has landed in this rank's receive buffer, then merges them, normalises,
+// applies the gate and writes the output rows.  Run by the NW * 32 consumer threads of the CTA that
+// owns the unit, after that CTA has finished streaming.  On expiry the output is left as it was, the
+// check word reports it, and the CTA's later units are skipped without waiting again.
+template <int HD, int KVB>
+__device__ __forceinline__ void finalize_unit(const DecodeParams &p, const UnitRef ur, uint32_t epoch, uint32_t bank, uint32_t tid,
+                                              volatile uint32_t *gave_up) {
+    constexpr uint32_t TPR = HD / 4;
+    constexpr uint32_t ROWS_PER_PASS = (NW * 32) / TPR;
+    if (!gave_up[0] && tid < p.world) {
+        const uint32_t *f = unit_flag(p.peer_recv[p.rank], p, bank, tid, ur.U);
+        bool ok = (int32_t)(ld_acquire_sys(f) - epoch) >= 0;
+        if (!ok) {
+            const uint64_t t0 = globaltimer_ns();
+            for (uint32_t i = 0; i < (1u << 30); ++i) {
+                if ((int32_t)(ld_acquire_sys(f) - epoch) >= 0) { ok = true; break; }
+                if ((i & 63u) == 63u && globaltimer_ns() - t0 > p.wait_ns) break;
+            }
+        }
+        if (!ok) {
+            gave_up[0] = 1u;   // benign race: every writer stores 1
+            atomicOr(p.status, BRC_DEV_WAIT_LIMIT);
+            p.status[1] = 3000000u + tid;   // which rank's partial never arrived
+            p.status[2] = ur.U;
+        }
+    }
+    brc::named_bar_sync(1, NW * 32);
+    const uint32_t skip = gave_up[0];
+    brc::named_bar_sync(1, NW * 32);   // nobody sets the flag for the next unit before everyone has read it
+    if (skip) return;
+    const uint32_t n_groups = p.n_kv_head / KVB;
+    const uint32_t s = ur.u / n_groups, kv0 = (ur.u % n_groups) * KVB;
+    const uint32_t n_rows = KVB * p.group;
+    const uint32_t d = (tid % TPR) * 4;
+    for (uint32_t row = tid / TPR; row < n_rows; row += ROWS_PER_PASS) {
+        const uint32_t k2 = row / p.group, h = row % p.group;
+        const uint32_t head = (kv0 + k2) * p.group_all + p.head0 + h;
+        const size_t R = ((size_t)ur.layer * p.n_seqs + s) * p.n_head + head;
+        float ms[BRC_MAX_WORLD], ls[BRC_MAX_WORLD];
+        float M = -INFINITY;
+#pragma unroll
+        for (uint32_t r = 0; r < BRC_MAX_WORLD; ++r) {
+            if (r < p.world) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2 *>(p.peer_recv[p.rank] + push_ml_off(p, bank, r, R, HD)));
+                ms[r] = ml.x;
+                ls[r] = ml.y;
+                if (ml.y > 0.f) M = fmaxf(M, ml.x);
+            }
+        }
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float L = 0.f;
+#pragma unroll
+        for (uint32_t r = 0; r < BRC_MAX_WORLD; ++r) {
+            if (r < p.world && ls[r] > 0.f) {
+                const float w = exp2f(ms[r] - M);
+                const float4 a = __ldcg(reinterpret_cast<const float4 *>(p.peer_recv[p.rank] + push_acc_off(p, bank, r, R, HD, d)));
+                L += w * ls[r];
+                acc.x += w * a.x;
+                acc.y += w * a.y;
+                acc.z += w * a.z;
+                acc.w += w * a.w;
+            }
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        float4 o = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        if (p.gate) {
+            const float *g = p.gate + ur.layer * p.gate_layer_stride + ((size_t)s * p.n_head + head) * p.gate_head_stride + d;
+            o.x *= sigmoid_f32(g[0]);
+            o.y *= sigmoid_f32(g[1]);
+            o.z *= sigmoid_f32(g[2]);
+            o.w *= sigmoid_f32(g[3]);
+        }
+        *reinterpret_cast<float4 *>(p.out + ur.layer * p.out_layer_stride + ((size_t)s * p.n_head + head) * HD + d) = o;
     }
 }
 
@@ -326,12 +475,18 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     // small words after the barriers (2 x 24 barriers at most = 384 bytes): flags, merge weights
     volatile uint32_t *flags = reinterpret_cast<volatile uint32_t *>(bars + 64);
     volatile uint32_t *dead_cta = flags + 1;
+    volatile uint32_t *gave_up = flags + 2;
     float *wts = reinterpret_cast<float *>(const_cast<uint32_t *>(flags) + 8);  // [NWP][KVB * GROUP_TILE]
     float *inv_l = wts + NW * GROUP_TILE;                                       // [KVB * GROUP_TILE] 1 / l of the merged rows
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t n_groups = p.n_kv_head / KVB;   // kv-head groups per sequence
-    const uint32_t n_units = p.n_seqs * n_groups;
+    const uint32_t n_units = p.n_seqs * n_groups;  // units of one layer
+    const bool push = p.world > 1;
+    // Split-KV across GPUs: this launch's epoch is the number of exchanges completed so far plus one
+    // (read by every CTA before any of them can take the launch's last ticket, which advances it).
+    const uint32_t epoch = push ? *reinterpret_cast<volatile uint32_t *>(p.calls) + 1u : 0u;
+    const uint32_t bank = epoch % BRC_COMM_BANKS;
 
     if (tid == 0) {
         for (uint32_t i = 0; i < p.n_stages; ++i) {
@@ -341,8 +496,10 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         brc::mbar_fence_init();
         brc::tma_prefetch_desc(&tm_kv);
         dead_cta[0] = 0u;
+        gave_up[0] = 0u;
     }
-    // Exclusive prefix of pages per unit, S[0..n_units]; every CTA computes it (n_units <= 2048).
+    // Exclusive prefix of pages per unit of ONE layer, S[0..n_units] (the layers of a launch share the
+    // sequence lengths); every CTA computes it (n_units <= 2048).
     if (warp == 0) {
         uint32_t run = 0;
         for (uint32_t base = 0; base < n_units; base += 32) {
@@ -370,29 +527,42 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     }
     __syncthreads();
 
+    const uint32_t total_l = S[n_units];            // page-units of one layer
+    const uint32_t total = total_l * p.n_layers;    // of the launch (the host keeps this below 2^32)
+    const uint32_t n_units_all = n_units * p.n_layers;
+
     // A sequence without cells has no pages, hence no share and no ticket: its rows are written here.
-    for (uint32_t u = blockIdx.x; u < n_units; u += gridDim.x) {
+    for (uint32_t U = blockIdx.x; U < n_units_all; U += gridDim.x) {
+        const uint32_t layer = U / n_units, u = U - layer * n_units;
         if (S[u + 1] != S[u]) continue;
         const uint32_t s = u / n_groups, kv0 = (u % n_groups) * KVB;
         for (uint32_t i = tid; i < KVB * p.group * HD; i += NTHREADS) {
             const uint32_t head = (kv0 + (i / HD) / p.group) * p.group_all + p.head0 + (i / HD) % p.group;
-            p.out[((size_t)s * p.n_head + head) * HD + i % HD] = 0.f;
-            if (p.out_ml && i % HD == 0) {
-                p.out_ml[((size_t)s * p.n_head + head) * 2] = -INFINITY;
-                p.out_ml[((size_t)s * p.n_head + head) * 2 + 1] = 0.f;
+            if (push) {
+                const size_t R = ((size_t)layer * p.n_seqs + s) * p.n_head + head;
+                const uint64_t oa = push_acc_off(p, bank, p.rank, R, HD, i % HD), om = push_ml_off(p, bank, p.rank, R, HD);
+                for (uint32_t r = 0; r < p.world; ++r) {
+                    *reinterpret_cast<float *>(p.peer_recv[r] + oa) = 0.f;
+                    if (i % HD == 0) *reinterpret_cast<float2 *>(p.peer_recv[r] + om) = make_float2(-INFINITY, 0.f);
+                }
+                continue;
             }
+            p.out[layer * p.out_layer_stride + ((size_t)s * p.n_head + head) * HD + i % HD] = 0.f;
+            if (p.out_ml && i % HD == 0) {
+                float *om = p.out_ml + layer * p.out_ml_layer_stride + ((size_t)s * p.n_head + head) * 2;
+                om[0] = -INFINITY;
+                om[1] = 0.f;
+            }
+        }
+        if (push) {
+            __threadfence_system();
+            __syncthreads();
+            if (tid < p.world) st_release_sys(unit_flag(p.peer_recv[tid], p, bank, p.rank, U), epoch);
         }
     }
 
-    // Programmatic dependent launch: the next kernel of the stream (the next layer of the same decode
-    // step, which reads nothing this kernel writes and has its own partial buffers and counters) may
-    // take over each SM as soon as this kernel's CTA there retires, instead of idling through the tail.
-    if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
-    const uint32_t total = S[n_units];
     const uint32_t a = share_begin(blockIdx.x, total, gridDim.x);
     const uint32_t b = share_begin(blockIdx.x + 1, total, gridDim.x);
-    if (a >= b) return;
     const uint32_t count = b - a;
 
     if (warp == NW) {
@@ -403,21 +573,25 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         for (uint32_t k0 = 0; k0 < count && !dead; k0 += 32) {
             const uint32_t k = k0 + lane;
             uint32_t row = 0;
-            uint32_t app = 0;  // fused append: bit 31 = this page holds the sequence's newest cell, low bits = (s, kv0)
+            uint32_t app = 0;  // fused append: bit 31 = this page holds the sequence's newest cell, then cell (4 bits), layer (6), unit (11)
             if (k < count) {
                 const uint32_t g = a + k;
-                const uint32_t u = unit_of(S, n_units, g);
+                const uint32_t layer = g / total_l, gl = g - layer * total_l;
+                const uint32_t u = unit_of(S, n_units, gl);
                 const uint32_t s = u / n_groups, kv0 = (u % n_groups) * KVB;
-                uint32_t page = __ldg(p.block_tables + (uint64_t)s * p.table_stride + (g - S[u]));
+                uint32_t page = __ldg(p.block_tables + (uint64_t)s * p.table_stride + (gl - S[u]));
                 if (page >= p.n_pages) {
                     atomicOr(p.status, BRC_DEV_BAD_PAGE);
                     p.status[1] = page;
                     page = 0;  // stay inside the pool; the result of this unit is void and the call reports it
                 } else if (p.k_new) {
-                    const uint32_t len = min(p.seq_lens[s], p.max_seq_len);
-                    if (g - S[u] == (len - 1u) >> 4) app = 0x80000000u | (((len - 1u) & 15u) << 24) | u;
+                    // a sequence beyond the caller's bound is reported and attended up to the bound; nothing
+                    // is appended for it (the append kernel skips such tokens too)
+                    const uint32_t len = p.seq_lens[s];
+                    if (len <= p.max_seq_len && gl - S[u] == (len - 1u) >> 4)
+                        app = 0x80000000u | (((len - 1u) & 15u) << 24) | (layer << 16) | u;
                 }
-                row = p.layer_row0 + (page * p.n_kv_head + kv0) * 16u;
+                row = p.layer_row0 + layer * p.layer_rows + (page * p.n_kv_head + kv0) * 16u;
             }
             const uint32_t n_here = min(32u, count - k0);
             for (uint32_t i = 0; i < n_here; ++i) {
@@ -440,12 +614,12 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                     // generic-proxy stores before the TMA (async-proxy) read of the same rows.
                     const uint32_t ap = __shfl_sync(0xffffffffu, app, i);
                     if (ap & 0x80000000u) {
-                        const uint32_t au = ap & 0xffffffu, cell = (ap >> 24) & 15u;
+                        const uint32_t au = ap & 0xffffu, cell = (ap >> 24) & 15u, al = (ap >> 16) & 63u;
                         const uint32_t as = au / n_groups, akv0 = (au % n_groups) * KVB;
                         if (lane < HD / 8) {
 #pragma unroll
                             for (int k2 = 0; k2 < KVB; ++k2) {
-                                const uint64_t src = ((uint64_t)as * p.n_kv_head + akv0 + k2) * HD + lane * 8u;
+                                const uint64_t src = al * p.kv_new_layer_stride + ((uint64_t)as * p.n_kv_head + akv0 + k2) * HD + lane * 8u;
                                 const uint64_t dst = ((uint64_t)(r + k2 * 16u + cell) * HD + lane * 8u) * 2u;
                                 uint4 ko, vo;
                                 if (p.kv_new_f32) {
@@ -511,13 +685,21 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     uint32_t stage = cw % p.n_stages, parity = 0;
     uint32_t dead = 0;
 
-    uint32_t u = unit_of(S, n_units, a);
+    // the first unit of the share: (layer, u) with flat index U = layer * n_units + u
+    uint32_t layer = 0, u = 0;
+    if (a < b) {
+        layer = a / total_l;
+        u = unit_of(S, n_units, a - layer * total_l);
+    }
+    const uint32_t first_layer = layer, first_u = u;
     uint32_t g0 = a;
     while (g0 < b) {
-        const uint32_t ge = min(b, S[u + 1]);
+        const uint32_t lbase = layer * total_l;     // first page-unit of this layer in the flat list
+        const uint32_t ge = min(b, lbase + S[u + 1]);
         const uint32_t s = u / n_groups, kvh = (u % n_groups) * KVB + kl;
         const uint32_t len = min(p.seq_lens[s], p.max_seq_len);
-        const uint32_t unit_first = S[u];
+        const uint32_t unit_first = lbase + S[u];
+        const UnitRef ur = {layer * n_units + u, layer, u};
 
         // Q^T fragments (B operand, k = d, n = head): b0 = Q[head t0][16 ks + 2 (lane & 3) + {0,1}],
         // b1 = same + 8.  Heads past the group read as zero.
@@ -525,7 +707,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         uint32_t ql[Q_F32 ? C::KSTEPS : 1][2];
         {
             const bool live = t0 < p.group;
-            const uint64_t qoff = ((uint64_t)s * p.n_head + kvh * p.group_all + p.head0 + t0) * HD + (lane & 3u) * 2u;
+            const uint64_t qoff = layer * p.q_layer_stride + ((uint64_t)s * p.n_head + kvh * p.group_all + p.head0 + t0) * HD + (lane & 3u) * 2u;
 #pragma unroll
             for (int ks = 0; ks < C::KSTEPS; ++ks) {
 #pragma unroll
@@ -668,12 +850,16 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             ml[h0 * 2 + 2] = m1;
             ml[h0 * 2 + 3] = l1;
         }
-        const size_t slot0 = (size_t)(u + blockIdx.x) * KVB;
+        const size_t slot0 = (size_t)(ur.U + blockIdx.x) * KVB;
         // A unit that lies wholly inside this CTA's share has no other share to meet: its rows go
         // straight to the output (normalised and gated, or as the merged partial), with no partial slot,
-        // no fence, no ticket and no read-back.  With many short sequences most units are of this kind.
-        const bool whole = WHOLE_FAST && unit_first >= a && S[u + 1] <= b;
+        // no fence, no ticket and no read-back.  With many short sequences, or with several layers in one
+        // launch, most units are of this kind.
+        const bool whole = WHOLE_FAST && unit_first >= a && lbase + S[u + 1] <= b;
         const uint32_t seq_of_u = u / n_groups, kv0_of_u = (u % n_groups) * KVB;
+        float *const out_l = p.out + layer * p.out_layer_stride;
+        float *const out_ml_l = p.out_ml ? p.out_ml + layer * p.out_ml_layer_stride : nullptr;
+        const float *const gate_l = p.gate ? p.gate + layer * p.gate_layer_stride : nullptr;
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
 #pragma unroll
@@ -709,8 +895,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                         float *ml_out = p.part_ml + ((slot0 + k2) * GROUP_TILE + h) * 2;
                         ml_out[0] = M;
                         ml_out[1] = L;
-                    } else if (p.out_ml) {
-                        float *ml_out = p.out_ml + ((size_t)seq_of_u * p.n_head + (kv0_of_u + k2) * p.group_all + p.head0 + h) * 2;
+                    } else if (out_ml_l) {
+                        float *ml_out = out_ml_l + ((size_t)seq_of_u * p.n_head + (kv0_of_u + k2) * p.group_all + p.head0 + h) * 2;
                         ml_out[0] = M;
                         ml_out[1] = L;
                     }
@@ -732,89 +918,130 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                     } else {
                         const size_t row = (size_t)seq_of_u * p.n_head + (kv0_of_u + k2) * p.group_all + p.head0 + h;
                         const uint32_t col = hf * (HD / 2) + d;
-                        if (!p.out_ml) {
+                        if (!out_ml_l) {
                             v *= inv_l[kh];
-                            if (p.gate) v *= sigmoid_f32(p.gate[row * p.gate_head_stride + col]);
+                            if (gate_l) v *= sigmoid_f32(gate_l[row * p.gate_head_stride + col]);
                         }
-                        p.out[row * HD + col] = v;
+                        out_l[row * HD + col] = v;
                     }
                 }
             }
             if (!whole && hf == 1) __threadfence();  // publish this thread's partial (both halves) before the unit's ticket is taken
             brc::named_bar_sync(1, NW * 32);
         }
-        if (whole) {
-            g0 = ge;
-            ++u;
-            while (u < n_units && S[u + 1] == S[u]) ++u;  // units without pages have no share
-            continue;
-        }
-
-        // ---- ticket: the CTA that completes the last share of a unit combines all of its shares
-        uint32_t i_lo, i_hi;
-        share_range(unit_first, S[u + 1] - 1, total, gridDim.x, i_lo, i_hi);
-        // A unit that spans many CTAs (one long sequence alone on the GPU spans all of them) is merged
-        // in two levels, or its last arriver would pull every share through one SM: runs of `fan`
-        // consecutive shares have a ticket of their own, the run's last arriver merges the run into the
-        // slot of its first share, and the last run to finish merges the runs.
-        const uint32_t span = i_hi - i_lo + 1;
-        const bool two_level = total >= gridDim.x && span > TWO_LEVEL_MIN && gridDim.x <= MAX_RUN_CTAS;
-        if (!two_level) {
-            if (tid == 0) {
-                uint32_t pieces = span;
-                if (total < gridDim.x) {   // fewer page-units than CTAs: some shares in between are empty
-                    pieces = 0;
-                    for (uint32_t i = i_lo; i <= i_hi; ++i)
-                        pieces += share_begin(i, total, gridDim.x) != share_begin(i + 1, total, gridDim.x);
-                }
-                const uint32_t ticket = atomicAdd(p.done + u, 1u);
-                const uint32_t last = ticket + 1u == pieces;
-                if (last) p.done[u] = 0;   // every share has arrived: leave the counter clean for the next launch
-                flags[0] = last;
-            }
-            brc::named_bar_sync(1, NW * 32);
-            if (flags[0]) {
-                __threadfence();
-                combine_unit<HD, KVB>(p, u, i_lo, i_hi, 1, false, total, tid, scratch);
-            }
-        } else {
-            uint32_t fan = 1;
-            while (fan * fan < span) ++fan;                 // ~sqrt: both levels merge about as many
-            const uint32_t run = (blockIdx.x - i_lo) / fan;
-            const uint32_t r_lo = i_lo + run * fan, r_hi = min(r_lo + fan - 1, i_hi);
-            if (tid == 0) {
-                // Runs of neighbouring units can start on the same CTA only as (last run of one unit,
-                // first run of the next): the second word of the pair keeps those apart.
-                uint32_t *cnt = p.done + MAX_UNITS + 2u * r_lo + (run != 0u);
-                const uint32_t ticket = atomicAdd(cnt, 1u);
-                const uint32_t last = ticket + 1u == r_hi - r_lo + 1u;
-                if (last) *cnt = 0;
-                flags[0] = last;
-            }
-            brc::named_bar_sync(1, NW * 32);
-            if (flags[0]) {
-                __threadfence();
-                combine_unit<HD, KVB>(p, u, r_lo, r_hi, 1, true, total, tid, scratch);
-                __threadfence();   // the run's merged partial is visible before the unit's ticket is taken
-                brc::named_bar_sync(1, NW * 32);
+        if (!whole) {
+            // ---- ticket: the CTA that completes the last share of a unit combines all of its shares
+            uint32_t i_lo, i_hi;
+            share_range(unit_first, lbase + S[u + 1] - 1, total, gridDim.x, i_lo, i_hi);
+            uint32_t *const unit_ticket = p.done + layer * BRC_DONE_BANK_WORDS + u;
+            // A unit that spans many CTAs (one long sequence alone on the GPU spans all of them) is merged
+            // in two levels, or its last arriver would pull every share through one SM: runs of `fan`
+            // consecutive shares have a ticket of their own, the run's last arriver merges the run into the
+            // slot of its first share, and the last run to finish merges the runs.
+            const uint32_t span = i_hi - i_lo + 1;
+            const bool two_level = total >= gridDim.x && span > TWO_LEVEL_MIN && gridDim.x <= MAX_RUN_CTAS;
+            if (!two_level) {
                 if (tid == 0) {
-                    const uint32_t ticket = atomicAdd(p.done + u, 1u);
-                    const uint32_t last = ticket + 1u == (span + fan - 1u) / fan;
-                    if (last) p.done[u] = 0;
+                    uint32_t pieces = span;
+                    if (total < gridDim.x) {   // fewer page-units than CTAs: some shares in between are empty
+                        pieces = 0;
+                        for (uint32_t i = i_lo; i <= i_hi; ++i)
+                            pieces += share_begin(i, total, gridDim.x) != share_begin(i + 1, total, gridDim.x);
+                    }
+                    const uint32_t ticket = atomicAdd(unit_ticket, 1u);
+                    const uint32_t last = ticket + 1u == pieces;
+                    if (last) *unit_ticket = 0;   // every share has arrived: leave the counter clean for the next launch
                     flags[0] = last;
                 }
                 brc::named_bar_sync(1, NW * 32);
                 if (flags[0]) {
                     __threadfence();
-                    combine_unit<HD, KVB>(p, u, i_lo, i_hi, fan, false, total, tid, scratch);
+                    combine_unit<HD, KVB>(p, ur, i_lo, i_hi, 1, false, total, tid, scratch, epoch, bank);
+                }
+            } else {
+                uint32_t fan = 1;
+                while (fan * fan < span) ++fan;                 // ~sqrt: both levels merge about as many
+                const uint32_t run = (blockIdx.x - i_lo) / fan;
+                const uint32_t r_lo = i_lo + run * fan, r_hi = min(r_lo + fan - 1, i_hi);
+                if (tid == 0) {
+                    // Runs of neighbouring units can start on the same CTA only as (last run of one unit,
+                    // first run of the next): the second word of the pair keeps those apart.
+                    uint32_t *cnt = p.done + MAX_UNITS + 2u * r_lo + (run != 0u);
+                    const uint32_t ticket = atomicAdd(cnt, 1u);
+                    const uint32_t last = ticket + 1u == r_hi - r_lo + 1u;
+                    if (last) *cnt = 0;
+                    flags[0] = last;
+                }
+                brc::named_bar_sync(1, NW * 32);
+                if (flags[0]) {
+                    __threadfence();
+                    combine_unit<HD, KVB>(p, ur, r_lo, r_hi, 1, true, total, tid, scratch, epoch, bank);
+                    __threadfence();   // the run's merged partial is visible before the unit's ticket is taken
+                    brc::named_bar_sync(1, NW * 32);
+                    if (tid == 0) {
+                        const uint32_t ticket = atomicAdd(unit_ticket, 1u);
+                        const uint32_t last = ticket + 1u == (span + fan - 1u) / fan;
+                        if (last) *unit_ticket = 0;
+                        flags[0] = last;
+                    }
+                    brc::named_bar_sync(1, NW * 32);
+                    if (flags[0]) {
+                        __threadfence();
+                        combine_unit<HD, KVB>(p, ur, i_lo, i_hi, fan, false, total, tid, scratch, epoch, bank);
+                    }
                 }
             }
+            brc::named_bar_sync(1, NW * 32);
         }
-        brc::named_bar_sync(1, NW * 32);
 
+        // ---- next unit of the flat (layer, unit) list that has pages
         g0 = ge;
         ++u;
-        while (u < n_units && S[u + 1] == S[u]) ++u;  // units without pages have no share
+        for (;;) {
+            if (u == n_units) {
+                u = 0;
+                if (++layer == p.n_layers) break;
+            }
+            if (S[u + 1] != S[u]) break;
+            ++u;
+        }
+    }
+
+    if (!push) return;
+    // ---------------------------------------------------------------------- cross-rank merge
+    // This CTA owns the units whose last page lies in its share, and its stride of the units without pages.
+    // All of its streaming and local merging is done, so waiting here holds nothing else up; the ranks
+    // that still stream never wait for this one.
+    if (a < b) {
+        uint32_t fl = first_layer, fu = first_u;
+        while (fl < p.n_layers) {
+            const uint32_t uend = fl * total_l + S[fu + 1];   // one past the unit's last page-unit
+            if (S[fu + 1] != S[fu]) {
+                if (uend > b) break;
+                const UnitRef ur = {fl * n_units + fu, fl, fu};
+                finalize_unit<HD, KVB>(p, ur, epoch, bank, tid, gave_up);
+                if (uend == b) break;
+            }
+            if (++fu == n_units) {
+                fu = 0;
+                ++fl;
+            }
+        }
+    }
+    for (uint32_t U = blockIdx.x; U < n_units_all; U += gridDim.x) {
+        const uint32_t fl = U / n_units, fu = U - fl * n_units;
+        if (S[fu + 1] != S[fu]) continue;
+        const UnitRef ur = {U, fl, fu};
+        finalize_unit<HD, KVB>(p, ur, epoch, bank, tid, gave_up);
+    }
+    // ---- the launch's last CTA advances the epoch (every CTA has read it by now)
+    brc::named_bar_sync(1, NW * 32);
+    if (tid == 0) {
+        const uint32_t t = atomicAdd(p.fin_ticket, 1u);
+        if (t + 1u == gridDim.x) {
+            *p.fin_ticket = 0u;
+            *p.calls = epoch;
+        }
     }
 }
 
@@ -872,12 +1099,15 @@ uint32_t seqs_per_launch(const brc_pool *pool) { return MAX_UNITS / (pool->n_kv_
 
 uint32_t grid_ctas(const brc_pool *pool) { return (uint32_t)(pool->sm_count > 0 ? pool->sm_count : 148); }
 
-// Workspace: partial slots for one launch, (units + CTAs) x KVB kv heads; acc then (m, l).
-uint64_t slots_for(const brc_pool *pool, uint32_t n_seqs) {
+// Partial slots of one launch over `n_layers` layers of `n_seqs` sequences: one per (layer, unit) plus one
+// per CTA (a share boundary inside a unit makes one more partial), x KVB kv heads; acc then (m, l).
+uint64_t slots_for(const brc_pool *pool, uint32_t n_seqs, uint32_t n_layers = 1) {
     const uint32_t per = std::min<uint32_t>(n_seqs, seqs_per_launch(pool));
     const uint32_t kvb = kvb_of(pool);
-    return ((uint64_t)per * (pool->n_kv_head / kvb) + grid_ctas(pool)) * kvb;
+    return ((uint64_t)n_layers * per * (pool->n_kv_head / kvb) + grid_ctas(pool)) * kvb;
 }
+
+uint64_t slot_floats(const brc_pool *pool) { return (uint64_t)GROUP_TILE * (pool->head_dim + 2u); }
 
 template <int HD, bool Q_F32, int KVB>
 brc_status launch_partial(brc_pool *pool, const DecodeParams &p, uint32_t grid, uint32_t smem, cudaStream_t st) {
@@ -889,24 +1119,12 @@ brc_status launch_partial(brc_pool *pool, const DecodeParams &p, uint32_t grid, 
                                       (int)SMEM_LIMIT));
         configured[pool->device] = true;
     }
-    const bool many_units = p.n_seqs * (p.n_kv_head / KVB) >= grid;
+    // With at least as many units as CTAs most units lie inside one share: compile their direct-output
+    // path in.  The cross-GPU form always goes through the partial slots (one place pushes to the peers).
+    const bool many_units = p.world <= 1 && (uint64_t)p.n_layers * p.n_seqs * (p.n_kv_head / KVB) >= grid;
     auto kern = many_units ? decode_partial_kernel<HD, Q_F32, KVB, true> : decode_partial_kernel<HD, Q_F32, KVB, false>;
     brc_stage_begin(pool, BRC_STAGE_ATTN_PARTIAL, st);
-    if (p.pdl) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(grid);
-        cfg.blockDim = dim3(NTHREADS);
-        cfg.dynamicSmemBytes = smem;
-        cfg.stream = st;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        BRC_CUDA(cudaLaunchKernelEx(&cfg, kern, KVB == 2 ? pool->tm_kv2 : pool->tm_kv, p));
-    } else {
-        kern<<<grid, NTHREADS, smem, st>>>(KVB == 2 ? pool->tm_kv2 : pool->tm_kv, p);
-    }
+    kern<<<grid, NTHREADS, smem, st>>>(KVB == 2 ? pool->tm_kv2 : pool->tm_kv, p);
     brc_stage_end(pool, BRC_STAGE_ATTN_PARTIAL, st);
     BRC_CUDA(cudaGetLastError());
     return BRC_OK;
@@ -918,14 +1136,17 @@ brc_status launch_partial_kvb(brc_pool *pool, const DecodeParams &p, uint32_t gr
                              : launch_partial<HD, Q_F32, 1>(pool, p, grid, smem, st);
 }
 
-brc_status validate_decode(const brc_pool *pool, const char *who, uint32_t layer, const void *q, int32_t q_dtype,
-                           uint32_t n_head, const uint32_t *bt, uint32_t table_stride, const uint32_t *lens,
+brc_status validate_decode(const brc_pool *pool, const char *who, uint32_t layer0, uint32_t n_layers, const void *q,
+                           int32_t q_dtype, uint32_t n_head, const uint32_t *bt, uint32_t table_stride, const uint32_t *lens,
                            uint32_t n_seqs, uint32_t max_seq_len, const void *out, const void *ws, uint64_t ws_bytes) {
     if (!pool) return brc_fail(BRC_ERR_INVALID, "%s: pool is NULL", who);
     BRC_REFUSE_Q8V(pool, who);
     if (pool->device < 0 || !pool->has_tma)
         return brc_fail(BRC_ERR_CUDA, "%s: this pool holds bookkeeping only (no device memory); compute calls need a GPU pool", who);
-    if (layer >= pool->n_layers) return brc_fail(BRC_ERR_INVALID, "%s: layer %u but the pool has %u", who, layer, pool->n_layers);
+    if ((uint64_t)layer0 + n_layers > pool->n_layers)
+        return n_layers == 1 ? brc_fail(BRC_ERR_INVALID, "%s: layer %u but the pool has %u", who, layer0, pool->n_layers)
+                             : brc_fail(BRC_ERR_INVALID, "%s: layers %u..%u but the pool has %u", who, layer0, layer0 + n_layers,
+                                        pool->n_layers);
     if (q_dtype != BRC_DTYPE_F32 && q_dtype != BRC_DTYPE_F16)
         return brc_fail(BRC_ERR_INVALID, "%s: q_dtype %d is neither f32 (0) nor f16 (1)", who, q_dtype);
     if (n_head == 0 || n_head % pool->n_kv_head != 0)
@@ -937,7 +1158,7 @@ brc_status validate_decode(const brc_pool *pool, const char *who, uint32_t layer
     if (max_seq_len > capacity)
         return brc_fail(BRC_ERR_CAPACITY, "%s would read cells up to %u but each block table holds %llu (%u pages of %u cells)",
                         who, max_seq_len, (unsigned long long)capacity, table_stride, pool->page_tokens);
-    if (n_seqs == 0) return BRC_OK;
+    if (n_seqs == 0 || n_layers == 0) return BRC_OK;
     if (!q || !bt || !lens || !out) return brc_fail(BRC_ERR_INVALID, "%s: NULL query, block table, length or output pointer", who);
     if ((reinterpret_cast<uintptr_t>(q) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u))
         return brc_fail(BRC_ERR_INVALID, "%s: query and output pointers must be 16-byte aligned", who);
@@ -949,133 +1170,205 @@ brc_status validate_decode(const brc_pool *pool, const char *who, uint32_t layer
     return BRC_OK;
 }
 
-// Optional fused append of one decode step (all nullptr / 0 when the call only attends).
-struct FusedAppend {
-    const void *k_new = nullptr;   // [n_seqs][n_kv_head * head_dim], the cell seq_len - 1 of every sequence
-    const void *v_new = nullptr;
-    int32_t dtype = BRC_DTYPE_F32;
-    // Overlap with the neighbouring layers of the same step: this launch uses bank `bank` (0 / 1) of
-    // the partial buffers and arrival counters, so the kernel before it may still be combining.
-    bool overlap = false;
-    uint32_t bank = 0;
-};
+// Decode calls on one pool share its arrival counters.  Calls on one stream are ordered anyway; a call
+// on another stream than the previous one is made to wait for it (an event recorded after every decode
+// launch), so two streams can never have decode kernels of one pool in flight together.  While a stream
+// is being captured nothing is recorded or awaited: a captured graph must be replayed on its own.
+brc_status order_after_previous_decode(brc_pool *pool, cudaStream_t st, bool *capturing) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess) cudaGetLastError();
+    *capturing = cs != cudaStreamCaptureStatusNone;
+    if (*capturing) return BRC_OK;
+    if (pool->decode_event && pool->decode_stream_set && pool->decode_stream != st)
+        BRC_CUDA(cudaStreamWaitEvent(st, pool->decode_event, 0));
+    return BRC_OK;
+}
 
-// out_ml != nullptr: partial mode (out = merged acc, out_ml = (m, l)); else final output.  One launch
-// per <= 2048 units: the kernel streams the cache, merges its own shares and, through per-unit
-// tickets, combines them (no second kernel).
-brc_status run_decode(brc_pool *pool, uint32_t layer, const void *q, int32_t q_dtype, uint32_t n_head, const float *gate,
-                      uint32_t gate_head_stride, const uint32_t *bt, uint32_t table_stride, const uint32_t *lens,
-                      uint32_t n_seqs, uint32_t max_seq_len, float scale, float *out, float *out_ml, void *ws,
-                      cudaStream_t st, const FusedAppend &app = FusedAppend()) {
-    brc_device_guard guard(pool->device);
-    const uint32_t hd = pool->head_dim;
-    const uint32_t kvb = kvb_of(pool);
-    const uint32_t n_stages = stages_for(hd, kvb);
-    const uint32_t smem = n_stages * stage_bytes_of(hd, kvb) + fixed_bytes_of(hd);
-    const uint32_t grid = grid_ctas(pool);
-    const uint32_t per = seqs_per_launch(pool);
-    const uint64_t slots = slots_for(pool, n_seqs);
-    const uint64_t bank_floats = slots * GROUP_TILE * ((uint64_t)hd + 2u);
-    float *part_acc = static_cast<float *>(ws) + (app.overlap ? app.bank * bank_floats : 0);
-    float *part_ml = part_acc + slots * GROUP_TILE * hd;
-    const size_t q_elem = q_dtype == BRC_DTYPE_F32 ? 4 : 2;
-    const size_t kv_elem = app.dtype == BRC_DTYPE_F32 ? 4 : 2;
-    for (uint32_t s0 = 0; s0 < n_seqs; s0 += per) {
-        const uint32_t ns = std::min(per, n_seqs - s0);
-        DecodeParams p;
-        p.q = static_cast<const uint8_t *>(q) + (size_t)s0 * n_head * hd * q_elem;
-        p.block_tables = bt + (size_t)s0 * table_stride;
-        p.seq_lens = lens + s0;
-        p.part_acc = part_acc;
-        p.part_ml = part_ml;
-        p.done = pool->status_dev + BRC_STATUS_WORDS + (app.overlap ? app.bank * BRC_DONE_BANK_WORDS : 0u);
-        p.pdl = app.overlap && !pool->timing && n_seqs <= per;   // per-stage events would serialise anyway
-        p.out = out + (size_t)s0 * n_head * hd;
-        p.out_ml = out_ml ? out_ml + (size_t)s0 * n_head * 2 : nullptr;
-        p.gate = gate ? gate + (size_t)s0 * n_head * gate_head_stride : nullptr;
-        p.gate_head_stride = gate_head_stride;
-        p.k_new = app.k_new ? static_cast<const uint8_t *>(app.k_new) + (size_t)s0 * pool->n_kv_head * hd * kv_elem : nullptr;
-        p.v_new = app.v_new ? static_cast<const uint8_t *>(app.v_new) + (size_t)s0 * pool->n_kv_head * hd * kv_elem : nullptr;
-        p.kv_new_f32 = app.dtype == BRC_DTYPE_F32;
-        p.k_base = pool->k_base;
-        p.v_offset = (uint64_t)(pool->v_base - pool->k_base);
-        p.status = pool->status_dev;
-        p.n_seqs = ns;
-        p.table_stride = table_stride;
-        p.max_seq_len = max_seq_len;
-        p.n_kv_head = pool->n_kv_head;
-        p.group_all = n_head / pool->n_kv_head;
-        p.n_head = n_head;
-        p.n_pages = pool->n_pages;
-        p.layer_row0 = layer * pool->n_pages * pool->n_kv_head * pool->page_tokens;
-        p.n_stages = n_stages;
-        p.scale_log2 = scale * 1.4426950408889634f;
-        // A tile holds GROUP_TILE query heads per kv head.  More than that (the reference model has 12) are
-        // taken in passes of GROUP_TILE heads, each streaming the cache again: correct, at that price.  The
-        // passes share one bank of partials and counters, so they run strictly one after the other, and
-        // only the first one appends.
-        const uint32_t passes = (p.group_all + GROUP_TILE - 1) / GROUP_TILE;
-        if (passes > 1) p.pdl = 0;
-        for (uint32_t pass = 0; pass < passes; ++pass) {
-            p.head0 = pass * GROUP_TILE;
-            p.group = std::min<uint32_t>(GROUP_TILE, p.group_all - p.head0);
-            if (pass > 0) p.k_new = p.v_new = nullptr;
-            brc_status rc;
-            if (hd == 256)
-                rc = q_dtype == BRC_DTYPE_F32 ? launch_partial_kvb<256, true>(pool, p, grid, smem, st)
-                                              : launch_partial_kvb<256, false>(pool, p, grid, smem, st);
-            else
-                rc = q_dtype == BRC_DTYPE_F32 ? launch_partial_kvb<128, true>(pool, p, grid, smem, st)
-                                              : launch_partial_kvb<128, false>(pool, p, grid, smem, st);
-            if (rc != BRC_OK) return rc;
-        }
-    }
+brc_status note_decode_issued(brc_pool *pool, cudaStream_t st, bool capturing) {
+    if (capturing) return BRC_OK;
+    if (!pool->decode_event) BRC_CUDA(cudaEventCreateWithFlags(&pool->decode_event, cudaEventDisableTiming));
+    BRC_CUDA(cudaEventRecord(pool->decode_event, st));
+    pool->decode_stream = st;
+    pool->decode_stream_set = true;
     return BRC_OK;
 }
 
 }  // namespace
 
-// Decode attention of one layer with this step's KV append fused in (used by brc_decode_step): the
-// cell seq_len - 1 of every sequence is written from k_new / v_new by the kernel itself.
-brc_status brc_decode_attn_append_fused(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype, uint32_t n_head,
-                                        const float *gate_dev, uint32_t gate_head_stride, const uint32_t *block_tables_dev,
-                                        uint32_t table_stride, const uint32_t *seq_lens_dev, uint32_t n_seqs,
-                                        uint32_t max_seq_len, float scale, float *out_dev, void *workspace_dev,
-                                        uint64_t workspace_bytes, const void *k_new_dev, const void *v_new_dev,
-                                        int32_t kv_dtype, uint32_t index_in_step, uint32_t layers_in_step, void *stream) {
-    if (brc_status rc = validate_decode(pool, "brc_decode_step", layer, q_dev, q_dtype, n_head, block_tables_dev, table_stride,
-                                        seq_lens_dev, n_seqs, max_seq_len, out_dev, workspace_dev, workspace_bytes))
+// The one implementation behind every decode entry point.  out_ml != nullptr: partial mode (out = merged
+// acc, out_ml = (m, l)); push != nullptr with world > 1: split-KV across GPUs; else the final output.
+// Launches: one per (chunk of <= 2048 units per layer) x (group of layers whose partial slots fit the
+// workspace, at most BRC_DONE_BANKS) x (pass of GROUP_TILE query heads per kv head).
+brc_status brc_decode_layers(brc_pool *pool, const char *who, const brc_layers_args &a, void *stream) {
+    if (brc_status rc = validate_decode(pool, who, a.layer0, a.n_layers, a.q, a.q_dtype, a.n_head, a.block_tables, a.table_stride,
+                                        a.seq_lens, a.n_seqs, a.max_seq_len, a.out, a.workspace, a.workspace_bytes))
         return rc;
-    if (gate_dev && gate_head_stride < pool->head_dim)
-        return brc_fail(BRC_ERR_INVALID, "brc_decode_step: gate_head_stride %u < head_dim %u", gate_head_stride, pool->head_dim);
-    if (kv_dtype != BRC_DTYPE_F32 && kv_dtype != BRC_DTYPE_F16)
-        return brc_fail(BRC_ERR_INVALID, "brc_decode_step: kv_dtype %d is neither f32 (0) nor f16 (1)", kv_dtype);
-    if (!k_new_dev || !v_new_dev || (reinterpret_cast<uintptr_t>(k_new_dev) & 15u) || (reinterpret_cast<uintptr_t>(v_new_dev) & 15u))
-        return brc_fail(BRC_ERR_INVALID, "brc_decode_step: new K/V pointers must be non-NULL and 16-byte aligned");
-    if (n_seqs == 0) return BRC_OK;
-    FusedAppend app;
-    app.k_new = k_new_dev;
-    app.v_new = v_new_dev;
-    app.dtype = kv_dtype;
-    // A workspace of layers_in_step times the minimum gives every layer of the step its own partial
-    // buffers and arrival counters: the layers (independent of one another) may then overlap freely.
-    // Nothing less is safe: a kernel whose CTAs have little or no work lets its successors start at
-    // once, so any number of the step's kernels can be in flight together.
-    uint64_t need = 0;
-    brc_decode_workspace_bytes(pool, n_seqs, n_head, &need);
-    app.overlap = layers_in_step > 1 && layers_in_step <= BRC_DONE_BANKS && workspace_bytes >= (uint64_t)layers_in_step * need;
-    app.bank = index_in_step;
-    return run_decode(pool, layer, q_dev, q_dtype, n_head, gate_dev, gate_head_stride, block_tables_dev, table_stride,
-                      seq_lens_dev, n_seqs, max_seq_len, scale, out_dev, nullptr, workspace_dev, brc_stream(stream), app);
+    if (a.gate && a.gate_head_stride < pool->head_dim)
+        return brc_fail(BRC_ERR_INVALID, "%s: gate_head_stride %u < head_dim %u", who, a.gate_head_stride, pool->head_dim);
+    if (a.k_new || a.v_new) {
+        if (a.kv_dtype != BRC_DTYPE_F32 && a.kv_dtype != BRC_DTYPE_F16)
+            return brc_fail(BRC_ERR_INVALID, "%s: kv_dtype %d is neither f32 (0) nor f16 (1)", who, a.kv_dtype);
+        if (!a.k_new || !a.v_new || (reinterpret_cast<uintptr_t>(a.k_new) & 15u) || (reinterpret_cast<uintptr_t>(a.v_new) & 15u))
+            return brc_fail(BRC_ERR_INVALID, "%s: new K/V pointers must be non-NULL and 16-byte aligned", who);
+    }
+    if (a.n_seqs == 0 || a.n_layers == 0) return BRC_OK;
+
+    brc_device_guard guard(pool->device);
+    cudaStream_t st = brc_stream(stream);
+    const uint32_t hd = pool->head_dim;
+    const uint32_t kvb = kvb_of(pool);
+    const uint32_t n_groups = pool->n_kv_head / kvb;
+    const uint32_t n_stages = stages_for(hd, kvb);
+    const uint32_t smem = n_stages * stage_bytes_of(hd, kvb) + fixed_bytes_of(hd);
+    const uint32_t grid = grid_ctas(pool);
+    const uint32_t per = seqs_per_launch(pool);
+    const size_t q_elem = a.q_dtype == BRC_DTYPE_F32 ? 4 : 2;
+    const size_t kv_elem = a.kv_dtype == BRC_DTYPE_F32 ? 4 : 2;
+    const bool push = a.push && a.push->world > 1;
+    const uint32_t ns_max = std::min(per, a.n_seqs);
+
+    // layers per launch: bounded by the counter banks, by the partial slots the workspace holds, and by
+    // 32-bit page-unit indices
+    const uint64_t ws_slots = a.workspace_bytes / (slot_floats(pool) * sizeof(float));
+    uint64_t lpl = std::min<uint64_t>(a.n_layers, BRC_DONE_BANKS);
+    {
+        const uint64_t unit_slots = (uint64_t)ns_max * n_groups * kvb;          // per layer
+        const uint64_t fit = (ws_slots - (uint64_t)grid * kvb) / unit_slots;    // >= 1: validated above
+        lpl = std::min(lpl, std::max<uint64_t>(fit, 1));
+        const uint64_t pu_layer = (uint64_t)ns_max * n_groups * ((a.max_seq_len + 15u) / 16u);
+        if (pu_layer >= (1ull << 32))
+            return brc_fail(BRC_ERR_UNSUPPORTED, "%s: %llu page-units in one layer of one launch (32-bit indices)", who,
+                            (unsigned long long)pu_layer);
+        if (pu_layer) lpl = std::min(lpl, std::max<uint64_t>(((1ull << 32) - 1) / pu_layer, 1));
+    }
+    if (push && (lpl < a.n_layers || a.n_seqs > per))
+        return brc_fail(BRC_ERR_CAPACITY,
+                        "%s: the exchange across GPUs takes one launch per call: %u layers x %u sequences need a workspace of "
+                        "%llu bytes (given %llu), at most %u layers and %u sequences",
+                        who, a.n_layers, a.n_seqs,
+                        (unsigned long long)(slots_for(pool, a.n_seqs, a.n_layers) * slot_floats(pool) * sizeof(float)),
+                        (unsigned long long)a.workspace_bytes, BRC_DONE_BANKS, per);
+
+    bool capturing = false;
+    if (brc_status rc = order_after_previous_decode(pool, st, &capturing)) return rc;
+
+    const uint64_t layer_rows = (uint64_t)pool->n_pages * pool->n_kv_head * pool->page_tokens;
+    for (uint32_t s0 = 0; s0 < a.n_seqs; s0 += per) {
+        const uint32_t ns = std::min(per, a.n_seqs - s0);
+        for (uint32_t l0 = 0; l0 < a.n_layers; l0 += (uint32_t)lpl) {
+            const uint32_t nl = std::min<uint32_t>((uint32_t)lpl, a.n_layers - l0);
+            const uint64_t slots = ((uint64_t)nl * ns * n_groups + grid) * kvb;
+            DecodeParams p = {};
+            p.q = static_cast<const uint8_t *>(a.q) + l0 * a.q_layer_stride_bytes + (size_t)s0 * a.n_head * hd * q_elem;
+            p.block_tables = a.block_tables + (size_t)s0 * a.table_stride;
+            p.seq_lens = a.seq_lens + s0;
+            p.part_acc = static_cast<float *>(a.workspace);
+            p.part_ml = p.part_acc + slots * GROUP_TILE * hd;
+            p.done = pool->status_dev + BRC_STATUS_WORDS;
+            p.out = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(a.out) + l0 * a.out_layer_stride_bytes) + (size_t)s0 * a.n_head * hd;
+            p.out_ml = a.out_ml ? a.out_ml + l0 * (a.out_ml_layer_stride_bytes / 4) + (size_t)s0 * a.n_head * 2 : nullptr;
+            p.gate = a.gate ? reinterpret_cast<const float *>(reinterpret_cast<const uint8_t *>(a.gate) + l0 * a.gate_layer_stride_bytes) +
+                                  (size_t)s0 * a.n_head * a.gate_head_stride
+                            : nullptr;
+            p.gate_head_stride = a.gate_head_stride;
+            p.k_new = a.k_new ? static_cast<const uint8_t *>(a.k_new) + l0 * a.kv_layer_stride_bytes + (size_t)s0 * pool->n_kv_head * hd * kv_elem : nullptr;
+            p.v_new = a.v_new ? static_cast<const uint8_t *>(a.v_new) + l0 * a.kv_layer_stride_bytes + (size_t)s0 * pool->n_kv_head * hd * kv_elem : nullptr;
+            p.kv_new_f32 = a.kv_dtype == BRC_DTYPE_F32;
+            p.k_base = pool->k_base;
+            p.v_offset = (uint64_t)(pool->v_base - pool->k_base);
+            p.status = pool->status_dev;
+            p.n_seqs = ns;
+            p.table_stride = a.table_stride;
+            p.max_seq_len = a.max_seq_len;
+            p.n_kv_head = pool->n_kv_head;
+            p.group_all = a.n_head / pool->n_kv_head;
+            p.n_head = a.n_head;
+            p.n_pages = pool->n_pages;
+            p.layer_rows = (uint32_t)layer_rows;
+            p.layer_row0 = (uint32_t)((a.layer0 + l0) * layer_rows);
+            p.n_stages = n_stages;
+            p.scale_log2 = a.scale * 1.4426950408889634f;
+            p.n_layers = nl;
+            p.q_layer_stride = a.q_layer_stride_bytes / q_elem;
+            p.out_layer_stride = a.out_layer_stride_bytes / 4;
+            p.out_ml_layer_stride = a.out_ml_layer_stride_bytes / 4;
+            p.gate_layer_stride = a.gate_layer_stride_bytes / 4;
+            p.kv_new_layer_stride = a.kv_layer_stride_bytes / kv_elem;
+            p.world = 1;
+            if (push) {
+                const brc_push_args &x = *a.push;
+                p.world = x.world;
+                p.rank = x.rank;
+                p.flag_items = x.flag_items;
+                p.rows_total = nl * ns * a.n_head;
+                for (uint32_t r = 0; r < x.world; ++r) p.peer_recv[r] = x.peer_recv[r];
+                p.slot_stride = x.slot_stride;
+                p.bank_stride = x.bank_stride;
+                p.flags_offset = x.flags_offset;
+                p.calls = x.calls;
+                p.fin_ticket = x.fin_ticket;
+                p.wait_ns = x.wait_ns;
+                if ((uint64_t)nl * ns * n_groups > x.flag_items || (uint64_t)p.rows_total * (hd + 2u) * 4u > x.slot_stride)
+                    return brc_fail(BRC_ERR_CAPACITY, "%s: %u layers x %u sequences exceed the exchange buffers", who, nl, ns);
+            }
+            // A tile holds GROUP_TILE query heads per kv head.  More than that (the reference model has 12) are
+            // taken in passes of GROUP_TILE heads, each streaming the cache again: correct, at that price.  The
+            // passes share the partials and counters, so they run strictly one after the other (stream
+            // order), and only the first one appends.
+            const uint32_t passes = (p.group_all + GROUP_TILE - 1) / GROUP_TILE;
+            for (uint32_t pass = 0; pass < passes; ++pass) {
+                p.head0 = pass * GROUP_TILE;
+                p.group = std::min<uint32_t>(GROUP_TILE, p.group_all - p.head0);
+                if (pass > 0) p.k_new = p.v_new = nullptr;
+                brc_status rc;
+                if (hd == 256)
+                    rc = a.q_dtype == BRC_DTYPE_F32 ? launch_partial_kvb<256, true>(pool, p, grid, smem, st)
+                                                    : launch_partial_kvb<256, false>(pool, p, grid, smem, st);
+                else
+                    rc = a.q_dtype == BRC_DTYPE_F32 ? launch_partial_kvb<128, true>(pool, p, grid, smem, st)
+                                                    : launch_partial_kvb<128, false>(pool, p, grid, smem, st);
+                if (rc != BRC_OK) return rc;
+            }
+        }
+    }
+    return note_decode_issued(pool, st, capturing);
 }
+
+uint32_t brc_decode_kvb(const brc_pool *pool) { return kvb_of(pool); }
+
+namespace {
+
+brc_layers_args one_layer(uint32_t layer, const void *q, int32_t q_dtype, uint32_t n_head, const float *gate, uint32_t gate_head_stride,
+                          const uint32_t *bt, uint32_t table_stride, const uint32_t *lens, uint32_t n_seqs, uint32_t max_seq_len,
+                          float scale, float *out, void *ws, uint64_t ws_bytes) {
+    brc_layers_args a;
+    a.layer0 = layer;
+    a.n_layers = 1;
+    a.q = q;
+    a.q_dtype = q_dtype;
+    a.n_head = n_head;
+    a.gate = gate;
+    a.gate_head_stride = gate_head_stride;
+    a.block_tables = bt;
+    a.table_stride = table_stride;
+    a.seq_lens = lens;
+    a.n_seqs = n_seqs;
+    a.max_seq_len = max_seq_len;
+    a.scale = scale;
+    a.out = out;
+    a.workspace = ws;
+    a.workspace_bytes = ws_bytes;
+    return a;
+}
+
+}  // namespace
 
 extern "C" {
 
 brc_status brc_decode_workspace_bytes(const brc_pool *pool, uint32_t n_seqs, uint32_t n_head, uint64_t *out_bytes) {
     if (!pool || !out_bytes) return brc_fail(BRC_ERR_INVALID, "brc_decode_workspace_bytes: NULL argument");
     (void)n_head;
-    const uint64_t slots = slots_for(pool, n_seqs);
-    *out_bytes = slots * GROUP_TILE * ((uint64_t)pool->head_dim + 2u) * sizeof(float);
+    *out_bytes = slots_for(pool, n_seqs) * slot_floats(pool) * sizeof(float);
     return BRC_OK;
 }
 
@@ -1084,16 +1377,10 @@ brc_status brc_paged_decode_attn(brc_pool *pool, uint32_t layer, const void *q_d
                                  uint32_t table_stride, const uint32_t *seq_lens_dev, uint32_t n_seqs,
                                  uint32_t max_seq_len, float scale, float *out_dev, void *workspace_dev,
                                  uint64_t workspace_bytes, void *stream) {
-    if (brc_status rc = validate_decode(pool, "brc_paged_decode_attn", layer, q_dev, q_dtype, n_head, block_tables_dev,
-                                        table_stride, seq_lens_dev, n_seqs, max_seq_len, out_dev, workspace_dev,
-                                        workspace_bytes))
-        return rc;
-    if (gate_dev && gate_head_stride < pool->head_dim)
-        return brc_fail(BRC_ERR_INVALID, "brc_paged_decode_attn: gate_head_stride %u < head_dim %u", gate_head_stride,
-                        pool->head_dim);
-    if (n_seqs == 0) return BRC_OK;
-    return run_decode(pool, layer, q_dev, q_dtype, n_head, gate_dev, gate_head_stride, block_tables_dev, table_stride,
-                      seq_lens_dev, n_seqs, max_seq_len, scale, out_dev, nullptr, workspace_dev, brc_stream(stream));
+    return brc_decode_layers(pool, "brc_paged_decode_attn",
+                             one_layer(layer, q_dev, q_dtype, n_head, gate_dev, gate_head_stride, block_tables_dev, table_stride,
+                                       seq_lens_dev, n_seqs, max_seq_len, scale, out_dev, workspace_dev, workspace_bytes),
+                             stream);
 }
 
 brc_status brc_decode_partial_bytes(uint32_t n_seqs, uint32_t n_head, uint32_t head_dim, uint64_t *out_bytes) {
@@ -1106,37 +1393,10 @@ brc_status brc_decode_partial(brc_pool *pool, uint32_t layer, const void *q_dev,
                               const uint32_t *block_tables_dev, uint32_t table_stride, const uint32_t *seq_lens_dev,
                               uint32_t n_seqs, uint32_t max_seq_len, float scale, void *partial_dev, void *workspace_dev,
                               uint64_t workspace_bytes, void *stream) {
-    if (brc_status rc = validate_decode(pool, "brc_decode_partial", layer, q_dev, q_dtype, n_head, block_tables_dev,
-                                        table_stride, seq_lens_dev, n_seqs, max_seq_len, partial_dev, workspace_dev,
-                                        workspace_bytes))
-        return rc;
-    if (n_seqs == 0) return BRC_OK;
-    float *acc = static_cast<float *>(partial_dev);
-    float *ml = acc + (size_t)n_seqs * n_head * pool->head_dim;
-    return run_decode(pool, layer, q_dev, q_dtype, n_head, nullptr, 0, block_tables_dev, table_stride, seq_lens_dev,
-                      n_seqs, max_seq_len, scale, acc, ml, workspace_dev, brc_stream(stream));
-}
-
-// brc_decode_partial as layer `index_in_step` of `layers_in_step` independent layers launched back to
-// back (brc_splitkv_step): with a workspace of layers_in_step times the minimum, every layer has its
-// own partial buffers and arrival counters and the kernels overlap through programmatic dependent
-// launch, exactly as in brc_decode_step.  acc and (m, l) go to separate pointers.
-brc_status brc_decode_partial_in_step(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype, uint32_t n_head,
-                                      const uint32_t *block_tables_dev, uint32_t table_stride, const uint32_t *seq_lens_dev,
-                                      uint32_t n_seqs, uint32_t max_seq_len, float scale, float *acc_dev, float *ml_dev,
-                                      void *workspace_dev, uint64_t workspace_bytes, uint32_t index_in_step,
-                                      uint32_t layers_in_step, void *stream) {
-    if (brc_status rc = validate_decode(pool, "brc_splitkv_step", layer, q_dev, q_dtype, n_head, block_tables_dev, table_stride,
-                                        seq_lens_dev, n_seqs, max_seq_len, acc_dev, workspace_dev, workspace_bytes))
-        return rc;
-    if (n_seqs == 0) return BRC_OK;
-    FusedAppend app;   // nothing to append: only the bank and the overlap are used
-    uint64_t need = 0;
-    brc_decode_workspace_bytes(pool, n_seqs, n_head, &need);
-    app.overlap = layers_in_step > 1 && layers_in_step <= BRC_DONE_BANKS && workspace_bytes >= (uint64_t)layers_in_step * need;
-    app.bank = index_in_step;
-    return run_decode(pool, layer, q_dev, q_dtype, n_head, nullptr, 0, block_tables_dev, table_stride, seq_lens_dev, n_seqs,
-                      max_seq_len, scale, acc_dev, ml_dev, workspace_dev, brc_stream(stream), app);
+    brc_layers_args a = one_layer(layer, q_dev, q_dtype, n_head, nullptr, 0, block_tables_dev, table_stride, seq_lens_dev, n_seqs,
+                                  max_seq_len, scale, static_cast<float *>(partial_dev), workspace_dev, workspace_bytes);
+    if (pool && partial_dev) a.out_ml = static_cast<float *>(partial_dev) + (size_t)n_seqs * n_head * pool->head_dim;
+    return brc_decode_layers(pool, "brc_decode_partial", a, stream);
 }
 
 brc_status brc_decode_combine(int32_t device, const void *parts_dev, uint32_t n_parts, uint64_t part_stride_bytes,
@@ -1236,15 +1496,10 @@ brc_status brc_paged_decode_attn_static(brc_pool *pool, uint32_t layer, const vo
         if (!guard.ok) return brc_fail(BRC_ERR_CUDA, "brc_paged_decode_attn_static: cannot make device %d current", pool->device);
         if (brc_status rc = static_ws_for(pool->device, &ws)) return rc;
     }
-    if (brc_status rc = validate_decode(pool, "brc_paged_decode_attn_static", layer, q_dev, q_dtype, n_head, block_tables_dev,
-                                        table_stride, seq_lens_dev, n_seqs, max_seq_len, out_dev, ws, BRC_STATIC_WS_BYTES))
-        return rc;
-    if (gate_dev && gate_head_stride < pool->head_dim)
-        return brc_fail(BRC_ERR_INVALID, "brc_paged_decode_attn_static: gate_head_stride %u < head_dim %u", gate_head_stride,
-                        pool->head_dim);
-    if (n_seqs == 0) return BRC_OK;
-    return run_decode(pool, layer, q_dev, q_dtype, n_head, gate_dev, gate_head_stride, block_tables_dev, table_stride,
-                      seq_lens_dev, n_seqs, max_seq_len, scale, out_dev, nullptr, ws, brc_stream(stream));
+    return brc_decode_layers(pool, "brc_paged_decode_attn_static",
+                             one_layer(layer, q_dev, q_dtype, n_head, gate_dev, gate_head_stride, block_tables_dev, table_stride,
+                                       seq_lens_dev, n_seqs, max_seq_len, scale, out_dev, ws, BRC_STATIC_WS_BYTES),
+                             stream);
 }
 
 }  // extern "C"

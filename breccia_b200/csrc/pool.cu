@@ -263,6 +263,7 @@ brc_status brc_pool_destroy(brc_pool *pool) {
         for (cudaEvent_t e : pool->host_uploaded) if (e) cudaEventDestroy(e);
         for (cudaEvent_t e : pool->host_computed) if (e) cudaEventDestroy(e);
         if (pool->host_all_down) cudaEventDestroy(pool->host_all_down);
+        if (pool->decode_event) cudaEventDestroy(pool->decode_event);
     }
     delete pool;
     return BRC_OK;

@@ -52,20 +52,33 @@ static brc_status decode_step_range(brc_pool *pool, uint32_t layer0, uint32_t n_
         advance_positions_kernel<<<(n_seqs + 255) / 256, 256, 0, brc_stream(stream)>>>(seq_lens_dev, pos0_dev, n_seqs);
         BRC_CUDA(cudaGetLastError());
     }
-    for (uint32_t i = first; i < first + count; ++i) {
-        const uint8_t *k = static_cast<const uint8_t *>(k_new_dev) + i * kv_layer_stride_bytes;
-        const uint8_t *v = static_cast<const uint8_t *>(v_new_dev) + i * kv_layer_stride_bytes;
-        const uint8_t *q = static_cast<const uint8_t *>(q_dev) + i * q_layer_stride_bytes;
-        const float *g = gate_dev ? reinterpret_cast<const float *>(reinterpret_cast<const uint8_t *>(gate_dev) + i * gate_layer_stride_bytes) : nullptr;
-        float *o = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(out_dev) + i * out_layer_stride_bytes);
-        // one kernel per layer: it writes the new cell (fused append) and attends over the whole cache
-        if (brc_status rc = brc_decode_attn_append_fused(pool, layer0 + i, q, q_dtype, n_head, g, gate_head_stride,
-                                                         block_tables_dev, table_stride, seq_lens_dev, n_seqs,
-                                                         max_seq_len_after, scale, o, workspace_dev, workspace_bytes, k, v,
-                                                         kv_dtype, i, n_layers, stream))
-            return rc;
-    }
-    return BRC_OK;
+    // one launch for all the layers of the part (when the workspace holds their partial slots): the kernel
+    // writes every sequence's new cell (fused append) and attends over the whole cache, layer after layer
+    brc_layers_args a;
+    a.layer0 = layer0 + first;
+    a.n_layers = count;
+    a.q = static_cast<const uint8_t *>(q_dev) + first * q_layer_stride_bytes;
+    a.q_dtype = q_dtype;
+    a.q_layer_stride_bytes = q_layer_stride_bytes;
+    a.n_head = n_head;
+    a.gate = gate_dev ? reinterpret_cast<const float *>(reinterpret_cast<const uint8_t *>(gate_dev) + first * gate_layer_stride_bytes) : nullptr;
+    a.gate_head_stride = gate_head_stride;
+    a.gate_layer_stride_bytes = gate_layer_stride_bytes;
+    a.block_tables = block_tables_dev;
+    a.table_stride = table_stride;
+    a.seq_lens = seq_lens_dev;
+    a.n_seqs = n_seqs;
+    a.max_seq_len = max_seq_len_after;
+    a.scale = scale;
+    a.out = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(out_dev) + first * out_layer_stride_bytes);
+    a.out_layer_stride_bytes = out_layer_stride_bytes;
+    a.workspace = workspace_dev;
+    a.workspace_bytes = workspace_bytes;
+    a.k_new = static_cast<const uint8_t *>(k_new_dev) + first * kv_layer_stride_bytes;
+    a.v_new = static_cast<const uint8_t *>(v_new_dev) + first * kv_layer_stride_bytes;
+    a.kv_dtype = kv_dtype;
+    a.kv_layer_stride_bytes = kv_layer_stride_bytes;
+    return brc_decode_layers(pool, "brc_decode_step", a, stream);
 }
 
 extern "C" {

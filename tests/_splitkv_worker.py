@@ -19,7 +19,8 @@ from breccia_b200.splitkv import SplitKvDecode, kv_range  # noqa: E402
 
 def _step_same_layer(split, q3, out3):
     """brc_splitkv_step over the three layers of the worker's pool (which hold the same pages), so the
-    three outputs must equal the single-layer result bit for bit."""
+    three outputs must equal the single-layer result (within 2e-6: one launch over three layers cuts its
+    shares differently from a launch over one, so the same sums are taken in another order)."""
     split.step(q3, out3)
 
 
@@ -78,7 +79,12 @@ def main():
             _step_same_layer(step, q3, out3)
             torch.cuda.synchronize()
             pool.check()
-            ok = ok and bool(torch.equal(out3[0], out)) and bool(torch.equal(out3[1], out)) and bool(torch.equal(out3[2], out))
+            step_err = max(float((out3[i] - out).abs().max()) for i in range(3))
+            ref3 = out3.clone()
+            dist.broadcast(ref3, 0)
+            ok = ok and step_err <= 2e-6 and bool(torch.equal(ref3, out3))
+            if rank == 0:
+                print(f"splitkv step over 3 layers, world {world}: max_abs vs single-layer call {step_err:.2e}", flush=True)
             step.close()
         split.close()
     flag = torch.tensor([1 if ok else 0], device="cuda")

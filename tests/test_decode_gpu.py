@@ -217,7 +217,8 @@ def test_decode_step_appends_bit_exactly_and_attends(cuda_device, kv_f16):
 def test_step_from_host_buffers_in_parts_equals_the_device_step(cuda_device, parts, pinned_out, download):
     """brc_decode_step_host (pinned host q / k / v in, output back to the host, layers in `parts` groups
     with uploads and downloads on streams of their own) against brc_decode_step on a twin pool: outputs,
-    both pools and the advanced lengths must be bit-identical, two steps in a row.  A pinned output buffer
+    both pools and the advanced lengths must be bit-identical, two steps in a row (the outputs bit-identical
+    for one group, within 2e-6 when the layers go in several launches, whose shares are cut differently).  A pinned output buffer
     is written by the kernels directly unless the caller asks for the download; a pageable one is downloaded
     group by group."""
     n_head, n_kv, hd, n_layers = 16, 2, 256, 5
@@ -241,7 +242,10 @@ def test_step_from_host_buffers_in_parts_equals_the_device_step(cuda_device, par
         host_batch.step_host(q_h, k_h, v_h, out_h, staging, parts=parts, download=download)
         for pool in pools:
             pool.check()
-        assert torch.equal(out_h, want.cpu()), f"step {step}"
+        if parts == 1:
+            assert torch.equal(out_h, want.cpu()), f"step {step}"
+        else:   # groups of layers are cut into shares of their own: same sums, another order
+            assert float((out_h - want.cpu()).abs().max()) <= 2e-6, f"step {step}"
         for layer in range(n_layers):
             for which in (0, 1):
                 assert np.array_equal(pools[0].read(which, layer), pools[1].read(which, layer)), f"pool {which} layer {layer}"
@@ -271,7 +275,7 @@ def test_step_in_two_parts_on_one_stream_equals_the_whole_step(cuda_device):
     split.step_part(2, 3, q, kn, vn, got)
     for pool in pools:
         pool.check()
-    assert torch.equal(got, want)
+    assert float((got - want).abs().max()) <= 2e-6   # two launches cut their shares differently: same sums, another order
     assert torch.equal(whole.seq_lens, split.seq_lens)
     for layer in range(n_layers):
         assert np.array_equal(pools[0].read(0, layer), pools[1].read(0, layer))
@@ -280,6 +284,75 @@ def test_step_in_two_parts_on_one_stream_equals_the_whole_step(cuda_device):
     assert err.value.code == _lib.ERR_INVALID
     for pool in pools:
         pool.release()
+
+
+def test_twelve_layers_in_one_launch_short_and_skewed_sequences_four_steps(cuda_device):
+    """One launch per step over twelve layers (the flat list runs over layer, unit, page): sequences of 1, 2
+    and 0 cells beside one of 5000, so most CTAs hold a stretch of one layer and many units lie whole inside
+    a share while others span several.  Four steps back to back without a host wait in between, then every
+    layer of every step against the oracle and the pool bit for bit."""
+    n_head, n_kv, hd, n_layers, n_steps = 16, 2, 256, 12, 4
+    lens = np.array([1, 2, 700, 0, 17, 16, 3, 5000])
+    tables, n_pool = synth.scattered_tables(58, lens, pool_factor=1.3, extra_tokens=n_steps + 1)
+    pool = KvPool(0, n_layers, n_kv, hd, n_pool)
+    host = []
+    for layer in range(n_layers):
+        k, v = fill_pool_from_host(pool, layer, 900 + 2 * layer)
+        host.append([k.view(np.uint32).copy(), v.view(np.uint32).copy()])
+    batch = DecodeBatch(pool, n_head, tables, lens)
+    qs, kns, vns, outs = [], [], [], []
+    for step in range(n_steps):
+        qs.append(oracle.to_f16(synth.normal(930 + step, n_layers * lens.size * n_head * hd)).reshape(n_layers, lens.size, n_head, hd))
+        kns.append(synth.normal(940 + step, n_layers * lens.size * n_kv * hd, 0.5).reshape(n_layers, lens.size, n_kv * hd))
+        vns.append(synth.normal(950 + step, n_layers * lens.size * n_kv * hd, 0.5).reshape(n_layers, lens.size, n_kv * hd))
+        outs.append(torch.full((n_layers, lens.size, n_head, hd), float("nan"), device="cuda"))
+    dev = [(torch.from_numpy(q).cuda().half(), torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda()) for q, k, v in zip(qs, kns, vns)]
+    for step in range(n_steps):
+        batch.step(dev[step][0], dev[step][1], dev[step][2], outs[step])
+    pool.check()
+    cur = lens.copy()
+    for step in range(n_steps):
+        got = outs[step].cpu().numpy()
+        for layer in range(n_layers):
+            kw, vw = host[layer]
+            for s in range(lens.size):
+                assert oracle.kv_append(kw, vw, tables[s], kns[step][layer, s], vns[step][layer, s], int(cur[s]), n_kv, hd) == 0
+            want, _ = oracle.decode_batch(kw.view(np.uint16), vw.view(np.uint16), tables, cur + 1, qs[step][layer], n_head, n_kv, hd)
+            assert_attention_close(got[layer], want, f"step {step} layer {layer}")
+        cur += 1
+    for layer in range(n_layers):
+        assert np.array_equal(pool.read(0, layer).reshape(-1), host[layer][0].view(np.uint16)), f"K pool, layer {layer}"
+        assert np.array_equal(pool.read(1, layer).reshape(-1), host[layer][1].view(np.uint16)), f"V pool, layer {layer}"
+    pool.release()
+
+
+def test_fused_append_skips_a_sequence_beyond_the_callers_bound(cuda_device):
+    """A step whose bound is below one sequence's new length: that sequence is reported (brc_pool_check),
+    attended up to the bound, and NOTHING is appended for it - the last cell under the bound keeps its
+    bytes - while the other sequence's cell is appended as usual."""
+    n_head, n_kv, hd = 16, 2, 256
+    lens = np.array([40, 20])
+    tables, n_pool = synth.scattered_tables(59, lens, pool_factor=1.5, extra_tokens=8)
+    pool = KvPool(0, 1, n_kv, hd, n_pool)
+    k, v = fill_pool_from_host(pool, 0, 960)
+    kw, vw = k.view(np.uint32).copy(), v.view(np.uint32).copy()
+    batch = DecodeBatch(pool, n_head, tables, lens)
+    q = torch.from_numpy(oracle.to_f16(synth.normal(961, lens.size * n_head * hd))).cuda().half().reshape(1, lens.size, n_head, hd)
+    kn = synth.normal(962, lens.size * n_kv * hd, 0.5).reshape(1, lens.size, n_kv * hd)
+    vn = synth.normal(963, lens.size * n_kv * hd, 0.5).reshape(1, lens.size, n_kv * hd)
+    kd, vd = torch.from_numpy(kn).cuda(), torch.from_numpy(vn).cuda()
+    out = torch.zeros((1, lens.size, n_head, hd), device="cuda")
+    bound = 30   # sequence 0 would reach 41 cells
+    _lib.call("brc_decode_step", pool.handle, 0, 1, C.c_void_p(batch.block_tables.data_ptr()), batch.table_stride,
+              C.c_void_p(batch.seq_lens.data_ptr()), C.c_void_p(batch.pos0.data_ptr()), lens.size, bound,
+              C.c_void_p(q.data_ptr()), DTYPE_F16, 0, n_head, C.c_void_p(kd.data_ptr()), C.c_void_p(vd.data_ptr()), DTYPE_F32, 0,
+              None, 0, 0, 0.0625, C.c_void_p(out.data_ptr()), 0, C.c_void_p(batch.scratch.data_ptr()), batch.scratch.numel(), None)
+    with pytest.raises(_lib.BrcError):
+        pool.check()
+    assert oracle.kv_append(kw, vw, tables[1], kn[0, 1], vn[0, 1], 20, n_kv, hd) == 0   # only sequence 1 appends
+    assert np.array_equal(pool.read(0, 0).reshape(-1), kw.view(np.uint16))
+    assert np.array_equal(pool.read(1, 0).reshape(-1), vw.view(np.uint16))
+    pool.release()
 
 
 def test_nan_poison_outside_live_cells_never_reaches_the_output(cuda_device):

@@ -1,4 +1,5 @@
-"""Split-KV decode across GPUs (NCCL all-gather of the partials + merge).  Needs at least two GPUs."""
+"""Split-KV decode across GPUs (partials pushed to the peers by the attention kernel itself; NCCL all-gather +
+merge as the baseline).  The cross-GPU cases need at least two GPUs."""
 import os
 import subprocess
 import sys
@@ -110,6 +111,48 @@ def test_a_peer_that_never_arrives_times_out_and_leaves_the_context_usable(cuda_
     assert bool((out == 7.0).all())
     pool.check()                      # the check word was cleared; the context still works
     assert float((out + 1).sum()) == 8.0 * n_head * hd
+    for c in comms:
+        _lib.call("brc_comm_destroy", c)
+    pool.release()
+
+
+def test_fused_exchange_whose_peer_never_arrives_times_out_and_leaves_the_context_usable(cuda_device):
+    """The same for the exchange that rides in the attention kernel (brc_splitkv_attend): rank 0 of a world
+    of two attends alone; its own partial lands and is flagged, rank 1's flag is never set, so the unit's
+    cross-rank merge gives up after 20 ms, leaves the output rows as they were and reports the expiry."""
+    import ctypes as C
+
+    import numpy as np
+
+    from breccia_b200 import _lib, synth
+    from breccia_b200.qsa import DecodeBatch, KvPool
+    from helpers import fill_pool_from_host
+
+    n_head, hd, lens = 16, 256, np.array([100])
+    tables, n_pool = synth.scattered_tables(3, lens, extra_tokens=1)
+    pool = KvPool(0, 1, 2, hd, n_pool)
+    fill_pool_from_host(pool, 0, 77)
+    batch = DecodeBatch(pool, n_head, tables, lens)
+    comms = [C.c_void_p(), C.c_void_p()]
+    for r in range(2):
+        _lib.call("brc_comm_create", pool.handle, 2, r, 1, n_head, C.byref(comms[r]))
+    arr = (C.c_void_p * 2)(comms[0], comms[1])
+    for r in range(2):
+        _lib.call("brc_comm_connect_local", comms[r], arr, 2)
+    _lib.call("brc_comm_set_wait_ms", comms[0], 20)
+    q = torch.randn((1, n_head, hd), device="cuda").half()
+    out = torch.full((1, n_head, hd), 7.0, device="cuda")
+    _lib.call("brc_splitkv_attend", comms[0], 0, C.c_void_p(q.data_ptr()), _lib.DTYPE_F16, None, 0,
+              C.c_void_p(batch.block_tables.data_ptr()), batch.table_stride, C.c_void_p(batch.seq_lens.data_ptr()), 1,
+              batch.capacity, 0.0625, C.c_void_p(out.data_ptr()), C.c_void_p(batch.scratch.data_ptr()), batch.scratch.numel(), None)
+    torch.cuda.synchronize()
+    with pytest.raises(_lib.BrcError, match="wait"):
+        pool.check()
+    assert bool((out == 7.0).all())
+    pool.check()
+    batch.attend(0, q, out)           # the plain call on the same pool still works
+    pool.check()
+    assert bool(torch.isfinite(out).all()) and not bool((out == 7.0).all())
     for c in comms:
         _lib.call("brc_comm_destroy", c)
     pool.release()
