@@ -82,6 +82,8 @@ struct brc_pool {
     // allocator
     mutable std::mutex mu;
     std::vector<uint32_t> refcount;
+    std::vector<uint32_t> tree_refs;  // of those, references held by radix trees (a page whose only holder is a tree
+                                      // is not "held by the caller": the tier neither offers nor demotes it)
     std::vector<uint32_t> free_list;  // LIFO
 };
 

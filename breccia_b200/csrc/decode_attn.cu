@@ -214,7 +214,7 @@ constexpr uint32_t MAX_RUN_CTAS = 256;    // run tickets: 2 words per CTA after 
 //
 // With p.world > 1 the final merge of a unit does not write the output: its (acc, m, l) go into this
 // rank's slot of every rank's receive buffer (its own included), then one flag per rank is released.
-template <int HD, int KVB>
+template <int HD, int KVB, bool CAN_PUSH>
 __device__ __forceinline__ void combine_unit(const DecodeParams &p, const UnitRef ur, uint32_t i_lo, uint32_t i_hi, uint32_t stride,
                                              bool to_slot, uint32_t total, uint32_t tid, float *sm, uint32_t epoch, uint32_t bank) {
     const uint32_t u = ur.u;
@@ -344,7 +344,7 @@ __device__ __forceinline__ void combine_unit(const DecodeParams &p, const UnitRe
             const size_t slot = ((size_t)(ur.U + i_lo) * KVB + k2) * GROUP_TILE + h;
             *reinterpret_cast<float4 *>(p.part_acc + slot * HD + d) = acc[ps];
             if (d == 0) *reinterpret_cast<float2 *>(p.part_ml + slot * 2) = ml;
-        } else if (p.world > 1) {
+        } else if (CAN_PUSH && p.world > 1) {
             const size_t R = ((size_t)ur.layer * p.n_seqs + s) * p.n_head + head;
             const uint64_t oa = push_acc_off(p, bank, p.rank, R, HD, d), om = push_ml_off(p, bank, p.rank, R, HD);
             for (uint32_t r = 0; r < p.world; ++r) {
@@ -371,7 +371,7 @@ __device__ __forceinline__ void combine_unit(const DecodeParams &p, const UnitRe
             *reinterpret_cast<float4 *>(p.out + o) = r;
         }
     }
-    if (!to_slot && p.world > 1) {
+    if (CAN_PUSH && !to_slot && p.world > 1) {
         // every thread's stores are ordered at system scope before the flags go out
         __threadfence_system();
         brc::named_bar_sync(1, NW * 32);
@@ -379,16 +379,20 @@ __device__ __forceinline__ void combine_unit(const DecodeParams &p, const UnitRe
     }
 }
 
-// Cross-rank merge of unit `ur` (split-KV across GPUs): waits, with a time limit, until every rank's
-// merged partial of the unit has landed in this rank's receive buffer, then merges them, normalises,
-// applies the gate and writes the output rows.  Run by the NW * 32 consumer threads of the CTA that
-// owns the unit, after that CTA has finished streaming.  On expiry the output is left as it was, the
-// check word reports it, and the CTA's later units are skipped without waiting again.
+// Cross-rank merge of rows row_first, row_first + row_step, ... of unit `ur` (split-KV across GPUs):
+// waits, with a time limit, until every rank's merged partial of the unit has landed in this rank's
+// receive buffer, then merges the rows, normalises, applies the gate and writes the output.  The rows of a
+// unit are dealt over the CTAs that streamed a share of it, each running this with its NW * 32 consumer
+// threads after it has finished streaming.  All loads of a row (every rank's (m, l) and acc) are issued
+// before any is used: one trip to L2 per row.  On expiry the rows are left as they were, the check word
+// reports it, and the CTA's later waits are skipped.
 template <int HD, int KVB>
-__device__ __forceinline__ void finalize_unit(const DecodeParams &p, const UnitRef ur, uint32_t epoch, uint32_t bank, uint32_t tid,
-                                              volatile uint32_t *gave_up) {
+__device__ __forceinline__ void finalize_unit(const DecodeParams &p, const UnitRef ur, uint32_t row_first, uint32_t row_step,
+                                              uint32_t epoch, uint32_t bank, uint32_t tid, volatile uint32_t *gave_up) {
     constexpr uint32_t TPR = HD / 4;
     constexpr uint32_t ROWS_PER_PASS = (NW * 32) / TPR;
+    const uint32_t n_rows = KVB * p.group;
+    if (row_first >= n_rows) return;   // CTA-uniform: more CTAs than rows
     if (!gave_up[0] && tid < p.world) {
         const uint32_t *f = unit_flag(p.peer_recv[p.rank], p, bank, tid, ur.U);
         bool ok = (int32_t)(ld_acquire_sys(f) - epoch) >= 0;
@@ -412,35 +416,36 @@ __device__ __forceinline__ void finalize_unit(const DecodeParams &p, const UnitR
     if (skip) return;
     const uint32_t n_groups = p.n_kv_head / KVB;
     const uint32_t s = ur.u / n_groups, kv0 = (ur.u % n_groups) * KVB;
-    const uint32_t n_rows = KVB * p.group;
     const uint32_t d = (tid % TPR) * 4;
-    for (uint32_t row = tid / TPR; row < n_rows; row += ROWS_PER_PASS) {
+    const uint8_t *own = p.peer_recv[p.rank];
+    for (uint32_t row = row_first + (tid / TPR) * row_step; row < n_rows; row += ROWS_PER_PASS * row_step) {
         const uint32_t k2 = row / p.group, h = row % p.group;
         const uint32_t head = (kv0 + k2) * p.group_all + p.head0 + h;
         const size_t R = ((size_t)ur.layer * p.n_seqs + s) * p.n_head + head;
-        float ms[BRC_MAX_WORLD], ls[BRC_MAX_WORLD];
-        float M = -INFINITY;
+        float2 ml[BRC_MAX_WORLD];
+        float4 a[BRC_MAX_WORLD];
 #pragma unroll
         for (uint32_t r = 0; r < BRC_MAX_WORLD; ++r) {
             if (r < p.world) {
-                const float2 ml = __ldcg(reinterpret_cast<const float2 *>(p.peer_recv[p.rank] + push_ml_off(p, bank, r, R, HD)));
-                ms[r] = ml.x;
-                ls[r] = ml.y;
-                if (ml.y > 0.f) M = fmaxf(M, ml.x);
+                ml[r] = __ldcg(reinterpret_cast<const float2 *>(own + push_ml_off(p, bank, r, R, HD)));
+                a[r] = __ldcg(reinterpret_cast<const float4 *>(own + push_acc_off(p, bank, r, R, HD, d)));
             }
         }
+        float M = -INFINITY;
+#pragma unroll
+        for (uint32_t r = 0; r < BRC_MAX_WORLD; ++r)
+            if (r < p.world && ml[r].y > 0.f) M = fmaxf(M, ml[r].x);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         float L = 0.f;
 #pragma unroll
         for (uint32_t r = 0; r < BRC_MAX_WORLD; ++r) {
-            if (r < p.world && ls[r] > 0.f) {
-                const float w = exp2f(ms[r] - M);
-                const float4 a = __ldcg(reinterpret_cast<const float4 *>(p.peer_recv[p.rank] + push_acc_off(p, bank, r, R, HD, d)));
-                L += w * ls[r];
-                acc.x += w * a.x;
-                acc.y += w * a.y;
-                acc.z += w * a.z;
-                acc.w += w * a.w;
+            if (r < p.world && ml[r].y > 0.f) {
+                const float w = exp2f(ml[r].x - M);
+                L += w * ml[r].y;
+                acc.x += w * a[r].x;
+                acc.y += w * a[r].y;
+                acc.z += w * a[r].z;
+                acc.w += w * a[r].w;
             }
         }
         const float inv = L > 0.f ? 1.f / L : 0.f;
@@ -482,7 +487,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t n_groups = p.n_kv_head / KVB;   // kv-head groups per sequence
     const uint32_t n_units = p.n_seqs * n_groups;  // units of one layer
-    const bool push = p.world > 1;
+    const bool push = !WHOLE_FAST && p.world > 1;   // the host launches the cross-GPU form without the direct-output path
     // Split-KV across GPUs: this launch's epoch is the number of exchanges completed so far plus one
     // (read by every CTA before any of them can take the launch's last ticket, which advances it).
     const uint32_t epoch = push ? *reinterpret_cast<volatile uint32_t *>(p.calls) + 1u : 0u;
@@ -956,7 +961,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                 brc::named_bar_sync(1, NW * 32);
                 if (flags[0]) {
                     __threadfence();
-                    combine_unit<HD, KVB>(p, ur, i_lo, i_hi, 1, false, total, tid, scratch, epoch, bank);
+                    combine_unit<HD, KVB, !WHOLE_FAST>(p, ur, i_lo, i_hi, 1, false, total, tid, scratch, epoch, bank);
                 }
             } else {
                 uint32_t fan = 1;
@@ -975,7 +980,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                 brc::named_bar_sync(1, NW * 32);
                 if (flags[0]) {
                     __threadfence();
-                    combine_unit<HD, KVB>(p, ur, r_lo, r_hi, 1, true, total, tid, scratch, epoch, bank);
+                    combine_unit<HD, KVB, !WHOLE_FAST>(p, ur, r_lo, r_hi, 1, true, total, tid, scratch, epoch, bank);
                     __threadfence();   // the run's merged partial is visible before the unit's ticket is taken
                     brc::named_bar_sync(1, NW * 32);
                     if (tid == 0) {
@@ -987,7 +992,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                     brc::named_bar_sync(1, NW * 32);
                     if (flags[0]) {
                         __threadfence();
-                        combine_unit<HD, KVB>(p, ur, i_lo, i_hi, fan, false, total, tid, scratch, epoch, bank);
+                        combine_unit<HD, KVB, !WHOLE_FAST>(p, ur, i_lo, i_hi, fan, false, total, tid, scratch, epoch, bank);
                     }
                 }
             }
@@ -1009,18 +1014,23 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 
     if (!push) return;
     // ---------------------------------------------------------------------- cross-rank merge
-    // This CTA owns the units whose last page lies in its share, and its stride of the units without pages.
-    // All of its streaming and local merging is done, so waiting here holds nothing else up; the ranks
-    // that still stream never wait for this one.
+    // The rows of a unit are dealt over the CTAs that streamed a share of it (with fewer page-units than
+    // CTAs some shares in between are empty: the CTA that holds the unit's last page then takes them all);
+    // units without pages go round the grid.  All of this CTA's streaming and local merging is done, so
+    // waiting here holds nothing else up; the ranks that still stream never wait for this one.
     if (a < b) {
         uint32_t fl = first_layer, fu = first_u;
         while (fl < p.n_layers) {
-            const uint32_t uend = fl * total_l + S[fu + 1];   // one past the unit's last page-unit
-            if (S[fu + 1] != S[fu]) {
-                if (uend > b) break;
+            const uint32_t ubeg = fl * total_l + S[fu], uend = fl * total_l + S[fu + 1];   // [ubeg, uend): the unit's page-units
+            if (ubeg >= b) break;
+            if (uend != ubeg) {
                 const UnitRef ur = {fl * n_units + fu, fl, fu};
-                finalize_unit<HD, KVB>(p, ur, epoch, bank, tid, gave_up);
-                if (uend == b) break;
+                uint32_t i_lo, i_hi;
+                share_range(ubeg, uend - 1, total, gridDim.x, i_lo, i_hi);
+                if (total >= gridDim.x)
+                    finalize_unit<HD, KVB>(p, ur, blockIdx.x - i_lo, i_hi - i_lo + 1, epoch, bank, tid, gave_up);
+                else if (blockIdx.x == i_hi)
+                    finalize_unit<HD, KVB>(p, ur, 0, 1, epoch, bank, tid, gave_up);
             }
             if (++fu == n_units) {
                 fu = 0;
@@ -1032,7 +1042,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         const uint32_t fl = U / n_units, fu = U - fl * n_units;
         if (S[fu + 1] != S[fu]) continue;
         const UnitRef ur = {U, fl, fu};
-        finalize_unit<HD, KVB>(p, ur, epoch, bank, tid, gave_up);
+        finalize_unit<HD, KVB>(p, ur, 0, 1, epoch, bank, tid, gave_up);
     }
     // ---- the launch's last CTA advances the epoch (every CTA has read it by now)
     brc::named_bar_sync(1, NW * 32);

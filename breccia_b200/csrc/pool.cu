@@ -197,6 +197,7 @@ static brc_status create_pool(int32_t device, uint32_t n_layers, uint32_t n_kv_h
     }
     p->has_tma = !v_q8;
     p->refcount.assign(n_pages, 0u);
+    p->tree_refs.assign(n_pages, 0u);
     p->free_list.resize(n_pages);
     for (uint32_t i = 0; i < n_pages; ++i) p->free_list[i] = n_pages - 1 - i;  // pop_back yields 0,1,2,...
     *out = p;
@@ -239,6 +240,7 @@ brc_status brc_pool_create_bookkeeping(uint32_t n_layers, uint32_t n_kv_head, ui
     p->layer_bytes = p->half_page_bytes * n_pages;
     p->v_layer_bytes = p->layer_bytes;
     p->refcount.assign(n_pages, 0u);
+    p->tree_refs.assign(n_pages, 0u);
     p->free_list.resize(n_pages);
     for (uint32_t i = 0; i < n_pages; ++i) p->free_list[i] = n_pages - 1 - i;
     *out = p;

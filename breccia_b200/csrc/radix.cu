@@ -39,9 +39,17 @@ struct brc_radix {
 
 namespace {
 
+// The pool counts, per page, how many of its references radix trees hold, so that the tier can tell a
+// page "held by exactly one caller" from a page only a tree holds.
+void tree_mark(brc_pool *pool, uint32_t page, int delta) {
+    std::lock_guard<std::mutex> lock(pool->mu);
+    if (page < pool->tree_refs.size()) pool->tree_refs[page] = (uint32_t)((int)pool->tree_refs[page] + delta);
+}
+
 void release_subtree(brc_radix *r, brc_radix_node *n) {
     for (auto &kv : n->children) {
         release_subtree(r, kv.second.get());
+        tree_mark(r->pool, kv.second->page, -1);
         brc_pages_release(r->pool, &kv.second->page, 1);
     }
     n->children.clear();
@@ -125,6 +133,7 @@ brc_status brc_radix_insert(brc_radix *radix, const uint32_t *tokens, uint32_t n
         if (it == n->children.end()) {
             // the tree takes its own reference; refused if the caller does not hold the page
             if (brc_status rc = brc_pages_retain(radix->pool, pages + i, 1)) return rc;
+            tree_mark(radix->pool, pages[i], +1);
             std::unique_ptr<brc_radix_node> child(new brc_radix_node());
             child->key = key;
             child->page = pages[i];
@@ -156,6 +165,7 @@ brc_status brc_radix_evict(brc_radix *radix, uint32_t n_pages, uint32_t *out_n_e
             if (!victim || leaf->tick < victim->tick) victim = leaf;
         }
         if (!victim) break;
+        tree_mark(radix->pool, victim->page, -1);
         brc_pages_release(radix->pool, &victim->page, 1);
         brc_radix_node *parent = victim->parent;
         const std::vector<uint32_t> key = victim->key;  // the node dies inside erase
@@ -166,6 +176,11 @@ brc_status brc_radix_evict(brc_radix *radix, uint32_t n_pages, uint32_t *out_n_e
     }
     if (out_n_evicted) *out_n_evicted = done;
     return BRC_OK;
+}
+
+brc_status brc_radix_release(brc_radix *radix, const uint32_t *pages, uint32_t n_pages) {
+    if (!radix) return brc_fail(BRC_ERR_INVALID, "brc_radix_release: radix is NULL");
+    return brc_pages_release(radix->pool, pages, n_pages);
 }
 
 brc_status brc_radix_stats(brc_radix *radix, uint64_t *out_nodes, uint64_t *out_hit_pages, uint64_t *out_miss_pages,

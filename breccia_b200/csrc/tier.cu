@@ -207,12 +207,23 @@ brc_status brc_tier_demote(brc_tier *tier, const uint32_t *page_ids, uint32_t n,
     if (tier->free_slot_count < n)
         return brc_fail(BRC_ERR_CAPACITY, "brc_tier_demote: %u pages but %u of %u host slots are free", n, tier->free_slot_count,
                         tier->host_pages);
-    for (uint32_t i = 0; i < n; ++i) {
-        uint32_t rc = 0;
-        if (brc_status st = brc_page_refcount(p, page_ids[i], &rc)) return st;
-        if (rc != 1)
-            return brc_fail(BRC_ERR_INVALID, "brc_tier_demote: page %u has %u holders; only a page with exactly one holder "
-                                             "(the caller) can leave HBM", page_ids[i], rc);
+    {
+        // everything is validated before the first copy is queued: ids in range, no id twice, exactly one
+        // holder, and that holder not a radix tree (its node would go on naming a freed page)
+        std::lock_guard<std::mutex> pool_lock(p->mu);
+        std::vector<uint8_t> seen(p->n_pages, 0);
+        for (uint32_t i = 0; i < n; ++i) {
+            const uint32_t pg = page_ids[i];
+            if (pg >= p->n_pages) return brc_fail(BRC_ERR_INVALID, "brc_tier_demote: page %u of %u", pg, p->n_pages);
+            if (seen[pg]) return brc_fail(BRC_ERR_INVALID, "brc_tier_demote: page %u is named twice", pg);
+            seen[pg] = 1;
+            if (p->refcount[pg] != 1)
+                return brc_fail(BRC_ERR_INVALID, "brc_tier_demote: page %u has %u holders; only a page with exactly one holder "
+                                                 "(the caller) can leave HBM", pg, p->refcount[pg]);
+            if (p->tree_refs[pg])
+                return brc_fail(BRC_ERR_INVALID, "brc_tier_demote: page %u is held by a radix tree; evict it from the tree "
+                                                 "(brc_radix_evict) before it leaves HBM", pg);
+        }
     }
     // the copies must see everything `after_stream` has written to these pages so far
     if (after_stream) {
@@ -360,7 +371,7 @@ brc_status brc_tier_lru(brc_tier *tier, uint32_t n, uint32_t *out_page_ids, uint
     {
         std::lock_guard<std::mutex> pool_lock(tier->pool->mu);   // one look at all refcounts, not a lock per page
         for (uint32_t pg = 0; pg < tier->pool->n_pages; ++pg)
-            if (tier->last_use[pg] && tier->pool->refcount[pg] == 1) cand.emplace_back(tier->last_use[pg], pg);
+            if (tier->last_use[pg] && tier->pool->refcount[pg] == 1 && !tier->pool->tree_refs[pg]) cand.emplace_back(tier->last_use[pg], pg);
     }
     const uint32_t k = std::min<uint32_t>(n, (uint32_t)cand.size());
     std::partial_sort(cand.begin(), cand.begin() + k, cand.end());

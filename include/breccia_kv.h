@@ -205,8 +205,13 @@ BRC_API brc_status brc_seq_fork(brc_pool *pool, const uint32_t *parent_table, ui
  *   out_dev   [n_seqs][n_head][head_dim] f32
  *   scale     the reference uses 1/sqrt(head_dim)
  *   workspace_dev  scratch of at least brc_decode_workspace_bytes(); contents
- *             are undefined afterwards; calls that overlap in time need
- *             separate workspaces.
+ *             are undefined afterwards.  Decode calls on one pool (every entry
+ *             point of this section, the step and split-KV ones included) share
+ *             the pool's arrival counters, so they never overlap in time: calls
+ *             on one stream are ordered by the stream, and a call issued on
+ *             another stream than the previous one is made to wait for it (an
+ *             event recorded behind every decode launch; not while a stream is
+ *             being captured - replay a captured decode on its own).
  *   max_seq_len    caller's bound on seq_lens; refused if > table_stride*page_tokens.
  * A sequence of length 0 yields zeros. */
 BRC_API brc_status brc_decode_workspace_bytes(const brc_pool *pool, uint32_t n_seqs, uint32_t n_head,
@@ -255,8 +260,10 @@ BRC_API brc_status brc_decode_combine(int32_t device, const void *parts_dev, uin
  *     capture.
  *   - All calls on a device share the one array and it keeps whatever the last
  *     call left there; nothing in it needs to start at zero.  Two calls that run
- *     at the same time on one GPU (different streams or threads) would overwrite
- *     each other's partials: issue them on one stream, or serialise them. */
+ *     at the same time on one GPU would overwrite each other's partials.  Calls
+ *     on ONE pool cannot overlap (see the workspace note above); calls on
+ *     different pools of one GPU can: issue those on one stream, or serialise
+ *     them. */
 BRC_API brc_status brc_paged_decode_attn_static(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype,
                                                 uint32_t n_head, const float *gate_dev, uint32_t gate_head_stride,
                                                 const uint32_t *block_tables_dev, uint32_t table_stride,
@@ -279,15 +286,22 @@ BRC_API brc_status brc_paged_decode_attn_static(brc_pool *pool, uint32_t layer, 
  * business) or directly (one process driving several GPUs:
  * brc_comm_connect_local with the handles of all ranks).
  *
- * brc_splitkv_attend = the local split-KV kernel (brc_decode_partial into the
- * comm's own buffer) + ONE kernel that stores the 16 512-byte-per-sequence
- * partial into every peer's slot with ordinary global stores over NVLink,
- * releases a flag per peer, waits for the peers' flags (time limit, default 1 s:
- * on expiry the output is left untouched and brc_pool_check reports
- * BRC_ERR_TIMEOUT) and merges.  Every rank computes the same output.  All ranks
- * must make the same sequence of calls.  No load ever targets peer memory and
- * nothing is multicast.  brc_splitkv_exchange_combine is the second half alone
- * (partial_dev NULL = the comm's own buffer). */
+ * brc_splitkv_attend = ONE launch of the split-KV attention kernel over this
+ * rank's cells in which the exchange rides along: the CTA that completes a
+ * (sequence, kv-head group) unit stores its merged partial (16 512 bytes per
+ * sequence at 16 heads of 256) into this rank's slot of every rank's receive
+ * buffer with ordinary global stores over NVLink and releases one flag per unit
+ * and rank; the CTA that owns the unit waits, after it has finished streaming,
+ * for all ranks' flags (time limit, default 1 s: on expiry the unit's output rows
+ * are left untouched and brc_pool_check reports BRC_ERR_TIMEOUT), merges and
+ * writes the output.  Every rank computes the same output.  All ranks must make
+ * the same sequence of calls with the same n_seqs / n_layers.  No load ever
+ * targets peer memory and nothing is multicast.  The workspace must hold the
+ * partial slots of the whole call (brc_decode_workspace_bytes() per layer);
+ * at most 64 layers and 2048 (sequence, kv-head group) units per call.
+ * brc_splitkv_exchange_combine is the exchange alone, as a kernel of its own,
+ * for a partial the caller already holds (partial_dev NULL = the comm's own
+ * buffer). */
 #define BRC_IPC_HANDLE_BYTES 64
 BRC_API brc_status brc_comm_create(brc_pool *pool, uint32_t world, uint32_t rank, uint32_t max_seqs,
                                    uint32_t n_head, brc_comm **out);
@@ -373,15 +387,15 @@ BRC_API brc_status brc_state_load(brc_pool *pool, uint32_t layer, const uint32_t
 
 /* One decode token over `n_layers` layers whose attention calls do not depend on
  * one another (the counterpart of brc_decode_step for the split-KV case, append
- * excluded): the local split-KV kernels of all layers are launched back to back
- * and overlap through programmatic dependent launch when `workspace_bytes` is at
- * least n_layers times brc_decode_workspace_bytes(); then ONE exchange + merge
- * kernel moves the partials of all layers (n_layers x 16 512 B per sequence per
- * peer).  The comm must have been created with max_seqs >= n_layers * n_seqs.
- * q is [n_layers] arrays `q_layer_stride_bytes` apart; out is
- * [n_layers][n_seqs][n_head][head_dim] f32, contiguous; gate (nullable) is
- * addressed as gate[row * gate_head_stride + d] with row = (layer, sequence,
- * head) in that order. */
+ * excluded): ONE launch whose flat work list runs over (layer, sequence, kv-head
+ * group, page), cut into equal shares per SM, so launch ramp and tail are paid
+ * once per token and a layer's exchange (see brc_splitkv_attend) overlaps the
+ * streaming of the layers behind it.  `workspace_bytes` must be at least n_layers
+ * times brc_decode_workspace_bytes(); the comm must have been created with
+ * max_seqs >= n_layers * n_seqs.  q is [n_layers] arrays `q_layer_stride_bytes`
+ * apart; out is [n_layers][n_seqs][n_head][head_dim] f32, contiguous; gate
+ * (nullable) is addressed as gate[row * gate_head_stride + d] with row = (layer,
+ * sequence, head) in that order. */
 BRC_API brc_status brc_splitkv_step(brc_comm *comm, uint32_t layer0, uint32_t n_layers, const void *q_dev,
                                     int32_t q_dtype, uint64_t q_layer_stride_bytes, const float *gate_dev,
                                     uint32_t gate_head_stride, const uint32_t *block_tables_dev,
@@ -401,15 +415,15 @@ BRC_API brc_status brc_splitkv_step(brc_comm *comm, uint32_t layer0, uint32_t n_
  * apart ([n_seqs][n_head][head_dim] and [n_seqs][n_kv_head*head_dim]).
  * `max_seq_len_after` bounds seq_lens AFTER the increment.
  * The append is carried out by the attention kernel itself (the CTA about to
- * stream the page of a sequence's newest cell writes that cell first), so a step
- * is one small kernel plus one kernel per layer.  The layers of a step do not
- * depend on one another; when `workspace_bytes` is at least n_layers times
- * brc_decode_workspace_bytes(), each layer gets its own partial buffers and the
- * kernels are launched so that a layer may start on every SM the previous one
- * has left (programmatic dependent launch).  With a smaller workspace the
- * layers run strictly one after another; results are the same.
- * Decode calls on one pool must not run concurrently on different streams: they
- * share the pool's arrival counters. */
+ * stream the page of a sequence's newest cell writes that cell first), and the
+ * layers of a step do not depend on one another, so a step is one small kernel
+ * plus ONE attention launch whose flat work list runs over (layer, sequence,
+ * kv-head group, page) when `workspace_bytes` is at least n_layers times
+ * brc_decode_workspace_bytes() (up to 64 layers per launch).  With a smaller
+ * workspace the layers go in as many launches as it takes, one after another;
+ * results agree to rounding (the launches cut their shares differently).  A
+ * sequence whose new length exceeds `max_seq_len_after` is reported through
+ * brc_pool_check, attended up to the bound, and gets no cell appended. */
 BRC_API brc_status brc_decode_step(brc_pool *pool, uint32_t layer0, uint32_t n_layers,
                                    const uint32_t *block_tables_dev, uint32_t table_stride, uint32_t *seq_lens_dev,
                                    uint32_t *pos0_dev, uint32_t n_seqs, uint32_t max_seq_len_after, const void *q_dev,
@@ -513,7 +527,11 @@ BRC_API brc_status brc_paged_prefill_attn(brc_pool *pool, uint32_t layer, const 
  *            `pages`; the tree takes its own reference on the pages it adopts
  *            (`*out_n_new` of them); existing nodes keep their page.
  *   evict  : drops up to n least-recently-used leaves whose page only the tree
- *            holds, returning those pages to the allocator. */
+ *            holds, returning those pages to the allocator.
+ *   release: gives back references `match` handed out (the same as
+ *            brc_pages_release on the tree's pool).
+ * A page the tree holds is marked in the pool: brc_tier_lru never offers it and
+ * brc_tier_demote refuses it, whatever its reference count. */
 BRC_API brc_status brc_radix_create(brc_pool *pool, brc_radix **out);
 BRC_API brc_status brc_radix_destroy(brc_radix *radix);
 BRC_API brc_status brc_radix_match(brc_radix *radix, const uint32_t *tokens, uint32_t n_tokens, uint32_t *out_pages,
@@ -521,6 +539,7 @@ BRC_API brc_status brc_radix_match(brc_radix *radix, const uint32_t *tokens, uin
 BRC_API brc_status brc_radix_insert(brc_radix *radix, const uint32_t *tokens, uint32_t n_tokens, const uint32_t *pages,
                                     uint32_t n_pages, uint32_t *out_n_new);
 BRC_API brc_status brc_radix_evict(brc_radix *radix, uint32_t n_pages, uint32_t *out_n_evicted);
+BRC_API brc_status brc_radix_release(brc_radix *radix, const uint32_t *pages, uint32_t n_pages);
 BRC_API brc_status brc_radix_stats(brc_radix *radix, uint64_t *out_nodes, uint64_t *out_hit_pages,
                                    uint64_t *out_miss_pages, uint64_t *out_evictions);
 
@@ -531,7 +550,8 @@ BRC_API brc_status brc_radix_stats(brc_radix *radix, uint64_t *out_nodes, uint64
  * RingStats) and the rules of its design note: whole pages only, a page lives in
  * exactly one tier, all layers move together, promotion is asynchronous
  * (docs/reference-engines/02-kv-and-context.md:543-581, 617-626).
- *   demote : pages with exactly one holder go HBM -> host slots on the tier's
+ *   demote : pages with exactly one holder (not a radix tree; no id twice -
+ *            checked before anything is queued) go HBM -> host slots on the tier's
  *            side stream (ordered after `after_stream`'s work so far, if given);
  *            the HBM pages return to the allocator, `out_slots` names the copies.
  *   promote: host slots -> freshly allocated HBM pages (`out_page_ids`), slots freed.

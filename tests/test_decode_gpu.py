@@ -116,13 +116,42 @@ def test_ragged_lengths_and_page_edges(cuda_device, lens):
     pool.release()
 
 
-def test_reference_geometry_shapes_2062_cells_with_gate(cuda_device):
-    """The reference's 2062-cell single-query case shape (dense, gate from the second half of each
-    head's 512-wide block, f32 query), crates/breccia-kernels/tests/attn_conformance.rs:897-1037,
-    at 16 heads (8 per kv head) since the kernels hold one 8-head tile."""
-    pool, _, _, got, want = _batch_case(16, 2, 256, [2062], seed=0xE3, gate=True, q_dtype=DTYPE_F32)
-    errs = assert_attention_close(got, want, "2062 cells")
-    print("2062 cells max_abs %.2e max_rel %.2e ref_measure %.2e" % errs)
+def test_reference_fixture_2062_cells_24_heads_lcg_streams_with_gate(cuda_device):
+    """The reference's own attention fixture (crates/breccia-kernels/tests/attn_conformance.rs:897-1037): its
+    LCG `normalish` streams 0xE3 (K) / 0xE4 (V) for 2062 cells x 2 kv heads x 256, appended in 256-cell chunks
+    as the test does, one f32 query 0xE5 of 24 heads at the last cell, the gate read in place from the second
+    half of each head's 512-wide block of stream 0xE6.  Here over ALL cells (the dense selection); expected
+    values = the oracle's f64 attend over the binary16-rounded K/V, bars as the reference's (1e-5 on its
+    measure).  The cache must hold the reference store rule's bits."""
+    n_head, n_kv, hd, cells = 24, 2, 256, 2062
+    k_all = oracle.normalish(0xE3, cells * n_kv * hd).reshape(cells, n_kv * hd)
+    v_all = oracle.normalish(0xE4, cells * n_kv * hd).reshape(cells, n_kv * hd)
+    q = oracle.normalish(0xE5, n_head * hd).reshape(1, n_head, hd)
+    q_full = oracle.normalish(0xE6, n_head * 2 * hd).reshape(1, n_head, 2, hd)
+    pool = KvPool(0, 1, n_kv, hd, 4096 // 16)
+    qsa = Qsa(pool, n_head)
+    state = QsaState(pool, cells)                      # identity-like table from the allocator
+    for start in range(0, cells, 256):
+        n = min(256, cells - start)
+        ws = qsa.workspace(n)
+        ws.k_cur.copy_(torch.from_numpy(k_all[start:start + n]))
+        ws.v_cur.copy_(torch.from_numpy(v_all[start:start + n]))
+        qsa.kv_append(state, ws, start)
+    ws1 = qsa.workspace(1, q_dtype=DTYPE_F32)
+    ws1.q.copy_(torch.from_numpy(q))
+    ws1.q_full = torch.from_numpy(q_full).cuda().reshape(1, n_head * 2 * hd)
+    qsa.topk_dense(ws1, cells - 1)
+    qsa.attend(state, ws1, cells - 1)
+    qsa.apply(state, ws1, cells - 1)
+    pool.check()
+    kg, vg = pool.gather(0, state.page_table_dev, cells)
+    assert np.array_equal(kg.view(torch.int16).cpu().numpy().view(np.uint16).reshape(cells, -1), oracle.f32_to_f16_bits_np(k_all))
+    assert np.array_equal(vg.view(torch.int16).cpu().numpy().view(np.uint16).reshape(cells, -1), oracle.f32_to_f16_bits_np(v_all))
+    want = oracle.attend(q[0], oracle.to_f16(k_all), oracle.to_f16(v_all), np.arange(cells, dtype=np.uint32), cells - 1,
+                         n_head, n_kv, hd, gate=q_full[0, :, 1, :])
+    errs = assert_attention_close(ws1.attn_out.cpu().numpy()[0], want, "reference fixture, 2062 cells")
+    print("reference fixture 2062 cells / 24 heads: max_abs %.2e max_rel %.2e ref_measure %.2e" % errs)
+    state.release()
     pool.release()
 
 

@@ -168,3 +168,45 @@ def test_back_to_back_batches_in_both_directions_keep_every_byte(cuda_device):
             assert np.array_equal(v[where[p]], want[layer][1][p]), f"V layer {layer} page {p}"
     L.brc_tier_destroy(tier)
     pool.release()
+
+
+def test_pages_held_by_a_radix_tree_stay_in_hbm_and_a_bad_batch_queues_nothing(cuda_device):
+    """A page whose only holder is the radix tree has one reference, like a page held by one caller: the
+    tier must neither offer it for demotion nor accept it (the tree's node would go on naming a freed
+    page).  And a batch that names a page twice is refused before any copy is queued: no slot is taken."""
+    pool = KvPool(0, 1, 2, 256, 24)
+    L = _lib.load()
+    mine, mp = arr(np.zeros(8))
+    assert L.brc_pages_alloc(pool.handle, 8, mp) == 0
+    radix, tier = C.c_void_p(), C.c_void_p()
+    assert L.brc_radix_create(pool.handle, C.byref(radix)) == 0
+    assert L.brc_tier_create(pool.handle, 8, C.byref(tier)) == 0
+    tokens, tp = arr(np.arange(4 * 16) + 11)
+    new = C.c_uint32()
+    assert L.brc_radix_insert(radix, tp, tokens.size, mp, 4, C.byref(new)) == 0 and new.value == 4
+    pool.release_pages(mine[:4])                       # pages 0..3: the tree is their only holder now
+    assert all(pool.refcount(int(p)) == 1 for p in mine)
+    assert L.brc_tier_touch(tier, mp, 8) == 0
+    out, op = arr(np.zeros(8))
+    n = C.c_uint32()
+    assert L.brc_tier_lru(tier, 8, op, C.byref(n)) == 0
+    assert sorted(out[:n.value].tolist()) == sorted(mine[4:].tolist())     # only the caller's own four
+    slots, sp = arr(np.zeros(8))
+    tree_page, tpp = arr(mine[:1])
+    assert L.brc_tier_demote(tier, tpp, 1, sp, None) == _lib.ERR_INVALID and b"radix tree" in L.brc_last_error()
+    twice, twp = arr([mine[4], mine[5], mine[4]])
+    assert L.brc_tier_demote(tier, twp, 3, sp, None) == _lib.ERR_INVALID and b"twice" in L.brc_last_error()
+    st = [C.c_uint64() for _ in range(4)]
+    fs = C.c_uint32()
+    assert L.brc_tier_stats(tier, *(C.byref(x) for x in st), C.byref(fs)) == 0
+    assert fs.value == 8 and st[0].value == 0           # nothing queued, no slot taken
+    # the tree's pages still match, and once evicted from the tree they are ordinary pages again
+    got, gp = arr(np.zeros(8))
+    assert L.brc_radix_match(radix, tp, tokens.size, gp, 8, C.byref(n)) == 0 and n.value == 4
+    assert L.brc_radix_release(radix, gp, 4) == 0
+    ev = C.c_uint32()
+    assert L.brc_radix_evict(radix, 4, C.byref(ev)) == 0 and ev.value == 4
+    assert pool.free_count() == 24 - 4
+    L.brc_tier_destroy(tier)
+    L.brc_radix_destroy(radix)
+    pool.release()
