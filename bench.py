@@ -17,6 +17,7 @@ device time.  Rank 0 prints ONE JSON line, which also carries
                     N GPUs, partials pushed to the peers by the attention kernel itself and merged there
                     (the only path that communicates), with the output checked against the CPU oracle
     fixed8k         (N = 1) the 32 x 8192 variant of the batched workload
+    q8v             (N = 1) the batched workload on a pool whose V page bodies are q8_0
 """
 from __future__ import annotations
 
@@ -215,7 +216,7 @@ class Ctx:
         return self.max_over_ranks(e0.elapsed_time(e1))
 
 
-def make_batch(ctx, lens0, seed, extra_tokens, n_layers=None):
+def make_batch(ctx, lens0, seed, extra_tokens, n_layers=None, v_q8=False):
     """Pool + block tables + lengths of a batch, the cache filled through the append kernel itself
     (f32 sources ~ N(0, 0.5^2), seeded on the device)."""
     import torch
@@ -226,7 +227,7 @@ def make_batch(ctx, lens0, seed, extra_tokens, n_layers=None):
 
     n_layers = n_layers or N_LAYERS
     tables, n_pool = synth.scattered_tables(seed + 7 + ctx.rank, lens0, page_tokens=PAGE, pool_factor=1.25, extra_tokens=extra_tokens)
-    pool = KvPool(ctx.local, n_layers, N_KV, HD, n_pool)
+    pool = KvPool(ctx.local, n_layers, N_KV, HD, n_pool, v_q8=v_q8)
     batch = DecodeBatch(pool, N_HEAD, tables, lens0, q_dtype=DTYPE_F16)
     gen = torch.Generator(device=ctx.dev)
     gen.manual_seed(seed + ctx.rank)
@@ -353,6 +354,33 @@ def roofline_of(res, peak, peak_src):
                                    "algorithmic_bytes_per_launch": alg1, "launches_timed": res["iso_launches"],
                                    "how": "one layer per launch (brc_paged_decode_attn), CUDA events around every launch"}
     return roof
+
+
+Q8_TOKEN_BYTES = N_KV * HD * 2 + N_KV * (HD // 32) * 36   # K binary16 + V q8_0 of one cell of one layer = 1600 B
+
+
+def bench_q8v(ctx, args, steps, warmup):
+    """The batched workload on a pool whose V page bodies are q8_0 (the reference's VLayout::Q8_0): same lengths, same
+    step (fused quantising append + attention in 12 layers, one launch); the roofline counts the bytes actually stored."""
+    import torch
+
+    lens0 = workload_lengths("cfg2", args.seed)
+    n_warm = max(warmup, 3)
+    pool, batch, q, k_new, v_new, out = make_batch(ctx, lens0, args.seed, extra_tokens=n_warm + steps + 2, v_q8=True)
+    ms = ctx.timed(lambda: batch.step(q, k_new, v_new, out), n_warm, steps, before=lambda: batch.reset_lengths(lens0)) / steps
+    pool.check()
+    pool.release()
+    del batch, q, k_new, v_new, out
+    torch.cuda.empty_cache()
+    peak, peak_src = measured_peaks()
+    lens_mid = lens0 + n_warm + (steps + 1) / 2.0
+    alg = float(lens_mid.sum() * Q8_TOKEN_BYTES + lens0.size * (N_HEAD * HD * 2 + N_HEAD * HD * 4) + ((lens_mid + PAGE - 1) // PAGE).sum() * 4) * N_LAYERS
+    achieved = alg / (ms * 1e-3) / 1e9
+    return {"workload": workload_name("cfg2") + "; V page bodies q8_0 (36 B per 32 values), K binary16: 1600 B per cached cell and layer",
+            "value": N_SEQS / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms,
+            "roofline": {"kernel": "decode_partial_kernel<256,f16 q,q8_0 V> (one launch = the 12 layers of a step)", "bound": "hbm",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "peak_source": peak_src, "algorithmic_bytes_per_launch": alg, "avg_launch_us": ms * 1e3}}
 
 
 def bench_strong(ctx, args, steps):
@@ -564,6 +592,7 @@ def run_native(args):
             if ctx.world == 1:
                 r8 = bench_batched(ctx, args, "fixed8k", steps, warmup, full=False)
                 m8 = min(r8["e2e_modes"], key=r8["e2e_modes"].get)
+                line["q8v"] = bench_q8v(ctx, args, steps, warmup)
                 line["fixed8k"] = {"workload": workload_name("fixed8k"), "value": N_SEQS / (r8["ms_step"] * 1e-3), "unit": "tok/s",
                                    "ms_per_step": r8["ms_step"], "roofline": roofline_of(r8, peak, peak_src),
                                    "e2e": {"value": N_SEQS / (r8["e2e_modes"][m8] * 1e-3), "unit": "tok/s",

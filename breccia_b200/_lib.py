@@ -83,6 +83,15 @@ SIGNATURES = {
     "brc_decode_step_part": [_vp, _u32, _u32, _u32, _u32, _vp, _u32, _vp, _vp, _u32, _u32, _vp, _i32, _u64, _u32, _vp, _vp,
                              _i32, _u64, _vp, _u32, _u64, _f32, _vp, _u64, _vp, _u64, _vp],
     "brc_topk_blocks": [_vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _i32, _vp, _vp, _vp],
+    "brc_cold_open": [_vp, C.c_char_p, _u32, _i32, _vpp],
+    "brc_cold_close": [_vp],
+    "brc_cold_spill": [_vp, _u32p, _u64p, _u32, _u32p],
+    "brc_cold_fetch": [_vp, _u32p, _u32, _i32, _u32p],
+    "brc_cold_find": [_vp, _u64, _u32p],
+    "brc_cold_stats": [_vp, _u32p, _u32p, _u64p, _u64p],
+    "brc_idx_pool": [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _f32, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _u32, _vp],
+    "brc_idx_tail": [_vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _vp],
+    "brc_idx_score": [_vp, _vp, _u32, _vp, _u32, _vp, _u32, _u32, _u32, _u32, _u32, _f32, _vp, _vp],
     "brc_pool_create_q8v": [_i32, _u32, _u32, _u32, _u32, _u32, _vpp],
     "brc_pool_v_layout": [_vp, C.POINTER(C.c_int32)],
     "brc_decode_step_host_staging_bytes": [_vp, _u32, _u32, _u32, _i32, _i32, _u64p],

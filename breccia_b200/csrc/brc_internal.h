@@ -58,6 +58,12 @@ struct brc_pool {
     // tile of one page of one kv head.
     alignas(64) CUtensorMap tm_kv;
     alignas(64) CUtensorMap tm_kv2;  // same view, box of 2 * page_tokens rows (two kv heads); even n_kv_head only
+    // q8_0 V pools: K alone as [rows][head_dim] f16 with a box of 2 * page_tokens rows (tm_k is the one-kv-head
+    // box), and the V rows as [rows][head_dim / 32 * 9] 32-bit words (288 B at head_dim 256), unswizzled,
+    // boxes of page_tokens and of 2 * page_tokens whole rows
+    alignas(64) CUtensorMap tm_k2;
+    alignas(64) CUtensorMap tm_v8;
+    alignas(64) CUtensorMap tm_v8_2;
     bool has_tma = false;
 
     // per-stage GPU timers (off unless brc_timing_enable)
@@ -103,7 +109,8 @@ brc_status brc_fail(brc_status code, const char *fmt, ...) __attribute__((format
     do {                                                                                                           \
         if ((pool)->v_q8)                                                                                          \
             return brc_fail(BRC_ERR_UNSUPPORTED,                                                                   \
-                            "%s: this pool stores V as q8_0; built for it are brc_kv_append (f32 sources), "      \
+                            "%s: this pool stores V as q8_0; built for it are brc_kv_append (f32 sources), the dense "  \
+                            "decode entry points (brc_paged_decode_attn, brc_decode_step, brc_splitkv_*), "            \
                             "brc_paged_sparse_attn, brc_page_copy / brc_seq_fork and brc_pool_read / brc_pool_write", \
                             who);                                                                                  \
     } while (0)

@@ -181,7 +181,6 @@ extern "C" {
 brc_status brc_comm_create(brc_pool *pool, uint32_t world, uint32_t rank, uint32_t max_seqs, uint32_t n_head,
                            brc_comm **out) {
     if (!pool || !out) return brc_fail(BRC_ERR_INVALID, "brc_comm_create: NULL pool or result pointer");
-    BRC_REFUSE_Q8V(pool, "brc_comm_create");
     if (pool->device < 0) return brc_fail(BRC_ERR_CUDA, "brc_comm_create: the pool holds bookkeeping only (no device memory)");
     if (world == 0 || world > MAX_WORLD || rank >= world)
         return brc_fail(BRC_ERR_INVALID, "brc_comm_create: rank %u of %u (1 to %u ranks)", rank, world, MAX_WORLD);

@@ -46,22 +46,32 @@
 
 namespace {
 
-constexpr int NW = 4;                      // consumer warps
-constexpr int NTHREADS = (NW + 1) * 32;    // + one producer warp
+// Consumer warps: 4 keep up with HBM on binary16 V (one per scheduler); the q8_0 V path issues about three times
+// the instructions per page (the quanta are converted in registers), so it runs 6 to hide their latency.
+__host__ __device__ constexpr int consumer_warps(bool v_q8) { return v_q8 ? 6 : 4; }
 constexpr int MAX_UNITS = 2048;            // (sequence, kv-head group) units per launch
 constexpr int GROUP_TILE = 8;              // query heads per kv head held by one n-tile
 constexpr uint32_t SMEM_LIMIT = 232448;    // 227 KiB opt-in maximum per CTA
 constexpr uint64_t WAIT_NS = 1000000000ull;  // one second: far beyond any legitimate wait here
+constexpr float Q8_P_SCALE = 128.f;          // see the q8_0 V path of the kernel
 
-template <int HD, int KVB>
+template <int HD, int KVB, bool VQ8 = false>
 struct Cfg {
+    static constexpr int NW = consumer_warps(VQ8);
+    static constexpr int NTHREADS = (NW + 1) * 32;         // + one producer warp
     static constexpr int KSTEPS = HD / 16;
     static constexpr int MT = HD / 16;
-    static constexpr int BOXES = HD / 64;                  // 64-column groups = TMA operations per stage
+    static constexpr int BOXES = HD / 64;                  // 64-column groups = TMA operations per stage (per K, or per K|V pair)
     static constexpr int ROWS = 16 * KVB;                  // pool rows per box: 16 cells of KVB kv heads
     static constexpr int SLAB_BYTES = ROWS * 128;          // one [rows][64 columns] slab
-    static constexpr int GROUP_BYTES = 2 * SLAB_BYTES;     // K slab then V slab of one column group
-    static constexpr int STAGE_BYTES = BOXES * GROUP_BYTES;
+    // binary16 V: [group][K slab | V slab].  q8_0 V: the K slabs, then the V rows as they lie in the pool
+    // ([rows][HD / 32 blocks of 36 bytes], unswizzled).
+    static constexpr int GROUP_BYTES = VQ8 ? SLAB_BYTES : 2 * SLAB_BYTES;   // from one column group of K to the next
+    static constexpr int VROW_BYTES = HD / 32 * 36;
+    static constexpr int VROW_WORDS = VROW_BYTES / 4;
+    static constexpr int V_OFF = BOXES * SLAB_BYTES;       // q8_0: where the V rows start in a stage
+    static constexpr int TX_BYTES = VQ8 ? BOXES * SLAB_BYTES + ROWS * VROW_BYTES : BOXES * 2 * SLAB_BYTES;   // bytes a stage receives
+    static constexpr int STAGE_BYTES = (TX_BYTES + 1023) / 1024 * 1024;     // stages start on the swizzle pattern's period
     static constexpr int NWP = NW / KVB;                   // warps that share one kv head (page interleave)
     static constexpr int OPAD = HD / 2 + 4;                // padded row of the merge scratch (half of head_dim)
     static constexpr int SCRATCH_WARP = GROUP_TILE * OPAD + 16;  // floats per warp
@@ -214,9 +224,10 @@ constexpr uint32_t MAX_RUN_CTAS = 256;    // run tickets: 2 words per CTA after 
 //
 // With p.world > 1 the final merge of a unit does not write the output: its (acc, m, l) go into this
 // rank's slot of every rank's receive buffer (its own included), then one flag per rank is released.
-template <int HD, int KVB, bool CAN_PUSH>
+template <int HD, int KVB, bool CAN_PUSH, bool VQ8>
 __device__ __forceinline__ void combine_unit(const DecodeParams &p, const UnitRef ur, uint32_t i_lo, uint32_t i_hi, uint32_t stride,
                                              bool to_slot, uint32_t total, uint32_t tid, float *sm, uint32_t epoch, uint32_t bank) {
+    constexpr int NW = consumer_warps(VQ8);
     const uint32_t u = ur.u;
     constexpr uint32_t TPR = HD / 4;                    // threads per output row (float4 each)
     constexpr uint32_t ROWS_PER_PASS = (NW * 32) / TPR;
@@ -386,9 +397,10 @@ __device__ __forceinline__ void combine_unit(const DecodeParams &p, const UnitRe
 // threads after it has finished streaming.  All loads of a row (every rank's (m, l) and acc) are issued
 // before any is used: one trip to L2 per row.  On expiry the rows are left as they were, the check word
 // reports it, and the CTA's later waits are skipped.
-template <int HD, int KVB>
+template <int HD, int KVB, bool VQ8>
 __device__ __forceinline__ void finalize_unit(const DecodeParams &p, const UnitRef ur, uint32_t row_first, uint32_t row_step,
                                               uint32_t epoch, uint32_t bank, uint32_t tid, volatile uint32_t *gave_up) {
+    constexpr int NW = consumer_warps(VQ8);
     constexpr uint32_t TPR = HD / 4;
     constexpr uint32_t ROWS_PER_PASS = (NW * 32) / TPR;
     const uint32_t n_rows = KVB * p.group;
@@ -464,10 +476,20 @@ __device__ __forceinline__ void finalize_unit(const DecodeParams &p, const UnitR
 // WHOLE_FAST: compile the direct-output path for units that lie wholly inside one CTA's share.  It pays when
 // there are at least as many units as CTAs (many short sequences); with few long sequences no unit can
 // be of that kind, and leaving the path out keeps the streaming loop's code as lean as it was.
-template <int HD, bool Q_F32, int KVB, bool WHOLE_FAST>
-__global__ void __launch_bounds__(NTHREADS, 1)
-    decode_partial_kernel(const __grid_constant__ CUtensorMap tm_kv, const DecodeParams p) {
-    using C = Cfg<HD, KVB>;
+//
+// VQ8: the pool stores V as q8_0 blocks (one f32 scale + 32 signed bytes per 32 values, 0.5625x the bytes;
+// crates/breccia-kernels/src/qsa/mod.rs:325-349, read rule shaders/qsa_attn_apply.comp:60-77).  tm_kv is then
+// the 2-D view of K alone and tm_v8 the view of the V rows in 32-bit words; a stage holds the K slabs and the
+// page's V rows as they lie in the pool.  The quanta enter the tensor cores as EXACT binary16 integers
+// (built in registers: no dequantised tile is ever written), and the per-(cell, block) scale is folded
+// into the probabilities of that block, split into a binary16 head and tail as before - so the result
+// carries the same ~22 significant bits as the binary16 path.
+template <int HD, bool Q_F32, int KVB, bool WHOLE_FAST, bool VQ8>
+__global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
+    decode_partial_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_v8, const DecodeParams p) {
+    using C = Cfg<HD, KVB, VQ8>;
+    constexpr int NW = C::NW;
+    constexpr int NTHREADS = C::NTHREADS;
     extern __shared__ uint8_t smem_raw[];
     // The 128-byte swizzle pattern repeats every 1024 bytes: tiles must start on that boundary.
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
@@ -500,6 +522,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         }
         brc::mbar_fence_init();
         brc::tma_prefetch_desc(&tm_kv);
+        if (VQ8) brc::tma_prefetch_desc(&tm_v8);
         dead_cta[0] = 0u;
         gave_up[0] = 0u;
     }
@@ -608,7 +631,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                     if (!wait_bounded(empty0 + 8u * stage, ((kk / p.n_stages) & 1u) ^ 1u))
                         dead = 1;
                     else
-                        brc::mbar_arrive_expect_tx(fb, C::STAGE_BYTES);
+                        brc::mbar_arrive_expect_tx(fb, C::TX_BYTES);
                 }
                 dead = __shfl_sync(0xffffffffu, dead, 0);
                 if (dead) break;
@@ -642,7 +665,32 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                                     vo = make_uint4(brc::flush_f16x2(vo.x), brc::flush_f16x2(vo.y), brc::flush_f16x2(vo.z), brc::flush_f16x2(vo.w));
                                 }
                                 *reinterpret_cast<uint4 *>(p.k_base + dst) = ko;
-                                *reinterpret_cast<uint4 *>(p.k_base + p.v_offset + dst) = vo;
+                                if (!VQ8) {
+                                    *reinterpret_cast<uint4 *>(p.k_base + p.v_offset + dst) = vo;
+                                } else {
+                                    // q8_0 store rule (shaders/qsa_kv_append.comp:117-133), from the f32 value: the four
+                                    // lanes of a 32-value block share its maximum; scale = amax / 127 (1 for an all-zero
+                                    // block), q = round-half-away(clamp(x / scale, +-127)); IEEE division and roundf, so the
+                                    // bytes equal the append kernel's
+                                    const float4 *vs = reinterpret_cast<const float4 *>(static_cast<const float *>(p.v_new) + src);
+                                    const float4 y0 = __ldg(vs), y1 = __ldg(vs + 1);
+                                    float amax = fmaxf(fmaxf(fmaxf(fabsf(y0.x), fabsf(y0.y)), fmaxf(fabsf(y0.z), fabsf(y0.w))),
+                                                       fmaxf(fmaxf(fabsf(y1.x), fabsf(y1.y)), fmaxf(fabsf(y1.z), fabsf(y1.w))));
+                                    constexpr uint32_t row_lanes = HD / 8 >= 32 ? 0xffffffffu : ((1u << (HD / 8 % 32)) - 1u);
+                                    amax = fmaxf(amax, __shfl_xor_sync(row_lanes, amax, 1));
+                                    amax = fmaxf(amax, __shfl_xor_sync(row_lanes, amax, 2));
+                                    const float scale = amax > 0.f ? __fdiv_rn(amax, 127.f) : 1.f;
+                                    auto quant = [scale](float x) {
+                                        return (uint32_t)(int32_t)roundf(fminf(fmaxf(__fdiv_rn(x, scale), -127.f), 127.f)) & 0xffu;
+                                    };
+                                    const uint32_t w0 = quant(y0.x) | (quant(y0.y) << 8) | (quant(y0.z) << 16) | (quant(y0.w) << 24);
+                                    const uint32_t w1 = quant(y1.x) | (quant(y1.y) << 8) | (quant(y1.z) << 16) | (quant(y1.w) << 24);
+                                    uint32_t *blk = reinterpret_cast<uint32_t *>(p.k_base + p.v_offset) +
+                                                    ((uint64_t)(r + k2 * 16u + cell) * (HD / 32) + (lane >> 2)) * 9u;
+                                    if ((lane & 3u) == 0u) blk[0] = __float_as_uint(scale);
+                                    blk[1u + 2u * (lane & 3u)] = w0;
+                                    blk[2u + 2u * (lane & 3u)] = w1;
+                                }
                             }
                             brc::fence_proxy_async_global();
                         }
@@ -650,10 +698,19 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                     }
                 }
                 // One operation per 64-column group (issued by neighbouring lanes of one instruction).
-                // Shared memory: [group][K|V][row = kv head * 16 + cell][64 columns], 128-byte swizzled.
-                if (lane < C::BOXES)
-                    brc::tma_load_3d(brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES) + lane * C::GROUP_BYTES, &tm_kv,
-                                     (int32_t)(lane * 64u), (int32_t)r, 0, fb, policy);
+                // Shared memory: [group][K|V][row = kv head * 16 + cell][64 columns], 128-byte swizzled; with q8_0 V the
+                // K slabs of all groups, then one more operation for the page's V rows (whole rows, unswizzled).
+                if (!VQ8) {
+                    if (lane < C::BOXES)
+                        brc::tma_load_3d(brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES) + lane * C::GROUP_BYTES, &tm_kv,
+                                         (int32_t)(lane * 64u), (int32_t)r, 0, fb, policy);
+                } else {
+                    if (lane < C::BOXES)
+                        brc::tma_load_2d(brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES) + lane * C::GROUP_BYTES, &tm_kv,
+                                         (int32_t)(lane * 64u), (int32_t)r, fb, policy);
+                    else if (lane == C::BOXES)
+                        brc::tma_load_2d(brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES) + C::V_OFF, &tm_v8, 0, (int32_t)r, fb, policy);
+                }
                 issued = kk + 1;
             }
         }
@@ -685,6 +742,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     const uint32_t v_r = (lane & 7u) + (lane >> 4) * 8u;
     const uint32_t v_x = ((lane >> 3) & 1u) ^ (v_r & 7u);
     const uint32_t v_lane = C::SLAB_BYTES + (kl * 16u + v_r) * 128u;
+    // q8_0 V: this lane's four cells in the B-operand layout (k = 2t, 2t + 1, 2t + 8, 2t + 9 with t = lane & 3) and its
+    // word of every 32-value block (bytes 4g .. 4g + 3 with g = lane >> 2); byte offsets from the stage's V rows
+    const uint32_t q8_c0 = C::V_OFF + (kl * 16u + (lane & 3u) * 2u) * C::VROW_BYTES;
 
     uint32_t kw = cw;                          // next local page-unit of this warp
     uint32_t stage = cw % p.n_stages, parity = 0;
@@ -757,11 +817,18 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                 if (nv < 16u) {
                     // Cells past the sequence end may hold anything (NaN included); their scores are
                     // masked below, and their V rows are cleared so 0 * NaN never reaches the sum.
-                    for (uint32_t i = lane; i < (16u - nv) * 8u * C::BOXES; i += 32) {
-                        const uint32_t row = kl * 16u + nv + i / (8u * C::BOXES);
-                        const uint32_t within = i % (8u * C::BOXES);
-                        const uint32_t addr = sbase + (within >> 3) * C::GROUP_BYTES + C::SLAB_BYTES + row * 128u + (within & 7u) * 16u;
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(addr), "r"(0u) : "memory");
+                    if (!VQ8) {
+                        for (uint32_t i = lane; i < (16u - nv) * 8u * C::BOXES; i += 32) {
+                            const uint32_t row = kl * 16u + nv + i / (8u * C::BOXES);
+                            const uint32_t within = i % (8u * C::BOXES);
+                            const uint32_t addr = sbase + (within >> 3) * C::GROUP_BYTES + C::SLAB_BYTES + row * 128u + (within & 7u) * 16u;
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(addr), "r"(0u) : "memory");
+                        }
+                    } else {   // scales and quanta alike: a zero scale times a zero probability is zero
+                        for (uint32_t i = lane; i < (16u - nv) * (C::VROW_BYTES / 16u); i += 32) {
+                            const uint32_t addr = sbase + C::V_OFF + (kl * 16u + nv) * C::VROW_BYTES + i * 16u;
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(addr), "r"(0u) : "memory");
+                        }
                     }
                     __syncwarp();
                 }
@@ -818,13 +885,67 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                 const uint32_t bh1 = brc::movmatrix_trans(*reinterpret_cast<const uint32_t *>(&ph23));
                 const uint32_t bl0 = brc::movmatrix_trans(brc::pack_half2(p0 - f01.x, p1 - f01.y));
                 const uint32_t bl1 = brc::movmatrix_trans(brc::pack_half2(p2 - f23.x, p3 - f23.y));
-                // ---- O^T += V^T . P^T
+                if (!VQ8) {
+                    // ---- O^T += V^T . P^T
 #pragma unroll
-                for (int mt = 0; mt < C::MT; ++mt) {
-                    uint32_t af[4];
-                    brc::ldmatrix_x4_trans(af, sbase + (mt >> 2) * C::GROUP_BYTES + v_lane + ((v_x ^ ((mt & 3) * 2u)) << 4));
-                    brc::mma_16816(o[mt], af, bh0, bh1);
-                    brc::mma_16816(o[mt], af, bl0, bl1);
+                    for (int mt = 0; mt < C::MT; ++mt) {
+                        uint32_t af[4];
+                        brc::ldmatrix_x4_trans(af, sbase + (mt >> 2) * C::GROUP_BYTES + v_lane + ((v_x ^ ((mt & 3) * 2u)) << 4));
+                        brc::mma_16816(o[mt], af, bh0, bh1);
+                        brc::mma_16816(o[mt], af, bl0, bl1);
+                    }
+                } else {
+                    // ---- q8_0 V.  The probabilities in the B-operand layout, back in f32 (head + tail): this lane holds
+                    //      cells 2t, 2t + 1, 2t + 8, 2t + 9 of head g.
+                    const float2 h0f = __half22float2(*reinterpret_cast<const __half2 *>(&bh0)), t0f = __half22float2(*reinterpret_cast<const __half2 *>(&bl0));
+                    const float2 h1f = __half22float2(*reinterpret_cast<const __half2 *>(&bh1)), t1f = __half22float2(*reinterpret_cast<const __half2 *>(&bl1));
+                    // Scaled by 2^7 here and back at the end of the unit: a block's scale is ~amax / 127, so p * scale is
+                    // small and the binary16 tail of the product would fall among the subnormals, whose fixed step
+                    // (2^-24) is then multiplied by quanta of up to 127.  The factor keeps the tails normal for any V
+                    // inside binary16's range and costs nothing (a power of two).
+                    const float pb0 = (h0f.x + t0f.x) * Q8_P_SCALE, pb1 = (h0f.y + t0f.y) * Q8_P_SCALE;
+                    const float pb2 = (h1f.x + t1f.x) * Q8_P_SCALE, pb3 = (h1f.y + t1f.y) * Q8_P_SCALE;
+                    const uint32_t vrow = sbase + q8_c0;
+#pragma unroll
+                    for (int blk = 0; blk < HD / 32; ++blk) {
+                        // the block's scale of each of the four cells folded into their probabilities, head + tail again
+                        const uint32_t at = vrow + blk * 36u;
+                        float s0, s1, s2, s3;
+                        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s0) : "r"(at));
+                        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s1) : "r"(at + C::VROW_BYTES));
+                        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s2) : "r"(at + 8u * C::VROW_BYTES));
+                        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s3) : "r"(at + 9u * C::VROW_BYTES));
+                        const float w0 = pb0 * s0, w1 = pb1 * s1, w2 = pb2 * s2, w3 = pb3 * s3;
+                        const __half2 wh01 = __floats2half2_rn(w0, w1), wh23 = __floats2half2_rn(w2, w3);
+                        const float2 g01 = __half22float2(wh01), g23 = __half22float2(wh23);
+                        const uint32_t ph0 = *reinterpret_cast<const uint32_t *>(&wh01), ph1 = *reinterpret_cast<const uint32_t *>(&wh23);
+                        const uint32_t pl0 = brc::pack_half2(w0 - g01.x, w1 - g01.y), pl1 = brc::pack_half2(w2 - g23.x, w3 - g23.y);
+                        // the quanta: this lane's word of the block in each of its four cells = values d = 32 blk + 4 g + j;
+                        // byte j of two neighbouring cells becomes one binary16 pair, EXACT: bits 0x6400 | (q ^ 0x80) are
+                        // 1024 + (q + 128), and 1152 is subtracted
+                        uint32_t x0, x1, x2, x3;
+                        const uint32_t qa = at + 4u + (lane >> 2) * 4u;
+                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(x0) : "r"(qa));
+                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(x1) : "r"(qa + C::VROW_BYTES));
+                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(x2) : "r"(qa + 8u * C::VROW_BYTES));
+                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(x3) : "r"(qa + 9u * C::VROW_BYTES));
+                        x0 ^= 0x80808080u, x1 ^= 0x80808080u, x2 ^= 0x80808080u, x3 ^= 0x80808080u;
+                        const uint32_t ya = __byte_perm(x0, x1, 0x5410), yb = __byte_perm(x0, x1, 0x7632);   // bytes (0, 1) and (2, 3) of cells 2t, 2t + 1
+                        const uint32_t za = __byte_perm(x2, x3, 0x5410), zb = __byte_perm(x2, x3, 0x7632);   // of cells 2t + 8, 2t + 9
+                        const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x6480));        // 1152
+                        auto ints = [bias](uint32_t y, uint32_t sel) {
+                            const uint32_t r = __byte_perm(y, 0x64646464u, sel);
+                            const __half2 v = __hsub2(*reinterpret_cast<const __half2 *>(&r), bias);
+                            return *reinterpret_cast<const uint32_t *>(&v);
+                        };
+                        // tile 2 blk: rows g, g + 8 = bytes 0, 1; tile 2 blk + 1: bytes 2, 3
+                        const uint32_t a_lo[4] = {ints(ya, 0x4240), ints(ya, 0x4341), ints(za, 0x4240), ints(za, 0x4341)};
+                        const uint32_t a_hi[4] = {ints(yb, 0x4240), ints(yb, 0x4341), ints(zb, 0x4240), ints(zb, 0x4341)};
+                        brc::mma_16816(o[2 * blk], a_lo, ph0, ph1);
+                        brc::mma_16816(o[2 * blk], a_lo, pl0, pl1);
+                        brc::mma_16816(o[2 * blk + 1], a_hi, ph0, ph1);
+                        brc::mma_16816(o[2 * blk + 1], a_hi, pl0, pl1);
+                    }
                 }
                 // ---- hand the stage back to the producer
                 if (nv < 16u) brc::fence_proxy_async_smem();
@@ -870,11 +991,16 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 #pragma unroll
             for (int mh = 0; mh < C::MT / 2; ++mh) {
                 const int mt = hf * (C::MT / 2) + mh;
-                const uint32_t d0 = mh * 16 + t0;
-                sw[h0 * C::OPAD + d0] = o[mt][0];
-                sw[(h0 + 1) * C::OPAD + d0] = o[mt][1];
-                sw[h0 * C::OPAD + d0 + 8] = o[mt][2];
-                sw[(h0 + 1) * C::OPAD + d0 + 8] = o[mt][3];
+                // rows t0 and t0 + 8 of accumulator tile mt hold value d0 and d1 of this half of head_dim: with
+                // binary16 V the tile's rows are consecutive values; with q8_0 V a lane's four bytes of a block
+                // sit in rows t0, t0 + 8 of two neighbouring tiles
+                const uint32_t d0 = VQ8 ? (mh >> 1) * 32 + t0 * 4 + (mh & 1) * 2 : mh * 16 + t0;
+                const uint32_t d1 = VQ8 ? d0 + 1 : d0 + 8;
+                constexpr float back = VQ8 ? 1.f / Q8_P_SCALE : 1.f;   // undoes the factor on the q8_0 probabilities (exact)
+                sw[h0 * C::OPAD + d0] = o[mt][0] * back;
+                sw[(h0 + 1) * C::OPAD + d0] = o[mt][1] * back;
+                sw[h0 * C::OPAD + d1] = o[mt][2] * back;
+                sw[(h0 + 1) * C::OPAD + d1] = o[mt][3] * back;
             }
             brc::named_bar_sync(1, NW * 32);
             if (hf == 0 && tid < KVB * GROUP_TILE) {
@@ -961,7 +1087,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                 brc::named_bar_sync(1, NW * 32);
                 if (flags[0]) {
                     __threadfence();
-                    combine_unit<HD, KVB, !WHOLE_FAST>(p, ur, i_lo, i_hi, 1, false, total, tid, scratch, epoch, bank);
+                    combine_unit<HD, KVB, !WHOLE_FAST, VQ8>(p, ur, i_lo, i_hi, 1, false, total, tid, scratch, epoch, bank);
                 }
             } else {
                 uint32_t fan = 1;
@@ -980,7 +1106,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                 brc::named_bar_sync(1, NW * 32);
                 if (flags[0]) {
                     __threadfence();
-                    combine_unit<HD, KVB, !WHOLE_FAST>(p, ur, r_lo, r_hi, 1, true, total, tid, scratch, epoch, bank);
+                    combine_unit<HD, KVB, !WHOLE_FAST, VQ8>(p, ur, r_lo, r_hi, 1, true, total, tid, scratch, epoch, bank);
                     __threadfence();   // the run's merged partial is visible before the unit's ticket is taken
                     brc::named_bar_sync(1, NW * 32);
                     if (tid == 0) {
@@ -992,7 +1118,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                     brc::named_bar_sync(1, NW * 32);
                     if (flags[0]) {
                         __threadfence();
-                        combine_unit<HD, KVB, !WHOLE_FAST>(p, ur, i_lo, i_hi, fan, false, total, tid, scratch, epoch, bank);
+                        combine_unit<HD, KVB, !WHOLE_FAST, VQ8>(p, ur, i_lo, i_hi, fan, false, total, tid, scratch, epoch, bank);
                     }
                 }
             }
@@ -1028,9 +1154,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                 uint32_t i_lo, i_hi;
                 share_range(ubeg, uend - 1, total, gridDim.x, i_lo, i_hi);
                 if (total >= gridDim.x)
-                    finalize_unit<HD, KVB>(p, ur, blockIdx.x - i_lo, i_hi - i_lo + 1, epoch, bank, tid, gave_up);
+                    finalize_unit<HD, KVB, VQ8>(p, ur, blockIdx.x - i_lo, i_hi - i_lo + 1, epoch, bank, tid, gave_up);
                 else if (blockIdx.x == i_hi)
-                    finalize_unit<HD, KVB>(p, ur, 0, 1, epoch, bank, tid, gave_up);
+                    finalize_unit<HD, KVB, VQ8>(p, ur, 0, 1, epoch, bank, tid, gave_up);
             }
             if (++fu == n_units) {
                 fu = 0;
@@ -1042,7 +1168,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         const uint32_t fl = U / n_units, fu = U - fl * n_units;
         if (S[fu + 1] != S[fu]) continue;
         const UnitRef ur = {U, fl, fu};
-        finalize_unit<HD, KVB>(p, ur, 0, 1, epoch, bank, tid, gave_up);
+        finalize_unit<HD, KVB, VQ8>(p, ur, 0, 1, epoch, bank, tid, gave_up);
     }
     // ---- the launch's last CTA advances the epoch (every CTA has read it by now)
     brc::named_bar_sync(1, NW * 32);
@@ -1086,10 +1212,17 @@ __global__ void __launch_bounds__(HD)
 // ---------------------------------------------------------------------------------------------
 uint32_t kvb_of(const brc_pool *pool) { return pool->n_kv_head % 2u == 0u ? 2u : 1u; }
 
-uint32_t stage_bytes_of(uint32_t head_dim, uint32_t kvb) { return kvb * 2u * 16u * head_dim * 2u; }
+// Bytes from one ring stage to the next (Cfg::STAGE_BYTES): K and V tiles of 16 cells of `kvb` kv heads; with q8_0 V
+// the V part is 36 bytes per 32 values, and the sum is rounded up to the swizzle pattern's 1024-byte period.
+uint32_t stage_bytes_of(uint32_t head_dim, uint32_t kvb, bool v_q8) {
+    const uint32_t k = kvb * 16u * head_dim * 2u;
+    const uint32_t v = v_q8 ? kvb * 16u * (head_dim / 32u * 36u) : k;
+    return (k + v + 1023u) / 1024u * 1024u;
+}
 
-uint32_t fixed_bytes_of(uint32_t head_dim) {
-    return head_dim == 256 ? Cfg<256, 1>::FIXED_BYTES : Cfg<128, 1>::FIXED_BYTES;  // independent of KVB
+uint32_t fixed_bytes_of(uint32_t head_dim, bool v_q8) {   // independent of KVB
+    if (v_q8) return head_dim == 256 ? Cfg<256, 1, true>::FIXED_BYTES : Cfg<128, 1, true>::FIXED_BYTES;
+    return head_dim == 256 ? Cfg<256, 1>::FIXED_BYTES : Cfg<128, 1>::FIXED_BYTES;
 }
 
 // Ring depth: what fits, rounded down to a multiple of the NW / KVB warps that interleave page-units.
@@ -1099,9 +1232,9 @@ uint32_t fixed_bytes_of(uint32_t head_dim) {
 // round r - 1 of a stage knows; a different warp asking for round r while round r - 1 is still
 // landing would see "parity r done" (it is round r - 2 that is), read a half-written stage and hand
 // it back a second time.
-uint32_t stages_for(uint32_t head_dim, uint32_t kvb) {
-    const uint32_t fit = std::min<uint32_t>((SMEM_LIMIT - fixed_bytes_of(head_dim)) / stage_bytes_of(head_dim, kvb), 24u);
-    const uint32_t nwp = NW / kvb;
+uint32_t stages_for(uint32_t head_dim, uint32_t kvb, bool v_q8) {
+    const uint32_t fit = std::min<uint32_t>((SMEM_LIMIT - fixed_bytes_of(head_dim, v_q8)) / stage_bytes_of(head_dim, kvb, v_q8), 24u);
+    const uint32_t nwp = (uint32_t)consumer_warps(v_q8) / kvb;
     return fit / nwp * nwp;
 }
 
@@ -1119,22 +1252,25 @@ uint64_t slots_for(const brc_pool *pool, uint32_t n_seqs, uint32_t n_layers = 1)
 
 uint64_t slot_floats(const brc_pool *pool) { return (uint64_t)GROUP_TILE * (pool->head_dim + 2u); }
 
-template <int HD, bool Q_F32, int KVB>
+template <int HD, bool Q_F32, int KVB, bool VQ8>
 brc_status launch_partial(brc_pool *pool, const DecodeParams &p, uint32_t grid, uint32_t smem, cudaStream_t st) {
     static bool configured[64] = {};
     if (pool->device < 64 && !configured[pool->device]) {
-        BRC_CUDA(cudaFuncSetAttribute(decode_partial_kernel<HD, Q_F32, KVB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        BRC_CUDA(cudaFuncSetAttribute(decode_partial_kernel<HD, Q_F32, KVB, false, VQ8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)SMEM_LIMIT));
-        BRC_CUDA(cudaFuncSetAttribute(decode_partial_kernel<HD, Q_F32, KVB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        BRC_CUDA(cudaFuncSetAttribute(decode_partial_kernel<HD, Q_F32, KVB, true, VQ8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)SMEM_LIMIT));
         configured[pool->device] = true;
     }
     // With at least as many units as CTAs most units lie inside one share: compile their direct-output
     // path in.  The cross-GPU form always goes through the partial slots (one place pushes to the peers).
     const bool many_units = p.world <= 1 && (uint64_t)p.n_layers * p.n_seqs * (p.n_kv_head / KVB) >= grid;
-    auto kern = many_units ? decode_partial_kernel<HD, Q_F32, KVB, true> : decode_partial_kernel<HD, Q_F32, KVB, false>;
+    auto kern = many_units ? decode_partial_kernel<HD, Q_F32, KVB, true, VQ8> : decode_partial_kernel<HD, Q_F32, KVB, false, VQ8>;
+    // binary16 V: one 3-D view over K and V.  q8_0 V: K alone, and the V rows in 32-bit words.
+    const CUtensorMap &tm_a = VQ8 ? (KVB == 2 ? pool->tm_k2 : pool->tm_k) : (KVB == 2 ? pool->tm_kv2 : pool->tm_kv);
+    const CUtensorMap &tm_b = VQ8 ? (KVB == 2 ? pool->tm_v8_2 : pool->tm_v8) : tm_a;
     brc_stage_begin(pool, BRC_STAGE_ATTN_PARTIAL, st);
-    kern<<<grid, NTHREADS, smem, st>>>(KVB == 2 ? pool->tm_kv2 : pool->tm_kv, p);
+    kern<<<grid, Cfg<HD, KVB, VQ8>::NTHREADS, smem, st>>>(tm_a, tm_b, p);
     brc_stage_end(pool, BRC_STAGE_ATTN_PARTIAL, st);
     BRC_CUDA(cudaGetLastError());
     return BRC_OK;
@@ -1142,15 +1278,17 @@ brc_status launch_partial(brc_pool *pool, const DecodeParams &p, uint32_t grid, 
 
 template <int HD, bool Q_F32>
 brc_status launch_partial_kvb(brc_pool *pool, const DecodeParams &p, uint32_t grid, uint32_t smem, cudaStream_t st) {
-    return kvb_of(pool) == 2 ? launch_partial<HD, Q_F32, 2>(pool, p, grid, smem, st)
-                             : launch_partial<HD, Q_F32, 1>(pool, p, grid, smem, st);
+    if (pool->v_q8)
+        return kvb_of(pool) == 2 ? launch_partial<HD, Q_F32, 2, true>(pool, p, grid, smem, st)
+                                 : launch_partial<HD, Q_F32, 1, true>(pool, p, grid, smem, st);
+    return kvb_of(pool) == 2 ? launch_partial<HD, Q_F32, 2, false>(pool, p, grid, smem, st)
+                             : launch_partial<HD, Q_F32, 1, false>(pool, p, grid, smem, st);
 }
 
 brc_status validate_decode(const brc_pool *pool, const char *who, uint32_t layer0, uint32_t n_layers, const void *q,
                            int32_t q_dtype, uint32_t n_head, const uint32_t *bt, uint32_t table_stride, const uint32_t *lens,
                            uint32_t n_seqs, uint32_t max_seq_len, const void *out, const void *ws, uint64_t ws_bytes) {
     if (!pool) return brc_fail(BRC_ERR_INVALID, "%s: pool is NULL", who);
-    BRC_REFUSE_Q8V(pool, who);
     if (pool->device < 0 || !pool->has_tma)
         return brc_fail(BRC_ERR_CUDA, "%s: this pool holds bookkeeping only (no device memory); compute calls need a GPU pool", who);
     if ((uint64_t)layer0 + n_layers > pool->n_layers)
@@ -1220,6 +1358,9 @@ brc_status brc_decode_layers(brc_pool *pool, const char *who, const brc_layers_a
             return brc_fail(BRC_ERR_INVALID, "%s: kv_dtype %d is neither f32 (0) nor f16 (1)", who, a.kv_dtype);
         if (!a.k_new || !a.v_new || (reinterpret_cast<uintptr_t>(a.k_new) & 15u) || (reinterpret_cast<uintptr_t>(a.v_new) & 15u))
             return brc_fail(BRC_ERR_INVALID, "%s: new K/V pointers must be non-NULL and 16-byte aligned", who);
+        if (pool->v_q8 && a.kv_dtype != BRC_DTYPE_F32)
+            return brc_fail(BRC_ERR_UNSUPPORTED, "%s: a q8_0 V pool quantises from f32 sources (as the reference's store rule does), "
+                                                 "never through binary16", who);
     }
     if (a.n_seqs == 0 || a.n_layers == 0) return BRC_OK;
 
@@ -1228,8 +1369,8 @@ brc_status brc_decode_layers(brc_pool *pool, const char *who, const brc_layers_a
     const uint32_t hd = pool->head_dim;
     const uint32_t kvb = kvb_of(pool);
     const uint32_t n_groups = pool->n_kv_head / kvb;
-    const uint32_t n_stages = stages_for(hd, kvb);
-    const uint32_t smem = n_stages * stage_bytes_of(hd, kvb) + fixed_bytes_of(hd);
+    const uint32_t n_stages = stages_for(hd, kvb, pool->v_q8);
+    const uint32_t smem = n_stages * stage_bytes_of(hd, kvb, pool->v_q8) + fixed_bytes_of(hd, pool->v_q8);
     const uint32_t grid = grid_ctas(pool);
     const uint32_t per = seqs_per_launch(pool);
     const size_t q_elem = a.q_dtype == BRC_DTYPE_F32 ? 4 : 2;
@@ -1485,7 +1626,6 @@ brc_status brc_paged_decode_attn_static(brc_pool *pool, uint32_t layer, const vo
                                         const uint32_t *seq_lens_dev, uint32_t n_seqs, uint32_t max_seq_len, float scale,
                                         float *out_dev, void *stream) {
     if (!pool) return brc_fail(BRC_ERR_INVALID, "brc_paged_decode_attn_static: pool is NULL");
-    BRC_REFUSE_Q8V(pool, "brc_paged_decode_attn_static");
     if (pool->device < 0 || !pool->has_tma)
         return brc_fail(BRC_ERR_CUDA, "brc_paged_decode_attn_static: this pool holds bookkeeping only (no device memory)");
     uint64_t need = 0;

@@ -91,12 +91,12 @@ static encode_tiled_fn get_encode_tiled() {
 
 // 2-D view [rows][head_dim] of a whole K or V allocation; box = one page of one kv head's rows by
 // 64 columns (128 bytes, the swizzle span).
-static brc_status make_map(CUtensorMap *tm, void *base, uint64_t rows, uint32_t head_dim, uint32_t page_tokens) {
+static brc_status make_map(CUtensorMap *tm, void *base, uint64_t rows, uint32_t head_dim, uint32_t box_rows) {
     encode_tiled_fn enc = get_encode_tiled();
     if (!enc) return brc_fail(BRC_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[2] = {head_dim, rows};
     cuuint64_t strides[1] = {(cuuint64_t)head_dim * 2u};
-    cuuint32_t box[2] = {64u, page_tokens};
+    cuuint32_t box[2] = {64u, box_rows};
     cuuint32_t estr[2] = {1u, 1u};
     CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, base, dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -104,6 +104,23 @@ static brc_status make_map(CUtensorMap *tm, void *base, uint64_t rows, uint32_t 
     if (r != CUDA_SUCCESS)
         return brc_fail(BRC_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rows %llu, head_dim %u)",
                         (int)r, (unsigned long long)rows, head_dim);
+    return BRC_OK;
+}
+
+// 2-D view [rows][row_words] of a q8_0 V allocation in 32-bit words (a row of head_dim / 32 blocks of 9 words);
+// box = `box_rows` whole rows, no swizzle (the consumers read single words).
+static brc_status make_q8_map(CUtensorMap *tm, void *base, uint64_t rows, uint32_t row_words, uint32_t box_rows) {
+    encode_tiled_fn enc = get_encode_tiled();
+    if (!enc) return brc_fail(BRC_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {row_words, rows};
+    cuuint64_t strides[1] = {(cuuint64_t)row_words * 4u};
+    cuuint32_t box[2] = {row_words, box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return brc_fail(BRC_ERR_CUDA, "cuTensorMapEncodeTiled (q8_0 V view) failed with CUresult %d (rows %llu, %u words per row)",
+                        (int)r, (unsigned long long)rows, row_words);
     return BRC_OK;
 }
 
@@ -191,11 +208,17 @@ static brc_status create_pool(int32_t device, uint32_t n_layers, uint32_t n_kv_h
     // a box of 2 * page_tokens rows brings both (8 KiB per operation instead of 4 KiB).
     if (rc == BRC_OK && !v_q8 && n_kv_head % 2u == 0u)
         rc = make_kv_map(&p->tm_kv2, p->k_base, bytes, rows, head_dim, 2u * page_tokens);
+    if (rc == BRC_OK && v_q8) {
+        const uint32_t row_words = head_dim / 32u * 9u;
+        rc = make_q8_map(&p->tm_v8, p->v_base, rows, row_words, page_tokens);
+        if (rc == BRC_OK && n_kv_head % 2u == 0u) rc = make_map(&p->tm_k2, p->k_base, rows, head_dim, 2u * page_tokens);
+        if (rc == BRC_OK && n_kv_head % 2u == 0u) rc = make_q8_map(&p->tm_v8_2, p->v_base, rows, row_words, 2u * page_tokens);
+    }
     if (rc != BRC_OK) {
         brc_pool_destroy(p);
         return rc;
     }
-    p->has_tma = !v_q8;
+    p->has_tma = true;
     p->refcount.assign(n_pages, 0u);
     p->tree_refs.assign(n_pages, 0u);
     p->free_list.resize(n_pages);

@@ -8,7 +8,10 @@
 // fp32 accumulation; gate optional (sigmoid, applied last).
 //
 // One CTA = one (sequence, kv head, 16 query tokens): a 128-row tile, row = token * 8 + query head of
-// the group (GQA: the 8 query heads of a kv head share every K/V byte the CTA stages).  Per block of
+// the group (GQA: the 8 query heads of a kv head share every K/V byte the CTA stages).  More than 8 query
+// heads per kv head (the reference model has 12, shaders/qsa_attn_scores_gqa.comp:51-133 hard-codes GROUP 12)
+// take `group` rows per token and floor(128 / group) tokens per tile: 10 tokens x 12 heads = 120 of the 128 rows.
+// Per block of
 // 64 cells (4 pages):
 //   S[128 x 64]  = Q[128 x 256] . K^T      tcgen05.mma kind::f16, M=128 N=64, 16 steps of K=16, fp32 in TMEM
 //   P            = 2^(scale' S - m)        4 softmax warps, one thread per row, tcgen05.ld; causal mask
@@ -33,7 +36,6 @@ namespace {
 
 constexpr int PF_HD = 256;
 constexpr int PF_ROWS = 128;              // 16 tokens x 8 head slots
-constexpr int PF_TOK = 16;
 constexpr int PF_BLK = 64;                // cells per block
 constexpr int PF_STAGES = 3;               // depth of the K ring and of the V ring
 constexpr int PF_SOFTMAX_WARPS = 4;       // warps 0-3: TMEM lane quarter = warp id
@@ -66,6 +68,8 @@ struct PrefillParams {
     uint32_t *status;
     uint32_t n_seqs, chunk, table_stride, max_pos_end;
     uint32_t n_kv_head, group, n_head, n_pages, q_f32, gate_head_stride;
+    uint32_t head_slots;           // rows per token in a tile: 8, or the group when it is larger
+    uint32_t tile_tokens;          // tokens per tile: 128 / head_slots
     float scale_log2;
 };
 
@@ -227,14 +231,14 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
     const uint32_t kvh = blockIdx.x % p.n_kv_head;
     const uint32_t tile = blockIdx.x / p.n_kv_head;
     const uint32_t s = blockIdx.y;
-    const uint32_t t0 = tile * PF_TOK;
+    const uint32_t t0 = tile * p.tile_tokens;
     const uint32_t pos0 = p.pos0[s];
     const uint32_t kv_len = pos0 + p.chunk;                    // cells in the cache (all of the chunk is appended)
     if (kv_len > p.max_pos_end) {
         if (tid == 0) { atomicOr(p.status, BRC_DEV_BAD_POS); p.status[1] = kv_len; }
         return;
     }
-    const uint32_t n_tok = min((uint32_t)PF_TOK, p.chunk - t0);
+    const uint32_t n_tok = min(p.tile_tokens, p.chunk - t0);
     const uint32_t cells_needed = pos0 + t0 + n_tok;           // the tile's last row sees cells < this
     const uint32_t n_blk = (cells_needed + PF_BLK - 1) / PF_BLK;
 
@@ -393,7 +397,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
     } else {
         // ------------------------------------------------------------------ softmax warps: thread = row
         const uint32_t row = tid;                       // TMEM lane
-        const uint32_t tl = row >> 3, h = row & 7u;
+        const uint32_t tl = row / p.head_slots, h = row - tl * p.head_slots;
         const uint32_t limit = pos0 + t0 + tl;          // last cell this row sees
         const uint32_t lane_base = (warp * 32u) << 16;  // this warp's TMEM lane quarter
         const bool live_row = tl < n_tok && h < p.group;
@@ -556,8 +560,8 @@ brc_status brc_paged_prefill_attn(brc_pool *pool, uint32_t layer, const void *q_
     if (n_head == 0 || n_head % pool->n_kv_head != 0)
         return brc_fail(BRC_ERR_INVALID, "brc_paged_prefill_attn: %u query heads do not divide over %u kv heads", n_head,
                         pool->n_kv_head);
-    if (n_head / pool->n_kv_head > 8)
-        return brc_fail(BRC_ERR_UNSUPPORTED, "brc_paged_prefill_attn: %u query heads per kv head (a tile holds up to 8)",
+    if (n_head / pool->n_kv_head > 32)
+        return brc_fail(BRC_ERR_UNSUPPORTED, "brc_paged_prefill_attn: %u query heads per kv head (a tile holds up to 32)",
                         n_head / pool->n_kv_head);
     const uint64_t capacity = (uint64_t)table_stride * pool->page_tokens;
     if (max_pos_end > capacity)
@@ -598,7 +602,9 @@ brc_status brc_paged_prefill_attn(brc_pool *pool, uint32_t layer, const void *q_
     p.q_f32 = q_dtype == BRC_DTYPE_F32;
     p.gate_head_stride = gate_head_stride;
     p.scale_log2 = scale * 1.4426950408889634f;
-    const uint32_t tiles = (chunk_len + PF_TOK - 1) / PF_TOK;
+    p.head_slots = std::max<uint32_t>(p.group, 8u);
+    p.tile_tokens = (uint32_t)PF_ROWS / p.head_slots;
+    const uint32_t tiles = (chunk_len + p.tile_tokens - 1) / p.tile_tokens;
     dim3 grid(tiles * pool->n_kv_head, n_seqs);
     brc_stage_begin(pool, BRC_STAGE_PREFILL, brc_stream(stream));
     prefill_attn_kernel<<<grid, PF_THREADS, PF_SMEM, brc_stream(stream)>>>(p);

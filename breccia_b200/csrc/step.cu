@@ -30,7 +30,6 @@ static brc_status decode_step_range(brc_pool *pool, uint32_t layer0, uint32_t n_
                                     float scale, float *out_dev, uint64_t out_layer_stride_bytes, void *workspace_dev,
                                     uint64_t workspace_bytes, void *stream) {
     if (!pool) return brc_fail(BRC_ERR_INVALID, "brc_decode_step: pool is NULL");
-    BRC_REFUSE_Q8V(pool, "brc_decode_step");
     if (pool->device < 0 || !pool->k_base)
         return brc_fail(BRC_ERR_CUDA, "brc_decode_step: this pool holds bookkeeping only (no device memory)");
     if ((uint64_t)layer0 + n_layers > pool->n_layers)
@@ -145,7 +144,6 @@ brc_status brc_decode_step_host(brc_pool *pool, uint32_t layer0, uint32_t n_laye
                                 int32_t kv_dtype, float scale, float *out_host, void *staging_dev, uint64_t staging_bytes,
                                 void *workspace_dev, uint64_t workspace_bytes, void *stream) {
     if (!pool) return brc_fail(BRC_ERR_INVALID, "brc_decode_step_host: pool is NULL");
-    BRC_REFUSE_Q8V(pool, "brc_decode_step_host");
     if (pool->device < 0 || !pool->k_base)
         return brc_fail(BRC_ERR_CUDA, "brc_decode_step_host: this pool holds bookkeeping only (no device memory)");
     if (!q_host || !k_new_host || !v_new_host || !out_host || !staging_dev)

@@ -393,3 +393,261 @@ brc_status brc_tier_stats(brc_tier *tier, uint64_t *out_demoted_pages, uint64_t 
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Cold store: a file of page records behind the host tier (the design note's third tier: NVMe, read
+// and written in whole-page records of 2 * n_layers * half_page_bytes, 384 KiB at 12 layers;
+// docs/reference-engines/02-kv-and-context.md:536-548, milestone item 5 of :617-626).  The reference has
+// no code for it.  A record is byte for byte what a host slot holds, so a page goes
+//     HBM --demote--> host slot --spill--> file record --fetch--> host slot --promote--> HBM
+// and nothing on the way reinterprets it.  Every record carries a caller-chosen 64-bit tag (for a cached
+// prefix: a hash of the tokens up to and including the page); the tag table lives in the file, so a
+// later process can open the file and find a prefix's pages again (a disk-persisted prefix cache).
+// File: a 4 KiB header (magic, geometry, slot count), the tag table, then the records, all on 4 KiB
+// boundaries.  Plain pread / pwrite on the calling thread; both calls are synchronous.
+// ---------------------------------------------------------------------------------------------
+#include <fcntl.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <cerrno>
+#include <cstring>
+#include <string>
+
+namespace {
+
+constexpr char COLD_MAGIC[8] = {'B', 'R', 'C', 'C', 'O', 'L', 'D', '1'};
+constexpr uint64_t COLD_ALIGN = 4096;
+
+struct ColdHeader {
+    char magic[8];
+    uint32_t n_layers, n_kv_head, head_dim, page_tokens;
+    uint64_t slot_bytes;
+    uint32_t n_slots, reserved;
+};
+
+struct ColdEntry {
+    uint64_t tag;
+    uint32_t used, reserved;
+};
+
+uint64_t round_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
+
+bool write_all(int fd, const void *buf, size_t n, uint64_t off) {
+    const uint8_t *p = static_cast<const uint8_t *>(buf);
+    while (n) {
+        const ssize_t w = pwrite(fd, p, n, (off_t)off);
+        if (w < 0 && errno == EINTR) continue;
+        if (w <= 0) return false;
+        p += w, n -= (size_t)w, off += (uint64_t)w;
+    }
+    return true;
+}
+
+bool read_all(int fd, void *buf, size_t n, uint64_t off) {
+    uint8_t *p = static_cast<uint8_t *>(buf);
+    while (n) {
+        const ssize_t r = pread(fd, p, n, (off_t)off);
+        if (r < 0 && errno == EINTR) continue;
+        if (r <= 0) return false;
+        p += r, n -= (size_t)r, off += (uint64_t)r;
+    }
+    return true;
+}
+
+}  // namespace
+
+struct brc_cold {
+    brc_tier *tier = nullptr;
+    int fd = -1;
+    std::string path;
+    uint32_t n_slots = 0;
+    uint64_t table_off = 0, data_off = 0;
+    std::vector<ColdEntry> table;
+    uint32_t used = 0;
+    uint64_t bytes_written = 0, bytes_read = 0;
+    std::mutex mu;
+};
+
+static brc_status cold_flush_table(brc_cold *c) {
+    if (!write_all(c->fd, c->table.data(), c->table.size() * sizeof(ColdEntry), c->table_off))
+        return brc_fail(BRC_ERR_INVALID, "cold store %s: writing the tag table failed: %s", c->path.c_str(), std::strerror(errno));
+    return BRC_OK;
+}
+
+extern "C" {
+
+brc_status brc_cold_open(brc_tier *tier, const char *path, uint32_t n_slots, int32_t create, brc_cold **out) {
+    if (!tier || !path || !out) return brc_fail(BRC_ERR_INVALID, "brc_cold_open: NULL argument");
+    *out = nullptr;
+    const brc_pool *p = tier->pool;
+    ColdHeader want = {};
+    std::memcpy(want.magic, COLD_MAGIC, 8);
+    want.n_layers = p->n_layers;
+    want.n_kv_head = p->n_kv_head;
+    want.head_dim = p->head_dim;
+    want.page_tokens = p->page_tokens;
+    want.slot_bytes = tier->slot_bytes;
+    brc_cold *c = new (std::nothrow) brc_cold();
+    if (!c) return brc_fail(BRC_ERR_INVALID, "brc_cold_open: out of host memory");
+    c->tier = tier;
+    c->path = path;
+    if (create) {
+        if (n_slots == 0) {
+            delete c;
+            return brc_fail(BRC_ERR_INVALID, "brc_cold_open: a new store needs n_slots > 0");
+        }
+        c->fd = open(path, O_RDWR | O_CREAT | O_TRUNC, 0644);
+        want.n_slots = n_slots;
+    } else {
+        c->fd = open(path, O_RDWR);
+    }
+    if (c->fd < 0) {
+        brc_status rc = brc_fail(BRC_ERR_INVALID, "brc_cold_open: cannot open %s: %s", path, std::strerror(errno));
+        delete c;
+        return rc;
+    }
+    ColdHeader h = want;
+    if (!create) {
+        if (!read_all(c->fd, &h, sizeof h, 0) || std::memcmp(h.magic, COLD_MAGIC, 8) != 0) {
+            close(c->fd);
+            delete c;
+            return brc_fail(BRC_ERR_INVALID, "brc_cold_open: %s is not a page store of this library", path);
+        }
+        if (h.n_layers != want.n_layers || h.n_kv_head != want.n_kv_head || h.head_dim != want.head_dim ||
+            h.page_tokens != want.page_tokens || h.slot_bytes != want.slot_bytes || h.n_slots == 0) {
+            close(c->fd);
+            delete c;
+            return brc_fail(BRC_ERR_INVALID,
+                            "brc_cold_open: %s holds pages of %u layers x %u kv heads x %u x %u cells (%llu bytes each); the pool's are "
+                            "%u x %u x %u x %u (%llu bytes)",
+                            path, h.n_layers, h.n_kv_head, h.head_dim, h.page_tokens, (unsigned long long)h.slot_bytes, want.n_layers,
+                            want.n_kv_head, want.head_dim, want.page_tokens, (unsigned long long)want.slot_bytes);
+        }
+    }
+    c->n_slots = h.n_slots;
+    c->table_off = COLD_ALIGN;
+    c->data_off = c->table_off + round_up((uint64_t)c->n_slots * sizeof(ColdEntry), COLD_ALIGN);
+    c->table.assign(c->n_slots, ColdEntry{0, 0, 0});
+    bool ok = true;
+    if (create) {
+        ok = write_all(c->fd, &h, sizeof h, 0) && cold_flush_table(c) == BRC_OK &&
+             ftruncate(c->fd, (off_t)(c->data_off + (uint64_t)c->n_slots * tier->slot_bytes)) == 0;
+    } else {
+        ok = read_all(c->fd, c->table.data(), c->table.size() * sizeof(ColdEntry), c->table_off);
+        for (const ColdEntry &e : c->table) c->used += e.used ? 1u : 0u;
+    }
+    if (!ok) {
+        brc_status rc = brc_fail(BRC_ERR_INVALID, "brc_cold_open: %s: %s", path, std::strerror(errno));
+        close(c->fd);
+        delete c;
+        return rc;
+    }
+    *out = c;
+    return BRC_OK;
+}
+
+brc_status brc_cold_close(brc_cold *c) {
+    if (!c) return BRC_OK;
+    brc_status rc = BRC_OK;
+    {
+        std::lock_guard<std::mutex> lock(c->mu);
+        rc = cold_flush_table(c);
+        if (fsync(c->fd) != 0 && rc == BRC_OK) rc = brc_fail(BRC_ERR_INVALID, "brc_cold_close: fsync of %s: %s", c->path.c_str(), std::strerror(errno));
+        close(c->fd);
+    }
+    delete c;
+    return rc;
+}
+
+brc_status brc_cold_spill(brc_cold *c, const uint32_t *host_slots, const uint64_t *tags, uint32_t n, uint32_t *out_cold_slots) {
+    if (!c || (!host_slots && n) || (!out_cold_slots && n)) return brc_fail(BRC_ERR_INVALID, "brc_cold_spill: NULL argument");
+    if (n == 0) return BRC_OK;
+    brc_tier *t = c->tier;
+    brc_device_guard guard(t->pool->device);
+    std::lock_guard<std::mutex> lock(c->mu);
+    std::lock_guard<std::mutex> tier_lock(t->mu);
+    if (c->n_slots - c->used < n)
+        return brc_fail(BRC_ERR_CAPACITY, "brc_cold_spill: %u pages but %u of %u records are free", n, c->n_slots - c->used, c->n_slots);
+    uint64_t dep = 0;
+    for (uint32_t i = 0; i < n; ++i) {
+        if (host_slots[i] >= t->host_pages || t->slot_used[host_slots[i]] != 1)
+            return brc_fail(BRC_ERR_NOT_RESIDENT, "brc_cold_spill: host slot %u holds no page", host_slots[i]);
+        for (uint32_t j = 0; j < i; ++j)
+            if (host_slots[j] == host_slots[i]) return brc_fail(BRC_ERR_INVALID, "brc_cold_spill: host slot %u is named twice", host_slots[i]);
+        dep = std::max(dep, t->slot_written_by[host_slots[i]]);
+    }
+    // the demotion that filled these slots must have landed in host memory before the file reads it
+    if (dep && dep + EVENT_RING > t->out_batch) BRC_CUDA(cudaEventSynchronize(t->out_done[dep % EVENT_RING]));
+    uint32_t at = 0;
+    for (uint32_t i = 0; i < n; ++i) {
+        while (c->table[at].used) ++at;
+        if (!write_all(c->fd, t->host + (uint64_t)host_slots[i] * t->slot_bytes, t->slot_bytes, c->data_off + (uint64_t)at * t->slot_bytes))
+            return brc_fail(BRC_ERR_INVALID, "brc_cold_spill: write to %s failed: %s", c->path.c_str(), std::strerror(errno));
+        c->table[at].tag = tags ? tags[i] : 0;
+        c->table[at].used = 1;
+        ++c->used;
+        c->bytes_written += t->slot_bytes;
+        out_cold_slots[i] = at;
+        t->slot_used[host_slots[i]] = 0;
+        t->slot_written_by[host_slots[i]] = 0;
+        ++t->free_slot_count;
+    }
+    return cold_flush_table(c);
+}
+
+brc_status brc_cold_fetch(brc_cold *c, const uint32_t *cold_slots, uint32_t n, int32_t keep, uint32_t *out_host_slots) {
+    if (!c || (!cold_slots && n) || (!out_host_slots && n)) return brc_fail(BRC_ERR_INVALID, "brc_cold_fetch: NULL argument");
+    if (n == 0) return BRC_OK;
+    brc_tier *t = c->tier;
+    brc_device_guard guard(t->pool->device);
+    std::lock_guard<std::mutex> lock(c->mu);
+    std::lock_guard<std::mutex> tier_lock(t->mu);
+    if (t->free_slot_count < n)
+        return brc_fail(BRC_ERR_CAPACITY, "brc_cold_fetch: %u pages but %u of %u host slots are free", n, t->free_slot_count, t->host_pages);
+    for (uint32_t i = 0; i < n; ++i)
+        if (cold_slots[i] >= c->n_slots || !c->table[cold_slots[i]].used)
+            return brc_fail(BRC_ERR_NOT_RESIDENT, "brc_cold_fetch: record %u of %s holds no page", cold_slots[i], c->path.c_str());
+    uint32_t hs = 0;
+    for (uint32_t i = 0; i < n; ++i) {
+        while (t->slot_used[hs]) ++hs;
+        // a promotion that emptied this slot may still be reading it
+        const uint64_t dep = t->slot_read_by[hs];
+        if (dep && dep + EVENT_RING > t->in_batch) BRC_CUDA(cudaEventSynchronize(t->in_done[dep % EVENT_RING]));
+        if (!read_all(c->fd, t->host + (uint64_t)hs * t->slot_bytes, t->slot_bytes, c->data_off + (uint64_t)cold_slots[i] * t->slot_bytes))
+            return brc_fail(BRC_ERR_INVALID, "brc_cold_fetch: read of %s failed: %s", c->path.c_str(), std::strerror(errno));
+        c->bytes_read += t->slot_bytes;
+        t->slot_used[hs] = 1;
+        t->slot_written_by[hs] = 0;   // filled by the host, nothing on the device to wait for
+        --t->free_slot_count;
+        out_host_slots[i] = hs;
+        if (!keep) {
+            c->table[cold_slots[i]].used = 0;
+            --c->used;
+        }
+    }
+    return keep ? BRC_OK : cold_flush_table(c);
+}
+
+brc_status brc_cold_find(brc_cold *c, uint64_t tag, uint32_t *out_cold_slot) {
+    if (!c || !out_cold_slot) return brc_fail(BRC_ERR_INVALID, "brc_cold_find: NULL argument");
+    std::lock_guard<std::mutex> lock(c->mu);
+    for (uint32_t i = 0; i < c->n_slots; ++i)
+        if (c->table[i].used && c->table[i].tag == tag) {
+            *out_cold_slot = i;
+            return BRC_OK;
+        }
+    return brc_fail(BRC_ERR_NOT_RESIDENT, "brc_cold_find: no record tagged %016llx in %s", (unsigned long long)tag, c->path.c_str());
+}
+
+brc_status brc_cold_stats(brc_cold *c, uint32_t *out_used, uint32_t *out_total, uint64_t *out_bytes_written, uint64_t *out_bytes_read) {
+    if (!c) return brc_fail(BRC_ERR_INVALID, "brc_cold_stats: NULL handle");
+    std::lock_guard<std::mutex> lock(c->mu);
+    if (out_used) *out_used = c->used;
+    if (out_total) *out_total = c->n_slots;
+    if (out_bytes_written) *out_bytes_written = c->bytes_written;
+    if (out_bytes_read) *out_bytes_read = c->bytes_read;
+    return BRC_OK;
+}
+
+}  // extern "C"

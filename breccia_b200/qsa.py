@@ -409,6 +409,43 @@ def topk_blocks(pool: KvPool, scores: torch.Tensor, pos0: torch.Tensor, rows_per
     return ids, counts
 
 
+IDX_DIM, IDX_BLOCK, IDX_N_HEAD = 128, 4, 4   # crates/breccia-kernels/src/qsa/mod.rs:77-81
+
+
+class IndexerState:
+    """The indexer's key cache of a batch of sequences (reference: `QsaState::idx_pooled` / `idx_tail`, one per
+    sequence, qsa/mod.rs:294-311, 353-386): one pooled key per completed 4-cell block and the raw keys of the
+    block being filled."""
+
+    def __init__(self, pool: KvPool, n_seqs: int, capacity_cells: int):
+        dev = f"cuda:{pool.device}"
+        self.pool, self.n_seqs = pool, n_seqs
+        self.max_blocks = capacity_cells // IDX_BLOCK + 1          # sizes::max_blocks, qsa/mod.rs:384-387
+        self.pooled = torch.zeros((n_seqs, self.max_blocks, IDX_DIM), dtype=torch.float32, device=dev)
+        self.tail = torch.zeros((n_seqs, IDX_BLOCK - 1, IDX_DIM), dtype=torch.float32, device=dev)
+
+    def append(self, raw: torch.Tensor, pos0: torch.Tensor, max_pos_end: int, gamma: torch.Tensor, rope_table: torch.Tensor,
+               n_rot: int, eps: float = 1e-6) -> None:
+        """raw [n_seqs, tokens, 128] f32: this call's raw indexer keys at positions pos0[s] ..: pools every block
+        the call completes, then stores the new incomplete block's keys in the tail (Qsa::idx_pool then
+        Qsa::idx_tail, the order of Qsa::forward)."""
+        n_seqs, tokens = raw.shape[0], raw.shape[1]
+        _lib.call("brc_idx_pool", self.pool.handle, _ptr(raw), _ptr(self.tail), _ptr(gamma), _ptr(rope_table), n_rot,
+                  rope_table.shape[0], eps, _ptr(pos0), n_seqs, tokens, max_pos_end, IDX_DIM, IDX_BLOCK, _ptr(self.pooled),
+                  self.max_blocks, _stream_ptr())
+        _lib.call("brc_idx_tail", self.pool.handle, _ptr(raw), _ptr(pos0), n_seqs, tokens, IDX_DIM, IDX_BLOCK, _ptr(self.tail),
+                  _stream_ptr())
+
+    def score(self, q: torch.Tensor, pos0: torch.Tensor, rows_per_seq: int, n_blocks: int) -> torch.Tensor:
+        """q [rows, idx_n_head, 128] f32 -> scores [rows, n_blocks] f32 (Qsa::idx_score), ready for topk_blocks."""
+        rows = q.shape[0]
+        scores = torch.empty((rows, n_blocks), dtype=torch.float32, device=q.device)
+        _lib.call("brc_idx_score", self.pool.handle, _ptr(q), q.shape[1], _ptr(self.pooled), self.max_blocks, _ptr(pos0),
+                  rows // rows_per_seq, rows_per_seq, n_blocks, IDX_DIM, IDX_BLOCK, 1.0 / math.sqrt(IDX_DIM), _ptr(scores),
+                  _stream_ptr())
+        return scores
+
+
 def decode_partial_bytes(n_seqs: int, n_head: int, head_dim: int) -> int:
     out = C.c_uint64()
     _lib.call("brc_decode_partial_bytes", n_seqs, n_head, head_dim, C.byref(out))

@@ -61,6 +61,7 @@ typedef int32_t brc_status;
 typedef struct brc_pool brc_pool;
 typedef struct brc_radix brc_radix;
 typedef struct brc_tier brc_tier;
+typedef struct brc_cold brc_cold;
 typedef struct brc_comm brc_comm;
 
 typedef struct brc_geometry {
@@ -90,11 +91,18 @@ BRC_API brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n
  * head_dim / 32 blocks of one f32 scale followed by 32 signed bytes (36 B for 32
  * values against 64 B: 0.5625x the V bytes), rows in the order of the binary16
  * layout; K stays binary16.  Built for such a pool: brc_kv_append from f32 sources
- * (store rule of shaders/qsa_kv_append.comp:117-133), brc_paged_sparse_attn
- * (in-register dequantisation, qsa_attn_apply.comp:69-77), brc_page_copy and
- * brc_seq_fork (whole pages, bytes as they are), brc_pool_read / brc_pool_write /
- * brc_pool_v_ptr, the allocator and the prefix tree.  Every other
- * entry point that reads or writes V refuses it with BRC_ERR_UNSUPPORTED. */
+ * (store rule of shaders/qsa_kv_append.comp:117-133); the dense decode entry
+ * points brc_paged_decode_attn(_static), brc_decode_partial, brc_decode_step(_part,
+ * _host) with f32 new K/V (the fused append quantises by the same rule) and
+ * brc_splitkv_attend / _step - the quanta reach the tensor cores as exact
+ * integers and the block scales ride on the probabilities (read rule
+ * qsa_attn_apply.comp:60-77), 1600 instead of 2048 bytes per cached cell at
+ * 2 kv heads of 256; brc_paged_sparse_attn (in-register dequantisation);
+ * brc_page_copy and brc_seq_fork (whole pages, bytes as they are); brc_pool_read
+ * / brc_pool_write / brc_pool_v_ptr, the allocator and the prefix tree.  The
+ * entry points that read V as binary16 tiles or rows (chunked prefill, page
+ * gather, tiering, page files, brc_qk_prepare_append) refuse it with
+ * BRC_ERR_UNSUPPORTED. */
 #define BRC_V_F16 0
 #define BRC_V_Q8_0 1
 BRC_API brc_status brc_pool_create_q8v(int32_t device, uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim,
@@ -327,7 +335,7 @@ BRC_API brc_status brc_splitkv_attend(brc_comm *comm, uint32_t layer, const void
  * mod.rs:620-625, 1382-1580; qsa_attn_scores.comp:8-19, 62-118;
  * qsa_attn_apply.comp:85-140; CPU statement: cpu::attend over cpu::cells_of,
  * qsa/cpu.rs:197-257).  The lists are taken as the reference's top-k stage
- * produces them; building them (indexer, top-k) is outside this library.
+ * produces them (here: brc_idx_score + brc_topk_blocks).
  * Rows are grouped by sequence: row r belongs to sequence r / rows_per_seq and
  * sits at position pos0[sequence] + r % rows_per_seq (T = 1 decode:
  * rows_per_seq = 1; speculative verify or prefill rows: > 1, causal per row).
@@ -479,6 +487,40 @@ BRC_API brc_status brc_decode_step_host(brc_pool *pool, uint32_t layer0, uint32_
                                         uint64_t staging_bytes, void *workspace_dev, uint64_t workspace_bytes,
                                         void *stream);
 
+/* ---------------------------------------------------------------- indexer: pooled-key cache and block scores
+ * Replaces shaders/qsa_idx_pool.comp, qsa_idx_tail.comp and qsa_idx_score.comp, driven as Qsa::idx_pool /
+ * idx_tail / idx_score (crates/breccia-kernels/src/qsa/mod.rs:1168-1262) in the order of Qsa::forward
+ * (:1618-1630): pool, then tail, then score, then brc_topk_blocks.  CPU statements: cpu::pool_keys and
+ * cpu::indexer_score (qsa/cpu.rs:97-121, 159-195).  The reference holds one indexer state per sequence;
+ * here the state arrays have a leading sequence dimension (caller-owned device memory, f32):
+ *   pooled [n_seqs][max_blocks][idx_dim]   one pooled key per COMPLETED 4-cell block
+ *   tail   [n_seqs][idx_block - 1][idx_dim]  raw keys of the block being filled
+ * and one call serves a batch whose sequences each bring `tokens_per_seq` raw keys
+ * raw [n_seqs][tokens_per_seq][idx_dim] at positions pos0[s] .. .
+ *   pool : for every block this call completes, pooled[s][b] = rope(rmsnorm(mean(raw keys of cells
+ *          4b..4b+3), gamma, eps), position 4b): mean over the RAW keys, NEOX pairs (j, j + n_rot/2) from
+ *          the caller's (cos, sin) table [max_pos][n_rot/2][2], rotated at the block's first cell.  Cells
+ *          before pos0 come from `tail` (call it BEFORE brc_idx_tail, as the reference does).  Refuses,
+ *          with the reference's wording, a call whose blocks would not fit max_blocks (`max_pos_end` is
+ *          the caller's bound on pos0[s] + tokens_per_seq, checked on the device too).
+ *   tail : stores the raw keys of the call's last, incomplete block (slot = cell % 4 < 3).
+ *   score: scores[row][b] = scale * sum_h relu(q[row][h] . pooled[s][b]) for b < n_blocks, row = s *
+ *          rows_per_seq + t at position pos0[s] + t; a block whose LAST cell lies beyond the row's
+ *          position gets -1e30, which brc_topk_blocks never selects (the shader's rule; the CPU
+ *          statement masks on the first cell, the two agree on every block a row fully sees).
+ *          q [rows][idx_n_head][idx_dim], idx_n_head <= 8, scale = 1/sqrt(idx_dim) in the reference.
+ * Built for idx_dim 128 and idx_block 4 (the reference's constants). */
+BRC_API brc_status brc_idx_pool(brc_pool *pool, const float *raw_dev, const float *tail_dev, const float *gamma_dev,
+                                const float *rope_table_dev, uint32_t n_rot, uint32_t max_pos, float eps,
+                                const uint32_t *pos0_dev, uint32_t n_seqs, uint32_t tokens_per_seq, uint32_t max_pos_end,
+                                uint32_t idx_dim, uint32_t idx_block, float *pooled_dev, uint32_t max_blocks, void *stream);
+BRC_API brc_status brc_idx_tail(brc_pool *pool, const float *raw_dev, const uint32_t *pos0_dev, uint32_t n_seqs,
+                                uint32_t tokens_per_seq, uint32_t idx_dim, uint32_t idx_block, float *tail_dev, void *stream);
+BRC_API brc_status brc_idx_score(brc_pool *pool, const float *q_dev, uint32_t idx_n_head, const float *pooled_dev,
+                                 uint32_t max_blocks, const uint32_t *pos0_dev, uint32_t n_seqs, uint32_t rows_per_seq,
+                                 uint32_t n_blocks, uint32_t idx_dim, uint32_t idx_block, float scale,
+                                 float *scores_out_dev, void *stream);
+
 /* ---------------------------------------------------------------- top-k block selection
  * Replaces shaders/qsa_topk.comp (CPU statement cpu::topk_blocks, qsa/cpu.rs:129-151): turns a row's
  * indexer scores into the `ids` / `counts` lists brc_paged_sparse_attn walks.  Per row (row = sequence *
@@ -506,7 +548,8 @@ BRC_API brc_status brc_topk_blocks(brc_pool *pool, const float *scores_dev, uint
  *            tensor cores); out_dev same shape, f32; gate as in brc_paged_decode_attn with
  *            rows (s, t, h).
  *   max_pos_end  caller's bound on pos0[s] + chunk_len; refused if > table_stride*page_tokens.
- * head_dim 256 and up to 8 query heads per kv head.  tcgen05.mma with accumulators in
+ * head_dim 256; up to 8 query heads per kv head share a tile of 16 tokens, more (up to 32; the
+ * reference model has 12) take floor(128 / heads) tokens per tile.  tcgen05.mma with accumulators in
  * TMEM; K/V pages gathered through the block table. */
 BRC_API brc_status brc_paged_prefill_attn(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype,
                                           uint32_t n_head, const float *gate_dev, uint32_t gate_head_stride,
@@ -570,6 +613,30 @@ BRC_API brc_status brc_tier_touch(brc_tier *tier, const uint32_t *page_ids, uint
 BRC_API brc_status brc_tier_lru(brc_tier *tier, uint32_t n, uint32_t *out_page_ids, uint32_t *out_n);
 BRC_API brc_status brc_tier_stats(brc_tier *tier, uint64_t *out_demoted_pages, uint64_t *out_promoted_pages,
                                   uint64_t *out_d2h_bytes, uint64_t *out_h2d_bytes, uint32_t *out_free_slots);
+
+/* ---------------------------------------------------------------- cold store behind the host tier
+ * A file of page records (NVMe in the design note: the third tier, and the disk-persisted prefix cache;
+ * docs/reference-engines/02-kv-and-context.md:536-548, item 5 of :617-626; no code in the reference).  A
+ * record is byte for byte a host slot of the tier (a page of every layer, K then V), so a page travels
+ *     HBM --brc_tier_demote--> host slot --spill--> record --fetch--> host slot --brc_tier_promote--> HBM
+ * unchanged.  Each record carries a caller-chosen 64-bit tag (for a cached prefix: a hash of the tokens up
+ * to and including the page); tags are stored in the file, so another process can open it later and find
+ * the pages again.
+ *   open  : create != 0 makes (or truncates) `path` with n_slots records; create == 0 opens an existing
+ *           store, refusing one written for another page geometry (n_slots ignored).
+ *   spill : host slots -> free records (waits for the demotion that filled the slots), host slots freed.
+ *   fetch : records -> free host slots, ready for brc_tier_promote; keep == 0 frees the records.
+ *   find  : the record with this tag, or BRC_ERR_NOT_RESIDENT.
+ * Synchronous file I/O on the calling thread. */
+BRC_API brc_status brc_cold_open(brc_tier *tier, const char *path, uint32_t n_slots, int32_t create, brc_cold **out);
+BRC_API brc_status brc_cold_close(brc_cold *cold);
+BRC_API brc_status brc_cold_spill(brc_cold *cold, const uint32_t *host_slots, const uint64_t *tags, uint32_t n,
+                                  uint32_t *out_cold_slots);
+BRC_API brc_status brc_cold_fetch(brc_cold *cold, const uint32_t *cold_slots, uint32_t n, int32_t keep,
+                                  uint32_t *out_host_slots);
+BRC_API brc_status brc_cold_find(brc_cold *cold, uint64_t tag, uint32_t *out_cold_slot);
+BRC_API brc_status brc_cold_stats(brc_cold *cold, uint32_t *out_used, uint32_t *out_total, uint64_t *out_bytes_written,
+                                  uint64_t *out_bytes_read);
 
 /* ---------------------------------------------------------------- per-stage GPU timers
  * Counterpart of the reference's BRECCIA_GPU_TIME probe and its stage ids

@@ -48,6 +48,16 @@ def check(got, want, what):
     (16, 2, [1000], 256),             # a config-4 sized chunk after a long prefix
     (8, 2, [130, 5], 33),             # 4 query heads per kv head (half-empty tiles)
     (8, 1, [20], 17),
+    # fewer rows than one 16-token tile: the reference's small path below 16 rows, causal per row
+    # (speculative verify, shaders/qsa_attn_scores_small.comp:74-77)
+    (16, 2, [100, 0], 2),
+    (16, 2, [37], 3),
+    (8, 2, [64, 1000], 15),
+    # the reference model's own geometry: 12 query heads per kv head (shaders/qsa_attn_scores_gqa.comp:51-133), tiles of
+    # 10 tokens x 12 heads; and 16 per kv head (8 tokens x 16)
+    (24, 2, [70, 0], 40),
+    (24, 2, [2048], 64),
+    (16, 1, [33], 20),
 ])
 def test_prefill_matches_oracle(cuda_device, n_head, n_kv, pos0s, chunk):
     hd = 256
@@ -111,7 +121,7 @@ def test_prefill_refusals(cuda_device):
                          C.c_void_p(out.data_ptr()), None]
     assert L.brc_paged_prefill_attn(*args(end=65)) == _lib.ERR_CAPACITY
     assert L.brc_paged_prefill_attn(*args(layer=2)) == _lib.ERR_INVALID
-    assert L.brc_paged_prefill_attn(*args(nh=24)) == _lib.ERR_UNSUPPORTED
+    assert L.brc_paged_prefill_attn(*args(nh=80)) == _lib.ERR_UNSUPPORTED     # 40 query heads per kv head: a tile holds up to 32
     assert L.brc_paged_prefill_attn(*args(dt=7)) == _lib.ERR_INVALID
     p128 = KvPool(0, 1, 2, 128, 8)
     a = args()

@@ -93,9 +93,8 @@ def test_entry_points_built_for_binary16_v_refuse_a_q8_0_pool(cuda_device):
     pool = KvPool(0, 1, 2, 256, 8, v_q8=True)
     x = torch.zeros(4096, device="cuda")
     t = dev_u32(np.zeros((1, 2)))
-    with pytest.raises(_lib.BrcError) as err:
-        _lib.call("brc_paged_decode_attn", pool.handle, 0, P(x), DTYPE_F32, 16, None, 0, P(t), 2, P(t), 1, 16, 0.0625, P(x),
-                  P(x), x.numel() * 4, None)
+    with pytest.raises(_lib.BrcError) as err:      # the tensor-core prefill path reads V as binary16 tiles
+        _lib.call("brc_paged_prefill_attn", pool.handle, 0, P(x), DTYPE_F32, 16, None, 0, P(t), 2, P(t), 1, 16, 16, 0.0625, P(x), None)
     assert err.value.code == _lib.ERR_UNSUPPORTED and "q8_0" in err.value.message
     with pytest.raises(_lib.BrcError) as err:
         _lib.call("brc_page_gather", pool.handle, 0, P(t), 2, 16, P(x), P(x), None)

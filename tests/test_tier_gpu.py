@@ -210,3 +210,65 @@ def test_pages_held_by_a_radix_tree_stay_in_hbm_and_a_bad_batch_queues_nothing(c
     L.brc_tier_destroy(tier)
     L.brc_radix_destroy(radix)
     pool.release()
+
+
+def test_pages_spilled_to_a_file_come_back_bit_exact_in_another_store_handle(cuda_device, tmp_path):
+    """HBM -> host slot -> file record, the store closed and opened again (as another process would), the records
+    found by their tags, -> host slot -> HBM: every byte of every layer as it was.  A store written for another
+    page geometry is refused."""
+    n_layers, n_pages = 2, 30
+    pool = KvPool(0, n_layers, 2, 256, n_pages)
+    L = _lib.load()
+    mine, mp = arr(np.zeros(12))
+    assert L.brc_pages_alloc(pool.handle, 12, mp) == 0
+    before = []
+    for layer in range(n_layers):
+        fill_pool_from_host(pool, layer, 950 + 2 * layer)
+        before.append((pool.read(0, layer).copy(), pool.read(1, layer).copy()))
+    tier, cold = C.c_void_p(), C.c_void_p()
+    assert L.brc_tier_create(pool.handle, 8, C.byref(tier)) == 0
+    path = str(tmp_path / "prefix.brccold").encode()
+    assert L.brc_cold_open(tier, path, 16, 1, C.byref(cold)) == 0
+    vict, vp = arr(mine[2:10])
+    slots, sp = arr(np.zeros(8))
+    assert L.brc_tier_demote(tier, vp, 8, sp, None) == 0
+    tags = np.ascontiguousarray([0xABCD0000 + int(p) * 7919 for p in vict], np.uint64)
+    recs, rp = arr(np.zeros(8))
+    assert L.brc_cold_spill(cold, sp, tags.ctypes.data_as(C.POINTER(C.c_uint64)), 8, rp) == 0
+    st = [C.c_uint64() for _ in range(4)]
+    fs = C.c_uint32()
+    assert L.brc_tier_stats(tier, *(C.byref(x) for x in st), C.byref(fs)) == 0 and fs.value == 8      # the host slots are free again
+    used, total = C.c_uint32(), C.c_uint32()
+    assert L.brc_cold_stats(cold, C.byref(used), C.byref(total), None, None) == 0 and (used.value, total.value) == (8, 16)
+    assert L.brc_cold_spill(cold, sp, None, 1, rp) == _lib.ERR_NOT_RESIDENT                             # that slot holds nothing now
+    assert L.brc_cold_close(cold) == 0
+    pool.poison_nan()                                                                                   # HBM forgets everything
+    # ---- later: open the same file, find the pages by tag, bring them back
+    assert L.brc_cold_open(tier, path, 0, 0, C.byref(cold)) == 0
+    found = np.zeros(8, np.uint32)
+    one = C.c_uint32()
+    for i, tag in enumerate(tags):
+        assert L.brc_cold_find(cold, int(tag), C.byref(one)) == 0
+        found[i] = one.value
+    assert L.brc_cold_find(cold, 12345, C.byref(one)) == _lib.ERR_NOT_RESIDENT
+    f, fp = arr(found)
+    hs, hp = arr(np.zeros(8))
+    assert L.brc_cold_fetch(cold, fp, 8, 1, hp) == 0
+    back, bp = arr(np.zeros(8))
+    assert L.brc_tier_promote(tier, hp, 8, bp) == 0
+    assert L.brc_tier_fence(tier, None) == 0
+    torch.cuda.synchronize()
+    for layer in range(n_layers):
+        k, v = pool.read(0, layer), pool.read(1, layer)
+        for old, new in zip(vict, back):
+            assert np.array_equal(k[new], before[layer][0][old]) and np.array_equal(v[new], before[layer][1][old]), f"layer {layer} page {old}->{new}"
+    assert L.brc_cold_close(cold) == 0
+    # ---- a pool of another geometry must not read these records as its own
+    other = KvPool(0, 3, 2, 256, 8)
+    tier2 = C.c_void_p()
+    assert L.brc_tier_create(other.handle, 2, C.byref(tier2)) == 0
+    assert L.brc_cold_open(tier2, path, 0, 0, C.byref(cold)) == _lib.ERR_INVALID and b"layers" in L.brc_last_error()
+    L.brc_tier_destroy(tier2)
+    other.release()
+    L.brc_tier_destroy(tier)
+    pool.release()

@@ -14,6 +14,7 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
 from breccia_b200 import _lib, synth
 from breccia_b200._lib import DTYPE_F16
 from breccia_b200.qsa import DecodeBatch, KvPool
@@ -35,15 +36,25 @@ def test_static_scratch_entry_point_equals_the_workspace_one_twice_in_a_row(cuda
         lens = np.asarray(lens)
         tables, n_pool = synth.scattered_tables(seed, lens, pool_factor=1.3)
         pool = KvPool(0, 2, n_kv, hd, n_pool)
-        fill_pool_from_host(pool, 1, seed + 10)
+        k_host, v_host = fill_pool_from_host(pool, 1, seed + 10)
         batch = DecodeBatch(pool, n_head, tables, lens)
-        q = torch.from_numpy(synth.normal(seed + 20, lens.size * n_head * hd)).cuda().half().view(lens.size, n_head, hd)
+        q32 = oracle.to_f16(synth.normal(seed + 20, lens.size * n_head * hd)).reshape(lens.size, n_head, hd)
+        q = torch.from_numpy(q32).cuda().half()
         want = torch.full((lens.size, n_head, hd), float("nan"), device="cuda")
         got = torch.full_like(want, float("nan"))
         batch.attend(1, q, want)                      # existing entry point, caller-owned workspace
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         _static_call(pool, batch, 1, q, got, n_head)  # new entry point, built-in scratch
+        torch.cuda.synchronize()
+        free_after = torch.cuda.mem_get_info()[0]
+        # the property in the entry point's name: the call (the very first one on this device included, which looks
+        # the array's address up) takes no device memory
+        assert free_after >= free_before, f"call {call}: {free_before - free_after} bytes of device memory went away"
         pool.check()
         w, g = want.cpu().numpy(), got.cpu().numpy()
+        ref, _ = oracle.decode_batch(k_host, v_host, tables, lens, q32, n_head, n_kv, hd)
+        assert np.abs(g - ref).max() <= 2e-3          # and against the CPU oracle directly
         assert np.isfinite(g).all()
         # same kernels, same schedule, same arithmetic: the tolerance of the attention tests is the
         # bar, and in fact the two agree to the last bit
