@@ -15,6 +15,8 @@
 // On a pool whose V pages are q8_0 (blocks of one f32 scale + 32 signed bytes) a lane reads the scale word of its
 // block and the one or two words that hold its own quanta and multiplies in registers (qsa_attn_apply.comp:69-77):
 // 36 bytes cross the memory system per 32 values instead of 64.
+#include <cooperative_groups.h>
+
 #include "brc_device.cuh"
 #include "brc_internal.h"
 
@@ -180,6 +182,334 @@ __global__ void __launch_bounds__(SP_WARPS * 32) sparse_attn_kernel(const Sparse
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// The same contract with the query heads of a kv head sharing every K / V byte (binary16 V, up to 16 query heads
+// per kv head): the reference's apply shader for chunks loads each V row once for its 12 heads
+// (shaders/qsa_attn_apply_gqa.comp:71-136); the kernel above re-reads every selected row once per QUERY head.
+//
+//   one thread-block CLUSTER per (row, kv head); its CTAs (four tile streams each) deal the row's selected blocks out in
+//   tiles of 16 cells (4 blocks); the warps that own a stream (one per group of 8 query heads) gather a tile's K and V rows
+//   with 16-byte cp.async (zero fill for cells beyond the row's position) into a 128-byte-swizzled tile, double
+//   buffered, and compute on the tensor cores as the dense decode kernel does: S^T[16 cells x 8 heads] = K . Q^T
+//   (mma.sync m16n8k16, Q^T fragments from shared memory), online softmax in base 2 by shuffles, P transposed in
+//   registers (movmatrix) and split into a binary16 head and tail, O^T += V^T . P^T with V^T fragments from ldmatrix.trans;
+//   the streams of a CTA merge their (m, l, O) in shared memory, and the CTAs of the cluster merge through DISTRIBUTED
+//   shared memory: CTA r reads the partials of all its peers for the heads r, r + cluster size, ... and writes those
+//   output rows.  No scratch in global memory, no second kernel.
+// ---------------------------------------------------------------------------------------------
+namespace gqa {
+
+constexpr int GROUPS_PER_CTA = 4;   // tiles in flight per CTA: each owned by NT warps (one per group of 8 heads)
+constexpr int MAX_CLUSTER = 8;
+
+template <int HD>
+struct Tile {
+    static constexpr int GROUPS = HD / 64;               // 64-column groups
+    static constexpr int SLAB = 16 * 128;                // [16 cells][64 columns] binary16
+    static constexpr int GROUP_BYTES = 2 * SLAB;         // K slab then V slab
+    static constexpr int BYTES = GROUPS * GROUP_BYTES;   // one tile: 16 KiB at head_dim 256
+    static constexpr int Q_STRIDE = HD * 2 + 16;         // bytes between heads of the query in shared memory (bank spread)
+    static constexpr int CHUNKS = HD / 8;                // 16-byte chunks per row
+};
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, bool live) {
+    const uint32_t n = live ? 16u : 0u;   // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// NT = groups of 8 query heads per kv head (1 or 2) = warps that share a tile: warp nt of a tile's owners computes heads
+// 8 nt .. 8 nt + 7 over the same K / V rows, so 12 heads per kv head keep 8 warps busy on 4 tiles.
+template <int HD, int NT>
+__global__ void __launch_bounds__(GROUPS_PER_CTA * NT * 32, 1) sparse_gqa_kernel(const SparseParams p) {
+    using T = Tile<HD>;
+    constexpr int KSTEPS = HD / 16, MT = HD / 16;
+    constexpr int THREADS = GROUPS_PER_CTA * NT * 32;
+    constexpr uint32_t OWNERS = NT * 32;                 // threads that share a tile
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t cs = cluster.num_blocks(), rank = cluster.block_rank();
+    extern __shared__ uint8_t sg_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(sg_raw) + 1023u) & ~uintptr_t(1023));
+    uint8_t *tiles = smem;                                                   // [GROUPS_PER_CTA][2][T::BYTES]
+    uint8_t *q_hi = tiles + GROUPS_PER_CTA * 2 * T::BYTES;                   // [NT * 8][Q_STRIDE] binary16 heads of the query
+    uint8_t *q_lo = q_hi + NT * 8 * T::Q_STRIDE;                             // tails (f32 queries only)
+    float *cta_o = reinterpret_cast<float *>(q_lo + NT * 8 * T::Q_STRIDE);   // [NT * 8][HD] this CTA's merged O
+    float *cta_ml = cta_o + NT * 8 * HD;                                     // [NT * 8][2]
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t grp = warp / NT, nt = warp % NT;                          // which tile stream, which 8 heads
+    const uint32_t row = blockIdx.y, kvh = blockIdx.x / cs;
+    const uint32_t s = row / p.rows_per_seq, t = row % p.rows_per_seq;
+    const uint32_t pos = p.pos0[s] + t;
+    const uint32_t group = p.n_head / p.n_kv_head;
+    const uint32_t head_base = kvh * group;
+    const bool bad_pos = pos >= p.max_pos_end;
+    if (bad_pos && tid == 0 && rank == 0) { atomicOr(p.status, BRC_DEV_BAD_POS); p.status[1] = pos; }
+
+    // ---- the query heads of this kv head into shared memory: binary16 head (and tail of an f32 query)
+    for (uint32_t i = tid; i < NT * 8 * (HD / 2); i += THREADS) {
+        const uint32_t h = i / (HD / 2), d2 = (i % (HD / 2)) * 2;
+        float2 x = make_float2(0.f, 0.f);
+        if (h < group) {
+            const size_t qo = ((size_t)row * p.n_head + head_base + h) * HD + d2;
+            if (p.q_f32) x = *reinterpret_cast<const float2 *>(static_cast<const float *>(p.q) + qo);
+            else x = __half22float2(*reinterpret_cast<const __half2 *>(static_cast<const __half *>(p.q) + qo));
+        }
+        const __half2 hi = __floats2half2_rn(x.x, x.y);
+        const float2 hf = __half22float2(hi);
+        *reinterpret_cast<__half2 *>(q_hi + h * T::Q_STRIDE + d2 * 2) = hi;
+        *reinterpret_cast<__half2 *>(q_lo + h * T::Q_STRIDE + d2 * 2) = __floats2half2_rn(x.x - hf.x, x.y - hf.y);
+    }
+    __syncthreads();
+
+    const uint32_t count = bad_pos ? 0u : min(p.counts[row], p.max_ids);
+    const uint32_t *ids = p.ids + (size_t)row * p.max_ids;
+    const uint32_t *table = p.block_tables + (size_t)s * p.table_stride;
+    const uint32_t n_tiles = (count + 3u) / 4u;
+    const uint32_t stride = cs * GROUPS_PER_CTA;
+    uint8_t *my_tiles = tiles + (size_t)grp * 2 * T::BYTES;
+    auto owners_sync = [&]() {
+        if (NT == 1) __syncwarp();
+        else brc::named_bar_sync(1 + grp, OWNERS);
+    };
+
+    // Gathers this warp's part of tile j (blocks 4j .. 4j + 3 of the list) into buffer b; returns the mask of live cells.
+    auto gather = [&](uint32_t j, uint32_t b) -> uint32_t {
+        // lane r < 16 resolves cell r of the tile: block r / 4 of the tile, cell r % 4 of the block
+        const uint32_t r = lane & 15u, li = j * 4u + (r >> 2);
+        bool live = false;
+        size_t src_row = 0;
+        if (li < count) {
+            const uint32_t cell = ids[li] * 4u + (r & 3u);
+            const uint32_t lp = cell >> 4;
+            if (cell <= pos && lp < p.table_stride) {
+                const uint32_t page = table[lp];
+                if (page < p.n_pages) {
+                    live = true;
+                    src_row = (((size_t)page * p.n_kv_head + kvh) * 16u + (cell & 15u)) * HD * 2u;
+                } else if (lane < 16 && nt == 0) {
+                    atomicOr(p.status, BRC_DEV_BAD_PAGE);
+                    p.status[1] = page;
+                }
+            }
+        }
+        const uint32_t mask = __ballot_sync(0xffffffffu, live) & 0xffffu;
+        const uint32_t base = brc::smem_u32(my_tiles + (size_t)b * T::BYTES);
+#pragma unroll
+        for (uint32_t i = 0; i < 2u * 16u * T::CHUNKS / OWNERS; ++i) {
+            const uint32_t idx = i * OWNERS + nt * 32u + lane;
+            const uint32_t which = idx / (16u * T::CHUNKS);                 // 0: K, 1: V
+            const uint32_t rr = (idx / T::CHUNKS) % 16u, ch = idx % T::CHUNKS;
+            const size_t off = __shfl_sync(0xffffffffu, src_row, rr);
+            const bool lv = (mask >> rr) & 1u;
+            const uint32_t dst = base + (ch >> 3) * T::GROUP_BYTES + which * T::SLAB + rr * 128u + (((ch & 7u) ^ (rr & 7u)) << 4);
+            cp_async_16(dst, (which ? p.v_layer : p.k_layer) + off + ch * 16u, lv);
+        }
+        return mask;
+    };
+
+    // fragment lane constants (as in the dense decode kernel)
+    const uint32_t t0 = lane >> 2, h0 = (lane & 3u) * 2u;
+    const uint32_t k_r = (lane & 7u) + ((lane >> 3) & 1u) * 8u, k_x = (lane >> 4) ^ (k_r & 7u), k_lane = k_r * 128u;
+    const uint32_t v_r = (lane & 7u) + (lane >> 4) * 8u, v_x = ((lane >> 3) & 1u) ^ (v_r & 7u), v_lane = T::SLAB + v_r * 128u;
+    // B operand of S^T = K . Q^T: head 8 nt + t0, elements 16 ks + 2 (lane & 3) + {0, 1} and + 8
+    const uint32_t q_lane = brc::smem_u32(q_hi) + (nt * 8u + t0) * T::Q_STRIDE + (lane & 3u) * 4u;
+    const uint32_t q_lo_off = (uint32_t)(q_lo - q_hi);
+
+    float o[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    uint32_t j = rank * GROUPS_PER_CTA + grp, buf = 0;
+    uint32_t mask = 0, mask_next = 0;
+    if (j < n_tiles) mask = gather(j, 0);
+    cp_async_commit();
+    for (; j < n_tiles; j += stride, buf ^= 1u) {
+        if (j + stride < n_tiles) mask_next = gather(j + stride, buf ^ 1u);
+        cp_async_commit();
+        cp_async_wait<1>();
+        owners_sync();        // every owner's copies of this tile have landed
+        const uint32_t sbase = brc::smem_u32(my_tiles + (size_t)buf * T::BYTES);
+        // ---- S^T = K . Q^T
+        float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            uint32_t af[4];
+            brc::ldmatrix_x4(af, sbase + (ks >> 2) * T::GROUP_BYTES + k_lane + ((k_x ^ ((ks & 3) * 2u)) << 4));
+            const uint32_t qa = q_lane + ks * 32u;
+            uint32_t b0, b1;
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(b0) : "r"(qa));
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(b1) : "r"(qa + 16u));
+            if (ks & 1) brc::mma_16816(sb, af, b0, b1); else brc::mma_16816(sa, af, b0, b1);
+            if (p.q_f32) {
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(b0) : "r"(qa + q_lo_off));
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(b1) : "r"(qa + q_lo_off + 16u));
+                if (ks & 1) brc::mma_16816(sb, af, b0, b1); else brc::mma_16816(sa, af, b0, b1);
+            }
+        }
+        float sc[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sc[i] = (sa[i] + sb[i]) * p.scale_log2;
+        if (!((mask >> t0) & 1u)) sc[0] = sc[1] = -INFINITY;
+        if (!((mask >> (t0 + 8u)) & 1u)) sc[2] = sc[3] = -INFINITY;
+        float x0 = fmaxf(sc[0], sc[2]), x1 = fmaxf(sc[1], sc[3]);
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, off));
+            x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, off));
+        }
+        const float n0 = fmaxf(m0, x0), n1 = fmaxf(m1, x1);
+        const float z0 = n0 == -INFINITY ? 0.f : n0, z1 = n1 == -INFINITY ? 0.f : n1;   // no live cell so far
+        const float al0 = brc::fast_exp2(m0 - z0), al1 = brc::fast_exp2(m1 - z1);
+        m0 = n0;
+        m1 = n1;
+        const float p0 = brc::fast_exp2(sc[0] - z0), p1 = brc::fast_exp2(sc[1] - z1);
+        const float p2 = brc::fast_exp2(sc[2] - z0), p3 = brc::fast_exp2(sc[3] - z1);
+        l0 = l0 * al0 + (p0 + p2);
+        l1 = l1 * al1 + (p1 + p3);
+        if (__any_sync(0xffffffffu, (al0 != 1.f) | (al1 != 1.f))) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                o[mt][0] *= al0;
+                o[mt][1] *= al1;
+                o[mt][2] *= al0;
+                o[mt][3] *= al1;
+            }
+        }
+        const __half2 ph01 = __floats2half2_rn(p0, p1), ph23 = __floats2half2_rn(p2, p3);
+        const float2 f01 = __half22float2(ph01), f23 = __half22float2(ph23);
+        const uint32_t bh0 = brc::movmatrix_trans(*reinterpret_cast<const uint32_t *>(&ph01));
+        const uint32_t bh1 = brc::movmatrix_trans(*reinterpret_cast<const uint32_t *>(&ph23));
+        const uint32_t bl0 = brc::movmatrix_trans(brc::pack_half2(p0 - f01.x, p1 - f01.y));
+        const uint32_t bl1 = brc::movmatrix_trans(brc::pack_half2(p2 - f23.x, p3 - f23.y));
+        // ---- O^T += V^T . P^T
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            uint32_t af[4];
+            brc::ldmatrix_x4_trans(af, sbase + (mt >> 2) * T::GROUP_BYTES + v_lane + ((v_x ^ ((mt & 3) * 2u)) << 4));
+            brc::mma_16816(o[mt], af, bh0, bh1);
+            brc::mma_16816(o[mt], af, bl0, bl1);
+        }
+        owners_sync();   // the buffer is refilled in the next iteration but one, by all owners
+        mask = mask_next;
+    }
+    cp_async_wait<0>();
+    __syncthreads();    // every warp is done with its tiles: their memory now carries the warps' partials
+
+    // ---- warps -> CTA: (m, l) and O of every tile stream through shared memory, merged per head
+    float *w_o = reinterpret_cast<float *>(tiles);                          // [GROUPS_PER_CTA][NT * 8][HD]
+    float *w_ml = w_o + GROUPS_PER_CTA * NT * 8 * HD;                       // [GROUPS_PER_CTA][NT * 8][2]
+    {
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+        }
+        float *wo = w_o + ((size_t)grp * NT * 8 + nt * 8) * HD;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            wo[h0 * HD + mt * 16 + t0] = o[mt][0];
+            wo[(h0 + 1) * HD + mt * 16 + t0] = o[mt][1];
+            wo[h0 * HD + mt * 16 + t0 + 8] = o[mt][2];
+            wo[(h0 + 1) * HD + mt * 16 + t0 + 8] = o[mt][3];
+        }
+        if (lane < 4) {
+            float *ml = w_ml + ((size_t)grp * NT * 8 + nt * 8 + h0) * 2;
+            ml[0] = m0, ml[1] = l0, ml[2] = m1, ml[3] = l1;
+        }
+    }
+    __syncthreads();
+    for (uint32_t h = warp; h < group; h += THREADS / 32) {     // a warp per head
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < GROUPS_PER_CTA; ++w)
+            if (w_ml[(w * NT * 8 + h) * 2 + 1] > 0.f) M = fmaxf(M, w_ml[(w * NT * 8 + h) * 2]);
+        float L = 0.f, wt[GROUPS_PER_CTA];
+#pragma unroll
+        for (int w = 0; w < GROUPS_PER_CTA; ++w) {
+            const float lw = w_ml[(w * NT * 8 + h) * 2 + 1];
+            wt[w] = lw > 0.f ? exp2f(w_ml[(w * NT * 8 + h) * 2] - M) : 0.f;
+            L += wt[w] * lw;
+        }
+        for (uint32_t d = lane; d < HD; d += 32) {
+            float acc = 0.f;
+#pragma unroll
+            for (int w = 0; w < GROUPS_PER_CTA; ++w) acc += wt[w] * w_o[((size_t)w * NT * 8 + h) * HD + d];
+            cta_o[h * HD + d] = acc;
+        }
+        if (lane == 0) { cta_ml[h * 2] = M; cta_ml[h * 2 + 1] = L; }
+    }
+    cluster.sync();
+
+    // ---- CTAs -> output: CTA `rank` finishes heads rank, rank + cs, ... from the partials of all its peers
+    for (uint32_t h = rank; h < group; h += cs) {
+        float M = -INFINITY, Ms[MAX_CLUSTER], Ls[MAX_CLUSTER];
+#pragma unroll
+        for (uint32_t r = 0; r < MAX_CLUSTER; ++r) {
+            if (r < cs) {
+                const float *ml = cluster.map_shared_rank(cta_ml, r);
+                Ms[r] = ml[h * 2];
+                Ls[r] = ml[h * 2 + 1];
+                if (Ls[r] > 0.f) M = fmaxf(M, Ms[r]);
+            }
+        }
+        float L = 0.f, wt[MAX_CLUSTER];
+#pragma unroll
+        for (uint32_t r = 0; r < MAX_CLUSTER; ++r) {
+            wt[r] = (r < cs && Ls[r] > 0.f) ? exp2f(Ms[r] - M) : 0.f;
+            if (r < cs) L += wt[r] * Ls[r];
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;    // a row with no selected live cell yields zeros
+        for (uint32_t d = tid; d < HD; d += THREADS) {
+            float acc = 0.f;
+#pragma unroll
+            for (uint32_t r = 0; r < MAX_CLUSTER; ++r)
+                if (r < cs) acc += wt[r] * cluster.map_shared_rank(cta_o, r)[h * HD + d];
+            float v = acc * inv;
+            const size_t orow = (size_t)row * p.n_head + head_base + h;
+            if (p.gate) v *= sp_sigmoid(p.gate[orow * p.gate_head_stride + d]);
+            p.out[orow * HD + d] = v;
+        }
+    }
+    cluster.sync();   // nobody leaves while a peer may still read its shared memory
+}
+
+template <int HD>
+constexpr uint32_t smem_bytes(int nt) {
+    return 1024u + GROUPS_PER_CTA * 2 * Tile<HD>::BYTES + 2u * nt * 8 * Tile<HD>::Q_STRIDE + nt * 8 * HD * 4u + nt * 8 * 2 * 4u + 64u;
+}
+
+template <int HD, int NT>
+cudaError_t launch(const SparseParams &p, uint32_t rows, uint32_t n_kv_head, uint32_t cs, cudaStream_t st) {
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(sparse_gqa_kernel<HD, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<HD>(NT));
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_kv_head * cs, rows);
+    cfg.blockDim = dim3(GROUPS_PER_CTA * NT * 32);
+    cfg.dynamicSmemBytes = smem_bytes<HD>(NT);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cs;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, sparse_gqa_kernel<HD, NT>, p);
+}
+
+}  // namespace gqa
+
 }  // namespace
 
 extern "C" {
@@ -238,6 +568,20 @@ brc_status brc_paged_sparse_attn(brc_pool *pool, uint32_t layer, const void *q_d
     brc_stage_begin(pool, BRC_STAGE_ATTN_PARTIAL, st);
     const uint64_t sms = (uint64_t)(pool->sm_count > 0 ? pool->sm_count : 148);
     const bool few = rows * n_head < 2u * sms;
+    const uint32_t group = n_head / pool->n_kv_head;
+    if (!pool->v_q8 && group <= 16u) {
+        // one cluster per (row, kv head): as many CTAs per cluster (a power of two, at most 8) as keep every SM busy
+        const uint64_t units = rows * pool->n_kv_head;
+        uint32_t cs = 1;
+        while (cs < (uint32_t)gqa::MAX_CLUSTER && units * cs * 2u <= sms) cs *= 2u;
+        cudaError_t e;
+        if (hd == 256) e = group <= 8u ? gqa::launch<256, 1>(p, (uint32_t)rows, pool->n_kv_head, cs, st) : gqa::launch<256, 2>(p, (uint32_t)rows, pool->n_kv_head, cs, st);
+        else e = group <= 8u ? gqa::launch<128, 1>(p, (uint32_t)rows, pool->n_kv_head, cs, st) : gqa::launch<128, 2>(p, (uint32_t)rows, pool->n_kv_head, cs, st);
+        brc_stage_end(pool, BRC_STAGE_ATTN_PARTIAL, st);
+        if (e != cudaSuccess) return brc_fail(BRC_ERR_CUDA, "brc_paged_sparse_attn: launch failed: %s", cudaGetErrorString(e));
+        BRC_CUDA(cudaGetLastError());
+        return BRC_OK;
+    }
     if (pool->v_q8) {
         if (hd == 256) {
             if (few) sparse_attn_kernel<256, 16, true><<<grid, 512, 0, st>>>(p);
