@@ -40,6 +40,7 @@
 //
 // HBM-bound by design: 8 FLOP per cached byte, all of it on the tensor pipe.
 #include <algorithm>
+#include <cstdlib>
 
 #include "brc_device.cuh"
 #include "brc_internal.h"
@@ -50,6 +51,7 @@ namespace {
 // the instructions per page (the quanta are converted in registers), so it runs 6 to hide their latency.
 __host__ __device__ constexpr int consumer_warps(bool v_q8) { return v_q8 ? 6 : 4; }
 constexpr int MAX_UNITS = 2048;            // (sequence, kv-head group) units per launch
+constexpr int MAX_CTAS = 256;              // CTAs of a launch (one per SM)
 constexpr int GROUP_TILE = 8;              // query heads per kv head held by one n-tile
 constexpr uint32_t SMEM_LIMIT = 232448;    // 227 KiB opt-in maximum per CTA
 constexpr uint64_t WAIT_NS = 1000000000ull;  // one second: far beyond any legitimate wait here
@@ -77,8 +79,10 @@ struct Cfg {
     static constexpr int SCRATCH_WARP = GROUP_TILE * OPAD + 16;  // floats per warp
     static constexpr int SCRATCH_BYTES = NW * SCRATCH_WARP * 4;
     static constexpr int PREFIX_BYTES = (MAX_UNITS + 4) * 4;
+    static constexpr int NZ_BYTES = (MAX_UNITS + 8) * 2;   // units with pages before unit u (16-bit)
+    static constexpr int CUT_BYTES = (MAX_CTAS + 4) * 4;   // where every CTA's share begins
     static constexpr int BAR_BYTES = 1024;
-    static constexpr int FIXED_BYTES = SCRATCH_BYTES + PREFIX_BYTES + BAR_BYTES + 1024 /*alignment slack*/;
+    static constexpr int FIXED_BYTES = SCRATCH_BYTES + PREFIX_BYTES + NZ_BYTES + CUT_BYTES + BAR_BYTES + 1024 /*alignment slack*/;
 };
 
 struct DecodeParams {
@@ -125,6 +129,7 @@ struct DecodeParams {
     uint32_t *calls;               // exchanges completed so far on this rank (device-resident epoch)
     uint32_t *fin_ticket;          // CTAs of this launch that have finished
     uint64_t wait_ns;
+    uint32_t unit_cost;            // page-units charged per unit with pages when the list is cut into shares
 };
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
@@ -156,8 +161,15 @@ __device__ __forceinline__ uint32_t unit_of(const uint32_t *S, uint32_t n_units,
     return lo;
 }
 
-__device__ __forceinline__ uint32_t share_begin(uint32_t cta, uint32_t total, uint32_t n_cta) {
-    return (uint32_t)(((uint64_t)cta * total) / n_cta);
+// Shares: CTA i streams the page-units [B[i], B[i + 1]) of the flat list; the table is built at the start of the
+// kernel (see there).  The share that holds page-unit g: the one with B[i] <= g < B[i + 1].
+__device__ __forceinline__ uint32_t share_of(const uint32_t *B, uint32_t n_cta, uint32_t g) {
+    uint32_t lo = 0, hi = n_cta;            // B[lo] <= g, B[hi] > g
+    while (hi - lo > 1) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (B[mid] <= g) lo = mid; else hi = mid;
+    }
+    return lo;
 }
 
 __device__ __forceinline__ float sigmoid_f32(float x) {
@@ -166,15 +178,10 @@ __device__ __forceinline__ float sigmoid_f32(float x) {
     return e / (1.f + e);
 }
 
-// CTAs whose share [begin(i), begin(i+1)) meets the page-unit range [first_g, last_g].
-__device__ __forceinline__ void share_range(uint32_t first_g, uint32_t last_g, uint32_t total, uint32_t n_cta,
-                                            uint32_t &i_lo, uint32_t &i_hi) {
-    i_lo = (uint32_t)(((uint64_t)first_g * n_cta) / total);
-    while (i_lo + 1 < n_cta && share_begin(i_lo + 1, total, n_cta) <= first_g) ++i_lo;
-    while (i_lo > 0 && share_begin(i_lo, total, n_cta) > first_g) --i_lo;
-    i_hi = (uint32_t)(((uint64_t)last_g * n_cta) / total);
-    while (i_hi + 1 < n_cta && share_begin(i_hi + 1, total, n_cta) <= last_g) ++i_hi;
-    while (i_hi > 0 && share_begin(i_hi, total, n_cta) > last_g) --i_hi;
+// CTAs whose share meets the page-unit range [first_g, last_g].
+__device__ __forceinline__ void share_range(const uint32_t *B, uint32_t n_cta, uint32_t first_g, uint32_t last_g, uint32_t &i_lo, uint32_t &i_hi) {
+    i_lo = share_of(B, n_cta, first_g);
+    i_hi = share_of(B, n_cta, last_g);
 }
 
 // A unit of a launch that covers several layers: flat index over (layer, unit) and its parts.
@@ -226,7 +233,7 @@ constexpr uint32_t MAX_RUN_CTAS = 256;    // run tickets: 2 words per CTA after 
 // rank's slot of every rank's receive buffer (its own included), then one flag per rank is released.
 template <int HD, int KVB, bool CAN_PUSH, bool VQ8>
 __device__ __forceinline__ void combine_unit(const DecodeParams &p, const UnitRef ur, uint32_t i_lo, uint32_t i_hi, uint32_t stride,
-                                             bool to_slot, uint32_t total, uint32_t tid, float *sm, uint32_t epoch, uint32_t bank) {
+                                             bool to_slot, const uint32_t *B, bool dense, uint32_t tid, float *sm, uint32_t epoch, uint32_t bank) {
     constexpr int NW = consumer_warps(VQ8);
     const uint32_t u = ur.u;
     constexpr uint32_t TPR = HD / 4;                    // threads per output row (float4 each)
@@ -237,7 +244,6 @@ __device__ __forceinline__ void combine_unit(const DecodeParams &p, const UnitRe
     const uint32_t n_groups = p.n_kv_head / KVB;
     const uint32_t s = u / n_groups, kv0 = (u % n_groups) * KVB;
     const uint32_t d = (tid % TPR) * 4;
-    const bool dense = total >= gridDim.x;              // then no CTA has an empty share
 
     uint32_t *list = reinterpret_cast<uint32_t *>(sm);                        // [COMBINE_CHUNK] share (CTA) ids
     uint32_t *n_list = list + COMBINE_CHUNK;                                  // [1] (+ padding)
@@ -262,7 +268,7 @@ __device__ __forceinline__ void combine_unit(const DecodeParams &p, const UnitRe
             if (tid == 0) {
                 uint32_t n = 0, i = i0;
                 for (; i <= i_hi && n < COMBINE_CHUNK; ++i)
-                    if (share_begin(i, total, gridDim.x) != share_begin(i + 1, total, gridDim.x)) list[n++] = i;
+                    if (B[i] != B[i + 1]) list[n++] = i;
                 n_list[0] = n;
                 n_list[1] = i;
             }
@@ -496,7 +502,9 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
     uint8_t *ring = smem;
     float *scratch = reinterpret_cast<float *>(ring + (size_t)p.n_stages * C::STAGE_BYTES);
     uint32_t *S = reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(scratch) + C::SCRATCH_BYTES);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(S) + C::PREFIX_BYTES);
+    uint16_t *nz = reinterpret_cast<uint16_t *>(reinterpret_cast<uint8_t *>(S) + C::PREFIX_BYTES);   // [n_units + 1] units with pages before u
+    uint32_t *B = reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(nz) + C::NZ_BYTES);          // [CTAs + 1] where every share begins
+    uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(B) + C::CUT_BYTES);
     const uint32_t full0 = brc::smem_u32(bars);
     const uint32_t empty0 = full0 + 8u * p.n_stages;
     // small words after the barriers (2 x 24 barriers at most = 384 bytes): flags, merge weights
@@ -527,9 +535,10 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
         gave_up[0] = 0u;
     }
     // Exclusive prefix of pages per unit of ONE layer, S[0..n_units] (the layers of a launch share the
-    // sequence lengths); every CTA computes it (n_units <= 2048).
+    // sequence lengths), and nz[0..n_units], how many of the units before u have pages; every CTA computes
+    // both (n_units <= 2048).
     if (warp == 0) {
-        uint32_t run = 0;
+        uint32_t run = 0, nz_run = 0;
         for (uint32_t base = 0; base < n_units; base += 32) {
             const uint32_t u = base + lane;
             uint32_t pg = 0;
@@ -548,16 +557,60 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
                 const uint32_t v = __shfl_up_sync(0xffffffffu, inc, o);
                 if ((int)lane >= o) inc += v;
             }
-            if (u < n_units) S[u] = run + inc - pg;
+            const uint32_t live = __ballot_sync(0xffffffffu, pg != 0);
+            if (u < n_units) {
+                S[u] = run + inc - pg;
+                nz[u] = (uint16_t)(nz_run + __popc(live & ((1u << lane) - 1u)));
+            }
             run += __shfl_sync(0xffffffffu, inc, 31);
+            nz_run += __popc(live);
         }
-        if (lane == 0) S[n_units] = run;
+        if (lane == 0) {
+            S[n_units] = run;
+            nz[n_units] = (uint16_t)nz_run;
+        }
     }
     __syncthreads();
 
     const uint32_t total_l = S[n_units];            // page-units of one layer
     const uint32_t total = total_l * p.n_layers;    // of the launch (the host keeps this below 2^32)
     const uint32_t n_units_all = n_units * p.n_layers;
+
+    // ---- the cut: where every CTA's share begins.  The flat list is cut into equal shares not of page-units
+    // but of COST: every unit with pages costs p.unit_cost page-units on top of its pages, charged where the
+    // unit begins (a CTA pays one epilogue per unit it touches: one in any case, one more for every unit that
+    // begins inside its share).  Cost position of page g of unit u in layer l:
+    //   l * cost_l + S[u] + unit_cost * (nz[u] + 1) + (g - S[u]),   cost_l = total_l + unit_cost * nz[n_units].
+    // A threshold that falls into a unit's surcharge cuts at the unit's first page.  Every CTA builds the same
+    // table; B is ascending, B[0] = 0, B[gridDim.x] = total.
+    {
+        const uint32_t E = p.unit_cost;
+        const uint64_t cost_l = (uint64_t)total_l + (uint64_t)E * nz[n_units];
+        const uint64_t cost = cost_l * p.n_layers;
+        for (uint32_t i = tid; i <= gridDim.x; i += NTHREADS) {
+            uint32_t at = total;
+            if (i < gridDim.x && total != 0) {
+                const uint64_t t = cost * i / gridDim.x;
+                const uint32_t l = (uint32_t)(t / cost_l);
+                const uint32_t tl = (uint32_t)(t - (uint64_t)l * cost_l);
+                uint32_t lo = 0, hi = n_units;          // largest u with S[u] + E * nz[u] <= tl: a unit with pages
+                while (hi - lo > 1) {
+                    const uint32_t mid = (lo + hi) >> 1;
+                    if (S[mid] + E * nz[mid] <= tl) lo = mid; else hi = mid;
+                }
+                const uint32_t off = tl - (S[lo] + E * nz[lo]);
+                at = l * total_l + S[lo] + (off > E ? off - E : 0u);
+            }
+            B[i] = at;
+        }
+        __syncthreads();
+        int live = 1;
+        for (uint32_t i = tid; i < gridDim.x; i += NTHREADS) live &= B[i] != B[i + 1];
+        live = __syncthreads_and(live);
+        if (tid == 0) B[MAX_CTAS + 2] = live != 0;      // read back where needed instead of held in a register
+        __syncthreads();
+    }
+#define all_shares_live (B[MAX_CTAS + 2] != 0u)         /* no CTA has an empty share */
 
     // A sequence without cells has no pages, hence no share and no ticket: its rows are written here.
     for (uint32_t U = blockIdx.x; U < n_units_all; U += gridDim.x) {
@@ -589,8 +642,8 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
         }
     }
 
-    const uint32_t a = share_begin(blockIdx.x, total, gridDim.x);
-    const uint32_t b = share_begin(blockIdx.x + 1, total, gridDim.x);
+    const uint32_t a = B[blockIdx.x];
+    const uint32_t b = B[blockIdx.x + 1];
     const uint32_t count = b - a;
 
     if (warp == NW) {
@@ -1063,21 +1116,20 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
         if (!whole) {
             // ---- ticket: the CTA that completes the last share of a unit combines all of its shares
             uint32_t i_lo, i_hi;
-            share_range(unit_first, lbase + S[u + 1] - 1, total, gridDim.x, i_lo, i_hi);
+            share_range(B, gridDim.x, unit_first, lbase + S[u + 1] - 1, i_lo, i_hi);
             uint32_t *const unit_ticket = p.done + layer * BRC_DONE_BANK_WORDS + u;
             // A unit that spans many CTAs (one long sequence alone on the GPU spans all of them) is merged
             // in two levels, or its last arriver would pull every share through one SM: runs of `fan`
             // consecutive shares have a ticket of their own, the run's last arriver merges the run into the
             // slot of its first share, and the last run to finish merges the runs.
             const uint32_t span = i_hi - i_lo + 1;
-            const bool two_level = total >= gridDim.x && span > TWO_LEVEL_MIN && gridDim.x <= MAX_RUN_CTAS;
+            const bool two_level = all_shares_live && span > TWO_LEVEL_MIN && gridDim.x <= MAX_RUN_CTAS;
             if (!two_level) {
                 if (tid == 0) {
                     uint32_t pieces = span;
-                    if (total < gridDim.x) {   // fewer page-units than CTAs: some shares in between are empty
+                    if (!all_shares_live) {   // few page-units: some shares in between may be empty
                         pieces = 0;
-                        for (uint32_t i = i_lo; i <= i_hi; ++i)
-                            pieces += share_begin(i, total, gridDim.x) != share_begin(i + 1, total, gridDim.x);
+                        for (uint32_t i = i_lo; i <= i_hi; ++i) pieces += B[i] != B[i + 1];
                     }
                     const uint32_t ticket = atomicAdd(unit_ticket, 1u);
                     const uint32_t last = ticket + 1u == pieces;
@@ -1087,7 +1139,7 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
                 brc::named_bar_sync(1, NW * 32);
                 if (flags[0]) {
                     __threadfence();
-                    combine_unit<HD, KVB, !WHOLE_FAST, VQ8>(p, ur, i_lo, i_hi, 1, false, total, tid, scratch, epoch, bank);
+                    combine_unit<HD, KVB, !WHOLE_FAST, VQ8>(p, ur, i_lo, i_hi, 1, false, B, all_shares_live, tid, scratch, epoch, bank);
                 }
             } else {
                 uint32_t fan = 1;
@@ -1106,7 +1158,7 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
                 brc::named_bar_sync(1, NW * 32);
                 if (flags[0]) {
                     __threadfence();
-                    combine_unit<HD, KVB, !WHOLE_FAST, VQ8>(p, ur, r_lo, r_hi, 1, true, total, tid, scratch, epoch, bank);
+                    combine_unit<HD, KVB, !WHOLE_FAST, VQ8>(p, ur, r_lo, r_hi, 1, true, B, all_shares_live, tid, scratch, epoch, bank);
                     __threadfence();   // the run's merged partial is visible before the unit's ticket is taken
                     brc::named_bar_sync(1, NW * 32);
                     if (tid == 0) {
@@ -1118,7 +1170,7 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
                     brc::named_bar_sync(1, NW * 32);
                     if (flags[0]) {
                         __threadfence();
-                        combine_unit<HD, KVB, !WHOLE_FAST, VQ8>(p, ur, i_lo, i_hi, fan, false, total, tid, scratch, epoch, bank);
+                        combine_unit<HD, KVB, !WHOLE_FAST, VQ8>(p, ur, i_lo, i_hi, fan, false, B, all_shares_live, tid, scratch, epoch, bank);
                     }
                 }
             }
@@ -1152,8 +1204,8 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
             if (uend != ubeg) {
                 const UnitRef ur = {fl * n_units + fu, fl, fu};
                 uint32_t i_lo, i_hi;
-                share_range(ubeg, uend - 1, total, gridDim.x, i_lo, i_hi);
-                if (total >= gridDim.x)
+                share_range(B, gridDim.x, ubeg, uend - 1, i_lo, i_hi);
+                if (all_shares_live)
                     finalize_unit<HD, KVB, VQ8>(p, ur, blockIdx.x - i_lo, i_hi - i_lo + 1, epoch, bank, tid, gave_up);
                 else if (blockIdx.x == i_hi)
                     finalize_unit<HD, KVB, VQ8>(p, ur, 0, 1, epoch, bank, tid, gave_up);
@@ -1207,6 +1259,8 @@ __global__ void __launch_bounds__(HD)
     out[(size_t)row * HD + tid] = v;
 }
 
+#undef all_shares_live
+
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
@@ -1240,7 +1294,21 @@ uint32_t stages_for(uint32_t head_dim, uint32_t kvb, bool v_q8) {
 
 uint32_t seqs_per_launch(const brc_pool *pool) { return MAX_UNITS / (pool->n_kv_head / kvb_of(pool)); }
 
-uint32_t grid_ctas(const brc_pool *pool) { return (uint32_t)(pool->sm_count > 0 ? pool->sm_count : 148); }
+uint32_t grid_ctas(const brc_pool *pool) { return std::min<uint32_t>((uint32_t)(pool->sm_count > 0 ? pool->sm_count : 148), MAX_CTAS); }
+
+// What every unit it touches costs a CTA on top of the unit's pages (merge of the warps, partial or output
+// written, ticket, perhaps the unit's merge), in page-units of this pool.  Measured on the 32-sequence batches
+// of skewed and of equal lengths: an isolated launch gets faster up to about 12 page-units of 32 KiB (66 -> 62 us
+// and 103 -> 100 us), a 12-layer launch by 2 %, and nothing changes beyond; hence 384 KiB worth of page-units.
+// BRC_DECODE_UNIT_COST in the environment overrides it (0 = cut into equal numbers of page-units).
+uint32_t unit_cost_of(uint32_t head_dim, uint32_t kvb, bool v_q8) {
+    static const long env = [] {
+        const char *e = std::getenv("BRC_DECODE_UNIT_COST");
+        return e && *e ? std::strtol(e, nullptr, 10) : -1L;
+    }();
+    if (env >= 0) return (uint32_t)std::min(env, 64L);
+    return std::max<uint32_t>(1u, (384u * 1024u + stage_bytes_of(head_dim, kvb, v_q8) / 2u) / stage_bytes_of(head_dim, kvb, v_q8));
+}
 
 // Partial slots of one launch over `n_layers` layers of `n_seqs` sequences: one per (layer, unit) plus one
 // per CTA (a share boundary inside a unit makes one more partial), x KVB kv heads; acc then (m, l).
@@ -1440,6 +1508,7 @@ brc_status brc_decode_layers(brc_pool *pool, const char *who, const brc_layers_a
             p.n_stages = n_stages;
             p.scale_log2 = a.scale * 1.4426950408889634f;
             p.n_layers = nl;
+            p.unit_cost = unit_cost_of(hd, kvb, pool->v_q8);
             p.q_layer_stride = a.q_layer_stride_bytes / q_elem;
             p.out_layer_stride = a.out_layer_stride_bytes / 4;
             p.out_ml_layer_stride = a.out_ml_layer_stride_bytes / 4;

@@ -528,6 +528,26 @@ def test_units_spanning_many_ctas_merge_in_two_levels(cuda_device, n_head, n_kv,
     pool.release()
 
 
+@pytest.mark.parametrize("name,lens,n_kv", [
+    # the per-unit surcharge of the cut dominates the pages: most thresholds fall into a surcharge and snap to a unit's start
+    ("400 one-page sequences", [1 + i % 16 for i in range(400)], 2),
+    # runs of sequences without cells between the others, at the start and at the end of the batch
+    ("empty runs", [0, 0, 0, 700, 0, 33, 0, 0, 0, 0, 5000, 0, 17, 0, 0], 2),
+    # fewer page-units than CTAs: shares in between are empty, the unit's pieces are counted from the table
+    ("nine pages", [40, 0, 64, 33], 2),
+    ("one unit of three pages among four kv heads", [0, 48], 4),
+    # one long unit beside many short ones: the long one spans most CTAs (two-level merge), the short ones share a CTA
+    ("one long, sixty short", [40000] + [20 + i for i in range(60)], 2),
+])
+def test_cost_weighted_cut_of_the_page_list(cuda_device, name, lens, n_kv):
+    pool, _, _, got, want = _batch_case(16 if n_kv == 2 else 8, n_kv, 256, lens, seed=131 + len(lens))
+    assert_attention_close(got, want, name)
+    for s, n in enumerate(lens):
+        if n == 0:
+            assert not got[s].any(), f"{name}: sequence {s} has no cells, its rows must be zero"
+    pool.release()
+
+
 def test_more_units_than_one_launch_holds(cuda_device):
     """1100 short sequences x 2 kv heads exceed the 2048 units one launch schedules: the host loops."""
     lens = (np.arange(1100) % 37 + 1).astype(np.int64)
