@@ -456,6 +456,13 @@ def bench_splitkv(ctx, args, steps):
     ms_step = ctx.timed(lambda: split.step(q, out), 3, steps) / steps
     ms_chain = ctx.timed(chain, 3, steps) / steps
     pool.check()
+    # the same chain recorded once as a CUDA graph and replayed: one driver call per token instead of twelve library
+    # calls, which is what bounds the plain loop once a layer's share of the cells streams in a few microseconds
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        chain()
+    ms_chain_graph = ctx.timed(graph.replay, 3, steps) / steps
+    pool.check()
 
     # ---- this rank's share alone (no exchange): the same launch over the local cells through a group of one
     local_comm = C.c_void_p()
@@ -535,6 +542,7 @@ def bench_splitkv(ctx, args, steps):
             "scaling": "strong", "n_gpus": ctx.world,
             "step": dict(form(ms_step), how="brc_splitkv_step: one launch per rank and token; the layers' attention calls do not depend on one another"),
             "layer_by_layer": dict(form(ms_chain), how="brc_splitkv_attend per layer, each ordered after the one before (a model's dependency chain)"),
+            "layer_by_layer_graph": dict(form(ms_chain_graph), how="the same twelve calls captured once in a CUDA graph, one replay per token"),
             "local_share_alone_ms_per_step": ms_local,
             "exchange_and_merge_ms_per_step": ms_step - ms_local,
             "one_gpu_same_run_ms_per_step": ms_one, "speedup_vs_one_gpu_same_run": ms_one / ms_step,

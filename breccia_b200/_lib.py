@@ -72,6 +72,7 @@ SIGNATURES = {
     "brc_page_copy": [_vp, _vp, _vp, _u32, _vp],
     "brc_seq_fork": [_vp, _u32p, _u32, _u32p, _u32p, _vp],
     "brc_decode_workspace_bytes": [_vp, _u32, _u32, _u64p],
+    "brc_decode_share_rates": [_vp, C.POINTER(C.c_float), _u32, _u32p],
     "brc_paged_decode_attn": [_vp, _u32, _vp, _i32, _u32, _vp, _u32, _vp, _u32, _vp, _u32, _u32, _f32, _vp, _vp,
                               _u64, _vp],
     "brc_paged_decode_attn_static": [_vp, _u32, _vp, _i32, _u32, _vp, _u32, _vp, _u32, _vp, _u32, _u32, _f32, _vp, _vp],

@@ -2,7 +2,7 @@
 --op qsa`, crates/breccia-kernels/src/qsa/bench.rs; one JSON line per cell with the fields of its
 `OpCell`: op, case, units, bytes or flops, us, GB/s or TFLOP/s, iters).
 
-    python -m breccia_b200.bench_ops [--op prefill|prepare|sparse|topk|movers|all] [--iters N]
+    python -m breccia_b200.bench_ops [--op prefill|prepare|sparse|topk|indexer|movers|all] [--iters N]
 
 Timing: CUDA events on the launching stream, 3 warm-up runs, the mean of `iters` runs.  Shapes are the
 benchmark configurations: prefill = 64 sequences sharing a 4096-token prefix, 256-token chunk each
@@ -196,6 +196,44 @@ def bench_topk(iters: int):
     pool.release()
 
 
+def bench_indexer(iters: int):
+    """Indexer stages at the reference's shapes: scores of one decode row, of 32 rows and of a 256-row chunk of 8
+    sequences over 8192 pooled keys (32 768 cells); pooling + tail of a 256-token chunk of 8 sequences."""
+    from .qsa import IDX_BLOCK, IDX_DIM, IDX_N_HEAD, IndexerState
+
+    pool = KvPool(0, 1, N_KV, HD, 4)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(8)
+    n_blocks = 8192
+    for n_seqs, rows_per_seq in ((1, 1), (32, 1), (8, 256)):
+        rows = n_seqs * rows_per_seq
+        idx = IndexerState(pool, n_seqs, n_blocks * IDX_BLOCK)
+        idx.pooled.copy_(torch.randn(idx.pooled.shape, generator=gen, device="cuda"))
+        q = torch.randn((rows, IDX_N_HEAD, IDX_DIM), generator=gen, device="cuda")
+        pos0 = dev_u32(np.full(n_seqs, IDX_BLOCK * n_blocks - rows_per_seq))
+        us = timed(lambda: idx.score(q, pos0, rows_per_seq, n_blocks), iters)
+        pool.check()
+        # every pooled key once per sequence (the rows of a sequence share them), the queries, the scores
+        nbytes = n_seqs * n_blocks * IDX_DIM * 4 + rows * IDX_N_HEAD * IDX_DIM * 4 + rows * n_blocks * 4
+        flops = 2 * rows * IDX_N_HEAD * n_blocks * IDX_DIM
+        emit(op="idx_score", case=f"{rows} row(s) x {n_blocks} pooled keys, {IDX_N_HEAD} index heads of {IDX_DIM}", units=rows,
+             bytes=nbytes, flops=flops, us=us, gbps=nbytes / us / 1e3, tflops=flops / us / 1e6, iters=iters)
+    n_seqs, tokens, max_pos = 8, 256, 32768
+    idx = IndexerState(pool, n_seqs, max_pos)
+    raw = torch.randn((n_seqs, tokens, IDX_DIM), generator=gen, device="cuda")
+    gamma = torch.ones(IDX_DIM, device="cuda")
+    half = 32
+    ang = torch.arange(max_pos, device="cuda", dtype=torch.float64)[:, None] * (1e7 ** (-torch.arange(half, device="cuda", dtype=torch.float64) / half))[None, :]
+    table = torch.stack([ang.cos(), ang.sin()], dim=-1).reshape(max_pos, 2 * half).float().contiguous()
+    pos0 = dev_u32(np.full(n_seqs, 16384))
+    us = timed(lambda: idx.append(raw, pos0, 16384 + tokens, gamma, table, 2 * half), iters)
+    pool.check()
+    nbytes = n_seqs * tokens * IDX_DIM * 4 + n_seqs * (tokens // IDX_BLOCK) * IDX_DIM * 4
+    emit(op="idx_pool+idx_tail", case=f"{n_seqs} sequences x {tokens}-token chunk: RMSNorm + rotary + mean of every completed 4-cell block, tail stored",
+         units=n_seqs * tokens, bytes=nbytes, us=us, gbps=nbytes / us / 1e3, iters=iters)
+    pool.release()
+
+
 def bench_movers(iters: int):
     n_layers, n_pages = 12, 4096
     pool = KvPool(0, n_layers, N_KV, HD, n_pages)
@@ -257,7 +295,7 @@ def bench_movers(iters: int):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "prefill", "prepare", "sparse", "topk", "movers"])
+    ap.add_argument("--op", default="all", choices=["all", "prefill", "prepare", "sparse", "topk", "indexer", "movers"])
     ap.add_argument("--iters", type=int, default=20)
     a = ap.parse_args()
     if not torch.cuda.is_available():
@@ -272,6 +310,8 @@ def main():
         bench_sparse(a.iters)
     if a.op in ("all", "topk"):
         bench_topk(a.iters)
+    if a.op in ("all", "indexer"):
+        bench_indexer(a.iters)
     if a.op in ("all", "movers"):
         bench_movers(a.iters)
 

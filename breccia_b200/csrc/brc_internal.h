@@ -19,9 +19,9 @@
 #define BRC_DEV_BAD_SHAPE 8u   // more work units than a kernel's table holds
 
 // brc_pool::status_dev: 64 words of check state, then the decode kernels' per-unit arrival counters
-// (2048 words, zero between launches: the kernels reset what they count).
+// (ticket words of the units, never cleared by the kernels: every launch adds a fixed amount per unit).
 #define BRC_STATUS_WORDS 64u
-#define BRC_DONE_BANK_WORDS 2560u  // 2048 unit tickets + 2 x 256 run tickets of the two-level merge
+#define BRC_DONE_BANK_WORDS 4096u  // two ticket words per unit of a layer (2048 units at most)
 #define BRC_DONE_BANKS 64u     // one bank per layer of a decode step whose layers overlap
 #define BRC_DONE_WORDS (BRC_DONE_BANK_WORDS * BRC_DONE_BANKS)
 #define BRC_STATUS_BYTES ((BRC_STATUS_WORDS + BRC_DONE_WORDS) * 4u)
@@ -65,6 +65,10 @@ struct brc_pool {
     alignas(64) CUtensorMap tm_v8;
     alignas(64) CUtensorMap tm_v8_2;
     bool has_tma = false;
+    // decode attention: where every CTA's share of a launch begins (fractions x 2^32, device memory owned by the
+    // library's per-device cache), from the streaming rates measured on this device; NULL = equal shares
+    const uint32_t *cut_prefix = nullptr;
+    std::vector<float> cut_rates;   // the rates behind it, relative to their mean (host copy, for reports)
 
     // per-stage GPU timers (off unless brc_timing_enable)
     bool timing = false;
@@ -175,6 +179,7 @@ struct brc_layers_args {
     uint64_t kv_layer_stride_bytes = 0;
     const brc_push_args *push = nullptr;
 };
+void brc_decode_calibrate(brc_pool *pool);
 brc_status brc_decode_layers(brc_pool *pool, const char *who, const brc_layers_args &args, void *stream);
 uint32_t brc_decode_kvb(const brc_pool *pool);   // kv heads that travel together in one unit (1 or 2)
 

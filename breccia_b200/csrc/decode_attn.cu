@@ -8,8 +8,9 @@
 //
 //   * work unit = (sequence, group of KVB kv heads); KVB = 2 when the number of kv heads is even, so a
 //     page's rows of two neighbouring kv heads (contiguous in the pool) travel together.  The pages of
-//     all units form one flat list of "page-units", cut into equal contiguous shares, one per CTA
-//     (one CTA per SM), so every SM streams the same number of tiles whatever the length distribution;
+//     all units form one flat list of "page-units", cut into contiguous shares of equal cost, one per CTA
+//     (one CTA per SM; cost = pages plus a surcharge per unit touched), so every SM is busy for the same
+//     time whatever the length distribution;
 //   * a producer warp walks the block table and issues, per page-unit, one TMA tiled load per
 //     64-column group: a 3-D box [64 columns][16 KVB rows][K|V] over a view that spans the K and the
 //     V pool (128-byte swizzle), 8 KiB per operation at KVB = 2.  Measured on B200, a TMA operation
@@ -23,24 +24,31 @@
 //     operand, and O^T[head_dim x 8 heads] += V^T . P^T with V^T fragments from ldmatrix.trans.  P is
 //     split into a binary16 head and tail so the product carries ~22 significant bits;
 //   * at the end of a unit's share the warps merge (m, l, O) per kv head through shared memory, write
-//     one partial per kv head and take a ticket on the unit; the CTA that takes a unit's last ticket
-//     merges all of its partials (log-sum-exp), normalises, applies the gate and writes the output
-//     rows.  No CTA ever waits for another, and there is no second kernel;
+//     one partial per kv head and add one to the unit's ticket.  When a CTA has streamed all of its share
+//     it merges the units it holds pieces of TOGETHER with the other CTAs that hold pieces of them: each
+//     waits (bounded) until the ticket shows every piece written and takes an equal run of the unit's
+//     (row, column) items - log-sum-exp weights, normalisation, gate, output rows.  The pieces of a unit
+//     complete at the same moment (the end of their CTAs' streaming), so the merge costs a few trips to
+//     L2 however many CTAs a unit spans.  The launch is cooperative (all CTAs resident), and there is no
+//     second kernel;
 //   * a decode step's KV append can ride along: the CTA that is about to stream the page holding a
 //     sequence's newest cell first writes that cell (same encoding and address rule as the append
 //     kernel), fenced against its own TMA read;
 //   * one launch can cover several layers: the flat list then runs over (layer, unit, page) and is cut
 //     into the same equal shares, so the launch ramp, the schedule scan and the tail are paid once per
 //     decode token instead of once per layer, and most units lie inside one CTA's share;
-//   * split-KV across GPUs rides in the same launch: the CTA that completes a unit stores the merged
+//   * split-KV across GPUs rides in the same launch: the CTAs that merge a unit store its merged
 //     (acc, m, l) into this rank's slot of every peer's receive buffer with plain global stores over
-//     NVLink and releases one flag per (unit, peer); the CTA that owns the unit's last page waits
-//     (bounded) for all ranks' flags after it has finished streaming, merges and writes the output, so a
-//     layer's exchange overlaps the streaming of the layers behind it.  No load targets peer memory.
+//     NVLink, and the last of them releases one flag per (unit, peer); the same CTAs then wait (bounded)
+//     for all ranks' flags, merge the ranks' rows and write the output, so a layer's exchange overlaps
+//     the streaming of the layers behind it.  No load targets peer memory.
 //
 // HBM-bound by design: 8 FLOP per cached byte, all of it on the tensor pipe.
 #include <algorithm>
+#include <cmath>
 #include <cstdlib>
+#include <mutex>
+#include <vector>
 
 #include "brc_device.cuh"
 #include "brc_internal.h"
@@ -91,7 +99,7 @@ struct DecodeParams {
     const uint32_t *seq_lens;      // [n_seqs]
     float *part_acc;               // [slots][KVB][GROUP_TILE][HD]
     float *part_ml;                // [slots][KVB][GROUP_TILE][2]
-    uint32_t *done;                // [n_units] shares of a unit completed so far (zero between launches)
+    uint32_t *done;                // [layer bank][2][2048] ticket words of the units (see TICKET_ALL)
     float *out;                    // final [n_seqs][n_head][HD]; partial mode: merged acc, same shape
     float *out_ml;                 // partial mode: [n_seqs][n_head][2] (m, l); nullptr = final output
     const float *gate;             // nullable
@@ -130,6 +138,7 @@ struct DecodeParams {
     uint32_t *fin_ticket;          // CTAs of this launch that have finished
     uint64_t wait_ns;
     uint32_t unit_cost;            // page-units charged per unit with pages when the list is cut into shares
+    const uint32_t *cut_prefix;    // nullable: [CTAs] where CTA i's share begins, as a fraction of the launch's cost x 2^32
 };
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
@@ -213,186 +222,263 @@ __device__ __forceinline__ uint64_t push_ml_off(const DecodeParams &p, uint32_t 
     return (uint64_t)bank * p.bank_stride + (uint64_t)src * p.slot_stride + ((size_t)p.rows_total * hd + R * 2u) * 4u;
 }
 
-// Log-sum-exp merge of all shares of unit u (every one of them is complete and visible), run by the
-// NW * 32 consumer threads of the CTA that took the unit's last ticket.  Writes the final output
-// rows (normalised, gated) or, in partial mode, the merged (acc, m, l).  Partials come from other SMs:
-// they are read from L2 (ld.global.cg), never from this SM's L1.  Shares are taken COMBINE_CHUNK at a
-// time: their (m, l) go to shared memory in one parallel sweep, one thread per output row turns them
-// into weights, and the accumulation then issues independent 16-byte loads (nothing in the inner loop
-// waits on a previous load).  `sm` is the CTA's merge scratch, free at this point.
-constexpr uint32_t COMBINE_CHUNK = 32;
-constexpr uint32_t TWO_LEVEL_MIN = 24;    // a unit over more shares than this is merged in two levels
-constexpr uint32_t MAX_RUN_CTAS = 256;    // run tickets: 2 words per CTA after the MAX_UNITS unit tickets
+// Ticket word of a unit: the CTA that has written piece j of the unit's k pieces adds piece_weight(j, k); the
+// weights of a unit's pieces add up to exactly 2^16 and no smaller group of them does, so the low 16 bits are zero
+// exactly when no piece or every piece is written - and a CTA that has added its own weight can only see the
+// second.  Nothing is ever cleared: every launch adds 2^16 per unit it streams, whatever k is this time (the
+// high bits count launches and wrap harmlessly).  A second word per unit (TICKET_PUSHED words further on) counts
+// the same way the CTAs that have stored their part of the unit's merged rows to the peers (split-KV across GPUs).
+constexpr uint32_t TICKET_ALL = 1u << 16, TICKET_LOW = TICKET_ALL - 1u;
+constexpr uint32_t TICKET_PUSHED = 2048u;
 
-//
-// The shares merged are i_lo, i_lo + stride, ... <= i_hi.  With to_slot the merged (acc, m, l) go back
-// into the partial slot of share i_lo instead of the output: that is the first level of the two-level
-// merge of a unit that spans many CTAs (see the ticket code in the kernel).
-//
-// With p.world > 1 the final merge of a unit does not write the output: its (acc, m, l) go into this
-// rank's slot of every rank's receive buffer (its own included), then one flag per rank is released.
+__device__ __forceinline__ uint32_t piece_weight(uint32_t j, uint32_t k) { return ((j + 1u) << 16) / k - (j << 16) / k; }
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *ptr) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+
+// Which of the shares i_lo .. i_hi hold pages (a unit's pieces): k of them, this CTA's is the j-th.  With `dense`
+// no share is empty and the answer is arithmetic.  One thread's view; no shared memory.
+__device__ __forceinline__ void piece_of(const uint32_t *B, bool dense, uint32_t i_lo, uint32_t i_hi, uint32_t &j, uint32_t &k) {
+    if (dense) {
+        k = i_hi - i_lo + 1;
+        j = blockIdx.x - i_lo;
+        return;
+    }
+    uint32_t n = 0, mine = 0;
+    for (uint32_t i = i_lo; i <= i_hi; ++i)
+        if (B[i] != B[i + 1]) {
+            if (i == blockIdx.x) mine = n;
+            ++n;
+        }
+    j = mine;
+    k = n;
+}
+
+// The same for a whole CTA, plus list[0 .. k) in shared memory: the CTAs that hold the pieces.
+__device__ __forceinline__ void unit_pieces(const uint32_t *B, bool dense, uint32_t i_lo, uint32_t i_hi, uint32_t tid, uint32_t n_threads,
+                                            uint16_t *list, volatile uint32_t *jk, uint32_t &j, uint32_t &k) {
+    if (dense) {
+        k = i_hi - i_lo + 1;
+        j = blockIdx.x - i_lo;
+        for (uint32_t t = tid; t < k; t += n_threads) list[t] = (uint16_t)(i_lo + t);
+        return;   // the caller's next barrier publishes the list
+    }
+    if (tid == 0) {
+        uint32_t n = 0, mine = 0;
+        for (uint32_t i = i_lo; i <= i_hi; ++i)
+            if (B[i] != B[i + 1]) {
+                if (i == blockIdx.x) mine = n;
+                list[n++] = (uint16_t)i;
+            }
+        jk[0] = mine;
+        jk[1] = n;
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(n_threads) : "memory");
+    j = jk[0];
+    k = jk[1];
+}
+
+// One merged row segment (row `row` of the unit, columns d .. d + 3) goes out: normalised and gated, or in partial
+// mode as the merged (acc, m, l), or with p.world > 1 into this rank's slot of every rank's receive buffer.
+template <int HD, int KVB, bool CAN_PUSH>
+__device__ __forceinline__ void merge_emit(const DecodeParams &p, const UnitRef ur, uint32_t s, uint32_t kv0, uint32_t row, uint32_t d,
+                                           float2 ml, float4 acc, uint32_t bank) {
+    const uint32_t k2 = row / p.group, h = row - k2 * p.group;
+    const uint32_t head = (kv0 + k2) * p.group_all + p.head0 + h;
+    const size_t o = ur.layer * p.out_layer_stride + ((size_t)s * p.n_head + head) * HD + d;
+    if (CAN_PUSH && p.world > 1) {
+        const size_t R = ((size_t)ur.layer * p.n_seqs + s) * p.n_head + head;
+        const uint64_t oa = push_acc_off(p, bank, p.rank, R, HD, d), om = push_ml_off(p, bank, p.rank, R, HD);
+        for (uint32_t r = 0; r < p.world; ++r) {
+            *reinterpret_cast<float4 *>(p.peer_recv[r] + oa) = acc;
+            if (d == 0) *reinterpret_cast<float2 *>(p.peer_recv[r] + om) = ml;
+        }
+    } else if (p.out_ml) {
+        *reinterpret_cast<float4 *>(p.out + o) = acc;
+        if (d == 0) {
+            float *om = p.out_ml + ur.layer * p.out_ml_layer_stride + ((size_t)s * p.n_head + head) * 2;
+            om[0] = ml.x;
+            om[1] = ml.y;
+        }
+    } else {
+        const float inv = ml.y > 0.f ? 1.f / ml.y : 0.f;
+        float4 r = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        if (p.gate) {
+            const float *gt = p.gate + ur.layer * p.gate_layer_stride + ((size_t)s * p.n_head + head) * p.gate_head_stride + d;
+            r.x *= sigmoid_f32(gt[0]);
+            r.y *= sigmoid_f32(gt[1]);
+            r.z *= sigmoid_f32(gt[2]);
+            r.w *= sigmoid_f32(gt[3]);
+        }
+        *reinterpret_cast<float4 *>(p.out + o) = r;
+    }
+}
+
+// What one CTA does of a unit's merge once every piece is written: items it0 .. it0 + items_c - 1, k pieces.
+// The code runs once per CTA, from a cold instruction cache (unrolled over registers it took 13 us where this
+// takes 2): small rolled loops.  All of the CTA's accumulator segments - items_c x k, 32 KiB at most - are
+// copied into `stage` (the ring's shared memory, idle once the CTA has streamed its share) with 16-byte
+// asynchronous copies, [piece][item], together with the (m, l) sweep: one trip to L2 for everything.  Then the
+// weights (one warp per row) and the sums: 2^lg threads per item (within a warp), each taking every 2^lg-th
+// piece, a shuffle reduction, and the segment goes out.
+template <int HD, int KVB, bool CAN_PUSH, int NT>
+__device__ __forceinline__ void merge_items(const DecodeParams &p, const UnitRef ur, const uint16_t *list, float2 *mls, float2 *rowml,
+                                            float4 *stage, uint32_t it0, uint32_t items_c, uint32_t k, uint32_t tid, uint32_t s,
+                                            uint32_t kv0, uint32_t bank) {
+    constexpr uint32_t TPR = HD / 4;
+    constexpr int NW = NT / 32;
+    const uint32_t lane = tid & 31u, warp = tid >> 5;
+    const uint32_t r0 = it0 / TPR, nr = (it0 + items_c - 1) / TPR - r0 + 1;
+    // ---- accumulator segments, stage[pc * items_c + il], and the (m, l) of this CTA's rows from every piece: every
+    //      thread an equal number of copies, all in flight together
+    for (uint32_t idx = tid; idx < k * items_c; idx += NT) {
+        const uint32_t pc = idx / items_c, il = idx - pc * items_c;
+        const uint32_t item = it0 + il, row = item / TPR, d = (item - row * TPR) * 4u;
+        const uint32_t k2 = row / p.group, h = row - k2 * p.group;
+        const float *src = p.part_acc + (((size_t)(ur.U + list[pc]) * KVB + k2) * GROUP_TILE + h) * HD + d;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(brc::smem_u32(stage + idx)), "l"(src) : "memory");
+    }
+    for (uint32_t idx = tid; idx < nr * k; idx += NT) {
+        const uint32_t rl = idx / k, pc = idx - rl * k, row = r0 + rl;
+        const uint32_t k2 = row / p.group, h = row - k2 * p.group;
+        const float *src = p.part_ml + (((size_t)(ur.U + list[pc]) * KVB + k2) * GROUP_TILE + h) * 2;
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(brc::smem_u32(mls + idx)), "l"(src) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    brc::named_bar_sync(1, NT);
+    // ---- weights 2^(m - M): one warp per row
+    for (uint32_t rl = warp; rl < nr; rl += NW) {
+        float M = -INFINITY;
+        for (uint32_t pc = lane; pc < k; pc += 32) {
+            const float2 ml = mls[rl * k + pc];
+            if (ml.y > 0.f) M = fmaxf(M, ml.x);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+        float L = 0.f;
+        for (uint32_t pc = lane; pc < k; pc += 32) {
+            const float2 ml = mls[rl * k + pc];
+            const float w = ml.y > 0.f ? exp2f(ml.x - M) : 0.f;
+            mls[rl * k + pc].x = w;
+            L += w * ml.y;
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
+        if (lane == 0) rowml[rl] = make_float2(M, L);
+    }
+    brc::named_bar_sync(1, NT);
+    // ---- weighted sums and the segments (the same trip counts for every thread: the shuffles are warp-wide)
+    uint32_t lg = 0;                                     // 2^lg threads per item: as many as leave every item a thread
+    while (lg < 5u && (items_c << (lg + 1)) <= NT) ++lg;
+    const uint32_t g = 1u << lg, per_round = NT >> lg, grp = tid & (g - 1u), slot = tid >> lg;
+    for (uint32_t base = 0; base < items_c; base += per_round) {
+        const uint32_t il = base + slot;
+        const bool act = il < items_c;
+        const uint32_t ilc = min(il, items_c - 1u);
+        const uint32_t item = it0 + ilc, row = item / TPR, d = (item - row * TPR) * 4u;
+        const float2 *wrow = mls + (row - r0) * k;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t pc = grp; pc < k; pc += g) {
+            const float4 v = stage[pc * items_c + ilc];
+            const float wt = wrow[pc].x;
+            acc.x += wt * v.x;
+            acc.y += wt * v.y;
+            acc.z += wt * v.z;
+            acc.w += wt * v.w;
+        }
+        for (uint32_t off = g >> 1; off > 0; off >>= 1) {
+            acc.x += __shfl_xor_sync(0xffffffffu, acc.x, off);
+            acc.y += __shfl_xor_sync(0xffffffffu, acc.y, off);
+            acc.z += __shfl_xor_sync(0xffffffffu, acc.z, off);
+            acc.w += __shfl_xor_sync(0xffffffffu, acc.w, off);
+        }
+        if (act && grp == 0u) merge_emit<HD, KVB, CAN_PUSH>(p, ur, s, kv0, row, d, rowml[row - r0], acc, bank);
+    }
+}
+
+// Log-sum-exp merge of the pieces of unit `ur`, done by the CTAs that streamed one of them (all but the holder of
+// the last piece), each with its NW * 32 consumer threads once its own streaming is over: the unit's (row,
+// 16-byte column) items are dealt over those CTAs in equal runs, so whatever the number of pieces k, a CTA reads
+// one or two pieces' worth of partials and the merge takes two trips to L2 instead of one per four pieces
+// through a single SM.  (All pieces of a unit but its last complete at the end of their CTAs' streaming, i.e. at
+// the same time, and those CTAs have nothing else left to do; a trip to L2 costs 1.5-3 us while other CTAs
+// still stream, and the last arriver merging alone took 7-11 us with 5-10 pieces and 40 us with 148.)  The CTA
+// first waits, with a time limit, until the unit's ticket shows every piece written (unless its own ticket
+// was the last: `all_written`, thread 0's knowledge); the launch is
+// cooperative, so all CTAs are resident and the pieces it waits for are being produced.  Then merge_items.
+// With p.world > 1 the CTA that stores last releases one flag per rank.  Partials come from other SMs: they
+// are read from L2 (.cg).  `sm` is the CTA's merge scratch and `stage` the ring, both free at this point.
 template <int HD, int KVB, bool CAN_PUSH, bool VQ8>
-__device__ __forceinline__ void combine_unit(const DecodeParams &p, const UnitRef ur, uint32_t i_lo, uint32_t i_hi, uint32_t stride,
-                                             bool to_slot, const uint32_t *B, bool dense, uint32_t tid, float *sm, uint32_t epoch, uint32_t bank) {
+__device__ __forceinline__ void merge_unit(const DecodeParams &p, const UnitRef ur, uint32_t i_lo, uint32_t i_hi, const uint32_t *B,
+                                           bool dense, uint32_t tid, float *sm, float4 *stage, uint32_t epoch, uint32_t bank,
+                                           volatile uint32_t *gave_up, bool all_written) {
     constexpr int NW = consumer_warps(VQ8);
-    const uint32_t u = ur.u;
-    constexpr uint32_t TPR = HD / 4;                    // threads per output row (float4 each)
-    constexpr uint32_t ROWS_PER_PASS = (NW * 32) / TPR;
-    constexpr uint32_t MAX_ROWS = KVB * GROUP_TILE;
-    constexpr uint32_t PASSES = (MAX_ROWS + ROWS_PER_PASS - 1) / ROWS_PER_PASS;
+    constexpr uint32_t NT = NW * 32;
+    constexpr uint32_t TPR = HD / 4;                    // 16-byte columns of a row
     const uint32_t n_rows = KVB * p.group;              // (kv head of the unit, query head)
+    const uint32_t n_items = n_rows * TPR;
     const uint32_t n_groups = p.n_kv_head / KVB;
-    const uint32_t s = u / n_groups, kv0 = (u % n_groups) * KVB;
-    const uint32_t d = (tid % TPR) * 4;
+    const uint32_t s = ur.u / n_groups, kv0 = (ur.u % n_groups) * KVB;
 
-    uint32_t *list = reinterpret_cast<uint32_t *>(sm);                        // [COMBINE_CHUNK] share (CTA) ids
-    uint32_t *n_list = list + COMBINE_CHUNK;                                  // [1] (+ padding)
-    float2 *mls = reinterpret_cast<float2 *>(list + COMBINE_CHUNK + 8);       // [COMBINE_CHUNK][MAX_ROWS]
-    float *wsm = reinterpret_cast<float *>(mls + COMBINE_CHUNK * MAX_ROWS);   // [COMBINE_CHUNK][MAX_ROWS]
-    float *row_scale = wsm + COMBINE_CHUNK * MAX_ROWS;                        // [MAX_ROWS] rescale of what is held
+    uint16_t *list = reinterpret_cast<uint16_t *>(sm);                           // [MAX_CTAS] CTAs that hold a piece
+    volatile uint32_t *jk = reinterpret_cast<volatile uint32_t *>(list + MAX_CTAS);   // [4]
+    float2 *rowml = reinterpret_cast<float2 *>(const_cast<uint32_t *>(jk) + 4);   // [<= n_rows] merged (m, l) of this CTA's rows
+    float2 *mls = rowml + KVB * GROUP_TILE;                                      // [rows of this CTA][k]: (m, l), then (weight, l)
 
-    float4 acc[PASSES];
-#pragma unroll
-    for (uint32_t ps = 0; ps < PASSES; ++ps) acc[ps] = make_float4(0.f, 0.f, 0.f, 0.f);
-    float M = -INFINITY, L = 0.f;                        // of row `tid`, held by threads tid < n_rows
-
-    for (uint32_t i0 = i_lo; i0 <= i_hi;) {
-        // ---- the next chunk of non-empty shares
-        uint32_t i_next;
-        if (dense) {
-            const uint32_t n = min(COMBINE_CHUNK, (i_hi - i0) / stride + 1);
-            if (tid < n) list[tid] = i0 + tid * stride;
-            if (tid == 0) n_list[0] = n;
-            i_next = i0 + n * stride;
-        } else {
-            if (tid == 0) {
-                uint32_t n = 0, i = i0;
-                for (; i <= i_hi && n < COMBINE_CHUNK; ++i)
-                    if (B[i] != B[i + 1]) list[n++] = i;
-                n_list[0] = n;
-                n_list[1] = i;
-            }
-            i_next = 0;
-        }
-        brc::named_bar_sync(1, NW * 32);
-        const uint32_t n = n_list[0];
-        if (!dense) i_next = n_list[1];
-        // ---- (m, l) of every (share, row), one load per thread per sweep
-        for (uint32_t idx = tid; idx < n * n_rows; idx += NW * 32) {
-            const uint32_t pc = idx / n_rows, row = idx % n_rows;
-            const uint32_t k2 = row / p.group, h = row % p.group;
-            mls[pc * MAX_ROWS + row] =
-                __ldcg(reinterpret_cast<const float2 *>(p.part_ml + (((size_t)(ur.U + list[pc]) * KVB + k2) * GROUP_TILE + h) * 2));
-        }
-        brc::named_bar_sync(1, NW * 32);
-        // ---- weights: thread = row
-        if (tid < n_rows) {
-            float Mc = M;
-            for (uint32_t pc = 0; pc < n; ++pc) {
-                const float2 ml = mls[pc * MAX_ROWS + tid];
-                if (ml.y > 0.f) Mc = fmaxf(Mc, ml.x);
-            }
-            const float keep = (L > 0.f) ? exp2f(M - Mc) : 0.f;   // rescale of what earlier chunks gave
-            L *= keep;
-            for (uint32_t pc = 0; pc < n; ++pc) {
-                const float2 ml = mls[pc * MAX_ROWS + tid];
-                const float w = ml.y > 0.f ? exp2f(ml.x - Mc) : 0.f;
-                wsm[pc * MAX_ROWS + tid] = w;
-                L += w * ml.y;
-            }
-            M = Mc;
-            row_scale[tid] = keep;
-        }
-        brc::named_bar_sync(1, NW * 32);
-        // ---- accumulate: every row pass of four shares at a time, i.e. 4 * PASSES independent 16-byte
-        //      loads in flight per thread before anything is consumed (the partials sit in L2)
-#pragma unroll
-        for (uint32_t ps = 0; ps < PASSES; ++ps) {
-            const uint32_t row = min(ps * ROWS_PER_PASS + tid / TPR, n_rows - 1);
-            const float keep = row_scale[row];
-            acc[ps].x *= keep;
-            acc[ps].y *= keep;
-            acc[ps].z *= keep;
-            acc[ps].w *= keep;
-        }
-        for (uint32_t pc0 = 0; pc0 < n; pc0 += 4) {
-            float4 a[PASSES][4];
-#pragma unroll
-            for (uint32_t ps = 0; ps < PASSES; ++ps) {
-                const uint32_t row = min(ps * ROWS_PER_PASS + tid / TPR, n_rows - 1);   // clamped rows are not stored
-                const uint32_t k2 = row / p.group, h = row % p.group;
-#pragma unroll
-                for (uint32_t j = 0; j < 4; ++j) {
-                    const uint32_t pc = min(pc0 + j, n - 1);                            // clamped shares get weight 0
-                    a[ps][j] = __ldcg(reinterpret_cast<const float4 *>(
-                        p.part_acc + (((size_t)(ur.U + list[pc]) * KVB + k2) * GROUP_TILE + h) * HD + d));
-                }
-            }
-#pragma unroll
-            for (uint32_t ps = 0; ps < PASSES; ++ps) {
-                const uint32_t row = min(ps * ROWS_PER_PASS + tid / TPR, n_rows - 1);
-#pragma unroll
-                for (uint32_t j = 0; j < 4; ++j) {
-                    const float w = pc0 + j < n ? wsm[(pc0 + j) * MAX_ROWS + row] : 0.f;
-                    acc[ps].x += w * a[ps][j].x;
-                    acc[ps].y += w * a[ps][j].y;
-                    acc[ps].z += w * a[ps][j].z;
-                    acc[ps].w += w * a[ps][j].w;
-                }
+    brc::named_bar_sync(1, NT);                          // the scratch is free (previous unit's merge, or the epilogue)
+    uint32_t j, k;
+    unit_pieces(B, dense, i_lo, i_hi, tid, NT, list, jk, j, k);
+    uint32_t *const ticket = p.done + ur.layer * BRC_DONE_BANK_WORDS + ur.u;
+    // The CTA that holds a unit's LAST piece streamed it first thing and has another unit's merge to attend to at
+    // its own end: the unit's other CTAs (all of them at the end of their streaming) share the merge among them.
+    if (k > 1u && j == k - 1u) return;                   // CTA-uniform
+    const uint32_t n_part = k > 1u ? k - 1u : 1u;        // CTAs that take part
+    // ---- every piece written?  (this CTA's own weight is in: zero low bits mean all of them)
+    if (tid == 0 && !gave_up[0]) {
+        bool ok = all_written;                           // thread 0 took the unit's last ticket itself: nothing to wait for
+        if (!ok) ok = (ld_acquire_gpu(ticket) & TICKET_LOW) == 0u;
+        if (!ok) {
+            const uint64_t t0 = globaltimer_ns();
+            for (uint32_t i = 0; i < (1u << 30); ++i) {
+                if ((ld_acquire_gpu(ticket) & TICKET_LOW) == 0u) { ok = true; break; }
+                if ((i & 63u) == 63u && globaltimer_ns() - t0 > WAIT_NS) break;
             }
         }
-        brc::named_bar_sync(1, NW * 32);   // the lists are rewritten by the next chunk
-        i0 = i_next;
-    }
-    // ---- rows' (M, L) to everyone, then the output
-    if (tid < n_rows) {
-        mls[tid] = make_float2(M, L);
-    }
-    brc::named_bar_sync(1, NW * 32);
-#pragma unroll
-    for (uint32_t ps = 0; ps < PASSES; ++ps) {
-        const uint32_t row = ps * ROWS_PER_PASS + tid / TPR;
-        if (row >= n_rows) continue;
-        const uint32_t k2 = row / p.group, h = row % p.group;
-        const float2 ml = mls[row];
-        const uint32_t head = (kv0 + k2) * p.group_all + p.head0 + h;
-        const size_t o = ur.layer * p.out_layer_stride + ((size_t)s * p.n_head + head) * HD + d;
-        if (to_slot) {
-            const size_t slot = ((size_t)(ur.U + i_lo) * KVB + k2) * GROUP_TILE + h;
-            *reinterpret_cast<float4 *>(p.part_acc + slot * HD + d) = acc[ps];
-            if (d == 0) *reinterpret_cast<float2 *>(p.part_ml + slot * 2) = ml;
-        } else if (CAN_PUSH && p.world > 1) {
-            const size_t R = ((size_t)ur.layer * p.n_seqs + s) * p.n_head + head;
-            const uint64_t oa = push_acc_off(p, bank, p.rank, R, HD, d), om = push_ml_off(p, bank, p.rank, R, HD);
-            for (uint32_t r = 0; r < p.world; ++r) {
-                *reinterpret_cast<float4 *>(p.peer_recv[r] + oa) = acc[ps];
-                if (d == 0) *reinterpret_cast<float2 *>(p.peer_recv[r] + om) = ml;
-            }
-        } else if (p.out_ml) {
-            *reinterpret_cast<float4 *>(p.out + o) = acc[ps];
-            if (d == 0) {
-                float *om = p.out_ml + ur.layer * p.out_ml_layer_stride + ((size_t)s * p.n_head + head) * 2;
-                om[0] = ml.x;
-                om[1] = ml.y;
-            }
-        } else {
-            const float inv = ml.y > 0.f ? 1.f / ml.y : 0.f;
-            float4 r = make_float4(acc[ps].x * inv, acc[ps].y * inv, acc[ps].z * inv, acc[ps].w * inv);
-            if (p.gate) {
-                const float *g = p.gate + ur.layer * p.gate_layer_stride + ((size_t)s * p.n_head + head) * p.gate_head_stride + d;
-                r.x *= sigmoid_f32(g[0]);
-                r.y *= sigmoid_f32(g[1]);
-                r.z *= sigmoid_f32(g[2]);
-                r.w *= sigmoid_f32(g[3]);
-            }
-            *reinterpret_cast<float4 *>(p.out + o) = r;
+        if (!ok) {
+            gave_up[0] = 1u;
+            atomicOr(p.status, BRC_DEV_WAIT_LIMIT);
+            p.status[1] = 4000000u + blockIdx.x;   // a piece of the unit was never written
+            p.status[2] = ur.U;
         }
     }
-    if (CAN_PUSH && !to_slot && p.world > 1) {
-        // every thread's stores are ordered at system scope before the flags go out
-        __threadfence_system();
-        brc::named_bar_sync(1, NW * 32);
-        if (tid < p.world) st_release_sys(unit_flag(p.peer_recv[tid], p, bank, p.rank, ur.U), epoch);
+    brc::named_bar_sync(1, NT);
+    if (gave_up[0]) return;                              // nobody clears the flag: every later wait of this CTA is skipped too
+
+    const uint32_t it0 = (uint32_t)((uint64_t)j * n_items / n_part), it1 = (uint32_t)((uint64_t)(j + 1) * n_items / n_part);
+    const uint32_t items_c = it1 - it0;
+    if (items_c != 0) {
+        merge_items<HD, KVB, CAN_PUSH, NT>(p, ur, list, mls, rowml, stage, it0, items_c, k, tid, s, kv0, bank);
+    }
+    if (CAN_PUSH && p.world > 1) {
+        // ---- across GPUs: the CTA whose stores land last tells the peers (the pattern of a grid-wide barrier: a CTA
+        //      barrier, then one thread fences - at system scope, the stores went to peers - and counts)
+        brc::named_bar_sync(1, NT);
+        if (tid == 0) {
+            __threadfence_system();
+            const uint32_t w = piece_weight(j, n_part);
+            const uint32_t old = atomicAdd(ticket + TICKET_PUSHED, w);
+            const bool last = ((old + w) & TICKET_LOW) == 0u;
+            if (last) __threadfence_system();
+            jk[2] = last;
+        }
+        brc::named_bar_sync(1, NT);
+        // one thread per peer: a release store waits for the thread's earlier stores to that scope, so one thread
+        // storing to the peers in turn would pay a trip over NVLink per peer
+        if (jk[2] && tid < p.world) st_release_sys(unit_flag(p.peer_recv[tid], p, bank, p.rank, ur.U), epoch);
     }
 }
 
@@ -590,7 +676,9 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
         for (uint32_t i = tid; i <= gridDim.x; i += NTHREADS) {
             uint32_t at = total;
             if (i < gridDim.x && total != 0) {
-                const uint64_t t = cost * i / gridDim.x;
+                // equal shares of the cost, or shares in proportion to the measured streaming rate of the CTAs' SMs
+                const uint64_t f = p.cut_prefix ? p.cut_prefix[i] : 0;
+                const uint64_t t = p.cut_prefix ? (cost >> 32) * f + (((cost & 0xffffffffull) * f) >> 32) : cost * i / gridDim.x;
                 const uint32_t l = (uint32_t)(t / cost_l);
                 const uint32_t tl = (uint32_t)(t - (uint64_t)l * cost_l);
                 uint32_t lo = 0, hi = n_units;          // largest u with S[u] + E * nz[u] <= tl: a unit with pages
@@ -810,6 +898,7 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
         u = unit_of(S, n_units, a - layer * total_l);
     }
     const uint32_t first_layer = layer, first_u = u;
+    uint32_t tk_unit = 0xffffffffu, tk_sum = 1u;   // thread 0: the unit it last took a ticket of, and the ticket's value then
     uint32_t g0 = a;
     while (g0 < b) {
         const uint32_t lbase = layer * total_l;     // first page-unit of this layer in the flat list
@@ -1110,71 +1199,19 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
                     }
                 }
             }
-            if (!whole && hf == 1) __threadfence();  // publish this thread's partial (both halves) before the unit's ticket is taken
             brc::named_bar_sync(1, NW * 32);
         }
-        if (!whole) {
-            // ---- ticket: the CTA that completes the last share of a unit combines all of its shares
-            uint32_t i_lo, i_hi;
+        if (!whole && tid == 0) {
+            // ---- ticket: this piece of the unit is written.  The barrier above ordered every thread's stores before
+            //      this thread's fence (the pattern of a grid-wide barrier).  What the add returns says whether this
+            //      was the unit's last piece to arrive: remembered for the merge of the share's last unit.
+            uint32_t i_lo, i_hi, j, k;
             share_range(B, gridDim.x, unit_first, lbase + S[u + 1] - 1, i_lo, i_hi);
-            uint32_t *const unit_ticket = p.done + layer * BRC_DONE_BANK_WORDS + u;
-            // A unit that spans many CTAs (one long sequence alone on the GPU spans all of them) is merged
-            // in two levels, or its last arriver would pull every share through one SM: runs of `fan`
-            // consecutive shares have a ticket of their own, the run's last arriver merges the run into the
-            // slot of its first share, and the last run to finish merges the runs.
-            const uint32_t span = i_hi - i_lo + 1;
-            const bool two_level = all_shares_live && span > TWO_LEVEL_MIN && gridDim.x <= MAX_RUN_CTAS;
-            if (!two_level) {
-                if (tid == 0) {
-                    uint32_t pieces = span;
-                    if (!all_shares_live) {   // few page-units: some shares in between may be empty
-                        pieces = 0;
-                        for (uint32_t i = i_lo; i <= i_hi; ++i) pieces += B[i] != B[i + 1];
-                    }
-                    const uint32_t ticket = atomicAdd(unit_ticket, 1u);
-                    const uint32_t last = ticket + 1u == pieces;
-                    if (last) *unit_ticket = 0;   // every share has arrived: leave the counter clean for the next launch
-                    flags[0] = last;
-                }
-                brc::named_bar_sync(1, NW * 32);
-                if (flags[0]) {
-                    __threadfence();
-                    combine_unit<HD, KVB, !WHOLE_FAST, VQ8>(p, ur, i_lo, i_hi, 1, false, B, all_shares_live, tid, scratch, epoch, bank);
-                }
-            } else {
-                uint32_t fan = 1;
-                while (fan * fan < span) ++fan;                 // ~sqrt: both levels merge about as many
-                const uint32_t run = (blockIdx.x - i_lo) / fan;
-                const uint32_t r_lo = i_lo + run * fan, r_hi = min(r_lo + fan - 1, i_hi);
-                if (tid == 0) {
-                    // Runs of neighbouring units can start on the same CTA only as (last run of one unit,
-                    // first run of the next): the second word of the pair keeps those apart.
-                    uint32_t *cnt = p.done + MAX_UNITS + 2u * r_lo + (run != 0u);
-                    const uint32_t ticket = atomicAdd(cnt, 1u);
-                    const uint32_t last = ticket + 1u == r_hi - r_lo + 1u;
-                    if (last) *cnt = 0;
-                    flags[0] = last;
-                }
-                brc::named_bar_sync(1, NW * 32);
-                if (flags[0]) {
-                    __threadfence();
-                    combine_unit<HD, KVB, !WHOLE_FAST, VQ8>(p, ur, r_lo, r_hi, 1, true, B, all_shares_live, tid, scratch, epoch, bank);
-                    __threadfence();   // the run's merged partial is visible before the unit's ticket is taken
-                    brc::named_bar_sync(1, NW * 32);
-                    if (tid == 0) {
-                        const uint32_t ticket = atomicAdd(unit_ticket, 1u);
-                        const uint32_t last = ticket + 1u == (span + fan - 1u) / fan;
-                        if (last) *unit_ticket = 0;
-                        flags[0] = last;
-                    }
-                    brc::named_bar_sync(1, NW * 32);
-                    if (flags[0]) {
-                        __threadfence();
-                        combine_unit<HD, KVB, !WHOLE_FAST, VQ8>(p, ur, i_lo, i_hi, fan, false, B, all_shares_live, tid, scratch, epoch, bank);
-                    }
-                }
-            }
-            brc::named_bar_sync(1, NW * 32);
+            piece_of(B, all_shares_live, i_lo, i_hi, j, k);
+            __threadfence();
+            const uint32_t w = piece_weight(j, k);
+            tk_sum = atomicAdd(p.done + layer * BRC_DONE_BANK_WORDS + u, w) + w;   // not waited for until the merges
+            tk_unit = ur.U;
         }
 
         // ---- next unit of the flat (layer, unit) list that has pages
@@ -1190,25 +1227,46 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
         }
     }
 
-    if (!push) return;
-    // ---------------------------------------------------------------------- cross-rank merge
-    // The rows of a unit are dealt over the CTAs that streamed a share of it (with fewer page-units than
-    // CTAs some shares in between are empty: the CTA that holds the unit's last page then takes them all);
-    // units without pages go round the grid.  All of this CTA's streaming and local merging is done, so
-    // waiting here holds nothing else up; the ranks that still stream never wait for this one.
+    // ---------------------------------------------------------------------- merges
+    // Every unit of which this CTA streamed a share that is not the whole unit (at most the first and the last unit
+    // of its share, when no share is empty) is merged now, together with the other CTAs that hold shares of it.
+    // All of this CTA's streaming is done and all of its shares are written, so waiting here holds nothing up
+    // and no CTA waits for one that waits for it.
     if (a < b) {
         uint32_t fl = first_layer, fu = first_u;
         while (fl < p.n_layers) {
             const uint32_t ubeg = fl * total_l + S[fu], uend = fl * total_l + S[fu + 1];   // [ubeg, uend): the unit's page-units
             if (ubeg >= b) break;
-            if (uend != ubeg) {
+            if (uend != ubeg && !(WHOLE_FAST && ubeg >= a && uend <= b)) {
                 const UnitRef ur = {fl * n_units + fu, fl, fu};
                 uint32_t i_lo, i_hi;
                 share_range(B, gridDim.x, ubeg, uend - 1, i_lo, i_hi);
-                if (all_shares_live)
-                    finalize_unit<HD, KVB, VQ8>(p, ur, blockIdx.x - i_lo, i_hi - i_lo + 1, epoch, bank, tid, gave_up);
-                else if (blockIdx.x == i_hi)
-                    finalize_unit<HD, KVB, VQ8>(p, ur, 0, 1, epoch, bank, tid, gave_up);
+                merge_unit<HD, KVB, !WHOLE_FAST, VQ8>(p, ur, i_lo, i_hi, B, all_shares_live, tid, scratch, reinterpret_cast<float4 *>(ring), epoch, bank,
+                                                      gave_up, tk_unit == ur.U && (tk_sum & TICKET_LOW) == 0u);
+            }
+            if (++fu == n_units) {
+                fu = 0;
+                ++fl;
+            }
+        }
+    }
+    if (!push) return;
+    // ---------------------------------------------------------------------- cross-rank merge
+    // The rows of a unit are dealt over the CTAs that streamed a share of it; units without pages go round the
+    // grid.  The ranks that still stream never wait for this one.
+    if (a < b) {
+        uint32_t fl = first_layer, fu = first_u;
+        while (fl < p.n_layers) {
+            const uint32_t ubeg = fl * total_l + S[fu], uend = fl * total_l + S[fu + 1];
+            if (ubeg >= b) break;
+            if (uend != ubeg) {
+                const UnitRef ur = {fl * n_units + fu, fl, fu};
+                uint32_t i_lo, i_hi, j, k;
+                share_range(B, gridDim.x, ubeg, uend - 1, i_lo, i_hi);
+                brc::named_bar_sync(1, NW * 32);
+                unit_pieces(B, all_shares_live, i_lo, i_hi, tid, NW * 32, reinterpret_cast<uint16_t *>(scratch),
+                            reinterpret_cast<volatile uint32_t *>(reinterpret_cast<uint16_t *>(scratch) + MAX_CTAS), j, k);
+                finalize_unit<HD, KVB, VQ8>(p, ur, j, k, epoch, bank, tid, gave_up);
             }
             if (++fu == n_units) {
                 fu = 0;
@@ -1261,6 +1319,57 @@ __global__ void __launch_bounds__(HD)
 
 #undef all_shares_live
 
+// How fast does each CTA's SM stream from HBM while all the others do too?  The SMs of a B200 do not get equal
+// shares of the memory system (always the same ones are slow, whatever is read), and with equal shares of a
+// 12-layer launch the last CTAs stream for 35 us of 520 after the median one has finished.  One thread per CTA keeps a ring of
+// CAL_STAGES bulk copies of CAL_CHUNK bytes in flight from pseudo-random places in `base` for `window_ns` and
+// counts what has landed; same grid, block size and shared memory as the decode kernel, launched the same
+// way, so that block i lands on the SM that the decode kernel's block i gets on an otherwise idle GPU.
+constexpr uint32_t CAL_CHUNK = 32768, CAL_STAGES = 6;
+
+__global__ void __launch_bounds__(160, 1) stream_rate_kernel(const uint8_t *base, uint32_t n_chunks, uint64_t window_ns, uint32_t *landed,
+                                                             uint32_t *status) {
+    extern __shared__ uint8_t cal_smem_raw[];
+    uint8_t *ring = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(cal_smem_raw) + 1023u) & ~uintptr_t(1023));
+    __shared__ uint64_t bars[CAL_STAGES];
+    if (threadIdx.x != 0) return;
+    const uint32_t bar0 = brc::smem_u32(bars), ring0 = brc::smem_u32(ring);
+    for (uint32_t i = 0; i < CAL_STAGES; ++i) brc::mbar_init(bar0 + 8u * i, 1);
+    brc::mbar_fence_init();
+    uint32_t next = 0, done = 0;
+    auto issue = [&](uint32_t stage) {
+        const uint32_t chunk = (uint32_t)(((uint64_t)blockIdx.x * 7919u + (uint64_t)next * 104729u) % n_chunks);
+        ++next;
+        brc::mbar_arrive_expect_tx(bar0 + 8u * stage, CAL_CHUNK);
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(ring0 + stage * CAL_CHUNK),
+                     "l"(base + (size_t)chunk * CAL_CHUNK), "r"(CAL_CHUNK), "r"(bar0 + 8u * stage)
+                     : "memory");
+    };
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t i = 0; i < CAL_STAGES; ++i) issue(i);
+    uint32_t in_flight = CAL_STAGES, stage = 0, parity = 0;
+    bool counting = true;
+    while (in_flight) {
+        if (!brc::mbar_wait(bar0 + 8u * stage, parity)) {   // bounded: gives up after seconds
+            atomicOr(status, BRC_DEV_WAIT_LIMIT);
+            status[1] = 5000000u + blockIdx.x;
+            break;
+        }
+        --in_flight;
+        counting = counting && globaltimer_ns() - t0 < window_ns;
+        if (counting) {
+            ++done;
+            issue(stage);
+            ++in_flight;
+        }
+        if (++stage == CAL_STAGES) {
+            stage = 0;
+            parity ^= 1u;
+        }
+    }
+    landed[blockIdx.x] = done;
+}
+
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
@@ -1291,6 +1400,97 @@ uint32_t stages_for(uint32_t head_dim, uint32_t kvb, bool v_q8) {
     const uint32_t nwp = (uint32_t)consumer_warps(v_q8) / kvb;
     return fit / nwp * nwp;
 }
+
+}  // namespace
+
+// Shares of a launch's cost per CTA, in proportion to the streaming rates measured by stream_rate_kernel.  OFF unless
+// BRC_DECODE_CALIBRATE=1 is in the environment: measured on B200, the rates differ by -19 .. +16 % between SMs in pure
+// streaming and by about -8 .. +9 % inside the decode kernel, but the launch as a whole is bound by HBM, not by
+// its slowest SM (while the slow CTAs finish alone they stream faster), so shares in proportion to a quarter of
+// the measured deviation bought 0.7 % (skewed lengths) to 1.3 % (32 x 8192) of a 12-layer launch and the full
+// deviation lost 4 % - not worth results whose last bits depend on a measurement.  When on: measured once per
+// device and process (every pool of the device cuts alike), on the first pool of at least 1 GiB (smaller ones
+// would be read from L2); deviations are scaled by BRC_DECODE_RATE_DAMP (default 0.25), rounded to 1/64 and kept
+// within 0.75 .. 1.25.  Never fails the caller: without a measurement the shares stay equal.
+void brc_decode_calibrate(brc_pool *pool) {
+    static std::mutex mu;
+    static uint32_t *prefix_of_device[64] = {};
+    static std::vector<float> rates_of_device[64];
+    static bool tried[64] = {};
+    if (pool->device < 0 || pool->device >= 64 || !pool->k_base) return;
+    std::lock_guard<std::mutex> lock(mu);
+    if (prefix_of_device[pool->device]) {
+        pool->cut_prefix = prefix_of_device[pool->device];
+        pool->cut_rates = rates_of_device[pool->device];
+        return;
+    }
+    const char *env = std::getenv("BRC_DECODE_CALIBRATE");
+    const uint64_t bytes = (uint64_t)(pool->v_base - pool->k_base);   // the K pool
+    if (tried[pool->device] || !(env && *env == '1') || bytes < (1ull << 30)) return;
+    tried[pool->device] = true;
+    const uint32_t grid = std::min<uint32_t>((uint32_t)(pool->sm_count > 0 ? pool->sm_count : 148), MAX_CTAS);
+    uint32_t *landed = nullptr, *prefix = nullptr;
+    if (cudaMalloc(&landed, (MAX_CTAS + 4) * 4) != cudaSuccess || cudaMalloc(&prefix, (MAX_CTAS + 4) * 4) != cudaSuccess) {
+        cudaGetLastError();
+        if (landed) cudaFree(landed);
+        return;
+    }
+    const uint32_t smem = CAL_STAGES * CAL_CHUNK + 2048;   // the ring, and room to start it on a 1024-byte boundary
+    cudaFuncSetAttribute(stream_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    std::vector<double> rate(grid, 0.0);
+    bool ok = true;
+    for (int rep = 0; rep < 4 && ok; ++rep) {            // the first run warms up; three are averaged
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(160);
+        cfg.dynamicSmemBytes = smem;                      // more than half an SM's shared memory: one CTA per SM, as the decode kernel
+        cfg.stream = nullptr;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeCooperative;
+        attr[0].val.cooperative = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        std::vector<uint32_t> host(grid);
+        ok = cudaLaunchKernelEx(&cfg, stream_rate_kernel, (const uint8_t *)pool->k_base, (uint32_t)(bytes / CAL_CHUNK), (uint64_t)300000,
+                                landed, pool->status_dev) == cudaSuccess &&
+             cudaMemcpy(host.data(), landed, grid * 4, cudaMemcpyDeviceToHost) == cudaSuccess;
+        if (ok && rep > 0)
+            for (uint32_t i = 0; i < grid; ++i) rate[i] += host[i];
+    }
+    cudaFree(landed);
+    double mean = 0.0;
+    for (double r : rate) mean += r / grid;
+    if (!ok || mean < 16.0) {   // nothing measured (or a failed launch): equal shares
+        cudaGetLastError();
+        cudaFree(prefix);
+        return;
+    }
+    const char *damp_env = std::getenv("BRC_DECODE_RATE_DAMP");
+    const double damp = damp_env && *damp_env ? std::atof(damp_env) : 0.25;
+    std::vector<uint32_t> host_prefix(grid + 1);
+    double total = 0.0;
+    for (uint32_t i = 0; i < grid; ++i) {
+        rate[i] = std::min(1.25, std::max(0.75, std::round((1.0 + damp * (rate[i] / mean - 1.0)) * 64.0) / 64.0));
+        total += rate[i];
+    }
+    double run = 0.0;
+    for (uint32_t i = 0; i < grid; ++i) {
+        host_prefix[i] = (uint32_t)std::min(4294967295.0, run / total * 4294967296.0);
+        run += rate[i];
+    }
+    host_prefix[grid] = 0xffffffffu;
+    if (cudaMemcpy(prefix, host_prefix.data(), (grid + 1) * 4, cudaMemcpyHostToDevice) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(prefix);
+        return;
+    }
+    prefix_of_device[pool->device] = prefix;             // kept for the life of the process
+    pool->cut_prefix = prefix;
+    rates_of_device[pool->device].assign(rate.begin(), rate.end());
+    pool->cut_rates = rates_of_device[pool->device];
+}
+
+namespace {
 
 uint32_t seqs_per_launch(const brc_pool *pool) { return MAX_UNITS / (pool->n_kv_head / kvb_of(pool)); }
 
@@ -1338,8 +1538,22 @@ brc_status launch_partial(brc_pool *pool, const DecodeParams &p, uint32_t grid, 
     const CUtensorMap &tm_a = VQ8 ? (KVB == 2 ? pool->tm_k2 : pool->tm_k) : (KVB == 2 ? pool->tm_kv2 : pool->tm_kv);
     const CUtensorMap &tm_b = VQ8 ? (KVB == 2 ? pool->tm_v8_2 : pool->tm_v8) : tm_a;
     brc_stage_begin(pool, BRC_STAGE_ATTN_PARTIAL, st);
-    kern<<<grid, Cfg<HD, KVB, VQ8>::NTHREADS, smem, st>>>(tm_a, tm_b, p);
+    // Cooperative: the CTAs of a unit wait for one another's shares at the end of the launch, so all of them must be
+    // resident at once (one per SM; the launch fails instead of starting when the device cannot hold the grid).
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(Cfg<HD, KVB, VQ8>::NTHREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    static const bool coop_off = [] { const char *e = std::getenv("BRC_DECODE_COOPERATIVE"); return e && *e == '0'; }();
+    cfg.numAttrs = coop_off ? 0 : 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, p);
     brc_stage_end(pool, BRC_STAGE_ATTN_PARTIAL, st);
+    BRC_CUDA(e);
     BRC_CUDA(cudaGetLastError());
     return BRC_OK;
 }
@@ -1509,6 +1723,7 @@ brc_status brc_decode_layers(brc_pool *pool, const char *who, const brc_layers_a
             p.scale_log2 = a.scale * 1.4426950408889634f;
             p.n_layers = nl;
             p.unit_cost = unit_cost_of(hd, kvb, pool->v_q8);
+            p.cut_prefix = grid == grid_ctas(pool) ? pool->cut_prefix : nullptr;
             p.q_layer_stride = a.q_layer_stride_bytes / q_elem;
             p.out_layer_stride = a.out_layer_stride_bytes / 4;
             p.out_ml_layer_stride = a.out_ml_layer_stride_bytes / 4;
@@ -1584,6 +1799,15 @@ brc_layers_args one_layer(uint32_t layer, const void *q, int32_t q_dtype, uint32
 }  // namespace
 
 extern "C" {
+
+brc_status brc_decode_share_rates(const brc_pool *pool, float *rates, uint32_t capacity, uint32_t *out_n) {
+    if (!pool || !out_n || (!rates && capacity)) return brc_fail(BRC_ERR_INVALID, "brc_decode_share_rates: NULL argument");
+    const uint32_t n = pool->cut_prefix ? (uint32_t)pool->cut_rates.size() : 0u;
+    if (n > capacity) return brc_fail(BRC_ERR_CAPACITY, "brc_decode_share_rates: %u rates, room for %u", n, capacity);
+    for (uint32_t i = 0; i < n; ++i) rates[i] = pool->cut_rates[i];
+    *out_n = n;
+    return BRC_OK;
+}
 
 brc_status brc_decode_workspace_bytes(const brc_pool *pool, uint32_t n_seqs, uint32_t n_head, uint64_t *out_bytes) {
     if (!pool || !out_bytes) return brc_fail(BRC_ERR_INVALID, "brc_decode_workspace_bytes: NULL argument");

@@ -219,6 +219,7 @@ static brc_status create_pool(int32_t device, uint32_t n_layers, uint32_t n_kv_h
         return rc;
     }
     p->has_tma = true;
+    brc_decode_calibrate(p);   // per-SM streaming rates of this device (measured once per process; large pools only)
     p->refcount.assign(n_pages, 0u);
     p->tree_refs.assign(n_pages, 0u);
     p->free_list.resize(n_pages);

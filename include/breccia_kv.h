@@ -221,7 +221,20 @@ BRC_API brc_status brc_seq_fork(brc_pool *pool, const uint32_t *parent_table, ui
  *             event recorded behind every decode launch; not while a stream is
  *             being captured - replay a captured decode on its own).
  *   max_seq_len    caller's bound on seq_lens; refused if > table_stride*page_tokens.
- * A sequence of length 0 yields zeros. */
+ * A sequence of length 0 yields zeros.
+ *
+ * One launch streams the cache with one CTA per SM, each an equal share of
+ * the launch's work.  The SMs of a B200 do not stream at equal rates when all
+ * of them do (always the same SMs are slow); with BRC_DECODE_CALIBRATE=1 in
+ * the environment the first pool of at least 1 GiB created on a device in
+ * this process measures them once (about a millisecond) and every pool of
+ * that device then cuts a launch's work in proportion (gain measured on
+ * B200: about 1 %; the last bits of the f32 output then depend on the
+ * measurement, which is why it is off by default).  brc_decode_share_rates
+ * reports what is in force: *out_n = the number of CTAs and rates[i] = CTA
+ * i's share relative to the mean, or *out_n = 0 for equal shares (no
+ * counterpart in the reference). */
+BRC_API brc_status brc_decode_share_rates(const brc_pool *pool, float *rates, uint32_t capacity, uint32_t *out_n);
 BRC_API brc_status brc_decode_workspace_bytes(const brc_pool *pool, uint32_t n_seqs, uint32_t n_head,
                                               uint64_t *out_bytes);
 BRC_API brc_status brc_paged_decode_attn(brc_pool *pool, uint32_t layer, const void *q_dev, int32_t q_dtype,

@@ -86,6 +86,21 @@ def main():
             if rank == 0:
                 print(f"splitkv step over 3 layers, world {world}: max_abs vs single-layer call {step_err:.2e}", flush=True)
             step.close()
+            # two calls recorded in a CUDA graph and replayed more often than the receive buffer has banks: the call
+            # count lives on the device, so every replay uses the next bank on every rank
+            out_g = torch.full((2, 1, n_head, hd), float("nan"), device="cuda")
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                split.attend(0, qd, out_g[0])
+                split.attend(0, qd, out_g[1])
+            for _ in range(7):
+                graph.replay()
+            torch.cuda.synchronize()
+            pool.check()
+            graph_same = bool(torch.equal(out_g[0], out)) and bool(torch.equal(out_g[1], out))
+            ok = ok and graph_same
+            if rank == 0:
+                print(f"splitkv two calls in a CUDA graph, 7 replays, world {world}: equal to the plain call {graph_same}", flush=True)
         split.close()
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

@@ -548,6 +548,25 @@ def test_cost_weighted_cut_of_the_page_list(cuda_device, name, lens, n_kv):
     pool.release()
 
 
+def test_shares_in_proportion_to_measured_rates_when_asked(cuda_device):
+    """BRC_DECODE_CALIBRATE=1: a pool of more than 1 GiB measures the SMs' streaming rates once, launches cut their work
+    in proportion (brc_decode_share_rates reports the shares), and the output still matches the oracle.  Without the
+    variable (every other test of this suite) the shares are equal and the report is empty."""
+    import os
+    import subprocess
+    import sys
+
+    pool = KvPool(0, 1, 2, 256, 8)
+    rates, n = (C.c_float * 256)(), C.c_uint32(7)
+    _lib.call("brc_decode_share_rates", pool.handle, rates, 256, C.byref(n))
+    assert n.value == 0
+    pool.release()
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_calibrated_worker.py")
+    r = subprocess.run([sys.executable, worker], env=dict(os.environ, BRC_DECODE_CALIBRATE="1"), capture_output=True, text=True, timeout=600)
+    print(r.stdout[-400:], r.stderr[-2000:])
+    assert r.returncode == 0
+
+
 def test_more_units_than_one_launch_holds(cuda_device):
     """1100 short sequences x 2 kv heads exceed the 2048 units one launch schedules: the host loops."""
     lens = (np.arange(1100) % 37 + 1).astype(np.int64)
