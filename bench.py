@@ -11,7 +11,8 @@ independent, so N GPUs each own 32 sequences of the SAME lengths and their own p
 data-path collective); torch.distributed is used only for the barrier and the max-over-ranks of the
 device time.  Rank 0 prints ONE JSON line, which also carries
 
-    layer_by_layer  the same step as a model's dependent chain sees it (append + attention call per layer)
+    layer_by_layer  the same step as a model's dependent chain sees it (append + attention call per layer);
+                    layer_by_layer_fused: one fused launch per layer
     strong          the same 32 sequences dealt round-robin by descending length over the N GPUs
     splitkv         the long-context workload: ONE sequence of 131 072 cells whose KV range is split over the
                     N GPUs, partials pushed to the peers by the attention kernel itself and merged there
@@ -288,6 +289,14 @@ def bench_batched(ctx, args, kind, steps, warmup, sampler=None, with_cpu=False, 
             batch.attend(layer, q[layer], out[layer])
 
     res["ms_chain"] = ctx.timed(chain, 3, steps, before=reset) / steps if full else None
+
+    # ---- the same chain with the append fused into each layer's attention launch (brc_decode_step_part, one layer
+    #      per call): 12 launches and one position kernel per step
+    def chain_fused():
+        for layer in range(N_LAYERS):
+            batch.step_part(layer, 1, q, k_new, v_new, out)
+
+    res["ms_chain_fused"] = ctx.timed(chain_fused, 3, steps, before=reset) / steps if full else None
 
     # ---- one attention launch alone: CUDA events around every launch of the per-layer calls
     iso_us = None
@@ -594,6 +603,10 @@ def run_native(args):
                                   "us_per_layer": res["ms_chain"] * 1e3 / N_LAYERS,
                                   "how": "per layer brc_kv_append then brc_paged_decode_attn on one stream (24 launches per step): what a "
                                          "model sees whose next layer's query depends on this layer's output"}
+        line["layer_by_layer_fused"] = {"value": tok(res["ms_chain_fused"]), "unit": "tok/s", "ms_per_step": res["ms_chain_fused"],
+                                        "us_per_layer": res["ms_chain_fused"] * 1e3 / N_LAYERS,
+                                        "how": "per layer ONE launch that appends and attends (brc_decode_step_part with one layer per "
+                                               "call; 13 launches per step): the same dependency chain through the fused entry point"}
     if full:
         if args.workload == "cfg2":
             line["strong"] = bench_strong(ctx, args, steps)

@@ -40,8 +40,8 @@
 //   * split-KV across GPUs rides in the same launch: the CTAs that merge a unit store its merged
 //     (acc, m, l) into this rank's slot of every peer's receive buffer with plain global stores over
 //     NVLink, and the last of them releases one flag per (unit, peer); the same CTAs then wait (bounded)
-//     for all ranks' flags, merge the ranks' rows and write the output, so a layer's exchange overlaps
-//     the streaming of the layers behind it.  No load targets peer memory.
+//     for all ranks' flags, merge the ranks' rows and write the output: the exchange of all layers of a
+//     token is one round of stores and flags at the end of one launch.  No load targets peer memory.
 //
 // HBM-bound by design: 8 FLOP per cached byte, all of it on the tensor pipe.
 #include <algorithm>
