@@ -1549,8 +1549,7 @@ brc_status launch_partial(brc_pool *pool, const DecodeParams &p, uint32_t grid, 
     attr[0].id = cudaLaunchAttributeCooperative;
     attr[0].val.cooperative = 1;
     cfg.attrs = attr;
-    static const bool coop_off = [] { const char *e = std::getenv("BRC_DECODE_COOPERATIVE"); return e && *e == '0'; }();
-    cfg.numAttrs = coop_off ? 0 : 1;
+    cfg.numAttrs = 1;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, p);
     brc_stage_end(pool, BRC_STAGE_ATTN_PARTIAL, st);
     BRC_CUDA(e);
