@@ -440,6 +440,7 @@ __device__ __forceinline__ void merge_unit(const DecodeParams &p, const UnitRef 
     // ---- every piece written?  (this CTA's own weight is in: zero low bits mean all of them)
     if (tid == 0 && !gave_up[0]) {
         bool ok = all_written;                           // thread 0 took the unit's last ticket itself: nothing to wait for
+        if (ok) __threadfence();                         // the add that told it so was relaxed: order the reads below after it
         if (!ok) ok = (ld_acquire_gpu(ticket) & TICKET_LOW) == 0u;
         if (!ok) {
             const uint64_t t0 = globaltimer_ns();

@@ -163,6 +163,91 @@ __global__ void __launch_bounds__(SC_THREADS) idx_score_kernel(const ScoreParams
     }
 }
 
+// Several rows of one sequence per CTA (prefill chunks, speculative rows): the rows share the sequence's pooled
+// keys, so a key is loaded once and held in registers while SC_ROWS rows are scored against it - one row per
+// CTA re-read every key from L2 for every row (8.6 GB of L2 reads for a 2048-row chunk over 8192 blocks).
+// A lane holds its 16 dims of TWO blocks (slots `slot` and `slot + 32` of a step of 64 blocks); per row the
+// eight partial dots (2 blocks x 4 heads) of the eight lanes that share the blocks are reduced TRANSPOSED
+// (7 shuffles for 8 dots: each step halves the values a lane holds), so that lane `sub` ends with the whole dot
+// of (block sub / 4, head sub % 4); relu, and two more shuffles sum the heads.  Built for 4 index heads (the
+// reference's IDX_N_HEAD); other head counts take the one-row kernel.
+constexpr uint32_t SC_ROWS = 8;
+constexpr uint32_t SC_TILE_BLOCKS = 512;   // blocks one CTA scores: 8 steps of 64
+
+// grid = (ceil(n_blocks / SC_TILE_BLOCKS), n_seqs * ceil(rows_per_seq / SC_ROWS)).
+__global__ void __launch_bounds__(SC_THREADS) idx_score_rows_kernel(const ScoreParams p) {
+    __shared__ float4 s_q[SC_ROWS * 4 * IDX_DIM / 4];
+    const uint32_t tid = threadIdx.x;
+    const uint32_t tiles_per_seq = (p.rows_per_seq + SC_ROWS - 1u) / SC_ROWS;
+    const uint32_t s = blockIdx.y / tiles_per_seq, t0 = (blockIdx.y % tiles_per_seq) * SC_ROWS;
+    const uint32_t n_rows = min(SC_ROWS, p.rows_per_seq - t0);
+    const size_t row0 = (size_t)s * p.rows_per_seq + t0;
+    const uint32_t pos_first = p.pos0[s] + t0;
+    for (uint32_t i = tid; i < n_rows * 4u * IDX_DIM / 4u; i += SC_THREADS)
+        s_q[i] = reinterpret_cast<const float4 *>(p.q + row0 * 4u * IDX_DIM)[i];
+    __syncthreads();
+    const uint32_t sub = tid & 7u, slot = tid >> 3;
+    const bool hi4 = (sub & 4u) != 0u, hi2 = (sub & 2u) != 0u, hi1 = (sub & 1u) != 0u;
+    const float *pooled = p.pooled + (size_t)s * p.max_blocks * IDX_DIM;
+    for (uint32_t step = 0; step < SC_TILE_BLOCKS / 64u; ++step) {   // the same trip count for every lane
+        const uint32_t bA = blockIdx.x * SC_TILE_BLOCKS + step * 64u + slot, bB = bA + 32u;
+        // a block that even the tile's last row cannot see whole is dead for all of them: no need to load it
+        const uint32_t pos_last = pos_first + n_rows - 1u;
+        const bool liveA = bA < p.n_blocks && bA * IDX_BLOCK + IDX_BLOCK - 1u <= pos_last;
+        const bool liveB = bB < p.n_blocks && bB * IDX_BLOCK + IDX_BLOCK - 1u <= pos_last;
+        float4 ka[4], kb[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ka[j] = kb[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (liveA) {
+            const float4 *kp = reinterpret_cast<const float4 *>(pooled + (size_t)bA * IDX_DIM) + sub;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) ka[j] = __ldg(kp + 8 * j);
+        }
+        if (liveB) {
+            const float4 *kp = reinterpret_cast<const float4 *>(pooled + (size_t)bB * IDX_DIM) + sub;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) kb[j] = __ldg(kp + 8 * j);
+        }
+        for (uint32_t r = 0; r < n_rows; ++r) {
+            float v[8];   // partial dots: v[4 blk + h]
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                const float4 *qp = s_q + (r * 4u + h) * (IDX_DIM / 4) + sub;
+                float da = 0.f, db = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 q4 = qp[8 * j];
+                    da += ka[j].x * q4.x + ka[j].y * q4.y + ka[j].z * q4.z + ka[j].w * q4.w;
+                    db += kb[j].x * q4.x + kb[j].y * q4.y + kb[j].z * q4.z + kb[j].w * q4.w;
+                }
+                v[h] = da;
+                v[4 + h] = db;
+            }
+            float w[4], x[2];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float got = __shfl_xor_sync(0xffffffffu, hi4 ? v[i] : v[i + 4], 4);
+                w[i] = (hi4 ? v[i + 4] : v[i]) + got;
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const float got = __shfl_xor_sync(0xffffffffu, hi2 ? w[i] : w[i + 2], 2);
+                x[i] = (hi2 ? w[i + 2] : w[i]) + got;
+            }
+            const float got = __shfl_xor_sync(0xffffffffu, hi1 ? x[0] : x[1], 1);
+            float sum = fmaxf((hi1 ? x[1] : x[0]) + got, 0.f);   // relu of the dot of (block sub / 4, head sub % 4)
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            if ((sub & 3u) == 0u) {
+                const uint32_t b = hi4 ? bB : bA;
+                // the pooled key averages ALL cells of its block: usable only by a row that sees the whole block
+                if (b < p.n_blocks)
+                    p.scores[(row0 + r) * p.n_blocks + b] = b * IDX_BLOCK + IDX_BLOCK - 1u > pos_first + r ? MASK_DEAD : sum * p.scale;
+            }
+        }
+    }
+}
+
 brc_status check_pool(const brc_pool *pool, const char *who) {
     if (!pool) return brc_fail(BRC_ERR_INVALID, "%s: pool is NULL", who);
     if (pool->device < 0 || !pool->status_dev)
@@ -259,7 +344,12 @@ brc_status brc_idx_score(brc_pool *pool, const float *q_dev, uint32_t idx_n_head
     p.max_blocks = max_blocks;
     p.n_head = idx_n_head;
     p.scale = scale;
-    idx_score_kernel<<<dim3((n_blocks + SC_BLOCKS_PER_CTA - 1) / SC_BLOCKS_PER_CTA, (uint32_t)rows), SC_THREADS, 0, brc_stream(stream)>>>(p);
+    if (rows_per_seq >= 2u && idx_n_head == 4u) {
+        const uint32_t tiles = n_seqs * ((rows_per_seq + SC_ROWS - 1u) / SC_ROWS);
+        idx_score_rows_kernel<<<dim3((n_blocks + SC_TILE_BLOCKS - 1) / SC_TILE_BLOCKS, tiles), SC_THREADS, 0, brc_stream(stream)>>>(p);
+    } else {
+        idx_score_kernel<<<dim3((n_blocks + SC_BLOCKS_PER_CTA - 1) / SC_BLOCKS_PER_CTA, (uint32_t)rows), SC_THREADS, 0, brc_stream(stream)>>>(p);
+    }
     BRC_CUDA(cudaGetLastError());
     return BRC_OK;
 }

@@ -137,3 +137,27 @@ def test_scores_of_a_batch_with_multi_row_chunks(cuda_device):
             assert ref_measure(scores[row][~dead], want[~dead]) <= 1e-5
     assert (scores[2 * rows_per_seq + 0] > -1e29).sum() == 2 and (scores[2 * rows_per_seq + 4] > -1e29).sum() == 3
     pool.release()
+
+
+@pytest.mark.parametrize("rows_per_seq,n_blocks,pos0s", [(17, 777, [3100, 40]), (8, 512, [2047, 2040]), (2, 65, [300, 3])])
+def test_scores_of_row_tiles_that_share_the_keys(cuda_device, rows_per_seq, n_blocks, pos0s):
+    """More than one row per sequence takes the kernel that holds a key in registers for eight rows: tiles that are
+    not full (17 = 8 + 8 + 1), blocks past the last row's reach, block counts that are no multiple of the 512
+    a CTA covers."""
+    n_seqs = len(pos0s)
+    pool = KvPool(0, 1, 2, 256, 4)
+    idx = IndexerState(pool, n_seqs, n_blocks * IDX_BLOCK)
+    pooled = oracle.normalish(0x81, n_seqs * idx.max_blocks * IDX_DIM).reshape(n_seqs, idx.max_blocks, IDX_DIM)
+    idx.pooled.copy_(torch.from_numpy(pooled))
+    q = oracle.normalish(0x82, n_seqs * rows_per_seq * IDX_N_HEAD * IDX_DIM).reshape(n_seqs * rows_per_seq, IDX_N_HEAD, IDX_DIM)
+    scores = idx.score(torch.from_numpy(q).cuda(), dev_u32(pos0s), rows_per_seq, n_blocks).cpu().numpy()
+    pool.check()
+    for s in range(n_seqs):
+        for t in range(rows_per_seq):
+            row = s * rows_per_seq + t
+            want = indexer_ref.indexer_score(q[row], pooled[s], n_blocks, int(pos0s[s]) + t, mask="last")
+            dead = np.isneginf(want)
+            assert np.array_equal(scores[row] <= -1e29, dead), f"sequence {s} row {t}: dead blocks differ"
+            if (~dead).any():
+                assert ref_measure(scores[row][~dead], want[~dead]) <= 1e-5
+    pool.release()
