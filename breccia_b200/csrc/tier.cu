@@ -6,7 +6,8 @@
 // asynchronous and off the decode critical path, all layers of a page move together
 // (docs/reference-engines/02-kv-and-context.md:543-581, 617-626).  Here:
 //   * the host tier is one pinned allocation of `host_pages` slots; a slot holds a page of every
-//     layer, K then V ([K: layer][half page] [V: layer][half page] = 2 * n_layers * half_page_bytes);
+//     layer, K then V ([K: layer][half page] [V: layer][half page] = 2 * n_layers * half_page_bytes; on a
+//     q8_0 V pool the V half pages are 9/16 of the K ones);
 //   * demote packs the pages of a batch (24 separate 16 KiB pieces each at 12 layers) into a staging
 //     buffer in HBM with one kernel, then copies staging -> slots with one cudaMemcpyAsync per run of
 //     neighbouring slots (free slots are handed out lowest first, so a batch is mostly one run), on the
@@ -63,17 +64,22 @@ struct PageList {
 };
 
 // One CTA per (page of the batch, layer, K|V): a 16-byte-vector copy of one half page between the pool
-// and staging slot `i` ([K: layer][half page] [V: layer][half page]).
+// and staging slot `i` ([K: layer][K half page] [V: layer][V half page]; on a q8_0 V pool the V half of a
+// page is 9/16 of the K half, crates/breccia-kernels/src/qsa/mod.rs:339-349).
 template <bool TO_STAGING>
 __global__ void __launch_bounds__(256) tier_pack_kernel(uint8_t *k_base, uint8_t *v_base, uint8_t *staging, const PageList pages,
-                                                        uint32_t n_layers, uint64_t half_page_bytes, uint64_t layer_bytes) {
+                                                        uint32_t n_layers, uint64_t k_half_bytes, uint64_t k_layer_bytes,
+                                                        uint64_t v_half_bytes, uint64_t v_layer_bytes) {
     const uint32_t i = blockIdx.x / (2u * n_layers), piece = blockIdx.x % (2u * n_layers);
     const bool is_v = piece >= n_layers;
     const uint32_t layer = is_v ? piece - n_layers : piece;
-    uint4 *pool = reinterpret_cast<uint4 *>((is_v ? v_base : k_base) + (uint64_t)layer * layer_bytes +
-                                            (uint64_t)pages.ids[i] * half_page_bytes);
-    uint4 *stage = reinterpret_cast<uint4 *>(staging + ((uint64_t)i * 2u * n_layers + piece) * half_page_bytes);
-    const uint32_t n_vec = (uint32_t)(half_page_bytes / 16);
+    const uint64_t half = is_v ? v_half_bytes : k_half_bytes;
+    uint4 *pool = reinterpret_cast<uint4 *>((is_v ? v_base + (uint64_t)layer * v_layer_bytes : k_base + (uint64_t)layer * k_layer_bytes) +
+                                            (uint64_t)pages.ids[i] * half);
+    const uint64_t slot_bytes = n_layers * (k_half_bytes + v_half_bytes);
+    uint4 *stage = reinterpret_cast<uint4 *>(staging + (uint64_t)i * slot_bytes +
+                                             (is_v ? n_layers * k_half_bytes + (uint64_t)layer * v_half_bytes : (uint64_t)layer * k_half_bytes));
+    const uint32_t n_vec = (uint32_t)(half / 16);
     for (uint32_t v = threadIdx.x; v < n_vec; v += 256) {
         if (TO_STAGING)
             stage[v] = pool[v];
@@ -89,7 +95,6 @@ extern "C" {
 brc_status brc_tier_create(brc_pool *pool, uint32_t host_pages, brc_tier **out) {
     if (!pool || !out) return brc_fail(BRC_ERR_INVALID, "brc_tier_create: NULL argument");
     *out = nullptr;
-    BRC_REFUSE_Q8V(pool, "brc_tier_create");
     if (pool->device < 0 || !pool->k_base)
         return brc_fail(BRC_ERR_CUDA, "brc_tier_create: this pool holds bookkeeping only (no device memory)");
     if (host_pages == 0) return brc_fail(BRC_ERR_INVALID, "brc_tier_create: host_pages is 0");
@@ -98,7 +103,7 @@ brc_status brc_tier_create(brc_pool *pool, uint32_t host_pages, brc_tier **out) 
     if (!t) return brc_fail(BRC_ERR_INVALID, "brc_tier_create: out of host memory");
     t->pool = pool;
     t->host_pages = host_pages;
-    t->slot_bytes = 2ull * pool->n_layers * pool->half_page_bytes;
+    t->slot_bytes = (uint64_t)pool->n_layers * (pool->half_page_bytes + pool->v_layer_bytes / pool->n_pages);   // K half + V half (9/16 of it on q8_0 V)
     cudaError_t e;
     if ((e = cudaMallocHost(&t->host, (size_t)t->slot_bytes * host_pages)) != cudaSuccess ||
         (e = cudaMalloc(&t->out_staging, (size_t)t->slot_bytes * STAGE_PAGES)) != cudaSuccess ||
@@ -176,10 +181,12 @@ static void launch_pack(brc_tier *t, const PageList &pl, uint32_t n, bool to_sta
     const uint32_t grid = n * 2u * p->n_layers;
     if (to_staging)
         tier_pack_kernel<true><<<grid, 256, 0, t->out_stream>>>(p->k_base, p->v_base, t->out_staging, pl, p->n_layers,
-                                                                p->half_page_bytes, p->layer_bytes);
+                                                                p->half_page_bytes, p->layer_bytes, p->v_layer_bytes / p->n_pages,
+                                                                p->v_layer_bytes);
     else
         tier_pack_kernel<false><<<grid, 256, 0, t->in_stream>>>(p->k_base, p->v_base, t->in_staging, pl, p->n_layers,
-                                                                p->half_page_bytes, p->layer_bytes);
+                                                                p->half_page_bytes, p->layer_bytes, p->v_layer_bytes / p->n_pages,
+                                                                p->v_layer_bytes);
 }
 
 // Make `waiter` wait for batch `dep` of the other direction unless that batch is known to be complete:

@@ -98,11 +98,12 @@ BRC_API brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n
  * integers and the block scales ride on the probabilities (read rule
  * qsa_attn_apply.comp:60-77), 1600 instead of 2048 bytes per cached cell at
  * 2 kv heads of 256; brc_paged_sparse_attn (in-register dequantisation);
- * brc_page_copy and brc_seq_fork (whole pages, bytes as they are); brc_pool_read
- * / brc_pool_write / brc_pool_v_ptr, the allocator and the prefix tree.  The
- * entry points that read V as binary16 tiles or rows (chunked prefill, page
- * gather, tiering, page files, brc_qk_prepare_append) refuse it with
- * BRC_ERR_UNSUPPORTED. */
+ * brc_page_copy and brc_seq_fork (whole pages, bytes as they are); tiering and
+ * the cold store (brc_tier_*, brc_cold_*: a host slot then holds K halves of
+ * 16 KiB and V halves of 9 KiB per layer); brc_pool_read / brc_pool_write /
+ * brc_pool_v_ptr, the allocator and the prefix tree.  The entry points that
+ * read V as binary16 tiles or rows (chunked prefill, page gather, page files,
+ * brc_qk_prepare_append) refuse it with BRC_ERR_UNSUPPORTED. */
 #define BRC_V_F16 0
 #define BRC_V_Q8_0 1
 BRC_API brc_status brc_pool_create_q8v(int32_t device, uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim,

@@ -5,6 +5,7 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
 from breccia_b200 import _lib, synth
 from breccia_b200.qsa import DecodeBatch, KvPool
 from helpers import fill_pool_from_host
@@ -270,5 +271,74 @@ def test_pages_spilled_to_a_file_come_back_bit_exact_in_another_store_handle(cud
     assert L.brc_cold_open(tier2, path, 0, 0, C.byref(cold)) == _lib.ERR_INVALID and b"layers" in L.brc_last_error()
     L.brc_tier_destroy(tier2)
     other.release()
+    L.brc_tier_destroy(tier)
+    pool.release()
+
+
+def test_q8_0_v_pool_pages_move_between_the_tiers_and_a_file_byte_for_byte(cuda_device, tmp_path):
+    """A pool whose V pages are q8_0 blocks: a host slot holds 16 KiB of K and 9 KiB of V per layer; demote ->
+    spill to a file -> fetch -> promote brings back every byte of both, and decode attention over the promoted
+    pages equals attention before the demotion bit for bit."""
+    n_layers, n_pages, n_kv, hd = 2, 40, 2, 256
+    pool = KvPool(0, n_layers, n_kv, hd, n_pages, v_q8=True)
+    L = _lib.load()
+    mine, mp = arr(np.zeros(20))
+    assert L.brc_pages_alloc(pool.handle, 20, mp) == 0
+    rng = np.random.default_rng(77)
+    before = []
+    for layer in range(n_layers):
+        k = oracle.f32_to_f16_bits_np(synth.normal(960 + layer, n_pages * n_kv * 16 * hd, 0.5))
+        rows = n_pages * n_kv * 16
+        v = np.zeros((rows, hd // 32, 36), np.uint8)          # [row][block]: f32 scale then 32 quanta
+        v[:, :, :4] = rng.uniform(0.001, 0.05, (rows, hd // 32)).astype(np.float32).view(np.uint8).reshape(rows, hd // 32, 4)
+        v[:, :, 4:] = rng.integers(-127, 128, (rows, hd // 32, 32), dtype=np.int8).view(np.uint8)
+        pool.write(0, layer, k)
+        pool.write(1, layer, v)
+        before.append((pool.read(0, layer).copy(), pool.read(1, layer).copy()))
+    v_page = n_kv * 16 * (hd // 32 * 36)                      # bytes of the V half of a page
+    # attention over a sequence that lives in pages mine[4:12], before anything moves
+    lens = np.array([8 * 16 - 5])
+    tables = mine[4:12][None, :].astype(np.uint32)
+    q = torch.randn((1, 16, hd), device="cuda").half()
+    out0 = torch.full((1, 16, hd), float("nan"), device="cuda")
+    DecodeBatch(pool, 16, tables, lens).attend(1, q, out0)
+    pool.check()
+    tier, cold = C.c_void_p(), C.c_void_p()
+    assert L.brc_tier_create(pool.handle, 8, C.byref(tier)) == 0
+    assert L.brc_cold_open(tier, str(tmp_path / "q8.brccold").encode(), 8, 1, C.byref(cold)) == 0
+    vict, vp = arr(mine[4:12])
+    slots, sp = arr(np.zeros(8))
+    assert L.brc_tier_demote(tier, vp, 8, sp, None) == 0
+    st = [C.c_uint64() for _ in range(4)]
+    fs = C.c_uint32()
+    assert L.brc_tier_stats(tier, *(C.byref(x) for x in st), C.byref(fs)) == 0
+    slot_bytes = n_layers * (pool.half_page_bytes + v_page)
+    assert st[2].value == 8 * slot_bytes and v_page * 16 == pool.half_page_bytes * 9
+    recs, rp = arr(np.zeros(8))
+    assert L.brc_cold_spill(cold, sp, None, 8, rp) == 0
+    pool.poison_nan()
+    for layer in range(n_layers):                             # the pages that stayed keep their bytes
+        pool.write(0, layer, before[layer][0])
+        pool.write(1, layer, before[layer][1])
+        for pg in vict:
+            pool.write(0, layer, np.full(pool.half_page_bytes // 2, 0xABCD, np.uint16), byte_offset=int(pg) * pool.half_page_bytes)
+            pool.write(1, layer, np.full(v_page, 0xEE, np.uint8), byte_offset=int(pg) * v_page)
+    hs, hp = arr(np.zeros(8))
+    assert L.brc_cold_fetch(cold, rp, 8, 0, hp) == 0
+    back, bp = arr(np.zeros(8))
+    assert L.brc_tier_promote(tier, hp, 8, bp) == 0
+    assert L.brc_tier_fence(tier, None) == 0
+    torch.cuda.synchronize()
+    rows_per_page = n_kv * 16
+    for layer in range(n_layers):
+        k, v = pool.read(0, layer), pool.read(1, layer)
+        for old, new in zip(vict, back):
+            assert np.array_equal(k[new], before[layer][0][old]), f"K layer {layer} page {old}->{new}"
+            assert np.array_equal(v[new * rows_per_page:(new + 1) * rows_per_page], before[layer][1][old * rows_per_page:(old + 1) * rows_per_page])
+    out1 = torch.full_like(out0, float("nan"))
+    DecodeBatch(pool, 16, back[None, :].astype(np.uint32), lens).attend(1, q, out1)
+    pool.check()
+    assert torch.equal(out0, out1)
+    assert L.brc_cold_close(cold) == 0
     L.brc_tier_destroy(tier)
     pool.release()
