@@ -145,6 +145,28 @@ __global__ void __launch_bounds__(256)
     }
 }
 
+// The same for ONE of K / V with rows of `row_bytes` (a multiple of 16): the V rows of a q8_0 pool are
+// head_dim / 32 blocks of 36 bytes and come out as they are stored.
+__global__ void __launch_bounds__(256)
+    row_gather_kernel(const uint8_t *layer_base, uint32_t row_bytes, const uint32_t *block_table, uint32_t n_tokens, uint32_t n_kv_head,
+                      uint32_t page_tokens, uint32_t n_pages, uint4 *out, uint32_t *status) {
+    const uint32_t vec_per_row = row_bytes / 16u;
+    const uint32_t vec_per_token = n_kv_head * vec_per_row;
+    const uint64_t total = (uint64_t)n_tokens * vec_per_token;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t cell = (uint32_t)(i / vec_per_token);
+        const uint32_t r = (uint32_t)(i % vec_per_token);
+        const uint32_t kvh = r / vec_per_row, vec = r % vec_per_row;
+        const uint32_t page = block_table[cell / page_tokens];
+        if (page >= n_pages) {
+            if (r == 0) { atomicOr(status, BRC_DEV_BAD_PAGE); status[1] = page; }
+            continue;
+        }
+        const uint64_t row = ((uint64_t)page * n_kv_head + kvh) * page_tokens + cell % page_tokens;
+        out[i] = *reinterpret_cast<const uint4 *>(layer_base + row * row_bytes + (uint64_t)vec * 16u);
+    }
+}
+
 // Whole-page copies in every layer, K and V.  blockIdx.y = pair; the x dimension strides over the
 // (layer, K|V, 16-byte vector) space of one page.  The V half of a page may be smaller than the K half
 // (q8_0 bodies: 9/16 of it); both are whole numbers of 16-byte vectors.
@@ -251,7 +273,7 @@ brc_status brc_kv_append(brc_pool *pool, uint32_t layer, const uint32_t *block_t
 
 brc_status brc_page_gather(brc_pool *pool, uint32_t layer, const uint32_t *block_table_dev, uint32_t table_len,
                            uint32_t n_tokens, void *k_out_dev, void *v_out_dev, void *stream) {
-    if (brc_status rc = need_device_pool(pool, "brc_page_gather")) return rc;
+    if (brc_status rc = need_device_pool(pool, "brc_page_gather", true)) return rc;
     if (layer >= pool->n_layers)
         return brc_fail(BRC_ERR_INVALID, "brc_page_gather: layer %u but the pool has %u", layer, pool->n_layers);
     if ((uint64_t)n_tokens > (uint64_t)table_len * pool->page_tokens)
@@ -263,6 +285,17 @@ brc_status brc_page_gather(brc_pool *pool, uint32_t layer, const uint32_t *block
     brc_device_guard guard(pool->device);
     const uint64_t work = (uint64_t)n_tokens * pool->n_kv_head * (pool->head_dim / 8u);
     const uint32_t grid = grid_for(work, 256, pool->sm_count, 8);
+    if (pool->v_q8) {   // K as binary16 rows, V as the stored q8_0 rows
+        const uint32_t v_row = pool->head_dim / 32u * 36u;
+        row_gather_kernel<<<grid, 256, 0, brc_stream(stream)>>>(pool->k_base + (uint64_t)layer * pool->layer_bytes, pool->head_dim * 2u,
+                                                              block_table_dev, n_tokens, pool->n_kv_head, pool->page_tokens,
+                                                              pool->n_pages, static_cast<uint4 *>(k_out_dev), pool->status_dev);
+        row_gather_kernel<<<grid, 256, 0, brc_stream(stream)>>>(pool->v_base + (uint64_t)layer * pool->v_layer_bytes, v_row,
+                                                              block_table_dev, n_tokens, pool->n_kv_head, pool->page_tokens,
+                                                              pool->n_pages, static_cast<uint4 *>(v_out_dev), pool->status_dev);
+        BRC_CUDA(cudaGetLastError());
+        return BRC_OK;
+    }
     page_gather_kernel<<<grid, 256, 0, brc_stream(stream)>>>(
         pool->k_base + (uint64_t)layer * pool->layer_bytes, pool->v_base + (uint64_t)layer * pool->layer_bytes,
         block_table_dev, n_tokens, pool->n_kv_head, pool->head_dim, pool->page_tokens, pool->n_pages,

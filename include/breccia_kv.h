@@ -100,10 +100,12 @@ BRC_API brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n
  * 2 kv heads of 256; brc_paged_sparse_attn (in-register dequantisation);
  * brc_page_copy and brc_seq_fork (whole pages, bytes as they are); tiering and
  * the cold store (brc_tier_*, brc_cold_*: a host slot then holds K halves of
- * 16 KiB and V halves of 9 KiB per layer); brc_pool_read / brc_pool_write /
- * brc_pool_v_ptr, the allocator and the prefix tree.  The entry points that
- * read V as binary16 tiles or rows (chunked prefill, page gather, page files,
- * brc_qk_prepare_append) refuse it with BRC_ERR_UNSUPPORTED. */
+ * 16 KiB and V halves of 9 KiB per layer); brc_page_gather (V rows as stored);
+ * the page files (brc_state_dump / _load: the reference's `qsa_vq8` part,
+ * crates/breccia-engine/src/graph.rs:2183-2186); brc_pool_read /
+ * brc_pool_write / brc_pool_v_ptr, the allocator and the prefix tree.  Chunked
+ * prefill and brc_qk_prepare_append, which read or write V as binary16, refuse
+ * it with BRC_ERR_UNSUPPORTED. */
 #define BRC_V_F16 0
 #define BRC_V_Q8_0 1
 BRC_API brc_status brc_pool_create_q8v(int32_t device, uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim,
@@ -178,7 +180,8 @@ BRC_API brc_status brc_kv_append(brc_pool *pool, uint32_t layer, const uint32_t 
  * Gather: the reference reads pages back only through an identity table
  * (crates/breccia-engine/src/graph.rs:2204-2228, `dump_state`); this reads
  * `n_tokens` cells of one sequence through a real block table into logical
- * [n_tokens][n_kv_head][head_dim] binary16 arrays. */
+ * [n_tokens][n_kv_head][head_dim] binary16 arrays; on a q8_0 V pool v_out
+ * receives the stored rows, [n_tokens][n_kv_head][head_dim / 32 * 36] bytes. */
 BRC_API brc_status brc_page_gather(brc_pool *pool, uint32_t layer, const uint32_t *block_table_dev,
                                    uint32_t table_len, uint32_t n_tokens, void *k_out_dev, void *v_out_dev,
                                    void *stream);

@@ -96,9 +96,6 @@ def test_entry_points_built_for_binary16_v_refuse_a_q8_0_pool(cuda_device):
     with pytest.raises(_lib.BrcError) as err:      # the tensor-core prefill path reads V as binary16 tiles
         _lib.call("brc_paged_prefill_attn", pool.handle, 0, P(x), DTYPE_F32, 16, None, 0, P(t), 2, P(t), 1, 16, 16, 0.0625, P(x), None)
     assert err.value.code == _lib.ERR_UNSUPPORTED and "q8_0" in err.value.message
-    with pytest.raises(_lib.BrcError) as err:
-        _lib.call("brc_page_gather", pool.handle, 0, P(t), 2, 16, P(x), P(x), None)
-    assert err.value.code == _lib.ERR_UNSUPPORTED
     with pytest.raises(_lib.BrcError) as err:      # binary16 sources are refused: the rule quantises from f32
         _lib.call("brc_kv_append", pool.handle, 0, P(t), 2, P(t), 1, 1, None, 1, 1, P(x), P(x), _lib.DTYPE_F16, None)
     assert err.value.code == _lib.ERR_UNSUPPORTED
@@ -131,4 +128,27 @@ def test_fork_copies_the_partial_last_page_of_a_q8_0_pool_as_it_is(cuda_device):
         assert np.array_equal(k_now[keep], before[layer][0][keep])
         v_pages_now, v_pages_before = v_now.reshape(8, -1), before[layer][1].reshape(8, -1)
         assert np.array_equal(v_pages_now[keep], v_pages_before[keep])
+    pool.release()
+
+
+def test_gather_on_a_q8_0_pool_returns_k_rows_and_the_stored_v_rows(cuda_device):
+    """brc_page_gather through a scattered block table: K as binary16 rows, V as the 36-byte blocks the append
+    stored, in logical cell order."""
+    from oracle import q8v
+
+    n_kv, hd, cells = 2, 256, 37
+    pool = KvPool(0, 1, n_kv, hd, 16, v_q8=True)
+    table = np.array([9, 2, 14], np.uint32)
+    pool.alloc(16)
+    k = synth.normal(71, cells * n_kv * hd, 0.5).reshape(cells, n_kv * hd)
+    v = synth.normal(72, cells * n_kv * hd, 0.5).reshape(cells, n_kv * hd)
+    t_dev, pos0, k_dev, v_dev = dev_u32(table[None, :]), dev_u32([0]), torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda()   # kept alive
+    _lib.call("brc_kv_append", pool.handle, 0, P(t_dev), 3, P(pos0), 1, cells, None, cells, cells, P(k_dev), P(v_dev), DTYPE_F32, None)
+    k_out = torch.zeros((cells, n_kv, hd), dtype=torch.float16, device="cuda")
+    v_out = torch.zeros((cells, n_kv, q8v.row_bytes(hd)), dtype=torch.uint8, device="cuda")
+    _lib.call("brc_page_gather", pool.handle, 0, P(t_dev), 3, cells, P(k_out), P(v_out), None)
+    pool.check()
+    assert np.array_equal(k_out.view(torch.int16).cpu().numpy().view(np.uint16).reshape(cells, -1), oracle.f32_to_f16_bits_np(k.reshape(-1)).reshape(cells, -1))
+    want_v = q8v.pack_rows(v.reshape(cells * n_kv, hd)).reshape(cells, n_kv, -1)
+    assert np.array_equal(v_out.cpu().numpy(), want_v)
     pool.release()

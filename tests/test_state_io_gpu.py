@@ -64,3 +64,42 @@ def test_dump_matches_identity_pool_bytes_and_load_restores(cuda_device, tmp_pat
     assert b"does not hold exactly" in L.brc_last_error()
     pool.release_pages(spare)
     pool.release()
+
+
+def test_q8_0_v_pool_dumps_the_reference_vq8_part_and_loads_it_back(cuda_device, tmp_path):
+    """A q8_0 V pool writes p<pos>-b<block>-qsa_vq8.bin (q8v_pool_bytes(pages) raw bytes, graph.rs:2183-2186) beside
+    the binary16 K file: the bytes an identity-mapped pool would hold after the same appends."""
+    from oracle import q8v
+
+    n_head, n_kv, hd, n_tokens, pos = 24, 2, 256, 100, 99
+    n_pages = pos // 16 + 1                       # 7
+    pool = KvPool(0, 1, n_kv, hd, 32, v_q8=True)
+    table = synth.permutation(31, 32)[:n_pages].astype(np.uint32)
+    spare = pool.alloc(32)
+    state = QsaState(pool, n_pages * 16, layer=0, block_table=table)
+    qsa = Qsa(pool, n_head)
+    ws = qsa.workspace(n_tokens)
+    k = synth.normal(32, n_tokens * n_kv * hd, 0.5).reshape(n_tokens, n_kv * hd)
+    v = synth.normal(33, n_tokens * n_kv * hd, 0.5).reshape(n_tokens, n_kv * hd)
+    ws.k_cur.copy_(torch.from_numpy(k))
+    ws.v_cur.copy_(torch.from_numpy(v))
+    qsa.kv_append(state, ws, 0)
+    torch.cuda.synchronize()
+    want_v = np.zeros((n_pages * n_kv * 16, q8v.row_bytes(hd)), np.uint8)      # the pool was zeroed at creation
+    q8v.v_append(want_v, np.arange(n_pages, dtype=np.uint32), v, 0, n_kv, hd)
+    d = str(tmp_path).encode()
+    _lib.call("brc_state_dump", pool.handle, 0, table.ctypes.data_as(U32P), n_pages, pos, 3, d, None)
+    vf = np.fromfile(os.path.join(str(tmp_path), "p000099-b03-qsa_vq8.bin"), np.uint8)
+    kf = np.fromfile(os.path.join(str(tmp_path), "p000099-b03-qsa_k.bin"), np.uint8)
+    assert vf.size == n_pages * n_kv * 16 * (hd // 32) * 36 and kf.size == n_pages * n_kv * 16 * hd * 2
+    assert np.array_equal(vf, want_v.reshape(-1))
+    assert not os.path.exists(os.path.join(str(tmp_path), "p000099-b03-qsa_v.bin"))
+    table2 = synth.permutation(34, 32)[:n_pages].astype(np.uint32)
+    before_k = pool.read(0, 0).reshape(32, -1)[table].copy()
+    _lib.call("brc_state_load", pool.handle, 0, table2.ctypes.data_as(U32P), n_pages, pos, 3, d, None)
+    rows = n_kv * 16
+    v_now = pool.read(1, 0).reshape(32, rows * q8v.row_bytes(hd))
+    assert np.array_equal(v_now[table2].reshape(-1), want_v.reshape(-1))
+    assert np.array_equal(pool.read(0, 0).reshape(32, -1)[table2], before_k)
+    pool.release_pages(spare)
+    pool.release()
