@@ -28,6 +28,7 @@ struct PrepareParams {
     uint32_t *status;
     uint32_t n_seqs, tokens_per_seq, table_stride, max_pos_end;
     uint32_t n_head, n_kv_head, q_head_stride, n_rot, max_pos, n_pages, q_out_f16;
+    uint32_t v_q8;            // the pool stores V as q8_0 blocks
     float eps;
 };
 
@@ -119,6 +120,26 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) qk_prepare_kernel(const Prepa
         if (lane == 0) { atomicOr(p.status, BRC_DEV_BAD_PAGE); p.status[1] = page; }
         return;
     }
+    if (is_v && p.v_q8) {
+        // q8_0 V row (store rule of shaders/qsa_kv_append.comp:117-133, as in the append kernel): the eight lanes
+        // that hold a block's 32 values share its maximum; scale = amax / 127 (1 for an all-zero block), quanta
+        // = round-half-away(clamp(x / scale, +-127)); a block is one f32 scale then 32 signed bytes.
+        const size_t row = ((size_t)page * p.n_kv_head + kvh) * 16u + (pos & 15u);
+        uint32_t *vrow = reinterpret_cast<uint32_t *>(p.v_layer) + row * (HD / 32) * 9u;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            float amax = fmaxf(fmaxf(fabsf(x[c].x), fabsf(x[c].y)), fmaxf(fabsf(x[c].z), fabsf(x[c].w)));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+            const float scale = amax > 0.f ? __fdiv_rn(amax, 127.f) : 1.f;
+            auto quant = [scale](float v) { return (uint32_t)(int32_t)roundf(fminf(fmaxf(__fdiv_rn(v, scale), -127.f), 127.f)) & 0xffu; };
+            uint32_t *blk = vrow + (c * 4 + (lane >> 3)) * 9u;
+            if ((lane & 7u) == 0u) blk[0] = __float_as_uint(scale);
+            blk[1u + (lane & 7u)] = quant(x[c].x) | (quant(x[c].y) << 8) | (quant(x[c].z) << 16) | (quant(x[c].w) << 24);
+        }
+        return;
+    }
     uint16_t *dst = reinterpret_cast<uint16_t *>(is_v ? p.v_layer : p.k_layer) + (((size_t)page * p.n_kv_head + kvh) * 16u + (pos & 15u)) * HD;
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
@@ -140,7 +161,6 @@ brc_status brc_qk_prepare_append(brc_pool *pool, uint32_t layer, const float *q_
                                  const uint32_t *pos0_dev, uint32_t n_seqs, uint32_t tokens_per_seq, uint32_t max_pos_end,
                                  void *q_out_dev, int32_t q_out_dtype, void *stream) {
     if (!pool) return brc_fail(BRC_ERR_INVALID, "brc_qk_prepare_append: pool is NULL");
-    BRC_REFUSE_Q8V(pool, "brc_qk_prepare_append");
     if (pool->device < 0 || !pool->k_base)
         return brc_fail(BRC_ERR_CUDA, "brc_qk_prepare_append: this pool holds bookkeeping only (no device memory)");
     if (layer >= pool->n_layers) return brc_fail(BRC_ERR_INVALID, "brc_qk_prepare_append: layer %u but the pool has %u", layer, pool->n_layers);
@@ -176,7 +196,8 @@ brc_status brc_qk_prepare_append(brc_pool *pool, uint32_t layer, const float *q_
     p.pos0 = pos0_dev;
     p.q_out = q_out_dev;
     p.k_layer = pool->k_base + (uint64_t)layer * pool->layer_bytes;
-    p.v_layer = pool->v_base + (uint64_t)layer * pool->layer_bytes;
+    p.v_layer = pool->v_base + (uint64_t)layer * pool->v_layer_bytes;
+    p.v_q8 = pool->v_q8 ? 1u : 0u;
     p.status = pool->status_dev;
     p.n_seqs = n_seqs;
     p.tokens_per_seq = tokens_per_seq;

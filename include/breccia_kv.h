@@ -103,9 +103,9 @@ BRC_API brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n
  * 16 KiB and V halves of 9 KiB per layer); brc_page_gather (V rows as stored);
  * the page files (brc_state_dump / _load: the reference's `qsa_vq8` part,
  * crates/breccia-engine/src/graph.rs:2183-2186); brc_pool_read /
- * brc_pool_write / brc_pool_v_ptr, the allocator and the prefix tree.  Chunked
- * prefill and brc_qk_prepare_append, which read or write V as binary16, refuse
- * it with BRC_ERR_UNSUPPORTED. */
+ * brc_pool_write / brc_pool_v_ptr, the allocator and the prefix tree;
+ * brc_qk_prepare_append (V quantised by the append's rule).  Chunked prefill,
+ * which reads V as binary16 tiles, refuses it with BRC_ERR_UNSUPPORTED. */
 #define BRC_V_F16 0
 #define BRC_V_Q8_0 1
 BRC_API brc_status brc_pool_create_q8v(int32_t device, uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim,

@@ -98,3 +98,37 @@ def test_prepare_refusals(cuda_device):
     with pytest.raises(_lib.BrcError, match="position past bound"):
         pool.check()
     pool.release()
+
+
+def test_prepare_on_a_q8_0_v_pool_quantises_v_by_the_append_rule(cuda_device):
+    """On a q8_0 V pool the fused launch stores V as q8_0 blocks, byte for byte what brc_kv_append stores from the
+    same f32 rows (store rule of shaders/qsa_kv_append.comp:117-133); K and the prepared query as on any pool."""
+    from oracle import q8v
+
+    n_head, n_kv, hd, q_stride, n_rot, T = 24, 2, 256, 512, 64, 21
+    pos0s = np.array([5, 40])
+    n_seqs, max_pos = pos0s.size, 512
+    tables, n_pool = synth.scattered_tables(91, pos0s + T, pool_factor=1.5)
+    pool = KvPool(0, 1, n_kv, hd, n_pool, v_q8=True)
+    tok = n_seqs * T
+    q_full = synth.normal(92, tok * n_head * q_stride, 1.3).reshape(tok, n_head, q_stride)
+    k_cur = synth.normal(93, tok * n_kv * hd, 0.7).reshape(tok, n_kv * hd)
+    v_cur = synth.normal(94, tok * n_kv * hd, 0.5).reshape(tok, n_kv * hd)
+    v_cur[3, :32] = 0.0                                   # an all-zero block: scale 1, quanta 0
+    gam = np.ones(hd, np.float32)
+    table = prepare_ref.rope_table(1.0e6, n_rot, max_pos)
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    qf, kc, vc, qg, tb = d(q_full), d(k_cur), d(v_cur), d(gam), d(table)
+    t_dev, p_dev = dev_u32(tables), dev_u32(pos0s)
+    q_out = torch.empty((tok, n_head, hd), device="cuda")
+    _lib.call("brc_qk_prepare_append", pool.handle, 0, C.c_void_p(qf.data_ptr()), q_stride, n_head, C.c_void_p(kc.data_ptr()),
+              C.c_void_p(vc.data_ptr()), C.c_void_p(qg.data_ptr()), C.c_void_p(qg.data_ptr()), 1e-6, C.c_void_p(tb.data_ptr()),
+              n_rot, max_pos, C.c_void_p(t_dev.data_ptr()), tables.shape[1], C.c_void_p(p_dev.data_ptr()), n_seqs, T,
+              int(pos0s.max() + T), C.c_void_p(q_out.data_ptr()), DTYPE_F32, None)
+    pool.check()
+    got_v = pool.read(1, 0)                                # [rows][288] bytes
+    want_v = np.zeros_like(got_v)
+    for s in range(n_seqs):
+        q8v.v_append(want_v, tables[s], v_cur[s * T:(s + 1) * T], int(pos0s[s]), n_kv, hd)
+    assert np.array_equal(got_v, want_v)
+    pool.release()
