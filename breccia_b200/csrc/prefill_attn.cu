@@ -70,6 +70,7 @@ struct PrefillParams {
     uint32_t n_kv_head, group, n_head, n_pages, q_f32, gate_head_stride;
     uint32_t head_slots;           // rows per token in a tile: 8, or the group when it is larger
     uint32_t tile_tokens;          // tokens per tile: 128 / head_slots
+    uint32_t v_q8;                 // the pool stores V as q8_0 blocks (one f32 scale + 32 signed bytes per 32 values)
     float scale_log2;
 };
 
@@ -305,6 +306,39 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_kernel(const Prefi
                 }
                 const uint32_t dst0 = brc::smem_u32(kv ? v_sm0 : k_sm0) + stg * PF_K_BYTES;
                 const uint8_t *base = kv ? p.v_layer : p.k_layer;
+                if (kv && p.v_q8) {
+                    // q8_0 V (crates/breccia-kernels/src/qsa/mod.rs:325-349; read rule shaders/qsa_attn_apply.comp:60-77):
+                    // the thread's eight values of a row are a quarter of one 36-byte block; scale x quantum in fp32,
+                    // rounded to the binary16 the tile holds (the tensor cores take binary16 V: the rounding, 2^-11
+                    // relative, is inside this path's tolerance).  Loads first, all sixteen rows in flight, then the
+                    // conversions and plain shared-memory stores, then an ordinary arrival on the stage's barrier.
+                    uint32_t sc[16], qa[16], qb[16];
+#pragma unroll
+                    for (uint32_t i = 0; i < 16; ++i) {
+                        const uint32_t r = r0 + 4u * i;
+                        const uint32_t cell = j * PF_BLK + r;
+                        sc[i] = qa[i] = qb[i] = 0u;
+                        if (cell < kv_len) {
+                            const uint32_t *blk = reinterpret_cast<const uint32_t *>(base) +
+                                                  ((((uint64_t)page[i >> 2] * p.n_kv_head + kvh) * 16u + (r & 15u)) * (PF_HD / 32u) + (ch >> 2)) * 9u;
+                            sc[i] = __ldg(blk);
+                            qa[i] = __ldg(blk + 1u + 2u * (ch & 3u));
+                            qb[i] = __ldg(blk + 2u + 2u * (ch & 3u));
+                        }
+                    }
+#pragma unroll
+                    for (uint32_t i = 0; i < 16; ++i) {
+                        const uint32_t r = r0 + 4u * i;
+                        const uint32_t off = (ch >> 3) * PF_KV_SLAB + r * 128u + (((ch & 7u) ^ (r & 7u)) << 4);
+                        const float d = __uint_as_float(sc[i]);
+                        auto v = [d](uint32_t w, int b) { return d * (float)(int)(int8_t)(w >> (8 * b)); };
+                        const uint32_t w0 = brc::pack_half2(v(qa[i], 0), v(qa[i], 1)), w1 = brc::pack_half2(v(qa[i], 2), v(qa[i], 3));
+                        const uint32_t w2 = brc::pack_half2(v(qb[i], 0), v(qb[i], 1)), w3 = brc::pack_half2(v(qb[i], 2), v(qb[i], 3));
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst0 + off), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+                    }
+                    brc::mbar_arrive(bar_vfull + 8u * stg);
+                    continue;
+                }
 #pragma unroll
                 for (uint32_t i = 0; i < 16; ++i) {
                     const uint32_t r = r0 + 4u * i;
@@ -547,7 +581,6 @@ brc_status brc_paged_prefill_attn(brc_pool *pool, uint32_t layer, const void *q_
                                   uint32_t table_stride, const uint32_t *pos0_dev, uint32_t n_seqs, uint32_t chunk_len,
                                   uint32_t max_pos_end, float scale, float *out_dev, void *stream) {
     if (!pool) return brc_fail(BRC_ERR_INVALID, "brc_paged_prefill_attn: pool is NULL");
-    BRC_REFUSE_Q8V(pool, "brc_paged_prefill_attn");
     if (pool->device < 0 || !pool->k_base)
         return brc_fail(BRC_ERR_CUDA, "brc_paged_prefill_attn: this pool holds bookkeeping only (no device memory)");
     if (layer >= pool->n_layers)
@@ -585,7 +618,8 @@ brc_status brc_paged_prefill_attn(brc_pool *pool, uint32_t layer, const void *q_
     PrefillParams p;
     p.q = q_dev;
     p.k_layer = pool->k_base + (uint64_t)layer * pool->layer_bytes;
-    p.v_layer = pool->v_base + (uint64_t)layer * pool->layer_bytes;
+    p.v_layer = pool->v_base + (uint64_t)layer * pool->v_layer_bytes;
+    p.v_q8 = pool->v_q8 ? 1u : 0u;
     p.block_tables = block_tables_dev;
     p.pos0 = pos0_dev;
     p.gate = gate_dev;

@@ -104,8 +104,12 @@ BRC_API brc_status brc_pool_create(int32_t device, uint32_t n_layers, uint32_t n
  * the page files (brc_state_dump / _load: the reference's `qsa_vq8` part,
  * crates/breccia-engine/src/graph.rs:2183-2186); brc_pool_read /
  * brc_pool_write / brc_pool_v_ptr, the allocator and the prefix tree;
- * brc_qk_prepare_append (V quantised by the append's rule).  Chunked prefill,
- * which reads V as binary16 tiles, refuses it with BRC_ERR_UNSUPPORTED. */
+ * brc_qk_prepare_append (V quantised by the append's rule); and
+ * brc_paged_prefill_attn, whose loaders dequantise the blocks into the
+ * binary16 V tile (scale x quantum rounded to binary16: up to 2^-11 |v| of
+ * absolute error on top of the binary16 path's).  Every entry point takes it;
+ * only binary16 K/V sources to brc_kv_append are refused (the rule quantises
+ * from f32). */
 #define BRC_V_F16 0
 #define BRC_V_Q8_0 1
 BRC_API brc_status brc_pool_create_q8v(int32_t device, uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim,

@@ -89,13 +89,10 @@ def test_q8_0_v_append_bit_exact_and_sparse_attention(cuda_device, n_head, n_kv,
     pool.release()
 
 
-def test_entry_points_built_for_binary16_v_refuse_a_q8_0_pool(cuda_device):
+def test_binary16_sources_are_refused_on_a_q8_0_pool(cuda_device):
     pool = KvPool(0, 1, 2, 256, 8, v_q8=True)
     x = torch.zeros(4096, device="cuda")
     t = dev_u32(np.zeros((1, 2)))
-    with pytest.raises(_lib.BrcError) as err:      # the tensor-core prefill path reads V as binary16 tiles
-        _lib.call("brc_paged_prefill_attn", pool.handle, 0, P(x), DTYPE_F32, 16, None, 0, P(t), 2, P(t), 1, 16, 16, 0.0625, P(x), None)
-    assert err.value.code == _lib.ERR_UNSUPPORTED and "q8_0" in err.value.message
     with pytest.raises(_lib.BrcError) as err:      # binary16 sources are refused: the rule quantises from f32
         _lib.call("brc_kv_append", pool.handle, 0, P(t), 2, P(t), 1, 1, None, 1, 1, P(x), P(x), _lib.DTYPE_F16, None)
     assert err.value.code == _lib.ERR_UNSUPPORTED
@@ -151,4 +148,43 @@ def test_gather_on_a_q8_0_pool_returns_k_rows_and_the_stored_v_rows(cuda_device)
     assert np.array_equal(k_out.view(torch.int16).cpu().numpy().view(np.uint16).reshape(cells, -1), oracle.f32_to_f16_bits_np(k.reshape(-1)).reshape(cells, -1))
     want_v = q8v.pack_rows(v.reshape(cells * n_kv, hd)).reshape(cells, n_kv, -1)
     assert np.array_equal(v_out.cpu().numpy(), want_v)
+    pool.release()
+
+
+@pytest.mark.parametrize("n_head,pos0,chunk", [(16, 100, 40), (24, 0, 21), (16, 1000, 130)])
+def test_chunked_prefill_over_a_q8_0_v_pool(cuda_device, n_head, pos0, chunk):
+    """The tensor-core prefill path on a q8_0 V pool: the loaders dequantise the blocks into the binary16 V tile
+    (scale x quantum, rounded to binary16).  Oracle: f64 attention over K as binary16 and V as the q8_0 round
+    trip (cpu::to_q8_0).  The binary16 rounding of the dequantised V adds up to 2^-11 |v| (about 4e-4 here) in
+    absolute terms whatever the output's size, so the 2e-3 absolute bar holds everywhere and the 1 % relative bar
+    is applied where |want| > 0.05 (0.02 on binary16 pools, whose V needs no rounding)."""
+    n_kv, hd = 2, 256
+    cells = pos0 + chunk
+    dim = n_kv * hd
+    n_pages = (cells + 15) // 16
+    pool = KvPool(0, 1, n_kv, hd, n_pages + 5, v_q8=True)
+    table = synth.permutation(41 + chunk, n_pages + 5)[:n_pages].astype(np.uint32)
+    pool.alloc(n_pages + 5)
+    k_all = synth.normal(42 + chunk, cells * dim, 0.5).reshape(cells, dim)
+    v_all = synth.normal(43 + chunk, cells * dim, 0.5).reshape(cells, dim)
+    t_dev, zero, k_dev, v_dev = dev_u32(table[None, :]), dev_u32([0]), torch.from_numpy(k_all).cuda(), torch.from_numpy(v_all).cuda()
+    _lib.call("brc_kv_append", pool.handle, 0, P(t_dev), n_pages, P(zero), 1, cells, None, cells, cells, P(k_dev), P(v_dev), DTYPE_F32, None)
+    q = oracle.to_f16(synth.normal(44 + chunk, chunk * n_head * hd)).reshape(1, chunk, n_head, hd)
+    qd = torch.from_numpy(q).cuda().half()
+    out = torch.full((1, chunk, n_head, hd), float("nan"), device="cuda")
+    p_dev = dev_u32([pos0])
+    _lib.call("brc_paged_prefill_attn", pool.handle, 0, P(qd), _lib.DTYPE_F16, n_head, None, 0, P(t_dev), n_pages, P(p_dev), 1, chunk,
+              cells, 1.0 / np.sqrt(hd), P(out), None)
+    pool.check()
+    got = out.cpu().numpy()[0]
+    kf, vq = oracle.to_f16(k_all), q8v.to_q8_0(v_all.reshape(cells * n_kv, hd)).reshape(cells, dim)
+    worst = 0.0
+    for t in range(chunk):
+        want = oracle.attend(q[0, t], kf, vq, np.arange(cells, dtype=np.uint32), pos0 + t, n_head, n_kv, hd)
+        diff = np.abs(got[t].astype(np.float64) - want)
+        big = np.abs(want) > 0.05
+        max_abs, max_rel = float(diff.max()), float((diff[big] / np.abs(want[big])).max()) if big.any() else 0.0
+        worst = max(worst, max_abs)
+        assert np.isfinite(got[t]).all() and max_abs <= ATTN_MAX_ABS and max_rel <= ATTN_MAX_REL, f"row {t}: max_abs {max_abs:.2e} max_rel {max_rel:.2e}"
+    print(f"prefill over q8_0 V, {n_head} heads, pos0 {pos0}, chunk {chunk}: worst max_abs {worst:.2e}")
     pool.release()
