@@ -108,17 +108,6 @@ brc_status brc_fail(brc_status code, const char *fmt, ...) __attribute__((format
                             __FILE__, __LINE__);                                                 \
     } while (0)
 
-// Entry points whose kernels read or write V as binary16 refuse a pool that stores it as q8_0.
-#define BRC_REFUSE_Q8V(pool, who)                                                                                  \
-    do {                                                                                                           \
-        if ((pool)->v_q8)                                                                                          \
-            return brc_fail(BRC_ERR_UNSUPPORTED,                                                                   \
-                            "%s: this pool stores V as q8_0; built for it are brc_kv_append (f32 sources), the dense "  \
-                            "decode entry points (brc_paged_decode_attn, brc_decode_step, brc_splitkv_*), "            \
-                            "brc_paged_sparse_attn, brc_page_copy / brc_seq_fork / brc_page_gather, brc_tier_* / brc_cold_*, the page files, " \
-                            "brc_qk_prepare_append and brc_pool_read / brc_pool_write",                                                           \
-                            who);                                                                                  \
-    } while (0)
 
 // RAII: make the pool's device current for the duration of a call, restore after.
 struct brc_device_guard {

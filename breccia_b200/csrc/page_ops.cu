@@ -202,9 +202,8 @@ uint32_t grid_for(uint64_t work_items, uint32_t block, int sm_count, uint32_t pe
     return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(need, cap));
 }
 
-brc_status need_device_pool(const brc_pool *pool, const char *who, bool q8v_ok = false) {
+brc_status need_device_pool(const brc_pool *pool, const char *who) {
     if (!pool) return brc_fail(BRC_ERR_INVALID, "%s: pool is NULL", who);
-    if (!q8v_ok) BRC_REFUSE_Q8V(pool, who);
     if (pool->device < 0 || !pool->k_base)
         return brc_fail(BRC_ERR_CUDA, "%s: this pool holds bookkeeping only (no device memory); compute calls need a GPU pool",
                         who);
@@ -219,7 +218,7 @@ brc_status brc_kv_append(brc_pool *pool, uint32_t layer, const uint32_t *block_t
                          const uint32_t *pos0_dev, uint32_t n_seqs, uint32_t tokens_per_seq,
                          const uint32_t *cu_tokens_dev, uint32_t total_tokens, uint32_t max_pos_end,
                          const void *k_src_dev, const void *v_src_dev, int32_t src_dtype, void *stream) {
-    if (brc_status rc = need_device_pool(pool, "brc_kv_append", true)) return rc;
+    if (brc_status rc = need_device_pool(pool, "brc_kv_append")) return rc;
     if (pool->v_q8 && src_dtype != BRC_DTYPE_F32)
         return brc_fail(BRC_ERR_UNSUPPORTED, "brc_kv_append: a q8_0 V pool quantises from f32 sources only (src_dtype %d)", src_dtype);
     if (layer >= pool->n_layers)
@@ -273,7 +272,7 @@ brc_status brc_kv_append(brc_pool *pool, uint32_t layer, const uint32_t *block_t
 
 brc_status brc_page_gather(brc_pool *pool, uint32_t layer, const uint32_t *block_table_dev, uint32_t table_len,
                            uint32_t n_tokens, void *k_out_dev, void *v_out_dev, void *stream) {
-    if (brc_status rc = need_device_pool(pool, "brc_page_gather", true)) return rc;
+    if (brc_status rc = need_device_pool(pool, "brc_page_gather")) return rc;
     if (layer >= pool->n_layers)
         return brc_fail(BRC_ERR_INVALID, "brc_page_gather: layer %u but the pool has %u", layer, pool->n_layers);
     if ((uint64_t)n_tokens > (uint64_t)table_len * pool->page_tokens)
@@ -306,7 +305,7 @@ brc_status brc_page_gather(brc_pool *pool, uint32_t layer, const uint32_t *block
 
 brc_status brc_page_copy(brc_pool *pool, const uint32_t *src_ids_dev, const uint32_t *dst_ids_dev, uint32_t n,
                          void *stream) {
-    if (brc_status rc = need_device_pool(pool, "brc_page_copy", true)) return rc;
+    if (brc_status rc = need_device_pool(pool, "brc_page_copy")) return rc;
     if (n == 0) return BRC_OK;
     if (!src_ids_dev || !dst_ids_dev) return brc_fail(BRC_ERR_INVALID, "brc_page_copy: NULL id list");
     if (n > 65535u) return brc_fail(BRC_ERR_INVALID, "brc_page_copy: %u pairs in one call (limit 65535)", n);
@@ -332,7 +331,7 @@ brc_status brc_seq_fork(brc_pool *pool, const uint32_t *parent_table, uint32_t n
     const uint32_t full = n_tokens / pt;
     const bool partial = (n_tokens % pt) != 0;
     if (partial)
-        if (brc_status rc = need_device_pool(pool, "brc_seq_fork (partial last page needs a device copy)", true)) return rc;
+        if (brc_status rc = need_device_pool(pool, "brc_seq_fork (partial last page needs a device copy)")) return rc;
     for (uint32_t i = 0; i < full + (partial ? 1u : 0u); ++i)
         if (parent_table[i] >= pool->n_pages)
             return brc_fail(BRC_ERR_INVALID, "brc_seq_fork: parent table entry %u is page %u of %u", i, parent_table[i],
