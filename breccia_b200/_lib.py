@@ -105,6 +105,7 @@ SIGNATURES = {
     "brc_radix_insert": [_vp, _u32p, _u32, _u32p, _u32, _u32p],
     "brc_radix_evict": [_vp, _u32, _u32p],
     "brc_radix_release": [_vp, _u32p, _u32],
+    "brc_radix_prefix_tags": [_u32p, _u32, _u32, _u64p, _u32, _u32p],
     "brc_radix_stats": [_vp, _u64p, _u64p, _u64p, _u64p],
     "brc_tier_create": [_vp, _u32, _vpp],
     "brc_tier_destroy": [_vp],

@@ -183,6 +183,27 @@ brc_status brc_radix_release(brc_radix *radix, const uint32_t *pages, uint32_t n
     return brc_pages_release(radix->pool, pages, n_pages);
 }
 
+brc_status brc_radix_prefix_tags(const uint32_t *tokens, uint32_t n_tokens, uint32_t page_tokens, uint64_t *out_tags,
+                                 uint32_t capacity, uint32_t *out_n) {
+    if (!out_n || (!tokens && n_tokens) || page_tokens == 0) return brc_fail(BRC_ERR_INVALID, "brc_radix_prefix_tags: NULL argument or zero page size");
+    const uint32_t pages = n_tokens / page_tokens;
+    if (pages > capacity || (pages && !out_tags))
+        return brc_fail(BRC_ERR_CAPACITY, "brc_radix_prefix_tags: %u full pages but room for %u tags", pages, capacity);
+    // splitmix64 finaliser over a running state: the tag of page i depends on every token of pages 0 .. i
+    uint64_t h = 0x9E3779B97F4A7C15ull;
+    for (uint32_t pg = 0; pg < pages; ++pg) {
+        for (uint32_t t = 0; t < page_tokens; ++t) {
+            uint64_t z = h ^ ((uint64_t)tokens[(size_t)pg * page_tokens + t] + 0x9E3779B97F4A7C15ull);
+            z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+            z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+            h = z ^ (z >> 31);
+        }
+        out_tags[pg] = h | 1ull;   // never zero: zero is the cold store's "untagged"
+    }
+    *out_n = pages;
+    return BRC_OK;
+}
+
 brc_status brc_radix_stats(brc_radix *radix, uint64_t *out_nodes, uint64_t *out_hit_pages, uint64_t *out_miss_pages,
                            uint64_t *out_evictions) {
     if (!radix) return brc_fail(BRC_ERR_INVALID, "brc_radix_stats: radix is NULL");

@@ -604,6 +604,15 @@ BRC_API brc_status brc_radix_insert(brc_radix *radix, const uint32_t *tokens, ui
                                     uint32_t n_pages, uint32_t *out_n_new);
 BRC_API brc_status brc_radix_evict(brc_radix *radix, uint32_t n_pages, uint32_t *out_n_evicted);
 BRC_API brc_status brc_radix_release(brc_radix *radix, const uint32_t *pages, uint32_t n_pages);
+/* A 64-bit tag per full page of a prompt, the tag of page i a hash of all tokens
+ * of pages 0 .. i ("blocks identified by their tokens and everything before
+ * them", the design note's hash granularity).  The same prompt gives the same
+ * tags in every process: they are the keys under which prefix pages are spilled
+ * to a cold store (brc_cold_spill) and found again later (brc_cold_find) - the
+ * disk-persisted prefix cache of
+ * docs/reference-engines/02-kv-and-context.md:536-548, 617-626.  Never zero. */
+BRC_API brc_status brc_radix_prefix_tags(const uint32_t *tokens, uint32_t n_tokens, uint32_t page_tokens,
+                                         uint64_t *out_tags, uint32_t capacity, uint32_t *out_n);
 BRC_API brc_status brc_radix_stats(brc_radix *radix, uint64_t *out_nodes, uint64_t *out_hit_pages,
                                    uint64_t *out_miss_pages, uint64_t *out_evictions);
 

@@ -130,3 +130,30 @@ def test_insert_refuses_pages_the_caller_does_not_hold(env):
     new = C.c_uint32()
     assert L.brc_radix_insert(radix, tp, 16, bp, 1, C.byref(new)) == _lib.ERR_INVALID
     assert b"not allocated" in L.brc_last_error()
+
+
+def test_prefix_tags_name_a_page_by_everything_up_to_it():
+    """brc_radix_prefix_tags: one tag per FULL page; equal prefixes give equal tags, a change in an earlier page
+    changes every later tag; the values are fixed (another process must compute the same ones)."""
+    L = _lib.load()
+
+    def tags_of(tokens, cap=16):
+        tokens = np.ascontiguousarray(tokens, np.uint32)
+        out = np.zeros(cap, np.uint64)
+        n = C.c_uint32()
+        rc = L.brc_radix_prefix_tags(tokens.ctypes.data_as(C.POINTER(C.c_uint32)), tokens.size, 16, out.ctypes.data_as(C.POINTER(C.c_uint64)),
+                                     cap, C.byref(n))
+        return rc, out[:n.value]
+
+    a = np.arange(100, dtype=np.uint32)
+    rc, ta = tags_of(a)
+    assert rc == 0 and ta.size == 6 and len(set(ta.tolist())) == 6 and (ta & 1).all()
+    b = a.copy()
+    b[20] = 999                                   # in the second page
+    _, tb = tags_of(b)
+    assert tb[0] == ta[0] and all(tb[i] != ta[i] for i in range(1, 6))
+    assert np.array_equal(tags_of(a[:47])[1], ta[:2])
+    assert tags_of(a[:15])[1].size == 0
+    assert tags_of(a, cap=3)[0] == _lib.ERR_CAPACITY
+    # pinned values: the hash is part of the file format of a persisted prefix
+    assert [hex(int(t)) for t in tags_of(np.zeros(32, np.uint32))[1]] == ['0x94853c2e03ed1ec5', '0x735b619c55021e81']

@@ -342,3 +342,86 @@ def test_q8_0_v_pool_pages_move_between_the_tiers_and_a_file_byte_for_byte(cuda_
     assert L.brc_cold_close(cold) == 0
     L.brc_tier_destroy(tier)
     pool.release()
+
+
+def test_a_prompt_prefix_persisted_to_a_file_is_found_again_by_its_tokens(cuda_device, tmp_path):
+    """The disk-persisted prefix cache end to end: a first "process" fills the pages of a 5-page prompt prefix,
+    demotes them and spills them to a cold store under brc_radix_prefix_tags; a second one (fresh pool, tier, tree
+    and store handle) computes the tags of ITS prompt (the same first four pages, then different tokens), finds
+    four records, fetches and promotes them, adopts them into its prefix tree - and attention over the restored
+    prefix equals attention over the original pages bit for bit."""
+    n_layers, n_kv, hd = 2, 2, 256
+    L = _lib.load()
+    path = str(tmp_path / "prefix.brccold").encode()
+    prompt_a = (np.arange(5 * 16) * 7 + 3).astype(np.uint32)
+    prompt_b = prompt_a.copy()
+    prompt_b[4 * 16 + 5] += 1                                    # the fifth page differs
+    q = torch.randn((1, 16, hd), generator=torch.Generator().manual_seed(5)).cuda().half()
+
+    def tags_of(prompt):
+        tags = np.zeros(8, np.uint64)
+        n = C.c_uint32()
+        assert L.brc_radix_prefix_tags(prompt.ctypes.data_as(C.POINTER(C.c_uint32)), prompt.size, 16, tags.ctypes.data_as(C.POINTER(C.c_uint64)),
+                                       8, C.byref(n)) == 0
+        return tags[:n.value]
+
+    ta, tb = tags_of(prompt_a), tags_of(prompt_b)
+    assert ta.size == 5 and np.array_equal(ta[:4], tb[:4]) and ta[4] != tb[4] and (ta != 0).all() and len(set(ta.tolist())) == 5
+    assert np.array_equal(tags_of(prompt_a[:40]), ta[:2])        # a partial page has no tag
+
+    # ---- first process: compute (here: fill) the prefix, attend, persist
+    pool = KvPool(0, n_layers, n_kv, hd, 16)
+    pages, pp = arr(np.zeros(5))
+    assert L.brc_pages_alloc(pool.handle, 5, pp) == 0
+    for layer in range(n_layers):
+        fill_pool_from_host(pool, layer, 700 + layer)
+    out_a = torch.full((1, 16, hd), float("nan"), device="cuda")
+    DecodeBatch(pool, 16, pages[None, :4].astype(np.uint32), np.array([64])).attend(1, q, out_a)
+    pool.check()
+    tier, cold = C.c_void_p(), C.c_void_p()
+    assert L.brc_tier_create(pool.handle, 8, C.byref(tier)) == 0
+    assert L.brc_cold_open(tier, path, 8, 1, C.byref(cold)) == 0
+    slots, sp = arr(np.zeros(5))
+    assert L.brc_tier_demote(tier, pp, 5, sp, None) == 0
+    recs, rp = arr(np.zeros(5))
+    assert L.brc_cold_spill(cold, sp, ta.ctypes.data_as(C.POINTER(C.c_uint64)), 5, rp) == 0
+    assert L.brc_cold_close(cold) == 0
+    L.brc_tier_destroy(tier)
+    pool.release()
+
+    # ---- second process: another pool (other page ids), the store found on disk
+    pool = KvPool(0, n_layers, n_kv, hd, 24)
+    pool.poison_nan()
+    taken = pool.alloc(7)                                         # so that the restored pages get other ids
+    tier, cold, radix = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    assert L.brc_tier_create(pool.handle, 8, C.byref(tier)) == 0
+    assert L.brc_cold_open(tier, path, 0, 0, C.byref(cold)) == 0
+    assert L.brc_radix_create(pool.handle, C.byref(radix)) == 0
+    found = []
+    one = C.c_uint32()
+    for tag in tb:                                                # the longest run of prefix pages the store holds
+        if L.brc_cold_find(cold, int(tag), C.byref(one)) != 0:
+            break
+        found.append(one.value)
+    assert len(found) == 4
+    f, fp = arr(found)
+    hs, hp = arr(np.zeros(4))
+    assert L.brc_cold_fetch(cold, fp, 4, 1, hp) == 0
+    back, bp = arr(np.zeros(4))
+    assert L.brc_tier_promote(tier, hp, 4, bp) == 0
+    assert L.brc_tier_fence(tier, None) == 0
+    new = C.c_uint32()
+    assert L.brc_radix_insert(radix, prompt_b.ctypes.data_as(C.POINTER(C.c_uint32)), 64, bp, 4, C.byref(new)) == 0 and new.value == 4
+    got, gp = arr(np.zeros(8))
+    n = C.c_uint32()
+    assert L.brc_radix_match(radix, prompt_b.ctypes.data_as(C.POINTER(C.c_uint32)), prompt_b.size, gp, 8, C.byref(n)) == 0 and n.value == 4
+    assert got[:4].tolist() == back.tolist() and not set(back.tolist()) & set(taken.tolist())
+    out_b = torch.full((1, 16, hd), float("nan"), device="cuda")
+    DecodeBatch(pool, 16, got[None, :4].astype(np.uint32), np.array([64])).attend(1, q, out_b)
+    pool.check()
+    assert torch.equal(out_a, out_b)
+    assert L.brc_radix_release(radix, gp, 4) == 0
+    assert L.brc_cold_close(cold) == 0
+    L.brc_radix_destroy(radix)
+    L.brc_tier_destroy(tier)
+    pool.release()
