@@ -502,21 +502,21 @@ def test_partials_then_combine_equals_fused_call(cuda_device):
 
 
 @pytest.mark.parametrize("n_head,n_kv,lens", [
-    (16, 2, [24000]),            # one unit over every CTA: runs of ~13 shares, then the runs
+    (16, 2, [24000]),            # one unit over every CTA: 148 pieces, a handful of (row, column) items per CTA
     (16, 2, [9000, 12000]),      # two units of ~60 and ~85 shares; they meet inside one CTA
     (8, 1, [13000, 40, 9000]),   # one kv head per unit (a 16-row box), a short unit in between
     (32, 4, [30000]),            # two units per sequence (4 kv heads), head_dim 128
 ])
-def test_units_spanning_many_ctas_merge_in_two_levels(cuda_device, n_head, n_kv, lens):
-    """Long sequences alone on the GPU: every unit spans more than 24 CTA shares, so the in-kernel merge
-    runs in two levels (runs of shares, then the runs).  Final output and the partial (acc, m, l) form,
-    twice over, so that the tickets are seen to reset."""
+def test_units_spanning_many_ctas(cuda_device, n_head, n_kv, lens):
+    """Long sequences alone on the GPU: every unit spans dozens of CTA shares, each of which takes a few of the
+    unit's (row, column) items in the merge, several threads per item.  Final output and the partial (acc, m, l)
+    form, twice over, so that the ticket words (never cleared, 2^16 more per launch) are seen to work again."""
     hd = 128 if n_head == 32 else 256
     pool, batch, qd, got, want = _batch_case(n_head, n_kv, hd, lens, seed=120 + len(lens) + n_kv)
-    assert_attention_close(got, want, f"two-level merge {lens}")
+    assert_attention_close(got, want, f"units over many CTAs {lens}")
     again = torch.full_like(torch.from_numpy(got), float("nan")).cuda()
     batch.attend(0, qd, again)
-    assert np.array_equal(again.cpu().numpy(), got), "second launch differs: a ticket was left dirty"
+    assert np.array_equal(again.cpu().numpy(), got), "second launch differs"
     n = len(lens)
     nbytes = decode_partial_bytes(n, n_head, hd)
     part = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
@@ -524,7 +524,7 @@ def test_units_spanning_many_ctas_merge_in_two_levels(cuda_device, n_head, n_kv,
     out = torch.empty((n, n_head, hd), device="cuda")
     decode_combine(0, part, 1, nbytes, n, n_head, hd, out)
     pool.check()
-    assert_attention_close(out.cpu().numpy(), want, f"two-level merge, partial form {lens}")
+    assert_attention_close(out.cpu().numpy(), want, f"units over many CTAs, partial form {lens}")
     pool.release()
 
 
@@ -536,7 +536,7 @@ def test_units_spanning_many_ctas_merge_in_two_levels(cuda_device, n_head, n_kv,
     # fewer page-units than CTAs: shares in between are empty, the unit's pieces are counted from the table
     ("nine pages", [40, 0, 64, 33], 2),
     ("one unit of three pages among four kv heads", [0, 48], 4),
-    # one long unit beside many short ones: the long one spans most CTAs (two-level merge), the short ones share a CTA
+    # one long unit beside many short ones: the long one spans most CTAs, the short ones share a CTA
     ("one long, sixty short", [40000] + [20 + i for i in range(60)], 2),
 ])
 def test_cost_weighted_cut_of_the_page_list(cuda_device, name, lens, n_kv):
