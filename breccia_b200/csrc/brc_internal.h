@@ -22,7 +22,7 @@
 // (ticket words of the units, never cleared by the kernels: every launch adds a fixed amount per unit).
 #define BRC_STATUS_WORDS 64u
 #define BRC_DONE_BANK_WORDS 4096u  // two ticket words per unit of a layer (2048 units at most)
-#define BRC_DONE_BANKS 64u     // one bank per layer of a decode step whose layers overlap
+#define BRC_DONE_BANKS 64u     // one bank per layer of a launch (a launch covers up to 64 layers)
 #define BRC_DONE_WORDS (BRC_DONE_BANK_WORDS * BRC_DONE_BANKS)
 #define BRC_STATUS_BYTES ((BRC_STATUS_WORDS + BRC_DONE_WORDS) * 4u)
 

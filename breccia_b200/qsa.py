@@ -285,7 +285,7 @@ class DecodeBatch:
         self.pos0 = torch.empty_like(self.seq_lens)
         ws_bytes = C.c_uint64()
         _lib.call("brc_decode_workspace_bytes", pool.handle, self.n_seqs, n_head, C.byref(ws_bytes))
-        # one bank of partials per layer: brc_decode_step then lets the layers of a step overlap
+        # partial slots for every layer: brc_decode_step covers all layers of a step in one launch
         self.scratch = torch.empty(pool.n_layers * ws_bytes.value, dtype=torch.uint8, device=dev)
         self.scale = 1.0 / math.sqrt(pool.head_dim)
 

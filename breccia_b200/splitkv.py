@@ -97,8 +97,8 @@ class SplitKvDecode:
 
     def step(self, q: torch.Tensor, out: torch.Tensor, layer0: int = 0) -> None:
         """One decode token over the layers q carries, the layers' attention calls being independent of
-        one another: q [L, 1, n_head, hd] -> out [L, 1, n_head, hd] f32 (contiguous).  The local kernels of
-        all layers overlap; one exchange kernel moves all partials (brc_splitkv_step)."""
+        one another: q [L, 1, n_head, hd] -> out [L, 1, n_head, hd] f32 (contiguous).  One launch streams the
+        local cells of all layers, pushes the merged partials to the peers and merges theirs (brc_splitkv_step)."""
         b = self.batch
         if self.comm is None:
             for i in range(q.shape[0]):

@@ -418,8 +418,8 @@ BRC_API brc_status brc_state_load(brc_pool *pool, uint32_t layer, const uint32_t
  * one another (the counterpart of brc_decode_step for the split-KV case, append
  * excluded): ONE launch whose flat work list runs over (layer, sequence, kv-head
  * group, page), cut into equal shares per SM, so launch ramp and tail are paid
- * once per token and a layer's exchange (see brc_splitkv_attend) overlaps the
- * streaming of the layers behind it.  `workspace_bytes` must be at least n_layers
+ * once per token and the exchange of all layers (see brc_splitkv_attend) is one
+ * round of stores and flags at the end of the launch.  `workspace_bytes` must be at least n_layers
  * times brc_decode_workspace_bytes(); the comm must have been created with
  * max_seqs >= n_layers * n_seqs.  q is [n_layers] arrays `q_layer_stride_bytes`
  * apart; out is [n_layers][n_seqs][n_head][head_dim] f32, contiguous; gate
