@@ -36,8 +36,8 @@ def _u32_array(a) -> np.ndarray:
 
 class KvPool:
     """Paged f16 K/V pools of all layers on one GPU plus the page allocator (brc_pool).  v_q8: V page bodies
-    as q8_0 blocks (the reference's VLayout::Q8_0, qsa/mod.rs:245-349): append from f32 and attention over
-    selected blocks work on such a pool, the dense kernels refuse it."""
+    as q8_0 blocks (the reference's VLayout::Q8_0, qsa/mod.rs:245-349): K stays binary16, append quantises
+    from f32, and every operator reads the blocks."""
 
     def __init__(self, device: int, n_layers: int, n_kv_head: int, head_dim: int, n_pages: int,
                  page_tokens: int = PAGE_CELLS, bookkeeping_only: bool = False, v_q8: bool = False):
@@ -156,11 +156,11 @@ class KvPool:
         return child[:n_pages], (None if fresh.value == 0xFFFFFFFF else fresh.value)
 
     def gather(self, layer: int, block_table_dev: torch.Tensor, n_tokens: int, stream=None):
-        """Cells 0..n_tokens-1 of one sequence -> (K, V) int16-typed tensors [n_tokens, n_kv, head_dim]
-        holding binary16 bits."""
+        """Cells 0..n_tokens-1 of one sequence -> (K, V) tensors [n_tokens, n_kv, head_dim] holding binary16
+        bits; on a q8_0 V pool V is the stored rows, uint8 [n_tokens, n_kv, head_dim / 32 * 36]."""
         dev = f"cuda:{self.device}"
         k = torch.empty((n_tokens, self.n_kv_head, self.head_dim), dtype=torch.float16, device=dev)
-        v = torch.empty_like(k)
+        v = torch.empty((n_tokens, self.n_kv_head, self.head_dim // 32 * 36), dtype=torch.uint8, device=dev) if self.v_q8 else torch.empty_like(k)
         _lib.call("brc_page_gather", self.handle, layer, _ptr(block_table_dev), block_table_dev.numel(), n_tokens,
                   _ptr(k), _ptr(v), _stream_ptr(stream))
         return k, v
