@@ -21,7 +21,7 @@
 // brc_pool::status_dev: 64 words of check state, then the decode kernels' per-unit arrival counters
 // (ticket words of the units, never cleared by the kernels: every launch adds a fixed amount per unit).
 #define BRC_STATUS_WORDS 64u
-#define BRC_DONE_BANK_WORDS 4096u  // two ticket words per unit of a layer (2048 units at most)
+#define BRC_DONE_BANK_WORDS 2048u  // one ticket word per unit of a layer (2048 units at most)
 #define BRC_DONE_BANKS 64u     // one bank per layer of a launch (a launch covers up to 64 layers)
 #define BRC_DONE_WORDS (BRC_DONE_BANK_WORDS * BRC_DONE_BANKS)
 #define BRC_STATUS_BYTES ((BRC_STATUS_WORDS + BRC_DONE_WORDS) * 4u)
@@ -30,6 +30,7 @@
 // call apart, so a peer's next partial must not land on the one still being merged).
 #define BRC_MAX_WORLD 16u
 #define BRC_COMM_BANKS 4u
+#define BRC_PIECE_FLAGS 32u   // flag words per (bank, source rank, unit) of the fused split-KV exchange: one per pushing CTA
 
 // Stage ids of the optional GPU timers are public (breccia_kv.h); this is their count.
 #define BRC_STAGE_COUNT 6

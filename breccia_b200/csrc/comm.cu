@@ -205,7 +205,7 @@ brc_status brc_comm_create(brc_pool *pool, uint32_t world, uint32_t rank, uint32
     const uint64_t ticket_off = c->flags_offset + flag_bytes;
     c->unit_flags_offset = ticket_off + 256;
     c->flag_items = max_seqs * (pool->n_kv_head / brc_decode_kvb(pool));
-    const uint64_t unit_flag_bytes = (((uint64_t)N_BANKS * MAX_WORLD * c->flag_items * 4u) + 255u) & ~255ull;
+    const uint64_t unit_flag_bytes = (((uint64_t)N_BANKS * MAX_WORLD * c->flag_items * BRC_PIECE_FLAGS * 4u) + 255u) & ~255ull;
     const uint64_t local_off = c->unit_flags_offset + unit_flag_bytes;
     c->recv_bytes = local_off + c->slot_stride;
     cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&c->recv), c->recv_bytes);

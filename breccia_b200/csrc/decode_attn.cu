@@ -99,7 +99,7 @@ struct DecodeParams {
     const uint32_t *seq_lens;      // [n_seqs]
     float *part_acc;               // [slots][KVB][GROUP_TILE][HD]
     float *part_ml;                // [slots][KVB][GROUP_TILE][2]
-    uint32_t *done;                // [layer bank][2][2048] ticket words of the units (see TICKET_ALL)
+    uint32_t *done;                // [layer bank][2048] ticket words of the units (see TICKET_ALL)
     float *out;                    // final [n_seqs][n_head][HD]; partial mode: merged acc, same shape
     float *out_ml;                 // partial mode: [n_seqs][n_head][2] (m, l); nullptr = final output
     const float *gate;             // nullable
@@ -208,10 +208,16 @@ __device__ __forceinline__ void st_release_sys(uint32_t *ptr, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
 }
 
-// Flag of (bank, source rank, unit) in the receive buffer `recv`.
+// Flags of (bank, source rank, unit) in the receive buffer `recv`: BRC_PIECE_FLAGS words, one per CTA of the source
+// rank that stores a part of the unit's merged rows.  A flag's value is flag_word(epoch, n): the exchange it belongs
+// to in the low 24 bits, and in the high 8 bits how many CTAs of the source store parts (minus one) - word 0 is
+// always written, so a reader learns from it which of the other words to wait for.
 __device__ __forceinline__ uint32_t *unit_flag(uint8_t *recv, const DecodeParams &p, uint32_t bank, uint32_t src, uint32_t U) {
-    return reinterpret_cast<uint32_t *>(recv + p.flags_offset) + ((size_t)(bank * BRC_MAX_WORLD + src) * p.flag_items + U);
+    return reinterpret_cast<uint32_t *>(recv + p.flags_offset) + ((size_t)(bank * BRC_MAX_WORLD + src) * p.flag_items + U) * BRC_PIECE_FLAGS;
 }
+__device__ __forceinline__ uint32_t flag_word(uint32_t epoch, uint32_t n_parts) { return (epoch & 0xffffffu) | ((n_parts - 1u) << 24); }
+// The flag belongs to exchange `epoch` or a later one (epochs compared modulo 2^24).
+__device__ __forceinline__ bool flag_reached(uint32_t word, uint32_t epoch) { return ((word - epoch) & 0xffffffu) < 0x800000u; }
 
 // Byte offset, inside any rank's receive buffer, of row R of THIS rank's partial in bank `bank`:
 // acc [rows_total][HD] f32, then (m, l) [rows_total][2] f32.
@@ -226,10 +232,8 @@ __device__ __forceinline__ uint64_t push_ml_off(const DecodeParams &p, uint32_t 
 // weights of a unit's pieces add up to exactly 2^16 and no smaller group of them does, so the low 16 bits are zero
 // exactly when no piece or every piece is written - and a CTA that has added its own weight can only see the
 // second.  Nothing is ever cleared: every launch adds 2^16 per unit it streams, whatever k is this time (the
-// high bits count launches and wrap harmlessly).  A second word per unit (TICKET_PUSHED words further on) counts
-// the same way the CTAs that have stored their part of the unit's merged rows to the peers (split-KV across GPUs).
+// high bits count launches and wrap harmlessly).
 constexpr uint32_t TICKET_ALL = 1u << 16, TICKET_LOW = TICKET_ALL - 1u;
-constexpr uint32_t TICKET_PUSHED = 2048u;
 
 __device__ __forceinline__ uint32_t piece_weight(uint32_t j, uint32_t k) { return ((j + 1u) << 16) / k - (j << 16) / k; }
 
@@ -435,8 +439,10 @@ __device__ __forceinline__ void merge_unit(const DecodeParams &p, const UnitRef 
     uint32_t *const ticket = p.done + ur.layer * BRC_DONE_BANK_WORDS + ur.u;
     // The CTA that holds a unit's LAST piece streamed it first thing and has another unit's merge to attend to at
     // its own end: the unit's other CTAs (all of them at the end of their streaming) share the merge among them.
-    if (k > 1u && j == k - 1u) return;                   // CTA-uniform
-    const uint32_t n_part = k > 1u ? k - 1u : 1u;        // CTAs that take part
+    const bool pushing = CAN_PUSH && p.world > 1;
+    uint32_t n_part = k > 1u ? k - 1u : 1u;              // CTAs that take part
+    if (pushing) n_part = min(n_part, BRC_PIECE_FLAGS);  // across GPUs each of them owns one flag word per peer
+    if (j >= n_part) return;                             // CTA-uniform
     // ---- every piece written?  (this CTA's own weight is in: zero low bits mean all of them)
     if (tid == 0 && !gave_up[0]) {
         bool ok = all_written;                           // thread 0 took the unit's last ticket itself: nothing to wait for
@@ -464,22 +470,14 @@ __device__ __forceinline__ void merge_unit(const DecodeParams &p, const UnitRef 
     if (items_c != 0) {
         merge_items<HD, KVB, CAN_PUSH, NT>(p, ur, list, mls, rowml, stage, it0, items_c, k, tid, s, kv0, bank);
     }
-    if (CAN_PUSH && p.world > 1) {
-        // ---- across GPUs: the CTA whose stores land last tells the peers (the pattern of a grid-wide barrier: a CTA
-        //      barrier, then one thread fences - at system scope, the stores went to peers - and counts)
+    if (pushing) {
+        // ---- across GPUs: this CTA's part of the unit is on its way to every rank; after a CTA barrier one thread
+        //      per peer releases this CTA's flag there (a release store orders every store the barrier ordered
+        //      before it, at system scope; one thread per peer, because a thread storing to the peers in turn
+        //      would pay a trip over NVLink per peer).  No count of the CTAs that have stored is kept on this
+        //      side: the flag's value tells the reader how many of them to expect.
         brc::named_bar_sync(1, NT);
-        if (tid == 0) {
-            __threadfence_system();
-            const uint32_t w = piece_weight(j, n_part);
-            const uint32_t old = atomicAdd(ticket + TICKET_PUSHED, w);
-            const bool last = ((old + w) & TICKET_LOW) == 0u;
-            if (last) __threadfence_system();
-            jk[2] = last;
-        }
-        brc::named_bar_sync(1, NT);
-        // one thread per peer: a release store waits for the thread's earlier stores to that scope, so one thread
-        // storing to the peers in turn would pay a trip over NVLink per peer
-        if (jk[2] && tid < p.world) st_release_sys(unit_flag(p.peer_recv[tid], p, bank, p.rank, ur.U), epoch);
+        if (tid < p.world) st_release_sys(unit_flag(p.peer_recv[tid], p, bank, p.rank, ur.U) + j, flag_word(epoch, n_part));
     }
 }
 
@@ -498,21 +496,28 @@ __device__ __forceinline__ void finalize_unit(const DecodeParams &p, const UnitR
     constexpr uint32_t ROWS_PER_PASS = (NW * 32) / TPR;
     const uint32_t n_rows = KVB * p.group;
     if (row_first >= n_rows) return;   // CTA-uniform: more CTAs than rows
-    if (!gave_up[0] && tid < p.world) {
-        const uint32_t *f = unit_flag(p.peer_recv[p.rank], p, bank, tid, ur.U);
-        bool ok = (int32_t)(ld_acquire_sys(f) - epoch) >= 0;
-        if (!ok) {
+    if (!gave_up[0]) {
+        // thread = (source rank, flag word): word 0 tells how many of the rank's CTAs store parts of the unit
+        for (uint32_t t = tid; t < p.world * BRC_PIECE_FLAGS; t += NW * 32) {
+            const uint32_t src = t / BRC_PIECE_FLAGS, part = t % BRC_PIECE_FLAGS;
+            const uint32_t *f = unit_flag(p.peer_recv[p.rank], p, bank, src, ur.U);
+            bool ok = false;
             const uint64_t t0 = globaltimer_ns();
             for (uint32_t i = 0; i < (1u << 30); ++i) {
-                if ((int32_t)(ld_acquire_sys(f) - epoch) >= 0) { ok = true; break; }
+                const uint32_t w0 = ld_acquire_sys(f);
+                if (flag_reached(w0, epoch) && (part == 0u || part > (w0 >> 24) || flag_reached(ld_acquire_sys(f + part), epoch))) {
+                    ok = true;
+                    break;
+                }
                 if ((i & 63u) == 63u && globaltimer_ns() - t0 > p.wait_ns) break;
             }
-        }
-        if (!ok) {
-            gave_up[0] = 1u;   // benign race: every writer stores 1
-            atomicOr(p.status, BRC_DEV_WAIT_LIMIT);
-            p.status[1] = 3000000u + tid;   // which rank's partial never arrived
-            p.status[2] = ur.U;
+            if (!ok) {
+                gave_up[0] = 1u;   // benign race: every writer stores 1
+                atomicOr(p.status, BRC_DEV_WAIT_LIMIT);
+                p.status[1] = 3000000u + src;   // which rank's partial never arrived
+                p.status[2] = ur.U;
+                break;
+            }
         }
     }
     brc::named_bar_sync(1, NW * 32);
@@ -727,7 +732,7 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
         if (push) {
             __threadfence_system();
             __syncthreads();
-            if (tid < p.world) st_release_sys(unit_flag(p.peer_recv[tid], p, bank, p.rank, U), epoch);
+            if (tid < p.world) st_release_sys(unit_flag(p.peer_recv[tid], p, bank, p.rank, U), flag_word(epoch, 1u));
         }
     }
 
