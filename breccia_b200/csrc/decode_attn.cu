@@ -1410,14 +1410,16 @@ uint32_t stages_for(uint32_t head_dim, uint32_t kvb, bool v_q8) {
 }  // namespace
 
 // Shares of a launch's cost per CTA, in proportion to the streaming rates measured by stream_rate_kernel.  OFF unless
-// BRC_DECODE_CALIBRATE=1 is in the environment: measured on B200, the rates differ by -19 .. +16 % between SMs in pure
-// streaming and by about -8 .. +9 % inside the decode kernel, but the launch as a whole is bound by HBM, not by
-// its slowest SM (while the slow CTAs finish alone they stream faster), so shares in proportion to a quarter of
-// the measured deviation bought 0.7 % (skewed lengths) to 1.3 % (32 x 8192) of a 12-layer launch and the full
-// deviation lost 4 % - not worth results whose last bits depend on a measurement.  When on: measured once per
-// device and process (every pool of the device cuts alike), on the first pool of at least 1 GiB (smaller ones
-// would be read from L2); deviations are scaled by BRC_DECODE_RATE_DAMP (default 0.25), rounded to 1/64 and kept
-// within 0.75 .. 1.25.  Never fails the caller: without a measurement the shares stay equal.
+// BRC_DECODE_CALIBRATE=1 is in the environment.  Measured on B200: the rates differ by -19 .. +16 % between SMs in
+// pure streaming and by about -8 .. +9 % inside the decode kernel; a launch as a whole is bound by HBM rather than
+// by its slowest SM (while the slow CTAs finish alone they stream faster), so only a part of the measured
+// deviation is applied (BRC_DECODE_RATE_DAMP, default 0.4).  With that, a 12-layer launch over ONE long sequence
+// gets 3-4 % faster (485 -> 468 us for 131 072 cells, 135.6 -> 130 us for 32 768); the batched workloads move
+// between +1 % and -2 % from box to box, and the q8_0 V path, which is bound by instruction issue and not by the
+// memory system, loses 9 % - hence off by default, and results never depend on a measurement unless asked to.
+// When on: measured once per device and process (every pool of the device cuts alike), on the first pool of at
+// least 1 GiB (smaller ones would be read from L2); deviations are rounded to 1/64 and kept within 0.75 .. 1.25.
+// Never fails the caller: without a measurement the shares stay equal.
 void brc_decode_calibrate(brc_pool *pool) {
     static std::mutex mu;
     static uint32_t *prefix_of_device[64] = {};
@@ -1472,7 +1474,7 @@ void brc_decode_calibrate(brc_pool *pool) {
         return;
     }
     const char *damp_env = std::getenv("BRC_DECODE_RATE_DAMP");
-    const double damp = damp_env && *damp_env ? std::atof(damp_env) : 0.25;
+    const double damp = damp_env && *damp_env ? std::atof(damp_env) : 0.4;
     std::vector<uint32_t> host_prefix(grid + 1);
     double total = 0.0;
     for (uint32_t i = 0; i < grid; ++i) {

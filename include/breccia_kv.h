@@ -236,12 +236,13 @@ BRC_API brc_status brc_seq_fork(brc_pool *pool, const uint32_t *parent_table, ui
  * of them do (always the same SMs are slow); with BRC_DECODE_CALIBRATE=1 in
  * the environment the first pool of at least 1 GiB created on a device in
  * this process measures them once (about a millisecond) and every pool of
- * that device then cuts a launch's work in proportion (gain measured on
- * B200: about 1 %; the last bits of the f32 output then depend on the
- * measurement, which is why it is off by default).  brc_decode_share_rates
- * reports what is in force: *out_n = the number of CTAs and rates[i] = CTA
- * i's share relative to the mean, or *out_n = 0 for equal shares (no
- * counterpart in the reference). */
+ * that device then cuts a launch's work in proportion to a part of the
+ * measured deviation (measured on B200: 3-4 % faster on long single
+ * sequences, +1 .. -2 % on batches, slower on q8_0 V pools; the last bits of
+ * the f32 output then depend on the measurement - off by default).
+ * brc_decode_share_rates reports what is in force: *out_n = the number of
+ * CTAs and rates[i] = CTA i's share relative to the mean, or *out_n = 0 for
+ * equal shares (no counterpart in the reference). */
 BRC_API brc_status brc_decode_share_rates(const brc_pool *pool, float *rates, uint32_t capacity, uint32_t *out_n);
 BRC_API brc_status brc_decode_workspace_bytes(const brc_pool *pool, uint32_t n_seqs, uint32_t n_head,
                                               uint64_t *out_bytes);

@@ -1,7 +1,7 @@
-"""Worker of test_decode_gpu.py::test_shares_in_proportion_to_measured_rates_when_asked, run with
-BRC_DECODE_CALIBRATE=1: a pool of more than 1 GiB measures the streaming rates of the device's SMs, the decode
-launches then cut their work in proportion, and the attention output still matches the oracle.  Prints one line
-and exits 0 / 1."""
+"""Worker of test_decode_gpu.py::test_shares_in_proportion_to_measured_rates_when_asked (run with
+BRC_DECODE_CALIBRATE=1): a pool of more than 1 GiB measures
+the streaming rates of the device's SMs, the decode launches then cut their work in proportion, and the attention
+output still matches the oracle.  Prints one line and exits 0 / 1."""
 import ctypes as C
 import os
 import sys

@@ -549,9 +549,9 @@ def test_cost_weighted_cut_of_the_page_list(cuda_device, name, lens, n_kv):
 
 
 def test_shares_in_proportion_to_measured_rates_when_asked(cuda_device):
-    """BRC_DECODE_CALIBRATE=1: a pool of more than 1 GiB measures the SMs' streaming rates once, launches cut their work
-    in proportion (brc_decode_share_rates reports the shares), and the output still matches the oracle.  Without the
-    variable (every other test of this suite) the shares are equal and the report is empty."""
+    """BRC_DECODE_CALIBRATE=1: a pool of more than 1 GiB measures the SMs' streaming rates once per device, launches
+    cut their work in proportion (brc_decode_share_rates reports the shares), and the output still matches the
+    oracle.  Without the variable (every other test of this suite) the shares are equal and the report is empty."""
     import os
     import subprocess
     import sys
