@@ -121,6 +121,7 @@ SIGNATURES = {
     "brc_comm_connect_ipc": [_vp, _vp, _u32],
     "brc_comm_connect_local": [_vp, _vpp, _u32],
     "brc_comm_set_wait_ms": [_vp, _u32],
+    "brc_comm_reset": [_vp, _vp],
     "brc_comm_destroy": [_vp],
     "brc_splitkv_exchange_combine": [_vp, _vp, _u32, _vp, _u32, _vp, _vp],
     "brc_splitkv_attend": [_vp, _u32, _vp, _i32, _vp, _u32, _vp, _u32, _vp, _u32, _u32, _f32, _vp, _vp, _u64, _vp],

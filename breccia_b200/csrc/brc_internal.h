@@ -30,7 +30,6 @@
 // call apart, so a peer's next partial must not land on the one still being merged).
 #define BRC_MAX_WORLD 16u
 #define BRC_COMM_BANKS 4u
-#define BRC_PIECE_FLAGS 32u   // flag words per (bank, source rank, unit) of the fused split-KV exchange: one per pushing CTA
 
 // Stage ids of the optional GPU timers are public (breccia_kv.h); this is their count.
 #define BRC_STAGE_COUNT 6
@@ -133,8 +132,8 @@ struct brc_push_args {
     uint32_t world = 1, rank = 0;
     uint8_t *peer_recv[BRC_MAX_WORLD] = {};   // receive buffers of all ranks as mapped here ([rank] = this rank's own)
     uint64_t slot_stride = 0, bank_stride = 0;
-    uint64_t flags_offset = 0;                // byte offset of the per-unit flags in a receive buffer
-    uint32_t flag_items = 0;                  // flag words per (bank, source rank)
+    uint64_t push_offset = 0;                 // byte offset, in a receive buffer, of the banks the decode launch stores into
+    uint32_t unit_items = 0;                  // units those banks were sized for
     uint32_t *calls = nullptr;                // exchanges completed on this rank
     uint32_t *fin_ticket = nullptr;           // CTAs of the running launch that have finished
     uint64_t wait_ns = 0;

@@ -164,8 +164,8 @@ struct brc_comm {
     brc_pool *pool = nullptr;
     uint32_t world = 1, rank = 0, max_seqs = 0, n_head = 0;
     uint64_t slot_stride = 0, bank_stride = 0, flags_offset = 0, recv_bytes = 0;
-    uint64_t unit_flags_offset = 0;    // per-(bank, source rank, unit) flags of the fused exchange
-    uint32_t flag_items = 0;           // units the buffers hold: max_seqs x kv-head groups
+    uint64_t push_offset = 0;          // the banks the decode launch itself stores into (kept full of 0xFF words between exchanges)
+    uint32_t unit_items = 0;           // units the buffers hold: max_seqs x kv-head groups
     uint8_t *recv = nullptr;           // this rank's receive buffer (+ flags, + ticket, + local partial)
     uint8_t *local_part = nullptr;     // inside recv's allocation
     uint32_t *ticket = nullptr;        // [0] ticket of the running exchange kernel, [1] exchanges completed, [2] CTAs of the
@@ -203,11 +203,10 @@ brc_status brc_comm_create(brc_pool *pool, uint32_t world, uint32_t rank, uint32
     c->flags_offset = c->bank_stride * N_BANKS;
     const uint64_t flag_bytes = (uint64_t)N_BANKS * MAX_WORLD * FLAG_STRIDE * 4u;
     const uint64_t ticket_off = c->flags_offset + flag_bytes;
-    c->unit_flags_offset = ticket_off + 256;
-    c->flag_items = max_seqs * (pool->n_kv_head / brc_decode_kvb(pool));
-    const uint64_t unit_flag_bytes = (((uint64_t)N_BANKS * MAX_WORLD * c->flag_items * BRC_PIECE_FLAGS * 4u) + 255u) & ~255ull;
-    const uint64_t local_off = c->unit_flags_offset + unit_flag_bytes;
-    c->recv_bytes = local_off + c->slot_stride;
+    c->unit_items = max_seqs * (pool->n_kv_head / brc_decode_kvb(pool));
+    const uint64_t local_off = ticket_off + 256;
+    c->push_offset = local_off + c->slot_stride;
+    c->recv_bytes = c->push_offset + c->bank_stride * N_BANKS;
     cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&c->recv), c->recv_bytes);
     if (e != cudaSuccess) {
         delete c;
@@ -215,6 +214,13 @@ brc_status brc_comm_create(brc_pool *pool, uint32_t world, uint32_t rank, uint32
                         cudaGetErrorString(e));
     }
     e = cudaMemset(c->recv, 0, c->recv_bytes);
+    if (e != cudaSuccess) {
+        cudaFree(c->recv);
+        delete c;
+        return brc_fail(BRC_ERR_CUDA, "brc_comm_create: cudaMemset failed: %s", cudaGetErrorString(e));
+    }
+    // the fused exchange has no flags: an empty slot is one that holds 0xFFFFFFFF in every word
+    e = cudaMemset(c->recv + c->push_offset, 0xFF, c->bank_stride * N_BANKS);
     if (e != cudaSuccess) {
         cudaFree(c->recv);
         delete c;
@@ -292,6 +298,16 @@ brc_status brc_comm_set_wait_ms(brc_comm *c, uint32_t ms) {
     return BRC_OK;
 }
 
+brc_status brc_comm_reset(brc_comm *c, void *stream) {
+    if (!c) return brc_fail(BRC_ERR_INVALID, "brc_comm_reset: NULL handle");
+    brc_device_guard guard(c->pool->device);
+    cudaStream_t st = brc_stream(stream);
+    BRC_CUDA(cudaMemsetAsync(c->recv + c->push_offset, 0xFF, c->bank_stride * N_BANKS, st));   // every slot empty
+    BRC_CUDA(cudaMemsetAsync(c->recv, 0, c->push_offset, st));                                 // flags, tickets, call counts
+    BRC_CUDA(cudaStreamSynchronize(st));
+    return BRC_OK;
+}
+
 brc_status brc_comm_destroy(brc_comm *c) {
     if (!c) return BRC_OK;
     brc_device_guard guard(c->pool->device);
@@ -357,8 +373,8 @@ static brc_push_args push_args_of(const brc_comm *c) {
     for (uint32_t r = 0; r < c->world; ++r) x.peer_recv[r] = c->peer[r];
     x.slot_stride = c->slot_stride;
     x.bank_stride = c->bank_stride;
-    x.flags_offset = c->unit_flags_offset;
-    x.flag_items = c->flag_items;
+    x.push_offset = c->push_offset;
+    x.unit_items = c->unit_items;
     x.calls = c->ticket + 1;
     x.fin_ticket = c->ticket + 2;
     x.wait_ns = c->wait_ns;

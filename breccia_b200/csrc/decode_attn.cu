@@ -130,10 +130,10 @@ struct DecodeParams {
     // split-KV across GPUs (world > 1): merged partials go to the receive buffers, the output is written by
     // the cross-rank merge at the end of the launch
     uint32_t world, rank;
-    uint32_t flag_items;           // flag words per (bank, source rank)
+    uint32_t unit_items;           // units the receive buffers were sized for
     uint32_t rows_total;           // n_layers * n_seqs * n_head: rows of the partial as laid out in a slot
     uint8_t *peer_recv[BRC_MAX_WORLD];
-    uint64_t slot_stride, bank_stride, flags_offset;
+    uint64_t slot_stride, bank_stride, push_offset;   // push_offset: where the banks of this exchange begin in a receive buffer
     uint32_t *calls;               // exchanges completed so far on this rank (device-resident epoch)
     uint32_t *fin_ticket;          // CTAs of this launch that have finished
     uint64_t wait_ns;
@@ -208,24 +208,39 @@ __device__ __forceinline__ void st_release_sys(uint32_t *ptr, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
 }
 
-// Flags of (bank, source rank, unit) in the receive buffer `recv`: BRC_PIECE_FLAGS words, one per CTA of the source
-// rank that stores a part of the unit's merged rows.  A flag's value is flag_word(epoch, n): the exchange it belongs
-// to in the low 24 bits, and in the high 8 bits how many CTAs of the source store parts (minus one) - word 0 is
-// always written, so a reader learns from it which of the other words to wait for.
-__device__ __forceinline__ uint32_t *unit_flag(uint8_t *recv, const DecodeParams &p, uint32_t bank, uint32_t src, uint32_t U) {
-    return reinterpret_cast<uint32_t *>(recv + p.flags_offset) + ((size_t)(bank * BRC_MAX_WORLD + src) * p.flag_items + U) * BRC_PIECE_FLAGS;
+// The exchange carries no flags: a slot of a receive buffer that nothing has been stored to yet holds the word
+// PUSH_EMPTY everywhere (a NaN pattern that no arithmetic produces; a pusher that would send it sends the canonical
+// NaN instead), every 16-byte segment and every (m, l) pair is polled by the very thread that consumes it, and the
+// consumer puts PUSH_EMPTY back when it has read it.  So no store has to be ordered after another one and the
+// senders need neither a fence nor a count of who has stored: what is there is there.  A bank is reused four
+// exchanges later, which a peer cannot begin before this rank has finished the launch that emptied it.
+constexpr uint32_t PUSH_EMPTY = 0xffffffffu;
+
+__device__ __forceinline__ float keep_off_empty(float v) { return __float_as_uint(v) == PUSH_EMPTY ? __uint_as_float(0x7fffffffu) : v; }
+
+__device__ __forceinline__ float4 ld_volatile_f4(const void *ptr) {
+    float4 v;
+    asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(ptr) : "memory");
+    return v;
 }
-__device__ __forceinline__ uint32_t flag_word(uint32_t epoch, uint32_t n_parts) { return (epoch & 0xffffffu) | ((n_parts - 1u) << 24); }
-// The flag belongs to exchange `epoch` or a later one (epochs compared modulo 2^24).
-__device__ __forceinline__ bool flag_reached(uint32_t word, uint32_t epoch) { return ((word - epoch) & 0xffffffu) < 0x800000u; }
+__device__ __forceinline__ float2 ld_volatile_f2(const void *ptr) {
+    float2 v;
+    asm volatile("ld.volatile.global.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(ptr) : "memory");
+    return v;
+}
+__device__ __forceinline__ bool landed(float4 v) {
+    return __float_as_uint(v.x) != PUSH_EMPTY && __float_as_uint(v.y) != PUSH_EMPTY && __float_as_uint(v.z) != PUSH_EMPTY &&
+           __float_as_uint(v.w) != PUSH_EMPTY;
+}
+__device__ __forceinline__ bool landed(float2 v) { return __float_as_uint(v.x) != PUSH_EMPTY && __float_as_uint(v.y) != PUSH_EMPTY; }
 
 // Byte offset, inside any rank's receive buffer, of row R of THIS rank's partial in bank `bank`:
 // acc [rows_total][HD] f32, then (m, l) [rows_total][2] f32.
 __device__ __forceinline__ uint64_t push_acc_off(const DecodeParams &p, uint32_t bank, uint32_t src, size_t R, uint32_t hd, uint32_t d) {
-    return (uint64_t)bank * p.bank_stride + (uint64_t)src * p.slot_stride + (R * hd + d) * 4u;
+    return p.push_offset + (uint64_t)bank * p.bank_stride + (uint64_t)src * p.slot_stride + (R * hd + d) * 4u;
 }
 __device__ __forceinline__ uint64_t push_ml_off(const DecodeParams &p, uint32_t bank, uint32_t src, size_t R, uint32_t hd) {
-    return (uint64_t)bank * p.bank_stride + (uint64_t)src * p.slot_stride + ((size_t)p.rows_total * hd + R * 2u) * 4u;
+    return p.push_offset + (uint64_t)bank * p.bank_stride + (uint64_t)src * p.slot_stride + ((size_t)p.rows_total * hd + R * 2u) * 4u;
 }
 
 // Ticket word of a unit: the CTA that has written piece j of the unit's k pieces adds piece_weight(j, k); the
@@ -296,9 +311,11 @@ __device__ __forceinline__ void merge_emit(const DecodeParams &p, const UnitRef 
     if (CAN_PUSH && p.world > 1) {
         const size_t R = ((size_t)ur.layer * p.n_seqs + s) * p.n_head + head;
         const uint64_t oa = push_acc_off(p, bank, p.rank, R, HD, d), om = push_ml_off(p, bank, p.rank, R, HD);
+        const float4 a4 = make_float4(keep_off_empty(acc.x), keep_off_empty(acc.y), keep_off_empty(acc.z), keep_off_empty(acc.w));
+        const float2 ml2 = make_float2(keep_off_empty(ml.x), keep_off_empty(ml.y));
         for (uint32_t r = 0; r < p.world; ++r) {
-            *reinterpret_cast<float4 *>(p.peer_recv[r] + oa) = acc;
-            if (d == 0) *reinterpret_cast<float2 *>(p.peer_recv[r] + om) = ml;
+            *reinterpret_cast<float4 *>(p.peer_recv[r] + oa) = a4;
+            if (d == 0) *reinterpret_cast<float2 *>(p.peer_recv[r] + om) = ml2;
         }
     } else if (p.out_ml) {
         *reinterpret_cast<float4 *>(p.out + o) = acc;
@@ -441,7 +458,6 @@ __device__ __forceinline__ void merge_unit(const DecodeParams &p, const UnitRef 
     // its own end: the unit's other CTAs (all of them at the end of their streaming) share the merge among them.
     const bool pushing = CAN_PUSH && p.world > 1;
     uint32_t n_part = k > 1u ? k - 1u : 1u;              // CTAs that take part
-    if (pushing) n_part = min(n_part, BRC_PIECE_FLAGS);  // across GPUs each of them owns one flag word per peer
     if (j >= n_part) return;                             // CTA-uniform
     // ---- every piece written?  (this CTA's own weight is in: zero low bits mean all of them)
     if (tid == 0 && !gave_up[0]) {
@@ -470,76 +486,63 @@ __device__ __forceinline__ void merge_unit(const DecodeParams &p, const UnitRef 
     if (items_c != 0) {
         merge_items<HD, KVB, CAN_PUSH, NT>(p, ur, list, mls, rowml, stage, it0, items_c, k, tid, s, kv0, bank);
     }
-    if (pushing) {
-        // ---- across GPUs: this CTA's part of the unit is on its way to every rank; after a CTA barrier one thread
-        //      per peer releases this CTA's flag there (a release store orders every store the barrier ordered
-        //      before it, at system scope; one thread per peer, because a thread storing to the peers in turn
-        //      would pay a trip over NVLink per peer).  No count of the CTAs that have stored is kept on this
-        //      side: the flag's value tells the reader how many of them to expect.
-        brc::named_bar_sync(1, NT);
-        if (tid < p.world) st_release_sys(unit_flag(p.peer_recv[tid], p, bank, p.rank, ur.U) + j, flag_word(epoch, n_part));
-    }
 }
 
-// Cross-rank merge of rows row_first, row_first + row_step, ... of unit `ur` (split-KV across GPUs):
-// waits, with a time limit, until every rank's merged partial of the unit has landed in this rank's
-// receive buffer, then merges the rows, normalises, applies the gate and writes the output.  The rows of a
-// unit are dealt over the CTAs that streamed a share of it, each running this with its NW * 32 consumer
-// threads after it has finished streaming.  All loads of a row (every rank's (m, l) and acc) are issued
-// before any is used: one trip to L2 per row.  On expiry the rows are left as they were, the check word
-// reports it, and the CTA's later waits are skipped.
+// Cross-rank merge of rows row_first, row_first + row_step, ... of unit `ur` (split-KV across GPUs).  The rows of a
+// unit are dealt over the CTAs that streamed a share of it, each running this with its NW * 32 consumer threads
+// after it has finished streaming.  A thread owns one 16-byte segment of a row: it polls, with a time limit,
+// that segment and the row's (m, l) in every rank's slot of this rank's receive buffer until none of them holds
+// PUSH_EMPTY any more (all loads of a sweep are issued together), merges, normalises, applies the gate, writes
+// its segment of the output and puts PUSH_EMPTY back.  On expiry the segment is left as it was, the check word
+// reports it, and the CTA's later waits give up at once.
 template <int HD, int KVB, bool VQ8>
 __device__ __forceinline__ void finalize_unit(const DecodeParams &p, const UnitRef ur, uint32_t row_first, uint32_t row_step,
-                                              uint32_t epoch, uint32_t bank, uint32_t tid, volatile uint32_t *gave_up) {
+                                              uint32_t bank, uint32_t tid, volatile uint32_t *gave_up) {
     constexpr int NW = consumer_warps(VQ8);
     constexpr uint32_t TPR = HD / 4;
     constexpr uint32_t ROWS_PER_PASS = (NW * 32) / TPR;
     const uint32_t n_rows = KVB * p.group;
     if (row_first >= n_rows) return;   // CTA-uniform: more CTAs than rows
-    if (!gave_up[0]) {
-        // thread = (source rank, flag word): word 0 tells how many of the rank's CTAs store parts of the unit
-        for (uint32_t t = tid; t < p.world * BRC_PIECE_FLAGS; t += NW * 32) {
-            const uint32_t src = t / BRC_PIECE_FLAGS, part = t % BRC_PIECE_FLAGS;
-            const uint32_t *f = unit_flag(p.peer_recv[p.rank], p, bank, src, ur.U);
-            bool ok = false;
-            const uint64_t t0 = globaltimer_ns();
-            for (uint32_t i = 0; i < (1u << 30); ++i) {
-                const uint32_t w0 = ld_acquire_sys(f);
-                if (flag_reached(w0, epoch) && (part == 0u || part > (w0 >> 24) || flag_reached(ld_acquire_sys(f + part), epoch))) {
-                    ok = true;
-                    break;
-                }
-                if ((i & 63u) == 63u && globaltimer_ns() - t0 > p.wait_ns) break;
-            }
-            if (!ok) {
-                gave_up[0] = 1u;   // benign race: every writer stores 1
-                atomicOr(p.status, BRC_DEV_WAIT_LIMIT);
-                p.status[1] = 3000000u + src;   // which rank's partial never arrived
-                p.status[2] = ur.U;
-                break;
-            }
-        }
-    }
-    brc::named_bar_sync(1, NW * 32);
-    const uint32_t skip = gave_up[0];
-    brc::named_bar_sync(1, NW * 32);   // nobody sets the flag for the next unit before everyone has read it
-    if (skip) return;
     const uint32_t n_groups = p.n_kv_head / KVB;
     const uint32_t s = ur.u / n_groups, kv0 = (ur.u % n_groups) * KVB;
     const uint32_t d = (tid % TPR) * 4;
-    const uint8_t *own = p.peer_recv[p.rank];
+    uint8_t *own = p.peer_recv[p.rank];
+    const float4 empty4 = make_float4(__uint_as_float(PUSH_EMPTY), __uint_as_float(PUSH_EMPTY), __uint_as_float(PUSH_EMPTY),
+                                      __uint_as_float(PUSH_EMPTY));
     for (uint32_t row = row_first + (tid / TPR) * row_step; row < n_rows; row += ROWS_PER_PASS * row_step) {
         const uint32_t k2 = row / p.group, h = row % p.group;
         const uint32_t head = (kv0 + k2) * p.group_all + p.head0 + h;
         const size_t R = ((size_t)ur.layer * p.n_seqs + s) * p.n_head + head;
         float2 ml[BRC_MAX_WORLD];
         float4 a[BRC_MAX_WORLD];
+        bool ok = false;
+        const uint64_t t0 = globaltimer_ns();
+        for (uint32_t i = 0; i < (1u << 30) && !gave_up[0]; ++i) {
+            bool all = true;
 #pragma unroll
-        for (uint32_t r = 0; r < BRC_MAX_WORLD; ++r) {
-            if (r < p.world) {
-                ml[r] = __ldcg(reinterpret_cast<const float2 *>(own + push_ml_off(p, bank, r, R, HD)));
-                a[r] = __ldcg(reinterpret_cast<const float4 *>(own + push_acc_off(p, bank, r, R, HD, d)));
+            for (uint32_t r = 0; r < BRC_MAX_WORLD; ++r) {
+                if (r < p.world) {
+                    ml[r] = ld_volatile_f2(own + push_ml_off(p, bank, r, R, HD));
+                    a[r] = ld_volatile_f4(own + push_acc_off(p, bank, r, R, HD, d));
+                }
             }
+#pragma unroll
+            for (uint32_t r = 0; r < BRC_MAX_WORLD; ++r)
+                if (r < p.world) all = all && landed(ml[r]) && landed(a[r]);
+            if (all) {
+                ok = true;
+                break;
+            }
+            if ((i & 15u) == 15u && globaltimer_ns() - t0 > p.wait_ns) break;
+        }
+        if (!ok) {
+            if (!gave_up[0]) {
+                gave_up[0] = 1u;   // benign race: every writer stores 1
+                atomicOr(p.status, BRC_DEV_WAIT_LIMIT);
+                p.status[1] = 3000000u + p.rank;   // a rank's partial never arrived here
+                p.status[2] = ur.U;
+            }
+            continue;
         }
         float M = -INFINITY;
 #pragma unroll
@@ -568,6 +571,18 @@ __device__ __forceinline__ void finalize_unit(const DecodeParams &p, const UnitR
             o.w *= sigmoid_f32(g[3]);
         }
         *reinterpret_cast<float4 *>(p.out + ur.layer * p.out_layer_stride + ((size_t)s * p.n_head + head) * HD + d) = o;
+        for (uint32_t r = 0; r < p.world; ++r) *reinterpret_cast<float4 *>(own + push_acc_off(p, bank, r, R, HD, d)) = empty4;
+    }
+    // ---- the (m, l) of a row is read by every thread of the row: it is emptied when all of them are through
+    brc::named_bar_sync(1, NW * 32);
+    if (d == 0 && !gave_up[0]) {
+        for (uint32_t row = row_first + (tid / TPR) * row_step; row < n_rows; row += ROWS_PER_PASS * row_step) {
+            const uint32_t k2 = row / p.group, h = row % p.group;
+            const uint32_t head = (kv0 + k2) * p.group_all + p.head0 + h;
+            const size_t R = ((size_t)ur.layer * p.n_seqs + s) * p.n_head + head;
+            for (uint32_t r = 0; r < p.world; ++r)
+                *reinterpret_cast<float2 *>(own + push_ml_off(p, bank, r, R, HD)) = make_float2(empty4.x, empty4.y);
+        }
     }
 }
 
@@ -728,11 +743,6 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
                 om[0] = -INFINITY;
                 om[1] = 0.f;
             }
-        }
-        if (push) {
-            __threadfence_system();
-            __syncthreads();
-            if (tid < p.world) st_release_sys(unit_flag(p.peer_recv[tid], p, bank, p.rank, U), flag_word(epoch, 1u));
         }
     }
 
@@ -1272,7 +1282,7 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
                 brc::named_bar_sync(1, NW * 32);
                 unit_pieces(B, all_shares_live, i_lo, i_hi, tid, NW * 32, reinterpret_cast<uint16_t *>(scratch),
                             reinterpret_cast<volatile uint32_t *>(reinterpret_cast<uint16_t *>(scratch) + MAX_CTAS), j, k);
-                finalize_unit<HD, KVB, VQ8>(p, ur, j, k, epoch, bank, tid, gave_up);
+                finalize_unit<HD, KVB, VQ8>(p, ur, j, k, bank, tid, gave_up);
             }
             if (++fu == n_units) {
                 fu = 0;
@@ -1284,7 +1294,7 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
         const uint32_t fl = U / n_units, fu = U - fl * n_units;
         if (S[fu + 1] != S[fu]) continue;
         const UnitRef ur = {U, fl, fu};
-        finalize_unit<HD, KVB, VQ8>(p, ur, 0, 1, epoch, bank, tid, gave_up);
+        finalize_unit<HD, KVB, VQ8>(p, ur, 0, 1, bank, tid, gave_up);
     }
     // ---- the launch's last CTA advances the epoch (every CTA has read it by now)
     brc::named_bar_sync(1, NW * 32);
@@ -1741,16 +1751,16 @@ brc_status brc_decode_layers(brc_pool *pool, const char *who, const brc_layers_a
                 const brc_push_args &x = *a.push;
                 p.world = x.world;
                 p.rank = x.rank;
-                p.flag_items = x.flag_items;
+                p.unit_items = x.unit_items;
                 p.rows_total = nl * ns * a.n_head;
                 for (uint32_t r = 0; r < x.world; ++r) p.peer_recv[r] = x.peer_recv[r];
                 p.slot_stride = x.slot_stride;
                 p.bank_stride = x.bank_stride;
-                p.flags_offset = x.flags_offset;
+                p.push_offset = x.push_offset;
                 p.calls = x.calls;
                 p.fin_ticket = x.fin_ticket;
                 p.wait_ns = x.wait_ns;
-                if ((uint64_t)nl * ns * n_groups > x.flag_items || (uint64_t)p.rows_total * (hd + 2u) * 4u > x.slot_stride)
+                if ((uint64_t)nl * ns * n_groups > x.unit_items || (uint64_t)p.rows_total * (hd + 2u) * 4u > x.slot_stride)
                     return brc_fail(BRC_ERR_CAPACITY, "%s: %u layers x %u sequences exceed the exchange buffers", who, nl, ns);
             }
             // A tile holds GROUP_TILE query heads per kv head.  More than that (the reference model has 12) are

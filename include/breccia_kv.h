@@ -317,18 +317,23 @@ BRC_API brc_status brc_paged_decode_attn_static(brc_pool *pool, uint32_t layer, 
  * brc_comm_connect_local with the handles of all ranks).
  *
  * brc_splitkv_attend = ONE launch of the split-KV attention kernel over this
- * rank's cells in which the exchange rides along: the CTA that completes a
- * (sequence, kv-head group) unit stores its merged partial (16 512 bytes per
+ * rank's cells in which the exchange rides along: the CTAs that merge a
+ * (sequence, kv-head group) unit store its merged partial (16 512 bytes per
  * sequence at 16 heads of 256) into this rank's slot of every rank's receive
- * buffer with ordinary global stores over NVLink and releases one flag per unit
- * and rank; the CTA that owns the unit waits, after it has finished streaming,
- * for all ranks' flags (time limit, default 1 s: on expiry the unit's output rows
- * are left untouched and brc_pool_check reports BRC_ERR_TIMEOUT), merges and
- * writes the output.  Every rank computes the same output.  All ranks must make
- * the same sequence of calls with the same n_seqs / n_layers.  No load ever
- * targets peer memory and nothing is multicast.  The workspace must hold the
- * partial slots of the whole call (brc_decode_workspace_bytes() per layer);
- * at most 64 layers and 2048 (sequence, kv-head group) units per call.
+ * buffer with ordinary global stores over NVLink.  There are no flags and no
+ * fences on that path: an empty slot holds the word 0xFFFFFFFF throughout, and
+ * the thread that needs a 16-byte segment polls that very segment in every
+ * rank's slot (time limit, default 1 s: on expiry the segment of the output is
+ * left untouched and brc_pool_check reports BRC_ERR_TIMEOUT), merges, writes
+ * the output and empties the slot again.  Every rank computes the same output.
+ * All ranks must make the same sequence of calls with the same n_seqs /
+ * n_layers.  No load ever targets peer memory and nothing is multicast.  The
+ * workspace must hold the partial slots of the whole call
+ * (brc_decode_workspace_bytes() per layer); at most 64 layers and 2048
+ * (sequence, kv-head group) units per call.  After a BRC_ERR_TIMEOUT the
+ * receive buffers may hold what arrived too late: every rank calls
+ * brc_comm_reset (which empties them and restarts the call count) before the
+ * group exchanges again.
  * brc_splitkv_exchange_combine is the exchange alone, as a kernel of its own,
  * for a partial the caller already holds (partial_dev NULL = the comm's own
  * buffer). */
@@ -339,6 +344,7 @@ BRC_API brc_status brc_comm_ipc_handle(brc_comm *comm, void *handle_out64);
 BRC_API brc_status brc_comm_connect_ipc(brc_comm *comm, const void *handles, uint32_t n_handles);
 BRC_API brc_status brc_comm_connect_local(brc_comm *comm, brc_comm *const *comms, uint32_t n_comms);
 BRC_API brc_status brc_comm_set_wait_ms(brc_comm *comm, uint32_t ms);
+BRC_API brc_status brc_comm_reset(brc_comm *comm, void *stream);
 BRC_API brc_status brc_comm_destroy(brc_comm *comm);
 BRC_API brc_status brc_splitkv_exchange_combine(brc_comm *comm, const void *partial_dev, uint32_t n_seqs,
                                                 const float *gate_dev, uint32_t gate_head_stride,
