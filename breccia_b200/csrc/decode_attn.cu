@@ -39,9 +39,10 @@
 //     decode token instead of once per layer, and most units lie inside one CTA's share;
 //   * split-KV across GPUs rides in the same launch: the CTAs that merge a unit store its merged
 //     (acc, m, l) into this rank's slot of every peer's receive buffer with plain global stores over
-//     NVLink, and the last of them releases one flag per (unit, peer); the same CTAs then wait (bounded)
-//     for all ranks' flags, merge the ranks' rows and write the output: the exchange of all layers of a
-//     token is one round of stores and flags at the end of one launch.  No load targets peer memory.
+//     NVLink - no flags, no fences: an empty slot holds 0xFFFFFFFF words, and the same CTAs then poll
+//     (bounded), segment by segment, all ranks' slots of their own buffer, merge the ranks' rows, write
+//     the output and empty the slots again: the exchange of all layers of a token is one round of stores
+//     at the end of one launch.  No load targets peer memory.
 //
 // HBM-bound by design: 8 FLOP per cached byte, all of it on the tensor pipe.
 #include <algorithm>
