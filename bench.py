@@ -15,7 +15,7 @@ device time.  Rank 0 prints ONE JSON line, which also carries
                     layer_by_layer_fused: one fused launch per layer
     strong          the same 32 sequences dealt round-robin by descending length over the N GPUs
     splitkv         the long-context workload: ONE sequence of 131 072 cells whose KV range is split over the
-                    N GPUs, partials pushed to the peers by the attention kernel itself and merged there
+                    N GPUs, partials stored into the peers' memory by the attention kernel itself and merged there
                     (the only path that communicates), with the output checked against the CPU oracle
     fixed8k         (N = 1) the 32 x 8192 variant of the batched workload
     q8v             (N = 1) the batched workload on a pool whose V page bodies are q8_0
@@ -556,8 +556,9 @@ def bench_splitkv(ctx, args, steps):
             "exchange_and_merge_ms_per_step": ms_step - ms_local,
             "one_gpu_same_run_ms_per_step": ms_one, "speedup_vs_one_gpu_same_run": ms_one / ms_step,
             "exchange": "merged (acc, m, l) of each (layer, kv-head group) stored into every peer's receive buffer by the attention "
-                        "kernel (16 512 B per layer per peer, plain stores over NVLink, one release flag per unit and peer), merged by the "
-                        "CTA that owns the unit in the same launch; no NCCL collective on the data path",
+                        "kernel (16 512 B per layer per peer, plain stores over NVLink, no flags or fences: an empty slot holds 0xFFFFFFFF "
+                        "words and the consumer polls the segment it needs), merged by the CTAs of the unit in the same launch; no NCCL "
+                        "collective on the data path",
             "max_abs_vs_cpu_oracle": max_abs, "identical_on_all_ranks": same, "tolerance": "max-abs 2e-3 (measured ~1e-8)"}
 
 
