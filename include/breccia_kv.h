@@ -310,7 +310,8 @@ BRC_API brc_status brc_paged_decode_attn_static(brc_pool *pool, uint32_t layer, 
  *
  * A brc_comm is one rank's end of the exchange: a receive buffer in this rank's
  * HBM with one slot per source rank (and four banks, so that ranks may be a
- * call apart), plus release flags.  Peers map it either through CUDA IPC (one
+ * call apart; the separate exchange kernel also keeps release flags there).
+ * Peers map it either through CUDA IPC (one
  * process per GPU: pass the 64-byte handles of all ranks, in rank order, to
  * brc_comm_connect_ipc; how they travel between processes is the caller's
  * business) or directly (one process driving several GPUs:
@@ -426,7 +427,7 @@ BRC_API brc_status brc_state_load(brc_pool *pool, uint32_t layer, const uint32_t
  * excluded): ONE launch whose flat work list runs over (layer, sequence, kv-head
  * group, page), cut into equal shares per SM, so launch ramp and tail are paid
  * once per token and the exchange of all layers (see brc_splitkv_attend) is one
- * round of stores and flags at the end of the launch.  `workspace_bytes` must be at least n_layers
+ * round of stores at the end of the launch.  `workspace_bytes` must be at least n_layers
  * times brc_decode_workspace_bytes(); the comm must have been created with
  * max_seqs >= n_layers * n_seqs.  q is [n_layers] arrays `q_layer_stride_bytes`
  * apart; out is [n_layers][n_seqs][n_head][head_dim] f32, contiguous; gate
