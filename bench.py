@@ -55,6 +55,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--only-headline", action="store_true",
                     help="skip the strong / splitkv / fixed8k sub-benchmarks (small profiler captures)")
+    ap.add_argument("--only-q8v", action="store_true",
+                    help="run the q8_0 V variant of the batched workload alone and print its object (small profiler captures)")
     ap.add_argument("--layers", type=int, default=12,
                     help="attention layers per step (12 = the full workload; fewer only for small profiler captures)")
     return ap.parse_args()
@@ -565,6 +567,9 @@ def bench_splitkv(ctx, args, steps):
 def run_native(args):
     ctx = Ctx(args)
     steps, warmup = args.steps, max(args.warmup, 0)
+    if args.only_q8v:
+        print(json.dumps(bench_q8v(ctx, args, steps, warmup)), flush=True)
+        return
     peak, peak_src = measured_peaks()
     full = not args.only_headline
     sampler = ClockSampler(ctx.local) if ctx.rank == 0 else None
