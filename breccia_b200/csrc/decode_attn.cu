@@ -1517,8 +1517,8 @@ uint32_t grid_ctas(const brc_pool *pool) { return std::min<uint32_t>((uint32_t)(
 
 // What every unit it touches costs a CTA on top of the unit's pages (merge of the warps, partial or output
 // written, ticket, perhaps the unit's merge), in page-units of this pool.  Measured on the 32-sequence batches
-// of skewed and of equal lengths: an isolated launch gets faster up to about 12 page-units of 32 KiB (66 -> 62 us
-// and 103 -> 100 us), a 12-layer launch by 2 %, and nothing changes beyond; hence 384 KiB worth of page-units.
+// of skewed and of equal lengths: an isolated launch gets faster up to about 16 page-units of 32 KiB (64 -> 60 us
+// and 101 -> 98 us), a 12-layer launch by 1.5 %, and nothing changes beyond; hence 512 KiB worth of page-units.
 // BRC_DECODE_UNIT_COST in the environment overrides it (0 = cut into equal numbers of page-units).
 uint32_t unit_cost_of(uint32_t head_dim, uint32_t kvb, bool v_q8) {
     static const long env = [] {
@@ -1526,7 +1526,7 @@ uint32_t unit_cost_of(uint32_t head_dim, uint32_t kvb, bool v_q8) {
         return e && *e ? std::strtol(e, nullptr, 10) : -1L;
     }();
     if (env >= 0) return (uint32_t)std::min(env, 64L);
-    return std::max<uint32_t>(1u, (384u * 1024u + stage_bytes_of(head_dim, kvb, v_q8) / 2u) / stage_bytes_of(head_dim, kvb, v_q8));
+    return std::max<uint32_t>(1u, (512u * 1024u + stage_bytes_of(head_dim, kvb, v_q8) / 2u) / stage_bytes_of(head_dim, kvb, v_q8));
 }
 
 // Partial slots of one launch over `n_layers` layers of `n_seqs` sequences: one per (layer, unit) plus one
