@@ -760,11 +760,13 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
             const uint32_t k = k0 + lane;
             uint32_t row = 0;
             uint32_t app = 0;  // fused append: bit 31 = this page holds the sequence's newest cell, then cell (4 bits), layer (6), unit (11)
+            uint32_t q_of = 0xffffffffu;   // (layer << 16 | unit) when this page opens a unit the consumers have not reached yet
             if (k < count) {
                 const uint32_t g = a + k;
                 const uint32_t layer = g / total_l, gl = g - layer * total_l;
                 const uint32_t u = unit_of(S, n_units, gl);
                 const uint32_t s = u / n_groups, kv0 = (u % n_groups) * KVB;
+                if (k > 0 && gl == S[u]) q_of = (layer << 16) | u;
                 uint32_t page = __ldg(p.block_tables + (uint64_t)s * p.table_stride + (gl - S[u]));
                 if (page >= p.n_pages) {
                     atomicOr(p.status, BRC_DEV_BAD_PAGE);
@@ -778,6 +780,20 @@ __global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
                         app = 0x80000000u | (((len - 1u) & 15u) << 24) | (layer << 16) | u;
                 }
                 row = p.layer_row0 + layer * p.layer_rows + (page * p.n_kv_head + kv0) * 16u;
+            }
+            // The consumers load a unit's query rows when they reach its first page, a ring's depth from now:
+            // bring the rows into L2 meanwhile (they may lie in host memory, a PCIe round trip away).
+            for (uint32_t opens = __ballot_sync(0xffffffffu, q_of != 0xffffffffu); opens; opens &= opens - 1u) {
+                const uint32_t qo = __shfl_sync(0xffffffffu, q_of, __ffs(opens) - 1);
+                const uint32_t ql = qo >> 16, qu = qo & 0xffffu;
+                const uint32_t q_elem = Q_F32 ? 4u : 2u, head_bytes = p.group * HD * q_elem;
+#pragma unroll
+                for (int k2 = 0; k2 < KVB; ++k2) {
+                    const uint64_t first = ql * p.q_layer_stride + ((uint64_t)(qu / n_groups) * p.n_head + ((qu % n_groups) * KVB + k2) * p.group_all + p.head0) * HD;
+                    const uint8_t *rows = static_cast<const uint8_t *>(p.q) + first * q_elem;
+                    for (uint32_t off = lane * 128u; off < head_bytes; off += 32u * 128u)
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(rows + off));
+                }
             }
             const uint32_t n_here = min(32u, count - k0);
             for (uint32_t i = 0; i < n_here; ++i) {

@@ -350,14 +350,14 @@ class DecodeBatch:
         return torch.empty(need.value, dtype=torch.uint8, device=self.seq_lens.device)
 
     def step_host(self, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor, out_host: torch.Tensor,
-                  staging: torch.Tensor, layer0: int = 0, parts: int = 1, kv_dtype: int = DTYPE_F32,
-                  download: bool = False) -> None:
-        """The same step for a caller whose activations live in (pinned) host memory, one call into the
-        library (brc_decode_step_host): q / k / v are uploaded, the kernels store the attention output
-        straight into a pinned out_host (a pageable one is downloaded).  `parts` > 1 uploads the layers in
-        groups on a second stream; on the machines measured the hand-over between the streams cost more
-        than the hidden copy saved, so one part is the default.  Returns when out_host is complete.
-        `staging` comes from host_staging()."""
+                  staging: torch.Tensor | None, layer0: int = 0, parts: int = 1, kv_dtype: int = DTYPE_F32,
+                  download: bool = False, upload: bool = False) -> None:
+        """The same step for a caller whose activations live in host memory, one call into the library
+        (brc_decode_step_host).  Pinned q / k / v are read by the kernels where they lie and the attention
+        output is stored straight into a pinned out_host; pageable buffers (or `upload` / `download`) go
+        through `staging` (from host_staging()).  `parts` > 1 uploads the layers in groups on a second
+        stream; on the machines measured the hand-over between the streams cost more than the hidden copy
+        saved, so one part is the default.  Returns when out_host is complete."""
         for t in (q_host, k_host, v_host, out_host):
             if t.is_cuda or not t.is_contiguous():
                 raise ValueError("step_host takes contiguous host tensors")
@@ -365,11 +365,13 @@ class DecodeBatch:
             raise BrcError(_lib.ERR_CAPACITY, f"decode step would write cell {int(self.seq_lens_host.max())} but each "
                                               f"block table holds {self.capacity}")
         self.seq_lens_host += 1
-        _lib.call("brc_decode_step_host", self.pool.handle, layer0, q_host.shape[0], parts, 1 if download else 0,
+        _lib.call("brc_decode_step_host", self.pool.handle, layer0, q_host.shape[0], parts,
+                  (1 if download else 0) | (2 if upload else 0),
                   _ptr(self.block_tables),
                   self.table_stride, _ptr(self.seq_lens), _ptr(self.pos0), self.n_seqs, int(self.seq_lens_host.max()),
                   _ptr(q_host), self.q_dtype, self.n_head, _ptr(k_host), _ptr(v_host), kv_dtype, self.scale, _ptr(out_host),
-                  _ptr(staging), staging.numel(), _ptr(self.scratch), self.scratch.numel(), _stream_ptr())
+                  _ptr(staging), staging.numel() if staging is not None else 0, _ptr(self.scratch), self.scratch.numel(),
+                  _stream_ptr())
 
     def reset_lengths(self, seq_lens) -> None:
         self.seq_lens_host = np.asarray(seq_lens, np.int64).copy()

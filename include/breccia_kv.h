@@ -489,24 +489,30 @@ BRC_API brc_status brc_decode_step_part(brc_pool *pool, uint32_t layer0, uint32_
                                         uint64_t out_layer_stride_bytes, void *workspace_dev,
                                         uint64_t workspace_bytes, void *stream);
 
-/* The same step for a caller whose activations live in HOST memory (pinned, or the
- * copies are synchronous): q_host [n_layers][n_seqs][n_head][head_dim] (q_dtype),
- * k_new_host / v_new_host [n_layers][n_seqs][n_kv_head*head_dim] (kv_dtype),
- * out_host [n_layers][n_seqs][n_head][head_dim] f32, all contiguous.  The layers go
- * in `parts` groups (1..8, clamped to n_layers): uploads run ahead on a stream of
- * the pool's own and each group's kernels go to `stream` (brc_decode_step_part), so
- * only the first group's upload is not hidden behind the attention kernels.  When
- * out_host is pinned (addressable from the device) the kernels store the output
- * straight into it and nothing is downloaded; otherwise each group's output leaves
- * on a third stream while the next group computes.  `staging_dev` (256-byte aligned, at least
- * brc_decode_step_host_staging_bytes()) holds the device copies and belongs to the
- * call while it runs.  Returns when out_host is complete; `stream` is ordered after
- * the downloads.  Positions, block tables and the workspace are device-resident as
- * for brc_decode_step. */
+/* The same step for a caller whose activations live in HOST memory:
+ * q_host [n_layers][n_seqs][n_head][head_dim] (q_dtype), k_new_host / v_new_host
+ * [n_layers][n_seqs][n_kv_head*head_dim] (kv_dtype), out_host
+ * [n_layers][n_seqs][n_head][head_dim] f32, all contiguous.
+ *   Pinned buffers (addressable from the device) are used in place: the kernels
+ * read q / k / v over PCIe as they reach each (layer, sequence) and store the output
+ * straight into out_host, so the step's bytes cross the link while the attention
+ * runs, nothing is staged and `staging_dev` may be NULL.  (The three inputs are
+ * taken in place together or not at all.)
+ *   Pageable buffers, or BRC_STEP_HOST_UPLOAD / BRC_STEP_HOST_DOWNLOAD in `flags`,
+ * go through `staging_dev` (256-byte aligned, at least
+ * brc_decode_step_host_staging_bytes(); it belongs to the call while it runs): the
+ * layers go in `parts` groups (1..8, clamped to n_layers), uploads run ahead on a
+ * stream of the pool's own and each group's kernels go to `stream`
+ * (brc_decode_step_part); a staged output leaves group by group on a third stream
+ * while the next group computes.
+ *   Returns when out_host is complete; `stream` is ordered after everything the call
+ * issued.  Positions, block tables and the workspace are device-resident as for
+ * brc_decode_step. */
 BRC_API brc_status brc_decode_step_host_staging_bytes(const brc_pool *pool, uint32_t n_layers, uint32_t n_seqs,
                                                       uint32_t n_head, int32_t q_dtype, int32_t kv_dtype,
                                                       uint64_t *out_bytes);
 #define BRC_STEP_HOST_DOWNLOAD 1u /* flags: stage the output on the device and copy it down even when out_host is pinned */
+#define BRC_STEP_HOST_UPLOAD 2u   /* flags: copy q / k / v to the device first even when they are pinned */
 BRC_API brc_status brc_decode_step_host(brc_pool *pool, uint32_t layer0, uint32_t n_layers, uint32_t parts, uint32_t flags,
                                         const uint32_t *block_tables_dev, uint32_t table_stride,
                                         uint32_t *seq_lens_dev, uint32_t *pos0_dev, uint32_t n_seqs,

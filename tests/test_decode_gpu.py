@@ -241,11 +241,14 @@ def test_decode_step_appends_bit_exactly_and_attends(cuda_device, kv_f16):
     pool.release()
 
 
-@pytest.mark.parametrize("parts,pinned_out,download", [(1, True, False), (2, True, False), (5, True, False), (1, False, False),
-                                                       (3, False, False), (1, True, True), (3, True, True)])
-def test_step_from_host_buffers_in_parts_equals_the_device_step(cuda_device, parts, pinned_out, download):
-    """brc_decode_step_host (pinned host q / k / v in, output back to the host, layers in `parts` groups
-    with uploads and downloads on streams of their own) against brc_decode_step on a twin pool: outputs,
+@pytest.mark.parametrize("parts,pinned_out,download,upload", [(1, True, False, True), (2, True, False, True), (5, True, False, True),
+                                                              (1, False, False, True), (3, False, False, True), (1, True, True, True),
+                                                              (3, True, True, True), (1, True, False, False), (3, True, False, False),
+                                                              (1, False, False, False), (1, True, True, False)])
+def test_step_from_host_buffers_in_parts_equals_the_device_step(cuda_device, parts, pinned_out, download, upload):
+    """brc_decode_step_host (pinned host q / k / v either read in place by the kernels or uploaded, output
+    back to the host, layers in `parts` groups with uploads and downloads on streams of their own; with
+    everything in place no staging buffer is given at all) against brc_decode_step on a twin pool: outputs,
     both pools and the advanced lengths must be bit-identical, two steps in a row (the outputs bit-identical
     for one group, within 2e-6 when the layers go in several launches, whose shares are cut differently).  A pinned output buffer
     is written by the kernels directly unless the caller asks for the download; a pageable one is downloaded
@@ -268,10 +271,11 @@ def test_step_from_host_buffers_in_parts_equals_the_device_step(cuda_device, par
         want = torch.full(shape_q, float("nan"), device="cuda")
         dev_batch.step(q_h.cuda(), k_h.cuda(), v_h.cuda(), want)
         out_h.fill_(float("nan"))
-        host_batch.step_host(q_h, k_h, v_h, out_h, staging, parts=parts, download=download)
+        in_place = pinned_out and not download and not upload
+        host_batch.step_host(q_h, k_h, v_h, out_h, None if in_place else staging, parts=parts, download=download, upload=upload)
         for pool in pools:
             pool.check()
-        if parts == 1:
+        if parts == 1 or not upload:   # inputs in place: one launch whatever `parts` says
             assert torch.equal(out_h, want.cpu()), f"step {step}"
         else:   # groups of layers are cut into shares of their own: same sums, another order
             assert float((out_h - want.cpu()).abs().max()) <= 2e-6, f"step {step}"
