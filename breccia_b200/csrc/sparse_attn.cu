@@ -15,6 +15,8 @@
 // On a pool whose V pages are q8_0 (blocks of one f32 scale + 32 signed bytes) a lane reads the scale word of its
 // block and the one or two words that hold its own quanta and multiplies in registers (qsa_attn_apply.comp:69-77):
 // 36 bytes cross the memory system per 32 values instead of 64.
+// Up to 16 query heads per kv head go to the clustered tensor-core kernel further down instead (both V layouts);
+// this one serves wider head groups.
 #include <cooperative_groups.h>
 
 #include "brc_device.cuh"
@@ -184,8 +186,8 @@ __global__ void __launch_bounds__(SP_WARPS * 32) sparse_attn_kernel(const Sparse
 
 
 // ---------------------------------------------------------------------------------------------
-// The same contract with the query heads of a kv head sharing every K / V byte (binary16 V, up to 16 query heads
-// per kv head): the reference's apply shader for chunks loads each V row once for its 12 heads
+// The same contract with the query heads of a kv head sharing every K / V byte (binary16 or q8_0 V, up to 16 query
+// heads per kv head): the reference's apply shader for chunks loads each V row once for its 12 heads
 // (shaders/qsa_attn_apply_gqa.comp:71-136); the kernel above re-reads every selected row once per QUERY head.
 //
 //   one thread-block CLUSTER per (row, kv head); its CTAs (four tile streams each) deal the row's selected blocks out in
@@ -193,7 +195,9 @@ __global__ void __launch_bounds__(SP_WARPS * 32) sparse_attn_kernel(const Sparse
 //   with 16-byte cp.async (zero fill for cells beyond the row's position) into a 128-byte-swizzled tile, double
 //   buffered, and compute on the tensor cores as the dense decode kernel does: S^T[16 cells x 8 heads] = K . Q^T
 //   (mma.sync m16n8k16, Q^T fragments from shared memory), online softmax in base 2 by shuffles, P transposed in
-//   registers (movmatrix) and split into a binary16 head and tail, O^T += V^T . P^T with V^T fragments from ldmatrix.trans;
+//   registers (movmatrix) and split into a binary16 head and tail, O^T += V^T . P^T with V^T fragments from ldmatrix.trans
+//   (q8_0 V: the rows are gathered as they lie in the pool and the quanta reach the tensor cores as exact binary16
+//   integers, the block scales folded into the probabilities);
 //   the streams of a CTA merge their (m, l, O) in shared memory, and the CTAs of the cluster merge through DISTRIBUTED
 //   shared memory: CTA r reads the partials of all its peers for the heads r, r + cluster size, ... and writes those
 //   output rows.  No scratch in global memory, no second kernel.
@@ -203,14 +207,21 @@ namespace gqa {
 constexpr int GROUPS_PER_CTA = 4;   // tiles in flight per CTA: each owned by NT warps (one per group of 8 heads)
 constexpr int MAX_CLUSTER = 8;
 
-template <int HD>
+constexpr float Q8_P_SCALE = 128.f;                     // see the q8_0 V product below
+
+template <int HD, bool V_Q8>
 struct Tile {
     static constexpr int GROUPS = HD / 64;               // 64-column groups
     static constexpr int SLAB = 16 * 128;                // [16 cells][64 columns] binary16
-    static constexpr int GROUP_BYTES = 2 * SLAB;         // K slab then V slab
-    static constexpr int BYTES = GROUPS * GROUP_BYTES;   // one tile: 16 KiB at head_dim 256
+    // binary16 V: per column group a K slab then a V slab.  q8_0 V: the K slabs, then the 16 V rows as they lie in
+    // the pool (HD / 32 blocks of 36 bytes each, unswizzled).
+    static constexpr int GROUP_BYTES = V_Q8 ? SLAB : 2 * SLAB;
+    static constexpr int VROW_BYTES = HD / 32 * 36;
+    static constexpr int V_OFF = GROUPS * SLAB;
+    static constexpr int BYTES = V_Q8 ? (GROUPS * SLAB + 16 * VROW_BYTES + 1023) / 1024 * 1024 : GROUPS * GROUP_BYTES;   // 16 KiB / 13 KiB at head_dim 256
     static constexpr int Q_STRIDE = HD * 2 + 16;         // bytes between heads of the query in shared memory (bank spread)
-    static constexpr int CHUNKS = HD / 8;                // 16-byte chunks per row
+    static constexpr int CHUNKS = HD / 8;                // 16-byte chunks per K (or binary16 V) row
+    static constexpr int VCHUNKS = VROW_BYTES / 16;      // 16-byte chunks per q8_0 V row
 };
 
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, bool live) {
@@ -223,9 +234,9 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 // NT = groups of 8 query heads per kv head (1 or 2) = warps that share a tile: warp nt of a tile's owners computes heads
 // 8 nt .. 8 nt + 7 over the same K / V rows, so 12 heads per kv head keep 8 warps busy on 4 tiles.
-template <int HD, int NT>
+template <int HD, int NT, bool V_Q8>
 __global__ void __launch_bounds__(GROUPS_PER_CTA * NT * 32, 1) sparse_gqa_kernel(const SparseParams p) {
-    using T = Tile<HD>;
+    using T = Tile<HD, V_Q8>;
     constexpr int KSTEPS = HD / 16, MT = HD / 16;
     constexpr int THREADS = GROUPS_PER_CTA * NT * 32;
     constexpr uint32_t OWNERS = NT * 32;                 // threads that share a tile
@@ -289,7 +300,7 @@ __global__ void __launch_bounds__(GROUPS_PER_CTA * NT * 32, 1) sparse_gqa_kernel
                 const uint32_t page = table[lp];
                 if (page < p.n_pages) {
                     live = true;
-                    src_row = (((size_t)page * p.n_kv_head + kvh) * 16u + (cell & 15u)) * HD * 2u;
+                    src_row = ((size_t)page * p.n_kv_head + kvh) * 16u + (cell & 15u);   // row of the layer's K (and V) pool
                 } else if (lane < 16 && nt == 0) {
                     atomicOr(p.status, BRC_DEV_BAD_PAGE);
                     p.status[1] = page;
@@ -298,15 +309,36 @@ __global__ void __launch_bounds__(GROUPS_PER_CTA * NT * 32, 1) sparse_gqa_kernel
         }
         const uint32_t mask = __ballot_sync(0xffffffffu, live) & 0xffffu;
         const uint32_t base = brc::smem_u32(my_tiles + (size_t)b * T::BYTES);
+        if (!V_Q8) {
 #pragma unroll
-        for (uint32_t i = 0; i < 2u * 16u * T::CHUNKS / OWNERS; ++i) {
-            const uint32_t idx = i * OWNERS + nt * 32u + lane;
-            const uint32_t which = idx / (16u * T::CHUNKS);                 // 0: K, 1: V
-            const uint32_t rr = (idx / T::CHUNKS) % 16u, ch = idx % T::CHUNKS;
-            const size_t off = __shfl_sync(0xffffffffu, src_row, rr);
-            const bool lv = (mask >> rr) & 1u;
-            const uint32_t dst = base + (ch >> 3) * T::GROUP_BYTES + which * T::SLAB + rr * 128u + (((ch & 7u) ^ (rr & 7u)) << 4);
-            cp_async_16(dst, (which ? p.v_layer : p.k_layer) + off + ch * 16u, lv);
+            for (uint32_t i = 0; i < 2u * 16u * T::CHUNKS / OWNERS; ++i) {
+                const uint32_t idx = i * OWNERS + nt * 32u + lane;
+                const uint32_t which = idx / (16u * T::CHUNKS);                 // 0: K, 1: V
+                const uint32_t rr = (idx / T::CHUNKS) % 16u, ch = idx % T::CHUNKS;
+                const size_t off = __shfl_sync(0xffffffffu, src_row, rr) * (HD * 2u);
+                const bool lv = (mask >> rr) & 1u;
+                const uint32_t dst = base + (ch >> 3) * T::GROUP_BYTES + which * T::SLAB + rr * 128u + (((ch & 7u) ^ (rr & 7u)) << 4);
+                cp_async_16(dst, (which ? p.v_layer : p.k_layer) + off + ch * 16u, lv);
+            }
+        } else {
+            // K rows into the swizzled slabs, then the V rows whole.  A dead cell's destination is zero-filled: quanta
+            // of zero under a scale of zero.
+            constexpr uint32_t K_CH = 16u * T::CHUNKS, ALL_CH = K_CH + 16u * T::VCHUNKS;
+#pragma unroll
+            for (uint32_t i = 0; i < (ALL_CH + OWNERS - 1u) / OWNERS; ++i) {
+                const uint32_t idx = i * OWNERS + nt * 32u + lane;
+                const bool in = idx < ALL_CH, is_k = idx < K_CH;
+                const uint32_t v_idx = in && !is_k ? idx - K_CH : 0u;
+                const uint32_t rr = is_k ? idx / T::CHUNKS : v_idx / T::VCHUNKS;
+                const uint32_t ch = is_k ? idx % T::CHUNKS : v_idx % T::VCHUNKS;
+                const size_t r = __shfl_sync(0xffffffffu, src_row, rr);
+                const bool lv = (mask >> rr) & 1u;
+                if (is_k)
+                    cp_async_16(base + (ch >> 3) * T::GROUP_BYTES + rr * 128u + (((ch & 7u) ^ (rr & 7u)) << 4),
+                                p.k_layer + r * (HD * 2u) + ch * 16u, lv);
+                else if (in)
+                    cp_async_16(base + T::V_OFF + rr * T::VROW_BYTES + ch * 16u, p.v_layer + r * T::VROW_BYTES + ch * 16u, lv);
+            }
         }
         return mask;
     };
@@ -386,13 +418,62 @@ __global__ void __launch_bounds__(GROUPS_PER_CTA * NT * 32, 1) sparse_gqa_kernel
         const uint32_t bh1 = brc::movmatrix_trans(*reinterpret_cast<const uint32_t *>(&ph23));
         const uint32_t bl0 = brc::movmatrix_trans(brc::pack_half2(p0 - f01.x, p1 - f01.y));
         const uint32_t bl1 = brc::movmatrix_trans(brc::pack_half2(p2 - f23.x, p3 - f23.y));
-        // ---- O^T += V^T . P^T
+        if (!V_Q8) {
+            // ---- O^T += V^T . P^T
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-            uint32_t af[4];
-            brc::ldmatrix_x4_trans(af, sbase + (mt >> 2) * T::GROUP_BYTES + v_lane + ((v_x ^ ((mt & 3) * 2u)) << 4));
-            brc::mma_16816(o[mt], af, bh0, bh1);
-            brc::mma_16816(o[mt], af, bl0, bl1);
+            for (int mt = 0; mt < MT; ++mt) {
+                uint32_t af[4];
+                brc::ldmatrix_x4_trans(af, sbase + (mt >> 2) * T::GROUP_BYTES + v_lane + ((v_x ^ ((mt & 3) * 2u)) << 4));
+                brc::mma_16816(o[mt], af, bh0, bh1);
+                brc::mma_16816(o[mt], af, bl0, bl1);
+            }
+        } else {
+            // ---- q8_0 V (VLayout::Q8_0, shaders/qsa_attn_apply.comp with BRECCIA_KV_Q8V): as in the dense decode
+            //      kernel.  The probabilities in the B-operand layout back in f32 (this lane: cells 2t, 2t + 1, 2t + 8,
+            //      2t + 9 of head g), times 2^7 so that the binary16 tail of probability x scale stays normal; each
+            //      block's scale is folded into them (head + tail again), and the quanta go to the tensor cores as EXACT
+            //      binary16 integers (bits 0x6400 | (q ^ 0x80) are 1024 + q + 128; 1152 is subtracted).  Rows of the
+            //      product are permuted: tile 2 blk holds values 32 blk + 4 g + {0, 1}, tile 2 blk + 1 values + {2, 3}.
+            const float2 h0f = __half22float2(*reinterpret_cast<const __half2 *>(&bh0)), t0f = __half22float2(*reinterpret_cast<const __half2 *>(&bl0));
+            const float2 h1f = __half22float2(*reinterpret_cast<const __half2 *>(&bh1)), t1f = __half22float2(*reinterpret_cast<const __half2 *>(&bl1));
+            const float pb0 = (h0f.x + t0f.x) * Q8_P_SCALE, pb1 = (h0f.y + t0f.y) * Q8_P_SCALE;
+            const float pb2 = (h1f.x + t1f.x) * Q8_P_SCALE, pb3 = (h1f.y + t1f.y) * Q8_P_SCALE;
+            const uint32_t vrow = sbase + T::V_OFF + (lane & 3u) * 2u * T::VROW_BYTES;
+#pragma unroll
+            for (int blk = 0; blk < HD / 32; ++blk) {
+                const uint32_t at = vrow + blk * 36u;
+                float s0, s1, s2, s3;
+                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s0) : "r"(at));
+                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s1) : "r"(at + T::VROW_BYTES));
+                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s2) : "r"(at + 8u * T::VROW_BYTES));
+                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s3) : "r"(at + 9u * T::VROW_BYTES));
+                const float w0 = pb0 * s0, w1 = pb1 * s1, w2 = pb2 * s2, w3 = pb3 * s3;
+                const __half2 wh01 = __floats2half2_rn(w0, w1), wh23 = __floats2half2_rn(w2, w3);
+                const float2 g01 = __half22float2(wh01), g23 = __half22float2(wh23);
+                const uint32_t ph0 = *reinterpret_cast<const uint32_t *>(&wh01), ph1 = *reinterpret_cast<const uint32_t *>(&wh23);
+                const uint32_t pl0 = brc::pack_half2(w0 - g01.x, w1 - g01.y), pl1 = brc::pack_half2(w2 - g23.x, w3 - g23.y);
+                uint32_t x0, x1, x2, x3;
+                const uint32_t qa = at + 4u + (lane >> 2) * 4u;
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(x0) : "r"(qa));
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(x1) : "r"(qa + T::VROW_BYTES));
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(x2) : "r"(qa + 8u * T::VROW_BYTES));
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(x3) : "r"(qa + 9u * T::VROW_BYTES));
+                x0 ^= 0x80808080u, x1 ^= 0x80808080u, x2 ^= 0x80808080u, x3 ^= 0x80808080u;
+                const uint32_t ya = __byte_perm(x0, x1, 0x5410), yb = __byte_perm(x0, x1, 0x7632);   // bytes (0, 1) and (2, 3) of cells 2t, 2t + 1
+                const uint32_t za = __byte_perm(x2, x3, 0x5410), zb = __byte_perm(x2, x3, 0x7632);   // of cells 2t + 8, 2t + 9
+                const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x6480));        // 1152
+                auto ints = [bias](uint32_t y, uint32_t sel) {
+                    const uint32_t r = __byte_perm(y, 0x64646464u, sel);
+                    const __half2 v = __hsub2(*reinterpret_cast<const __half2 *>(&r), bias);
+                    return *reinterpret_cast<const uint32_t *>(&v);
+                };
+                const uint32_t a_lo[4] = {ints(ya, 0x4240), ints(ya, 0x4341), ints(za, 0x4240), ints(za, 0x4341)};
+                const uint32_t a_hi[4] = {ints(yb, 0x4240), ints(yb, 0x4341), ints(zb, 0x4240), ints(zb, 0x4341)};
+                brc::mma_16816(o[2 * blk], a_lo, ph0, ph1);
+                brc::mma_16816(o[2 * blk], a_lo, pl0, pl1);
+                brc::mma_16816(o[2 * blk + 1], a_hi, ph0, ph1);
+                brc::mma_16816(o[2 * blk + 1], a_hi, pl0, pl1);
+            }
         }
         owners_sync();   // the buffer is refilled in the next iteration but one, by all owners
         mask = mask_next;
@@ -412,10 +493,14 @@ __global__ void __launch_bounds__(GROUPS_PER_CTA * NT * 32, 1) sparse_gqa_kernel
         float *wo = w_o + ((size_t)grp * NT * 8 + nt * 8) * HD;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
-            wo[h0 * HD + mt * 16 + t0] = o[mt][0];
-            wo[(h0 + 1) * HD + mt * 16 + t0] = o[mt][1];
-            wo[h0 * HD + mt * 16 + t0 + 8] = o[mt][2];
-            wo[(h0 + 1) * HD + mt * 16 + t0 + 8] = o[mt][3];
+            // binary16 V: rows t0 and t0 + 8 of tile mt; q8_0 V: the permuted rows of the product above
+            const uint32_t d0 = V_Q8 ? (mt >> 1) * 32 + t0 * 4 + (mt & 1) * 2 : mt * 16 + t0;
+            const uint32_t d1 = V_Q8 ? d0 + 1 : d0 + 8;
+            constexpr float back = V_Q8 ? 1.f / Q8_P_SCALE : 1.f;   // undoes the factor on the q8_0 probabilities (exact)
+            wo[h0 * HD + d0] = o[mt][0] * back;
+            wo[(h0 + 1) * HD + d0] = o[mt][1] * back;
+            wo[h0 * HD + d1] = o[mt][2] * back;
+            wo[(h0 + 1) * HD + d1] = o[mt][3] * back;
         }
         if (lane < 4) {
             float *ml = w_ml + ((size_t)grp * NT * 8 + nt * 8 + h0) * 2;
@@ -478,25 +563,25 @@ __global__ void __launch_bounds__(GROUPS_PER_CTA * NT * 32, 1) sparse_gqa_kernel
     cluster.sync();   // nobody leaves while a peer may still read its shared memory
 }
 
-template <int HD>
+template <int HD, bool V_Q8>
 constexpr uint32_t smem_bytes(int nt) {
-    return 1024u + GROUPS_PER_CTA * 2 * Tile<HD>::BYTES + 2u * nt * 8 * Tile<HD>::Q_STRIDE + nt * 8 * HD * 4u + nt * 8 * 2 * 4u + 64u;
+    return 1024u + GROUPS_PER_CTA * 2 * Tile<HD, V_Q8>::BYTES + 2u * nt * 8 * Tile<HD, V_Q8>::Q_STRIDE + nt * 8 * HD * 4u + nt * 8 * 2 * 4u + 64u;
 }
 
-template <int HD, int NT>
+template <int HD, int NT, bool V_Q8>
 cudaError_t launch(const SparseParams &p, uint32_t rows, uint32_t n_kv_head, uint32_t cs, cudaStream_t st) {
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(sparse_gqa_kernel<HD, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<HD>(NT));
+        cudaError_t e = cudaFuncSetAttribute(sparse_gqa_kernel<HD, NT, V_Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<HD, V_Q8>(NT));
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_kv_head * cs, rows);
     cfg.blockDim = dim3(GROUPS_PER_CTA * NT * 32);
-    cfg.dynamicSmemBytes = smem_bytes<HD>(NT);
+    cfg.dynamicSmemBytes = smem_bytes<HD, V_Q8>(NT);
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -505,7 +590,7 @@ cudaError_t launch(const SparseParams &p, uint32_t rows, uint32_t n_kv_head, uin
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, sparse_gqa_kernel<HD, NT>, p);
+    return cudaLaunchKernelEx(&cfg, sparse_gqa_kernel<HD, NT, V_Q8>, p);
 }
 
 }  // namespace gqa
@@ -569,14 +654,20 @@ brc_status brc_paged_sparse_attn(brc_pool *pool, uint32_t layer, const void *q_d
     const uint64_t sms = (uint64_t)(pool->sm_count > 0 ? pool->sm_count : 148);
     const bool few = rows * n_head < 2u * sms;
     const uint32_t group = n_head / pool->n_kv_head;
-    if (!pool->v_q8 && group <= 16u) {
+    if (group <= 16u) {
         // one cluster per (row, kv head): as many CTAs per cluster (a power of two, at most 8) as keep every SM busy
         const uint64_t units = rows * pool->n_kv_head;
         uint32_t cs = 1;
         while (cs < (uint32_t)gqa::MAX_CLUSTER && units * cs * 2u <= sms) cs *= 2u;
         cudaError_t e;
-        if (hd == 256) e = group <= 8u ? gqa::launch<256, 1>(p, (uint32_t)rows, pool->n_kv_head, cs, st) : gqa::launch<256, 2>(p, (uint32_t)rows, pool->n_kv_head, cs, st);
-        else e = group <= 8u ? gqa::launch<128, 1>(p, (uint32_t)rows, pool->n_kv_head, cs, st) : gqa::launch<128, 2>(p, (uint32_t)rows, pool->n_kv_head, cs, st);
+        const uint32_t r32 = (uint32_t)rows, nkv = pool->n_kv_head;
+        if (pool->v_q8) {
+            if (hd == 256) e = group <= 8u ? gqa::launch<256, 1, true>(p, r32, nkv, cs, st) : gqa::launch<256, 2, true>(p, r32, nkv, cs, st);
+            else e = group <= 8u ? gqa::launch<128, 1, true>(p, r32, nkv, cs, st) : gqa::launch<128, 2, true>(p, r32, nkv, cs, st);
+        } else {
+            if (hd == 256) e = group <= 8u ? gqa::launch<256, 1, false>(p, r32, nkv, cs, st) : gqa::launch<256, 2, false>(p, r32, nkv, cs, st);
+            else e = group <= 8u ? gqa::launch<128, 1, false>(p, r32, nkv, cs, st) : gqa::launch<128, 2, false>(p, r32, nkv, cs, st);
+        }
         brc_stage_end(pool, BRC_STAGE_ATTN_PARTIAL, st);
         if (e != cudaSuccess) return brc_fail(BRC_ERR_CUDA, "brc_paged_sparse_attn: launch failed: %s", cudaGetErrorString(e));
         BRC_CUDA(cudaGetLastError());

@@ -11,7 +11,7 @@ import torch
 import oracle
 from oracle import q8v
 from breccia_b200 import _lib, synth
-from breccia_b200._lib import DTYPE_F32
+from breccia_b200._lib import DTYPE_F16, DTYPE_F32
 from breccia_b200.qsa import KvPool
 from helpers import ATTN_MAX_ABS, ATTN_MAX_REL, attention_errors, dev_u32
 
@@ -86,6 +86,54 @@ def test_q8_0_v_append_bit_exact_and_sparse_attention(cuda_device, n_head, n_kv,
     want_f16 = oracle.attend(q[0], kf, oracle.to_f16(v_all), oracle.cells_of(ids, 4), cells - 1, n_head, n_kv, hd,
                              gate=q_full[0, :, 1, :])
     assert np.abs(got - want_f16).max() <= 0.05
+    pool.release()
+
+
+def test_q8_0_v_sparse_rows_of_two_sequences(cuda_device):
+    """Three rows each of two sequences over a q8_0 V pool (rows_per_seq = 3, binary16 query): row t sees cells up to
+    pos0 + t only; a list of 401 blocks (several CTAs per cluster, tiles interleaved between them, the last block partly
+    in the future) beside short lists and a row with an empty list, which yields zeros."""
+    n_head, n_kv, hd = 16, 2, 256
+    lens, pages = [2064, 80], [129, 5]
+    pool = KvPool(0, 1, n_kv, hd, 140, v_q8=True)
+    perm = synth.permutation(93, 140).astype(np.uint32)
+    tables = np.zeros((2, 129), np.uint32)
+    tables[0], tables[1, :5] = perm[:129], perm[129:134]
+    dim = n_kv * hd
+    ks, vs = [], []
+    for s in range(2):
+        ks.append(oracle.normalish(0x101 + s, lens[s] * dim).reshape(lens[s], dim))
+        vs.append(oracle.normalish(0x111 + s, lens[s] * dim).reshape(lens[s], dim))
+        append(pool, 0, tables[s, :pages[s]].copy(), 0, ks[s], vs[s])
+    pos0s = np.array([2059, 70])
+    ids = np.zeros((6, 513), np.uint32)
+    counts = np.zeros(6, np.uint32)
+    for r in range(3):
+        ids[r, :400] = np.sort(synth.permutation(94 + r, 514)[:400])
+        ids[r, 400] = (2059 + r) // 4
+        counts[r] = 401
+        ids[3 + r, :5] = [0, 5, 9, 15, 17]                      # block 17 = cells 68 .. 71: partly in the future
+        counts[3 + r] = 5
+    counts[4] = 0
+    q = oracle.to_f16(synth.normal(95, 6 * n_head * hd)).reshape(6, n_head, hd)
+    qd = torch.from_numpy(q).cuda().half()
+    out = torch.full((6, n_head, hd), float("nan"), device="cuda")
+    t_dev, p_dev, i_dev, c_dev = dev_u32(tables), dev_u32(pos0s), dev_u32(ids), dev_u32(counts)
+    _lib.call("brc_paged_sparse_attn", pool.handle, 0, P(qd), DTYPE_F16, n_head, None, 0, P(t_dev), tables.shape[1], P(p_dev), 2, 3,
+              P(i_dev), ids.shape[1], P(c_dev), int(pos0s.max()) + 3, 1.0 / np.sqrt(hd), P(out), None)
+    pool.check()
+    got = out.cpu().numpy()
+    for r in range(6):
+        s, t = divmod(r, 3)
+        if counts[r] == 0:
+            assert not got[r].any()
+            continue
+        kf = oracle.to_f16(ks[s])
+        vq = q8v.to_q8_0(vs[s].reshape(lens[s] * n_kv, hd)).reshape(lens[s], dim)
+        want = oracle.attend(q[r], kf, vq, oracle.cells_of(ids[r, :counts[r]], 4), int(pos0s[s]) + t, n_head, n_kv, hd)
+        max_abs, max_rel, ref = attention_errors(got[r], want)
+        assert np.isfinite(got[r]).all()
+        assert max_abs <= ATTN_MAX_ABS and max_rel <= ATTN_MAX_REL and ref <= 1e-5, f"row {r}: {max_abs:.2e} {max_rel:.2e} {ref:.2e}"
     pool.release()
 
 
