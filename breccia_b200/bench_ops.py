@@ -37,6 +37,26 @@ def timed(fn, iters: int) -> float:
     return e0.elapsed_time(e1) * 1e3 / iters  # us
 
 
+def timed_graph(fn, iters: int) -> float:
+    """The same calls captured once in a CUDA graph and replayed: the device's time per call without the
+    host's cost of issuing it (for calls of a few tens of microseconds `timed` measures the host)."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(iters):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / iters  # us
+
+
 def emit(**kw):
     print(json.dumps(kw), flush=True)
 
@@ -168,12 +188,13 @@ def bench_sparse(iters: int):
             sparse_attend(pool, 0, q, n_head, t_dev, p_dev, 1, i_dev, c_dev, ctx, out)
 
         us = timed(run, iters)
+        us_graph = timed_graph(run, iters)
         pool.check()
         # every selected cell's K and V once per kv head; a q8_0 V row is 9/16 of a binary16 one
         nbytes = int(n_seqs * n_sel * 4 * N_KV * HD * 2 * (1 + (0.5625 if v_q8 else 1)))
         emit(op="paged_sparse_attn", case=f"{n_seqs} sequence(s), 1 row each, {n_sel} selected blocks = {n_sel * 4} cells of {ctx}, "
              f"{n_head}q/{N_KV}kv hd{HD}, 1 layer, V {'q8_0' if v_q8 else 'f16'}", units=n_seqs, bytes=nbytes, us=us,
-             gbps=nbytes / us / 1e3, iters=iters)
+             us_graph=us_graph, gbps=nbytes / us_graph / 1e3, iters=iters)
         pool.release()
 
 
@@ -190,9 +211,10 @@ def bench_topk(iters: int):
         scores = torch.randn((rows, n_blocks), generator=gen, device="cuda")
         pos0 = dev_u32(np.full(n_seqs, 4 * n_blocks - rows_per_seq))
         us = timed(lambda: topk_blocks(pool, scores, pos0, rows_per_seq), iters)
+        us_graph = timed_graph(lambda: topk_blocks(pool, scores, pos0, rows_per_seq), iters)
         pool.check()
         emit(op="topk_blocks", case=f"{rows} row(s) x {n_blocks} blocks, top 512 + own block", units=rows,
-             bytes=rows * n_blocks * 4, us=us, gbps=rows * n_blocks * 4 / us / 1e3, iters=iters)
+             bytes=rows * n_blocks * 4, us=us, us_graph=us_graph, gbps=rows * n_blocks * 4 / us_graph / 1e3, iters=iters)
     pool.release()
 
 
@@ -212,12 +234,13 @@ def bench_indexer(iters: int):
         q = torch.randn((rows, IDX_N_HEAD, IDX_DIM), generator=gen, device="cuda")
         pos0 = dev_u32(np.full(n_seqs, IDX_BLOCK * n_blocks - rows_per_seq))
         us = timed(lambda: idx.score(q, pos0, rows_per_seq, n_blocks), iters)
+        us_graph = timed_graph(lambda: idx.score(q, pos0, rows_per_seq, n_blocks), iters)
         pool.check()
         # every pooled key once per sequence (the rows of a sequence share them), the queries, the scores
         nbytes = n_seqs * n_blocks * IDX_DIM * 4 + rows * IDX_N_HEAD * IDX_DIM * 4 + rows * n_blocks * 4
         flops = 2 * rows * IDX_N_HEAD * n_blocks * IDX_DIM
         emit(op="idx_score", case=f"{rows} row(s) x {n_blocks} pooled keys, {IDX_N_HEAD} index heads of {IDX_DIM}", units=rows,
-             bytes=nbytes, flops=flops, us=us, gbps=nbytes / us / 1e3, tflops=flops / us / 1e6, iters=iters)
+             bytes=nbytes, flops=flops, us=us, us_graph=us_graph, gbps=nbytes / us_graph / 1e3, tflops=flops / us_graph / 1e6, iters=iters)
     n_seqs, tokens, max_pos = 8, 256, 32768
     idx = IndexerState(pool, n_seqs, max_pos)
     raw = torch.randn((n_seqs, tokens, IDX_DIM), generator=gen, device="cuda")

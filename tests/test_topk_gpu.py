@@ -41,7 +41,9 @@ def make_scores(seed, rows, n_blocks, levels):
 
 
 @pytest.mark.parametrize("n_blocks,k,levels", [(3, 512, 2), (100, 512, 4), (513, 512, 50), (700, 512, 3), (8192, 512, 1000),
-                                               (8193, 512, 20), (20000, 512, 5000), (20000, 37, 3), (65536, 512, 100000)])
+                                               (8193, 512, 20), (20000, 512, 5000), (20000, 37, 3), (65536, 512, 100000),
+                                               (512, 512, 30), (600, 300, 7), (2048, 512, 2), (5000, 1000, 40), (4096, 1024, 100000),
+                                               (9000, 1024, 9), (3000, 512, 1000), (4096, 500, 50), (8192, 512, 10 ** 7), (6000, 512, 1)])
 def test_selection_matches_the_oracle_id_for_id(cuda_device, n_blocks, k, levels):
     pool = KvPool(0, 1, 2, 256, 4)
     n_seqs, rows_per_seq = 3, 2
