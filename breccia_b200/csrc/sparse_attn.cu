@@ -192,8 +192,8 @@ __global__ void __launch_bounds__(SP_WARPS * 32) sparse_attn_kernel(const Sparse
 //
 //   one thread-block CLUSTER per (row, kv head); its CTAs (four tile streams each) deal the row's selected blocks out in
 //   tiles of 16 cells (4 blocks); the warps that own a stream (one per group of 8 query heads) gather a tile's K and V rows
-//   with 16-byte cp.async (zero fill for cells beyond the row's position) into a 128-byte-swizzled tile, double
-//   buffered, and compute on the tensor cores as the dense decode kernel does: S^T[16 cells x 8 heads] = K . Q^T
+//   with 16-byte cp.async (zero fill for cells beyond the row's position) into a 128-byte-swizzled tile, in three
+//   buffers (the copies of two tiles in flight while a third is computed), and compute on the tensor cores as the dense decode kernel does: S^T[16 cells x 8 heads] = K . Q^T
 //   (mma.sync m16n8k16, Q^T fragments from shared memory), online softmax in base 2 by shuffles, P transposed in
 //   registers (movmatrix) and split into a binary16 head and tail, O^T += V^T . P^T with V^T fragments from ldmatrix.trans
 //   (q8_0 V: the rows are gathered as they lie in the pool and the quanta reach the tensor cores as exact binary16
@@ -204,7 +204,8 @@ __global__ void __launch_bounds__(SP_WARPS * 32) sparse_attn_kernel(const Sparse
 // ---------------------------------------------------------------------------------------------
 namespace gqa {
 
-constexpr int GROUPS_PER_CTA = 4;   // tiles in flight per CTA: each owned by NT warps (one per group of 8 heads)
+constexpr int GROUPS_PER_CTA = 4;   // tile streams per CTA: each owned by NT warps (one per group of 8 heads)
+constexpr int NBUF = 3;             // tile buffers per stream: two tiles' copies in flight while a third is computed
 constexpr int MAX_CLUSTER = 8;
 
 constexpr float Q8_P_SCALE = 128.f;                     // see the q8_0 V product below
@@ -245,8 +246,8 @@ __global__ void __launch_bounds__(GROUPS_PER_CTA * NT * 32, 1) sparse_gqa_kernel
     const uint32_t cs = cluster.num_blocks(), rank = cluster.block_rank();
     extern __shared__ uint8_t sg_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(sg_raw) + 1023u) & ~uintptr_t(1023));
-    uint8_t *tiles = smem;                                                   // [GROUPS_PER_CTA][2][T::BYTES]
-    uint8_t *q_hi = tiles + GROUPS_PER_CTA * 2 * T::BYTES;                   // [NT * 8][Q_STRIDE] binary16 heads of the query
+    uint8_t *tiles = smem;                                                   // [GROUPS_PER_CTA][NBUF][T::BYTES]
+    uint8_t *q_hi = tiles + GROUPS_PER_CTA * NBUF * T::BYTES;                   // [NT * 8][Q_STRIDE] binary16 heads of the query
     uint8_t *q_lo = q_hi + NT * 8 * T::Q_STRIDE;                             // tails (f32 queries only)
     float *cta_o = reinterpret_cast<float *>(q_lo + NT * 8 * T::Q_STRIDE);   // [NT * 8][HD] this CTA's merged O
     float *cta_ml = cta_o + NT * 8 * HD;                                     // [NT * 8][2]
@@ -259,6 +260,31 @@ __global__ void __launch_bounds__(GROUPS_PER_CTA * NT * 32, 1) sparse_gqa_kernel
     const uint32_t head_base = kvh * group;
     const bool bad_pos = pos >= p.max_pos_end;
     if (bad_pos && tid == 0 && rank == 0) { atomicOr(p.status, BRC_DEV_BAD_POS); p.status[1] = pos; }
+
+    const uint32_t count = bad_pos ? 0u : min(p.counts[row], p.max_ids);
+    const uint32_t *ids = p.ids + (size_t)row * p.max_ids;
+    const uint32_t *table = p.block_tables + (size_t)s * p.table_stride;
+    const uint32_t n_tiles = (count + 3u) / 4u;
+    const uint32_t stride = cs * GROUPS_PER_CTA;
+    // Lane r < 16 (and its twin r + 16) resolves cell r of a tile: block r / 4 of the tile's four, cell r % 4 of the
+    // block.  The way from a tile number to its rows is a chain of dependent loads (id list -> block table -> K / V
+    // rows), so it is walked in three steps, one tile further ahead each: the id of tile j + 4 strides, the page of tile
+    // j + 3 strides and the row copies of tile j + 2 strides are all issued while tile j is computed.
+    auto fetch_id = [&](uint32_t j) -> uint32_t {
+        const uint32_t li = j * 4u + ((lane & 15u) >> 2);
+        return (j < n_tiles && li < count) ? ids[li] : 0xffffffffu;
+    };
+    auto fetch_page = [&](uint32_t id, uint32_t &cell) -> uint32_t {   // cell = 0xffffffff: nothing to read
+        cell = 0xffffffffu;
+        if (id == 0xffffffffu) return 0u;
+        const uint32_t c = id * 4u + (lane & 3u), lp = c >> 4;
+        if (c > pos || lp >= p.table_stride) return 0u;
+        cell = c;
+        return table[lp];
+    };
+    const uint32_t j_first = rank * GROUPS_PER_CTA + warp / NT;
+    uint32_t id_a = fetch_id(j_first), id_b = fetch_id(j_first + stride), id_c = fetch_id(j_first + 2u * stride);
+    uint32_t id_d = fetch_id(j_first + 3u * stride);
 
     // ---- the query heads of this kv head into shared memory: binary16 head (and tail of an f32 query)
     for (uint32_t i = tid; i < NT * 8 * (HD / 2); i += THREADS) {
@@ -276,35 +302,23 @@ __global__ void __launch_bounds__(GROUPS_PER_CTA * NT * 32, 1) sparse_gqa_kernel
     }
     __syncthreads();
 
-    const uint32_t count = bad_pos ? 0u : min(p.counts[row], p.max_ids);
-    const uint32_t *ids = p.ids + (size_t)row * p.max_ids;
-    const uint32_t *table = p.block_tables + (size_t)s * p.table_stride;
-    const uint32_t n_tiles = (count + 3u) / 4u;
-    const uint32_t stride = cs * GROUPS_PER_CTA;
-    uint8_t *my_tiles = tiles + (size_t)grp * 2 * T::BYTES;
+    uint8_t *my_tiles = tiles + (size_t)grp * NBUF * T::BYTES;
     auto owners_sync = [&]() {
         if (NT == 1) __syncwarp();
         else brc::named_bar_sync(1 + grp, OWNERS);
     };
 
-    // Gathers this warp's part of tile j (blocks 4j .. 4j + 3 of the list) into buffer b; returns the mask of live cells.
-    auto gather = [&](uint32_t j, uint32_t b) -> uint32_t {
-        // lane r < 16 resolves cell r of the tile: block r / 4 of the tile, cell r % 4 of the block
-        const uint32_t r = lane & 15u, li = j * 4u + (r >> 2);
+    // Copies this warp's part of a tile, whose cells were resolved to (page, cell), into buffer b; returns the mask of live cells.
+    auto gather = [&](uint32_t page, uint32_t cell, uint32_t b) -> uint32_t {
         bool live = false;
         size_t src_row = 0;
-        if (li < count) {
-            const uint32_t cell = ids[li] * 4u + (r & 3u);
-            const uint32_t lp = cell >> 4;
-            if (cell <= pos && lp < p.table_stride) {
-                const uint32_t page = table[lp];
-                if (page < p.n_pages) {
-                    live = true;
-                    src_row = ((size_t)page * p.n_kv_head + kvh) * 16u + (cell & 15u);   // row of the layer's K (and V) pool
-                } else if (lane < 16 && nt == 0) {
-                    atomicOr(p.status, BRC_DEV_BAD_PAGE);
-                    p.status[1] = page;
-                }
+        if (cell != 0xffffffffu) {
+            if (page < p.n_pages) {
+                live = true;
+                src_row = ((size_t)page * p.n_kv_head + kvh) * 16u + (cell & 15u);   // row of the layer's K (and V) pool
+            } else if (lane < 16 && nt == 0) {
+                atomicOr(p.status, BRC_DEV_BAD_PAGE);
+                p.status[1] = page;
             }
         }
         const uint32_t mask = __ballot_sync(0xffffffffu, live) & 0xffffu;
@@ -356,14 +370,20 @@ __global__ void __launch_bounds__(GROUPS_PER_CTA * NT * 32, 1) sparse_gqa_kernel
     for (int mt = 0; mt < MT; ++mt) o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-    uint32_t j = rank * GROUPS_PER_CTA + grp, buf = 0;
-    uint32_t mask = 0, mask_next = 0;
-    if (j < n_tiles) mask = gather(j, 0);
+    uint32_t j = j_first, buf = 0;
+    uint32_t mask = 0, mask_1 = 0, mask_2 = 0;     // live cells of tile j, j + stride, j + 2 strides
+    uint32_t cell_a, cell_b, cell_c;
+    uint32_t page_a = fetch_page(id_a, cell_a), page_b = fetch_page(id_b, cell_b), page_c = fetch_page(id_c, cell_c);
+    if (j < n_tiles) mask = gather(page_a, cell_a, 0);
     cp_async_commit();
-    for (; j < n_tiles; j += stride, buf ^= 1u) {
-        if (j + stride < n_tiles) mask_next = gather(j + stride, buf ^ 1u);
+    if (j + stride < n_tiles) mask_1 = gather(page_b, cell_b, 1);
+    cp_async_commit();
+    for (; j < n_tiles; j += stride, buf = buf + 1u == NBUF ? 0u : buf + 1u) {
+        if (j + 2u * stride < n_tiles) mask_2 = gather(page_c, cell_c, buf >= 1u ? buf - 1u : buf + 2u);   // (buf + 2) % 3
         cp_async_commit();
-        cp_async_wait<1>();
+        page_c = fetch_page(id_d, cell_c);          // tile j + 3 strides: used in the next iteration
+        id_d = fetch_id(j + 4u * stride);           // tile j + 4 strides: used in the next iteration
+        cp_async_wait<NBUF - 1>();
         owners_sync();        // every owner's copies of this tile have landed
         const uint32_t sbase = brc::smem_u32(my_tiles + (size_t)buf * T::BYTES);
         // ---- S^T = K . Q^T
@@ -475,8 +495,9 @@ __global__ void __launch_bounds__(GROUPS_PER_CTA * NT * 32, 1) sparse_gqa_kernel
                 brc::mma_16816(o[2 * blk + 1], a_hi, pl0, pl1);
             }
         }
-        owners_sync();   // the buffer is refilled in the next iteration but one, by all owners
-        mask = mask_next;
+        owners_sync();   // the buffer is refilled in the next iteration, by all owners
+        mask = mask_1;
+        mask_1 = mask_2;
     }
     cp_async_wait<0>();
     __syncthreads();    // every warp is done with its tiles: their memory now carries the warps' partials
@@ -565,7 +586,7 @@ __global__ void __launch_bounds__(GROUPS_PER_CTA * NT * 32, 1) sparse_gqa_kernel
 
 template <int HD, bool V_Q8>
 constexpr uint32_t smem_bytes(int nt) {
-    return 1024u + GROUPS_PER_CTA * 2 * Tile<HD, V_Q8>::BYTES + 2u * nt * 8 * Tile<HD, V_Q8>::Q_STRIDE + nt * 8 * HD * 4u + nt * 8 * 2 * 4u + 64u;
+    return 1024u + GROUPS_PER_CTA * NBUF * Tile<HD, V_Q8>::BYTES + 2u * nt * 8 * Tile<HD, V_Q8>::Q_STRIDE + nt * 8 * HD * 4u + nt * 8 * 2 * 4u + 64u;
 }
 
 template <int HD, int NT, bool V_Q8>
