@@ -122,7 +122,7 @@ struct ScoreParams {
 };
 
 constexpr uint32_t SC_THREADS = 256;
-constexpr uint32_t SC_BLOCKS_PER_CTA = 256;   // blocks one CTA scores: 8 steps of its 8 warps x 4 blocks
+constexpr uint32_t SC_BLOCKS_PER_CTA = 128;   // blocks one CTA scores: 4 steps of its 8 warps x 4 blocks (small CTAs: a short tail)
 
 // grid = (ceil(n_blocks / SC_BLOCKS_PER_CTA), rows).
 __global__ void __launch_bounds__(SC_THREADS) idx_score_kernel(const ScoreParams p) {
@@ -137,29 +137,39 @@ __global__ void __launch_bounds__(SC_THREADS) idx_score_kernel(const ScoreParams
     const uint32_t slot = tid >> 3;             // block slot within a step of the CTA: 0 .. 31
     const uint32_t b_begin = blockIdx.x * SC_BLOCKS_PER_CTA;
     const float *pooled = p.pooled + (size_t)s * p.max_blocks * IDX_DIM;
-    for (uint32_t step = 0; step < SC_BLOCKS_PER_CTA / (SC_THREADS / 8); ++step) {   // the same trip count for every lane
+    constexpr uint32_t STEPS = SC_BLOCKS_PER_CTA / (SC_THREADS / 8);
+    // The pooled key averages ALL cells of its block, so a row may use it only when it sees the whole
+    // block: masked on the block's last cell (qsa_idx_score.comp:74-81).
+    auto load_key = [&](uint32_t step, float4 (&k)[4]) {
+        const uint32_t b = b_begin + step * (SC_THREADS / 8) + slot;
+        k[0] = k[1] = k[2] = k[3] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (b < p.n_blocks && b * IDX_BLOCK + IDX_BLOCK - 1u <= pos) {
+            const float4 *kp = reinterpret_cast<const float4 *>(pooled + (size_t)b * IDX_DIM) + sub;
+            k[0] = __ldg(kp), k[1] = __ldg(kp + 8), k[2] = __ldg(kp + 16), k[3] = __ldg(kp + 24);
+        }
+    };
+    float4 k[4], kn[4];
+    load_key(0, k);
+#pragma unroll
+    for (uint32_t step = 0; step < STEPS; ++step) {   // the same trip count for every lane
+        if (step + 1u < STEPS) load_key(step + 1u, kn);   // the next step's key is on its way while this one is scored
         const uint32_t b = b_begin + step * (SC_THREADS / 8) + slot;
         const bool valid = b < p.n_blocks;
-        // The pooled key averages ALL cells of its block, so a row may use it only when it sees the whole
-        // block: masked on the block's last cell (qsa_idx_score.comp:74-81).
         const bool dead = b * IDX_BLOCK + IDX_BLOCK - 1u > pos;
-        float4 k0 = make_float4(0.f, 0.f, 0.f, 0.f), k1 = k0, k2 = k0, k3 = k0;
-        if (valid && !dead) {
-            const float4 *kp = reinterpret_cast<const float4 *>(pooled + (size_t)b * IDX_DIM) + sub;
-            k0 = __ldg(kp), k1 = __ldg(kp + 8), k2 = __ldg(kp + 16), k3 = __ldg(kp + 24);
-        }
         float sum = 0.f;
         for (uint32_t h = 0; h < p.n_head; ++h) {
             const float4 *qp = s_q + h * (IDX_DIM / 4) + sub;
             const float4 q0 = qp[0], q1 = qp[8], q2 = qp[16], q3 = qp[24];
-            float dot = k0.x * q0.x + k0.y * q0.y + k0.z * q0.z + k0.w * q0.w + k1.x * q1.x + k1.y * q1.y + k1.z * q1.z + k1.w * q1.w +
-                        k2.x * q2.x + k2.y * q2.y + k2.z * q2.z + k2.w * q2.w + k3.x * q3.x + k3.y * q3.y + k3.z * q3.z + k3.w * q3.w;
+            float dot = k[0].x * q0.x + k[0].y * q0.y + k[0].z * q0.z + k[0].w * q0.w + k[1].x * q1.x + k[1].y * q1.y + k[1].z * q1.z + k[1].w * q1.w +
+                        k[2].x * q2.x + k[2].y * q2.y + k[2].z * q2.z + k[2].w * q2.w + k[3].x * q3.x + k[3].y * q3.y + k[3].z * q3.z + k[3].w * q3.w;
             dot += __shfl_xor_sync(0xffffffffu, dot, 1);
             dot += __shfl_xor_sync(0xffffffffu, dot, 2);
             dot += __shfl_xor_sync(0xffffffffu, dot, 4);
             sum += fmaxf(dot, 0.f);
         }
         if (valid && sub == 0u) p.scores[(size_t)row * p.n_blocks + b] = dead ? MASK_DEAD : sum * p.scale;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) k[j] = kn[j];
     }
 }
 
