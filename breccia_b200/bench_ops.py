@@ -110,9 +110,10 @@ def bench_prefill(iters: int, prefix: int):
                   n_seqs * chunk, prefix + chunk, _ptr(ks), _ptr(vs), DTYPE_F32, _stream_ptr())
 
     us = timed(append, iters)
+    us_graph = timed_graph(append, iters)
     nbytes = n_seqs * chunk * (N_KV * HD * 2 * 2 + N_KV * HD * 4 * 2)
     emit(op="kv_append", case=f"chunk append, {n_seqs} sequences x {chunk} tokens, f32 sources, 1 layer", units=n_seqs * chunk,
-         bytes=nbytes, us=us, gbps=nbytes / us / 1e3, iters=iters)
+         bytes=nbytes, us=us, us_graph=us_graph, gbps=nbytes / us_graph / 1e3, iters=iters)
     q = (torch.randn((n_seqs, chunk, N_HEAD, HD), generator=gen, device="cuda")).half()
     out = torch.empty((n_seqs, chunk, N_HEAD, HD), dtype=torch.float32, device="cuda")
 
@@ -159,10 +160,11 @@ def bench_prepare(iters: int):
                       4096 + T, _ptr(q_out), DTYPE_F16, _stream_ptr())
 
         us = timed(prepare, iters)
+        us_graph = timed_graph(prepare, iters)
         pool.check()
         nbytes = tokens * (N_HEAD * HD * 4 + 2 * N_KV * HD * 4 + N_HEAD * HD * 2 + 2 * N_KV * HD * 2)
         emit(op="qk_prepare_append", case=f"{n_seqs} sequences x {T} tokens: RMSNorm + rotary of 16 q / 2 k heads, f16 append of k and v, 1 layer",
-             units=tokens, bytes=nbytes, us=us, gbps=nbytes / us / 1e3, iters=iters)
+             units=tokens, bytes=nbytes, us=us, us_graph=us_graph, gbps=nbytes / us_graph / 1e3, iters=iters)
         pool.release()
 
 
@@ -250,10 +252,11 @@ def bench_indexer(iters: int):
     table = torch.stack([ang.cos(), ang.sin()], dim=-1).reshape(max_pos, 2 * half).float().contiguous()
     pos0 = dev_u32(np.full(n_seqs, 16384))
     us = timed(lambda: idx.append(raw, pos0, 16384 + tokens, gamma, table, 2 * half), iters)
+    us_graph = timed_graph(lambda: idx.append(raw, pos0, 16384 + tokens, gamma, table, 2 * half), iters)
     pool.check()
     nbytes = n_seqs * tokens * IDX_DIM * 4 + n_seqs * (tokens // IDX_BLOCK) * IDX_DIM * 4
     emit(op="idx_pool+idx_tail", case=f"{n_seqs} sequences x {tokens}-token chunk: RMSNorm + rotary + mean of every completed 4-cell block, tail stored",
-         units=n_seqs * tokens, bytes=nbytes, us=us, gbps=nbytes / us / 1e3, iters=iters)
+         units=n_seqs * tokens, bytes=nbytes, us=us, us_graph=us_graph, gbps=nbytes / us_graph / 1e3, iters=iters)
     pool.release()
 
 
@@ -270,9 +273,10 @@ def bench_movers(iters: int):
         _lib.call("brc_page_gather", pool.handle, 0, _ptr(table), 512, 8192, _ptr(k_out), _ptr(v_out), _stream_ptr())
 
     us = timed(gather, iters)
+    us_graph = timed_graph(gather, iters)
     nbytes = 2 * 8192 * N_KV * HD * 2 * 2
-    emit(op="page_gather", case="8192 cells of one sequence, 1 layer, K and V", units=512, bytes=nbytes, us=us,
-         gbps=nbytes / us / 1e3, iters=iters)
+    emit(op="page_gather", case="8192 cells of one sequence, 1 layer, K and V", units=512, bytes=nbytes, us=us, us_graph=us_graph,
+         gbps=nbytes / us_graph / 1e3, iters=iters)
     # copy: 1024 pages, all 12 layers, K and V
     src, dst = dev_u32(perm[:1024]), dev_u32(perm[1024:2048])
 
