@@ -260,6 +260,41 @@ def bench_indexer(iters: int):
     pool.release()
 
 
+def bench_qsa_chain(iters: int):
+    """What a selected-block (QSA) layer does per decode token behind the query: indexer scores over the pooled keys,
+    top-k selection, attention over the selected blocks (Qsa::forward, qsa/mod.rs:1618-1641) - the three calls in
+    a row, one query row per sequence at position ~32 k (8192 pooled keys, 512 blocks selected + the row's own),
+    24 query heads over 2 kv heads; one sequence and a batch of 32."""
+    from .qsa import IDX_BLOCK, IDX_DIM, IDX_N_HEAD, IndexerState, sparse_attend, topk_blocks
+
+    n_head, ctx = 24, 32768
+    n_blocks = ctx // IDX_BLOCK
+    for n_seqs in (1, 32):
+        pages = ctx // 16
+        pool = KvPool(0, 1, N_KV, HD, n_seqs * pages)
+        tables = dev_u32(synth.permutation(13, n_seqs * pages).reshape(n_seqs, pages))
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(12)
+        idx = IndexerState(pool, n_seqs, ctx)
+        idx.pooled.copy_(torch.randn(idx.pooled.shape, generator=gen, device="cuda"))
+        qi = torch.randn((n_seqs, IDX_N_HEAD, IDX_DIM), generator=gen, device="cuda")
+        q = torch.randn((n_seqs, n_head, HD), generator=gen, device="cuda")
+        out = torch.empty((n_seqs, n_head, HD), device="cuda")
+        pos0 = dev_u32(np.full(n_seqs, ctx - 1))
+
+        def chain():
+            scores = idx.score(qi, pos0, 1, n_blocks)
+            ids, counts = topk_blocks(pool, scores, pos0, 1)
+            sparse_attend(pool, 0, q, n_head, tables, pos0, 1, ids, counts, ctx, out)
+
+        us = timed(chain, iters)
+        us_graph = timed_graph(chain, iters)
+        pool.check()
+        emit(op="qsa_decode_chain", case=f"{n_seqs} sequence(s): idx_score over {n_blocks} pooled keys -> top 512 + own block -> attention over "
+             f"the selected cells, {n_head}q/{N_KV}kv hd{HD}, 1 layer", units=n_seqs, us=us, us_graph=us_graph, iters=iters)
+        pool.release()
+
+
 def bench_movers(iters: int):
     n_layers, n_pages = 12, 4096
     pool = KvPool(0, n_layers, N_KV, HD, n_pages)
@@ -322,7 +357,7 @@ def bench_movers(iters: int):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "prefill", "prepare", "sparse", "topk", "indexer", "movers"])
+    ap.add_argument("--op", default="all", choices=["all", "prefill", "prepare", "sparse", "topk", "indexer", "chain", "movers"])
     ap.add_argument("--iters", type=int, default=20)
     a = ap.parse_args()
     if not torch.cuda.is_available():
@@ -339,6 +374,8 @@ def main():
         bench_topk(a.iters)
     if a.op in ("all", "indexer"):
         bench_indexer(a.iters)
+    if a.op in ("all", "chain"):
+        bench_qsa_chain(a.iters)
     if a.op in ("all", "movers"):
         bench_movers(a.iters)
 
