@@ -255,13 +255,14 @@ __global__ void __launch_bounds__(GROUPS_PER_CTA * NT * 32, 1) sparse_gqa_kernel
     const uint32_t grp = warp / NT, nt = warp % NT;                          // which tile stream, which 8 heads
     const uint32_t row = blockIdx.y, kvh = blockIdx.x / cs;
     const uint32_t s = row / p.rows_per_seq, t = row % p.rows_per_seq;
+    const uint32_t count_listed = p.counts[row];        // asked for together with the position: neither waits for the other
     const uint32_t pos = p.pos0[s] + t;
     const uint32_t group = p.n_head / p.n_kv_head;
     const uint32_t head_base = kvh * group;
     const bool bad_pos = pos >= p.max_pos_end;
     if (bad_pos && tid == 0 && rank == 0) { atomicOr(p.status, BRC_DEV_BAD_POS); p.status[1] = pos; }
 
-    const uint32_t count = bad_pos ? 0u : min(p.counts[row], p.max_ids);
+    const uint32_t count = bad_pos ? 0u : min(count_listed, p.max_ids);
     const uint32_t *ids = p.ids + (size_t)row * p.max_ids;
     const uint32_t *table = p.block_tables + (size_t)s * p.table_stride;
     const uint32_t n_tiles = (count + 3u) / 4u;
@@ -283,8 +284,17 @@ __global__ void __launch_bounds__(GROUPS_PER_CTA * NT * 32, 1) sparse_gqa_kernel
         return table[lp];
     };
     const uint32_t j_first = rank * GROUPS_PER_CTA + warp / NT;
-    uint32_t id_a = fetch_id(j_first), id_b = fetch_id(j_first + stride), id_c = fetch_id(j_first + 2u * stride);
-    uint32_t id_d = fetch_id(j_first + 3u * stride);
+    // The first four tiles' ids are asked for before the row's count has arrived (one load less in the chain in front of
+    // the first tile); what lies beyond the count is dropped below, once both are here.
+    auto id_at = [&](uint32_t j) -> uint32_t {
+        const uint32_t li = j * 4u + ((lane & 15u) >> 2);
+        return li < p.max_ids ? ids[li] : 0xffffffffu;
+    };
+    auto within = [&](uint32_t id, uint32_t j) -> uint32_t {
+        return (j < n_tiles && j * 4u + ((lane & 15u) >> 2) < count) ? id : 0xffffffffu;
+    };
+    uint32_t id_a = id_at(j_first), id_b = id_at(j_first + stride), id_c = id_at(j_first + 2u * stride);
+    uint32_t id_d = id_at(j_first + 3u * stride);
 
     // ---- the query heads of this kv head into shared memory: binary16 head (and tail of an f32 query)
     for (uint32_t i = tid; i < NT * 8 * (HD / 2); i += THREADS) {
@@ -373,6 +383,8 @@ __global__ void __launch_bounds__(GROUPS_PER_CTA * NT * 32, 1) sparse_gqa_kernel
     uint32_t j = j_first, buf = 0;
     uint32_t mask = 0, mask_1 = 0, mask_2 = 0;     // live cells of tile j, j + stride, j + 2 strides
     uint32_t cell_a, cell_b, cell_c;
+    id_a = within(id_a, j_first), id_b = within(id_b, j_first + stride);
+    id_c = within(id_c, j_first + 2u * stride), id_d = within(id_d, j_first + 3u * stride);
     uint32_t page_a = fetch_page(id_a, cell_a), page_b = fetch_page(id_b, cell_b), page_c = fetch_page(id_c, cell_c);
     if (j < n_tiles) mask = gather(page_a, cell_a, 0);
     cp_async_commit();
