@@ -125,7 +125,7 @@ constexpr uint32_t SC_THREADS = 256;
 constexpr uint32_t SC_BLOCKS_PER_CTA = 128;   // blocks one CTA scores: 4 steps of its 8 warps x 4 blocks (small CTAs: a short tail)
 
 // grid = (ceil(n_blocks / SC_BLOCKS_PER_CTA), rows).
-__global__ void __launch_bounds__(SC_THREADS) idx_score_kernel(const ScoreParams p) {
+__global__ void __launch_bounds__(SC_THREADS, 4) idx_score_kernel(const ScoreParams p) {
     __shared__ float4 s_q[IDX_HEAD_MAX * IDX_DIM / 4];
     const uint32_t row = blockIdx.y, tid = threadIdx.x;
     const uint32_t s = row / p.rows_per_seq, t = row % p.rows_per_seq;
