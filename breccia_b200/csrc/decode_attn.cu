@@ -56,9 +56,11 @@
 
 namespace {
 
-// Consumer warps: 4 keep up with HBM on binary16 V (one per scheduler); the q8_0 V path issues about three times
-// the instructions per page (the quanta are converted in registers), so it runs 6 to hide their latency.
-__host__ __device__ constexpr int consumer_warps(bool v_q8) { return v_q8 ? 6 : 4; }
+// Consumer warps: 4 keep up with HBM on binary16 V at head_dim 256 (one per scheduler); the q8_0 V path issues about
+// three times the instructions per page (the quanta are converted in registers), and at head_dim 128 a page brings half
+// the bytes for the same softmax round and ring hand-over, so those run 6 to hide the latency of what they issue
+// (q8_0 V: +20 % against 4 warps; head_dim 128: +1 %, 5.0 -> 5.3 TB/s is what its page-sized stages allow).
+__host__ __device__ constexpr int consumer_warps(bool v_q8, int head_dim) { return v_q8 || head_dim == 128 ? 6 : 4; }
 constexpr int MAX_UNITS = 2048;            // (sequence, kv-head group) units per launch
 constexpr int MAX_CTAS = 256;              // CTAs of a launch (one per SM)
 constexpr int GROUP_TILE = 8;              // query heads per kv head held by one n-tile
@@ -68,7 +70,7 @@ constexpr float Q8_P_SCALE = 128.f;          // see the q8_0 V path of the kerne
 
 template <int HD, int KVB, bool VQ8 = false>
 struct Cfg {
-    static constexpr int NW = consumer_warps(VQ8);
+    static constexpr int NW = consumer_warps(VQ8, HD);
     static constexpr int NTHREADS = (NW + 1) * 32;         // + one producer warp
     static constexpr int KSTEPS = HD / 16;
     static constexpr int MT = HD / 16;
@@ -438,7 +440,7 @@ template <int HD, int KVB, bool CAN_PUSH, bool VQ8>
 __device__ __forceinline__ void merge_unit(const DecodeParams &p, const UnitRef ur, uint32_t i_lo, uint32_t i_hi, const uint32_t *B,
                                            bool dense, uint32_t tid, float *sm, float4 *stage, uint32_t epoch, uint32_t bank,
                                            volatile uint32_t *gave_up, bool all_written) {
-    constexpr int NW = consumer_warps(VQ8);
+    constexpr int NW = consumer_warps(VQ8, HD);
     constexpr uint32_t NT = NW * 32;
     constexpr uint32_t TPR = HD / 4;                    // 16-byte columns of a row
     const uint32_t n_rows = KVB * p.group;              // (kv head of the unit, query head)
@@ -499,7 +501,7 @@ __device__ __forceinline__ void merge_unit(const DecodeParams &p, const UnitRef 
 template <int HD, int KVB, bool VQ8>
 __device__ __forceinline__ void finalize_unit(const DecodeParams &p, const UnitRef ur, uint32_t row_first, uint32_t row_step,
                                               uint32_t bank, uint32_t tid, volatile uint32_t *gave_up) {
-    constexpr int NW = consumer_warps(VQ8);
+    constexpr int NW = consumer_warps(VQ8, HD);
     constexpr uint32_t TPR = HD / 4;
     constexpr uint32_t ROWS_PER_PASS = (NW * 32) / TPR;
     const uint32_t n_rows = KVB * p.group;
@@ -599,7 +601,7 @@ __device__ __forceinline__ void finalize_unit(const DecodeParams &p, const UnitR
 // into the probabilities of that block, split into a binary16 head and tail as before - so the result
 // carries the same ~22 significant bits as the binary16 path.
 template <int HD, bool Q_F32, int KVB, bool WHOLE_FAST, bool VQ8>
-__global__ void __launch_bounds__((consumer_warps(VQ8) + 1) * 32, 1)
+__global__ void __launch_bounds__((consumer_warps(VQ8, HD) + 1) * 32, 1)
     decode_partial_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_v8, const DecodeParams p) {
     using C = Cfg<HD, KVB, VQ8>;
     constexpr int NW = C::NW;
@@ -1430,7 +1432,7 @@ uint32_t fixed_bytes_of(uint32_t head_dim, bool v_q8) {   // independent of KVB
 // it back a second time.
 uint32_t stages_for(uint32_t head_dim, uint32_t kvb, bool v_q8) {
     const uint32_t fit = std::min<uint32_t>((SMEM_LIMIT - fixed_bytes_of(head_dim, v_q8)) / stage_bytes_of(head_dim, kvb, v_q8), 24u);
-    const uint32_t nwp = (uint32_t)consumer_warps(v_q8) / kvb;
+    const uint32_t nwp = (uint32_t)consumer_warps(v_q8, (int)head_dim) / kvb;
     return fit / nwp * nwp;
 }
 
