@@ -59,7 +59,7 @@ namespace {
 // Consumer warps: 4 keep up with HBM on binary16 V at head_dim 256 (one per scheduler); the q8_0 V path issues about
 // three times the instructions per page (the quanta are converted in registers), and at head_dim 128 a page brings half
 // the bytes for the same softmax round and ring hand-over, so those run 6 to hide the latency of what they issue
-// (q8_0 V: +20 % against 4 warps; head_dim 128: +1 %, 5.0 -> 5.3 TB/s is what its page-sized stages allow).
+// (head_dim 128: +1 % measured; 5.0 - 5.3 TB/s is what its page-sized stages allow).
 __host__ __device__ constexpr int consumer_warps(bool v_q8, int head_dim) { return v_q8 || head_dim == 128 ? 6 : 4; }
 constexpr int MAX_UNITS = 2048;            // (sequence, kv-head group) units per launch
 constexpr int MAX_CTAS = 256;              // CTAs of a launch (one per SM)
