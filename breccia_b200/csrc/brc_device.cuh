@@ -138,6 +138,16 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap
         : "memory");
 }
 
+// Four coordinates, innermost first.  c0 * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const CUtensorMap *tm, int32_t c0, int32_t c1, int32_t c2, int32_t c3,
+                                            uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%2, %3, %4, %5}], [%6], %7;" ::"r"(dst_smem),
+        "l"(reinterpret_cast<uint64_t>(tm)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar), "l"(policy)
+        : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // warp-level matrix helpers
 // ---------------------------------------------------------------------------------------------

@@ -58,6 +58,11 @@ struct brc_pool {
     // tile of one page of one kv head.
     alignas(64) CUtensorMap tm_kv;
     alignas(64) CUtensorMap tm_kv2;  // same view, box of 2 * page_tokens rows (two kv heads); even n_kv_head only
+    // 4-D views (column in a 64-column group, row, K|V, group): one box brings a whole page-unit, every column
+    // group of its K and V rows, in ONE operation; stage_maps says whether the driver accepted them
+    alignas(64) CUtensorMap tm_kv_stage;
+    alignas(64) CUtensorMap tm_kv2_stage;
+    bool stage_maps = false;
     // q8_0 V pools: K alone as [rows][head_dim] f16 with a box of 2 * page_tokens rows (tm_k is the one-kv-head
     // box), and the V rows as [rows][head_dim / 32 * 9] 32-bit words (288 B at head_dim 256), unswizzled,
     // boxes of page_tokens and of 2 * page_tokens whole rows

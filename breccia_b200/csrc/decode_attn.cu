@@ -11,11 +11,14 @@
 //     all units form one flat list of "page-units", cut into contiguous shares of equal cost, one per CTA
 //     (one CTA per SM; cost = pages plus a surcharge per unit touched), so every SM is busy for the same
 //     time whatever the length distribution;
-//   * a producer warp walks the block table and issues, per page-unit, one TMA tiled load per
-//     64-column group: a 3-D box [64 columns][16 KVB rows][K|V] over a view that spans the K and the
-//     V pool (128-byte swizzle), 8 KiB per operation at KVB = 2.  Measured on B200, a TMA operation
-//     costs >= ~215 SM cycles whatever its size, so 4 KiB operations cap a SM at ~19 B/cycle while
-//     8 KiB operations reach the HBM limit (~26 B/cycle/SM); this is why two kv heads share a box.
+//   * a producer warp walks the block table and issues, per page-unit, ONE TMA tiled load: a 4-D box
+//     [64 columns][16 KVB rows][K|V][head_dim / 64 column groups] over a view that spans the K and the V
+//     pool (128-byte swizzle; the group dimension's stride, 128 bytes, lies inside the row), 32 KiB per
+//     operation at head_dim 256 and KVB = 2.  Measured on B200, a TMA operation costs >= ~215 SM cycles
+//     whatever its size, so 4 KiB operations cap a SM at ~19 B/cycle while 8 KiB operations reach the HBM
+//     limit (~26 B/cycle/SM); this is why two kv heads share a box.  (Where the driver refuses the 4-D
+//     view the same stage comes as one 3-D box [64][16 KVB][K|V] per column group; against those the
+//     single operation is 0.5 % faster on the 32-sequence batch, 15 % with one kv head per unit.)
 //     Stages of a shared-memory ring are guarded by full/empty mbarriers;
 //   * four consumer warps: warp w serves kv head (w % KVB) of every (w / KVB)-th page-unit.  Per page:
 //     S^T[16 cells x 8 heads] = K . Q^T with mma.sync m16n8k16 (K fragments by ldmatrix from the
@@ -142,6 +145,7 @@ struct DecodeParams {
     uint64_t wait_ns;
     uint32_t unit_cost;            // page-units charged per unit with pages when the list is cut into shares
     const uint32_t *cut_prefix;    // nullable: [CTAs] where CTA i's share begins, as a fraction of the launch's cost x 2^32
+    uint32_t one_op;               // binary16 V: the second tensor map is the 4-D view that brings a whole stage in one operation
 };
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
@@ -640,7 +644,7 @@ __global__ void __launch_bounds__((consumer_warps(VQ8, HD) + 1) * 32, 1)
         }
         brc::mbar_fence_init();
         brc::tma_prefetch_desc(&tm_kv);
-        if (VQ8) brc::tma_prefetch_desc(&tm_v8);
+        if (VQ8 || p.one_op) brc::tma_prefetch_desc(&tm_v8);
         dead_cta[0] = 0u;
         gave_up[0] = 0u;
     }
@@ -877,7 +881,10 @@ __global__ void __launch_bounds__((consumer_warps(VQ8, HD) + 1) * 32, 1)
                 // Shared memory: [group][K|V][row = kv head * 16 + cell][64 columns], 128-byte swizzled; with q8_0 V the
                 // K slabs of all groups, then one more operation for the page's V rows (whole rows, unswizzled).
                 if (!VQ8) {
-                    if (lane < C::BOXES)
+                    if (p.one_op) {
+                        if (lane == 0)
+                            brc::tma_load_4d(brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES), &tm_v8, 0, (int32_t)r, 0, 0, fb, policy);
+                    } else if (lane < C::BOXES)
                         brc::tma_load_3d(brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES) + lane * C::GROUP_BYTES, &tm_kv,
                                          (int32_t)(lane * 64u), (int32_t)r, 0, fb, policy);
                 } else {
@@ -1533,6 +1540,16 @@ uint32_t seqs_per_launch(const brc_pool *pool) { return MAX_UNITS / (pool->n_kv_
 
 uint32_t grid_ctas(const brc_pool *pool) { return std::min<uint32_t>((uint32_t)(pool->sm_count > 0 ? pool->sm_count : 148), MAX_CTAS); }
 
+// One TMA operation per page-unit (the pool's 4-D view) instead of one per 64-column group; BRC_DECODE_STAGE_OP=0 in
+// the environment keeps the 3-D boxes.
+bool stage_in_one_operation() {
+    static const bool on = [] {
+        const char *e = std::getenv("BRC_DECODE_STAGE_OP");
+        return !(e && *e == '0');
+    }();
+    return on;
+}
+
 // What every unit it touches costs a CTA on top of the unit's pages (merge of the warps, partial or output
 // written, ticket, perhaps the unit's merge), in page-units of this pool.  Measured on the 32-sequence batches
 // of skewed and of equal lengths: an isolated launch gets faster up to about 16 page-units of 32 KiB (64 -> 60 us
@@ -1573,7 +1590,7 @@ brc_status launch_partial(brc_pool *pool, const DecodeParams &p, uint32_t grid, 
     auto kern = many_units ? decode_partial_kernel<HD, Q_F32, KVB, true, VQ8> : decode_partial_kernel<HD, Q_F32, KVB, false, VQ8>;
     // binary16 V: one 3-D view over K and V.  q8_0 V: K alone, and the V rows in 32-bit words.
     const CUtensorMap &tm_a = VQ8 ? (KVB == 2 ? pool->tm_k2 : pool->tm_k) : (KVB == 2 ? pool->tm_kv2 : pool->tm_kv);
-    const CUtensorMap &tm_b = VQ8 ? (KVB == 2 ? pool->tm_v8_2 : pool->tm_v8) : tm_a;
+    const CUtensorMap &tm_b = VQ8 ? (KVB == 2 ? pool->tm_v8_2 : pool->tm_v8) : p.one_op ? (KVB == 2 ? pool->tm_kv2_stage : pool->tm_kv_stage) : tm_a;
     brc_stage_begin(pool, BRC_STAGE_ATTN_PARTIAL, st);
     // Cooperative: the CTAs of a unit wait for one another's shares at the end of the launch, so all of them must be
     // resident at once (one per SM; the launch fails instead of starting when the device cannot hold the grid).
@@ -1759,6 +1776,7 @@ brc_status brc_decode_layers(brc_pool *pool, const char *who, const brc_layers_a
             p.scale_log2 = a.scale * 1.4426950408889634f;
             p.n_layers = nl;
             p.unit_cost = unit_cost_of(hd, kvb, pool->v_q8);
+            p.one_op = (!pool->v_q8 && pool->stage_maps && stage_in_one_operation()) ? 1u : 0u;
             p.cut_prefix = grid == grid_ctas(pool) ? pool->cut_prefix : nullptr;
             p.q_layer_stride = a.q_layer_stride_bytes / q_elem;
             p.out_layer_stride = a.out_layer_stride_bytes / 4;

@@ -144,6 +144,23 @@ static brc_status make_kv_map(CUtensorMap *tm, void *k_base, uint64_t v_offset_b
     return BRC_OK;
 }
 
+// 4-D view (column within a 64-column group, row, K|V, column group): the strides do not ascend (a group lies
+// 128 bytes after the one before, inside the row), which lets one box [64][rows][2][head_dim / 64] deliver a
+// whole page-unit - laid out in shared memory as [group][K|V][row][64 columns], the order the decode kernel's
+// stages have - in a single operation of 16 or 32 KiB.  Not fatal when the driver refuses the encoding: the
+// kernel then issues one 3-D box per column group.
+static bool make_kv_stage_map(CUtensorMap *tm, void *k_base, uint64_t v_offset_bytes, uint64_t rows, uint32_t head_dim,
+                              uint32_t box_rows) {
+    encode_tiled_fn enc = get_encode_tiled();
+    if (!enc) return false;
+    cuuint64_t dims[4] = {64u, rows, 2u, head_dim / 64u};
+    cuuint64_t strides[3] = {(cuuint64_t)head_dim * 2u, v_offset_bytes, 128u};
+    cuuint32_t box[4] = {64u, box_rows, 2u, head_dim / 64u};
+    cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    return enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, k_base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 static brc_status create_pool(int32_t device, uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim,
                               uint32_t page_tokens, uint32_t n_pages, bool v_q8, brc_pool **out) {
     if (!out) return brc_fail(BRC_ERR_INVALID, "brc_pool_create: out is NULL");
@@ -208,6 +225,10 @@ static brc_status create_pool(int32_t device, uint32_t n_layers, uint32_t n_kv_h
     // a box of 2 * page_tokens rows brings both (8 KiB per operation instead of 4 KiB).
     if (rc == BRC_OK && !v_q8 && n_kv_head % 2u == 0u)
         rc = make_kv_map(&p->tm_kv2, p->k_base, bytes, rows, head_dim, 2u * page_tokens);
+    if (rc == BRC_OK && !v_q8) {
+        p->stage_maps = make_kv_stage_map(&p->tm_kv_stage, p->k_base, bytes, rows, head_dim, page_tokens) &&
+                        (n_kv_head % 2u != 0u || make_kv_stage_map(&p->tm_kv2_stage, p->k_base, bytes, rows, head_dim, 2u * page_tokens));
+    }
     if (rc == BRC_OK && v_q8) {
         const uint32_t row_words = head_dim / 32u * 9u;
         rc = make_q8_map(&p->tm_v8, p->v_base, rows, row_words, page_tokens);
