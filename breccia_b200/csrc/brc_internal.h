@@ -62,6 +62,8 @@ struct brc_pool {
     // group of its K and V rows, in ONE operation; stage_maps says whether the driver accepted them
     alignas(64) CUtensorMap tm_kv_stage;
     alignas(64) CUtensorMap tm_kv2_stage;
+    alignas(64) CUtensorMap tm_k_stage;    // q8_0 V pools: 3-D view of K alone (column, row, group), all K slabs of a page-unit in one box
+    alignas(64) CUtensorMap tm_k2_stage;
     bool stage_maps = false;
     // q8_0 V pools: K alone as [rows][head_dim] f16 with a box of 2 * page_tokens rows (tm_k is the one-kv-head
     // box), and the V rows as [rows][head_dim / 32 * 9] 32-bit words (288 B at head_dim 256), unswizzled,

@@ -145,7 +145,8 @@ struct DecodeParams {
     uint64_t wait_ns;
     uint32_t unit_cost;            // page-units charged per unit with pages when the list is cut into shares
     const uint32_t *cut_prefix;    // nullable: [CTAs] where CTA i's share begins, as a fraction of the launch's cost x 2^32
-    uint32_t one_op;               // binary16 V: the second tensor map is the 4-D view that brings a whole stage in one operation
+    uint32_t one_op;               // binary16 V: the second tensor map is the 4-D view that brings a whole stage in one operation;
+                                   // q8_0 V: the first one is the 3-D view of K that brings all K slabs in one
 };
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
@@ -887,6 +888,11 @@ __global__ void __launch_bounds__((consumer_warps(VQ8, HD) + 1) * 32, 1)
                     } else if (lane < C::BOXES)
                         brc::tma_load_3d(brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES) + lane * C::GROUP_BYTES, &tm_kv,
                                          (int32_t)(lane * 64u), (int32_t)r, 0, fb, policy);
+                } else if (p.one_op) {   // the K slabs of all column groups in one box (3-D view of K), then the V rows
+                    if (lane == 0)
+                        brc::tma_load_3d(brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES), &tm_kv, 0, (int32_t)r, 0, fb, policy);
+                    else if (lane == 1)
+                        brc::tma_load_2d(brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES) + C::V_OFF, &tm_v8, 0, (int32_t)r, fb, policy);
                 } else {
                     if (lane < C::BOXES)
                         brc::tma_load_2d(brc::smem_u32(ring + (size_t)stage * C::STAGE_BYTES) + lane * C::GROUP_BYTES, &tm_kv,
@@ -1589,7 +1595,8 @@ brc_status launch_partial(brc_pool *pool, const DecodeParams &p, uint32_t grid, 
     const bool many_units = p.world <= 1 && (uint64_t)p.n_layers * p.n_seqs * (p.n_kv_head / KVB) >= grid;
     auto kern = many_units ? decode_partial_kernel<HD, Q_F32, KVB, true, VQ8> : decode_partial_kernel<HD, Q_F32, KVB, false, VQ8>;
     // binary16 V: one 3-D view over K and V.  q8_0 V: K alone, and the V rows in 32-bit words.
-    const CUtensorMap &tm_a = VQ8 ? (KVB == 2 ? pool->tm_k2 : pool->tm_k) : (KVB == 2 ? pool->tm_kv2 : pool->tm_kv);
+    const CUtensorMap &tm_a = VQ8 ? (p.one_op ? (KVB == 2 ? pool->tm_k2_stage : pool->tm_k_stage) : (KVB == 2 ? pool->tm_k2 : pool->tm_k))
+                                  : (KVB == 2 ? pool->tm_kv2 : pool->tm_kv);
     const CUtensorMap &tm_b = VQ8 ? (KVB == 2 ? pool->tm_v8_2 : pool->tm_v8) : p.one_op ? (KVB == 2 ? pool->tm_kv2_stage : pool->tm_kv_stage) : tm_a;
     brc_stage_begin(pool, BRC_STAGE_ATTN_PARTIAL, st);
     // Cooperative: the CTAs of a unit wait for one another's shares at the end of the launch, so all of them must be
@@ -1776,7 +1783,7 @@ brc_status brc_decode_layers(brc_pool *pool, const char *who, const brc_layers_a
             p.scale_log2 = a.scale * 1.4426950408889634f;
             p.n_layers = nl;
             p.unit_cost = unit_cost_of(hd, kvb, pool->v_q8);
-            p.one_op = (!pool->v_q8 && pool->stage_maps && stage_in_one_operation()) ? 1u : 0u;
+            p.one_op = (pool->stage_maps && stage_in_one_operation()) ? 1u : 0u;
             p.cut_prefix = grid == grid_ctas(pool) ? pool->cut_prefix : nullptr;
             p.q_layer_stride = a.q_layer_stride_bytes / q_elem;
             p.out_layer_stride = a.out_layer_stride_bytes / 4;

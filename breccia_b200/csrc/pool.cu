@@ -161,6 +161,18 @@ static bool make_kv_stage_map(CUtensorMap *tm, void *k_base, uint64_t v_offset_b
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The same for K alone (pools with q8_0 V pages): (column within a group, row, group), one box per page-unit.
+static bool make_k_stage_map(CUtensorMap *tm, void *k_base, uint64_t rows, uint32_t head_dim, uint32_t box_rows) {
+    encode_tiled_fn enc = get_encode_tiled();
+    if (!enc) return false;
+    cuuint64_t dims[3] = {64u, rows, head_dim / 64u};
+    cuuint64_t strides[2] = {(cuuint64_t)head_dim * 2u, 128u};
+    cuuint32_t box[3] = {64u, box_rows, head_dim / 64u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    return enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, k_base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 static brc_status create_pool(int32_t device, uint32_t n_layers, uint32_t n_kv_head, uint32_t head_dim,
                               uint32_t page_tokens, uint32_t n_pages, bool v_q8, brc_pool **out) {
     if (!out) return brc_fail(BRC_ERR_INVALID, "brc_pool_create: out is NULL");
@@ -234,6 +246,9 @@ static brc_status create_pool(int32_t device, uint32_t n_layers, uint32_t n_kv_h
         rc = make_q8_map(&p->tm_v8, p->v_base, rows, row_words, page_tokens);
         if (rc == BRC_OK && n_kv_head % 2u == 0u) rc = make_map(&p->tm_k2, p->k_base, rows, head_dim, 2u * page_tokens);
         if (rc == BRC_OK && n_kv_head % 2u == 0u) rc = make_q8_map(&p->tm_v8_2, p->v_base, rows, row_words, 2u * page_tokens);
+        if (rc == BRC_OK)
+            p->stage_maps = make_k_stage_map(&p->tm_k_stage, p->k_base, rows, head_dim, page_tokens) &&
+                            (n_kv_head % 2u != 0u || make_k_stage_map(&p->tm_k2_stage, p->k_base, rows, head_dim, 2u * page_tokens));
     }
     if (rc != BRC_OK) {
         brc_pool_destroy(p);
