@@ -59,7 +59,8 @@ struct brc_pool {
     alignas(64) CUtensorMap tm_kv;
     alignas(64) CUtensorMap tm_kv2;  // same view, box of 2 * page_tokens rows (two kv heads); even n_kv_head only
     // 4-D views (column in a 64-column group, row, K|V, group): one box brings a whole page-unit, every column
-    // group of its K and V rows, in ONE operation; stage_maps says whether the driver accepted them
+    // group of its K and V rows, in ONE operation (opt-in: BRC_DECODE_STAGE_OP=1); stage_maps says whether the driver
+    // accepted them
     alignas(64) CUtensorMap tm_kv_stage;
     alignas(64) CUtensorMap tm_kv2_stage;
     alignas(64) CUtensorMap tm_k_stage;    // q8_0 V pools: 3-D view of K alone (column, row, group), all K slabs of a page-unit in one box

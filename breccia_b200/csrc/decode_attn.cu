@@ -11,14 +11,12 @@
 //     all units form one flat list of "page-units", cut into contiguous shares of equal cost, one per CTA
 //     (one CTA per SM; cost = pages plus a surcharge per unit touched), so every SM is busy for the same
 //     time whatever the length distribution;
-//   * a producer warp walks the block table and issues, per page-unit, ONE TMA tiled load: a 4-D box
-//     [64 columns][16 KVB rows][K|V][head_dim / 64 column groups] over a view that spans the K and the V
-//     pool (128-byte swizzle; the group dimension's stride, 128 bytes, lies inside the row), 32 KiB per
-//     operation at head_dim 256 and KVB = 2.  Measured on B200, a TMA operation costs >= ~215 SM cycles
-//     whatever its size, so 4 KiB operations cap a SM at ~19 B/cycle while 8 KiB operations reach the HBM
-//     limit (~26 B/cycle/SM); this is why two kv heads share a box.  (Where the driver refuses the 4-D
-//     view the same stage comes as one 3-D box [64][16 KVB][K|V] per column group; against those the
-//     single operation is 0.5 % faster on the 32-sequence batch, 15 % with one kv head per unit.)
+//   * a producer warp walks the block table and issues, per page-unit, one TMA tiled load per
+//     64-column group: a 3-D box [64 columns][16 KVB rows][K|V] over a view that spans the K and the
+//     V pool (128-byte swizzle), 8 KiB per operation at KVB = 2.  Measured on B200, a TMA operation
+//     costs >= ~215 SM cycles whatever its size, so 4 KiB operations cap a SM at ~19 B/cycle while
+//     8 KiB operations reach the HBM limit (~26 B/cycle/SM); this is why two kv heads share a box.
+//     (Opt-in, see stage_in_one_operation(): one 4-D box [64][16 KVB][K|V][column groups] per page-unit.)
 //     Stages of a shared-memory ring are guarded by full/empty mbarriers;
 //   * four consumer warps: warp w serves kv head (w % KVB) of every (w / KVB)-th page-unit.  Per page:
 //     S^T[16 cells x 8 heads] = K . Q^T with mma.sync m16n8k16 (K fragments by ldmatrix from the
@@ -1546,12 +1544,17 @@ uint32_t seqs_per_launch(const brc_pool *pool) { return MAX_UNITS / (pool->n_kv_
 
 uint32_t grid_ctas(const brc_pool *pool) { return std::min<uint32_t>((uint32_t)(pool->sm_count > 0 ? pool->sm_count : 148), MAX_CTAS); }
 
-// One TMA operation per page-unit (the pool's 4-D view) instead of one per 64-column group; BRC_DECODE_STAGE_OP=0 in
-// the environment keeps the 3-D boxes.
+// One TMA operation per page-unit (the pool's views whose last dimension is the 64-column group) instead of one per
+// column group.  OFF unless BRC_DECODE_STAGE_OP=1 is in the environment: in those views the group's stride (128 bytes)
+// follows a larger one, which the driver's encoder accepts but its documentation does not allow (every stride a
+// multiple of the one before).  Measured here over some tens of thousands of launches without a fault and with
+// identical results - 0.5 % on the 32-sequence batch, 9 % over q8_0 V pages (67.4 k -> 73.6 k tok/s), 15 % with one kv
+// head per unit - but an earlier build with such a view saw bounded waits give up now and then, so the default
+// stays inside the documented rules.
 bool stage_in_one_operation() {
     static const bool on = [] {
         const char *e = std::getenv("BRC_DECODE_STAGE_OP");
-        return !(e && *e == '0');
+        return e && *e == '1';
     }();
     return on;
 }

@@ -147,8 +147,9 @@ static brc_status make_kv_map(CUtensorMap *tm, void *k_base, uint64_t v_offset_b
 // 4-D view (column within a 64-column group, row, K|V, column group): the strides do not ascend (a group lies
 // 128 bytes after the one before, inside the row), which lets one box [64][rows][2][head_dim / 64] deliver a
 // whole page-unit - laid out in shared memory as [group][K|V][row][64 columns], the order the decode kernel's
-// stages have - in a single operation of 16 or 32 KiB.  Not fatal when the driver refuses the encoding: the
-// kernel then issues one 3-D box per column group.
+// stages have - in a single operation of 16 or 32 KiB.  The encoder accepts it although its documentation asks
+// for every stride to be a multiple of the one before; the decode kernel therefore uses these views only when
+// asked to (BRC_DECODE_STAGE_OP=1) and otherwise issues one 3-D box per column group.
 static bool make_kv_stage_map(CUtensorMap *tm, void *k_base, uint64_t v_offset_bytes, uint64_t rows, uint32_t head_dim,
                               uint32_t box_rows) {
     encode_tiled_fn enc = get_encode_tiled();
