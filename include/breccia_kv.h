@@ -242,7 +242,15 @@ BRC_API brc_status brc_seq_fork(brc_pool *pool, const uint32_t *parent_table, ui
  * the f32 output then depend on the measurement - off by default).
  * brc_decode_share_rates reports what is in force: *out_n = the number of
  * CTAs and rates[i] = CTA i's share relative to the mean, or *out_n = 0 for
- * equal shares (no counterpart in the reference). */
+ * equal shares (no counterpart in the reference).
+ *
+ * Two more environment switches, read once per process: BRC_DECODE_UNIT_COST=n
+ * (page-units charged per unit when a launch's work is cut into shares; the
+ * default is 512 KiB worth) and BRC_DECODE_STAGE_OP=1 (one TMA operation per
+ * page-unit through tensor-map views whose strides do not ascend: measured
+ * faster - 0.5 % on batches, 9 % on q8_0 V pools - but outside what the
+ * driver's documentation allows for a tensor map, hence off by default).
+ * Results do not depend on either. */
 BRC_API brc_status brc_decode_share_rates(const brc_pool *pool, float *rates, uint32_t capacity, uint32_t *out_n);
 BRC_API brc_status brc_decode_workspace_bytes(const brc_pool *pool, uint32_t n_seqs, uint32_t n_head,
                                               uint64_t *out_bytes);
