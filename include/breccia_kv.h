@@ -250,7 +250,8 @@ BRC_API brc_status brc_seq_fork(brc_pool *pool, const uint32_t *parent_table, ui
  * page-unit through tensor-map views whose strides do not ascend: measured
  * faster - 0.5 % on batches, 9 % on q8_0 V pools - but outside what the
  * driver's documentation allows for a tensor map, hence off by default).
- * Results do not depend on either. */
+ * The second does not change a result; the first moves the share boundaries
+ * and with them the order of the f32 sums (last bits). */
 BRC_API brc_status brc_decode_share_rates(const brc_pool *pool, float *rates, uint32_t capacity, uint32_t *out_n);
 BRC_API brc_status brc_decode_workspace_bytes(const brc_pool *pool, uint32_t n_seqs, uint32_t n_head,
                                               uint64_t *out_bytes);
