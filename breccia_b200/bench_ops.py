@@ -2,9 +2,12 @@
 --op qsa`, crates/breccia-kernels/src/qsa/bench.rs; one JSON line per cell with the fields of its
 `OpCell`: op, case, units, bytes or flops, us, GB/s or TFLOP/s, iters).
 
-    python -m breccia_b200.bench_ops [--op prefill|prepare|sparse|topk|indexer|movers|all] [--iters N]
+    python -m breccia_b200.bench_ops [--op prefill|prepare|sparse|topk|indexer|chain|movers|all] [--iters N]
 
-Timing: CUDA events on the launching stream, 3 warm-up runs, the mean of `iters` runs.  Shapes are the
+Timing: CUDA events on the launching stream, 3 warm-up runs, the mean of `iters` runs (`us`).  Calls of a few
+tens of microseconds are also replayed from a CUDA graph (`us_graph`): back to back from Python such a call
+measures the host's cost of issuing it, the replay the device's time; GB/s and TFLOP/s of those lines are
+computed from `us_graph`.  `chain` = block scores -> top-k -> selected-block attention in a row.  Shapes are the
 benchmark configurations: prefill = 64 sequences sharing a 4096-token prefix, 256-token chunk each
 (GQA 16q/2kv, head_dim 256); the byte movers run on the same pool.
 """
